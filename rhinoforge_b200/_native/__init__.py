@@ -1,0 +1,115 @@
+"""ctypes binding of ``librf_b200.so`` (the sm_100a kernel + runtime library).
+
+The library is built in-tree by :mod:`rhinoforge_b200.csrc.build` and loaded
+lazily: importing the package never touches it, host-only code paths
+(planners, registries) work without it, and anything that needs a kernel
+raises :class:`NativeLibraryError` if it is missing instead of silently
+falling back to PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "librf_b200.so"
+
+_lock = threading.Lock()
+_lib: C.CDLL | None = None
+
+
+class NativeLibraryError(RuntimeError):
+    """librf_b200.so is missing or a native call failed."""
+
+
+class RfGemm(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("ldx", C.c_int64),
+        ("w", C.c_void_p), ("ldw", C.c_int64),
+        ("out", C.c_void_p), ("ldo", C.c_int64),
+        ("residual", C.c_void_p), ("ldr", C.c_int64),
+        ("bias", C.c_void_p), ("scale", C.c_void_p), ("row_scale", C.c_void_p),
+        ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
+        ("dtype", C.c_int32), ("act", C.c_int32), ("dual_offset", C.c_int32), ("w_int8", C.c_int32),
+        ("ws", C.c_void_p), ("ws_bytes", C.c_uint64),
+        ("sem", C.c_void_p), ("sem_count", C.c_int32),
+        ("status", C.c_void_p),
+        ("ar_world", C.c_int32), ("ar_rank", C.c_int32),
+        ("ar_recv", C.c_void_p), ("ar_flags", C.c_void_p), ("ar_state", C.c_void_p),
+        ("ar_recv_bytes", C.c_uint64), ("ar_flag_count", C.c_int32),
+        ("force_splits", C.c_int32), ("force_swap", C.c_int32), ("force_bn", C.c_int32),
+    ]
+
+
+class RfRopeKv(C.Structure):
+    _fields_ = [
+        ("qkv", C.c_void_p), ("ld", C.c_int64),
+        ("q_out", C.c_void_p), ("ldq", C.c_int64),
+        ("tokens", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("hd", C.c_int32), ("rot_dim", C.c_int32),
+        ("q_norm_w", C.c_void_p), ("k_norm_w", C.c_void_p),
+        ("eps", C.c_float), ("norm_mode", C.c_int32),
+        ("cos", C.c_void_p), ("sin", C.c_void_p),
+        ("pos", C.c_void_p), ("pos_stride", C.c_int32),
+        ("axis_of_freq", C.c_void_p),
+        ("k_pool", C.c_void_p), ("v_pool", C.c_void_p),
+        ("page_table", C.c_void_p), ("pt_stride", C.c_int32),
+        ("seq_of_tok", C.c_void_p), ("cache_pos", C.c_void_p),
+        ("rope_before_norm", C.c_int32), ("write_k_inplace", C.c_int32), ("dtype", C.c_int32),
+    ]
+
+
+class RfAttn(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("ldq", C.c_int64),
+        ("out", C.c_void_p), ("ldo", C.c_int64),
+        ("q_rows_total", C.c_int64),
+        ("k_pool", C.c_void_p), ("v_pool", C.c_void_p), ("pool_pages", C.c_int64),
+        ("page_table", C.c_void_p), ("pt_stride", C.c_int32),
+        ("k", C.c_void_p), ("v", C.c_void_p), ("ldk", C.c_int64), ("ldv", C.c_int64), ("kv_rows_total", C.c_int64),
+        ("num_seqs", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("hd", C.c_int32),
+        ("q_start", C.c_void_p), ("q_len", C.c_void_p), ("kv_start", C.c_void_p), ("kv_len", C.c_void_p),
+        ("max_q_len", C.c_int32), ("max_kv_len", C.c_int32),
+        ("causal", C.c_int32), ("window", C.c_int32),
+        ("mask", C.c_void_p), ("mask_ld", C.c_int64), ("mask_seq_stride", C.c_int64),
+        ("seg_q", C.c_void_p), ("seg_k", C.c_void_p),
+        ("scale", C.c_float),
+        ("ws", C.c_void_p), ("ws_bytes", C.c_uint64),
+        ("status", C.c_void_p), ("dtype", C.c_int32),
+    ]
+
+
+def available() -> bool:
+    return LIB_PATH.exists()
+
+
+def lib() -> C.CDLL:
+    """Return the loaded library, building it first when nvcc is present."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not LIB_PATH.exists():
+            if os.environ.get("RF_B200_NO_BUILD") == "1":
+                raise NativeLibraryError(f"{LIB_PATH} not found and RF_B200_NO_BUILD=1")
+            try:
+                from ..csrc.build import build
+                build()
+            except Exception as e:  # noqa: BLE001
+                raise NativeLibraryError(f"{LIB_PATH} not found and building it failed: {e}") from e
+        l = C.CDLL(str(LIB_PATH))
+        l.rf_last_error.restype = C.c_char_p
+        l.rf_argmax_scratch_bytes.restype = C.c_uint64
+        l.rf_attn_decode_scratch_bytes.restype = C.c_uint64
+        _lib = l
+    return _lib
+
+
+def check(rc: int, what: str = "native call") -> None:
+    if rc != 0:
+        msg = lib().rf_last_error().decode(errors="replace")
+        from ..api.errors import RPUBackendError
+        raise RPUBackendError(f"{what} failed ({rc}): {msg}")

@@ -1,0 +1,101 @@
+// 16-bit float helpers shared by the kernels (fp16 and bf16 instantiations).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace rf {
+
+enum DType : int32_t { kF16 = 0, kBF16 = 1, kF32 = 2, kI8 = 3 };
+
+template <typename T> struct Num;
+template <> struct Num<__half> {
+  static constexpr int kFmt = 0;
+  using T2 = __half2;
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ float2 to_f2(__half2 v) { return __half22float2(v); }
+  static __device__ __forceinline__ __half2 from_f2(float a, float b) {
+    return __floats2half2_rn(a, b);
+  }
+};
+template <> struct Num<__nv_bfloat16> {
+  static constexpr int kFmt = 1;
+  using T2 = __nv_bfloat162;
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) {
+    return __float2bfloat16_rn(v);
+  }
+  static __device__ __forceinline__ float2 to_f2(__nv_bfloat162 v) {
+    return __bfloat1622float2(v);
+  }
+  static __device__ __forceinline__ __nv_bfloat162 from_f2(float a, float b) {
+    return __floats2bfloat162_rn(a, b);
+  }
+};
+
+// 8 x 16-bit values in one 16-byte register quad.
+template <typename T> struct alignas(16) Vec8 {
+  typename Num<T>::T2 v[4];
+};
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&f)[8]) {
+  Vec8<T> x = *reinterpret_cast<const Vec8<T>*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = Num<T>::to_f2(x.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
+  Vec8<T> x;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) x.v[i] = Num<T>::from_f2(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<Vec8<T>*>(p) = x;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float gelu_erf_f(float x) {
+  return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+}
+
+enum Act : int32_t {
+  kActNone = 0,
+  kActSiluMul = 1,      // dual accumulator: silu(g) * u
+  kActGeluTanhMul = 2,  // dual accumulator: gelu_tanh(g) * u
+  kActGeluTanh = 3,
+  kActGeluErf = 4,
+  kActSilu = 5,
+};
+
+__device__ __forceinline__ float apply_act(int act, float g, float u) {
+  switch (act) {
+    case kActSiluMul: return silu_f(g) * u;
+    case kActGeluTanhMul: return gelu_tanh_f(g) * u;
+    case kActGeluTanh: return gelu_tanh_f(g);
+    case kActGeluErf: return gelu_erf_f(g);
+    case kActSilu: return silu_f(g);
+    default: return g;
+  }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+}  // namespace rf

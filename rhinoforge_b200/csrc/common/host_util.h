@@ -1,0 +1,49 @@
+// Host-side helpers: last-error string, CUDA error checks, TMA tensor-map
+// encoding through the driver entry point (no link-time libcuda dependency, so
+// the library also loads on a machine without a driver).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+
+#include "../rf_api.h"
+
+namespace rf {
+
+void set_error(const std::string& msg);
+int fail(int code, const char* fmt, ...);
+
+#define RF_CUDA_CHECK(expr)                                                                  \
+  do {                                                                                       \
+    cudaError_t _e = (expr);                                                                 \
+    if (_e != cudaSuccess)                                                                   \
+      return ::rf::fail(RF_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                        __FILE__, __LINE__);                                                 \
+  } while (0)
+
+#define RF_REQUIRE(cond, ...)                                   \
+  do {                                                          \
+    if (!(cond)) return ::rf::fail(RF_ERR_BAD_ARG, __VA_ARGS__); \
+  } while (0)
+
+// 2-D K-major tensor map over a row-major [rows, inner] matrix of 16-bit (or
+// 8-bit when elem_bytes == 1) elements with row pitch ld (elements).  The box is
+// [box_rows, box_inner]; swizzle 128 B requires box_inner * elem_bytes == 128.
+// Returns 0 or a negative RfError.
+int make_tmap_2d(CUtensorMap* out, const void* base, int dtype, int elem_bytes, uint64_t inner,
+                 uint64_t rows, uint64_t ld, uint32_t box_inner, uint32_t box_rows,
+                 bool swizzle128);
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+inline int round_up(int a, int b) { return ceil_div(a, b) * b; }
+inline uint32_t next_pow2(uint32_t v) {
+  uint32_t p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+int sm_count();
+
+}  // namespace rf

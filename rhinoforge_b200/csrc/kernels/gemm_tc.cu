@@ -1,0 +1,562 @@
+// tcgen05 GEMM for sm_100a:  out[M,N] = epilogue( x[M,K] . w[N,K]^T ).
+//
+// One kernel covers decode (M <= 256 tokens) and prefill:
+//  * operands are staged by TMA into 128-byte-swizzled K-major smem tiles and
+//    multiplied by tcgen05.mma (kind::f16, fp32 accumulators in TMEM);
+//  * "swap" mode puts the WEIGHT rows on the 128-wide MMA M axis and the tokens
+//    on the MMA N axis (16..256), so a decode step streams every weight byte
+//    exactly once with no padded-token traffic; "normal" mode puts tokens on M;
+//  * "dual" mode keeps two accumulators (gate and up projection of the same
+//    output feature) and applies act(gate) * up in the epilogue (SwiGLU/GeGLU);
+//  * split-K spreads one output tile over several CTAs so that skinny decode
+//    GEMMs still fill 148 SMs; partials meet in an fp32 workspace and the last
+//    CTA to arrive reduces them in split order (deterministic);
+//  * the epilogue can push its tile to every tensor-parallel peer over NVLink
+//    (plain peer stores), wait (bounded) for the peers' tiles and finish the
+//    all-reduce + residual in the same kernel.
+//
+// Replaces the reference's parallel_linear_* tile family, llama_gemv, the
+// SiLU/GELU + multiply launches and llama_reduce_sum (src/ops/rpu_linear.cpp:1047-1544,
+// src/ops/rpu_linear_gemv.cpp, src/core/fused_model_base.cpp:8515-8567,
+// src/core/rpu_runtime_extras.cpp:1035-1092).
+#include "../common/dtype.cuh"
+#include "../common/host_util.h"
+#include "../common/ptx.cuh"
+#include "../rf_api.h"
+
+namespace rf {
+
+constexpr int kBM = 128;          // MMA M (rows of operand A per CTA)
+constexpr int kBK = 64;           // K elements per smem stage (128 bytes)
+constexpr int kATileBytes = kBM * kBK * 2;
+constexpr int kMaxStages = 8;
+
+struct GemmTcParams {
+  void* out; int64_t ldo;
+  const void* residual; int64_t ldr;
+  const void* bias; const void* scale; const float* row_scale;
+  float* ws; uint32_t* sem; int32_t* status;
+  int M, N;
+  int k_blocks, splits, bn, stages, act, dual_offset, tmem_cols;
+  int ar_world, ar_rank;
+  void* const* ar_recv; uint32_t* const* ar_flags; uint32_t* ar_state;
+  uint64_t ar_half_bytes;
+};
+
+struct alignas(8) GemmSmemCtl {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t accum;
+  uint32_t tmem_base;
+  int32_t abort_flag;
+  int32_t is_last;
+  uint32_t ar_call;
+};
+
+template <typename T, bool SWAP, bool DUAL>
+__global__ void __launch_bounds__(128)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const GemmTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int bn = p.bn;
+  constexpr int kATiles = (SWAP && DUAL) ? 2 : 1;
+  constexpr int kBTiles = (!SWAP && DUAL) ? 2 : 1;
+  const int b_tile_bytes = bn * kBK * 2;
+  const int stage_bytes = kATiles * kATileBytes + kBTiles * b_tile_bytes;
+  GemmSmemCtl* ctl = reinterpret_cast<GemmSmemCtl*>(smem + (size_t)p.stages * stage_bytes);
+
+  const int a0 = blockIdx.x * kBM;
+  const int b0 = blockIdx.y * bn;
+  const int z = blockIdx.z;
+  const int kb_base = p.k_blocks / p.splits, kb_rem = p.k_blocks % p.splits;
+  const int kb0 = z * kb_base + min(z, kb_rem);
+  const int kb_count = kb_base + (z < kb_rem ? 1 : 0);
+
+  if (tid == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->empty[s], 1);
+    }
+    mbar_init(&ctl->accum, 1);
+    ctl->abort_flag = 0;
+    ctl->is_last = 1;
+    ctl->ar_call = (p.ar_world > 1) ? *reinterpret_cast<volatile uint32_t*>(p.ar_state) : 0u;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, (uint32_t)p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  // ------------------------------------------------------- TMA producer ----
+  if (warp == 0 && lane_id() == 0) {
+    const uint32_t tx = (uint32_t)stage_bytes;
+    int issued = 0;
+    bool ok = true;
+    for (int i = 0; i < kb_count; ++i) {
+      const int s = i % p.stages;
+      const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
+      if (!mbar_wait(&ctl->empty[s], ph ^ 1u)) {
+        report_status(p.status, kStatusTmaTimeout, kTagGemmTc, i);
+        ok = false;
+        break;
+      }
+      if (*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag)) { ok = false; break; }
+      uint8_t* st = smem + (size_t)s * stage_bytes;
+      const int kc = (kb0 + i) * kBK;
+      mbar_arrive_expect_tx(&ctl->full[s], tx);
+      tma_load_2d(st, &tmA, &ctl->full[s], kc, a0);
+      if (kATiles == 2) tma_load_2d(st + kATileBytes, &tmA, &ctl->full[s], kc, p.dual_offset + a0);
+      uint8_t* sb = st + kATiles * kATileBytes;
+      tma_load_2d(sb, &tmB, &ctl->full[s], kc, b0);
+      if (kBTiles == 2) tma_load_2d(sb + b_tile_bytes, &tmB, &ctl->full[s], kc, p.dual_offset + b0);
+      issued = i + 1;
+    }
+    if (!ok) {
+      ctl->abort_flag = 1;
+      // Let every copy that was issued land before the CTA can exit.
+      const int first = issued > p.stages ? issued - p.stages : 0;
+      for (int i = first; i < issued; ++i)
+        mbar_wait(&ctl->full[i % p.stages], (uint32_t)(i / p.stages) & 1u, 20ull * 1000 * 1000);
+    }
+  }
+  // --------------------------------------------------------- MMA issuer ----
+  if (warp == 1 && lane_id() == 0) {
+    const uint32_t idesc = umma_idesc_f16(kBM, bn, Num<T>::kFmt);
+    bool ok = true;
+    for (int i = 0; i < kb_count; ++i) {
+      const int s = i % p.stages;
+      const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
+      if (!mbar_wait(&ctl->full[s], ph)) {
+        report_status(p.status, kStatusMmaTimeout, kTagGemmTc, i);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
+      const uint32_t b_addr = a_addr + kATiles * kATileBytes;
+#pragma unroll
+      for (int k = 0; k < kBK / 16; ++k) {
+        const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+        const uint64_t da = umma_desc_k128(a_addr + k * 32);
+        const uint64_t db = umma_desc_k128(b_addr + k * 32);
+        umma_f16(tmem_base, da, db, idesc, acc);
+        if (DUAL) {
+          if (SWAP) {
+            const uint64_t da1 = umma_desc_k128(a_addr + kATileBytes + k * 32);
+            umma_f16(tmem_base + bn, da1, db, idesc, acc);
+          } else {
+            const uint64_t db1 = umma_desc_k128(b_addr + b_tile_bytes + k * 32);
+            umma_f16(tmem_base + bn, da, db1, idesc, acc);
+          }
+        }
+      }
+      umma_commit(&ctl->empty[s]);
+    }
+    if (ok) umma_commit(&ctl->accum);
+    else ctl->abort_flag = 1;
+  }
+  __syncwarp();
+
+  // ----------------------------------------------------------- epilogue ----
+  bool have_acc = mbar_wait(&ctl->accum, 0);
+  if (!have_acc) {
+    if (!*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag))
+      report_status(p.status, kStatusEpilogueTimeout, kTagGemmTc, (int)blockIdx.y);
+    ctl->abort_flag = 1;
+  }
+  tc_fence_after_sync();
+  __syncwarp();
+
+  const uint32_t trow = tmem_base + ((uint32_t)(warp * 32) << 16);
+  const int a_idx = a0 + tid;
+  const int M = p.M, N = p.N;
+  const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+  constexpr int kAcc = DUAL ? 2 : 1;
+
+  // Split-K: park this CTA's partial in the workspace; the last CTA to arrive
+  // re-reads every split in order.
+  if (p.splits > 1) {
+    if (have_acc) {
+      for (int c = 0; c < bn; c += 16) {
+        uint32_t rg[16], ru[16];
+        tmem_ld16(trow + c, rg);
+        if (DUAL) tmem_ld16(trow + bn + c, ru);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int tok = SWAP ? (b0 + c + j) : a_idx;
+          const int n = SWAP ? a_idx : (b0 + c + j);
+          if (tok < M && n < N) {
+            const size_t o = ((size_t)(z * kAcc) * M + tok) * N + n;
+            p.ws[o] = __uint_as_float(rg[j]);
+            if (DUAL) p.ws[o + (size_t)M * N] = __uint_as_float(ru[j]);
+          }
+        }
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const uint32_t prev = atomicAdd(&p.sem[tile_id], 1u);
+      const int last = (prev == (uint32_t)(p.splits - 1));
+      if (last) p.sem[tile_id] = 0u;
+      ctl->is_last = last;
+    }
+    __syncthreads();
+    __threadfence();
+  }
+
+  const bool finisher = ctl->is_last != 0;
+  const bool aborted = *reinterpret_cast<volatile int32_t*>(&ctl->abort_flag) != 0;
+  if (finisher && !aborted) {
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    const T* scale = reinterpret_cast<const T*>(p.scale);
+    const T* resid = reinterpret_cast<const T*>(p.residual);
+    T* out = reinterpret_cast<T*>(p.out);
+    const bool use_bias = bias != nullptr && (p.ar_world <= 1 || p.ar_rank == 0);
+    const uint32_t call = ctl->ar_call;
+    const uint64_t slot_off = (uint64_t)(call & 1u) * p.ar_half_bytes;
+
+    for (int c = 0; c < bn; c += 16) {
+      float g[16], u[16];
+      if (p.splits > 1) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int tok = SWAP ? (b0 + c + j) : a_idx;
+          const int n = SWAP ? a_idx : (b0 + c + j);
+          float sg = 0.f, su = 0.f;
+          if (tok < M && n < N) {
+            for (int s = 0; s < p.splits; ++s) {
+              const size_t o = ((size_t)(s * kAcc) * M + tok) * N + n;
+              sg += __ldcg(p.ws + o);
+              if (DUAL) su += __ldcg(p.ws + o + (size_t)M * N);
+            }
+          }
+          g[j] = sg;
+          u[j] = su;
+        }
+      } else {
+        uint32_t rg[16], ru[16];
+        tmem_ld16(trow + c, rg);
+        if (DUAL) tmem_ld16(trow + bn + c, ru);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          g[j] = __uint_as_float(rg[j]);
+          u[j] = DUAL ? __uint_as_float(ru[j]) : 0.f;
+        }
+      }
+      // scale / bias / activation
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int tok = SWAP ? (b0 + c + j) : a_idx;
+        const int n = SWAP ? a_idx : (b0 + c + j);
+        float vg = g[j], vu = u[j];
+        if (tok < M && n < N) {
+          if (p.row_scale) {
+            const float rs = p.row_scale[tok];
+            vg *= rs;
+            vu *= rs;
+          }
+          if (scale) {
+            vg *= Num<T>::to_f(scale[n]);
+            if (DUAL) vu *= Num<T>::to_f(scale[p.dual_offset + n]);
+          }
+          if (use_bias) {
+            vg += Num<T>::to_f(bias[n]);
+            if (DUAL) vu += Num<T>::to_f(bias[p.dual_offset + n]);
+          }
+        }
+        v[j] = apply_act(p.act, vg, vu);
+      }
+      if (p.ar_world > 1) {
+        // push this rank's partial tile into every rank's receive buffer
+        for (int dst = 0; dst < p.ar_world; ++dst) {
+          float* rb = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ar_recv[dst]) + slot_off) +
+                      (size_t)p.ar_rank * M * N;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int tok = SWAP ? (b0 + c + j) : a_idx;
+            const int n = SWAP ? a_idx : (b0 + c + j);
+            if (tok < M && n < N) rb[(size_t)tok * N + n] = v[j];
+          }
+        }
+      } else if (SWAP) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int tok = b0 + c + j;
+          if (tok < M && a_idx < N) {
+            float r = v[j];
+            if (resid) r += Num<T>::to_f(resid[(size_t)tok * p.ldr + a_idx]);
+            out[(size_t)tok * p.ldo + a_idx] = Num<T>::from_f(r);
+          }
+        }
+      } else {
+        const int n0 = b0 + c;
+        if (a_idx < M) {
+          const bool vec = (n0 + 16 <= N) && ((p.ldo & 7) == 0) && (!resid || (p.ldr & 7) == 0);
+          if (vec) {
+            if (resid) {
+              float r0[8], r1[8];
+              load8(resid + (size_t)a_idx * p.ldr + n0, r0);
+              load8(resid + (size_t)a_idx * p.ldr + n0 + 8, r1);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { v[j] += r0[j]; v[8 + j] += r1[j]; }
+            }
+            float lo[8], hi[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
+            store8(out + (size_t)a_idx * p.ldo + n0, lo);
+            store8(out + (size_t)a_idx * p.ldo + n0 + 8, hi);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int n = n0 + j;
+              if (n < N) {
+                float r = v[j];
+                if (resid) r += Num<T>::to_f(resid[(size_t)a_idx * p.ldr + n]);
+                out[(size_t)a_idx * p.ldo + n] = Num<T>::from_f(r);
+              }
+            }
+          }
+        }
+      }
+    }
+
+    if (p.ar_world > 1) {
+      // publish, wait for every rank's tile (bounded), then reduce in rank order
+      __threadfence_system();
+      __syncthreads();
+      const uint32_t want = call + 1u;
+      if (tid < p.ar_world)
+        st_release_sys(p.ar_flags[tid] + (size_t)tile_id * p.ar_world + p.ar_rank, want);
+      if (tid < p.ar_world) {
+        const uint32_t* mine = p.ar_flags[p.ar_rank] + (size_t)tile_id * p.ar_world + tid;
+        if (!wait_flag_ge_sys(mine, want)) {
+          report_status(p.status, kStatusPeerTimeout, kTagGemmAr, tid);
+          ctl->abort_flag = 1;
+        }
+      }
+      __syncthreads();
+      if (!*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag)) {
+        const float* rb = reinterpret_cast<const float*>(
+            reinterpret_cast<const uint8_t*>(p.ar_recv[p.ar_rank]) + slot_off);
+        for (int c = 0; c < bn; c += 16) {
+#pragma unroll 4
+          for (int j = 0; j < 16; ++j) {
+            const int tok = SWAP ? (b0 + c + j) : a_idx;
+            const int n = SWAP ? a_idx : (b0 + c + j);
+            if (tok < M && n < N) {
+              float acc = 0.f;
+              for (int r = 0; r < p.ar_world; ++r)
+                acc += __ldcg(rb + ((size_t)r * M + tok) * N + n);
+              if (resid) acc += Num<T>::to_f(resid[(size_t)tok * p.ldr + n]);
+              out[(size_t)tok * p.ldo + n] = Num<T>::from_f(acc);
+            }
+          }
+        }
+      }
+    }
+  }
+  if (p.ar_world > 1 && finisher) {
+    // the last tile to finish advances the call counter for the next launch
+    __syncthreads();
+    if (tid == 0) {
+      const uint32_t tiles = gridDim.x * gridDim.y;
+      const uint32_t done = atomicAdd(p.ar_state + 1, 1u);
+      if (done == tiles - 1u) {
+        p.ar_state[1] = 0u;
+        __threadfence();
+        p.ar_state[0] = ctl->ar_call + 1u;
+      }
+    }
+  }
+
+  // ----------------------------------------------------------- teardown ----
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+}
+
+// ------------------------------------------------------------ host side ----
+struct GemmPlan {
+  int swap, bn, splits, stages, tmem_cols, grid_x, grid_y, k_blocks;
+  size_t smem_bytes;
+  uint64_t ws_bytes;
+  int sem_count;
+};
+
+static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
+  const bool dual = g->dual_offset > 0;
+  pl->k_blocks = ceil_div(g->K, kBK);
+  int swap = g->force_swap >= 0 ? g->force_swap : (g->M <= 256 ? 1 : 0);
+  if (swap && g->M > 256 && g->force_swap < 0) swap = 0;
+  pl->swap = swap;
+  if (swap) {
+    int bn = g->force_bn > 0 ? g->force_bn : round_up(g->M < 16 ? 16 : g->M, 16);
+    if (bn > 256) bn = 256;
+    if (dual && bn > 256) bn = 256;
+    pl->bn = bn;
+    pl->grid_x = ceil_div(g->N, kBM);
+    pl->grid_y = ceil_div(g->M, bn);
+  } else {
+    int bn = g->force_bn > 0 ? g->force_bn : ((g->N % 256 == 0 && !dual) ? 256 : 128);
+    if (g->N < 128) bn = round_up(g->N, 16);
+    pl->bn = bn;
+    pl->grid_x = ceil_div(g->M, kBM);
+    pl->grid_y = ceil_div(g->N, bn);
+  }
+  pl->tmem_cols = (int)next_pow2((uint32_t)std::max(32, pl->bn * (dual ? 2 : 1)));
+  if (pl->tmem_cols > 512) return fail(RF_ERR_BAD_ARG, "accumulator needs %d TMEM columns", pl->tmem_cols);
+
+  const int tiles = pl->grid_x * pl->grid_y;
+  int splits = 1;
+  if (g->force_splits > 0) {
+    splits = g->force_splits;
+  } else if (g->ws != nullptr || g->ws_bytes == ~0ull) {
+    const int target = 2 * sm_count();
+    if (tiles < target) {
+      splits = target / tiles;
+      const int max_by_k = std::max(1, pl->k_blocks / 4);
+      splits = std::min(std::min(splits, max_by_k), 16);
+      if (splits < 1) splits = 1;
+    }
+  }
+  if (splits > pl->k_blocks) splits = pl->k_blocks;
+  pl->splits = splits;
+  pl->ws_bytes = splits > 1 ? (uint64_t)splits * (dual ? 2 : 1) * g->M * g->N * sizeof(float) : 0;
+  pl->sem_count = splits > 1 ? tiles : 0;
+
+  const int a_tiles = (swap && dual) ? 2 : 1, b_tiles = (!swap && dual) ? 2 : 1;
+  const int stage_bytes = a_tiles * kATileBytes + b_tiles * pl->bn * kBK * 2;
+  const int ctl_bytes = (int)sizeof(GemmSmemCtl) + 1024 /*alignment slack*/ + 64;
+  int stages = (110 * 1024 - ctl_bytes) / stage_bytes;
+  if (stages < 3) stages = (224 * 1024 - ctl_bytes) / stage_bytes;
+  stages = std::min(stages, kMaxStages);
+  stages = std::min(stages, std::max(2, ceil_div(pl->k_blocks, splits)));
+  if (stages < 2) return fail(RF_ERR_UNSUPPORTED, "GEMM tile does not fit in shared memory");
+  pl->stages = stages;
+  pl->smem_bytes = (size_t)stages * stage_bytes + ctl_bytes;
+  return RF_OK;
+}
+
+template <typename T, bool SWAP, bool DUAL>
+static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream) {
+  static bool attr_set = false;
+  auto kfn = gemm_tc_kernel<T, SWAP, DUAL>;
+  if (!attr_set) {
+    RF_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    attr_set = true;
+  }
+  const bool dual = DUAL;
+  const uint64_t w_rows = (uint64_t)(dual ? g->dual_offset + g->N : g->N);
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (SWAP) {
+    rc = make_tmap_2d(&tmA, g->w, g->dtype, 2, g->K, w_rows, g->ldw, kBK, kBM, true);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmB, g->x, g->dtype, 2, g->K, g->M, g->ldx, kBK, pl.bn, true);
+    if (rc) return rc;
+  } else {
+    rc = make_tmap_2d(&tmA, g->x, g->dtype, 2, g->K, g->M, g->ldx, kBK, kBM, true);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmB, g->w, g->dtype, 2, g->K, w_rows, g->ldw, kBK, pl.bn, true);
+    if (rc) return rc;
+  }
+  GemmTcParams p;
+  p.out = g->out; p.ldo = g->ldo;
+  p.residual = g->residual; p.ldr = g->ldr;
+  p.bias = g->bias; p.scale = g->scale; p.row_scale = g->row_scale;
+  p.ws = g->ws; p.sem = g->sem; p.status = g->status;
+  p.M = g->M; p.N = g->N;
+  p.k_blocks = pl.k_blocks; p.splits = pl.splits; p.bn = pl.bn; p.stages = pl.stages;
+  p.act = g->act; p.dual_offset = g->dual_offset; p.tmem_cols = pl.tmem_cols;
+  p.ar_world = g->ar_world; p.ar_rank = g->ar_rank;
+  p.ar_recv = g->ar_recv; p.ar_flags = g->ar_flags; p.ar_state = g->ar_state;
+  p.ar_half_bytes = g->ar_recv_bytes;
+  dim3 grid(pl.grid_x, pl.grid_y, pl.splits);
+  kfn<<<grid, 128, pl.smem_bytes, stream>>>(tmA, tmB, p);
+  RF_CUDA_CHECK(cudaGetLastError());
+  return RF_OK;
+}
+
+static int check_gemm(const RfGemm* g) {
+  RF_REQUIRE(g != nullptr, "null RfGemm");
+  RF_REQUIRE(g->x && g->w && g->out, "GEMM needs x, w and out");
+  RF_REQUIRE(g->M > 0 && g->N > 0 && g->K > 0, "GEMM shape %dx%dx%d", g->M, g->N, g->K);
+  RF_REQUIRE(g->K % 8 == 0, "GEMM K=%d must be a multiple of 8 (16-byte rows)", g->K);
+  RF_REQUIRE(g->ldx % 8 == 0 && g->ldw % 8 == 0, "GEMM row pitches must be multiples of 8 elements");
+  RF_REQUIRE(g->dtype == 0 || g->dtype == 1, "GEMM dtype must be fp16 or bf16");
+  const bool dual_act = g->act == kActSiluMul || g->act == kActGeluTanhMul;
+  RF_REQUIRE(dual_act == (g->dual_offset > 0), "dual_offset and a *_mul activation go together");
+  if (g->ar_world > 1) {
+    RF_REQUIRE(g->ar_world <= 8 && g->ar_rank >= 0 && g->ar_rank < g->ar_world, "bad ar rank/world");
+    RF_REQUIRE(g->ar_recv && g->ar_flags && g->ar_state, "fused all-reduce needs recv/flags/state");
+    RF_REQUIRE((uint64_t)g->ar_world * g->M * g->N * sizeof(float) <= g->ar_recv_bytes,
+               "all-reduce receive buffer too small for %dx%d", g->M, g->N);
+  }
+  return RF_OK;
+}
+
+}  // namespace rf
+
+using namespace rf;
+
+extern "C" int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem_count) {
+  int rc = check_gemm(g);
+  if (rc) return rc;
+  RfGemm t = *g;
+  if (t.ws == nullptr) t.ws_bytes = ~0ull;  // "assume scratch will be provided"
+  GemmPlan pl;
+  rc = plan_gemm(&t, &pl);
+  if (rc) return rc;
+  if (ws_bytes) *ws_bytes = pl.ws_bytes;
+  if (sem_count) *sem_count = pl.sem_count;
+  return RF_OK;
+}
+
+extern "C" int rf_gemm(const RfGemm* g, rf_stream_t stream_) {
+  int rc = check_gemm(g);
+  if (rc) return rc;
+  RF_REQUIRE(!g->w_int8, "rf_gemm takes 16-bit weights; use rf_gemm_w8a16 for int8");
+  GemmPlan pl;
+  rc = plan_gemm(g, &pl);
+  if (rc) return rc;
+  if (pl.splits > 1) {
+    RF_REQUIRE(g->ws && g->sem, "split-K needs ws and sem");
+    RF_REQUIRE(pl.ws_bytes <= g->ws_bytes, "split-K workspace too small: need %llu B, have %llu B",
+               (unsigned long long)pl.ws_bytes, (unsigned long long)g->ws_bytes);
+    RF_REQUIRE(pl.sem_count <= g->sem_count, "split-K needs %d semaphores, have %d", pl.sem_count,
+               g->sem_count);
+  }
+  if (g->ar_world > 1)
+    RF_REQUIRE(pl.grid_x * pl.grid_y * g->ar_world <= g->ar_flag_count,
+               "all-reduce needs %d flags, have %d", pl.grid_x * pl.grid_y * g->ar_world,
+               g->ar_flag_count);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const bool dual = g->dual_offset > 0;
+#define RF_GEMM_DISPATCH(T)                                                       \
+  if (pl.swap) {                                                                  \
+    return dual ? launch_gemm<T, true, true>(g, pl, stream)                       \
+                : launch_gemm<T, true, false>(g, pl, stream);                     \
+  } else {                                                                        \
+    return dual ? launch_gemm<T, false, true>(g, pl, stream)                      \
+                : launch_gemm<T, false, false>(g, pl, stream);                    \
+  }
+  if (g->dtype == 0) { RF_GEMM_DISPATCH(__half) }
+  RF_GEMM_DISPATCH(__nv_bfloat16)
+#undef RF_GEMM_DISPATCH
+}

@@ -1,0 +1,146 @@
+// C ABI of librf_b200: every entry point takes raw device pointers and a CUDA
+// stream, allocates nothing unless its comment says so, and returns 0 on
+// success or a negative RfError.  Python binds these through ctypes.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* rf_stream_t;  // cudaStream_t
+
+enum RfError {
+  RF_OK = 0,
+  RF_ERR_BAD_ARG = -1,
+  RF_ERR_CUDA = -2,
+  RF_ERR_UNSUPPORTED = -3,
+  RF_ERR_NO_MEMORY = -4,
+  RF_ERR_STATE = -5,
+};
+
+const char* rf_last_error(void);
+int rf_version(void);
+
+// ---------------------------------------------------------------- GEMM ----
+// out[M,N] = epilogue( x[M,K] . w[N,K]^T ), all row-major, 16-bit in, fp32 acc.
+typedef struct RfGemm {
+  const void* x; int64_t ldx;
+  const void* w; int64_t ldw;
+  void* out; int64_t ldo;
+  const void* residual; int64_t ldr;  // optional, added last
+  const void* bias;                   // optional [N] (dual: [dual_offset+N])
+  const void* scale;                  // optional per-output-channel scale [N], same dtype
+  const float* row_scale;             // optional per-token fp32 scale [M]
+  int32_t M, N, K;
+  int32_t dtype;        // 0 fp16, 1 bf16
+  int32_t act;          // rf::Act
+  int32_t dual_offset;  // >0: second weight block starts dual_offset rows below the first
+  int32_t w_int8;       // 1: w is int8 [N,K] (scale required)
+  float* ws; uint64_t ws_bytes;  // split-K scratch (fp32 partials), optional
+  uint32_t* sem; int32_t sem_count;  // split-K tile semaphores, zero-initialised once
+  int32_t* status;      // device status block, optional
+  // fused all-reduce over peer memory (world > 1): partial tiles are pushed
+  // into every rank's receive buffer, summed in rank order, residual added.
+  int32_t ar_world, ar_rank;
+  void* const* ar_recv;        // device array [world] of receive-buffer bases
+  uint32_t* const* ar_flags;   // device array [world] of flag-array bases
+  uint32_t* ar_state;          // local: [0] call counter, [1] finished-CTA counter
+  uint64_t ar_recv_bytes;      // bytes of one half of the (double-buffered) receive buffer
+  int32_t ar_flag_count;       // flags available per rank
+  int32_t force_splits;        // 0 = heuristic
+  int32_t force_swap;          // -1 = heuristic, 0/1 forced
+  int32_t force_bn;            // 0 = heuristic
+} RfGemm;
+
+int rf_gemm(const RfGemm* g, rf_stream_t stream);
+// Scratch a split-K launch of this shape would need (bytes of ws, number of sems).
+int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem_count);
+// CUDA-core skinny GEMM (M <= 8): reference path and small-batch decode.
+int rf_gemv(const RfGemm* g, rf_stream_t stream);
+
+
+// ------------------------------------------------------ norms / glue ----
+int rf_rmsnorm(const void* x, const void* residual, const void* w, void* y, void* residual_out,
+               const void* mod, int rows_per_mod, int rows, int H, int64_t ldx, int64_t ldy,
+               float eps, int mode, int dtype, rf_stream_t stream);
+int rf_layernorm(const void* x, const void* w, const void* b, void* y, int rows, int H,
+                 int64_t ldx, int64_t ldy, float eps, int dtype, rf_stream_t stream);
+int rf_l2norm(const void* x, void* y, int rows, int H, float eps, float out_scale, int dtype,
+              rf_stream_t stream);
+int rf_gated_residual(void* x, const void* y, const void* mod, int rows_per_mod, int rows, int H,
+                      int dtype, rf_stream_t stream);
+
+// Per-head RMSNorm(q,k) -> RoPE -> KV page insert on a packed [tokens, (Hq+2Hkv)*hd] buffer.
+typedef struct RfRopeKv {
+  void* qkv; int64_t ld;
+  void* q_out; int64_t ldq;        // optional: rotated q goes here instead of in place
+  int32_t tokens, Hq, Hkv, hd, rot_dim;
+  const void* q_norm_w; const void* k_norm_w;  // optional [hd]
+  float eps; int32_t norm_mode;     // bit0: (1+w) weight
+  const float* cos; const float* sin;  // [max_pos, rot_dim/2] fp32, optional
+  const int32_t* pos; int32_t pos_stride;  // [tokens, pos_stride]
+  const int8_t* axis_of_freq;       // optional [rot_dim/2]: which position axis a frequency uses
+  void* k_pool; void* v_pool;       // optional [pages, Hkv, 16, hd]
+  const int32_t* page_table; int32_t pt_stride;  // [seqs, pt_stride]
+  const int32_t* seq_of_tok;        // optional [tokens]; default token index
+  const int32_t* cache_pos;         // optional [tokens]; default pos[tok, 0]
+  int32_t rope_before_norm;
+  int32_t write_k_inplace;          // also write rotated k back into qkv
+  int32_t dtype;
+} RfRopeKv;
+int rf_qk_norm_rope_kv(const RfRopeKv* a, rf_stream_t stream);
+
+// out[i] = table[ids[i]] (row gather); ids < 0 give zero rows.  scale multiplies (Gemma sqrt(H)).
+int rf_embedding(const void* table, const int32_t* ids, void* out, int n_ids, int H, int64_t ldo,
+                 float scale, int dtype, const void* row_scale_i8, rf_stream_t stream);
+// dst[rows[i]] = src[i]  (splice vision rows into text rows)
+int rf_scatter_rows(void* dst, const void* src, const int32_t* rows, int n, int H, int64_t ldd,
+                    int64_t lds, int accumulate, int dtype, rf_stream_t stream);
+// Elementwise: op 0 add, 1 mul, 2 silu(a)*b, 3 gelu_tanh(a)*b, 4 a + alpha*b, 5 gelu_tanh(a),
+// 6 gelu_erf(a), 7 silu(a), 8 a*alpha, 9 sigmoid(a)*b, 10 a*(broadcast row vector b), 11 tanh(a)
+int rf_eltwise(int op, const void* a, const void* b, void* out, int64_t n, int64_t b_period,
+               float alpha, int dtype, rf_stream_t stream);
+int rf_cast_u8_f16(const uint8_t* src, void* dst, int64_t n, float scale, float shift, int dtype,
+                   rf_stream_t stream);
+// Greedy top-1 over the last dim; two-stage, writes int32 ids (and fp32 max when vals != null).
+// offset is added to every id (vocab shard base).
+int rf_argmax(const void* logits, int rows, int V, int64_t ld, int32_t* out_ids, float* out_vals,
+              int32_t offset, void* scratch, uint64_t scratch_bytes, int dtype, rf_stream_t stream);
+uint64_t rf_argmax_scratch_bytes(int rows, int V);
+
+
+// ----------------------------------------------------------- attention ----
+// q/out: [q_rows_total, Hq*hd] (pitch ldq/ldo).  KV comes either from the paged
+// pool ([pages, Hkv, 16, hd], page_table[seq, i] -> page id) or from contiguous
+// rows k/v[kv_rows_total, Hkv*hd].  The pool must only ever hold finite values
+// (it is zero-filled at creation): masked tokens still pass through the MMA.
+typedef struct RfAttn {
+  const void* q; int64_t ldq;
+  void* out; int64_t ldo;
+  int64_t q_rows_total;
+  const void* k_pool; const void* v_pool; int64_t pool_pages;
+  const int32_t* page_table; int32_t pt_stride;
+  const void* k; const void* v; int64_t ldk, ldv; int64_t kv_rows_total;
+  int32_t num_seqs, Hq, Hkv, hd;
+  const int32_t* q_start;   // [num_seqs] first q row (prefill)
+  const int32_t* q_len;     // [num_seqs] (prefill)
+  const int32_t* kv_start;  // [num_seqs] first kv row (contiguous mode)
+  const int32_t* kv_len;    // [num_seqs] valid kv tokens, device
+  int32_t max_q_len, max_kv_len;  // host-side bounds used for grid sizing
+  int32_t causal;           // q row i sits at position kv_len - q_len + i
+  int32_t window;           // > 0: sliding window
+  const uint8_t* mask; int64_t mask_ld, mask_seq_stride;  // optional boolean [q, kv] per sequence
+  const int32_t* seg_q; const int32_t* seg_k;             // optional segment ids per q row / kv row
+  float scale;              // <= 0: 1/sqrt(hd)
+  float* ws; uint64_t ws_bytes;  // decode split-KV scratch, optional
+  int32_t* status; int32_t dtype;
+} RfAttn;
+int rf_attn_prefill(const RfAttn* a, rf_stream_t stream);
+int rf_attn_decode(const RfAttn* a, rf_stream_t stream);
+uint64_t rf_attn_decode_scratch_bytes(int num_seqs, int Hq, int hd);
+
+#ifdef __cplusplus
+}
+#endif

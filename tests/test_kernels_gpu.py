@@ -1,0 +1,372 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DT = [torch.float16, torch.bfloat16]
+
+
+def _tol(dt):
+    return (2e-2, 2e-2) if dt == torch.bfloat16 else (4e-3, 4e-3)
+
+
+def _close(a, b, dt, scale=1.0):
+    rtol, atol = _tol(dt)
+    torch.testing.assert_close(a.float(), b.float(), rtol=rtol, atol=atol * scale)
+
+
+@pytest.fixture(autouse=True)
+def _seed():
+    torch.manual_seed(0)
+
+
+@pytest.fixture()
+def status():
+    s = torch.zeros(8, dtype=torch.int32, device="cuda")
+    yield s
+    torch.cuda.synchronize()
+    assert s[0].item() == 0, f"kernel status {s.tolist()}"
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M,N,K", [(1, 256, 512), (5, 384, 1024), (16, 4096, 4096), (64, 1000, 4304), (200, 640, 320),
+                                   (128, 256, 64), (300, 512, 1024), (1024, 768, 2048), (257, 1152, 1152)])
+def test_gemm_plain(dt, M, N, K, status):
+    from rhinoforge_b200.ops import kernels as K_
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(dt)
+    y = K_.gemm(x, w, status=status)
+    ref = x.float() @ w.float().t()
+    _close(y, ref, dt, scale=max(1.0, ref.abs().max().item()))
+
+
+@pytest.mark.parametrize("swap", [0, 1])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_gemm_epilogue_bias_residual_scale(swap, splits, status):
+    from rhinoforge_b200.ops import kernels as K_
+    dt = torch.float16
+    M, N, K = 48, 640, 1536
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(dt)
+    b = torch.randn(N, device="cuda").to(dt)
+    sc = (torch.rand(N, device="cuda") + 0.5).to(dt)
+    r = torch.randn(M, N, device="cuda").to(dt)
+    rs = torch.rand(M, device="cuda") + 0.5
+    y = K_.gemm(x, w, bias=b, scale=sc, residual=r, row_scale=rs, status=status, force_swap=swap,
+                force_splits=splits)
+    ref = (x.float() @ w.float().t()) * rs[:, None] * sc.float() + b.float() + r.float()
+    _close(y, ref, dt, scale=4.0)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M,swap,splits", [(3, 1, 1), (40, 1, 2), (40, 0, 1), (300, 0, 1)])
+@pytest.mark.parametrize("act", ["silu_mul", "gelu_tanh_mul"])
+def test_gemm_dual_glu(dt, M, swap, splits, act, status):
+    from rhinoforge_b200.ops import kernels as K_
+    N, K = 384, 1024
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    w = (torch.randn(2 * N, K, device="cuda") * 0.05).to(dt)
+    y = K_.gemm(x, w, act=act, dual=True, status=status, force_swap=swap, force_splits=splits)
+    g = x.float() @ w[:N].float().t()
+    u = x.float() @ w[N:].float().t()
+    a = torch.nn.functional.silu(g) if act == "silu_mul" else torch.nn.functional.gelu(g, approximate="tanh")
+    _close(y, a * u, dt, scale=2.0)
+
+
+@pytest.mark.parametrize("act", ["gelu_tanh", "gelu_erf", "silu"])
+def test_gemm_unary_act(act, status):
+    from rhinoforge_b200.ops import kernels as K_
+    dt = torch.float16
+    x = (torch.randn(70, 512, device="cuda") * 0.5).to(dt)
+    w = (torch.randn(256, 512, device="cuda") * 0.05).to(dt)
+    y = K_.gemm(x, w, act=act, status=status)
+    z = x.float() @ w.float().t()
+    ref = {"gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh"),
+           "gelu_erf": torch.nn.functional.gelu, "silu": torch.nn.functional.silu}[act](z)
+    _close(y, ref, dt)
+
+
+def test_gemm_is_deterministic(status):
+    from rhinoforge_b200.ops import kernels as K_
+    x = (torch.randn(32, 4096, device="cuda") * 0.5).half()
+    w = (torch.randn(1024, 4096, device="cuda") * 0.05).half()
+    a = K_.gemm(x, w, status=status, force_splits=4).clone()
+    b = K_.gemm(x, w, status=status, force_splits=4)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M", [1, 2, 3, 8])
+@pytest.mark.parametrize("int8", [False, True])
+def test_gemv(dt, M, int8):
+    from rhinoforge_b200.ops import kernels as K_
+    N, K = 515, 1024
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    r = torch.randn(M, N, device="cuda").to(dt)
+    if int8:
+        w = torch.randint(-127, 128, (N, K), device="cuda", dtype=torch.int8)
+        sc = (torch.rand(N, device="cuda") * 0.01).to(dt)
+        y = K_.gemm(x, w, scale=sc, residual=r, use_gemv=True)
+        ref = (x.float() @ w.float().t()) * sc.float() + r.float()
+    else:
+        w = (torch.randn(N, K, device="cuda") * 0.05).to(dt)
+        y = K_.gemm(x, w, residual=r, use_gemv=True)
+        ref = x.float() @ w.float().t() + r.float()
+    _close(y, ref, dt, scale=4.0)
+
+
+def test_gemv_dual():
+    from rhinoforge_b200.ops import kernels as K_
+    x = (torch.randn(2, 512, device="cuda") * 0.5).half()
+    w = (torch.randn(2 * 300, 512, device="cuda") * 0.05).half()
+    y = K_.gemm(x, w, act="silu_mul", dual=True, use_gemv=True)
+    g, u = x.float() @ w[:300].float().t(), x.float() @ w[300:].float().t()
+    _close(y, torch.nn.functional.silu(g) * u, torch.float16)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("gemma", [False, True])
+def test_rmsnorm(dt, gemma):
+    from rhinoforge_b200.ops import kernels as K_
+    x = torch.randn(37, 1024, device="cuda").to(dt)
+    r = torch.randn(37, 1024, device="cuda").to(dt)
+    w = (torch.randn(1024, device="cuda") * 0.1 + (0 if gemma else 1)).to(dt)
+    ro = torch.empty_like(x)
+    y = K_.rmsnorm(x, w, 1e-6, residual=r, residual_out=ro, gemma=gemma)
+    h = (x.float() + r.float()).to(dt).float()
+    n = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-6)
+    ref = n * (1 + w.float()) if gemma else w.float() * n.to(dt).float()
+    _close(y, ref, dt)
+    _close(ro, h, dt)
+
+
+def test_rmsnorm_adarms_and_gated_residual():
+    from rhinoforge_b200.ops import kernels as K_
+    dt = torch.float16
+    B, T, H = 3, 50, 1024
+    x = torch.randn(B * T, H, device="cuda").to(dt)
+    mod = (torch.randn(B, 3 * H, device="cuda") * 0.3).to(dt)
+    y = K_.rmsnorm(x, None, 1e-6, mod=mod, rows_per_mod=T)
+    n = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)
+    sc, sh, gt = mod.float().view(B, 1, 3 * H).chunk(3, -1)
+    ref = (n.view(B, T, H) * (1 + sc) + sh).view(B * T, H)
+    _close(y, ref, dt)
+    x2 = x.clone()
+    K_.gated_residual(x2, y, mod, T)
+    _close(x2, (x.float().view(B, T, H) + gt * y.float().view(B, T, H)).view(B * T, H), dt)
+
+
+@pytest.mark.parametrize("dt", DT)
+def test_layernorm_l2norm(dt):
+    from rhinoforge_b200.ops import kernels as K_
+    x = torch.randn(33, 1152, device="cuda").to(dt)
+    w, b = torch.randn(1152, device="cuda").to(dt), torch.randn(1152, device="cuda").to(dt)
+    y = K_.layernorm(x, w, b, 1e-6)
+    _close(y, torch.nn.functional.layer_norm(x.float(), (1152,), w.float(), b.float(), 1e-6), dt)
+    z = K_.l2norm(x[:, :128].contiguous(), 1e-6)
+    xf = x[:, :128].float()
+    _close(z, xf * torch.rsqrt(xf.pow(2).sum(-1, keepdim=True) + 1e-6), dt)
+
+
+def _rope_tables(max_pos, rot, theta, device):
+    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, device=device).float() / rot))
+    ang = torch.arange(max_pos, device=device).float()[:, None] * inv[None]
+    return ang.cos().contiguous(), ang.sin().contiguous()
+
+
+def _rot_half(x):
+    h = x.shape[-1] // 2
+    return torch.cat([-x[..., h:], x[..., :h]], -1)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("hd,rot", [(128, 128), (256, 64), (64, 64)])
+def test_qk_norm_rope_kv_insert(dt, hd, rot):
+    from rhinoforge_b200.ops import kernels as K_
+    Hq, Hkv, T = 6, 2, 21
+    seqs = 3
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * hd, device="cuda").to(dt)
+    orig = qkv.clone()
+    qw, kw = (torch.rand(hd, device="cuda") + 0.5).to(dt), (torch.rand(hd, device="cuda") + 0.5).to(dt)
+    cos, sin = _rope_tables(512, rot, 1e6, "cuda")
+    seq_of_tok = torch.arange(T, device="cuda", dtype=torch.int32) % seqs
+    pos = (torch.arange(T, device="cuda", dtype=torch.int32) // seqs + 30).contiguous()
+    pages = 16
+    k_pool = torch.zeros(pages, Hkv, 16, hd, device="cuda", dtype=dt)
+    v_pool = torch.zeros_like(k_pool)
+    page_table = torch.arange(seqs * 4, device="cuda", dtype=torch.int32).view(seqs, 4).contiguous()
+    K_.qk_norm_rope_kv(qkv, Hq, Hkv, hd, pos=pos, cos=cos, sin=sin, rot_dim=rot, q_norm_w=qw, k_norm_w=kw,
+                       k_pool=k_pool, v_pool=v_pool, page_table=page_table, seq_of_tok=seq_of_tok)
+    o = orig.float().view(T, Hq + 2 * Hkv, hd)
+
+    def ref(x, w):
+        n = (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)).to(dt).float() * w.float()
+        n = n.to(dt).float()
+        c = cos[pos.long()][:, None, :].repeat(1, 1, 2)
+        s = sin[pos.long()][:, None, :].repeat(1, 1, 2)
+        r = n[..., :rot] * c + _rot_half(n[..., :rot]) * s
+        return torch.cat([r, n[..., rot:]], -1)
+
+    q_ref, k_ref, v_ref = ref(o[:, :Hq], qw), ref(o[:, Hq:Hq + Hkv], kw), o[:, Hq + Hkv:]
+    _close(qkv.view(T, -1, hd)[:, :Hq], q_ref, dt)
+    for t in range(T):
+        s, p = int(seq_of_tok[t]), int(pos[t])
+        page = int(page_table[s, p // 16])
+        _close(k_pool[page, :, p % 16], k_ref[t], dt)
+        _close(v_pool[page, :, p % 16], v_ref[t], dt)
+
+
+def test_mrope_axis_select():
+    from rhinoforge_b200.ops import kernels as K_
+    dt, hd, T = torch.float16, 128, 9
+    qkv = torch.randn(T, 3 * hd, device="cuda").to(dt)
+    orig = qkv.clone()
+    cos, sin = _rope_tables(256, hd, 1e6, "cuda")
+    pos = torch.randint(0, 200, (T, 3), device="cuda", dtype=torch.int32)
+    sec = [24, 20, 20]
+    axis = torch.zeros(hd // 2, dtype=torch.int8)
+    for dim, off in ((1, 1), (2, 2)):
+        axis[off:sec[dim] * 3:3] = dim
+    K_.qk_norm_rope_kv(qkv, 1, 1, hd, pos=pos, cos=cos, sin=sin, axis_of_freq=axis.cuda(), write_k_inplace=True)
+    idx = pos.long()[:, axis.long().cuda()]  # [T, hd/2]
+    f = torch.arange(hd // 2, device="cuda")
+    c = cos[idx, f].repeat(1, 2)
+    s = sin[idx, f].repeat(1, 2)
+    for h in range(2):
+        x = orig.float().view(T, 3, hd)[:, h]
+        _close(qkv.view(T, 3, hd)[:, h], x * c + _rot_half(x) * s, dt)
+
+
+def _sdpa_ref(q, k, v, mask):
+    # q [Hq, Lq, hd], k/v [Hkv, Lk, hd], mask [Lq, Lk] bool
+    G = q.shape[0] // k.shape[0]
+    k = k.repeat_interleave(G, 0)
+    v = v.repeat_interleave(G, 0)
+    s = (q.float() @ k.float().transpose(1, 2)) / math.sqrt(q.shape[-1])
+    s = s.masked_fill(~mask[None], float("-inf"))
+    p = torch.softmax(s, -1)
+    p = torch.nan_to_num(p)
+    return p @ v.float()
+
+
+def _paged(Hkv, hd, kv_lens, dt, extra_pages=3):
+    seqs = len(kv_lens)
+    maxp = max((l + 15) // 16 for l in kv_lens) + 1
+    total = seqs * maxp + extra_pages
+    perm = torch.randperm(total)[: seqs * maxp].to(torch.int32).view(seqs, maxp)
+    k_pool = torch.zeros(total, Hkv, 16, hd, device="cuda", dtype=dt)
+    v_pool = torch.zeros_like(k_pool)
+    ks, vs = [], []
+    for s, L in enumerate(kv_lens):
+        k = torch.randn(Hkv, L, hd, device="cuda").to(dt)
+        v = torch.randn(Hkv, L, hd, device="cuda").to(dt)
+        for t in range(L):
+            pg = int(perm[s, t // 16])
+            k_pool[pg, :, t % 16] = k[:, t]
+            v_pool[pg, :, t % 16] = v[:, t]
+        ks.append(k)
+        vs.append(v)
+    return k_pool, v_pool, perm.cuda().contiguous(), ks, vs
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("hd,Hq,Hkv", [(128, 8, 2), (64, 4, 4), (256, 8, 1)])
+def test_attn_prefill_paged_causal(dt, hd, Hq, Hkv, status):
+    from rhinoforge_b200.ops import kernels as K_
+    q_lens, kv_lens = [70, 33, 128], [70, 97, 128]
+    k_pool, v_pool, pt, ks, vs = _paged(Hkv, hd, kv_lens, dt)
+    q_start = [0, 70, 103]
+    Tq = sum(q_lens)
+    q = torch.randn(Tq, Hq * hd, device="cuda").to(dt)
+    out = torch.zeros_like(q)
+    i32 = lambda l: torch.tensor(l, dtype=torch.int32, device="cuda")
+    K_.attention_prefill(q, out, Hq=Hq, Hkv=Hkv, hd=hd, q_start=i32(q_start), q_len=i32(q_lens), kv_len=i32(kv_lens),
+                         max_q_len=max(q_lens), k_pool=k_pool, v_pool=v_pool, page_table=pt, causal=True,
+                         status=status)
+    for s in range(3):
+        Lq, Lk = q_lens[s], kv_lens[s]
+        qs = q[q_start[s]:q_start[s] + Lq].view(Lq, Hq, hd).transpose(0, 1)
+        qi = torch.arange(Lq, device="cuda")[:, None] + (Lk - Lq)
+        mask = torch.arange(Lk, device="cuda")[None] <= qi
+        ref = _sdpa_ref(qs, ks[s], vs[s], mask).transpose(0, 1).reshape(Lq, Hq * hd)
+        _close(out[q_start[s]:q_start[s] + Lq], ref, dt)
+
+
+@pytest.mark.parametrize("mode", ["bidir", "mask", "segments", "window"])
+def test_attn_prefill_contiguous_masks(mode, status):
+    from rhinoforge_b200.ops import kernels as K_
+    dt, hd, H = torch.float16, 64, 4
+    L = 201
+    qkv = torch.randn(L, 3 * H * hd, device="cuda").to(dt)
+    q, k, v = qkv[:, :H * hd], qkv[:, H * hd:2 * H * hd], qkv[:, 2 * H * hd:]
+    out = torch.zeros(L, H * hd, device="cuda", dtype=dt)
+    i32 = lambda l: torch.tensor(l, dtype=torch.int32, device="cuda")
+    kw = dict(Hq=H, Hkv=H, hd=hd, q_start=i32([0]), q_len=i32([L]), kv_len=i32([L]), max_q_len=L, k=k, v=v,
+              kv_start=i32([0]), causal=False, status=status)
+    full = torch.ones(L, L, dtype=torch.bool, device="cuda")
+    if mode == "bidir":
+        mask = full
+    elif mode == "mask":
+        mask = torch.rand(L, L, device="cuda") > 0.3
+        mask[:, 0] = True
+        kw["mask"] = mask.contiguous()
+    elif mode == "segments":
+        seg = (torch.arange(L, device="cuda") // 37).to(torch.int32)
+        mask = seg[:, None] == seg[None]
+        kw["seg_q"], kw["seg_k"] = seg, seg
+    else:
+        kw["causal"], kw["window"] = True, 48
+        i = torch.arange(L, device="cuda")
+        mask = (i[None] <= i[:, None]) & (i[None] > i[:, None] - 48)
+    K_.attention_prefill(q, out, **kw)
+    tr = lambda t: t.reshape(L, H, hd).transpose(0, 1)
+    ref = _sdpa_ref(tr(q), tr(k), tr(v), mask).transpose(0, 1).reshape(L, H * hd)
+    _close(out, ref, dt)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("hd,Hq,Hkv", [(128, 32, 8), (128, 8, 1), (64, 4, 2), (256, 8, 1)])
+@pytest.mark.parametrize("split", [False, True])
+def test_attn_decode_paged(dt, hd, Hq, Hkv, split, status):
+    from rhinoforge_b200.ops import kernels as K_
+    kv_lens = [1, 17, 300, 1025, 64]
+    k_pool, v_pool, pt, ks, vs = _paged(Hkv, hd, kv_lens, dt)
+    B = len(kv_lens)
+    q = torch.randn(B, Hq * hd, device="cuda").to(dt)
+    out = torch.zeros_like(q)
+    ws = K_.attn_decode_scratch(B, Hq, hd, "cuda") if split else None
+    K_.attention_decode(q, out, Hq=Hq, Hkv=Hkv, hd=hd, kv_len=torch.tensor(kv_lens, dtype=torch.int32, device="cuda"),
+                        max_kv_len=max(kv_lens), k_pool=k_pool, v_pool=v_pool, page_table=pt, ws=ws, status=status)
+    for s in range(B):
+        L = kv_lens[s]
+        ref = _sdpa_ref(q[s].view(Hq, 1, hd), ks[s], vs[s], torch.ones(1, L, dtype=torch.bool, device="cuda"))
+        _close(out[s], ref.reshape(Hq * hd), dt)
+
+
+def test_embedding_scatter_eltwise_cast_argmax():
+    from rhinoforge_b200.ops import kernels as K_
+    dt = torch.float16
+    table = torch.randn(1000, 256, device="cuda").to(dt)
+    ids = torch.tensor([3, 999, -1, 0, 17], dtype=torch.int32, device="cuda")
+    e = K_.embedding(table, ids, scale=2.0)
+    ref = table[ids.clamp(min=0).long()].float() * 2.0
+    ref[2] = 0
+    _close(e, ref, dt)
+    dst = torch.zeros(10, 256, device="cuda", dtype=dt)
+    K_.scatter_rows(dst, e, torch.tensor([9, 1, -1, 4, 0], dtype=torch.int32, device="cuda"))
+    assert torch.equal(dst[9], e[0]) and torch.equal(dst[0], e[4]) and dst[2].abs().sum() == 0
+    a, b = torch.randn(77, 256, device="cuda").to(dt), torch.randn(77, 256, device="cuda").to(dt)
+    _close(K_.eltwise("silu_mul", a, b), torch.nn.functional.silu(a.float()) * b.float(), dt)
+    _close(K_.eltwise("axpy", a, b, alpha=-0.1), a.float() - 0.1 * b.float(), dt)
+    _close(K_.eltwise("mul_row", a, b[0].contiguous()), a.float() * b[0].float(), dt)
+    u8 = torch.randint(0, 256, (3, 64), dtype=torch.uint8, device="cuda")
+    _close(K_.cast_u8(u8, dt, 1 / 127.5, -1.0), u8.float() / 127.5 - 1.0, dt)
+    logits = torch.randn(5, 151936, device="cuda").to(dt)
+    logits[2, 77] = 100.0
+    logits[3, 151935] = 100.0
+    ids2, vals = K_.argmax(logits, offset=10, return_vals=True)
+    assert torch.equal(ids2.long() - 10, logits.float().argmax(-1))
+    _close(vals, logits.float().max(-1).values, dt)
