@@ -80,6 +80,47 @@ class RfAttn(C.Structure):
     ]
 
 
+class RfStackConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("layers", "hidden", "Hq", "Hkv", "hd", "inter", "rot_dim", "norm_kind",
+                                         "mlp_kind")] + [("eps", C.c_float)] + \
+               [(n, C.c_int32) for n in ("qk_norm", "rope_before_norm", "gated_residual", "sandwich_norm", "paged_kv",
+                                         "causal", "window")] + [("attn_scale", C.c_float)] + \
+               [(n, C.c_int32) for n in ("true_hd", "dtype", "max_tokens", "max_seqs", "vocab_local", "vocab_offset",
+                                         "tp_world", "tp_rank", "weights_int8", "decode_gemv_max_m")]
+
+
+class RfLayerWeights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in (
+        "norm1_w", "norm1_b", "wqkv", "bqkv", "sqkv", "q_norm_w", "k_norm_w", "wo", "bo", "so", "norm2_w", "norm2_b",
+        "w_up", "b_up", "s_up", "w_down", "b_down", "s_down", "post_attn_norm_w", "post_mlp_norm_w", "k_pool",
+        "v_pool")]
+
+
+class RfStackComm(C.Structure):
+    _fields_ = [("recv", C.c_void_p), ("flags", C.c_void_p), ("state", C.c_void_p),
+                ("recv_half_bytes", C.c_uint64), ("flag_count", C.c_int32)]
+
+
+class RfStackForward(C.Structure):
+    _fields_ = [
+        ("hidden", C.c_void_p), ("tokens", C.c_int32), ("decode", C.c_int32),
+        ("pos", C.c_void_p), ("pos_stride", C.c_int32),
+        ("cos", C.c_void_p), ("sin", C.c_void_p), ("axis_of_freq", C.c_void_p),
+        ("seq_of_tok", C.c_void_p), ("cache_pos", C.c_void_p),
+        ("num_seqs", C.c_int32),
+        ("q_start", C.c_void_p), ("q_len", C.c_void_p), ("kv_start", C.c_void_p), ("kv_len", C.c_void_p),
+        ("max_q_len", C.c_int32), ("max_kv_len", C.c_int32),
+        ("page_table", C.c_void_p), ("pt_stride", C.c_int32), ("pool_pages", C.c_int64),
+        ("mask", C.c_void_p), ("mask_ld", C.c_int64), ("mask_seq_stride", C.c_int64),
+        ("seg_q", C.c_void_p), ("seg_k", C.c_void_p),
+        ("mod", C.c_void_p), ("rows_per_mod", C.c_int32),
+        ("layer_begin", C.c_int32), ("layer_end", C.c_int32),
+        ("deepstack", C.c_void_p), ("deepstack_rows", C.c_void_p), ("n_deepstack", C.c_int32),
+        ("n_deepstack_rows", C.c_int32),
+        ("taps", C.c_void_p), ("tap_layers", C.c_void_p), ("n_taps", C.c_int32),
+    ]
+
+
 def available() -> bool:
     return LIB_PATH.exists()
 
@@ -104,6 +145,15 @@ def lib() -> C.CDLL:
         l.rf_last_error.restype = C.c_char_p
         l.rf_argmax_scratch_bytes.restype = C.c_uint64
         l.rf_attn_decode_scratch_bytes.restype = C.c_uint64
+        l.rf_stack_create.restype = C.c_int64
+        l.rf_stack_arena_bytes.restype = C.c_uint64
+        l.rf_stack_status_ptr.restype = C.c_void_p
+        l.rf_kvpool_create.restype = C.c_int64
+        for fn in ("rf_stack_destroy", "rf_stack_set_layer", "rf_stack_set_head", "rf_stack_set_comm",
+                   "rf_stack_arena_bytes", "rf_stack_bind_arena", "rf_stack_status_ptr", "rf_stack_forward",
+                   "rf_stack_head", "rf_stack_final_norm", "rf_kvpool_destroy", "rf_kvpool_reserve",
+                   "rf_kvpool_release", "rf_kvpool_free_pages"):
+            getattr(l, fn).argtypes = None
         _lib = l
     return _lib
 

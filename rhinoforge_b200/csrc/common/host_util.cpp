@@ -3,6 +3,7 @@
 #include <cudaTypedefs.h>
 #include <stdarg.h>
 
+#include <atomic>
 #include <mutex>
 
 namespace rf {
@@ -70,6 +71,9 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int dtype, int elem_bytes, 
   return RF_OK;
 }
 
+static std::atomic<uint64_t> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -85,3 +89,4 @@ int sm_count() {
 
 extern "C" const char* rf_last_error(void) { return rf::g_last_error.c_str(); }
 extern "C" int rf_version(void) { return 100; }
+extern "C" uint64_t rf_launch_count(void) { return rf::g_launches.load(); }

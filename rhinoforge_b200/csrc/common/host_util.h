@@ -46,4 +46,7 @@ inline uint32_t next_pow2(uint32_t v) {
 
 int sm_count();
 
+// Number of kernel launches this library has enqueued (captured launches count once).
+void count_launch(int n = 1);
+
 }  // namespace rf

@@ -568,10 +568,12 @@ static int launch_decode(const RfAttn* a, AttnParams& p, cudaStream_t s) {
   dim3 grid(splits, a->Hkv, a->num_seqs);
   kfn<<<grid, 160, smem, s>>>(tmK, tmV, p);
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   if (splits > 1) {
     dim3 g2(a->Hq, a->num_seqs);
     attn_decode_combine_kernel<T><<<g2, HD < 128 ? HD : 128, 0, s>>>(p.ws_o, p.ws_lse, (T*)a->out, a->ldo, a->Hq, HD, splits);
     RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   }
   return RF_OK;
 }
@@ -597,6 +599,7 @@ static int launch_prefill(const RfAttn* a, AttnParams& p, cudaStream_t s) {
   dim3 grid(ceil_div(a->max_q_len, 64), a->Hq, a->num_seqs);
   kfn<<<grid, 160, smem, s>>>(tmQ, tmK, tmV, p);
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   return RF_OK;
 }
 

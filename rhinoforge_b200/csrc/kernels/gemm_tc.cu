@@ -8,9 +8,10 @@
 //    exactly once with no padded-token traffic; "normal" mode puts tokens on M;
 //  * "dual" mode keeps two accumulators (gate and up projection of the same
 //    output feature) and applies act(gate) * up in the epilogue (SwiGLU/GeGLU);
-//  * split-K spreads one output tile over several CTAs so that skinny decode
-//    GEMMs still fill 148 SMs; partials meet in an fp32 workspace and the last
-//    CTA to arrive reduces them in split order (deterministic);
+//  * split-K spreads one output tile over a thread-block CLUSTER (up to 8 CTAs
+//    along z) so that skinny decode GEMMs still fill 148 SMs; each CTA parks its
+//    fp32 partial in its own shared memory and the cluster reduces over
+//    distributed shared memory in split order (deterministic, no global scratch);
 //  * the epilogue can push its tile to every tensor-parallel peer over NVLink
 //    (plain peer stores), wait (bounded) for the peers' tiles and finish the
 //    all-reduce + residual in the same kernel.
@@ -29,7 +30,7 @@ namespace rf {
 constexpr int kBM = 128;          // MMA M (rows of operand A per CTA)
 constexpr int kBK = 64;           // K elements per smem stage (128 bytes)
 constexpr int kATileBytes = kBM * kBK * 2;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 8;   // ring depth (barrier slots); extra smem beyond it only backs the split-K partial
 
 struct GemmTcParams {
   void* out; int64_t ldo;
@@ -37,7 +38,7 @@ struct GemmTcParams {
   const void* bias; const void* scale; const float* row_scale;
   float* ws; uint32_t* sem; int32_t* status;
   int M, N;
-  int k_blocks, splits, bn, stages, act, dual_offset, tmem_cols;
+  int k_blocks, splits, bn, stages, act, dual_offset, tmem_cols, ctl_offset;
   int ar_world, ar_rank;
   void* const* ar_recv; uint32_t* const* ar_flags; uint32_t* ar_state;
   uint64_t ar_half_bytes;
@@ -49,7 +50,6 @@ struct alignas(8) GemmSmemCtl {
   uint64_t accum;
   uint32_t tmem_base;
   int32_t abort_flag;
-  int32_t is_last;
   uint32_t ar_call;
 };
 
@@ -68,7 +68,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   constexpr int kBTiles = (!SWAP && DUAL) ? 2 : 1;
   const int b_tile_bytes = bn * kBK * 2;
   const int stage_bytes = kATiles * kATileBytes + kBTiles * b_tile_bytes;
-  GemmSmemCtl* ctl = reinterpret_cast<GemmSmemCtl*>(smem + (size_t)p.stages * stage_bytes);
+  GemmSmemCtl* ctl = reinterpret_cast<GemmSmemCtl*>(smem + p.ctl_offset);
 
   const int a0 = blockIdx.x * kBM;
   const int b0 = blockIdx.y * bn;
@@ -84,7 +84,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     mbar_init(&ctl->accum, 1);
     ctl->abort_flag = 0;
-    ctl->is_last = 1;
     ctl->ar_call = (p.ar_world > 1) ? *reinterpret_cast<volatile uint32_t*>(p.ar_state) : 0u;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
@@ -185,10 +184,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
   constexpr int kAcc = DUAL ? 2 : 1;
 
-  // Split-K: park this CTA's partial in the workspace; the last CTA to arrive
-  // re-reads every split in order.
+  const T* bias = reinterpret_cast<const T*>(p.bias);
+  const T* scale = reinterpret_cast<const T*>(p.scale);
+  const T* resid = reinterpret_cast<const T*>(p.residual);
+  T* out = reinterpret_cast<T*>(p.out);
+  const bool use_bias = bias != nullptr && (p.ar_world <= 1 || p.ar_rank == 0);
+  const uint32_t call = ctl->ar_call;
+  const uint64_t slot_off = (uint64_t)(call & 1u) * p.ar_half_bytes;
+  const uint32_t crank = p.splits > 1 ? cluster_ctarank() : 0u;
+
+  // per-element epilogue math shared by both paths
+  auto finish = [&](int tok, int n, float vg, float vu) -> float {
+    if (p.row_scale) {
+      const float rs = p.row_scale[tok];
+      vg *= rs;
+      vu *= rs;
+    }
+    if (scale) {
+      vg *= Num<T>::to_f(scale[n]);
+      if (DUAL) vu *= Num<T>::to_f(scale[p.dual_offset + n]);
+    }
+    if (use_bias) {
+      vg += Num<T>::to_f(bias[n]);
+      if (DUAL) vu += Num<T>::to_f(bias[p.dual_offset + n]);
+    }
+    return apply_act(p.act, vg, vu);
+  };
+  auto push_partial = [&](int tok, int n, float v) {
+    for (int dst = 0; dst < p.ar_world; ++dst) {
+      float* rb = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ar_recv[dst]) + slot_off) +
+                  (size_t)p.ar_rank * M * N;
+      rb[(size_t)tok * N + n] = v;
+    }
+  };
+
+  bool aborted = __syncthreads_or(*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag) != 0);
+  const int ncols = min(bn, (SWAP ? M : N) - b0);  // valid accumulator columns of this tile
+
   if (p.splits > 1) {
-    if (have_acc) {
+    // ---- split-K: the CTAs of one output tile form a cluster (cluster dim z =
+    // splits).  Each parks its fp32 partial in its own shared memory
+    // ([column][lane], conflict-free), then CTA r reduces columns r, r+S, ...
+    // over distributed shared memory in split order and finishes them.
+    float* part = reinterpret_cast<float*>(smem);
+    if (!aborted) {
       for (int c = 0; c < bn; c += 16) {
         uint32_t rg[16], ru[16];
         tmem_ld16(trow + c, rg);
@@ -196,103 +235,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const int tok = SWAP ? (b0 + c + j) : a_idx;
-          const int n = SWAP ? a_idx : (b0 + c + j);
-          if (tok < M && n < N) {
-            const size_t o = ((size_t)(z * kAcc) * M + tok) * N + n;
-            p.ws[o] = __uint_as_float(rg[j]);
-            if (DUAL) p.ws[o + (size_t)M * N] = __uint_as_float(ru[j]);
+          part[(c + j) * kBM + tid] = __uint_as_float(rg[j]);
+          if (DUAL) part[(bn + c + j) * kBM + tid] = __uint_as_float(ru[j]);
+        }
+      }
+    }
+    cluster_sync_all();
+    if (!aborted) {
+      const uint32_t my_part = smem_u32(part);
+      for (int c = (int)crank; c < ncols; c += p.splits) {
+        float g = 0.f, u = 0.f;
+        for (int s = 0; s < p.splits; ++s) {
+          const uint32_t base = dsmem_addr(my_part, (uint32_t)s);
+          g += ld_dsmem_f32(base + (uint32_t)(c * kBM + tid) * 4u);
+          if (DUAL) u += ld_dsmem_f32(base + (uint32_t)((bn + c) * kBM + tid) * 4u);
+        }
+        const int tok = SWAP ? (b0 + c) : a_idx;
+        const int n = SWAP ? a_idx : (b0 + c);
+        if (tok < M && n < N) {
+          const float v = finish(tok, n, g, u);
+          if (p.ar_world > 1) {
+            push_partial(tok, n, v);
+          } else {
+            float r = v;
+            if (resid) r += Num<T>::to_f(resid[(size_t)tok * p.ldr + n]);
+            out[(size_t)tok * p.ldo + n] = Num<T>::from_f(r);
           }
         }
       }
     }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const uint32_t prev = atomicAdd(&p.sem[tile_id], 1u);
-      const int last = (prev == (uint32_t)(p.splits - 1));
-      if (last) p.sem[tile_id] = 0u;
-      ctl->is_last = last;
-    }
-    __syncthreads();
-    __threadfence();
-  }
-
-  const bool finisher = ctl->is_last != 0;
-  const bool aborted = *reinterpret_cast<volatile int32_t*>(&ctl->abort_flag) != 0;
-  if (finisher && !aborted) {
-    const T* bias = reinterpret_cast<const T*>(p.bias);
-    const T* scale = reinterpret_cast<const T*>(p.scale);
-    const T* resid = reinterpret_cast<const T*>(p.residual);
-    T* out = reinterpret_cast<T*>(p.out);
-    const bool use_bias = bias != nullptr && (p.ar_world <= 1 || p.ar_rank == 0);
-    const uint32_t call = ctl->ar_call;
-    const uint64_t slot_off = (uint64_t)(call & 1u) * p.ar_half_bytes;
-
+  } else if (!aborted) {
     for (int c = 0; c < bn; c += 16) {
-      float g[16], u[16];
-      if (p.splits > 1) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int tok = SWAP ? (b0 + c + j) : a_idx;
-          const int n = SWAP ? a_idx : (b0 + c + j);
-          float sg = 0.f, su = 0.f;
-          if (tok < M && n < N) {
-            for (int s = 0; s < p.splits; ++s) {
-              const size_t o = ((size_t)(s * kAcc) * M + tok) * N + n;
-              sg += __ldcg(p.ws + o);
-              if (DUAL) su += __ldcg(p.ws + o + (size_t)M * N);
-            }
-          }
-          g[j] = sg;
-          u[j] = su;
-        }
-      } else {
-        uint32_t rg[16], ru[16];
-        tmem_ld16(trow + c, rg);
-        if (DUAL) tmem_ld16(trow + bn + c, ru);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          g[j] = __uint_as_float(rg[j]);
-          u[j] = DUAL ? __uint_as_float(ru[j]) : 0.f;
-        }
-      }
-      // scale / bias / activation
+      uint32_t rg[16], ru[16];
+      tmem_ld16(trow + c, rg);
+      if (DUAL) tmem_ld16(trow + bn + c, ru);
+      tmem_ld_wait();
       float v[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const int tok = SWAP ? (b0 + c + j) : a_idx;
         const int n = SWAP ? a_idx : (b0 + c + j);
-        float vg = g[j], vu = u[j];
-        if (tok < M && n < N) {
-          if (p.row_scale) {
-            const float rs = p.row_scale[tok];
-            vg *= rs;
-            vu *= rs;
-          }
-          if (scale) {
-            vg *= Num<T>::to_f(scale[n]);
-            if (DUAL) vu *= Num<T>::to_f(scale[p.dual_offset + n]);
-          }
-          if (use_bias) {
-            vg += Num<T>::to_f(bias[n]);
-            if (DUAL) vu += Num<T>::to_f(bias[p.dual_offset + n]);
-          }
-        }
-        v[j] = apply_act(p.act, vg, vu);
+        const float vg = __uint_as_float(rg[j]);
+        const float vu = DUAL ? __uint_as_float(ru[j]) : 0.f;
+        v[j] = (tok < M && n < N) ? finish(tok, n, vg, vu) : 0.f;
       }
       if (p.ar_world > 1) {
-        // push this rank's partial tile into every rank's receive buffer
-        for (int dst = 0; dst < p.ar_world; ++dst) {
-          float* rb = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ar_recv[dst]) + slot_off) +
-                      (size_t)p.ar_rank * M * N;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int tok = SWAP ? (b0 + c + j) : a_idx;
-            const int n = SWAP ? a_idx : (b0 + c + j);
-            if (tok < M && n < N) rb[(size_t)tok * N + n] = v[j];
-          }
+        for (int j = 0; j < 16; ++j) {
+          const int tok = SWAP ? (b0 + c + j) : a_idx;
+          const int n = SWAP ? a_idx : (b0 + c + j);
+          if (tok < M && n < N) push_partial(tok, n, v[j]);
         }
       } else if (SWAP) {
 #pragma unroll
@@ -335,55 +327,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       }
     }
+  }
 
-    if (p.ar_world > 1) {
-      // publish, wait for every rank's tile (bounded), then reduce in rank order
-      __threadfence_system();
-      __syncthreads();
-      const uint32_t want = call + 1u;
-      if (tid < p.ar_world)
-        st_release_sys(p.ar_flags[tid] + (size_t)tile_id * p.ar_world + p.ar_rank, want);
-      if (tid < p.ar_world) {
-        const uint32_t* mine = p.ar_flags[p.ar_rank] + (size_t)tile_id * p.ar_world + tid;
-        if (!wait_flag_ge_sys(mine, want)) {
-          report_status(p.status, kStatusPeerTimeout, kTagGemmAr, tid);
-          ctl->abort_flag = 1;
-        }
+  if (p.ar_world > 1) {
+    // Publish this CTA's share of the tile to every rank, wait (bounded) for
+    // every rank's share, then reduce in rank order and add the residual.
+    // Flags are per (tile, cluster rank, source rank) and carry the call number.
+    __threadfence_system();
+    __syncthreads();
+    const uint32_t want = call + 1u;
+    const size_t fbase = ((size_t)tile_id * 8 + crank) * p.ar_world;
+    if (tid < p.ar_world && !aborted) st_release_sys(p.ar_flags[tid] + fbase + p.ar_rank, want);
+    if (tid < p.ar_world && !aborted) {
+      if (!wait_flag_ge_sys(p.ar_flags[p.ar_rank] + fbase + tid, want)) {
+        report_status(p.status, kStatusPeerTimeout, kTagGemmAr, tid);
+        ctl->abort_flag = 1;
       }
-      __syncthreads();
-      if (!*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag)) {
-        const float* rb = reinterpret_cast<const float*>(
-            reinterpret_cast<const uint8_t*>(p.ar_recv[p.ar_rank]) + slot_off);
-        for (int c = 0; c < bn; c += 16) {
-#pragma unroll 4
-          for (int j = 0; j < 16; ++j) {
-            const int tok = SWAP ? (b0 + c + j) : a_idx;
-            const int n = SWAP ? a_idx : (b0 + c + j);
-            if (tok < M && n < N) {
-              float acc = 0.f;
-              for (int r = 0; r < p.ar_world; ++r)
-                acc += __ldcg(rb + ((size_t)r * M + tok) * N + n);
-              if (resid) acc += Num<T>::to_f(resid[(size_t)tok * p.ldr + n]);
-              out[(size_t)tok * p.ldo + n] = Num<T>::from_f(acc);
-            }
-          }
+    }
+    aborted = __syncthreads_or(*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag) != 0);
+    if (!aborted) {
+      const float* rb = reinterpret_cast<const float*>(
+          reinterpret_cast<const uint8_t*>(p.ar_recv[p.ar_rank]) + slot_off);
+      const int cstep = p.splits > 1 ? p.splits : 1;
+      for (int c = (int)crank; c < ncols; c += cstep) {
+        const int tok = SWAP ? (b0 + c) : a_idx;
+        const int n = SWAP ? a_idx : (b0 + c);
+        if (tok < M && n < N) {
+          float acc = 0.f;
+          for (int r = 0; r < p.ar_world; ++r) acc += __ldcg(rb + ((size_t)r * M + tok) * N + n);
+          if (resid) acc += Num<T>::to_f(resid[(size_t)tok * p.ldr + n]);
+          out[(size_t)tok * p.ldo + n] = Num<T>::from_f(acc);
         }
       }
     }
-  }
-  if (p.ar_world > 1 && finisher) {
-    // the last tile to finish advances the call counter for the next launch
+    // the last CTA to finish advances the call counter for the next launch
     __syncthreads();
     if (tid == 0) {
-      const uint32_t tiles = gridDim.x * gridDim.y;
+      const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
       const uint32_t done = atomicAdd(p.ar_state + 1, 1u);
-      if (done == tiles - 1u) {
+      if (done == total - 1u) {
         p.ar_state[1] = 0u;
         __threadfence();
-        p.ar_state[0] = ctl->ar_call + 1u;
+        p.ar_state[0] = call + 1u;
       }
     }
   }
+  // peers may still be reading this CTA's partial over DSMEM
+  if (p.splits > 1) cluster_sync_all();
 
   // ----------------------------------------------------------- teardown ----
   tc_fence_before_sync();
@@ -393,7 +383,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
 // ------------------------------------------------------------ host side ----
 struct GemmPlan {
-  int swap, bn, splits, stages, tmem_cols, grid_x, grid_y, k_blocks;
+  int swap, bn, splits, stages, tmem_cols, grid_x, grid_y, k_blocks, ctl_offset;
   size_t smem_bytes;
   uint64_t ws_bytes;
   int sem_count;
@@ -426,19 +416,20 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   int splits = 1;
   if (g->force_splits > 0) {
     splits = g->force_splits;
-  } else if (g->ws != nullptr || g->ws_bytes == ~0ull) {
+  } else {
     const int target = 2 * sm_count();
     if (tiles < target) {
       splits = target / tiles;
       const int max_by_k = std::max(1, pl->k_blocks / 4);
-      splits = std::min(std::min(splits, max_by_k), 16);
+      splits = std::min(std::min(splits, max_by_k), 8);
       if (splits < 1) splits = 1;
     }
   }
+  if (splits > 8) splits = 8;  // portable cluster size
   if (splits > pl->k_blocks) splits = pl->k_blocks;
   pl->splits = splits;
-  pl->ws_bytes = splits > 1 ? (uint64_t)splits * (dual ? 2 : 1) * g->M * g->N * sizeof(float) : 0;
-  pl->sem_count = splits > 1 ? tiles : 0;
+  pl->ws_bytes = 0;
+  pl->sem_count = 0;
 
   const int a_tiles = (swap && dual) ? 2 : 1, b_tiles = (!swap && dual) ? 2 : 1;
   const int stage_bytes = a_tiles * kATileBytes + b_tiles * pl->bn * kBK * 2;
@@ -448,8 +439,16 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   stages = std::min(stages, kMaxStages);
   stages = std::min(stages, std::max(2, ceil_div(pl->k_blocks, splits)));
   if (stages < 2) return fail(RF_ERR_UNSUPPORTED, "GEMM tile does not fit in shared memory");
+  // the split-K partial ([columns][128] fp32 per accumulator) reuses the stage ring
+  int part_bytes = pl->splits > 1 ? pl->bn * (dual ? 2 : 1) * kBM * 4 : 0;
+  if ((size_t)std::max(stages * stage_bytes, part_bytes) + ctl_bytes > 227 * 1024) {
+    if (g->force_splits > 1) return fail(RF_ERR_UNSUPPORTED, "split-K partial does not fit in shared memory");
+    pl->splits = 1;
+    part_bytes = 0;
+  }
   pl->stages = stages;
-  pl->smem_bytes = (size_t)stages * stage_bytes + ctl_bytes;
+  pl->ctl_offset = round_up(std::max(stages * stage_bytes, part_bytes), 1024);
+  pl->smem_bytes = (size_t)pl->ctl_offset + ctl_bytes;
   return RF_OK;
 }
 
@@ -482,14 +481,25 @@ static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream)
   p.bias = g->bias; p.scale = g->scale; p.row_scale = g->row_scale;
   p.ws = g->ws; p.sem = g->sem; p.status = g->status;
   p.M = g->M; p.N = g->N;
-  p.k_blocks = pl.k_blocks; p.splits = pl.splits; p.bn = pl.bn; p.stages = pl.stages;
+  p.k_blocks = pl.k_blocks; p.splits = pl.splits; p.bn = pl.bn; p.stages = pl.stages; p.ctl_offset = pl.ctl_offset;
   p.act = g->act; p.dual_offset = g->dual_offset; p.tmem_cols = pl.tmem_cols;
   p.ar_world = g->ar_world; p.ar_rank = g->ar_rank;
   p.ar_recv = g->ar_recv; p.ar_flags = g->ar_flags; p.ar_state = g->ar_state;
   p.ar_half_bytes = g->ar_recv_bytes;
-  dim3 grid(pl.grid_x, pl.grid_y, pl.splits);
-  kfn<<<grid, 128, pl.smem_bytes, stream>>>(tmA, tmB, p);
-  RF_CUDA_CHECK(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pl.grid_x, pl.grid_y, pl.splits);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = (unsigned)pl.splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  RF_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kfn, tmA, tmB, p));
+  ::rf::count_launch();
   return RF_OK;
 }
 
@@ -518,10 +528,8 @@ using namespace rf;
 extern "C" int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem_count) {
   int rc = check_gemm(g);
   if (rc) return rc;
-  RfGemm t = *g;
-  if (t.ws == nullptr) t.ws_bytes = ~0ull;  // "assume scratch will be provided"
   GemmPlan pl;
-  rc = plan_gemm(&t, &pl);
+  rc = plan_gemm(g, &pl);
   if (rc) return rc;
   if (ws_bytes) *ws_bytes = pl.ws_bytes;
   if (sem_count) *sem_count = pl.sem_count;
@@ -535,16 +543,9 @@ extern "C" int rf_gemm(const RfGemm* g, rf_stream_t stream_) {
   GemmPlan pl;
   rc = plan_gemm(g, &pl);
   if (rc) return rc;
-  if (pl.splits > 1) {
-    RF_REQUIRE(g->ws && g->sem, "split-K needs ws and sem");
-    RF_REQUIRE(pl.ws_bytes <= g->ws_bytes, "split-K workspace too small: need %llu B, have %llu B",
-               (unsigned long long)pl.ws_bytes, (unsigned long long)g->ws_bytes);
-    RF_REQUIRE(pl.sem_count <= g->sem_count, "split-K needs %d semaphores, have %d", pl.sem_count,
-               g->sem_count);
-  }
   if (g->ar_world > 1)
-    RF_REQUIRE(pl.grid_x * pl.grid_y * g->ar_world <= g->ar_flag_count,
-               "all-reduce needs %d flags, have %d", pl.grid_x * pl.grid_y * g->ar_world,
+    RF_REQUIRE(pl.grid_x * pl.grid_y * 8 * g->ar_world <= g->ar_flag_count,
+               "all-reduce needs %d flags, have %d", pl.grid_x * pl.grid_y * 8 * g->ar_world,
                g->ar_flag_count);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const bool dual = g->dual_offset > 0;

@@ -136,6 +136,7 @@ static int launch_gemv(const GemvParams& p, cudaStream_t s) {
   else if (p.M <= 4) gemv_kernel<T, 4, I8><<<blocks, wpb * 32, 0, s>>>(p);
   else gemv_kernel<T, 8, I8><<<blocks, wpb * 32, 0, s>>>(p);
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   return RF_OK;
 }
 

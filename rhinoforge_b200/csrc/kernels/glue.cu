@@ -193,6 +193,7 @@ extern "C" int rf_embedding(const void* table, const int32_t* ids, void* out, in
     RF_DISPATCH_T(dtype, embedding_kernel<T><<<n_ids, 128, 0, s>>>((const T*)table, ids, (T*)out, H, ldo, scale));
   }
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   return RF_OK;
 }
 
@@ -204,6 +205,7 @@ extern "C" int rf_scatter_rows(void* dst, const void* src, const int32_t* rows, 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   RF_DISPATCH_T(dtype, scatter_rows_kernel<T><<<n, 128, 0, s>>>((T*)dst, (const T*)src, rows, H, ldd, lds, accumulate));
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   return RF_OK;
 }
 
@@ -219,6 +221,7 @@ extern "C" int rf_eltwise(int op, const void* a, const void* b, void* out, int64
   const int blocks = (int)(((n + 7) / 8 + threads - 1) / threads);
   RF_DISPATCH_T(dtype, eltwise_kernel<T><<<blocks, threads, 0, s>>>(op, (const T*)a, (const T*)b, (T*)out, n, b_period, alpha));
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   return RF_OK;
 }
 
@@ -231,6 +234,7 @@ extern "C" int rf_cast_u8_f16(const uint8_t* src, void* dst, int64_t n, float sc
   const int blocks = (int)((n + threads - 1) / threads);
   RF_DISPATCH_T(dtype, cast_u8_kernel<T><<<blocks, threads, 0, s>>>(src, (T*)dst, n, scale, shift));
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   return RF_OK;
 }
 
@@ -251,5 +255,6 @@ extern "C" int rf_argmax(const void* logits, int rows, int V, int64_t ld, int32_
   RF_DISPATCH_T(dtype, argmax_stage1<T><<<g1, 256, 0, s>>>((const T*)logits, V, ld, (ArgPair*)scratch, chunks));
   argmax_stage2<<<rows, 128, 0, s>>>((const ArgPair*)scratch, chunks, out_ids, out_vals, offset);
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   return RF_OK;
 }

@@ -180,6 +180,7 @@ extern "C" int rf_rmsnorm(const void* x, const void* residual, const void* w, vo
         (__nv_bfloat16*)y, (__nv_bfloat16*)residual_out, (const __nv_bfloat16*)mod, rows_per_mod,
         H, ldx, ldy, eps, mode);
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   return RF_OK;
 }
 
@@ -199,6 +200,7 @@ extern "C" int rf_layernorm(const void* x, const void* w, const void* b, void* y
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b,
         (__nv_bfloat16*)y, H, ldx, ldy, eps);
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   return RF_OK;
 }
 
@@ -215,6 +217,7 @@ extern "C" int rf_l2norm(const void* x, void* y, int rows, int H, float eps, flo
     l2norm_kernel<__nv_bfloat16><<<blocks, wpb * 32, 0, s>>>((const __nv_bfloat16*)x,
                                                              (__nv_bfloat16*)y, rows, H, eps, out_scale);
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   return RF_OK;
 }
 
@@ -234,5 +237,6 @@ extern "C" int rf_gated_residual(void* x, const void* y, const void* mod, int ro
     gated_residual_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>(
         (__nv_bfloat16*)x, (const __nv_bfloat16*)y, (const __nv_bfloat16*)mod, rows_per_mod, H, total);
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   return RF_OK;
 }

@@ -116,5 +116,6 @@ extern "C" int rf_qk_norm_rope_kv(const RfRopeKv* a, rf_stream_t stream) {
   else
     qk_norm_rope_kv_kernel<__nv_bfloat16><<<a->tokens, warps * 32, smem, s>>>(*a);
   RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
   return RF_OK;
 }

@@ -1,0 +1,391 @@
+// Transformer-stack runtime (see stack.h).  Host-side C++ only: every device
+// operation is one of the kernels in ../kernels, enqueued on the caller's stream.
+#include "stack.h"
+
+#include <algorithm>
+#include <memory>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "../common/dtype.cuh"
+#include "../common/host_util.h"
+#include "../common/status.h"
+#include "../runtime/handle_registry.h"
+
+namespace rf {
+
+struct Stack {
+  RfStackConfig cfg;
+  std::vector<RfLayerWeights> layers;
+  const void* final_norm_w = nullptr;
+  const void* final_norm_b = nullptr;
+  const void* w_lm = nullptr;
+  const void* s_lm = nullptr;
+  RfStackComm comm{};
+  bool has_comm = false;
+  // arena
+  uint8_t* base = nullptr;
+  uint64_t bytes = 0;
+  uint64_t off_xn = 0, off_attn = 0, off_tmp = 0, off_wide = 0, off_head_xn = 0, off_logits = 0,
+           off_argmax = 0, off_attn_ws = 0, off_status = 0, total = 0;
+  uint64_t attn_ws_bytes = 0, argmax_bytes = 0;
+
+  int qkv_dim() const { return (cfg.Hq + 2 * cfg.Hkv) * cfg.hd; }
+  bool glu() const { return cfg.mlp_kind == RF_MLP_SWIGLU || cfg.mlp_kind == RF_MLP_GEGLU_TANH; }
+
+  void plan() {
+    auto al = [](uint64_t v) { return (v + 1023) & ~uint64_t(1023); };
+    const uint64_t T = (uint64_t)cfg.max_tokens, e = 2;
+    uint64_t o = 0;
+    off_xn = o; o += al(T * cfg.hidden * e);
+    off_attn = o; o += al(T * cfg.Hq * cfg.hd * e);
+    off_tmp = o; o += al(T * cfg.hidden * e);
+    off_wide = o; o += al(T * std::max<uint64_t>(qkv_dim(), cfg.inter) * e);
+    off_head_xn = o; o += al((uint64_t)cfg.max_seqs * cfg.hidden * e);
+    off_logits = o; o += al((uint64_t)cfg.max_seqs * std::max(cfg.vocab_local, 1) * e);
+    argmax_bytes = rf_argmax_scratch_bytes(cfg.max_seqs, std::max(cfg.vocab_local, 1));
+    off_argmax = o; o += al(argmax_bytes);
+    attn_ws_bytes = cfg.paged_kv ? rf_attn_decode_scratch_bytes(cfg.max_seqs, cfg.Hq, cfg.hd) : 0;
+    off_attn_ws = o; o += al(attn_ws_bytes);
+    off_status = o; o += al(kStatusWords * sizeof(int32_t));
+    total = o;
+  }
+  template <typename P = void> P* at(uint64_t off) const { return reinterpret_cast<P*>(base + off); }
+  int32_t* status() const { return base ? at<int32_t>(off_status) : nullptr; }
+};
+
+static HandleRegistry<Stack>& registry() {
+  static HandleRegistry<Stack> r;
+  return r;
+}
+
+static int act_of(int mlp_kind) {
+  switch (mlp_kind) {
+    case RF_MLP_SWIGLU: return kActSiluMul;
+    case RF_MLP_GEGLU_TANH: return kActGeluTanhMul;
+    case RF_MLP_GELU_TANH: return kActGeluTanh;
+    case RF_MLP_GELU_ERF: return kActGeluErf;
+    case RF_MLP_SILU: return kActSilu;
+  }
+  return kActNone;
+}
+
+// One linear layer: picks GEMV / tcgen05 GEMM / W8A16 and wires the fused all-reduce.
+static int linear(const Stack& s, const void* x, int64_t ldx, const void* w, const void* scale,
+                  const void* bias, void* out, int64_t ldo, const void* residual, int64_t ldr, int M,
+                  int N, int K, int act, int dual_offset, bool all_reduce, cudaStream_t st) {
+  RfGemm g = {};
+  g.x = x; g.ldx = ldx; g.w = w; g.ldw = K; g.out = out; g.ldo = ldo;
+  g.residual = residual; g.ldr = ldr; g.bias = bias; g.scale = scale;
+  g.M = M; g.N = N; g.K = K; g.dtype = s.cfg.dtype; g.act = act; g.dual_offset = dual_offset;
+  g.w_int8 = s.cfg.weights_int8 && scale != nullptr;
+  g.status = s.status();
+  g.force_swap = -1;
+  const bool ar = all_reduce && s.cfg.tp_world > 1;
+  if (ar) {
+    if (!s.has_comm) return fail(RF_ERR_STATE, "tensor-parallel stack has no comm buffers bound");
+    g.ar_world = s.cfg.tp_world; g.ar_rank = s.cfg.tp_rank;
+    g.ar_recv = s.comm.recv; g.ar_flags = s.comm.flags; g.ar_state = s.comm.state;
+    g.ar_recv_bytes = s.comm.recv_half_bytes; g.ar_flag_count = s.comm.flag_count;
+  }
+  if (!ar && M <= 8 && (M <= s.cfg.decode_gemv_max_m) && K % (g.w_int8 ? 16 : 8) == 0) return rf_gemv(&g, st);
+  if (g.w_int8) return rf_gemm_w8a16(&g, st);
+  return rf_gemm(&g, st);
+}
+
+static int norm(const Stack& s, const void* x, const void* w, const void* b, void* y, int rows,
+                const void* mod, int rows_per_mod, cudaStream_t st) {
+  const int H = s.cfg.hidden;
+  switch (s.cfg.norm_kind) {
+    case RF_NORM_LAYERNORM:
+      return rf_layernorm(x, w, b, y, rows, H, H, H, s.cfg.eps, s.cfg.dtype, st);
+    case RF_NORM_ADARMS:
+      return rf_rmsnorm(x, nullptr, nullptr, y, nullptr, mod, rows_per_mod, rows, H, H, H, s.cfg.eps, 0,
+                        s.cfg.dtype, st);
+    case RF_NORM_RMS_GEMMA:
+      return rf_rmsnorm(x, nullptr, w, y, nullptr, nullptr, 1, rows, H, H, H, s.cfg.eps, 1, s.cfg.dtype, st);
+    default:
+      return rf_rmsnorm(x, nullptr, w, y, nullptr, nullptr, 1, rows, H, H, H, s.cfg.eps, 0, s.cfg.dtype, st);
+  }
+}
+
+static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
+  const RfStackConfig& c = s.cfg;
+  RF_REQUIRE(s.base != nullptr, "stack arena is not bound");
+  RF_REQUIRE(f.hidden && f.tokens >= 0 && f.tokens <= c.max_tokens, "forward: %d tokens (max %d)", f.tokens, c.max_tokens);
+  RF_REQUIRE(f.num_seqs > 0 && f.num_seqs <= c.max_seqs, "forward: %d sequences (max %d)", f.num_seqs, c.max_seqs);
+  if (f.tokens == 0) return RF_OK;
+  if (c.norm_kind == RF_NORM_ADARMS) RF_REQUIRE(f.mod && f.rows_per_mod > 0, "adaRMS stack needs mod");
+  const int T = f.tokens, H = c.hidden, QD = s.qkv_dim(), AD = c.Hq * c.hd, I = c.inter;
+  const int lb = f.layer_end > 0 ? f.layer_begin : 0, le = f.layer_end > 0 ? f.layer_end : c.layers;
+  void* xn = s.at(s.off_xn);
+  void* attn = s.at(s.off_attn);
+  void* tmp = s.at(s.off_tmp);
+  void* wide = s.at(s.off_wide);
+  const size_t esz = 2;
+  const int nmods = c.norm_kind == RF_NORM_ADARMS ? T / f.rows_per_mod : 0;
+  const bool side = c.gated_residual || c.sandwich_norm;  // sublayer output goes to tmp first
+  int rc;
+
+  for (int l = lb; l < le; ++l) {
+    const RfLayerWeights& w = s.layers[l];
+    const uint8_t* mod1 = f.mod ? (const uint8_t*)f.mod + ((size_t)(l * 2 + 0) * nmods) * 3 * H * esz : nullptr;
+    const uint8_t* mod2 = f.mod ? (const uint8_t*)f.mod + ((size_t)(l * 2 + 1) * nmods) * 3 * H * esz : nullptr;
+    // ---- attention block
+    rc = norm(s, f.hidden, w.norm1_w, w.norm1_b, xn, T, mod1, f.rows_per_mod, st);
+    if (rc) return rc;
+    rc = linear(s, xn, H, w.wqkv, w.sqkv, w.bqkv, wide, QD, nullptr, 0, T, QD, H, kActNone, 0, false, st);
+    if (rc) return rc;
+    {
+      RfRopeKv a = {};
+      a.qkv = wide; a.ld = QD; a.tokens = T; a.Hq = c.Hq; a.Hkv = c.Hkv; a.hd = c.hd;
+      a.rot_dim = f.cos ? c.rot_dim : 0;
+      a.q_norm_w = c.qk_norm ? w.q_norm_w : nullptr;
+      a.k_norm_w = c.qk_norm ? w.k_norm_w : nullptr;
+      a.eps = c.eps; a.norm_mode = c.norm_kind == RF_NORM_RMS_GEMMA ? 1 : 0;
+      a.cos = f.cos; a.sin = f.sin; a.pos = f.pos; a.pos_stride = f.pos_stride > 0 ? f.pos_stride : 1;
+      a.axis_of_freq = f.axis_of_freq;
+      if (c.paged_kv) {
+        a.k_pool = w.k_pool; a.v_pool = w.v_pool; a.page_table = f.page_table; a.pt_stride = f.pt_stride;
+        a.seq_of_tok = f.seq_of_tok; a.cache_pos = f.cache_pos;
+      } else {
+        a.write_k_inplace = 1;
+      }
+      a.rope_before_norm = c.rope_before_norm; a.dtype = c.dtype;
+      const bool needed = a.q_norm_w || a.rot_dim > 0 || c.paged_kv;
+      if (needed) {
+        RF_REQUIRE(f.pos != nullptr, "forward: positions are required");
+        rc = rf_qk_norm_rope_kv(&a, st);
+        if (rc) return rc;
+      }
+    }
+    {
+      RfAttn a = {};
+      a.q = wide; a.ldq = QD; a.out = attn; a.ldo = AD; a.q_rows_total = T;
+      a.num_seqs = f.num_seqs; a.Hq = c.Hq; a.Hkv = c.Hkv; a.hd = c.hd;
+      a.kv_len = f.kv_len; a.max_kv_len = f.max_kv_len; a.max_q_len = f.max_q_len;
+      a.scale = c.attn_scale > 0.f ? c.attn_scale : 1.0f / sqrtf((float)(c.true_hd > 0 ? c.true_hd : c.hd));
+      a.status = s.status(); a.dtype = c.dtype;
+      if (c.paged_kv) {
+        a.k_pool = w.k_pool; a.v_pool = w.v_pool; a.pool_pages = f.pool_pages;
+        a.page_table = f.page_table; a.pt_stride = f.pt_stride;
+      } else {
+        a.k = (const uint8_t*)wide + (size_t)c.Hq * c.hd * esz;
+        a.v = (const uint8_t*)wide + (size_t)(c.Hq + c.Hkv) * c.hd * esz;
+        a.ldk = QD; a.ldv = QD; a.kv_rows_total = T;
+        a.kv_start = f.kv_start ? f.kv_start : f.q_start;
+      }
+      if (f.decode) {
+        RF_REQUIRE(c.paged_kv, "decode needs a paged KV pool");
+        a.ws = s.at<float>(s.off_attn_ws); a.ws_bytes = s.attn_ws_bytes;
+        rc = rf_attn_decode(&a, st);
+      } else {
+        a.q_start = f.q_start; a.q_len = f.q_len;
+        a.causal = c.causal; a.window = c.window;
+        a.mask = f.mask; a.mask_ld = f.mask_ld; a.mask_seq_stride = f.mask_seq_stride;
+        a.seg_q = f.seg_q; a.seg_k = f.seg_k;
+        rc = rf_attn_prefill(&a, st);
+      }
+      if (rc) return rc;
+    }
+    if (!side) {
+      rc = linear(s, attn, AD, w.wo, w.so, w.bo, f.hidden, H, f.hidden, H, T, H, AD, kActNone, 0, true, st);
+      if (rc) return rc;
+    } else {
+      rc = linear(s, attn, AD, w.wo, w.so, w.bo, tmp, H, nullptr, 0, T, H, AD, kActNone, 0, true, st);
+      if (rc) return rc;
+      if (c.sandwich_norm) {
+        rc = rf_rmsnorm(tmp, nullptr, w.post_attn_norm_w, tmp, nullptr, nullptr, 1, T, H, H, H, c.eps,
+                        c.norm_kind == RF_NORM_RMS_GEMMA ? 1 : 0, c.dtype, st);
+        if (rc) return rc;
+      }
+      if (c.gated_residual) rc = rf_gated_residual(f.hidden, tmp, mod1, f.rows_per_mod, T, H, c.dtype, st);
+      else rc = rf_eltwise(0, f.hidden, tmp, f.hidden, (int64_t)T * H, 0, 1.f, c.dtype, st);
+      if (rc) return rc;
+    }
+    // ---- MLP block
+    rc = norm(s, f.hidden, w.norm2_w, w.norm2_b, xn, T, mod2, f.rows_per_mod, st);
+    if (rc) return rc;
+    rc = linear(s, xn, H, w.w_up, w.s_up, w.b_up, wide, I, nullptr, 0, T, I, H, act_of(c.mlp_kind),
+                s.glu() ? I : 0, false, st);
+    if (rc) return rc;
+    if (!side) {
+      rc = linear(s, wide, I, w.w_down, w.s_down, w.b_down, f.hidden, H, f.hidden, H, T, H, I, kActNone, 0, true, st);
+      if (rc) return rc;
+    } else {
+      rc = linear(s, wide, I, w.w_down, w.s_down, w.b_down, tmp, H, nullptr, 0, T, H, I, kActNone, 0, true, st);
+      if (rc) return rc;
+      if (c.sandwich_norm) {
+        rc = rf_rmsnorm(tmp, nullptr, w.post_mlp_norm_w, tmp, nullptr, nullptr, 1, T, H, H, H, c.eps,
+                        c.norm_kind == RF_NORM_RMS_GEMMA ? 1 : 0, c.dtype, st);
+        if (rc) return rc;
+      }
+      if (c.gated_residual) rc = rf_gated_residual(f.hidden, tmp, mod2, f.rows_per_mod, T, H, c.dtype, st);
+      else rc = rf_eltwise(0, f.hidden, tmp, f.hidden, (int64_t)T * H, 0, 1.f, c.dtype, st);
+      if (rc) return rc;
+    }
+    // ---- hooks between layers
+    if (f.deepstack && l < f.n_deepstack && f.deepstack[l]) {
+      rc = rf_scatter_rows(f.hidden, f.deepstack[l], f.deepstack_rows, f.n_deepstack_rows, H, H, H, 1, c.dtype, st);
+      if (rc) return rc;
+    }
+    for (int i = 0; i < f.n_taps; ++i) {
+      if (f.tap_layers[i] == l)
+        RF_CUDA_CHECK(cudaMemcpyAsync(f.taps[i], f.hidden, (size_t)T * H * esz, cudaMemcpyDeviceToDevice, st));
+    }
+  }
+  return RF_OK;
+}
+
+__global__ void decode_advance_kernel(int32_t* pos, int pos_stride, int32_t* kv_len, int n,
+                                      const int32_t* out_ids, int32_t* ids, int32_t* hist, int32_t* step,
+                                      int hist_cap) {
+  // single block: n <= 1024 sequences
+  const int i = threadIdx.x;
+  const int st = step ? *step : 0;
+  __syncthreads();
+  if (i < n) {
+    if (pos) for (int a = 0; a < pos_stride; ++a) pos[i * pos_stride + a] += 1;
+    if (kv_len) kv_len[i] += 1;
+    if (out_ids) {
+      const int t = out_ids[i];
+      if (ids) ids[i] = t;
+      if (hist && st < hist_cap) hist[(size_t)st * n + i] = t;
+    }
+  }
+  if (i == 0 && step) *step = st + 1;
+}
+
+}  // namespace rf
+
+using namespace rf;
+
+extern "C" int64_t rf_stack_create(const RfStackConfig* cfg) {
+  if (!cfg) { fail(RF_ERR_BAD_ARG, "null config"); return -1; }
+  if (cfg->layers <= 0 || cfg->hidden <= 0 || cfg->hidden % 8 || cfg->Hq <= 0 || cfg->Hkv <= 0 ||
+      cfg->Hq % cfg->Hkv || (cfg->hd != 64 && cfg->hd != 128 && cfg->hd != 256) || cfg->inter <= 0 ||
+      cfg->inter % 8 || cfg->max_tokens <= 0 || cfg->max_seqs <= 0 || (cfg->dtype != 0 && cfg->dtype != 1) ||
+      cfg->tp_world < 1 || cfg->tp_world > 8 || cfg->tp_rank < 0 || cfg->tp_rank >= cfg->tp_world) {
+    fail(RF_ERR_BAD_ARG, "invalid stack config (layers=%d hidden=%d Hq=%d Hkv=%d hd=%d inter=%d)", cfg->layers,
+         cfg->hidden, cfg->Hq, cfg->Hkv, cfg->hd, cfg->inter);
+    return -1;
+  }
+  auto s = std::make_unique<Stack>();
+  s->cfg = *cfg;
+  s->layers.resize(cfg->layers);
+  s->plan();
+  return registry().insert(std::move(s));
+}
+
+extern "C" int rf_stack_destroy(int64_t h) {
+  return registry().erase(h) ? RF_OK : fail(RF_ERR_BAD_ARG, "unknown stack handle %lld", (long long)h);
+}
+
+#define RF_GET_STACK(h)                                                              \
+  std::shared_ptr<Stack> sp = registry().get(h);                                     \
+  if (!sp) return fail(RF_ERR_BAD_ARG, "unknown stack handle %lld", (long long)(h)); \
+  Stack& s = *sp;
+
+extern "C" int rf_stack_set_layer(int64_t h, int32_t layer, const RfLayerWeights* w) {
+  RF_GET_STACK(h);
+  RF_REQUIRE(w && layer >= 0 && layer < s.cfg.layers, "layer index %d out of range", layer);
+  RF_REQUIRE(w->wqkv && w->wo && w->w_up && w->w_down, "layer %d: missing projection weights", layer);
+  if (s.cfg.paged_kv) RF_REQUIRE(w->k_pool && w->v_pool, "layer %d: missing KV pool", layer);
+  if (s.cfg.weights_int8) RF_REQUIRE(w->sqkv && w->so && w->s_up && w->s_down, "layer %d: int8 weights need scales", layer);
+  s.layers[layer] = *w;
+  return RF_OK;
+}
+
+extern "C" int rf_stack_set_head(int64_t h, const void* final_norm_w, const void* final_norm_b,
+                                 const void* w_lm, const void* s_lm) {
+  RF_GET_STACK(h);
+  s.final_norm_w = final_norm_w; s.final_norm_b = final_norm_b; s.w_lm = w_lm; s.s_lm = s_lm;
+  return RF_OK;
+}
+
+extern "C" int rf_stack_set_comm(int64_t h, const RfStackComm* c) {
+  RF_GET_STACK(h);
+  RF_REQUIRE(c && c->recv && c->flags && c->state, "comm buffers");
+  s.comm = *c;
+  s.has_comm = true;
+  return RF_OK;
+}
+
+extern "C" uint64_t rf_stack_arena_bytes(int64_t h) {
+  std::shared_ptr<Stack> sp = registry().get(h);
+  return sp ? sp->total : 0;
+}
+
+extern "C" int rf_stack_bind_arena(int64_t h, void* base, uint64_t bytes) {
+  RF_GET_STACK(h);
+  RF_REQUIRE(base && bytes >= s.total, "arena of %llu B is smaller than the plan (%llu B)",
+             (unsigned long long)bytes, (unsigned long long)s.total);
+  RF_REQUIRE((reinterpret_cast<uintptr_t>(base) & 1023) == 0, "arena base must be 1024-byte aligned");
+  s.base = static_cast<uint8_t*>(base);
+  s.bytes = bytes;
+  return RF_OK;
+}
+
+extern "C" int32_t* rf_stack_status_ptr(int64_t h) {
+  std::shared_ptr<Stack> sp = registry().get(h);
+  return sp ? sp->status() : nullptr;
+}
+
+extern "C" int rf_stack_forward(int64_t h, const RfStackForward* f, rf_stream_t stream) {
+  RF_GET_STACK(h);
+  RF_REQUIRE(f != nullptr, "null forward args");
+  return forward(s, *f, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int rf_stack_final_norm(int64_t h, const void* hidden, void* out, int32_t rows, rf_stream_t stream) {
+  RF_GET_STACK(h);
+  RF_REQUIRE(s.final_norm_w, "stack has no final norm");
+  RfStackConfig c = s.cfg;
+  Stack tmp = s;
+  if (c.norm_kind == RF_NORM_ADARMS) tmp.cfg.norm_kind = RF_NORM_RMS;
+  return norm(tmp, hidden, s.final_norm_w, s.final_norm_b, out, rows, nullptr, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int rf_stack_head(int64_t h, const void* hidden, const int32_t* row_idx, int32_t rows,
+                             int32_t* out_ids, float* out_vals, void* logits_out, rf_stream_t stream) {
+  RF_GET_STACK(h);
+  const RfStackConfig& c = s.cfg;
+  RF_REQUIRE(s.base && s.final_norm_w && s.w_lm && c.vocab_local > 0, "stack has no lm head");
+  RF_REQUIRE(rows > 0 && rows <= c.max_seqs, "head rows %d (max %d)", rows, c.max_seqs);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int H = c.hidden;
+  void* hx = s.at(s.off_head_xn);
+  const void* src = hidden;
+  int rc;
+  if (row_idx) {
+    // gather the selected rows (embedding gather on the hidden matrix)
+    rc = rf_embedding(hidden, row_idx, s.at(s.off_tmp), rows, H, H, 1.f, c.dtype, nullptr, st);
+    if (rc) return rc;
+    src = s.at(s.off_tmp);
+  }
+  Stack tmp = s;
+  if (c.norm_kind == RF_NORM_ADARMS) tmp.cfg.norm_kind = RF_NORM_RMS;
+  rc = norm(tmp, src, s.final_norm_w, s.final_norm_b, hx, rows, nullptr, 1, st);
+  if (rc) return rc;
+  void* logits = logits_out ? logits_out : s.at(s.off_logits);
+  rc = linear(s, hx, H, s.w_lm, s.s_lm, nullptr, logits, c.vocab_local, nullptr, 0, rows, c.vocab_local, H,
+              kActNone, 0, false, st);
+  if (rc) return rc;
+  if (out_ids)
+    rc = rf_argmax(logits, rows, c.vocab_local, c.vocab_local, out_ids, out_vals, c.vocab_offset,
+                   s.at(s.off_argmax), s.argmax_bytes, c.dtype, st);
+  return rc;
+}
+
+extern "C" int rf_decode_advance(int32_t* pos, int32_t pos_stride, int32_t* kv_len, int32_t n,
+                                 const int32_t* out_ids, int32_t* ids, int32_t* hist, int32_t* step,
+                                 int32_t hist_cap, rf_stream_t stream) {
+  if (n <= 0) return RF_OK;
+  RF_REQUIRE(n <= 1024, "decode_advance handles up to 1024 sequences, got %d", n);
+  decode_advance_kernel<<<1, ((n + 31) / 32) * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      pos, pos_stride > 0 ? pos_stride : 1, kv_len, n, out_ids, ids, hist, step, hist_cap);
+  RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
+  return RF_OK;
+}

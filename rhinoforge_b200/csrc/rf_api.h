@@ -22,6 +22,7 @@ enum RfError {
 
 const char* rf_last_error(void);
 int rf_version(void);
+uint64_t rf_launch_count(void);  // kernels enqueued by this library so far
 
 // ---------------------------------------------------------------- GEMM ----
 // out[M,N] = epilogue( x[M,K] . w[N,K]^T ), all row-major, 16-bit in, fp32 acc.
@@ -57,6 +58,9 @@ typedef struct RfGemm {
 int rf_gemm(const RfGemm* g, rf_stream_t stream);
 // Scratch a split-K launch of this shape would need (bytes of ws, number of sems).
 int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem_count);
+// Same contract with int8 weights [N,K] and a per-output-channel scale (W8A16):
+// the int8 tile is widened to the activation dtype inside the mainloop.
+int rf_gemm_w8a16(const RfGemm* g, rf_stream_t stream);
 // CUDA-core skinny GEMM (M <= 8): reference path and small-batch decode.
 int rf_gemv(const RfGemm* g, rf_stream_t stream);
 
@@ -140,6 +144,27 @@ typedef struct RfAttn {
 int rf_attn_prefill(const RfAttn* a, rf_stream_t stream);
 int rf_attn_decode(const RfAttn* a, rf_stream_t stream);
 uint64_t rf_attn_decode_scratch_bytes(int num_seqs, int Hq, int hd);
+
+
+// ------------------------------------------------------------- KV pool ----
+int64_t rf_kvpool_create(int32_t num_pages, int32_t max_seqs, int32_t pages_per_seq);
+int rf_kvpool_destroy(int64_t h);
+int rf_kvpool_reserve(int64_t h, int32_t seq, int32_t tokens, int32_t* table_row);
+int rf_kvpool_release(int64_t h, int32_t seq);
+int32_t rf_kvpool_free_pages(int64_t h);
+
+
+// ------------------------------------------------ peer memory (TP) ----
+int rf_comm_alloc(uint64_t bytes, void** out);   // cudaMalloc + zero fill
+int rf_comm_free(void* p);
+int rf_ipc_export(void* p, uint8_t* handle64);
+int rf_ipc_import(const uint8_t* handle64, void** out);
+int rf_ipc_close(void* p);
+int rf_tp_argmax_merge(void* const* aux, uint32_t* const* flags, int flag_base, uint32_t* state, int world,
+                       int rank, int rows, int max_rows, const float* vals, int32_t* ids, int32_t* status,
+                       rf_stream_t stream);
+int rf_peer_barrier(uint32_t* const* flags, int flag_base, uint32_t* state, int world, int rank,
+                    int32_t* status, rf_stream_t stream);
 
 #ifdef __cplusplus
 }

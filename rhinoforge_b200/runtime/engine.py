@@ -1,0 +1,477 @@
+"""Causal-LM serving engine on the native transformer-stack runtime.
+
+One engine = one native stack handle (weights packed once, static activation
+arena, paged KV pool with 16-token pages) plus the device-resident decode state
+(token ids, positions, KV lengths, page table).  A decode step -- embedding,
+all layers, final norm, lm_head, arg-max, bookkeeping -- is captured once per
+batch size into a CUDA graph and replayed; nothing in it depends on host values.
+
+This is the B200 counterpart of the reference's shared causal-decoder runtime
+(``python/rpu_backend/runtime/decoder.py:1012-1519`` install,
+``:623-873`` forward) and of its BUILD/REPLAY graph capture
+(``python/rpu_backend/graph/_runtime.py:124-340``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+
+from .. import _native as N
+from ..models.decoder import DecoderConfig, mrope_axis_of_freq, rope_tables
+from ..ops import kernels as K
+from ..parallel.tp import CommBuffers, TPContext, kv_head_range, shard_range
+from .errors import RPUBackendError
+
+WeightGetter = Callable[[str], torch.Tensor]
+
+NORM_KIND = {"rms": 0, "rms_gemma": 1, "layernorm": 2, "adarms": 3}
+MLP_KIND = {"swiglu": 0, "geglu_tanh": 1, "gelu_tanh": 2, "gelu_erf": 3, "silu": 4}
+
+
+def random_weight_getter(cfg: DecoderConfig, *, seed: int = 0, std: float = 0.02, dtype=torch.float16,
+                         device="cuda") -> WeightGetter:
+    """Random-init weights generated on demand on ``device`` (one seeded generator per tensor
+    name), so an 8B/32B-shape model never exists in host memory and every tensor-parallel
+    rank derives identical full tensors before slicing its shard."""
+    from ..models.decoder import weight_shapes
+    table = {name: (idx, shape, kind) for idx, (name, shape, kind) in enumerate(weight_shapes(cfg))}
+    dev = torch.device(device)
+
+    def get(name: str) -> torch.Tensor:
+        if name == "lm_head.weight" and name not in table:
+            return get("model.embed_tokens.weight")
+        idx, shape, kind = table[name]
+        if kind == "norm":
+            return torch.full(shape, 0.0 if cfg.norm == "rms_gemma" else 1.0, dtype=dtype, device=dev)
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed * 1_000_003 + idx)
+        t = torch.empty(shape, dtype=torch.float32, device=dev) if len(shape) == 1 else None
+        if t is not None:
+            return (t.normal_(0.0, std, generator=g)).to(dtype)
+        out = torch.empty(shape, dtype=dtype, device=dev)
+        rows = max(1, (64 << 20) // (shape[1] * 4))
+        for r in range(0, shape[0], rows):
+            blk = torch.empty((min(rows, shape[0] - r), shape[1]), dtype=torch.float32, device=dev)
+            out[r:r + blk.shape[0]] = blk.normal_(0.0, std, generator=g).to(dtype)
+        return out
+
+    return get
+
+
+def quantize_per_channel(w: torch.Tensor, dtype=torch.float16):
+    """Symmetric per-output-channel int8 (reference semantics: ``quant/_common.py:10-41``)."""
+    amax = w.float().abs().amax(dim=1).clamp(min=1e-8)
+    scale = (amax / 127.0).to(dtype)
+    q = torch.round(w.float() / scale.float()[:, None]).clamp(-127, 127).to(torch.int8)
+    return q, scale
+
+
+class DecoderEngine:
+    def __init__(self, cfg: DecoderConfig, get_weight: WeightGetter, *, device="cuda", dtype=torch.float16,
+                 max_batch: int = 1, max_seq_len: int = 2048, max_prefill_tokens: int = 8192,
+                 tp: Optional[TPContext] = None, quant: Optional[str] = None, decode_gemv_max_m: int = 0,
+                 hist_steps: int = 4096):
+        if not torch.cuda.is_available():
+            raise RPUBackendError("DecoderEngine needs a CUDA device")
+        self.cfg, self.dtype = cfg, dtype
+        self.tp = tp or TPContext.single(device)
+        self.device = torch.device(self.tp.device if self.tp.device is not None else device)
+        W, R = self.tp.world, self.tp.rank
+        self.max_batch, self.max_seq_len = max_batch, max_seq_len
+        self.max_tokens = max(max_prefill_tokens, max_batch)
+        self.quant = quant
+        if quant not in (None, "w8a16"):
+            raise RPUBackendError(f"unknown quantisation {quant!r}")
+        H, hd = cfg.hidden_size, cfg.head_dim
+        if cfg.num_heads % W or cfg.intermediate_size % W or cfg.vocab_size % W:
+            raise RPUBackendError(f"{cfg.name}: heads/intermediate/vocab do not split over {W} ranks")
+        self.Hq = cfg.num_heads // W
+        kv0, kv1 = kv_head_range(cfg.num_kv_heads, W, R)
+        self.Hkv = kv1 - kv0
+        self.inter = cfg.intermediate_size // W
+        self.vocab_local = cfg.vocab_size // W
+        lib = N.lib()
+
+        sc = N.RfStackConfig()
+        sc.layers, sc.hidden, sc.Hq, sc.Hkv, sc.hd, sc.inter = cfg.num_layers, H, self.Hq, self.Hkv, hd, self.inter
+        sc.rot_dim, sc.norm_kind, sc.mlp_kind, sc.eps = cfg.rot_dim, NORM_KIND[cfg.norm], MLP_KIND[cfg.mlp], cfg.rms_eps
+        sc.qk_norm, sc.paged_kv, sc.causal, sc.true_hd = int(cfg.qk_norm), 1, 1, hd
+        sc.dtype = K.dtype_code(dtype)
+        sc.max_tokens, sc.max_seqs = self.max_tokens, max_batch
+        sc.vocab_local, sc.vocab_offset = self.vocab_local, R * self.vocab_local
+        sc.tp_world, sc.tp_rank = W, R
+        sc.weights_int8 = 1 if quant == "w8a16" else 0
+        sc.decode_gemv_max_m = decode_gemv_max_m
+        h = lib.rf_stack_create(C.byref(sc))
+        if h < 0:
+            N.check(-1, "rf_stack_create")
+        self.handle = C.c_int64(h)
+
+        # ---- KV pool: [layers, 2, pages, Hkv, 16, hd], zero-filled (masked rows pass through the MMA)
+        self.pages_per_seq = (max_seq_len + 15) // 16
+        self.num_pages = max_batch * self.pages_per_seq
+        self.kv = torch.zeros((cfg.num_layers, 2, self.num_pages, self.Hkv, 16, hd), dtype=dtype, device=self.device)
+        self.pool = C.c_int64(lib.rf_kvpool_create(self.num_pages, max_batch, self.pages_per_seq))
+        self._pt_host = torch.zeros((max_batch, self.pages_per_seq), dtype=torch.int32).pin_memory()
+        self.page_table = torch.zeros((max_batch, self.pages_per_seq), dtype=torch.int32, device=self.device)
+
+        # ---- weights: packed once, kept alive here
+        self._keep: List[torch.Tensor] = []
+        self._pack_weights(get_weight, kv0, kv1)
+
+        # ---- arena + comm
+        nbytes = lib.rf_stack_arena_bytes(self.handle)
+        self.arena = torch.zeros(nbytes + 1024, dtype=torch.uint8, device=self.device)
+        base = (self.arena.data_ptr() + 1023) // 1024 * 1024
+        N.check(lib.rf_stack_bind_arena(self.handle, C.c_void_p(base), C.c_uint64(nbytes)), "rf_stack_bind_arena")
+        off = lib.rf_stack_status_ptr(self.handle) - self.arena.data_ptr()
+        self.status = self.arena[off:off + 32].view(torch.int32)
+        self.comm: Optional[CommBuffers] = None
+        if self.tp.enabled:
+            rows = self.max_tokens
+            self.comm = CommBuffers(self.tp, W * rows * H * 4)
+            cc = self.comm.stack_comm()
+            N.check(lib.rf_stack_set_comm(self.handle, C.byref(cc)), "rf_stack_set_comm")
+
+        # ---- rope tables and decode state
+        cos, sin = rope_tables(cfg, max_seq_len + 16, self.device)
+        self.cos, self.sin = cos, sin
+        ax = mrope_axis_of_freq(cfg)
+        self.axis = ax.to(self.device) if ax is not None else None
+        self.pos_stride = 3 if ax is not None else 1
+        i32 = dict(dtype=torch.int32, device=self.device)
+        self.hidden = torch.zeros((self.max_tokens, H), dtype=dtype, device=self.device)
+        self.ids = torch.zeros(max_batch, **i32)
+        self.out_ids = torch.zeros(max_batch, **i32)
+        self.out_vals = torch.zeros(max_batch, dtype=torch.float32, device=self.device)
+        self.pos = torch.zeros((max_batch, self.pos_stride), **i32)
+        self.kv_len = torch.zeros(max_batch, **i32)
+        self.step = torch.zeros(1, **i32)
+        self.hist_steps = hist_steps
+        self.hist = torch.zeros((hist_steps, max_batch), **i32)
+        self._host_len = [0] * max_batch
+        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.batch = 0
+        self.launches_per_step = 0
+
+    # ------------------------------------------------------------------ weights
+    def _dev(self, t: torch.Tensor) -> torch.Tensor:
+        t = t.to(self.device, self.dtype if t.is_floating_point() else t.dtype).contiguous()
+        self._keep.append(t)
+        return t
+
+    def _lin(self, w: torch.Tensor):
+        """Device weight (+ scale when quantised)."""
+        if self.quant == "w8a16":
+            if w.dtype != torch.int8:
+                q, s = quantize_per_channel(w.to(self.device), self.dtype)
+            else:
+                raise RPUBackendError("pre-quantised tensors must be passed with their scales")
+            return self._dev(q), self._dev(s)
+        return self._dev(w), None
+
+    def _pack_weights(self, get: WeightGetter, kv0: int, kv1: int) -> None:
+        cfg, lib = self.cfg, N.lib()
+        W, R = self.tp.world, self.tp.rank
+        hd = cfg.head_dim
+        q0, q1 = shard_range(cfg.num_heads, W, R)
+        i0, i1 = shard_range(cfg.intermediate_size, W, R)
+        v0, v1 = shard_range(cfg.vocab_size, W, R)
+        ptr = lambda t: None if t is None else t.data_ptr()
+        for l in range(cfg.num_layers):
+            p = f"model.layers.{l}."
+            wq, wk, wv = get(p + "self_attn.q_proj.weight"), get(p + "self_attn.k_proj.weight"), get(p + "self_attn.v_proj.weight")
+            wqkv = torch.cat((wq[q0 * hd:q1 * hd], wk[kv0 * hd:kv1 * hd], wv[kv0 * hd:kv1 * hd]), 0)
+            del wq, wk, wv
+            bqkv = None
+            if cfg.attention_bias:
+                bq, bk, bv = (get(p + f"self_attn.{n}_proj.bias") for n in "qkv")
+                bqkv = self._dev(torch.cat((bq[q0 * hd:q1 * hd], bk[kv0 * hd:kv1 * hd], bv[kv0 * hd:kv1 * hd]), 0))
+            wo = get(p + "self_attn.o_proj.weight")[:, q0 * hd:q1 * hd]
+            wgu = torch.cat((get(p + "mlp.gate_proj.weight")[i0:i1], get(p + "mlp.up_proj.weight")[i0:i1]), 0)
+            wd = get(p + "mlp.down_proj.weight")[:, i0:i1]
+            lw = N.RfLayerWeights()
+            t_qkv, s_qkv = self._lin(wqkv)
+            t_o, s_o = self._lin(wo)
+            t_gu, s_gu = self._lin(wgu)
+            t_d, s_d = self._lin(wd)
+            del wqkv, wo, wgu, wd
+            lw.wqkv, lw.sqkv, lw.bqkv = ptr(t_qkv), ptr(s_qkv), ptr(bqkv)
+            lw.wo, lw.so = ptr(t_o), ptr(s_o)
+            lw.w_up, lw.s_up = ptr(t_gu), ptr(s_gu)
+            lw.w_down, lw.s_down = ptr(t_d), ptr(s_d)
+            lw.norm1_w = ptr(self._dev(get(p + "input_layernorm.weight")))
+            lw.norm2_w = ptr(self._dev(get(p + "post_attention_layernorm.weight")))
+            if cfg.qk_norm:
+                lw.q_norm_w = ptr(self._dev(get(p + "self_attn.q_norm.weight")))
+                lw.k_norm_w = ptr(self._dev(get(p + "self_attn.k_norm.weight")))
+            lw.k_pool, lw.v_pool = self.kv[l, 0].data_ptr(), self.kv[l, 1].data_ptr()
+            N.check(lib.rf_stack_set_layer(self.handle, l, C.byref(lw)), "rf_stack_set_layer")
+        emb = get("model.embed_tokens.weight")
+        self.embed = self._dev(emb)
+        lm = emb if cfg.tie_embeddings else get("lm_head.weight")
+        t_lm, s_lm = self._lin(lm[v0:v1])
+        self.final_norm = self._dev(get("model.norm.weight"))
+        N.check(lib.rf_stack_set_head(self.handle, C.c_void_p(self.final_norm.data_ptr()), None,
+                                      C.c_void_p(t_lm.data_ptr()), C.c_void_p(ptr(s_lm))), "rf_stack_set_head")
+        del emb, lm
+        torch.cuda.empty_cache()
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._keep)
+
+    # ------------------------------------------------------------------ helpers
+    def _stream(self):
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def check_status(self) -> None:
+        """Raise if any kernel recorded a timeout / bad-argument code (reads 8 ints from the device)."""
+        torch.cuda.synchronize()
+        st = self.status.tolist()
+        if st[0] != 0:
+            raise RPUBackendError(f"device status {st[:4]} (code, block, kernel, detail)")
+        if self.comm is not None and int(self.comm.status[0]) != 0:
+            raise RPUBackendError(f"peer wait timed out: {self.comm.status.tolist()[:4]}")
+
+    def reset(self) -> None:
+        lib = N.lib()
+        for s in range(self.max_batch):
+            lib.rf_kvpool_release(self.pool, s)
+            self._host_len[s] = 0
+        self.step.zero_()
+        self.batch = 0
+
+    def _reserve(self, seq: int, tokens: int) -> None:
+        row = self._pt_host[seq]
+        rc = N.lib().rf_kvpool_reserve(self.pool, seq, tokens, C.c_void_p(row.data_ptr()))
+        if rc != 0:
+            from ..api.errors import SPMExhaustionError
+            raise SPMExhaustionError(N.lib().rf_last_error().decode())
+
+    def _embed(self, ids: torch.Tensor, n: int) -> None:
+        K.embedding(self.embed, ids, out=self.hidden[:n], scale=self.cfg.embed_scale)
+
+    def _head(self, rows: int, row_idx: Optional[torch.Tensor], logits_out: Optional[torch.Tensor] = None) -> None:
+        N.check(N.lib().rf_stack_head(self.handle, C.c_void_p(self.hidden.data_ptr()),
+                                      C.c_void_p(None if row_idx is None else row_idx.data_ptr()), rows,
+                                      C.c_void_p(self.out_ids.data_ptr()), C.c_void_p(self.out_vals.data_ptr()),
+                                      C.c_void_p(None if logits_out is None else logits_out.data_ptr()),
+                                      self._stream()), "rf_stack_head")
+        if self.comm is not None:
+            self.comm.argmax_merge(self.out_vals, self.out_ids, rows)
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def prefill(self, prompts: Sequence[torch.Tensor], *, return_logits: bool = False,
+                inputs_embeds: Optional[Sequence[torch.Tensor]] = None,
+                positions3: Optional[Sequence[torch.Tensor]] = None) -> torch.Tensor:
+        """Prefill sequences 0..B-1 with ``prompts`` (1-D int tensors, host or device).  Returns the
+        first greedy token of every sequence ([B] int32 on the device) and leaves the engine ready
+        for ``decode``.  Long batches run as several packed varlen chunks of at most
+        ``max_prefill_tokens`` rows (chunked prefill)."""
+        B = len(prompts)
+        if B > self.max_batch:
+            raise RPUBackendError(f"batch {B} exceeds max_batch {self.max_batch}")
+        self.reset()
+        lens = [int(p.numel()) for p in prompts]
+        for s, L in enumerate(lens):
+            if L < 1 or L + 1 > self.max_seq_len:
+                raise RPUBackendError(f"prompt of {L} tokens does not fit max_seq_len {self.max_seq_len}")
+            self._reserve(s, self.max_seq_len)
+        self.page_table.copy_(self._pt_host, non_blocking=True)
+        logits_all = torch.empty((B, self.vocab_local), dtype=self.dtype, device=self.device) if return_logits else None
+        first = torch.zeros(B, dtype=torch.int32, device=self.device)
+        # work items: (seq, start, count) packed into chunks of <= max_tokens rows
+        chunk: List[tuple] = []
+        used = 0
+        items: List[List[tuple]] = []
+        for s, L in enumerate(lens):
+            off = 0
+            while off < L:
+                take = min(L - off, self.max_tokens - used)
+                if take == 0:
+                    items.append(chunk)
+                    chunk, used = [], 0
+                    continue
+                chunk.append((s, off, take))
+                used += take
+                off += take
+        if chunk:
+            items.append(chunk)
+        for ch in items:
+            self._prefill_chunk(ch, prompts, lens, first, logits_all, inputs_embeds, positions3)
+        self.batch = B
+        for s, L in enumerate(lens):
+            self._host_len[s] = L
+        # decode state: the token to feed next is `first`, at position L
+        self.ids[:B].copy_(first)
+        if positions3 is not None:
+            nxt = torch.stack([p[:, -1].to(self.device) + 1 for p in positions3]).to(torch.int32)
+            self.pos[:B].copy_(nxt)
+        else:
+            posv = torch.tensor(lens, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+            self.pos[:B].copy_(posv[:, None].expand(B, self.pos_stride))
+        self.kv_len[:B].copy_(torch.tensor([l + 1 for l in lens], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True))
+        return (first, logits_all) if return_logits else first
+
+    def _prefill_chunk(self, ch, prompts, lens, first, logits_all, inputs_embeds, positions3) -> None:
+        T = sum(c[2] for c in ch)
+        n = len(ch)
+        meta = torch.empty((5, max(n, 1)), dtype=torch.int32)
+        tokmeta = torch.empty((2, T), dtype=torch.int32)
+        ids_host = torch.empty(T, dtype=torch.int32)
+        o = 0
+        emb_rows = []
+        pos3 = []
+        for j, (s, off, cnt) in enumerate(ch):
+            meta[0, j], meta[1, j], meta[2, j] = o, cnt, off + cnt   # q_start, q_len, kv_len
+            meta[3, j] = s
+            meta[4, j] = o + cnt - 1
+            tokmeta[0, o:o + cnt] = s
+            tokmeta[1, o:o + cnt] = torch.arange(off, off + cnt, dtype=torch.int32)
+            ids_host[o:o + cnt] = prompts[s][off:off + cnt].to("cpu", torch.int32)
+            if inputs_embeds is not None:
+                emb_rows.append(inputs_embeds[s][off:off + cnt])
+            if positions3 is not None:
+                pos3.append(positions3[s][:, off:off + cnt].t())
+            o += cnt
+        meta_d = meta.pin_memory().to(self.device, non_blocking=True)
+        tok_d = tokmeta.pin_memory().to(self.device, non_blocking=True)
+        ids_d = ids_host.pin_memory().to(self.device, non_blocking=True)
+        # the page table the kernels see is indexed by chunk-local sequence number
+        pt = self.page_table[meta_d[3].long()].contiguous()
+        seq_local = torch.repeat_interleave(torch.arange(n, dtype=torch.int32, device=self.device), meta_d[1].long())
+        if inputs_embeds is not None:
+            self.hidden[:T].copy_(torch.cat(emb_rows).to(self.device, self.dtype))
+        else:
+            self._embed(ids_d, T)
+        if positions3 is not None:
+            pos_d = torch.cat(pos3).to(self.device, torch.int32).contiguous()
+            cache_pos = tok_d[1].contiguous()
+        else:
+            pos_d = tok_d[1].contiguous() if self.pos_stride == 1 else tok_d[1][:, None].expand(T, 3).contiguous()
+            cache_pos = tok_d[1].contiguous()
+        f = N.RfStackForward()
+        f.hidden, f.tokens, f.decode = self.hidden.data_ptr(), T, 0
+        f.pos, f.pos_stride = pos_d.data_ptr(), self.pos_stride
+        f.cos, f.sin = self.cos.data_ptr(), self.sin.data_ptr()
+        f.axis_of_freq = None if self.axis is None else self.axis.data_ptr()
+        f.seq_of_tok, f.cache_pos = seq_local.data_ptr(), cache_pos.data_ptr()
+        f.num_seqs = n
+        qs, ql, kl = meta_d[0].contiguous(), meta_d[1].contiguous(), meta_d[2].contiguous()
+        f.q_start, f.q_len, f.kv_len = qs.data_ptr(), ql.data_ptr(), kl.data_ptr()
+        f.max_q_len = max(c[2] for c in ch)
+        f.max_kv_len = max(c[1] + c[2] for c in ch)
+        f.page_table, f.pt_stride, f.pool_pages = pt.data_ptr(), pt.stride(0), self.num_pages
+        N.check(N.lib().rf_stack_forward(self.handle, C.byref(f), self._stream()), "rf_stack_forward")
+        # sequences whose prompt ends in this chunk get their first token
+        done = [(j, s) for j, (s, off, cnt) in enumerate(ch) if off + cnt == lens[s]]
+        if done:
+            rows = meta_d[4][torch.tensor([j for j, _ in done], device=self.device)].contiguous()
+            for b0 in range(0, len(done), self.max_batch):
+                sub = done[b0:b0 + self.max_batch]
+                lg = torch.empty((len(sub), self.vocab_local), dtype=self.dtype, device=self.device) if logits_all is not None else None
+                self._head(len(sub), rows[b0:b0 + len(sub)].contiguous(), lg)
+                dst = torch.tensor([s for _, s in sub], device=self.device)
+                first[dst] = self.out_ids[:len(sub)]
+                if logits_all is not None:
+                    logits_all[dst] = lg
+
+    # ------------------------------------------------------------------- decode
+    def _decode_step(self, B: int, logits_out: Optional[torch.Tensor] = None) -> None:
+        self._embed(self.ids[:B], B)
+        f = N.RfStackForward()
+        f.hidden, f.tokens, f.decode = self.hidden.data_ptr(), B, 1
+        f.pos, f.pos_stride = self.pos.data_ptr(), self.pos_stride
+        f.cos, f.sin = self.cos.data_ptr(), self.sin.data_ptr()
+        f.axis_of_freq = None if self.axis is None else self.axis.data_ptr()
+        f.num_seqs = B
+        f.kv_len = self.kv_len.data_ptr()
+        f.max_q_len, f.max_kv_len = 1, self.max_seq_len
+        f.page_table, f.pt_stride, f.pool_pages = self.page_table.data_ptr(), self.page_table.stride(0), self.num_pages
+        N.check(N.lib().rf_stack_forward(self.handle, C.byref(f), self._stream()), "rf_stack_forward")
+        self._head(B, None, logits_out)
+        N.check(N.lib().rf_decode_advance(C.c_void_p(self.pos.data_ptr()), self.pos_stride,
+                                          C.c_void_p(self.kv_len.data_ptr()), B, C.c_void_p(self.out_ids.data_ptr()),
+                                          C.c_void_p(self.ids.data_ptr()), C.c_void_p(self.hist.data_ptr()),
+                                          C.c_void_p(self.step.data_ptr()), self.hist_steps, self._stream()),
+                "rf_decode_advance")
+
+    def capture(self, B: int) -> None:
+        """BUILD: run one eager step (loads kernels, sets attributes), rewind, then capture."""
+        if B in self.graphs:
+            return
+        snap = (self.pos.clone(), self.kv_len.clone(), self.ids.clone(), self.step.clone())
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._decode_step(B)
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            self._decode_step(B)
+        torch.cuda.synchronize()
+        self.pos.copy_(snap[0]); self.kv_len.copy_(snap[1]); self.ids.copy_(snap[2]); self.step.copy_(snap[3])
+        self.graphs[B] = g
+
+    def decode(self, n_steps: int, *, use_graph: bool = True) -> torch.Tensor:
+        """Run ``n_steps`` greedy steps for the prefilled batch; returns tokens [B, n_steps] (device).
+        The token produced by prefill is NOT included; step i's output is the (i+2)-th new token."""
+        B = self.batch
+        if B == 0:
+            raise RPUBackendError("decode() before prefill()")
+        for s in range(B):
+            if self._host_len[s] + n_steps + 1 > self.max_seq_len:
+                raise RPUBackendError("decode would overflow the KV pages of the sequence")
+        start = int(self.step.item())
+        if start + n_steps > self.hist_steps:
+            self.step.zero_()
+            start = 0
+        if use_graph:
+            self.capture(B)
+            g = self.graphs[B]
+            for _ in range(n_steps):
+                g.replay()
+        else:
+            for _ in range(n_steps):
+                self._decode_step(B)
+        for s in range(B):
+            self._host_len[s] += n_steps
+        return self.hist[start:start + n_steps, :B].t()
+
+    def step_from_host(self, host_ids: torch.Tensor, host_out: torch.Tensor) -> None:
+        """One decode step driven from the host: copy this step's input ids from pinned host
+        memory, replay the graph, copy the produced ids back (asynchronous; the caller syncs)."""
+        B = self.batch
+        self.ids[:B].copy_(host_ids, non_blocking=True)
+        self.graphs[B].replay()
+        host_out.copy_(self.out_ids[:B], non_blocking=True)
+        for s in range(B):
+            self._host_len[s] += 1
+
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[torch.Tensor], max_new_tokens: int, *, use_graph: bool = True) -> torch.Tensor:
+        first = self.prefill(prompts)
+        if max_new_tokens <= 1:
+            return first[:, None]
+        rest = self.decode(max_new_tokens - 1, use_graph=use_graph)
+        out = torch.cat((first[:, None], rest), 1)
+        self.check_status()
+        return out
+
+    def close(self) -> None:
+        lib = N.lib()
+        torch.cuda.synchronize()
+        self.graphs.clear()
+        if self.comm is not None:
+            self.comm.close()
+            self.comm = None
+        if getattr(self, "handle", None) is not None:
+            lib.rf_stack_destroy(self.handle)
+            self.handle = None
+        if getattr(self, "pool", None) is not None:
+            lib.rf_kvpool_destroy(self.pool)
+            self.pool = None
