@@ -638,3 +638,74 @@ extern "C" int rf_attn_prefill(const RfAttn* a, rf_stream_t stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   RF_ATTN_DISPATCH(launch_prefill)
 }
+
+// ---------------------------------------------------------------------------
+// Decode attention with built-in scratch (see attn_decode_static.h).
+#include "attn_decode_static.h"
+
+#include <mutex>
+
+// Split-KV partials of rf_attn_decode_static().  In host code this name is only
+// a stand-in for the symbol, never a device address: the address handed to the
+// kernels comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_attn_decode_static_scratch[RF_ATTN_DECODE_STATIC_SCRATCH_BYTES];
+
+namespace rf {
+
+constexpr int kMaxStaticDevices = 64;
+static std::mutex g_static_mu;
+static void* g_static_ptr[kMaxStaticDevices] = {};
+
+// Device address of the built-in scratch on the current device (looked up once per device).
+static int static_scratch_ptr(void** out) {
+  int dev = -1;
+  RF_CUDA_CHECK(cudaGetDevice(&dev));
+  RF_REQUIRE(dev >= 0 && dev < kMaxStaticDevices, "device ordinal %d is outside the supported range", dev);
+  std::lock_guard<std::mutex> g(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    RF_CUDA_CHECK(cudaGetSymbolAddress(&p, g_attn_decode_static_scratch));
+    RF_REQUIRE(p != nullptr && (reinterpret_cast<uintptr_t>(p) & 255) == 0,
+               "built-in scratch has no usable device address on device %d", dev);
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return RF_OK;
+}
+
+// Bytes of split-KV partials the launcher will ask for (mirrors its split choice).
+static uint64_t decode_scratch_need(const RfAttn* a) {
+  const int max_pages = (a->max_kv_len + 15) / 16;
+  const int ctas = a->num_seqs * a->Hkv;
+  int splits = 1;
+  if (ctas < 2 * sm_count()) {
+    splits = std::min(std::max(1, (2 * sm_count()) / ctas), std::max(1, max_pages / 8));
+    splits = std::min(splits, 64);
+  }
+  int pps = round_up(ceil_div(std::max(1, max_pages), splits), 4);
+  splits = std::max(1, ceil_div(std::max(1, max_pages), pps));
+  if (splits <= 1) return 0;
+  return (uint64_t)a->num_seqs * a->Hq * splits * (a->hd + 1) * sizeof(float);
+}
+
+}  // namespace rf
+
+extern "C" int rf_attn_decode_static(const RfAttn* a, rf_stream_t stream) {
+  RF_REQUIRE(a != nullptr, "null RfAttn");
+  RF_REQUIRE(a->num_seqs > 0 && a->Hkv > 0 && a->Hq > 0 && a->hd > 0 && a->max_kv_len > 0,
+             "decode attention shape: seqs=%d Hq=%d Hkv=%d hd=%d max_kv_len=%d", a->num_seqs, a->Hq, a->Hkv,
+             a->hd, a->max_kv_len);
+  const uint64_t need = decode_scratch_need(a);
+  if (need > RF_ATTN_DECODE_STATIC_SCRATCH_BYTES)
+    return fail(RF_ERR_NO_MEMORY,
+                "decode attention for %d sequences x %d heads needs %llu B of split-KV scratch; the built-in buffer "
+                "holds %u B -- call rf_attn_decode() with caller-provided scratch",
+                a->num_seqs, a->Hq, (unsigned long long)need, (unsigned)RF_ATTN_DECODE_STATIC_SCRATCH_BYTES);
+  void* ptr = nullptr;
+  int rc = static_scratch_ptr(&ptr);
+  if (rc) return rc;
+  RfAttn b = *a;
+  b.ws = static_cast<float*>(ptr);
+  b.ws_bytes = RF_ATTN_DECODE_STATIC_SCRATCH_BYTES;
+  return rf_attn_decode(&b, stream);
+}
