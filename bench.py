@@ -56,7 +56,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
             self.proc = None
@@ -132,10 +132,10 @@ def run(args) -> dict:
         c0 = lib.rf_launch_count()
         eng.capture(B)
         per_step_launches = (lib.rf_launch_count() - c0) // 2   # one eager + one captured step
-        eng.decode(args.warmup)
         sampler = ClockSampler(dev.index or 0)
-        tp.barrier(); torch.cuda.synchronize()
         sampler.start()
+        eng.decode(args.warmup)
+        tp.barrier(); torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         g = eng.graphs[B]
@@ -145,8 +145,7 @@ def run(args) -> dict:
         tp.barrier(); torch.cuda.synchronize()
         clocks = sampler.stop()
         ms = tp.max_float(e0.elapsed_time(e1)) / args.steps
-        for s in range(B):
-            eng._host_len[s] += args.steps
+        eng.advance_lengths(args.steps)
         eng.check_status()
         # ---- end to end through the host-driven step API: per step H2D of the input ids from pinned
         # memory, graph replay, D2H of the produced ids, host sync

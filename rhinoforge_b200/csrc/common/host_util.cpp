@@ -2,6 +2,7 @@
 
 #include <cudaTypedefs.h>
 #include <stdarg.h>
+#include <stdlib.h>
 
 #include <atomic>
 #include <mutex>
@@ -73,6 +74,15 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int dtype, int elem_bytes, 
 
 static std::atomic<uint64_t> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("RF_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
 
 int sm_count() {
   static int n = 0;

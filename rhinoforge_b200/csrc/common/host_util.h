@@ -46,6 +46,45 @@ inline uint32_t next_pow2(uint32_t v) {
 
 int sm_count();
 
+// Whether kernels are launched with programmatic stream serialization (RF_PDL=0 turns it off).
+bool pdl_enabled();
+
+// Launch with the library's standard attributes: programmatic dependent launch and,
+// when cluster_z > 1, a (1,1,cluster_z) thread-block cluster.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                            int cluster_z, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_z > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = (unsigned)cluster_z;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// True while this thread is inside a graph scope in REPLAY mode: launchers return at once.
+bool replay_mode();
+#define RF_SKIP_IF_REPLAYING()             \
+  do {                                     \
+    if (::rf::replay_mode()) return RF_OK; \
+  } while (0)
+
 // Number of kernel launches this library has enqueued (captured launches count once).
 void count_launch(int n = 1);
 

@@ -37,6 +37,21 @@ __device__ __forceinline__ void report_status(int32_t* status, int32_t code, int
   }
 }
 
+// ------------------------------------------- programmatic dependent launch ----
+// Every kernel in this library starts with pdl_prologue(): it lets the next
+// kernel in the stream begin launching at once and then blocks until the
+// previous kernel has completed and flushed.  Work that does not depend on the
+// previous kernel (barrier set-up, TMEM allocation, weight prefetch) may be
+// placed between launch_dependents and wait.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
+
 // ------------------------------------------------------------ mbarrier ----
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));

@@ -98,6 +98,7 @@ template <typename T, int HD>
 __global__ void __launch_bounds__(160)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const AttnParams p) {
+  pdl_prologue();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -279,6 +280,7 @@ template <typename T>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ ws_o,
                                            const float* __restrict__ ws_lse, T* __restrict__ out,
                                            int64_t ldo, int Hq, int hd, int splits) {
+  pdl_prologue();
   const int head = blockIdx.x, seq = blockIdx.y;
   const size_t base = ((size_t)seq * Hq + head) * splits;
   float M = -INFINITY;
@@ -301,6 +303,7 @@ template <typename T, int HD>
 __global__ void __launch_bounds__(160)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  pdl_prologue();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -566,12 +569,12 @@ static int launch_decode(const RfAttn* a, AttnParams& p, cudaStream_t s) {
   p.splits = splits;
   p.pages_per_split = pps;
   dim3 grid(splits, a->Hkv, a->num_seqs);
-  kfn<<<grid, 160, smem, s>>>(tmK, tmV, p);
+  RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(grid), dim3(160), smem, s, 1, tmK, tmV, p));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   if (splits > 1) {
     dim3 g2(a->Hq, a->num_seqs);
-    attn_decode_combine_kernel<T><<<g2, HD < 128 ? HD : 128, 0, s>>>(p.ws_o, p.ws_lse, (T*)a->out, a->ldo, a->Hq, HD, splits);
+    RF_CUDA_CHECK(::rf::launch_k(attn_decode_combine_kernel<T>, dim3(g2), dim3(HD < 128 ? HD : 128), 0, s, 1, p.ws_o, p.ws_lse, (T*)a->out, a->ldo, a->Hq, HD, splits));
     RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   }
@@ -597,7 +600,7 @@ static int launch_prefill(const RfAttn* a, AttnParams& p, cudaStream_t s) {
     attr = true;
   }
   dim3 grid(ceil_div(a->max_q_len, 64), a->Hq, a->num_seqs);
-  kfn<<<grid, 160, smem, s>>>(tmQ, tmK, tmV, p);
+  RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(grid), dim3(160), smem, s, 1, tmQ, tmK, tmV, p));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;
@@ -622,6 +625,7 @@ extern "C" uint64_t rf_attn_decode_scratch_bytes(int num_seqs, int Hq, int hd) {
 }
 
 extern "C" int rf_attn_decode(const RfAttn* a, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   AttnParams p;
   int rc = fill_params(a, &p);
   if (rc) return rc;
@@ -632,6 +636,7 @@ extern "C" int rf_attn_decode(const RfAttn* a, rf_stream_t stream) {
 }
 
 extern "C" int rf_attn_prefill(const RfAttn* a, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   AttnParams p;
   int rc = fill_params(a, &p);
   if (rc) return rc;

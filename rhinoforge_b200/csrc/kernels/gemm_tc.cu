@@ -50,7 +50,6 @@ struct alignas(8) GemmSmemCtl {
   uint64_t accum;
   uint32_t tmem_base;
   int32_t abort_flag;
-  uint32_t ar_call;
 };
 
 template <typename T, bool SWAP, bool DUAL>
@@ -84,7 +83,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     mbar_init(&ctl->accum, 1);
     ctl->abort_flag = 0;
-    ctl->ar_call = (p.ar_world > 1) ? *reinterpret_cast<volatile uint32_t*>(p.ar_state) : 0u;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -97,13 +95,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
+  // Only now may the next kernel start launching: its CTAs could take the last
+  // TMEM columns of this SM and then sit in their dependency wait, so this CTA
+  // must already own its columns (tcgen05.alloc blocks without a time limit).
+  // This kernel's own dependency wait comes later, after the weight prefetch.
+  pdl_launch_dependents();
 
   // ------------------------------------------------------- TMA producer ----
   if (warp == 0 && lane_id() == 0) {
     const uint32_t tx = (uint32_t)stage_bytes;
     int issued = 0;
     bool ok = true;
-    for (int i = 0; i < kb_count; ++i) {
+    auto load_weights = [&](int i, int s) {
+      uint8_t* st = smem + (size_t)s * stage_bytes;
+      const int kc = (kb0 + i) * kBK;
+      if (SWAP) {
+        tma_load_2d(st, &tmA, &ctl->full[s], kc, a0);
+        if (kATiles == 2) tma_load_2d(st + kATileBytes, &tmA, &ctl->full[s], kc, p.dual_offset + a0);
+      } else {
+        uint8_t* sb = st + kATiles * kATileBytes;
+        tma_load_2d(sb, &tmB, &ctl->full[s], kc, b0);
+        if (kBTiles == 2) tma_load_2d(sb + b_tile_bytes, &tmB, &ctl->full[s], kc, p.dual_offset + b0);
+      }
+    };
+    auto load_acts = [&](int i, int s) {
+      uint8_t* st = smem + (size_t)s * stage_bytes;
+      const int kc = (kb0 + i) * kBK;
+      if (SWAP) tma_load_2d(st + kATiles * kATileBytes, &tmB, &ctl->full[s], kc, b0);
+      else tma_load_2d(st, &tmA, &ctl->full[s], kc, a0);
+    };
+    // weights never depend on the previous kernel: fill the ring with them first
+    const int pre = min(p.stages, kb_count);
+    for (int i = 0; i < pre; ++i) {
+      mbar_arrive_expect_tx(&ctl->full[i], tx);
+      load_weights(i, i);
+    }
+    pdl_wait();
+    for (int i = 0; i < pre; ++i) load_acts(i, i);
+    issued = pre;
+    for (int i = pre; i < kb_count; ++i) {
       const int s = i % p.stages;
       const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
       if (!mbar_wait(&ctl->empty[s], ph ^ 1u)) {
@@ -112,14 +142,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         break;
       }
       if (*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag)) { ok = false; break; }
-      uint8_t* st = smem + (size_t)s * stage_bytes;
-      const int kc = (kb0 + i) * kBK;
       mbar_arrive_expect_tx(&ctl->full[s], tx);
-      tma_load_2d(st, &tmA, &ctl->full[s], kc, a0);
-      if (kATiles == 2) tma_load_2d(st + kATileBytes, &tmA, &ctl->full[s], kc, p.dual_offset + a0);
-      uint8_t* sb = st + kATiles * kATileBytes;
-      tma_load_2d(sb, &tmB, &ctl->full[s], kc, b0);
-      if (kBTiles == 2) tma_load_2d(sb + b_tile_bytes, &tmB, &ctl->full[s], kc, p.dual_offset + b0);
+      load_weights(i, s);
+      load_acts(i, s);
       issued = i + 1;
     }
     if (!ok) {
@@ -129,6 +154,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int i = first; i < issued; ++i)
         mbar_wait(&ctl->full[i % p.stages], (uint32_t)(i / p.stages) & 1u, 20ull * 1000 * 1000);
     }
+  } else {
+    pdl_wait();
   }
   // --------------------------------------------------------- MMA issuer ----
   if (warp == 1 && lane_id() == 0) {
@@ -189,7 +216,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const T* resid = reinterpret_cast<const T*>(p.residual);
   T* out = reinterpret_cast<T*>(p.out);
   const bool use_bias = bias != nullptr && (p.ar_world <= 1 || p.ar_rank == 0);
-  const uint32_t call = ctl->ar_call;
+  const uint32_t call = (p.ar_world > 1) ? *reinterpret_cast<volatile uint32_t*>(p.ar_state) : 0u;
   const uint64_t slot_off = (uint64_t)(call & 1u) * p.ar_half_bytes;
   const uint32_t crank = p.splits > 1 ? cluster_ctarank() : 0u;
 
@@ -243,23 +270,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     cluster_sync_all();
     if (!aborted) {
       const uint32_t my_part = smem_u32(part);
-      for (int c = (int)crank; c < ncols; c += p.splits) {
-        float g = 0.f, u = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-          const uint32_t base = dsmem_addr(my_part, (uint32_t)s);
-          g += ld_dsmem_f32(base + (uint32_t)(c * kBM + tid) * 4u);
-          if (DUAL) u += ld_dsmem_f32(base + (uint32_t)((bn + c) * kBM + tid) * 4u);
+      uint32_t peer_part[8];
+#pragma unroll
+      for (int s = 0; s < 8; ++s) peer_part[s] = dsmem_addr(my_part, (uint32_t)(s < p.splits ? s : 0));
+      // four columns per round: all remote loads are issued before the first add
+      for (int c0 = (int)crank; c0 < ncols; c0 += 4 * p.splits) {
+        float pg[4][8], pu[4][8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int c = c0 + q * p.splits;
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
+            pg[q][s] = 0.f;
+            pu[q][s] = 0.f;
+            if (s < p.splits && c < ncols) {
+              pg[q][s] = ld_dsmem_f32(peer_part[s] + (uint32_t)(c * kBM + tid) * 4u);
+              if (DUAL) pu[q][s] = ld_dsmem_f32(peer_part[s] + (uint32_t)((bn + c) * kBM + tid) * 4u);
+            }
+          }
         }
-        const int tok = SWAP ? (b0 + c) : a_idx;
-        const int n = SWAP ? a_idx : (b0 + c);
-        if (tok < M && n < N) {
-          const float v = finish(tok, n, g, u);
-          if (p.ar_world > 1) {
-            push_partial(tok, n, v);
-          } else {
-            float r = v;
-            if (resid) r += Num<T>::to_f(resid[(size_t)tok * p.ldr + n]);
-            out[(size_t)tok * p.ldo + n] = Num<T>::from_f(r);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int c = c0 + q * p.splits;
+          if (c >= ncols) break;
+          float g = 0.f, u = 0.f;
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
+            g += pg[q][s];
+            u += pu[q][s];
+          }
+          const int tok = SWAP ? (b0 + c) : a_idx;
+          const int n = SWAP ? a_idx : (b0 + c);
+          if (tok < M && n < N) {
+            const float v = finish(tok, n, g, u);
+            if (p.ar_world > 1) {
+              push_partial(tok, n, v);
+            } else {
+              float r = v;
+              if (resid) r += Num<T>::to_f(resid[(size_t)tok * p.ldr + n]);
+              out[(size_t)tok * p.ldo + n] = Num<T>::from_f(r);
+            }
           }
         }
       }
@@ -486,19 +536,8 @@ static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream)
   p.ar_world = g->ar_world; p.ar_rank = g->ar_rank;
   p.ar_recv = g->ar_recv; p.ar_flags = g->ar_flags; p.ar_state = g->ar_state;
   p.ar_half_bytes = g->ar_recv_bytes;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(pl.grid_x, pl.grid_y, pl.splits);
-  cfg.blockDim = dim3(128);
-  cfg.dynamicSmemBytes = pl.smem_bytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = (unsigned)pl.splits;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  RF_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kfn, tmA, tmB, p));
+  RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.grid_x, pl.grid_y, pl.splits), dim3(128), pl.smem_bytes, stream, pl.splits,
+                               tmA, tmB, p));
   ::rf::count_launch();
   return RF_OK;
 }
@@ -537,6 +576,7 @@ extern "C" int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem
 }
 
 extern "C" int rf_gemm(const RfGemm* g, rf_stream_t stream_) {
+  RF_SKIP_IF_REPLAYING();
   int rc = check_gemm(g);
   if (rc) return rc;
   RF_REQUIRE(!g->w_int8, "rf_gemm takes 16-bit weights; use rf_gemm_w8a16 for int8");

@@ -6,6 +6,7 @@
 // Replaces llama_gemv / llama_gemv_wint8 (src/ops/rpu_linear_gemv.cpp:1-275).
 #include "../common/dtype.cuh"
 #include "../common/host_util.h"
+#include "../common/ptx.cuh"
 #include "../rf_api.h"
 
 namespace rf {
@@ -78,6 +79,7 @@ __device__ __forceinline__ void gemv_rows(const GemvParams& p, int n0, int n1, b
 
 template <typename T, int MT, bool I8>
 __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
+  pdl_prologue();
   const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const bool dual = p.dual_offset > 0;
@@ -131,10 +133,10 @@ static int launch_gemv(const GemvParams& p, cudaStream_t s) {
   const int warps = dual ? p.N : (p.N + 1) / 2;
   const int wpb = 8;
   const int blocks = (warps + wpb - 1) / wpb;
-  if (p.M <= 1) gemv_kernel<T, 1, I8><<<blocks, wpb * 32, 0, s>>>(p);
-  else if (p.M <= 2) gemv_kernel<T, 2, I8><<<blocks, wpb * 32, 0, s>>>(p);
-  else if (p.M <= 4) gemv_kernel<T, 4, I8><<<blocks, wpb * 32, 0, s>>>(p);
-  else gemv_kernel<T, 8, I8><<<blocks, wpb * 32, 0, s>>>(p);
+  if (p.M <= 1) RF_CUDA_CHECK(::rf::launch_k(gemv_kernel<T, 1, I8>, dim3(blocks), dim3(wpb * 32), 0, s, 1, p));
+  else if (p.M <= 2) RF_CUDA_CHECK(::rf::launch_k(gemv_kernel<T, 2, I8>, dim3(blocks), dim3(wpb * 32), 0, s, 1, p));
+  else if (p.M <= 4) RF_CUDA_CHECK(::rf::launch_k(gemv_kernel<T, 4, I8>, dim3(blocks), dim3(wpb * 32), 0, s, 1, p));
+  else RF_CUDA_CHECK(::rf::launch_k(gemv_kernel<T, 8, I8>, dim3(blocks), dim3(wpb * 32), 0, s, 1, p));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;
@@ -145,6 +147,7 @@ static int launch_gemv(const GemvParams& p, cudaStream_t s) {
 using namespace rf;
 
 extern "C" int rf_gemv(const RfGemm* g, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(g && g->x && g->w && g->out, "gemv needs x, w and out");
   RF_REQUIRE(g->M >= 1 && g->M <= 8, "gemv handles 1..8 tokens, got %d", g->M);
   const int vec = g->w_int8 ? 16 : 8;

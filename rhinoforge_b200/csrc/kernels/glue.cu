@@ -6,6 +6,7 @@
 // host NEON lm_head_logits_top1 scan (src/core/rpu_backend.cpp:200-316).
 #include "../common/dtype.cuh"
 #include "../common/host_util.h"
+#include "../common/ptx.cuh"
 #include "../rf_api.h"
 
 namespace rf {
@@ -13,6 +14,7 @@ namespace rf {
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids,
                                  T* __restrict__ out, int H, int64_t ldo, float scale) {
+  pdl_prologue();
   const int i = blockIdx.x;
   const int id = ids[i];
   for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
@@ -36,6 +38,7 @@ template <typename T>
 __global__ void embedding_i8_kernel(const int8_t* __restrict__ table, const T* __restrict__ rscale,
                                     const int32_t* __restrict__ ids, T* __restrict__ out, int H,
                                     int64_t ldo, float scale) {
+  pdl_prologue();
   const int i = blockIdx.x;
   const int id = ids[i];
   const float s = id >= 0 ? Num<T>::to_f(rscale[id]) * scale : 0.f;
@@ -47,6 +50,7 @@ template <typename T>
 __global__ void scatter_rows_kernel(T* __restrict__ dst, const T* __restrict__ src,
                                     const int32_t* __restrict__ rows, int H, int64_t ldd,
                                     int64_t lds, int accumulate) {
+  pdl_prologue();
   const int i = blockIdx.x;
   const int r = rows[i];
   if (r < 0) return;
@@ -84,6 +88,7 @@ __device__ __forceinline__ float elt_op(int op, float a, float b, float alpha) {
 template <typename T>
 __global__ void eltwise_kernel(int op, const T* __restrict__ a, const T* __restrict__ b,
                                T* __restrict__ out, int64_t n, int64_t b_period, float alpha) {
+  pdl_prologue();
   const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= n) return;
   if (i + 8 <= n && (b_period == 0 || b_period % 8 == 0)) {
@@ -104,6 +109,7 @@ __global__ void eltwise_kernel(int op, const T* __restrict__ a, const T* __restr
 template <typename T>
 __global__ void cast_u8_kernel(const uint8_t* __restrict__ src, T* __restrict__ dst, int64_t n,
                                float scale, float shift) {
+  pdl_prologue();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) dst[i] = Num<T>::from_f((float)src[i] * scale + shift);
 }
@@ -146,6 +152,7 @@ __device__ __forceinline__ ArgPair block_argmax(ArgPair p, ArgPair* red) {
 template <typename T>
 __global__ void argmax_stage1(const T* __restrict__ x, int V, int64_t ld, ArgPair* __restrict__ part,
                               int chunks) {
+  pdl_prologue();
   __shared__ ArgPair red[32];
   const int row = blockIdx.y, ch = blockIdx.x;
   const int beg = ch * kArgmaxChunk, end = min(V, beg + kArgmaxChunk);
@@ -161,6 +168,7 @@ __global__ void argmax_stage1(const T* __restrict__ x, int V, int64_t ld, ArgPai
 
 __global__ void argmax_stage2(const ArgPair* __restrict__ part, int chunks, int32_t* out_ids,
                               float* out_vals, int32_t offset) {
+  pdl_prologue();
   __shared__ ArgPair red[32];
   const int row = blockIdx.x;
   ArgPair best{-INFINITY, 0x7fffffff};
@@ -183,14 +191,15 @@ using namespace rf;
 extern "C" int rf_embedding(const void* table, const int32_t* ids, void* out, int n_ids, int H,
                             int64_t ldo, float scale, int dtype, const void* row_scale_i8,
                             rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(table && ids && out && H % 8 == 0 && ldo % 8 == 0, "embedding arguments");
   if (n_ids == 0) return RF_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (row_scale_i8) {
-    RF_DISPATCH_T(dtype, embedding_i8_kernel<T><<<n_ids, 128, 0, s>>>(
-                             (const int8_t*)table, (const T*)row_scale_i8, ids, (T*)out, H, ldo, scale));
+    RF_DISPATCH_T(dtype, RF_CUDA_CHECK(::rf::launch_k(embedding_i8_kernel<T>, dim3(n_ids), dim3(128), 0, s, 1, 
+                             (const int8_t*)table, (const T*)row_scale_i8, ids, (T*)out, H, ldo, scale)));
   } else {
-    RF_DISPATCH_T(dtype, embedding_kernel<T><<<n_ids, 128, 0, s>>>((const T*)table, ids, (T*)out, H, ldo, scale));
+    RF_DISPATCH_T(dtype, RF_CUDA_CHECK(::rf::launch_k(embedding_kernel<T>, dim3(n_ids), dim3(128), 0, s, 1, (const T*)table, ids, (T*)out, H, ldo, scale)));
   }
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
@@ -200,10 +209,11 @@ extern "C" int rf_embedding(const void* table, const int32_t* ids, void* out, in
 extern "C" int rf_scatter_rows(void* dst, const void* src, const int32_t* rows, int n, int H,
                                int64_t ldd, int64_t lds, int accumulate, int dtype,
                                rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(dst && src && rows && H % 8 == 0 && ldd % 8 == 0 && lds % 8 == 0, "scatter_rows arguments");
   if (n == 0) return RF_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  RF_DISPATCH_T(dtype, scatter_rows_kernel<T><<<n, 128, 0, s>>>((T*)dst, (const T*)src, rows, H, ldd, lds, accumulate));
+  RF_DISPATCH_T(dtype, RF_CUDA_CHECK(::rf::launch_k(scatter_rows_kernel<T>, dim3(n), dim3(128), 0, s, 1, (T*)dst, (const T*)src, rows, H, ldd, lds, accumulate)));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;
@@ -211,6 +221,7 @@ extern "C" int rf_scatter_rows(void* dst, const void* src, const int32_t* rows, 
 
 extern "C" int rf_eltwise(int op, const void* a, const void* b, void* out, int64_t n,
                           int64_t b_period, float alpha, int dtype, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(a && out && n >= 0, "eltwise arguments");
   if (n == 0) return RF_OK;
   RF_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
@@ -219,7 +230,7 @@ extern "C" int rf_eltwise(int op, const void* a, const void* b, void* out, int64
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int threads = 256;
   const int blocks = (int)(((n + 7) / 8 + threads - 1) / threads);
-  RF_DISPATCH_T(dtype, eltwise_kernel<T><<<blocks, threads, 0, s>>>(op, (const T*)a, (const T*)b, (T*)out, n, b_period, alpha));
+  RF_DISPATCH_T(dtype, RF_CUDA_CHECK(::rf::launch_k(eltwise_kernel<T>, dim3(blocks), dim3(threads), 0, s, 1, op, (const T*)a, (const T*)b, (T*)out, n, b_period, alpha)));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;
@@ -227,12 +238,13 @@ extern "C" int rf_eltwise(int op, const void* a, const void* b, void* out, int64
 
 extern "C" int rf_cast_u8_f16(const uint8_t* src, void* dst, int64_t n, float scale, float shift,
                               int dtype, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(src && dst && n >= 0, "cast arguments");
   if (n == 0) return RF_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int threads = 256;
   const int blocks = (int)((n + threads - 1) / threads);
-  RF_DISPATCH_T(dtype, cast_u8_kernel<T><<<blocks, threads, 0, s>>>(src, (T*)dst, n, scale, shift));
+  RF_DISPATCH_T(dtype, RF_CUDA_CHECK(::rf::launch_k(cast_u8_kernel<T>, dim3(blocks), dim3(threads), 0, s, 1, src, (T*)dst, n, scale, shift)));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;
@@ -246,14 +258,15 @@ extern "C" uint64_t rf_argmax_scratch_bytes(int rows, int V) {
 extern "C" int rf_argmax(const void* logits, int rows, int V, int64_t ld, int32_t* out_ids,
                          float* out_vals, int32_t offset, void* scratch, uint64_t scratch_bytes,
                          int dtype, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(logits && out_ids && scratch && rows >= 0 && V > 0, "argmax arguments");
   if (rows == 0) return RF_OK;
   RF_REQUIRE(scratch_bytes >= rf_argmax_scratch_bytes(rows, V), "argmax scratch too small");
   const int chunks = (V + kArgmaxChunk - 1) / kArgmaxChunk;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 g1(chunks, rows);
-  RF_DISPATCH_T(dtype, argmax_stage1<T><<<g1, 256, 0, s>>>((const T*)logits, V, ld, (ArgPair*)scratch, chunks));
-  argmax_stage2<<<rows, 128, 0, s>>>((const ArgPair*)scratch, chunks, out_ids, out_vals, offset);
+  RF_DISPATCH_T(dtype, RF_CUDA_CHECK(::rf::launch_k(argmax_stage1<T>, dim3(g1), dim3(256), 0, s, 1, (const T*)logits, V, ld, (ArgPair*)scratch, chunks)));
+  RF_CUDA_CHECK(::rf::launch_k(argmax_stage2, dim3(rows), dim3(128), 0, s, 1, (const ArgPair*)scratch, chunks, out_ids, out_vals, offset));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;

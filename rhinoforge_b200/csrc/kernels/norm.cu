@@ -5,6 +5,7 @@
 // and the adaRMS SUB/MUL/ADD chain (src/fused/rpu_pi05_denoise_step_model.cpp:848-857).
 #include "../common/dtype.cuh"
 #include "../common/host_util.h"
+#include "../common/ptx.cuh"
 #include "../rf_api.h"
 
 namespace rf {
@@ -35,6 +36,7 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ re
                                T* __restrict__ residual_out, const T* __restrict__ mod,
                                int rows_per_mod, int H, int64_t ldx, int64_t ldy, float eps,
                                int mode) {
+  pdl_prologue();
   extern __shared__ float srow[];  // H floats + 32
   float* red = srow + H;
   const int row = blockIdx.x;
@@ -88,6 +90,7 @@ template <typename T>
 __global__ void layernorm_kernel(const T* __restrict__ x, const T* __restrict__ w,
                                  const T* __restrict__ b, T* __restrict__ y, int H, int64_t ldx,
                                  int64_t ldy, float eps) {
+  pdl_prologue();
   extern __shared__ float srow[];
   float* red = srow + H;
   const int row = blockIdx.x;
@@ -123,6 +126,7 @@ __global__ void layernorm_kernel(const T* __restrict__ x, const T* __restrict__ 
 template <typename T>
 __global__ void l2norm_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int H,
                               float eps, float out_scale) {
+  pdl_prologue();
   // one warp per row
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -143,6 +147,7 @@ template <typename T>
 __global__ void gated_residual_kernel(T* __restrict__ x, const T* __restrict__ y,
                                       const T* __restrict__ mod, int rows_per_mod, int H,
                                       int64_t total) {
+  pdl_prologue();
   const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= total) return;
   const int row = (int)(i / H), col = (int)(i % H);
@@ -163,6 +168,7 @@ extern "C" int rf_rmsnorm(const void* x, const void* residual, const void* w, vo
                           void* residual_out, const void* mod, int rows_per_mod, int rows, int H,
                           int64_t ldx, int64_t ldy, float eps, int mode, int dtype,
                           rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(rows >= 0 && H > 0 && H % 8 == 0, "rmsnorm H=%d must be a multiple of 8", H);
   RF_REQUIRE(ldx % 8 == 0 && ldy % 8 == 0, "rmsnorm pitches must be multiples of 8");
   if (rows == 0) return RF_OK;
@@ -171,14 +177,14 @@ extern "C" int rf_rmsnorm(const void* x, const void* residual, const void* w, vo
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (rows_per_mod <= 0) rows_per_mod = 1;
   if (dtype == 0)
-    rmsnorm_kernel<__half><<<rows, threads, smem, s>>>(
+    RF_CUDA_CHECK(::rf::launch_k(rmsnorm_kernel<__half>, dim3(rows), dim3(threads), smem, s, 1, 
         (const __half*)x, (const __half*)residual, (const __half*)w, (__half*)y,
-        (__half*)residual_out, (const __half*)mod, rows_per_mod, H, ldx, ldy, eps, mode);
+        (__half*)residual_out, (const __half*)mod, rows_per_mod, H, ldx, ldy, eps, mode));
   else
-    rmsnorm_kernel<__nv_bfloat16><<<rows, threads, smem, s>>>(
+    RF_CUDA_CHECK(::rf::launch_k(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), smem, s, 1, 
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w,
         (__nv_bfloat16*)y, (__nv_bfloat16*)residual_out, (const __nv_bfloat16*)mod, rows_per_mod,
-        H, ldx, ldy, eps, mode);
+        H, ldx, ldy, eps, mode));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;
@@ -186,19 +192,20 @@ extern "C" int rf_rmsnorm(const void* x, const void* residual, const void* w, vo
 
 extern "C" int rf_layernorm(const void* x, const void* w, const void* b, void* y, int rows, int H,
                             int64_t ldx, int64_t ldy, float eps, int dtype, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(rows >= 0 && H > 0 && H % 8 == 0, "layernorm H=%d must be a multiple of 8", H);
   if (rows == 0) return RF_OK;
   const int threads = H >= 2048 ? 256 : 128;
   const size_t smem = (size_t)(H + 32) * sizeof(float);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == 0)
-    layernorm_kernel<__half><<<rows, threads, smem, s>>>((const __half*)x, (const __half*)w,
+    RF_CUDA_CHECK(::rf::launch_k(layernorm_kernel<__half>, dim3(rows), dim3(threads), smem, s, 1, (const __half*)x, (const __half*)w,
                                                         (const __half*)b, (__half*)y, H, ldx, ldy,
-                                                        eps);
+                                                        eps));
   else
-    layernorm_kernel<__nv_bfloat16><<<rows, threads, smem, s>>>(
+    RF_CUDA_CHECK(::rf::launch_k(layernorm_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), smem, s, 1, 
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b,
-        (__nv_bfloat16*)y, H, ldx, ldy, eps);
+        (__nv_bfloat16*)y, H, ldx, ldy, eps));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;
@@ -206,16 +213,17 @@ extern "C" int rf_layernorm(const void* x, const void* w, const void* b, void* y
 
 extern "C" int rf_l2norm(const void* x, void* y, int rows, int H, float eps, float out_scale,
                          int dtype, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(rows >= 0 && H > 0, "l2norm shape");
   if (rows == 0) return RF_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int wpb = 4;
   const int blocks = ceil_div(rows, wpb);
   if (dtype == 0)
-    l2norm_kernel<__half><<<blocks, wpb * 32, 0, s>>>((const __half*)x, (__half*)y, rows, H, eps, out_scale);
+    RF_CUDA_CHECK(::rf::launch_k(l2norm_kernel<__half>, dim3(blocks), dim3(wpb * 32), 0, s, 1, (const __half*)x, (__half*)y, rows, H, eps, out_scale));
   else
-    l2norm_kernel<__nv_bfloat16><<<blocks, wpb * 32, 0, s>>>((const __nv_bfloat16*)x,
-                                                             (__nv_bfloat16*)y, rows, H, eps, out_scale);
+    RF_CUDA_CHECK(::rf::launch_k(l2norm_kernel<__nv_bfloat16>, dim3(blocks), dim3(wpb * 32), 0, s, 1, (const __nv_bfloat16*)x,
+                                                             (__nv_bfloat16*)y, rows, H, eps, out_scale));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;
@@ -223,6 +231,7 @@ extern "C" int rf_l2norm(const void* x, void* y, int rows, int H, float eps, flo
 
 extern "C" int rf_gated_residual(void* x, const void* y, const void* mod, int rows_per_mod,
                                  int rows, int H, int dtype, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(H % 8 == 0 && rows >= 0, "gated_residual H=%d must be a multiple of 8", H);
   if (rows == 0) return RF_OK;
   const int64_t total = (int64_t)rows * H;
@@ -231,11 +240,11 @@ extern "C" int rf_gated_residual(void* x, const void* y, const void* mod, int ro
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (rows_per_mod <= 0) rows_per_mod = 1;
   if (dtype == 0)
-    gated_residual_kernel<__half><<<blocks, threads, 0, s>>>((__half*)x, (const __half*)y,
-                                                           (const __half*)mod, rows_per_mod, H, total);
+    RF_CUDA_CHECK(::rf::launch_k(gated_residual_kernel<__half>, dim3(blocks), dim3(threads), 0, s, 1, (__half*)x, (const __half*)y,
+                                                           (const __half*)mod, rows_per_mod, H, total));
   else
-    gated_residual_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>(
-        (__nv_bfloat16*)x, (const __nv_bfloat16*)y, (const __nv_bfloat16*)mod, rows_per_mod, H, total);
+    RF_CUDA_CHECK(::rf::launch_k(gated_residual_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, 1, 
+        (__nv_bfloat16*)x, (const __nv_bfloat16*)y, (const __nv_bfloat16*)mod, rows_per_mod, H, total));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;

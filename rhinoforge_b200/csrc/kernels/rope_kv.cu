@@ -8,12 +8,14 @@
 // src/ops/rpu_rope.cpp, src/ops/rpu_mrope.cpp:37-124, src/ops/rpu_llama_kvcache.cpp).
 #include "../common/dtype.cuh"
 #include "../common/host_util.h"
+#include "../common/ptx.cuh"
 #include "../rf_api.h"
 
 namespace rf {
 
 template <typename T>
 __global__ void qk_norm_rope_kv_kernel(const RfRopeKv a) {
+  pdl_prologue();
   extern __shared__ float sh[];  // warps * hd floats
   const int tok = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -101,6 +103,7 @@ __global__ void qk_norm_rope_kv_kernel(const RfRopeKv a) {
 using namespace rf;
 
 extern "C" int rf_qk_norm_rope_kv(const RfRopeKv* a, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(a && a->qkv, "rope_kv: null arguments");
   RF_REQUIRE(a->hd > 0 && a->hd % 2 == 0 && a->rot_dim <= a->hd && a->rot_dim % 2 == 0,
              "rope_kv: head_dim %d / rot_dim %d", a->hd, a->rot_dim);
@@ -112,9 +115,9 @@ extern "C" int rf_qk_norm_rope_kv(const RfRopeKv* a, rf_stream_t stream) {
   const size_t smem = (size_t)warps * a->hd * sizeof(float);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (a->dtype == 0)
-    qk_norm_rope_kv_kernel<__half><<<a->tokens, warps * 32, smem, s>>>(*a);
+    RF_CUDA_CHECK(::rf::launch_k(qk_norm_rope_kv_kernel<__half>, dim3(a->tokens), dim3(warps * 32), smem, s, 1, *a));
   else
-    qk_norm_rope_kv_kernel<__nv_bfloat16><<<a->tokens, warps * 32, smem, s>>>(*a);
+    RF_CUDA_CHECK(::rf::launch_k(qk_norm_rope_kv_kernel<__nv_bfloat16>, dim3(a->tokens), dim3(warps * 32), smem, s, 1, *a));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;

@@ -10,6 +10,7 @@
 
 #include "../common/dtype.cuh"
 #include "../common/host_util.h"
+#include "../common/ptx.cuh"
 #include "../common/status.h"
 #include "../runtime/handle_registry.h"
 
@@ -241,6 +242,7 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
 __global__ void decode_advance_kernel(int32_t* pos, int pos_stride, int32_t* kv_len, int n,
                                       const int32_t* out_ids, int32_t* ids, int32_t* hist, int32_t* step,
                                       int hist_cap) {
+  pdl_prologue();
   // single block: n <= 1024 sequences
   const int i = threadIdx.x;
   const int st = step ? *step : 0;
@@ -297,6 +299,14 @@ extern "C" int rf_stack_set_layer(int64_t h, int32_t layer, const RfLayerWeights
   return RF_OK;
 }
 
+extern "C" int rf_stack_set_kv(int64_t h, int32_t layer, void* k_pool, void* v_pool) {
+  RF_GET_STACK(h);
+  RF_REQUIRE(layer >= 0 && layer < s.cfg.layers && k_pool && v_pool, "set_kv: layer %d", layer);
+  s.layers[layer].k_pool = k_pool;
+  s.layers[layer].v_pool = v_pool;
+  return RF_OK;
+}
+
 extern "C" int rf_stack_set_head(int64_t h, const void* final_norm_w, const void* final_norm_b,
                                  const void* w_lm, const void* s_lm) {
   RF_GET_STACK(h);
@@ -333,12 +343,14 @@ extern "C" int32_t* rf_stack_status_ptr(int64_t h) {
 }
 
 extern "C" int rf_stack_forward(int64_t h, const RfStackForward* f, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_GET_STACK(h);
   RF_REQUIRE(f != nullptr, "null forward args");
   return forward(s, *f, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int rf_stack_final_norm(int64_t h, const void* hidden, void* out, int32_t rows, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_GET_STACK(h);
   RF_REQUIRE(s.final_norm_w, "stack has no final norm");
   RfStackConfig c = s.cfg;
@@ -349,6 +361,7 @@ extern "C" int rf_stack_final_norm(int64_t h, const void* hidden, void* out, int
 
 extern "C" int rf_stack_head(int64_t h, const void* hidden, const int32_t* row_idx, int32_t rows,
                              int32_t* out_ids, float* out_vals, void* logits_out, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_GET_STACK(h);
   const RfStackConfig& c = s.cfg;
   RF_REQUIRE(s.base && s.final_norm_w && s.w_lm && c.vocab_local > 0, "stack has no lm head");
@@ -381,11 +394,19 @@ extern "C" int rf_stack_head(int64_t h, const void* hidden, const int32_t* row_i
 extern "C" int rf_decode_advance(int32_t* pos, int32_t pos_stride, int32_t* kv_len, int32_t n,
                                  const int32_t* out_ids, int32_t* ids, int32_t* hist, int32_t* step,
                                  int32_t hist_cap, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   if (n <= 0) return RF_OK;
   RF_REQUIRE(n <= 1024, "decode_advance handles up to 1024 sequences, got %d", n);
-  decode_advance_kernel<<<1, ((n + 31) / 32) * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      pos, pos_stride > 0 ? pos_stride : 1, kv_len, n, out_ids, ids, hist, step, hist_cap);
+  RF_CUDA_CHECK(::rf::launch_k(decode_advance_kernel, dim3(1), dim3(((n + 31) / 32) * 32), 0, static_cast<cudaStream_t>(stream), 1, 
+      pos, pos_stride > 0 ? pos_stride : 1, kv_len, n, out_ids, ids, hist, step, hist_cap));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;
+}
+
+// sizeof of every argument block, in the order the Python binding checks them
+extern "C" void rf_struct_sizes(int32_t* out) {
+  out[0] = (int32_t)sizeof(RfGemm); out[1] = (int32_t)sizeof(RfRopeKv); out[2] = (int32_t)sizeof(RfAttn);
+  out[3] = (int32_t)sizeof(RfStackConfig); out[4] = (int32_t)sizeof(RfLayerWeights);
+  out[5] = (int32_t)sizeof(RfStackComm); out[6] = (int32_t)sizeof(RfStackForward); out[7] = 0;
 }

@@ -88,6 +88,8 @@ typedef struct RfStackForward {
 int64_t rf_stack_create(const RfStackConfig* cfg);
 int rf_stack_destroy(int64_t h);
 int rf_stack_set_layer(int64_t h, int32_t layer, const RfLayerWeights* w);
+// Re-point one layer at another KV pool (binding a different cache object).
+int rf_stack_set_kv(int64_t h, int32_t layer, void* k_pool, void* v_pool);
 int rf_stack_set_head(int64_t h, const void* final_norm_w, const void* final_norm_b, const void* w_lm,
                       const void* s_lm);
 int rf_stack_set_comm(int64_t h, const RfStackComm* c);

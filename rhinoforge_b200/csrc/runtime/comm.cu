@@ -17,6 +17,7 @@ namespace rf {
 // flag line reach the same epoch.  One block, `world` threads.
 __global__ void peer_barrier_kernel(uint32_t* const* flags, int flag_base, uint32_t* state, int world,
                                     int rank, int32_t* status) {
+  pdl_prologue();
   const int t = threadIdx.x;
   const uint32_t want = state[2] + 1u;
   __threadfence_system();
@@ -36,6 +37,7 @@ struct ValIdx { float v; int32_t i; };
 __global__ void tp_argmax_merge_kernel(void* const* aux, uint32_t* const* flags, int flag_base,
                                        uint32_t* state, int world, int rank, int rows, int max_rows,
                                        const float* vals, int32_t* ids, int32_t* status) {
+  pdl_prologue();
   const int t = threadIdx.x;
   const uint32_t call = state[3];
   const uint32_t want = call + 1u;
@@ -82,10 +84,11 @@ using namespace rf;
 extern "C" int rf_tp_argmax_merge(void* const* aux, uint32_t* const* flags, int flag_base, uint32_t* state,
                                   int world, int rank, int rows, int max_rows, const float* vals,
                                   int32_t* ids, int32_t* status, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(aux && flags && state && vals && ids, "tp_argmax_merge arguments");
   RF_REQUIRE(world >= 1 && world <= 8 && rows > 0 && rows <= max_rows, "tp_argmax_merge shape");
-  tp_argmax_merge_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(aux, flags, flag_base, state, world, rank,
-                                                                         rows, max_rows, vals, ids, status);
+  RF_CUDA_CHECK(::rf::launch_k(tp_argmax_merge_kernel, dim3(1), dim3(128), 0, static_cast<cudaStream_t>(stream), 1, aux, flags, flag_base, state, world, rank,
+                                                                         rows, max_rows, vals, ids, status));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;
@@ -135,8 +138,9 @@ extern "C" int rf_ipc_close(void* p) {
 // [flag_base, flag_base + world) on every rank and state[2] as its epoch.
 extern "C" int rf_peer_barrier(uint32_t* const* flags, int flag_base, uint32_t* state, int world, int rank,
                                int32_t* status, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(flags && state && world >= 1 && world <= 8 && rank >= 0 && rank < world, "peer_barrier arguments");
-  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, flag_base, state, world, rank, status);
+  RF_CUDA_CHECK(::rf::launch_k(peer_barrier_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), 1, flags, flag_base, state, world, rank, status));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;

@@ -1,0 +1,9 @@
+"""Graph namespace: signature-keyed CUDA-graph caches and the manual capture helper."""
+from ._runtime import (GraphCache, GraphHandle, GraphSignature, backend_loaded, configure_backend,  # noqa: F401
+                       get_default_graph_cache, install_torch_namespace, reset_graph_cache)
+
+GraphSignature.__module__ = "rpu_backend.graph"
+GraphCache.__module__ = "rpu_backend.graph"
+
+__all__ = ["GraphCache", "GraphSignature", "GraphHandle", "configure_backend", "get_default_graph_cache",
+           "reset_graph_cache"]

@@ -1,0 +1,124 @@
+"""Loading W8A16 checkpoints (layout written by :mod:`rhinoforge_b200.quant.convert_qwen3`).
+
+Two consumers:
+
+* :func:`w8a16_tensor_getter` -- the streamed path used by ``from_pretrained(device="rpu")``:
+  int8 weights and their ``.weight_scale`` siblings go from the safetensors shards straight
+  into the engine's packer; nothing is dequantised and no host model object is created.
+* :func:`load_w8a16_model` -- the CPU path: a Hugging Face skeleton built on the ``meta`` device
+  whose quantised ``nn.Linear`` modules keep int8 ``weight`` Parameters and gain a
+  ``weight_scale`` buffer (reference behaviour: ``python/rpu_backend/quant/load.py:227-357``).
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import Callable, Dict, List
+
+import torch
+from torch import nn
+
+from .convert_qwen3 import EMBED, LM_HEAD, PROJECTION_SUFFIXES, scale_name
+
+W8A16_METHOD = "w8a16"
+
+
+def is_w8a16_config(config) -> bool:
+    qc = getattr(config, "quant_config", None)
+    if qc is None and isinstance(config, dict):
+        qc = config.get("quant_config")
+    return isinstance(qc, dict) and qc.get("method") == W8A16_METHOD
+
+
+def _shards(ckpt: Path) -> List[Path]:
+    idx = ckpt / "model.safetensors.index.json"
+    if idx.is_file():
+        wm = json.loads(idx.read_text())["weight_map"]
+        return [ckpt / s for s in sorted(set(wm.values()))]
+    single = ckpt / "model.safetensors"
+    if single.is_file():
+        return [single]
+    raise FileNotFoundError(f"no safetensors checkpoint in {ckpt}")
+
+
+def w8a16_tensor_getter(ckpt_dir: str, config=None) -> Callable[[str], torch.Tensor]:
+    """``get(name)`` over a W8A16 checkpoint; ``get.scale(name)`` returns the fp16 per-channel scale
+    of an int8 tensor (or ``None``), ``get.names`` the tensor names present."""
+    from ..api._loading import checkpoint_tensor_getter
+    base = checkpoint_tensor_getter(ckpt_dir)
+    names = base.names
+
+    def get(name: str) -> torch.Tensor:
+        if name == LM_HEAD and name not in names:
+            return base(EMBED)
+        t = base(name)
+        if name.endswith(PROJECTION_SUFFIXES) and t.dtype != torch.int8 and scale_name(name) in names:
+            raise TypeError(f"W8A16 projection {name!r} must be int8, got {t.dtype}")
+        return t
+
+    def scale(name: str):
+        if name == LM_HEAD and name not in names:
+            name = EMBED
+        sn = scale_name(name)
+        return base(sn).to(torch.float16) if sn in names else None
+
+    get.scale = scale      # type: ignore[attr-defined]
+    get.names = names      # type: ignore[attr-defined]
+    return get
+
+
+def _set_tensor(model: nn.Module, name: str, tensor: torch.Tensor) -> None:
+    mod_name, _, leaf = name.rpartition(".")
+    mod = model.get_submodule(mod_name) if mod_name else model
+    if leaf in mod._parameters:
+        mod._parameters[leaf] = nn.Parameter(tensor, requires_grad=False)
+    elif leaf in mod._buffers:
+        mod._buffers[leaf] = tensor
+    else:
+        raise KeyError(f"checkpoint tensor {name!r} has no destination in the model")
+
+
+def load_w8a16_model(config, ckpt_dir: str, *, dtype: torch.dtype = torch.float16, **_ignored) -> nn.Module:
+    """CPU model with int8 projection Parameters and ``weight_scale`` buffers; every other tensor in
+    ``dtype``.  Fails on partial loads (a projection without its scale, or left on ``meta``)."""
+    from safetensors.torch import load_file
+    from transformers import AutoModelForCausalLM
+    ckpt = Path(ckpt_dir)
+    with torch.device("meta"):
+        model = AutoModelForCausalLM.from_config(config)
+    seen: set = set()
+    for shard in _shards(ckpt):
+        for name, t in load_file(str(shard)).items():
+            if name.endswith(".weight_scale"):
+                owner = model.get_submodule(name[:-len(".weight_scale")])
+                owner.register_buffer("weight_scale", t.to(torch.float16))
+                seen.add(name)
+                continue
+            if t.dtype == torch.int8:
+                if not (name.endswith(PROJECTION_SUFFIXES) or name in (LM_HEAD, EMBED)):
+                    raise TypeError(f"unexpected int8 tensor {name!r} in a W8A16 checkpoint")
+                _set_tensor(model, name, t)
+            else:
+                _set_tensor(model, name, t.to(dtype) if t.is_floating_point() else t)
+            seen.add(name)
+    if getattr(config, "tie_word_embeddings", False) and LM_HEAD not in seen:
+        model.lm_head.weight = model.model.embed_tokens.weight
+    for n, p in model.named_parameters():
+        if p.is_meta:
+            raise RuntimeError(f"W8A16 checkpoint left {n!r} unloaded")
+        if p.dtype == torch.int8 and scale_name(n) not in seen:
+            raise RuntimeError(f"W8A16 tensor {n!r} has no {scale_name(n)!r}")
+    # rotary buffers created on meta need real storage
+    for mod in model.modules():
+        for bn, b in list(mod._buffers.items()):
+            if b is not None and b.is_meta:
+                if bn == "inv_freq" and hasattr(mod, "rope_init_fn"):
+                    inv, _ = mod.rope_init_fn(mod.config, torch.device("cpu"))
+                    mod._buffers[bn] = inv
+                else:
+                    mod._buffers[bn] = torch.zeros(b.shape, dtype=b.dtype)
+    model._rpu_w8a16 = True
+    return model.eval()
+
+
+__all__ = ["is_w8a16_config", "load_w8a16_model", "w8a16_tensor_getter", "W8A16_METHOD"]

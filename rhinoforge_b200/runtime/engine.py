@@ -73,14 +73,14 @@ class DecoderEngine:
     def __init__(self, cfg: DecoderConfig, get_weight: WeightGetter, *, device="cuda", dtype=torch.float16,
                  max_batch: int = 1, max_seq_len: int = 2048, max_prefill_tokens: int = 8192,
                  tp: Optional[TPContext] = None, quant: Optional[str] = None, decode_gemv_max_m: int = 0,
-                 hist_steps: int = 4096):
+                 hist_steps: int = 4096, kv_cache=None):
         if not torch.cuda.is_available():
             raise RPUBackendError("DecoderEngine needs a CUDA device")
         self.cfg, self.dtype = cfg, dtype
         self.tp = tp or TPContext.single(device)
         self.device = torch.device(self.tp.device if self.tp.device is not None else device)
         W, R = self.tp.world, self.tp.rank
-        self.max_batch, self.max_seq_len = max_batch, max_seq_len
+        self.max_batch = max_batch
         self.max_tokens = max(max_prefill_tokens, max_batch)
         self.quant = quant
         if quant not in (None, "w8a16"):
@@ -110,13 +110,11 @@ class DecoderEngine:
             N.check(-1, "rf_stack_create")
         self.handle = C.c_int64(h)
 
-        # ---- KV pool: [layers, 2, pages, Hkv, 16, hd], zero-filled (masked rows pass through the MMA)
-        self.pages_per_seq = (max_seq_len + 15) // 16
-        self.num_pages = max_batch * self.pages_per_seq
-        self.kv = torch.zeros((cfg.num_layers, 2, self.num_pages, self.Hkv, 16, hd), dtype=dtype, device=self.device)
-        self.pool = C.c_int64(lib.rf_kvpool_create(self.num_pages, max_batch, self.pages_per_seq))
-        self._pt_host = torch.zeros((max_batch, self.pages_per_seq), dtype=torch.int32).pin_memory()
-        self.page_table = torch.zeros((max_batch, self.pages_per_seq), dtype=torch.int32, device=self.device)
+        # ---- KV cache: a PagedKV (or RPUCache) object; replaceable through bind_cache()
+        from .kv_cache import PagedKV
+        self.cache = kv_cache if kv_cache is not None else PagedKV(cfg.num_layers, max_batch, max_seq_len, self.Hkv,
+                                                                     hd, device=self.device, dtype=dtype)
+        self._check_cache(self.cache)
 
         # ---- weights: packed once, kept alive here
         self._keep: List[torch.Tensor] = []
@@ -152,7 +150,6 @@ class DecoderEngine:
         self.step = torch.zeros(1, **i32)
         self.hist_steps = hist_steps
         self.hist = torch.zeros((hist_steps, max_batch), **i32)
-        self._host_len = [0] * max_batch
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.batch = 0
         self.launches_per_step = 0
@@ -163,14 +160,32 @@ class DecoderEngine:
         self._keep.append(t)
         return t
 
-    def _lin(self, w: torch.Tensor):
-        """Device weight (+ scale when quantised)."""
+    def _lin(self, get: WeightGetter, parts, cols=None):
+        """One packed linear: ``parts`` is a list of (tensor name, row slice); the pieces are
+        concatenated along the output dim, ``cols`` slices the input dim (row-parallel shards).
+        Returns (device weight, device per-channel scale or None).  int8 checkpoints keep their
+        stored scales; 16-bit weights are quantised here when the engine runs W8A16."""
+        scale_of = getattr(get, "scale", None)
+        ws, ss = [], []
+        for name, rows in parts:
+            w = get(name)
+            sc = scale_of(name) if (scale_of is not None and w.dtype == torch.int8) else None
+            w = w[rows]
+            if cols is not None:
+                w = w[:, cols]
+            ws.append(w)
+            ss.append(None if sc is None else sc[rows])
+        w = ws[0] if len(ws) == 1 else torch.cat(ws, 0)
+        if w.dtype == torch.int8:
+            if any(x is None for x in ss):
+                raise RPUBackendError(f"int8 weight {parts[0][0]!r} has no weight_scale")
+            if self.quant != "w8a16":
+                raise RPUBackendError("int8 weights need quant='w8a16'")
+            sc = ss[0] if len(ss) == 1 else torch.cat(ss, 0)
+            return self._dev(w), self._dev(sc.to(self.dtype))
         if self.quant == "w8a16":
-            if w.dtype != torch.int8:
-                q, s = quantize_per_channel(w.to(self.device), self.dtype)
-            else:
-                raise RPUBackendError("pre-quantised tensors must be passed with their scales")
-            return self._dev(q), self._dev(s)
+            q, sc = quantize_per_channel(w.to(self.device), self.dtype)
+            return self._dev(q), self._dev(sc)
         return self._dev(w), None
 
     def _pack_weights(self, get: WeightGetter, kv0: int, kv1: int) -> None:
@@ -181,24 +196,20 @@ class DecoderEngine:
         i0, i1 = shard_range(cfg.intermediate_size, W, R)
         v0, v1 = shard_range(cfg.vocab_size, W, R)
         ptr = lambda t: None if t is None else t.data_ptr()
+        qs, ks, isl = slice(q0 * hd, q1 * hd), slice(kv0 * hd, kv1 * hd), slice(i0, i1)
+        full = slice(None)
         for l in range(cfg.num_layers):
             p = f"model.layers.{l}."
-            wq, wk, wv = get(p + "self_attn.q_proj.weight"), get(p + "self_attn.k_proj.weight"), get(p + "self_attn.v_proj.weight")
-            wqkv = torch.cat((wq[q0 * hd:q1 * hd], wk[kv0 * hd:kv1 * hd], wv[kv0 * hd:kv1 * hd]), 0)
-            del wq, wk, wv
             bqkv = None
             if cfg.attention_bias:
                 bq, bk, bv = (get(p + f"self_attn.{n}_proj.bias") for n in "qkv")
-                bqkv = self._dev(torch.cat((bq[q0 * hd:q1 * hd], bk[kv0 * hd:kv1 * hd], bv[kv0 * hd:kv1 * hd]), 0))
-            wo = get(p + "self_attn.o_proj.weight")[:, q0 * hd:q1 * hd]
-            wgu = torch.cat((get(p + "mlp.gate_proj.weight")[i0:i1], get(p + "mlp.up_proj.weight")[i0:i1]), 0)
-            wd = get(p + "mlp.down_proj.weight")[:, i0:i1]
+                bqkv = self._dev(torch.cat((bq[qs], bk[ks], bv[ks]), 0))
             lw = N.RfLayerWeights()
-            t_qkv, s_qkv = self._lin(wqkv)
-            t_o, s_o = self._lin(wo)
-            t_gu, s_gu = self._lin(wgu)
-            t_d, s_d = self._lin(wd)
-            del wqkv, wo, wgu, wd
+            t_qkv, s_qkv = self._lin(get, [(p + "self_attn.q_proj.weight", qs), (p + "self_attn.k_proj.weight", ks),
+                                           (p + "self_attn.v_proj.weight", ks)])
+            t_o, s_o = self._lin(get, [(p + "self_attn.o_proj.weight", full)], cols=qs)
+            t_gu, s_gu = self._lin(get, [(p + "mlp.gate_proj.weight", isl), (p + "mlp.up_proj.weight", isl)])
+            t_d, s_d = self._lin(get, [(p + "mlp.down_proj.weight", full)], cols=isl)
             lw.wqkv, lw.sqkv, lw.bqkv = ptr(t_qkv), ptr(s_qkv), ptr(bqkv)
             lw.wo, lw.so = ptr(t_o), ptr(s_o)
             lw.w_up, lw.s_up = ptr(t_gu), ptr(s_gu)
@@ -208,17 +219,30 @@ class DecoderEngine:
             if cfg.qk_norm:
                 lw.q_norm_w = ptr(self._dev(get(p + "self_attn.q_norm.weight")))
                 lw.k_norm_w = ptr(self._dev(get(p + "self_attn.k_norm.weight")))
-            lw.k_pool, lw.v_pool = self.kv[l, 0].data_ptr(), self.kv[l, 1].data_ptr()
+            lw.k_pool, lw.v_pool = self.cache.layer_ptrs(l)
             N.check(lib.rf_stack_set_layer(self.handle, l, C.byref(lw)), "rf_stack_set_layer")
         emb = get("model.embed_tokens.weight")
-        self.embed = self._dev(emb)
-        lm = emb if cfg.tie_embeddings else get("lm_head.weight")
-        t_lm, s_lm = self._lin(lm[v0:v1])
+        self.embed_scale_rows = None
+        if emb.dtype == torch.int8:
+            sc = getattr(get, "scale")("model.embed_tokens.weight")
+            self.embed = self._dev(emb)
+            self.embed_scale_rows = self._dev(sc.to(self.dtype))
+        else:
+            self.embed = self._dev(emb)
+        names = getattr(get, "names", None)
+        has_head = (names is None and not cfg.tie_embeddings) or (names is not None and "lm_head.weight" in names)
+        head_name = "lm_head.weight" if has_head else "model.embed_tokens.weight"
+        t_lm, s_lm = self._lin(get, [(head_name, slice(v0, v1))])
         self.final_norm = self._dev(get("model.norm.weight"))
         N.check(lib.rf_stack_set_head(self.handle, C.c_void_p(self.final_norm.data_ptr()), None,
                                       C.c_void_p(t_lm.data_ptr()), C.c_void_p(ptr(s_lm))), "rf_stack_set_head")
-        del emb, lm
+        del emb
         torch.cuda.empty_cache()
+
+    def advance_lengths(self, n_steps: int) -> None:
+        """Account for ``n_steps`` graph replays issued outside :meth:`decode`."""
+        for s in range(self.batch):
+            self.cache.lengths[s] += n_steps
 
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._keep)
@@ -236,23 +260,42 @@ class DecoderEngine:
         if self.comm is not None and int(self.comm.status[0]) != 0:
             raise RPUBackendError(f"peer wait timed out: {self.comm.status.tolist()[:4]}")
 
-    def reset(self) -> None:
+    def _check_cache(self, cache) -> None:
+        want = (self.cfg.num_layers, self.Hkv, self.cfg.head_dim)
+        got = (cache.num_layers, cache.num_kv_heads, cache.head_dim)
+        if want != got or cache.dtype != self.dtype or cache.batch_size > self.max_batch:
+            raise RPUBackendError(f"KV cache geometry {got}/{cache.dtype}/batch {cache.batch_size} does not match the "
+                                  f"model {want}/{self.dtype}/max_batch {self.max_batch}")
+
+    def bind_cache(self, cache) -> None:
+        """Make ``cache`` the engine's KV store (pool pointers are re-bound; captured graphs that
+        baked the previous pool are dropped)."""
+        if cache is self.cache:
+            return
+        self._check_cache(cache)
         lib = N.lib()
-        for s in range(self.max_batch):
-            lib.rf_kvpool_release(self.pool, s)
-            self._host_len[s] = 0
+        for l in range(self.cfg.num_layers):
+            k, v = cache.layer_ptrs(l)
+            N.check(lib.rf_stack_set_kv(self.handle, l, C.c_void_p(k), C.c_void_p(v)), "rf_stack_set_kv")
+        self.cache = cache
+        self.graphs.clear()
+
+    @property
+    def max_seq_len(self) -> int:
+        return self.cache.max_seq_len
+
+    @max_seq_len.setter
+    def max_seq_len(self, v) -> None:
+        self._max_seq_len_hint = v
+
+    def reset(self) -> None:
+        for s in range(self.cache.batch_size):
+            self.cache.lengths[s] = 0
         self.step.zero_()
         self.batch = 0
 
-    def _reserve(self, seq: int, tokens: int) -> None:
-        row = self._pt_host[seq]
-        rc = N.lib().rf_kvpool_reserve(self.pool, seq, tokens, C.c_void_p(row.data_ptr()))
-        if rc != 0:
-            from ..api.errors import SPMExhaustionError
-            raise SPMExhaustionError(N.lib().rf_last_error().decode())
-
     def _embed(self, ids: torch.Tensor, n: int) -> None:
-        K.embedding(self.embed, ids, out=self.hidden[:n], scale=self.cfg.embed_scale)
+        K.embedding(self.embed, ids, out=self.hidden[:n], scale=self.cfg.embed_scale, row_scale=self.embed_scale_rows)
 
     def _head(self, rows: int, row_idx: Optional[torch.Tensor], logits_out: Optional[torch.Tensor] = None) -> None:
         N.check(N.lib().rf_stack_head(self.handle, C.c_void_p(self.hidden.data_ptr()),
@@ -265,26 +308,33 @@ class DecoderEngine:
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
-    def prefill(self, prompts: Sequence[torch.Tensor], *, return_logits: bool = False,
-                inputs_embeds: Optional[Sequence[torch.Tensor]] = None,
-                positions3: Optional[Sequence[torch.Tensor]] = None) -> torch.Tensor:
-        """Prefill sequences 0..B-1 with ``prompts`` (1-D int tensors, host or device).  Returns the
-        first greedy token of every sequence ([B] int32 on the device) and leaves the engine ready
-        for ``decode``.  Long batches run as several packed varlen chunks of at most
-        ``max_prefill_tokens`` rows (chunked prefill)."""
-        B = len(prompts)
-        if B > self.max_batch:
-            raise RPUBackendError(f"batch {B} exceeds max_batch {self.max_batch}")
+    def prefill(self, prompts: Sequence[torch.Tensor], **kw):
+        """Start sequences 0..B-1 from empty with ``prompts``; see :meth:`extend`."""
         self.reset()
-        lens = [int(p.numel()) for p in prompts]
+        return self.extend(prompts, **kw)
+
+    @torch.no_grad()
+    def extend(self, tokens: Sequence[torch.Tensor], *, return_logits: bool = False,
+               inputs_embeds: Optional[Sequence[torch.Tensor]] = None,
+               positions3: Optional[Sequence[torch.Tensor]] = None):
+        """Append ``tokens[s]`` (1-D int tensors, host or device) to sequence ``s`` at its current
+        length and return the greedy next token of every sequence ([B] int32 on the device; with
+        ``return_logits`` also the last-row logits of this rank's vocab shard).  Long inputs run as
+        several packed varlen launches of at most ``max_prefill_tokens`` rows (chunked prefill);
+        the engine is left ready for :meth:`decode`."""
+        B = len(tokens)
+        cache = self.cache
+        if B > cache.batch_size:
+            raise RPUBackendError(f"batch {B} exceeds the cache's batch_size {cache.batch_size}")
+        starts = [cache.lengths[s] for s in range(B)]
+        lens = [int(p.numel()) for p in tokens]
         for s, L in enumerate(lens):
-            if L < 1 or L + 1 > self.max_seq_len:
-                raise RPUBackendError(f"prompt of {L} tokens does not fit max_seq_len {self.max_seq_len}")
-            self._reserve(s, self.max_seq_len)
-        self.page_table.copy_(self._pt_host, non_blocking=True)
+            if L < 1:
+                raise RPUBackendError("every sequence needs at least one new token")
+            cache.check_fits(s, L + 1)
+        cache.reserve_all()
         logits_all = torch.empty((B, self.vocab_local), dtype=self.dtype, device=self.device) if return_logits else None
         first = torch.zeros(B, dtype=torch.int32, device=self.device)
-        # work items: (seq, start, count) packed into chunks of <= max_tokens rows
         chunk: List[tuple] = []
         used = 0
         items: List[List[tuple]] = []
@@ -302,22 +352,25 @@ class DecoderEngine:
         if chunk:
             items.append(chunk)
         for ch in items:
-            self._prefill_chunk(ch, prompts, lens, first, logits_all, inputs_embeds, positions3)
+            self._prefill_chunk(ch, tokens, lens, starts, first, logits_all, inputs_embeds, positions3)
         self.batch = B
         for s, L in enumerate(lens):
-            self._host_len[s] = L
-        # decode state: the token to feed next is `first`, at position L
+            cache.lengths[s] = starts[s] + L
+        # decode state: the token to feed next is `first`, at position = new length
         self.ids[:B].copy_(first)
+        new_len = torch.tensor([cache.lengths[s] for s in range(B)], dtype=torch.int32)
+        if self.device.type == "cuda":
+            new_len = new_len.pin_memory()
+        new_len = new_len.to(self.device, non_blocking=True)
         if positions3 is not None:
             nxt = torch.stack([p[:, -1].to(self.device) + 1 for p in positions3]).to(torch.int32)
             self.pos[:B].copy_(nxt)
         else:
-            posv = torch.tensor(lens, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
-            self.pos[:B].copy_(posv[:, None].expand(B, self.pos_stride))
-        self.kv_len[:B].copy_(torch.tensor([l + 1 for l in lens], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True))
+            self.pos[:B].copy_(new_len[:, None].expand(B, self.pos_stride))
+        self.kv_len[:B].copy_(new_len + 1)
         return (first, logits_all) if return_logits else first
 
-    def _prefill_chunk(self, ch, prompts, lens, first, logits_all, inputs_embeds, positions3) -> None:
+    def _prefill_chunk(self, ch, prompts, lens, starts, first, logits_all, inputs_embeds, positions3) -> None:
         T = sum(c[2] for c in ch)
         n = len(ch)
         meta = torch.empty((5, max(n, 1)), dtype=torch.int32)
@@ -327,11 +380,12 @@ class DecoderEngine:
         emb_rows = []
         pos3 = []
         for j, (s, off, cnt) in enumerate(ch):
-            meta[0, j], meta[1, j], meta[2, j] = o, cnt, off + cnt   # q_start, q_len, kv_len
+            base = starts[s]
+            meta[0, j], meta[1, j], meta[2, j] = o, cnt, base + off + cnt   # q_start, q_len, kv_len
             meta[3, j] = s
             meta[4, j] = o + cnt - 1
             tokmeta[0, o:o + cnt] = s
-            tokmeta[1, o:o + cnt] = torch.arange(off, off + cnt, dtype=torch.int32)
+            tokmeta[1, o:o + cnt] = torch.arange(base + off, base + off + cnt, dtype=torch.int32)
             ids_host[o:o + cnt] = prompts[s][off:off + cnt].to("cpu", torch.int32)
             if inputs_embeds is not None:
                 emb_rows.append(inputs_embeds[s][off:off + cnt])
@@ -342,7 +396,7 @@ class DecoderEngine:
         tok_d = tokmeta.pin_memory().to(self.device, non_blocking=True)
         ids_d = ids_host.pin_memory().to(self.device, non_blocking=True)
         # the page table the kernels see is indexed by chunk-local sequence number
-        pt = self.page_table[meta_d[3].long()].contiguous()
+        pt = self.cache.page_table[meta_d[3].long()].contiguous()
         seq_local = torch.repeat_interleave(torch.arange(n, dtype=torch.int32, device=self.device), meta_d[1].long())
         if inputs_embeds is not None:
             self.hidden[:T].copy_(torch.cat(emb_rows).to(self.device, self.dtype))
@@ -364,8 +418,8 @@ class DecoderEngine:
         qs, ql, kl = meta_d[0].contiguous(), meta_d[1].contiguous(), meta_d[2].contiguous()
         f.q_start, f.q_len, f.kv_len = qs.data_ptr(), ql.data_ptr(), kl.data_ptr()
         f.max_q_len = max(c[2] for c in ch)
-        f.max_kv_len = max(c[1] + c[2] for c in ch)
-        f.page_table, f.pt_stride, f.pool_pages = pt.data_ptr(), pt.stride(0), self.num_pages
+        f.max_kv_len = max(starts[c[0]] + c[1] + c[2] for c in ch)
+        f.page_table, f.pt_stride, f.pool_pages = pt.data_ptr(), pt.stride(0), self.cache.num_pages
         N.check(N.lib().rf_stack_forward(self.handle, C.byref(f), self._stream()), "rf_stack_forward")
         # sequences whose prompt ends in this chunk get their first token
         done = [(j, s) for j, (s, off, cnt) in enumerate(ch) if off + cnt == lens[s]]
@@ -391,7 +445,8 @@ class DecoderEngine:
         f.num_seqs = B
         f.kv_len = self.kv_len.data_ptr()
         f.max_q_len, f.max_kv_len = 1, self.max_seq_len
-        f.page_table, f.pt_stride, f.pool_pages = self.page_table.data_ptr(), self.page_table.stride(0), self.num_pages
+        pt = self.cache.page_table
+        f.page_table, f.pt_stride, f.pool_pages = pt.data_ptr(), pt.stride(0), self.cache.num_pages
         N.check(N.lib().rf_stack_forward(self.handle, C.byref(f), self._stream()), "rf_stack_forward")
         self._head(B, None, logits_out)
         N.check(N.lib().rf_decode_advance(C.c_void_p(self.pos.data_ptr()), self.pos_stride,
@@ -424,8 +479,7 @@ class DecoderEngine:
         if B == 0:
             raise RPUBackendError("decode() before prefill()")
         for s in range(B):
-            if self._host_len[s] + n_steps + 1 > self.max_seq_len:
-                raise RPUBackendError("decode would overflow the KV pages of the sequence")
+            self.cache.check_fits(s, n_steps + 1)
         start = int(self.step.item())
         if start + n_steps > self.hist_steps:
             self.step.zero_()
@@ -439,7 +493,7 @@ class DecoderEngine:
             for _ in range(n_steps):
                 self._decode_step(B)
         for s in range(B):
-            self._host_len[s] += n_steps
+            self.cache.lengths[s] += n_steps
         return self.hist[start:start + n_steps, :B].t()
 
     def step_from_host(self, host_ids: torch.Tensor, host_out: torch.Tensor) -> None:
@@ -450,7 +504,7 @@ class DecoderEngine:
         self.graphs[B].replay()
         host_out.copy_(self.out_ids[:B], non_blocking=True)
         for s in range(B):
-            self._host_len[s] += 1
+            self.cache.lengths[s] += 1
 
     @torch.no_grad()
     def generate(self, prompts: Sequence[torch.Tensor], max_new_tokens: int, *, use_graph: bool = True) -> torch.Tensor:
@@ -472,6 +526,5 @@ class DecoderEngine:
         if getattr(self, "handle", None) is not None:
             lib.rf_stack_destroy(self.handle)
             self.handle = None
-        if getattr(self, "pool", None) is not None:
-            lib.rf_kvpool_destroy(self.pool)
-            self.pool = None
+        if getattr(self, "cache", None) is not None:
+            self.cache.close()

@@ -1,0 +1,165 @@
+"""Host-only contract of the public package surface (no GPU needed)."""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_host_only_import_is_silent():
+    site = [p for p in sys.path if "site-packages" in p]
+    script = (f"import sys; sys.path.insert(0, {str(ROOT)!r}); sys.path.extend({site!r}); "
+              "import rpu_backend, torch; assert rpu_backend.__version__; assert hasattr(torch, 'rpu'); "
+              "import rhinoforge_b200; assert rhinoforge_b200.RPUCache is rpu_backend.RPUCache")
+    env = os.environ.copy()
+    env.pop("PYTHONPATH", None)
+    env["CUDA_VISIBLE_DEVICES"] = ""
+    r = subprocess.run([sys.executable, "-S", "-c", script], cwd=ROOT, env=env, text=True, capture_output=True)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout == "" and r.stderr == ""
+
+
+def test_nofile_preflight_is_silent_and_best_effort(monkeypatch, capsys):
+    from rpu_backend import _bootstrap_env
+    calls = []
+    monkeypatch.setattr(_bootstrap_env.resource, "getrlimit", lambda _k: (1024, 4096))
+    monkeypatch.setattr(_bootstrap_env.resource, "setrlimit", lambda k, v: calls.append((k, v)))
+    _bootstrap_env.ensure_nofile_limit()
+    assert calls == [(_bootstrap_env.resource.RLIMIT_NOFILE, (4096, 4096))]
+
+    def deny(*_a):
+        raise OSError("denied")
+    monkeypatch.setattr(_bootstrap_env.resource, "setrlimit", deny)
+    _bootstrap_env.ensure_nofile_limit()
+    out = capsys.readouterr()
+    assert out.out == out.err == ""
+
+
+def test_public_api_and_host_graph_lifecycle():
+    import torch
+    import rpu_backend
+    from rpu_backend.graph import GraphCache, GraphSignature
+    assert rpu_backend.__all__ == ["__version__", "RPUCache", "RPUModelForCausalLM", "reset_graph_cache"]
+    assert sorted(dir(rpu_backend)) == sorted(rpu_backend.__all__)
+    if torch.cuda.is_available():
+        pytest.skip("host-only lifecycle is checked without a device")
+    cache = GraphCache()
+    sig = GraphSignature(op_id="host-contract", shapes=(1, 16))
+    assert cache.phase == "CONFIGURING" and cache.size() == 0 and cache.cache_invariant_ok()
+    cache.begin_warmup()
+    with cache.capture(sig):
+        pass
+    assert cache.phase == "WARMING"
+    with pytest.raises(RuntimeError, match=r"requires the C\+\+ backend"):
+        cache.freeze()
+    assert cache.explain_miss(sig).startswith("miss at GmId")
+
+
+def test_removed_names_point_to_replacements():
+    import rpu_backend
+    with pytest.raises(AttributeError, match="RPUCache.from_model"):
+        rpu_backend.build_rpu_cache
+    with pytest.warns(DeprecationWarning):
+        assert rpu_backend.GraphCache is rpu_backend.graph.GraphCache
+
+
+def test_external_adapter_registration():
+    from rpu_backend.runtime import registry
+
+    class PublicTestAdapter:
+        pass
+
+    arch = "RhinoForgePublicTestArchitecture"
+    try:
+        registry.register_adapter(arch, PublicTestAdapter)
+        assert registry.get_adapter(arch) is PublicTestAdapter
+        assert arch in registry.list_adapters()
+        registry.register_adapter(arch, PublicTestAdapter)
+        with pytest.raises(RuntimeError, match="already registered"):
+            registry.register_adapter(arch, type("OtherAdapter", (), {}))
+    finally:
+        registry.ADAPTERS.pop(arch, None)
+
+
+def test_plugins_cannot_shadow_builtins():
+    from rpu_backend.runtime import registry
+    api = registry._plugin_api(frozenset(registry.ADAPTERS))
+    with pytest.raises(RuntimeError, match="built-in"):
+        api.register_adapter("Qwen3ForCausalLM", type("Shadow", (), {}))
+    from rpu_backend.api.errors import UnsupportedModelError
+    with pytest.raises(UnsupportedModelError):
+        registry.get_adapter("NoSuchArchitectureForCausalLM")
+
+
+def test_builtin_adapters_load_lazily():
+    r = subprocess.run([sys.executable, "-c",
+                        "import sys; import rpu_backend; "
+                        "assert not any(m.startswith('rhinoforge_b200.adapters.qwen3') for m in sys.modules); "
+                        "from rpu_backend.runtime.registry import get_adapter; "
+                        "c = get_adapter('Qwen3ForCausalLM'); assert c.__name__ == 'Qwen3Adapter'"],
+                       cwd=ROOT, text=True, capture_output=True, env={**os.environ, "CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0, r.stderr
+
+
+def test_registry_excludes_unsupported_profiles():
+    from rpu_backend import model_registry
+    required = {"qwen3-0.6b", "llama-3.2-1b", "qwen3-vl-2b", "qwen3-vl-4b", "qwen3_5-0.8b", "dinov3-vit-b",
+                "pi05-libero-finetuned", "qwen3-14b-w8a16-lmhead-int8"}
+    excluded = {"qwen3-vl-8b", "dinov3-vit-s", "dinov3-vit-l", "gemma2", "paligemma2", "lingbot-vla-4b", "qwen3-14b",
+                "qwen3-0.6b-w8a16-lmhead-int8", "qwen3-8b-w8a16-lmhead-int8", "qwen3-0.6b-instruct"}
+    assert required <= model_registry.MODELS.keys()
+    assert excluded.isdisjoint(model_registry.MODELS)
+    for rel in model_registry.MODELS.values():
+        p = Path(rel)
+        assert not p.is_absolute() and ".." not in p.parts
+    with pytest.raises(KeyError, match="Unknown model"):
+        model_registry.model_path("nope")
+
+
+def test_model_cache_override(monkeypatch, tmp_path):
+    from rpu_backend import model_registry
+    monkeypatch.setenv("RPU_MODEL_CACHE", str(tmp_path))
+    monkeypatch.delenv("HF_HOME", raising=False)
+    assert model_registry.model_path("qwen3-0.6b") == tmp_path / "Qwen3-0.6B"
+    assert model_registry.hf_cache_root() == tmp_path / ".hf"
+
+
+def test_error_hierarchy():
+    from rpu_backend.api import errors as E
+    for name in ("RPUConfigError", "UnsupportedModelError", "RPUUnsupportedDtypeError", "RPUSingleHandleError",
+                 "SPMExhaustionError", "WeightShapeMismatchError"):
+        assert issubclass(getattr(E, name), E.RPUBackendError)
+
+
+def test_strict_boolean_env_parser(monkeypatch):
+    from rpu_backend.runtime.control import rpu_env_bool, rpu_env_exact1
+    monkeypatch.delenv("RPU_TEST_FLAG", raising=False)
+    assert rpu_env_bool("RPU_TEST_FLAG", True) is True
+    for raw, want in ((" On ", True), ("1", True), ("false", False), ("", False), ("0", False)):
+        monkeypatch.setenv("RPU_TEST_FLAG", raw)
+        assert rpu_env_bool("RPU_TEST_FLAG") is want
+    monkeypatch.setenv("RPU_TEST_FLAG", "yes")
+    with pytest.raises(ValueError, match="must be one of"):
+        rpu_env_bool("RPU_TEST_FLAG")
+    assert rpu_env_exact1("RPU_TEST_FLAG") is False
+    monkeypatch.setenv("RPU_TEST_FLAG", "1")
+    assert rpu_env_exact1("RPU_TEST_FLAG") is True
+
+
+def test_native_struct_layouts_match_ctypes():
+    """The ctypes mirrors must have the C sizes, or every kernel argument would be misread."""
+    import ctypes as C
+    from rhinoforge_b200 import _native as N
+    if not N.available():
+        pytest.skip("native library not built")
+    lib = N.lib()
+    sizes = (C.c_int32 * 8)()
+    lib.rf_struct_sizes(sizes)
+    got = [C.sizeof(t) for t in (N.RfGemm, N.RfRopeKv, N.RfAttn, N.RfStackConfig, N.RfLayerWeights, N.RfStackComm,
+                                 N.RfStackForward)]
+    assert list(sizes)[:7] == got

@@ -1,0 +1,103 @@
+"""W8A16 / W4 quantisation helpers, the offline converter and the loader layout (CPU)."""
+import json
+from pathlib import Path
+
+import pytest
+import torch
+
+
+def test_per_channel_int8_quantisation():
+    from rpu_backend.quant._common import (cosine, dequantize_linear_per_channel, quantize_linear_per_channel,
+                                           reference_linear)
+    w = torch.randn(64, 128) * 0.05
+    q, s = quantize_linear_per_channel(w)
+    assert q.dtype == torch.int8 and int(q.min()) >= -127 and int(q.max()) <= 127
+    assert s.dtype == torch.float16 and s.shape == (64,)
+    assert cosine(dequantize_linear_per_channel(q, s), w) > 0.999
+    x = torch.randn(5, 128)
+    assert cosine(reference_linear(x, q, s), x @ w.t()) > 0.999
+    with pytest.raises(ValueError):
+        quantize_linear_per_channel(torch.randn(3))
+
+
+def test_w8a16_config_marker():
+    from types import SimpleNamespace
+    from rpu_backend.quant.load import is_w8a16_config
+    assert is_w8a16_config(SimpleNamespace(quant_config={"method": "w8a16"}))
+    assert not is_w8a16_config(SimpleNamespace(quant_config={"method": "gptq"}))
+    assert not is_w8a16_config(SimpleNamespace())
+
+
+def test_int4_and_nvfp4_packers_round_trip():
+    from rpu_backend.quant.int4_pack import pack_int4, quantize_pack_int4, unpack_int4
+    from rpu_backend.quant.int4_pgrp_pack import dequantize_int4_pgrp, quantize_pack_int4_pgrp
+    from rpu_backend.quant.nvfp4_pack import dequantize_nvfp4, quantize_nvfp4
+    from rpu_backend.quant._common import cosine
+    q = torch.randint(-8, 8, (7, 64), dtype=torch.int8)
+    assert torch.equal(unpack_int4(pack_int4(q)), q)
+    w = torch.randn(32, 128) * 0.1
+    p, s = quantize_pack_int4(w)
+    assert p.shape == (32, 64) and s.shape == (32,)
+    pg, sg = quantize_pack_int4_pgrp(w, 32)
+    assert sg.shape == (32, 4) and cosine(dequantize_int4_pgrp(pg, sg, 32), w) > 0.98
+    pk, bs, ts = quantize_nvfp4(w)
+    assert pk.shape == (32, 64) and bs.shape == (32, 8) and bs.dtype == torch.uint8
+    assert cosine(dequantize_nvfp4(pk, bs, ts), w) > 0.97
+
+
+def _tiny_ckpt(path: Path, tie=True):
+    from safetensors.torch import save_file
+    from transformers import Qwen3Config
+    from rhinoforge_b200.models.decoder import random_state_dict, tiny_config
+    cfg = tiny_config(tie_embeddings=tie)
+    hf = Qwen3Config(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
+                     num_hidden_layers=cfg.num_layers, num_attention_heads=cfg.num_heads,
+                     num_key_value_heads=cfg.num_kv_heads, head_dim=cfg.head_dim, tie_word_embeddings=tie,
+                     max_position_embeddings=512, architectures=["Qwen3ForCausalLM"])
+    path.mkdir(parents=True)
+    hf.save_pretrained(path)
+    sd = random_state_dict(cfg, dtype=torch.float16)
+    save_file({k: v.contiguous() for k, v in sd.items()}, str(path / "model.safetensors"), metadata={"format": "pt"})
+    (path / "tokenizer_config.json").write_text("{}")
+    return cfg, sd
+
+
+def test_converter_layout_and_refusal_to_overwrite(tmp_path):
+    from safetensors.torch import load_file
+    from rpu_backend.quant.convert_qwen3 import convert_checkpoint, main
+    from rpu_backend.quant._common import cosine, dequantize_linear_per_channel
+    cfg, sd = _tiny_ckpt(tmp_path / "src", tie=True)
+    stats = convert_checkpoint(tmp_path / "src", tmp_path / "dst", ["lm_head"], quant_lm_head=True)
+    assert stats["n_quantized"] == 7 * cfg.num_layers + 1
+    out = load_file(str(tmp_path / "dst" / "model.safetensors"))
+    name = "model.layers.0.mlp.down_proj.weight"
+    assert out[name].dtype == torch.int8 and out["model.layers.0.mlp.down_proj.weight_scale"].dtype == torch.float16
+    assert cosine(dequantize_linear_per_channel(out[name], out[name[:-7] + ".weight_scale"]), sd[name]) > 0.999
+    assert out["lm_head.weight"].dtype == torch.int8 and out["model.embed_tokens.weight"].dtype == torch.float16
+    assert out["model.layers.0.input_layernorm.weight"].dtype == torch.float16
+    qc = json.loads((tmp_path / "dst" / "config.json").read_text())["quant_config"]
+    assert qc == {"method": "w8a16", "mode": "per_channel_symmetric", "qaxis": 0, "skip_modules": [],
+                  "quantized_lm_head": True, "quantized_embed_tokens": False, "lm_head_untied": True,
+                  "embed_tokens_untied": False}
+    assert (tmp_path / "dst" / "tokenizer_config.json").is_file()
+    assert main(["--src", str(tmp_path / "src"), "--dst", str(tmp_path / "dst")]) == 1
+    assert main(["--src", str(tmp_path / "src"), "--dst", str(tmp_path / "d2"), "--quant-embed-tokens"]) == 1
+    assert not list(tmp_path.glob(".*tmp*"))
+
+
+def test_w8a16_loader_keeps_int8_parameters(tmp_path):
+    from transformers import AutoConfig
+    from rpu_backend.quant.convert_qwen3 import convert_checkpoint
+    from rpu_backend.quant.load import is_w8a16_config, load_w8a16_model, w8a16_tensor_getter
+    _tiny_ckpt(tmp_path / "src", tie=False)
+    convert_checkpoint(tmp_path / "src", tmp_path / "dst", ["lm_head"])
+    config = AutoConfig.from_pretrained(tmp_path / "dst")
+    assert is_w8a16_config(config)
+    model = load_w8a16_model(config, str(tmp_path / "dst"))
+    lin = model.model.layers[0].self_attn.q_proj
+    assert lin.weight.dtype == torch.int8 and lin.weight_scale.dtype == torch.float16
+    assert model.lm_head.weight.dtype == torch.float16
+    get = w8a16_tensor_getter(str(tmp_path / "dst"))
+    assert get("model.layers.1.mlp.up_proj.weight").dtype == torch.int8
+    assert get.scale("model.layers.1.mlp.up_proj.weight").shape == (512,)
+    assert get.scale("model.norm.weight") is None
