@@ -1,0 +1,221 @@
+#!/usr/bin/env python
+"""Same-box baseline: the decoder in plain PyTorch eager mode (cuBLAS GEMMs, SDPA attention, dense
+KV cache) with Megatron-style tensor parallelism over NCCL.  None of this repository's kernels or
+runtime is used.  It measures the same metric as ``bench.py`` on the same configuration.
+
+    python baseline/eager_tp.py --gpus 1 --batch 64 --steps 64
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P baseline/eager_tp.py --gpus N --batch 64 --steps 64 [--cuda-graph]
+
+``--cuda-graph`` additionally captures the eager decode step in a CUDA graph (a stronger baseline).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+from pathlib import Path
+
+import torch
+import torch.nn.functional as F
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+from rhinoforge_b200.models.decoder import PROFILES, DecoderConfig, rope_tables  # noqa: E402  (shapes only)
+
+
+def _rand(shape, seed, dtype, dev, std=0.02):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    out = torch.empty(shape, dtype=dtype, device=dev)
+    rows = max(1, (64 << 20) // (shape[-1] * 4))
+    for r in range(0, shape[0], rows):
+        n = min(rows, shape[0] - r)
+        out[r:r + n] = (torch.randn((n, shape[-1]), generator=g, device=dev) * std).to(dtype)
+    return out
+
+
+class EagerTPDecoder:
+    def __init__(self, cfg: DecoderConfig, world: int, rank: int, dev, dtype, max_batch: int, max_len: int):
+        self.cfg, self.world, self.rank, self.dev, self.dtype = cfg, world, rank, dev, dtype
+        H, hd = cfg.hidden_size, cfg.head_dim
+        self.Hq = cfg.num_heads // world
+        self.Hkv = max(1, cfg.num_kv_heads // world)
+        I = cfg.intermediate_size // world
+        self.layers = []
+        for l in range(cfg.num_layers):
+            s = 1000 * l
+            self.layers.append(dict(
+                qkv=_rand(((self.Hq + 2 * self.Hkv) * hd, H), s + 1 + rank, dtype, dev),
+                o=_rand((H, self.Hq * hd), s + 2 + rank, dtype, dev),
+                gu=_rand((2 * I, H), s + 3 + rank, dtype, dev),
+                down=_rand((H, I), s + 4 + rank, dtype, dev),
+                n1=torch.ones(H, dtype=dtype, device=dev), n2=torch.ones(H, dtype=dtype, device=dev),
+                qn=torch.ones(hd, dtype=dtype, device=dev), kn=torch.ones(hd, dtype=dtype, device=dev)))
+        self.embed = _rand((cfg.vocab_size, H), 7, dtype, dev)
+        self.lm = _rand((cfg.vocab_size // world, H), 9 + rank, dtype, dev)
+        self.norm = torch.ones(H, dtype=dtype, device=dev)
+        cos, sin = rope_tables(cfg, max_len + 8, dev)
+        self.cos, self.sin = torch.cat((cos, cos), -1).to(dtype), torch.cat((sin, sin), -1).to(dtype)
+        self.k = [torch.zeros(max_batch, self.Hkv, max_len, hd, dtype=dtype, device=dev) for _ in range(cfg.num_layers)]
+        self.v = [torch.zeros_like(t) for t in self.k]
+        self.I = I
+
+    def _norm(self, x, w):
+        return F.rms_norm(x, (x.shape[-1],), w, self.cfg.rms_eps)
+
+    def _rope(self, t, pos):      # t [B, S, h, hd], pos [B, S]
+        c, s = self.cos[pos][:, :, None], self.sin[pos][:, :, None]
+        half = t.shape[-1] // 2
+        rot = torch.cat((-t[..., half:], t[..., :half]), -1)
+        return t * c + rot * s
+
+    def forward(self, ids: torch.Tensor, pos: torch.Tensor, kv_len: int):
+        """ids/pos [B, S]; positions are contiguous and equal across the batch; kv_len = tokens after this call."""
+        import torch.distributed as dist
+        cfg = self.cfg
+        B, S = ids.shape
+        hd = cfg.head_dim
+        x = F.embedding(ids, self.embed)
+        start = kv_len - S
+        for l, w in enumerate(self.layers):
+            h = self._norm(x, w["n1"])
+            qkv = F.linear(h, w["qkv"]).view(B, S, self.Hq + 2 * self.Hkv, hd)
+            q, k, v = qkv[:, :, :self.Hq], qkv[:, :, self.Hq:self.Hq + self.Hkv], qkv[:, :, self.Hq + self.Hkv:]
+            if cfg.qk_norm:
+                q, k = self._norm(q, w["qn"]), self._norm(k, w["kn"])
+            q, k = self._rope(q, pos), self._rope(k, pos)
+            self.k[l][:B, :, start:kv_len] = k.transpose(1, 2)
+            self.v[l][:B, :, start:kv_len] = v.transpose(1, 2)
+            a = F.scaled_dot_product_attention(q.transpose(1, 2), self.k[l][:B, :, :kv_len], self.v[l][:B, :, :kv_len],
+                                               is_causal=(S > 1), enable_gqa=True)
+            o = F.linear(a.transpose(1, 2).reshape(B, S, self.Hq * hd), w["o"])
+            if self.world > 1:
+                dist.all_reduce(o)
+            x = x + o
+            h = self._norm(x, w["n2"])
+            gu = F.linear(h, w["gu"])
+            m = F.linear(F.silu(gu[..., :self.I]) * gu[..., self.I:], w["down"])
+            if self.world > 1:
+                dist.all_reduce(m)
+            x = x + m
+        x = self._norm(x[:, -1], self.norm)
+        logits = F.linear(x, self.lm)
+        val, idx = logits.float().max(-1)
+        idx = idx + self.rank * logits.shape[-1]
+        if self.world > 1:
+            vals = [torch.empty_like(val) for _ in range(self.world)]
+            idxs = [torch.empty_like(idx) for _ in range(self.world)]
+            dist.all_gather(vals, val)
+            dist.all_gather(idxs, idx)
+            best = torch.stack(vals).argmax(0)
+            idx = torch.stack(idxs).gather(0, best[None])[0]
+        return idx
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--model", default="qwen3-8b")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--dtype", default="fp16")
+    ap.add_argument("--cuda-graph", action="store_true")
+    a = ap.parse_args()
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    assert world == a.gpus
+    dtype = torch.float16 if a.dtype == "fp16" else torch.bfloat16
+    cfg = PROFILES[a.model]
+    B, P = a.batch, a.prompt_len
+    max_len = P + a.steps + a.warmup + 8
+    m = EagerTPDecoder(cfg, world, rank, dev, dtype, B, max_len)
+    gen = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (B, P), generator=gen).to(dev)
+
+    def sync_max(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    with torch.no_grad():
+        ttft = []
+        for _ in range(2):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            nxt = None
+            for b0 in range(0, B, 8):      # 8192-token prefill chunks, like the engine
+                pos = torch.arange(P, device=dev)[None].expand(min(8, B - b0), P)
+                ks, vs = m.k, m.v          # the chunk works on a batch slice of the caches
+                m.k = [t[b0:b0 + 8] for t in ks]
+                m.v = [t[b0:b0 + 8] for t in vs]
+                part = m.forward(ids[b0:b0 + 8], pos, P)
+                m.k, m.v = ks, vs
+                nxt = part if nxt is None else torch.cat((nxt, part))
+            e1.record()
+            torch.cuda.synchronize()
+            ttft.append(sync_max(e0.elapsed_time(e1)))
+        cur = nxt[:, None]
+        step_pos = torch.full((B, 1), P, device=dev, dtype=torch.long)
+        graph = None
+        kv = P
+        if a.cuda_graph:
+            # eager SDPA takes the KV length as a host value, so one captured step has a fixed length:
+            # the graph variant replays a step at the final length (an upper bound on the work)
+            kv = P + a.warmup + a.steps
+            static_ids = cur.clone()
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                m.forward(static_ids, step_pos, kv)
+            torch.cuda.current_stream().wait_stream(s)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = m.forward(static_ids, step_pos, kv)
+
+        def step():
+            nonlocal cur, kv
+            if graph is not None:
+                graph.replay()
+            else:
+                kv += 1
+                cur = m.forward(cur, step_pos + (kv - 1 - P), kv)[:, None]
+
+        for _ in range(a.warmup):
+            step()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = sync_max(e0.elapsed_time(e1)) / a.steps
+    if rank == 0:
+        print(json.dumps({"impl": "baseline-eager-nccl" + ("-cudagraph" if a.cuda_graph else ""),
+                          "metric": "decode_tokens_per_s", "value": B * 1000.0 / ms, "unit": "tokens/s",
+                          "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms,
+                          "ttft_ms_p50": statistics.median(ttft), "dtype": a.dtype, "data": "synthetic",
+                          "config": {"model": cfg.name, "global_batch": B, "seq_len": P, "parallelism": f"tp{world}"}}))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

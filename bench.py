@@ -36,6 +36,9 @@ def parse_args(argv=None):
     ap.add_argument("--quant", default=None, choices=[None, "w8a16"])
     ap.add_argument("--sweep", default="", help="extra batch sizes to report, e.g. 1,8,32")
     ap.add_argument("--ttft-samples", type=int, default=3)
+    ap.add_argument("--no-graph", action="store_true", help="launch decode steps eagerly (kernel profiling only)")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     return ap.parse_args(argv)
 
 
@@ -108,7 +111,7 @@ def run(args) -> dict:
     max_seq = args.prompt_len + args.steps * 2 + args.warmup + 64
     t0 = time.time()
     eng = DecoderEngine(cfg, random_weight_getter(cfg, seed=0, std=0.02, dtype=dtype, device=dev), dtype=dtype,
-                        max_batch=max_b, max_seq_len=max_seq, max_prefill_tokens=8192 if tp.world == 1 else 2048,
+                        max_batch=max_b, max_seq_len=max_seq, max_prefill_tokens=8192,
                         tp=tp, quant=args.quant)
     torch.cuda.synchronize()
     startup_s = time.time() - t0
@@ -139,8 +142,16 @@ def run(args) -> dict:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         g = eng.graphs[B]
+        if args.profiler_range:
+            torch.cuda.profiler.start()
         for _ in range(args.steps):
-            g.replay()
+            if args.no_graph:
+                eng._decode_step(B)
+            else:
+                g.replay()
+        if args.profiler_range:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
         e1.record()
         tp.barrier(); torch.cuda.synchronize()
         clocks = sampler.stop()

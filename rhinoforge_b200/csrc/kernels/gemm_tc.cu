@@ -42,6 +42,8 @@ struct GemmTcParams {
   int ar_world, ar_rank;
   void* const* ar_recv; uint32_t* const* ar_flags; uint32_t* ar_state;
   uint64_t ar_half_bytes;
+  int ar_two_shot;    // large-M path: 16-bit reduce-scatter to the tile's owner, then broadcast
+  int ar_flag2_base;  // first flag of the "result has landed" range
 };
 
 struct alignas(8) GemmSmemCtl {
@@ -329,7 +331,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const float vu = DUAL ? __uint_as_float(ru[j]) : 0.f;
         v[j] = (tok < M && n < N) ? finish(tok, n, vg, vu) : 0.f;
       }
-      if (p.ar_world > 1) {
+      if (p.ar_world > 1 && p.ar_two_shot) {
+        // reduce-scatter leg: the 16-bit partial of this tile goes to the tile's owner only
+        if (!SWAP && a_idx < M) {
+          const int owner = tile_id % p.ar_world;
+          T* pb = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(p.ar_recv[owner]) + slot_off) +
+                  ((size_t)p.ar_rank * M + a_idx) * N + b0 + c;
+          if (b0 + c + 16 <= N && (N & 7) == 0) {
+            float lo[8], hi[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
+            store8(pb, lo);
+            store8(pb + 8, hi);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (b0 + c + j < N) pb[j] = Num<T>::from_f(v[j]);
+          }
+        }
+      } else if (p.ar_world > 1) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int tok = SWAP ? (b0 + c + j) : a_idx;
@@ -379,7 +399,98 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   }
 
-  if (p.ar_world > 1) {
+  if (p.ar_world > 1 && p.ar_two_shot) {
+    // Two-shot all-reduce for large M.  Leg 1 (above): every rank stored its 16-bit partial of
+    // this tile in the owner's buffer.  The owner waits for all ranks, sums in rank order in
+    // fp32, adds the residual and stores the finished tile into every rank's result region
+    // (leg 2); every rank then copies the tile into its own output.
+    const int owner = tile_id % p.ar_world;
+    const uint32_t want = call + 1u;
+    const size_t fbase = ((size_t)tile_id * 8) * p.ar_world;
+    const size_t f2 = (size_t)p.ar_flag2_base + tile_id;
+    const size_t result_off = slot_off + (uint64_t)p.ar_world * M * N * sizeof(T);
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0 && !aborted) st_release_sys(p.ar_flags[owner] + fbase + p.ar_rank, want);
+    if (p.ar_rank == owner) {
+      if (tid < p.ar_world && !aborted) {
+        if (!wait_flag_ge_sys(p.ar_flags[p.ar_rank] + fbase + tid, want)) {
+          report_status(p.status, kStatusPeerTimeout, kTagGemmAr, tid);
+          ctl->abort_flag = 1;
+        }
+      }
+      aborted = __syncthreads_or(*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag) != 0);
+      if (!aborted && !SWAP && a_idx < M) {
+        const T* part = reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(p.ar_recv[p.ar_rank]) + slot_off);
+        for (int c = 0; c < ncols; c += 8) {
+          const int n0 = b0 + c;
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          const bool vec = (n0 + 8 <= N) && ((N & 7) == 0) && (!resid || (p.ldr & 7) == 0);
+          for (int r = 0; r < p.ar_world; ++r) {
+            const T* src = part + ((size_t)r * M + a_idx) * N + n0;
+            if (vec) {
+              const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(src));
+              const typename Num<T>::T2* h = reinterpret_cast<const typename Num<T>::T2*>(&raw);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = Num<T>::to_f2(h[j]);
+                acc[2 * j] += f.x;
+                acc[2 * j + 1] += f.y;
+              }
+            } else {
+              for (int j = 0; j < 8; ++j)
+                if (n0 + j < N) acc[j] += Num<T>::to_f(src[j]);
+            }
+          }
+          if (resid) {
+            for (int j = 0; j < 8; ++j)
+              if (n0 + j < N) acc[j] += Num<T>::to_f(resid[(size_t)a_idx * p.ldr + n0 + j]);
+          }
+          for (int dst = 0; dst < p.ar_world; ++dst) {
+            T* rp = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(p.ar_recv[dst]) + result_off) +
+                    (size_t)a_idx * N + n0;
+            if (vec) store8(rp, acc);
+            else
+              for (int j = 0; j < 8; ++j)
+                if (n0 + j < N) rp[j] = Num<T>::from_f(acc[j]);
+          }
+        }
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (tid < p.ar_world && !aborted) st_release_sys(p.ar_flags[tid] + f2, want);
+    }
+    if (tid == 0 && !aborted) {
+      if (!wait_flag_ge_sys(p.ar_flags[p.ar_rank] + f2, want)) {
+        report_status(p.status, kStatusPeerTimeout, kTagGemmAr, 100 + owner);
+        ctl->abort_flag = 1;
+      }
+    }
+    aborted = __syncthreads_or(*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag) != 0);
+    if (!aborted && !SWAP && a_idx < M) {
+      const T* res = reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(p.ar_recv[p.ar_rank]) + result_off) +
+                     (size_t)a_idx * N;
+      for (int c = 0; c < ncols; c += 8) {
+        const int n0 = b0 + c;
+        if (n0 + 8 <= N && (N & 7) == 0 && (p.ldo & 7) == 0) {
+          *reinterpret_cast<uint4*>(out + (size_t)a_idx * p.ldo + n0) = __ldcg(reinterpret_cast<const uint4*>(res + n0));
+        } else {
+          for (int j = 0; j < 8; ++j)
+            if (n0 + j < N) out[(size_t)a_idx * p.ldo + n0 + j] = res[n0 + j];
+        }
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
+      const uint32_t done = atomicAdd(p.ar_state + 1, 1u);
+      if (done == total - 1u) {
+        p.ar_state[1] = 0u;
+        __threadfence();
+        p.ar_state[0] = call + 1u;
+      }
+    }
+  } else if (p.ar_world > 1) {
     // Publish this CTA's share of the tile to every rank, wait (bounded) for
     // every rank's share, then reduce in rank order and add the residual.
     // Flags are per (tile, cluster rank, source rank) and carry the call number.
@@ -484,8 +595,10 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   const int a_tiles = (swap && dual) ? 2 : 1, b_tiles = (!swap && dual) ? 2 : 1;
   const int stage_bytes = a_tiles * kATileBytes + b_tiles * pl->bn * kBK * 2;
   const int ctl_bytes = (int)sizeof(GemmSmemCtl) + 1024 /*alignment slack*/ + 64;
+  // Two CTAs per SM whenever two stages fit in half the shared memory: bytes in flight per SM are
+  // what hides HBM latency, and a second resident CTA keeps a 2x148-CTA grid in a single wave.
   int stages = (110 * 1024 - ctl_bytes) / stage_bytes;
-  if (stages < 3) stages = (224 * 1024 - ctl_bytes) / stage_bytes;
+  if (stages < 2 || tiles * splits <= sm_count()) stages = (224 * 1024 - ctl_bytes) / stage_bytes;
   stages = std::min(stages, kMaxStages);
   stages = std::min(stages, std::max(2, ceil_div(pl->k_blocks, splits)));
   if (stages < 2) return fail(RF_ERR_UNSUPPORTED, "GEMM tile does not fit in shared memory");
@@ -536,6 +649,8 @@ static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream)
   p.ar_world = g->ar_world; p.ar_rank = g->ar_rank;
   p.ar_recv = g->ar_recv; p.ar_flags = g->ar_flags; p.ar_state = g->ar_state;
   p.ar_half_bytes = g->ar_recv_bytes;
+  p.ar_two_shot = (g->ar_world > 1 && !SWAP && g->M > 256) ? 1 : 0;
+  p.ar_flag2_base = g->ar_flag_count / 2;
   RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.grid_x, pl.grid_y, pl.splits), dim3(128), pl.smem_bytes, stream, pl.splits,
                                tmA, tmB, p));
   ::rf::count_launch();
@@ -554,8 +669,10 @@ static int check_gemm(const RfGemm* g) {
   if (g->ar_world > 1) {
     RF_REQUIRE(g->ar_world <= 8 && g->ar_rank >= 0 && g->ar_rank < g->ar_world, "bad ar rank/world");
     RF_REQUIRE(g->ar_recv && g->ar_flags && g->ar_state, "fused all-reduce needs recv/flags/state");
-    RF_REQUIRE((uint64_t)g->ar_world * g->M * g->N * sizeof(float) <= g->ar_recv_bytes,
-               "all-reduce receive buffer too small for %dx%d", g->M, g->N);
+    const uint64_t need = (g->M > 256 && g->force_swap != 1) ? (uint64_t)(g->ar_world + 1) * g->M * g->N * 2
+                                     : (uint64_t)g->ar_world * g->M * g->N * sizeof(float);
+    RF_REQUIRE(need <= g->ar_recv_bytes, "all-reduce receive buffer too small for %dx%d: need %llu B, have %llu B",
+               g->M, g->N, (unsigned long long)need, (unsigned long long)g->ar_recv_bytes);
   }
   return RF_OK;
 }
@@ -584,7 +701,7 @@ extern "C" int rf_gemm(const RfGemm* g, rf_stream_t stream_) {
   rc = plan_gemm(g, &pl);
   if (rc) return rc;
   if (g->ar_world > 1)
-    RF_REQUIRE(pl.grid_x * pl.grid_y * 8 * g->ar_world <= g->ar_flag_count,
+    RF_REQUIRE(pl.grid_x * pl.grid_y * 8 * g->ar_world <= g->ar_flag_count / 2,
                "all-reduce needs %d flags, have %d", pl.grid_x * pl.grid_y * 8 * g->ar_world,
                g->ar_flag_count);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);

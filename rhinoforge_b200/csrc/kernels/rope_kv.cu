@@ -34,7 +34,8 @@ __global__ void qk_norm_rope_kv_kernel(const RfRopeKv a) {
     }
   }
 
-  for (int h = warp; h < heads; h += nwarps) {
+  // heads are spread over the warps of the block and over blockIdx.y (few tokens: more blocks)
+  for (int h = blockIdx.y * nwarps + warp; h < heads; h += nwarps * gridDim.y) {
     const bool is_q = h < a.Hq, is_k = !is_q && h < a.Hq + a.Hkv;
     T* src = row + (size_t)h * hd;
     if (is_q || is_k) {
@@ -111,13 +112,18 @@ extern "C" int rf_qk_norm_rope_kv(const RfRopeKv* a, rf_stream_t stream) {
   if (a->k_pool) RF_REQUIRE(a->v_pool && a->page_table && a->hd % 8 == 0, "rope_kv: KV pool arguments");
   if (a->tokens == 0) return RF_OK;
   const int heads = a->Hq + 2 * a->Hkv;
-  const int warps = heads < 8 ? heads : 8;
+  int warps = heads < 8 ? heads : 8;
+  int gy = 1;
+  if (a->tokens < 512) {  // decode-sized launches: one head per warp, heads across blockIdx.y
+    warps = heads < 4 ? heads : 4;
+    gy = ceil_div(heads, warps);
+  }
   const size_t smem = (size_t)warps * a->hd * sizeof(float);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (a->dtype == 0)
-    RF_CUDA_CHECK(::rf::launch_k(qk_norm_rope_kv_kernel<__half>, dim3(a->tokens), dim3(warps * 32), smem, s, 1, *a));
+    RF_CUDA_CHECK(::rf::launch_k(qk_norm_rope_kv_kernel<__half>, dim3(a->tokens, gy), dim3(warps * 32), smem, s, 1, *a));
   else
-    RF_CUDA_CHECK(::rf::launch_k(qk_norm_rope_kv_kernel<__nv_bfloat16>, dim3(a->tokens), dim3(warps * 32), smem, s, 1, *a));
+    RF_CUDA_CHECK(::rf::launch_k(qk_norm_rope_kv_kernel<__nv_bfloat16>, dim3(a->tokens, gy), dim3(warps * 32), smem, s, 1, *a));
   RF_CUDA_CHECK(cudaGetLastError());
   ::rf::count_launch();
   return RF_OK;

@@ -129,8 +129,9 @@ class DecoderEngine:
         self.status = self.arena[off:off + 32].view(torch.int32)
         self.comm: Optional[CommBuffers] = None
         if self.tp.enabled:
-            rows = self.max_tokens
-            self.comm = CommBuffers(self.tp, W * rows * H * 4)
+            # one-shot fp32 partials for <= 256 rows, two-shot 16-bit partials + result region above
+            need = max(W * min(self.max_tokens, 256) * H * 4, (W + 1) * self.max_tokens * H * 2)
+            self.comm = CommBuffers(self.tp, need)
             cc = self.comm.stack_comm()
             N.check(lib.rf_stack_set_comm(self.handle, C.byref(cc)), "rf_stack_set_comm")
 

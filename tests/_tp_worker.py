@@ -21,11 +21,12 @@ def main() -> int:
     report = {"rank": R, "world": W, "cases": []}
     ok = True
     # ---- 1. fused row-parallel GEMM + all-reduce + residual against an fp32 reference
-    comm = CommBuffers(tp, W * 320 * 1024 * 4)
+    comm = CommBuffers(tp, max(W * 320 * 1024 * 4, (W + 1) * 700 * 1024 * 2))
     status = torch.zeros(8, dtype=torch.int32, device=dev)
     g = torch.Generator(device=dev).manual_seed(123)
     for (M, Nn, Kd, splits, swap) in [(1, 512, 1024, 0, -1), (7, 384, 2048, 4, 1), (64, 1024, 1024, 0, -1),
-                                      (300, 640, 512, 1, 0), (33, 256, 4096, 8, 1), (64, 1024, 1024, 2, 1)]:
+                                      (300, 640, 512, 1, 0), (33, 256, 4096, 8, 1), (64, 1024, 1024, 2, 1),
+                                      (700, 1000, 1024, 0, -1), (513, 384, 2048, 0, -1)]:
         x = (torch.randn(M, Kd, device=dev, generator=g) * 0.5).half()
         w = (torch.randn(Nn, Kd, device=dev, generator=g) * 0.05).half()
         r = torch.randn(M, Nn, device=dev, generator=g).half()
