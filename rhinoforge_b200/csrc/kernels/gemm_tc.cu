@@ -49,15 +49,52 @@ struct GemmTcParams {
 struct alignas(8) GemmSmemCtl {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
+  uint64_t ready[kMaxStages];  // W8A16: the converter warps have written the 16-bit weight tile
   uint64_t accum;
   uint32_t tmem_base;
   int32_t abort_flag;
 };
 
-template <typename T, bool SWAP, bool DUAL>
-__global__ void __launch_bounds__(128)
+// Eight int8 values (two 32-bit words) -> eight 16-bit floats, exactly.
+// fp16: byte b = x + 128 is dropped into the mantissa of 1024.0 (0x6400 | b = 1024 + b), then 1152 is
+// subtracted -- two integer permutes and one half2 subtract per four values, no int->float convert.
+template <typename T> __device__ __forceinline__ uint4 widen_i8x8(uint2 q);
+template <> __device__ __forceinline__ uint4 widen_i8x8<__half>(uint2 q) {
+  const uint32_t bias = 0x64806480u;  // half2(1152, 1152)
+  uint4 r;
+  uint32_t x = q.x ^ 0x80808080u;
+  uint32_t lo = __byte_perm(x, 0x64646464u, 0x5140), hi = __byte_perm(x, 0x64646464u, 0x5342);
+  __half2 a = __hsub2(*reinterpret_cast<__half2*>(&lo), *reinterpret_cast<const __half2*>(&bias));
+  __half2 b = __hsub2(*reinterpret_cast<__half2*>(&hi), *reinterpret_cast<const __half2*>(&bias));
+  r.x = *reinterpret_cast<uint32_t*>(&a);
+  r.y = *reinterpret_cast<uint32_t*>(&b);
+  x = q.y ^ 0x80808080u;
+  lo = __byte_perm(x, 0x64646464u, 0x5140);
+  hi = __byte_perm(x, 0x64646464u, 0x5342);
+  a = __hsub2(*reinterpret_cast<__half2*>(&lo), *reinterpret_cast<const __half2*>(&bias));
+  b = __hsub2(*reinterpret_cast<__half2*>(&hi), *reinterpret_cast<const __half2*>(&bias));
+  r.z = *reinterpret_cast<uint32_t*>(&a);
+  r.w = *reinterpret_cast<uint32_t*>(&b);
+  return r;
+}
+template <> __device__ __forceinline__ uint4 widen_i8x8<__nv_bfloat16>(uint2 q) {
+  const int8_t* b = reinterpret_cast<const int8_t*>(&q);
+  uint4 r;
+  __nv_bfloat162 t;
+  t = __floats2bfloat162_rn((float)b[0], (float)b[1]); r.x = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn((float)b[2], (float)b[3]); r.y = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn((float)b[4], (float)b[5]); r.z = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn((float)b[6], (float)b[7]); r.w = *reinterpret_cast<uint32_t*>(&t);
+  return r;
+}
+
+// W8 = int8 weights (W8A16): TMA brings the int8 tile into a staging area of the stage, four extra
+// converter warps widen it into the 128-byte-swizzled 16-bit tile the MMA reads, and the
+// per-output-channel scale is applied in the epilogue: (X . Q^T) * s.
+template <typename T, bool SWAP, bool DUAL, bool W8>
+__global__ void __launch_bounds__(W8 ? 256 : 128)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const GemmTcParams p) {
+               const __grid_constant__ CUtensorMap tmW, const GemmTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -68,7 +105,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   constexpr int kATiles = (SWAP && DUAL) ? 2 : 1;
   constexpr int kBTiles = (!SWAP && DUAL) ? 2 : 1;
   const int b_tile_bytes = bn * kBK * 2;
-  const int stage_bytes = kATiles * kATileBytes + kBTiles * b_tile_bytes;
+  constexpr int kWTiles = DUAL ? 2 : 1;                    // weight tiles per stage
+  const int w_rows = SWAP ? kBM : bn;                      // rows of one weight tile
+  const int q_tile_bytes = W8 ? w_rows * kBK : 0;          // int8 staging of one weight tile
+  const int half_bytes = kATiles * kATileBytes + kBTiles * b_tile_bytes;   // the 16-bit tiles
+  const int stage_bytes = half_bytes + kWTiles * q_tile_bytes;
+  const int act_bytes = SWAP ? b_tile_bytes : kATileBytes;
   GemmSmemCtl* ctl = reinterpret_cast<GemmSmemCtl*>(smem + p.ctl_offset);
 
   const int a0 = blockIdx.x * kBM;
@@ -82,12 +124,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&ctl->full[s], 1);
       mbar_init(&ctl->empty[s], 1);
+      mbar_init(&ctl->ready[s], 4);
     }
     mbar_init(&ctl->accum, 1);
     ctl->abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (W8) tma_prefetch_desc(&tmW);
   }
   if (warp == 1) {
     tmem_alloc(&ctl->tmem_base, (uint32_t)p.tmem_cols);
@@ -105,13 +149,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   // ------------------------------------------------------- TMA producer ----
   if (warp == 0 && lane_id() == 0) {
-    const uint32_t tx = (uint32_t)stage_bytes;
+    const uint32_t tx = W8 ? (uint32_t)(act_bytes + kWTiles * q_tile_bytes) : (uint32_t)stage_bytes;
     int issued = 0;
     bool ok = true;
     auto load_weights = [&](int i, int s) {
       uint8_t* st = smem + (size_t)s * stage_bytes;
       const int kc = (kb0 + i) * kBK;
-      if (SWAP) {
+      if (W8) {
+        const int r0 = SWAP ? a0 : b0;
+        tma_load_2d(st + half_bytes, &tmW, &ctl->full[s], kc, r0);
+        if (kWTiles == 2) tma_load_2d(st + half_bytes + q_tile_bytes, &tmW, &ctl->full[s], kc, p.dual_offset + r0);
+      } else if (SWAP) {
         tma_load_2d(st, &tmA, &ctl->full[s], kc, a0);
         if (kATiles == 2) tma_load_2d(st + kATileBytes, &tmA, &ctl->full[s], kc, p.dual_offset + a0);
       } else {
@@ -159,6 +207,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     pdl_wait();
   }
+  // ------------------------------------------------- W8A16 converter warps ----
+  if (W8 && warp >= 4) {
+    const int ct = tid - 128;
+    for (int i = 0; i < kb_count; ++i) {
+      const int s = i % p.stages;
+      const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
+      if (!mbar_wait(&ctl->full[s], ph)) {
+        report_status(p.status, kStatusMmaTimeout, kTagW8A16, i);
+        ctl->abort_flag = 1;
+        break;
+      }
+      uint8_t* st = smem + (size_t)s * stage_bytes;
+#pragma unroll
+      for (int wt = 0; wt < kWTiles; ++wt) {
+        const uint8_t* src = st + half_bytes + wt * q_tile_bytes;
+        uint8_t* dst = SWAP ? st + wt * kATileBytes : st + kATiles * kATileBytes + wt * b_tile_bytes;
+        for (int row = ct; row < w_rows; row += 128) {
+          const uint4* q4 = reinterpret_cast<const uint4*>(src + row * kBK);
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            const uint4 q = q4[h];
+            const int c0 = 2 * h, c1 = 2 * h + 1;
+            *reinterpret_cast<uint4*>(dst + row * 128 + ((c0 ^ (row & 7)) << 4)) = widen_i8x8<T>(make_uint2(q.x, q.y));
+            *reinterpret_cast<uint4*>(dst + row * 128 + ((c1 ^ (row & 7)) << 4)) = widen_i8x8<T>(make_uint2(q.z, q.w));
+          }
+        }
+      }
+      fence_proxy_async();   // generic-proxy writes -> visible to the tensor core's async-proxy reads
+      __syncwarp();
+      if (lane_id() == 0) mbar_arrive(&ctl->ready[s]);
+    }
+  }
   // --------------------------------------------------------- MMA issuer ----
   if (warp == 1 && lane_id() == 0) {
     const uint32_t idesc = umma_idesc_f16(kBM, bn, Num<T>::kFmt);
@@ -168,6 +248,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
       if (!mbar_wait(&ctl->full[s], ph)) {
         report_status(p.status, kStatusMmaTimeout, kTagGemmTc, i);
+        ok = false;
+        break;
+      }
+      if (W8 && !mbar_wait(&ctl->ready[s], ph)) {
+        report_status(p.status, kStatusMmaTimeout, kTagW8A16, 1000 + i);
         ok = false;
         break;
       }
@@ -207,8 +292,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   tc_fence_after_sync();
   __syncwarp();
 
-  const uint32_t trow = tmem_base + ((uint32_t)(warp * 32) << 16);
-  const int a_idx = a0 + tid;
+  // a warp reads the TMEM lanes of its own quarter (warp % 4); converter warps alias warps 0-3
+  const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+  const bool epi = tid < kBM;                              // converter warps only keep the barriers company
+  const int a_idx = epi ? a0 + tid : 0x3fffffff;
   const int M = p.M, N = p.N;
   const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
   constexpr int kAcc = DUAL ? 2 : 1;
@@ -262,10 +349,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tmem_ld16(trow + c, rg);
         if (DUAL) tmem_ld16(trow + bn + c, ru);
         tmem_ld_wait();
+        if (epi) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          part[(c + j) * kBM + tid] = __uint_as_float(rg[j]);
-          if (DUAL) part[(bn + c + j) * kBM + tid] = __uint_as_float(ru[j]);
+          for (int j = 0; j < 16; ++j) {
+            part[(c + j) * kBM + tid] = __uint_as_float(rg[j]);
+            if (DUAL) part[(bn + c + j) * kBM + tid] = __uint_as_float(ru[j]);
+          }
         }
       }
     }
@@ -285,7 +374,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int s = 0; s < 8; ++s) {
             pg[q][s] = 0.f;
             pu[q][s] = 0.f;
-            if (s < p.splits && c < ncols) {
+            if (s < p.splits && c < ncols && epi) {
               pg[q][s] = ld_dsmem_f32(peer_part[s] + (uint32_t)(c * kBM + tid) * 4u);
               if (DUAL) pu[q][s] = ld_dsmem_f32(peer_part[s] + (uint32_t)((bn + c) * kBM + tid) * 4u);
             }
@@ -586,6 +675,8 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
       if (splits < 1) splits = 1;
     }
   }
+  // the two-shot all-reduce epilogue (large M, tensor parallel) works on whole tiles: no split-K there
+  if (g->ar_world > 1 && !swap && g->M > 256) splits = 1;
   if (splits > 8) splits = 8;  // portable cluster size
   if (splits > pl->k_blocks) splits = pl->k_blocks;
   pl->splits = splits;
@@ -593,7 +684,8 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   pl->sem_count = 0;
 
   const int a_tiles = (swap && dual) ? 2 : 1, b_tiles = (!swap && dual) ? 2 : 1;
-  const int stage_bytes = a_tiles * kATileBytes + b_tiles * pl->bn * kBK * 2;
+  int stage_bytes = a_tiles * kATileBytes + b_tiles * pl->bn * kBK * 2;
+  if (g->w_int8) stage_bytes += (dual ? 2 : 1) * (swap ? kBM : pl->bn) * kBK;   // int8 staging tiles
   const int ctl_bytes = (int)sizeof(GemmSmemCtl) + 1024 /*alignment slack*/ + 64;
   // Two CTAs per SM whenever two stages fit in half the shared memory: bytes in flight per SM are
   // what hides HBM latency, and a second resident CTA keeps a 2x148-CTA grid in a single wave.
@@ -615,28 +707,38 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   return RF_OK;
 }
 
-template <typename T, bool SWAP, bool DUAL>
+template <typename T, bool SWAP, bool DUAL, bool W8>
 static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream) {
   static bool attr_set = false;
-  auto kfn = gemm_tc_kernel<T, SWAP, DUAL>;
+  auto kfn = gemm_tc_kernel<T, SWAP, DUAL, W8>;
   if (!attr_set) {
     RF_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
   const bool dual = DUAL;
   const uint64_t w_rows = (uint64_t)(dual ? g->dual_offset + g->N : g->N);
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmW;
   int rc;
-  if (SWAP) {
+  if (W8) {
+    // int8 weights: their own byte-typed, unswizzled map; the 16-bit map of that operand is unused
+    rc = make_tmap_2d(&tmW, g->w, 0, 1, g->K, w_rows, g->ldw, kBK, SWAP ? kBM : pl.bn, false);
+    if (rc) return rc;
+    if (SWAP) rc = make_tmap_2d(&tmB, g->x, g->dtype, 2, g->K, g->M, g->ldx, kBK, pl.bn, true);
+    else rc = make_tmap_2d(&tmA, g->x, g->dtype, 2, g->K, g->M, g->ldx, kBK, kBM, true);
+    if (rc) return rc;
+    if (SWAP) tmA = tmB; else tmB = tmA;
+  } else if (SWAP) {
     rc = make_tmap_2d(&tmA, g->w, g->dtype, 2, g->K, w_rows, g->ldw, kBK, kBM, true);
     if (rc) return rc;
     rc = make_tmap_2d(&tmB, g->x, g->dtype, 2, g->K, g->M, g->ldx, kBK, pl.bn, true);
     if (rc) return rc;
+    tmW = tmA;
   } else {
     rc = make_tmap_2d(&tmA, g->x, g->dtype, 2, g->K, g->M, g->ldx, kBK, kBM, true);
     if (rc) return rc;
     rc = make_tmap_2d(&tmB, g->w, g->dtype, 2, g->K, w_rows, g->ldw, kBK, pl.bn, true);
     if (rc) return rc;
+    tmW = tmA;
   }
   GemmTcParams p;
   p.out = g->out; p.ldo = g->ldo;
@@ -651,8 +753,8 @@ static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream)
   p.ar_half_bytes = g->ar_recv_bytes;
   p.ar_two_shot = (g->ar_world > 1 && !SWAP && g->M > 256) ? 1 : 0;
   p.ar_flag2_base = g->ar_flag_count / 2;
-  RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.grid_x, pl.grid_y, pl.splits), dim3(128), pl.smem_bytes, stream, pl.splits,
-                               tmA, tmB, p));
+  RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.grid_x, pl.grid_y, pl.splits), dim3(W8 ? 256 : 128), pl.smem_bytes, stream,
+                               pl.splits, tmA, tmB, tmW, p));
   ::rf::count_launch();
   return RF_OK;
 }
@@ -662,7 +764,8 @@ static int check_gemm(const RfGemm* g) {
   RF_REQUIRE(g->x && g->w && g->out, "GEMM needs x, w and out");
   RF_REQUIRE(g->M > 0 && g->N > 0 && g->K > 0, "GEMM shape %dx%dx%d", g->M, g->N, g->K);
   RF_REQUIRE(g->K % 8 == 0, "GEMM K=%d must be a multiple of 8 (16-byte rows)", g->K);
-  RF_REQUIRE(g->ldx % 8 == 0 && g->ldw % 8 == 0, "GEMM row pitches must be multiples of 8 elements");
+  RF_REQUIRE(g->ldx % 8 == 0 && g->ldw % (g->w_int8 ? 16 : 8) == 0, "GEMM row pitches must be multiples of 16 bytes");
+  if (g->w_int8) RF_REQUIRE(g->scale != nullptr && g->K % 16 == 0, "int8 weights need a scale vector and K %% 16 == 0");
   RF_REQUIRE(g->dtype == 0 || g->dtype == 1, "GEMM dtype must be fp16 or bf16");
   const bool dual_act = g->act == kActSiluMul || g->act == kActGeluTanhMul;
   RF_REQUIRE(dual_act == (g->dual_offset > 0), "dual_offset and a *_mul activation go together");
@@ -692,29 +795,44 @@ extern "C" int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem
   return RF_OK;
 }
 
-extern "C" int rf_gemm(const RfGemm* g, rf_stream_t stream_) {
-  RF_SKIP_IF_REPLAYING();
+static int run_gemm(const RfGemm* g, cudaStream_t stream, bool w8) {
   int rc = check_gemm(g);
   if (rc) return rc;
-  RF_REQUIRE(!g->w_int8, "rf_gemm takes 16-bit weights; use rf_gemm_w8a16 for int8");
   GemmPlan pl;
   rc = plan_gemm(g, &pl);
   if (rc) return rc;
   if (g->ar_world > 1)
     RF_REQUIRE(pl.grid_x * pl.grid_y * 8 * g->ar_world <= g->ar_flag_count / 2,
-               "all-reduce needs %d flags, have %d", pl.grid_x * pl.grid_y * 8 * g->ar_world,
-               g->ar_flag_count);
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+               "all-reduce needs %d flags, have %d", pl.grid_x * pl.grid_y * 8 * g->ar_world, g->ar_flag_count / 2);
   const bool dual = g->dual_offset > 0;
-#define RF_GEMM_DISPATCH(T)                                                       \
-  if (pl.swap) {                                                                  \
-    return dual ? launch_gemm<T, true, true>(g, pl, stream)                       \
-                : launch_gemm<T, true, false>(g, pl, stream);                     \
-  } else {                                                                        \
-    return dual ? launch_gemm<T, false, true>(g, pl, stream)                      \
-                : launch_gemm<T, false, false>(g, pl, stream);                    \
+#define RF_GEMM_DISPATCH(T, W8)                                                          \
+  if (pl.swap) {                                                                         \
+    return dual ? launch_gemm<T, true, true, W8>(g, pl, stream)                          \
+                : launch_gemm<T, true, false, W8>(g, pl, stream);                        \
+  } else {                                                                               \
+    return dual ? launch_gemm<T, false, true, W8>(g, pl, stream)                         \
+                : launch_gemm<T, false, false, W8>(g, pl, stream);                       \
   }
-  if (g->dtype == 0) { RF_GEMM_DISPATCH(__half) }
-  RF_GEMM_DISPATCH(__nv_bfloat16)
+  if (w8) {
+    if (g->dtype == 0) { RF_GEMM_DISPATCH(__half, true) }
+    RF_GEMM_DISPATCH(__nv_bfloat16, true)
+  }
+  if (g->dtype == 0) { RF_GEMM_DISPATCH(__half, false) }
+  RF_GEMM_DISPATCH(__nv_bfloat16, false)
 #undef RF_GEMM_DISPATCH
+}
+
+extern "C" int rf_gemm(const RfGemm* g, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(g && !g->w_int8, "rf_gemm takes 16-bit weights; use rf_gemm_w8a16 for int8");
+  return run_gemm(g, static_cast<cudaStream_t>(stream), false);
+}
+
+// int8 weights [N,K] with a per-output-channel scale: widened to the activation dtype inside the
+// mainloop, (X . Q^T) * scale in the epilogue.  Same epilogue options as rf_gemm (bias, residual,
+// GLU, cluster split-K, fused all-reduce).
+extern "C" int rf_gemm_w8a16(const RfGemm* g, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(g && g->w_int8 && g->scale, "rf_gemm_w8a16 takes int8 weights and a scale vector");
+  return run_gemm(g, static_cast<cudaStream_t>(stream), true);
 }

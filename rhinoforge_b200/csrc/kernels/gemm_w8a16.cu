@@ -1,11 +1,5 @@
-// W8A16 tensor-core GEMM entry point (int8 per-output-channel weights, 16-bit
-// activations).  Placeholder dispatch: token counts up to 8 run on the
-// CUDA-core GEMV with in-loop dequantisation.
-#include "../common/host_util.h"
-#include "../rf_api.h"
-
-extern "C" int rf_gemm_w8a16(const RfGemm* g, rf_stream_t stream) {
-  RF_SKIP_IF_REPLAYING();
-  if (g && g->M <= 8 && g->ar_world <= 1) return rf_gemv(g, stream);
-  return rf::fail(RF_ERR_UNSUPPORTED, "W8A16 tensor-core GEMM for M=%d is not built yet", g ? g->M : -1);
-}
+// The W8A16 tensor-core path lives in gemm_tc.cu (template parameter W8 of gemm_tc_kernel and
+// the entry point rf_gemm_w8a16): the int8 weight tile is brought in by TMA, widened to the
+// activation dtype by four converter warps into the swizzled MMA tile, and the per-channel scale
+// is applied in the epilogue.  The CUDA-core path for up to 8 tokens is rf_gemv (gemv.cu).
+// Replaces parallel_linear_w8a16_* and llama_gemv_wint8 (src/ops/rpu_linear.cpp:1119-1209,1546-1670).

@@ -317,12 +317,17 @@ class DecoderEngine:
     @torch.no_grad()
     def extend(self, tokens: Sequence[torch.Tensor], *, return_logits: bool = False,
                inputs_embeds: Optional[Sequence[torch.Tensor]] = None,
-               positions3: Optional[Sequence[torch.Tensor]] = None):
+               positions3: Optional[Sequence[torch.Tensor]] = None,
+               deepstack: Optional[Sequence[Optional[tuple]]] = None):
         """Append ``tokens[s]`` (1-D int tensors, host or device) to sequence ``s`` at its current
         length and return the greedy next token of every sequence ([B] int32 on the device; with
         ``return_logits`` also the last-row logits of this rank's vocab shard).  Long inputs run as
         several packed varlen launches of at most ``max_prefill_tokens`` rows (chunked prefill);
-        the engine is left ready for :meth:`decode`."""
+        the engine is left ready for :meth:`decode`.
+
+        ``inputs_embeds[s]`` ``[L, hidden]`` replaces the embedding lookup (vision rows already spliced
+        in); ``positions3[s]`` ``[3, L]`` are M-RoPE positions; ``deepstack[s] = (rows, feats)`` adds
+        ``feats[l][i]`` to the hidden row ``rows[i]`` of sequence ``s`` after layer ``l`` (DeepStack)."""
         B = len(tokens)
         cache = self.cache
         if B > cache.batch_size:
@@ -353,7 +358,7 @@ class DecoderEngine:
         if chunk:
             items.append(chunk)
         for ch in items:
-            self._prefill_chunk(ch, tokens, lens, starts, first, logits_all, inputs_embeds, positions3)
+            self._prefill_chunk(ch, tokens, lens, starts, first, logits_all, inputs_embeds, positions3, deepstack)
         self.batch = B
         for s, L in enumerate(lens):
             cache.lengths[s] = starts[s] + L
@@ -364,14 +369,16 @@ class DecoderEngine:
             new_len = new_len.pin_memory()
         new_len = new_len.to(self.device, non_blocking=True)
         if positions3 is not None:
-            nxt = torch.stack([p[:, -1].to(self.device) + 1 for p in positions3]).to(torch.int32)
-            self.pos[:B].copy_(nxt)
+            # generation continues one past the largest position on all three axes
+            nxt = torch.stack([p.max().to(self.device) + 1 for p in positions3]).to(torch.int32)
+            self.pos[:B].copy_(nxt[:, None].expand(B, self.pos_stride))
         else:
             self.pos[:B].copy_(new_len[:, None].expand(B, self.pos_stride))
         self.kv_len[:B].copy_(new_len + 1)
         return (first, logits_all) if return_logits else first
 
-    def _prefill_chunk(self, ch, prompts, lens, starts, first, logits_all, inputs_embeds, positions3) -> None:
+    def _prefill_chunk(self, ch, prompts, lens, starts, first, logits_all, inputs_embeds, positions3,
+                       deepstack=None) -> None:
         T = sum(c[2] for c in ch)
         n = len(ch)
         meta = torch.empty((5, max(n, 1)), dtype=torch.int32)
@@ -380,6 +387,7 @@ class DecoderEngine:
         o = 0
         emb_rows = []
         pos3 = []
+        ds_rows, ds_feats = [], None
         for j, (s, off, cnt) in enumerate(ch):
             base = starts[s]
             meta[0, j], meta[1, j], meta[2, j] = o, cnt, base + off + cnt   # q_start, q_len, kv_len
@@ -392,6 +400,16 @@ class DecoderEngine:
                 emb_rows.append(inputs_embeds[s][off:off + cnt])
             if positions3 is not None:
                 pos3.append(positions3[s][:, off:off + cnt].t())
+            if deepstack is not None and deepstack[s] is not None:
+                rows_s, feats_s = deepstack[s]
+                rows_s = rows_s.to("cpu", torch.int64)
+                sel = ((rows_s >= off) & (rows_s < off + cnt)).nonzero().flatten()
+                if sel.numel():
+                    ds_rows.append(rows_s[sel] - off + o)
+                    if ds_feats is None:
+                        ds_feats = [[] for _ in feats_s]
+                    for l, ft in enumerate(feats_s):
+                        ds_feats[l].append(ft.to(self.device, self.dtype)[sel.to(self.device)])
             o += cnt
         meta_d = meta.pin_memory().to(self.device, non_blocking=True)
         tok_d = tokmeta.pin_memory().to(self.device, non_blocking=True)
@@ -421,6 +439,12 @@ class DecoderEngine:
         f.max_q_len = max(c[2] for c in ch)
         f.max_kv_len = max(starts[c[0]] + c[1] + c[2] for c in ch)
         f.page_table, f.pt_stride, f.pool_pages = pt.data_ptr(), pt.stride(0), self.cache.num_pages
+        if ds_rows:
+            ds_rows_d = torch.cat(ds_rows).to(torch.int32).pin_memory().to(self.device, non_blocking=True)
+            ds_layers = [torch.cat(parts).contiguous() for parts in ds_feats]
+            ds_ptrs = torch.tensor([t.data_ptr() for t in ds_layers], dtype=torch.int64)   # host array of device pointers
+            f.deepstack, f.deepstack_rows = ds_ptrs.data_ptr(), ds_rows_d.data_ptr()
+            f.n_deepstack, f.n_deepstack_rows = len(ds_layers), ds_rows_d.numel()
         N.check(N.lib().rf_stack_forward(self.handle, C.byref(f), self._stream()), "rf_stack_forward")
         # sequences whose prompt ends in this chunk get their first token
         done = [(j, s) for j, (s, off, cnt) in enumerate(ch) if off + cnt == lens[s]]

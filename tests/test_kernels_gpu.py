@@ -370,3 +370,61 @@ def test_embedding_scatter_eltwise_cast_argmax():
     ids2, vals = K_.argmax(logits, offset=10, return_vals=True)
     assert torch.equal(ids2.long() - 10, logits.float().argmax(-1))
     _close(vals, logits.float().max(-1).values, dt)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M,N,K,swap,splits", [(16, 384, 1024, -1, 0), (64, 1000, 2048, 1, 4), (9, 256, 512, 1, 1),
+                                               (300, 640, 1024, 0, 1), (1024, 512, 2048, 0, 1), (130, 256, 4096, 1, 2)])
+def test_gemm_w8a16_tensor_core(dt, M, N, K, swap, splits, status):
+    """int8 weights widened in the mainloop, (X . Q^T) * scale in the epilogue."""
+    from rhinoforge_b200.ops import kernels as K_
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    q = torch.randint(-127, 128, (N, K), device="cuda", dtype=torch.int8)
+    sc = (torch.rand(N, device="cuda") * 0.004 + 0.001).to(dt)
+    r = torch.randn(M, N, device="cuda").to(dt)
+    y = K_.gemm(x, q, scale=sc, residual=r, status=status, force_swap=swap, force_splits=splits)
+    ref = (x.float() @ q.float().t()) * sc.float() + r.float()
+    _close(y, ref, dt, scale=max(1.0, ref.abs().max().item()) * (4 if dt == torch.bfloat16 else 1))
+
+
+@pytest.mark.parametrize("M,swap", [(24, 1), (300, 0)])
+def test_gemm_w8a16_dual_glu(M, swap, status):
+    from rhinoforge_b200.ops import kernels as K_
+    dt, N, K = torch.float16, 384, 1024
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    q = torch.randint(-127, 128, (2 * N, K), device="cuda", dtype=torch.int8)
+    sc = (torch.rand(2 * N, device="cuda") * 0.002 + 0.0005).to(dt)
+    y = K_.gemm(x, q, scale=sc, act="silu_mul", dual=True, status=status, force_swap=swap)
+    z = (x.float() @ q.float().t()) * sc.float()
+    _close(y, torch.nn.functional.silu(z[:, :N]) * z[:, N:], dt, scale=2.0)
+
+
+def test_engine_w8a16_matches_dequantised_oracle():
+    """Whole decoder with int8 weights: greedy tokens follow the oracle run on the dequantised weights."""
+    from rhinoforge_b200.models.decoder import TorchDecoder, random_state_dict, tiny_config
+    from rhinoforge_b200.quant._common import dequantize_linear_per_channel, quantize_linear_per_channel
+    from rhinoforge_b200.runtime.engine import DecoderEngine
+    cfg = tiny_config(num_layers=2)
+    sd = random_state_dict(cfg, seed=0, dtype=torch.float16, norm_jitter=0.05)
+    deq = {}
+    for k, v in sd.items():
+        if v.dim() == 2 and "embed" not in k:
+            qq, s = quantize_linear_per_channel(v)
+            deq[k] = dequantize_linear_per_channel(qq, s)
+        else:
+            deq[k] = v
+    deq["lm_head.weight"] = dequantize_linear_per_channel(*quantize_linear_per_channel(sd["model.embed_tokens.weight"]))
+    oracle = TorchDecoder(cfg, deq, dtype=torch.float32, device="cuda")
+    eng = DecoderEngine(cfg, lambda n: sd[n] if n in sd else sd["model.embed_tokens.weight"], dtype=torch.float16,
+                        max_batch=2, max_seq_len=96, quant="w8a16")
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, cfg.vocab_size, (L,), generator=g) for L in (19, 40)]
+    _, logits = eng.prefill(prompts, return_logits=True)
+    for b, p in enumerate(prompts):
+        oracle.reset()
+        ref = oracle.forward(p[None].cuda())[0, -1]
+        torch.testing.assert_close(logits[b].float(), ref.float(), rtol=1e-2, atol=1e-2)
+    toks = eng.generate(prompts, 6)
+    assert toks.shape == (2, 6)
+    eng.check_status()
+    eng.close()
