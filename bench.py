@@ -29,6 +29,9 @@ def parse_args(argv=None):
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "pi05", "qwen3vl"],
+                    help="decode: causal-LM decode throughput (headline); pi05: action-chunk latency; "
+                         "qwen3vl: multimodal prefill + decode")
     ap.add_argument("--model", default="qwen3-8b")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt-len", type=int, default=1024)
@@ -203,12 +206,206 @@ def run(args) -> dict:
     return out if tp.rank == 0 else None
 
 
+def _timed(fn, steps: int, warmup: int):
+    """(per-call device ms list, clocks): CUDA events around every call, clocks sampled meanwhile."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    ms = []
+    for _ in range(steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    return ms, sampler.stop()
+
+
+def run_pi05(args) -> dict:
+    """Pi0.5-architecture action chunk: 3 views of 224x224, 200 prompt tokens, 10 Euler steps, chunk 50x32.
+    A "step" is one full chunk (vision + prefix prefill + denoise loop)."""
+    import ctypes
+    import torch
+    from rhinoforge_b200 import _native as N
+    from rhinoforge_b200.models.pi05 import Pi05Config, Pi05Engine, random_pi05_state_dict
+    if args.gpus != 1:
+        raise SystemExit("the pi05 workload runs on one GPU")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16
+    cfg = Pi05Config()
+    batches = sorted({1, *[int(b) for b in args.sweep.split(",") if b]})
+    t0 = time.time()
+    sd = random_pi05_state_dict(cfg, seed=0, std=0.02, dtype=dtype, device=dev)
+    eng = Pi05Engine(cfg, sd, dtype=dtype, max_batch=max(batches))
+    del sd
+    torch.cuda.synchronize()
+    startup_s = time.time() - t0
+    lib = N.lib()
+    lib.rf_launch_count.restype = ctypes.c_uint64
+    g = torch.Generator().manual_seed(0)
+    res = {}
+    for B in batches:
+        images = torch.rand(B, cfg.num_views, 3, 224, 224, generator=g).mul_(2).sub_(1).pin_memory()
+        imask = torch.ones(B, cfg.num_views, dtype=torch.bool)
+        tokens = torch.randint(0, cfg.vocab_size, (B, cfg.max_lang_tokens), generator=g).pin_memory()
+        tmask = torch.ones(B, cfg.max_lang_tokens, dtype=torch.bool)
+        noise = torch.randn(B, cfg.horizon, cfg.action_dim, generator=g).pin_memory()
+        d_img, d_noise = images.to(dev), noise.to(dev)
+        host_out = torch.empty(B, cfg.horizon, cfg.action_dim, dtype=dtype).pin_memory()
+
+        def device_only():
+            eng.predict(d_img, imask, tokens, tmask, d_noise, num_steps=10)
+
+        def end_to_end():           # inputs from pinned host memory every call, actions read back
+            out = eng.predict(images.to(dev, non_blocking=True), imask, tokens, tmask, noise.to(dev, non_blocking=True),
+                              num_steps=10)
+            host_out.copy_(out, non_blocking=True)
+            torch.cuda.synchronize()
+
+        device_only()               # BUILD
+        c0 = lib.rf_launch_count()
+        device_only()
+        eager_launches = lib.rf_launch_count() - c0       # kernels outside the graph (vision + prefix)
+        ms, clocks = _timed(device_only, args.steps, max(args.warmup, 3))
+        t1 = time.perf_counter()
+        for _ in range(args.steps):
+            end_to_end()
+        e2e_ms = (time.perf_counter() - t1) * 1000.0 / args.steps
+        eng.check_status()
+        # where the time goes: vision tower, prefix (rest of prefill), denoise loop
+        def vision_only():
+            eng.vision(d_img.flatten(0, 1))
+        lens = eng.prefill(d_img, imask, tokens, tmask)
+        v_ms, _ = _timed(vision_only, 5, 2)
+        p_ms, _ = _timed(lambda: eng.prefill(d_img, imask, tokens, tmask), 5, 2)
+        d_ms, _ = _timed(lambda: eng.denoise(lens, d_noise, 10), 5, 2)
+        if args.profiler_range:
+            torch.cuda.profiler.start()
+            eng.predict(d_img, imask, tokens, tmask, d_noise, num_steps=10, use_graph=not args.no_graph)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        parts = {"vision_ms": statistics.median(v_ms), "prefill_ms": statistics.median(p_ms),
+                 "denoise_ms": statistics.median(d_ms)}
+        res[B] = {"batch": B, **parts, "ms_p50": statistics.median(ms), "ms_p90": sorted(ms)[int(0.9 * (len(ms) - 1))],
+                  "chunks_per_s": B * 1000.0 / statistics.median(ms), "e2e_ms": e2e_ms,
+                  "launches_outside_graph": int(eager_launches), "clocks": clocks,
+                  "h2d": images.numel() * 4 + tokens.numel() * 8 + noise.numel() * 4, "d2h": host_out.numel() * 2}
+    eng.close()
+    h = res[1]
+    return {
+        "metric": "pi05_action_chunk_latency_ms", "value": h["ms_p50"], "unit": "ms", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": h["ms_p50"], "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "impl": "ours",
+        "config": {"model": "pi0.5-architecture random-init (std 0.02, seed 0): SigLIP-So400m/14 + Gemma-2B + Gemma-300M expert",
+                   "global_batch": 1, "views": cfg.num_views, "image": "224x224", "seq_len": cfg.max_lang_tokens,
+                   "denoise_steps": 10, "chunk": [cfg.horizon, cfg.action_dim], "parallelism": "tp1",
+                   "graph": "denoise loop in one CUDA graph; vision + prefix eager",
+                   "l2": "inputs larger than L2: ~6.7 GB of weights read per chunk"},
+        "clocks": h["clocks"], "p90_ms": h["ms_p90"],
+        "e2e": {"value": h["e2e_ms"], "unit": "ms", "h2d_bytes_per_step": h["h2d"], "d2h_bytes_per_step": h["d2h"]},
+        "gpu_launches": (h["launches_outside_graph"]) * args.steps,
+        "startup_s": startup_s,
+        "by_batch": {str(b): {k: v for k, v in r.items() if k != "clocks"} for b, r in res.items()},
+    }
+
+
+def run_qwen3vl(args) -> dict:
+    """Qwen3-VL-2B-architecture: one prompt of 2 images (448x448 -> 28x28 patches each) + 256 text tokens;
+    reports multimodal prefill ms (vision tower + text prefill with DeepStack) and greedy decode tokens/s."""
+    import torch
+    from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLConfig
+    from rhinoforge_b200.models.decoder import PROFILES, weight_shapes
+    from rhinoforge_b200.models.qwen3_vl import Qwen3VLEngine
+    if args.gpus != 1:
+        raise SystemExit("the qwen3vl workload runs on one GPU")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16
+    tc = PROFILES["qwen3-vl-2b-text"]
+    hf = Qwen3VLConfig(
+        text_config=dict(hidden_size=tc.hidden_size, intermediate_size=tc.intermediate_size, num_hidden_layers=tc.num_layers,
+                         num_attention_heads=tc.num_heads, num_key_value_heads=tc.num_kv_heads, head_dim=tc.head_dim,
+                         vocab_size=tc.vocab_size, max_position_embeddings=4096, tie_word_embeddings=True,
+                         rope_parameters={"rope_type": "default", "rope_theta": tc.rope_theta,
+                                          "mrope_section": list(tc.mrope_section), "mrope_interleaved": True}),
+        vision_config=dict(depth=24, hidden_size=1024, num_heads=16, intermediate_size=4096, out_hidden_size=tc.hidden_size,
+                           num_position_embeddings=2304, deepstack_visual_indexes=[5, 11, 17]),
+        tie_word_embeddings=True)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    cache = {}
+
+    def get(name: str) -> torch.Tensor:          # random weights drawn on the device by name
+        if name not in cache:
+            cache[name] = shape_of[name]()
+        return cache[name]
+    from transformers.models.qwen3_vl.modeling_qwen3_vl import Qwen3VLForConditionalGeneration
+    with torch.device("meta"):
+        skeleton = Qwen3VLForConditionalGeneration(hf)
+    shape_of = {}
+    for n, p in skeleton.state_dict().items():
+        shp = tuple(p.shape)
+        if p.dim() >= 2:
+            shape_of[n] = (lambda s=shp: (torch.randn(s, generator=gen, device=dev) * 0.02).to(dtype))
+        elif "norm" in n and n.endswith("weight"):
+            shape_of[n] = (lambda s=shp: torch.ones(s, device=dev, dtype=dtype))
+        else:
+            shape_of[n] = (lambda s=shp: torch.zeros(s, device=dev, dtype=dtype))
+    t0 = time.time()
+    eng = Qwen3VLEngine(hf, get, names=set(shape_of), dtype=dtype, max_seq_len=2048, max_patches=2 * 28 * 28,
+                        max_prefill_tokens=2048)
+    cache.clear()
+    torch.cuda.synchronize()
+    startup_s = time.time() - t0
+    grid = torch.tensor([[1, 28, 28], [1, 28, 28]])
+    n_img = 2 * (28 * 28 // 4)
+    g = torch.Generator().manual_seed(0)
+    text = torch.randint(0, 150000, (256,), generator=g)
+    ids = torch.cat((text[:8], torch.full((n_img // 2,), eng.image_token_id), text[8:16],
+                     torch.full((n_img // 2,), eng.image_token_id), text[16:]))
+    px = torch.randn(2 * 28 * 28, 3 * 2 * 16 * 16, generator=g).pin_memory()
+
+    def prefill():
+        eng.prefill(ids, px.to(dev, non_blocking=True), grid)
+    ms, clocks = _timed(prefill, max(3, args.ttft_samples), 3)
+    prefill()
+    eng.text.capture(1)
+    eng.decode(max(args.warmup, 3))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        eng.text.graphs[1].replay()
+    e1.record()
+    torch.cuda.synchronize()
+    dec_ms = e0.elapsed_time(e1) / args.steps
+    eng.text.advance_lengths(args.steps)
+    eng.text.check_status()
+    eng.close()
+    return {
+        "metric": "qwen3vl_decode_tokens_per_s", "value": 1000.0 / dec_ms, "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dec_ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "impl": "ours",
+        "config": {"model": "qwen3-vl-2b-architecture random-init", "global_batch": 1, "images": "2 x 448x448",
+                   "seq_len": int(ids.numel()), "parallelism": "tp1", "l2": "weights (4 GB) exceed L2"},
+        "prefill_ms_p50": statistics.median(ms), "clocks": clocks, "startup_s": startup_s,
+        "e2e": {"value": statistics.median(ms), "unit": "ms (prefill incl. pixel H2D)", "h2d_bytes_per_step": px.numel() * 4,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": args.steps * 300,
+    }
+
+
 def main(argv=None) -> int:
     args = parse_args(argv)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
-    out = run(args)
+    out = {"decode": run, "pi05": run_pi05, "qwen3vl": run_qwen3vl}[args.workload](args)
     if out is not None:
         print(json.dumps(out))
     try:

@@ -65,3 +65,30 @@ def resolve_checkpoint(config: dict) -> str:
 def ok(path, location) -> int:
     print(f"configuration OK: {path} ({location})")
     return 0
+
+
+def require_request(config: dict, *, image: bool = False, fields=()) -> dict:
+    req = config.get("request")
+    if not isinstance(req, dict):
+        raise ValueError("configuration needs a [request] table")
+    if image and not isinstance(req.get("image"), str):
+        raise ValueError("[request].image must be a path string")
+    for name, kind in fields:
+        if name in req and (not isinstance(req[name], kind) or isinstance(req[name], bool) and kind is int):
+            raise ValueError(f"[request].{name} must be of type {kind.__name__}")
+    return req
+
+
+def load_image(path: str):
+    """RGB float tensor ``[3, H, W]`` in [0, 1] from an image file (PIL) or a ``.pt``/``.npy`` array."""
+    import torch
+    p = Path(path).expanduser()
+    if p.suffix == ".pt":
+        return torch.load(p).float()
+    if p.suffix == ".npy":
+        import numpy as np
+        return torch.from_numpy(np.load(p)).float()
+    from PIL import Image
+    import numpy as np
+    arr = np.asarray(Image.open(p).convert("RGB"), dtype="float32") / 255.0
+    return torch.from_numpy(arr).permute(2, 0, 1)

@@ -39,7 +39,7 @@ class RfGemm(C.Structure):
         ("ar_world", C.c_int32), ("ar_rank", C.c_int32),
         ("ar_recv", C.c_void_p), ("ar_flags", C.c_void_p), ("ar_state", C.c_void_p),
         ("ar_recv_bytes", C.c_uint64), ("ar_flag_count", C.c_int32),
-        ("force_splits", C.c_int32), ("force_swap", C.c_int32), ("force_bn", C.c_int32),
+        ("force_splits", C.c_int32), ("force_swap", C.c_int32), ("force_bn", C.c_int32), ("w_packed", C.c_int32),
     ]
 
 
@@ -86,14 +86,16 @@ class RfStackConfig(C.Structure):
                [(n, C.c_int32) for n in ("qk_norm", "rope_before_norm", "gated_residual", "sandwich_norm", "paged_kv",
                                          "causal", "window")] + [("attn_scale", C.c_float)] + \
                [(n, C.c_int32) for n in ("true_hd", "dtype", "max_tokens", "max_seqs", "vocab_local", "vocab_offset",
-                                         "tp_world", "tp_rank", "weights_int8", "decode_gemv_max_m")]
+                                         "tp_world", "tp_rank", "weights_int8", "decode_gemv_max_m", "attn_gate",
+                                         "gdn_Hk", "gdn_Hv", "gdn_Dk", "gdn_Dv", "gdn_conv_k", "weights_packed")]
 
 
 class RfLayerWeights(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
         "norm1_w", "norm1_b", "wqkv", "bqkv", "sqkv", "q_norm_w", "k_norm_w", "wo", "bo", "so", "norm2_w", "norm2_b",
         "w_up", "b_up", "s_up", "w_down", "b_down", "s_down", "post_attn_norm_w", "post_mlp_norm_w", "k_pool",
-        "v_pool")]
+        "v_pool")] + [("mixer", C.c_int64)] + [(n, C.c_void_p) for n in (
+        "gdn_conv_w", "gdn_A_log", "gdn_dt_bias", "gdn_norm_w", "gdn_conv_state", "gdn_rec_state")]
 
 
 class RfStackComm(C.Structure):
@@ -118,7 +120,21 @@ class RfStackForward(C.Structure):
         ("deepstack", C.c_void_p), ("deepstack_rows", C.c_void_p), ("n_deepstack", C.c_int32),
         ("n_deepstack_rows", C.c_int32),
         ("taps", C.c_void_p), ("tap_layers", C.c_void_p), ("n_taps", C.c_int32),
+        ("state_slot", C.c_void_p), ("state_fresh", C.c_void_p),
     ]
+
+
+class RfConv1d(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("ldx", C.c_int64), ("y", C.c_void_p), ("ldy", C.c_int64), ("w", C.c_void_p),
+                ("state", C.c_void_p), ("q_start", C.c_void_p), ("q_len", C.c_void_p), ("slot", C.c_void_p)] + \
+               [(n, C.c_int32) for n in ("num_seqs", "max_q_len", "C", "K", "silu", "dtype")]
+
+
+class RfGdn(C.Structure):
+    _fields_ = [("qkv", C.c_void_p), ("ld", C.c_int64), ("b", C.c_void_p), ("a", C.c_void_p), ("ld_ba", C.c_int64),
+                ("out", C.c_void_p), ("ldo", C.c_int64), ("state", C.c_void_p), ("A_log", C.c_void_p),
+                ("dt_bias", C.c_void_p), ("q_start", C.c_void_p), ("q_len", C.c_void_p), ("slot", C.c_void_p),
+                ("fresh", C.c_void_p)] + [(n, C.c_int32) for n in ("num_seqs", "Hk", "Hv", "Dk", "Dv", "dtype")]
 
 
 def available() -> bool:
@@ -149,6 +165,7 @@ def lib() -> C.CDLL:
         l.rf_stack_arena_bytes.restype = C.c_uint64
         l.rf_stack_status_ptr.restype = C.c_void_p
         l.rf_kvpool_create.restype = C.c_int64
+        l.rf_pack_weight_bytes.restype = C.c_uint64
         for fn in ("rf_stack_destroy", "rf_stack_set_layer", "rf_stack_set_head", "rf_stack_set_comm",
                    "rf_stack_arena_bytes", "rf_stack_bind_arena", "rf_stack_status_ptr", "rf_stack_forward",
                    "rf_stack_head", "rf_stack_final_norm", "rf_kvpool_destroy", "rf_kvpool_reserve",

@@ -1,0 +1,386 @@
+// Gated-DeltaNet (linear attention) kernels for the Qwen3.5 hybrid decoder:
+//   * causal depthwise conv1d (kernel 4) with a carried per-sequence state + SiLU,
+//   * the gated delta-rule recurrence over a [Dk, Dv] fp32 state per value head
+//     (one launch covers decode -- one step from the stored state -- and prefill -- n
+//     steps with the state held in registers, written back once),
+//   * RMSNorm over Dv gated by silu(z),
+//   * sigmoid output gate of the full-attention layers,
+//   * last-dim cumulative sum and (I - M)^-1 of strictly-lower-triangular blocks, the two
+//     helper operators of the chunked formulation.
+// Semantics follow src/ops/rpu_gdn_recurrent.cpp:1-120 (decode step), src/ops/rpu_fla_conv1d.cpp,
+// src/ops/rpu_cumsum.cpp, src/ops/rpu_unit_tril_inv.cpp and the op order of
+// src/fused/rpu_qwen3_5_model.cpp:1301-1661.  The state of a head is split by COLUMNS over
+// CTAs: column j of S only ever needs k, q, v[j], so Dv/32 CTAs per head run independently
+// and a batch-1 decode step still fills Hv * Dv/32 SMs.
+#include "../common/dtype.cuh"
+#include "../common/host_util.h"
+#include "../common/ptx.cuh"
+#include "../rf_api.h"
+
+namespace rf {
+
+// ------------------------------------------------------------------ conv1d ----
+// y[t, c] = silu( sum_j w[c, j] * xin[t - (K-1) + j, c] ), xin = [state | x] per sequence.
+// One thread owns 8 adjacent channels of one token.
+template <typename T, int KW>
+__global__ void conv1d_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int64_t ldy,
+                              const T* __restrict__ w, const T* __restrict__ state,
+                              const int32_t* __restrict__ q_start, const int32_t* __restrict__ q_len,
+                              const int32_t* __restrict__ slot, int C, int tokens_per_block, int silu) {
+  pdl_prologue();
+  const int seq = blockIdx.z;
+  const int s0 = q_start ? q_start[seq] : seq;
+  const int n = q_len ? q_len[seq] : 1;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  const int sl = slot ? slot[seq] : seq;
+  const T* st = state + (size_t)sl * (KW - 1) * C;
+  float wk[KW][8];
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch) {
+#pragma unroll
+    for (int j = 0; j < KW; ++j) wk[j][ch] = Num<T>::to_f(w[(size_t)(c + ch) * KW + j]);
+  }
+  const int t0 = blockIdx.y * tokens_per_block;
+  const int t1 = min(n, t0 + tokens_per_block);
+  if (t0 >= n) return;
+  // sliding window of the last KW-1 inputs
+  float win[KW - 1][8];
+#pragma unroll
+  for (int j = 0; j < KW - 1; ++j) {
+    const int ti = t0 - (KW - 1) + j;     // input index relative to the sequence start
+    if (ti >= 0) load8(x + (size_t)(s0 + ti) * ldx + c, win[j]);
+    else load8(st + (size_t)(KW - 1 + ti) * C + c, win[j]);
+  }
+  for (int t = t0; t < t1; ++t) {
+    float cur[8], acc[8];
+    load8(x + (size_t)(s0 + t) * ldx + c, cur);
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+      float a = wk[KW - 1][ch] * cur[ch];
+#pragma unroll
+      for (int j = 0; j < KW - 1; ++j) a += wk[j][ch] * win[j][ch];
+      acc[ch] = silu ? silu_f(a) : a;
+    }
+    store8(y + (size_t)(s0 + t) * ldy + c, acc);
+#pragma unroll
+    for (int j = 0; j < KW - 2; ++j)
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) win[j][ch] = win[j + 1][ch];
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) win[KW - 2][ch] = cur[ch];
+  }
+}
+
+// new state = last KW-1 rows of [old state | x]; runs after conv1d_kernel of the same call.
+template <typename T, int KW>
+__global__ void conv1d_state_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ state,
+                                    const int32_t* __restrict__ q_start, const int32_t* __restrict__ q_len,
+                                    const int32_t* __restrict__ slot, int C) {
+  pdl_prologue();
+  const int seq = blockIdx.y;
+  const int s0 = q_start ? q_start[seq] : seq;
+  const int n = q_len ? q_len[seq] : 1;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  const int sl = slot ? slot[seq] : seq;
+  T* st = state + (size_t)sl * (KW - 1) * C;
+  float rows[KW - 1][8];
+#pragma unroll
+  for (int j = 0; j < KW - 1; ++j) {
+    const int ti = n - (KW - 1) + j;
+    if (ti >= 0) load8(x + (size_t)(s0 + ti) * ldx + c, rows[j]);
+    else load8(st + (size_t)(KW - 1 + ti) * C + c, rows[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < KW - 1; ++j) store8(st + (size_t)j * C + c, rows[j]);
+}
+
+// --------------------------------------------------------- delta rule ----
+constexpr int kGdnCols = 32;     // state columns per CTA
+constexpr int kGdnThreads = 128;  // 4 row groups x 32 columns
+
+template <typename T, int DK>
+__global__ void __launch_bounds__(kGdnThreads)
+gdn_recurrent_kernel(const RfGdn p) {
+  pdl_prologue();
+  constexpr int RG = kGdnThreads / kGdnCols;   // row groups
+  constexpr int RPT = DK / RG;                 // state rows per thread
+  const int seq = blockIdx.z, hv = blockIdx.y;
+  const int col = threadIdx.x % kGdnCols, rg = threadIdx.x / kGdnCols;
+  const int j = blockIdx.x * kGdnCols + col;   // state column = value channel
+  const int hk = hv / (p.Hv / p.Hk);
+  const int s0 = p.q_start ? p.q_start[seq] : seq;
+  const int n = p.q_len ? p.q_len[seq] : 1;
+  const int sl = p.slot ? p.slot[seq] : seq;
+  const int fresh = p.fresh ? p.fresh[seq] : 0;
+  float* S = p.state + (((size_t)sl * p.Hv + hv) * DK) * p.Dv;
+  const T* qkv = reinterpret_cast<const T*>(p.qkv);
+  const T* bp = reinterpret_cast<const T*>(p.b);
+  const T* ap = reinterpret_cast<const T*>(p.a);
+  T* out = reinterpret_cast<T*>(p.out);
+  const int q_off = hk * DK, k_off = p.Hk * DK + hk * DK, v_off = 2 * p.Hk * DK + hv * p.Dv;
+  const float A = -__expf(p.A_log[hv]), dtb = p.dt_bias[hv];
+  const float qscale = rsqrtf((float)DK);
+
+  __shared__ float sq[DK], sk[DK];
+  __shared__ float red[2][RG][kGdnCols];
+  __shared__ float ssum[2][kGdnThreads / 32];
+
+  float st[RPT];
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) st[r] = fresh ? 0.f : S[(size_t)(rg * RPT + r) * p.Dv + j];
+
+  for (int t = 0; t < n; ++t) {
+    const size_t row = (size_t)(s0 + t);
+    // L2-normalise q and k of this head (all 128 threads; DK == 128 -> one element each)
+    float qv = 0.f, kv = 0.f;
+    for (int i = threadIdx.x; i < DK; i += kGdnThreads) {
+      qv = Num<T>::to_f(qkv[row * p.ld + q_off + i]);
+      kv = Num<T>::to_f(qkv[row * p.ld + k_off + i]);
+    }
+    float q2 = qv * qv, k2 = kv * kv;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      q2 += __shfl_xor_sync(0xffffffffu, q2, o);
+      k2 += __shfl_xor_sync(0xffffffffu, k2, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+      ssum[0][threadIdx.x >> 5] = q2;
+      ssum[1][threadIdx.x >> 5] = k2;
+    }
+    __syncthreads();
+    float qn = 0.f, kn = 0.f;
+#pragma unroll
+    for (int w = 0; w < kGdnThreads / 32; ++w) {
+      qn += ssum[0][w];
+      kn += ssum[1][w];
+    }
+    if (threadIdx.x < DK) {
+      sq[threadIdx.x] = qv * rsqrtf(qn + 1e-6f) * qscale;
+      sk[threadIdx.x] = kv * rsqrtf(kn + 1e-6f);
+    }
+    const float beta = 1.f / (1.f + __expf(-Num<T>::to_f(bp[row * p.ld_ba + hv])));
+    const float ar = Num<T>::to_f(ap[row * p.ld_ba + hv]) + dtb;
+    const float sp = ar > 20.f ? ar : log1pf(__expf(ar));
+    const float decay = __expf(A * sp);
+    const float vj = Num<T>::to_f(qkv[row * p.ld + v_off + j]);
+    __syncthreads();
+    // S *= decay ; kv_mem[j] = sum_i S[i, j] k[i]
+    float part = 0.f;
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+      st[r] *= decay;
+      part += st[r] * sk[rg * RPT + r];
+    }
+    red[0][rg][col] = part;
+    __syncthreads();
+    float kvm = 0.f;
+#pragma unroll
+    for (int g = 0; g < RG; ++g) kvm += red[0][g][col];
+    const float delta = (vj - kvm) * beta;
+    float po = 0.f;
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+      st[r] += sk[rg * RPT + r] * delta;
+      po += st[r] * sq[rg * RPT + r];
+    }
+    red[1][rg][col] = po;
+    __syncthreads();
+    if (rg == 0) {
+      float o = 0.f;
+#pragma unroll
+      for (int g = 0; g < RG; ++g) o += red[1][g][col];
+      out[row * p.ldo + hv * p.Dv + j] = Num<T>::from_f(o);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) S[(size_t)(rg * RPT + r) * p.Dv + j] = st[r];
+}
+
+// ------------------------------------------------- gated RMSNorm over Dv ----
+// y = (w * rmsnorm(x)) * silu(z); one warp per (token, head) row of D <= 256 values.
+template <typename T>
+__global__ void rmsnorm_gated_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ z, int64_t ldz,
+                                     const T* __restrict__ w, T* __restrict__ y, int64_t ldy, int rows, int heads,
+                                     int D, float eps) {
+  pdl_prologue();
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int t = r / heads, h = r % heads;
+  const T* xr = x + (size_t)t * ldx + (size_t)h * D;
+  const T* zr = z + (size_t)t * ldz + (size_t)h * D;
+  T* yr = y + (size_t)t * ldy + (size_t)h * D;
+  float v[8];
+  float ss = 0.f;
+  const int per = D / 32;      // 2, 4 or 8
+  for (int i = 0; i < per; ++i) {
+    v[i] = Num<T>::to_f(xr[lane * per + i]);
+    ss += v[i] * v[i];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float inv = rsqrtf(ss / (float)D + eps);
+  for (int i = 0; i < per; ++i) {
+    const int c = lane * per + i;
+    const float nx = Num<T>::to_f(Num<T>::from_f(v[i] * inv));   // rounded like the unfused form
+    yr[c] = Num<T>::from_f(Num<T>::to_f(w[c]) * nx * silu_f(Num<T>::to_f(zr[c])));
+  }
+}
+
+// a[t, c] *= sigmoid(g[t, c])  (8 channels per thread; pitches in elements)
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ a, int64_t lda, const T* __restrict__ g, int64_t ldg,
+                                    int rows, int cols) {
+  pdl_prologue();
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int per_row = cols / 8;
+  if (idx >= (int64_t)rows * per_row) return;
+  const int t = (int)(idx / per_row), c = (int)(idx % per_row) * 8;
+  float x[8], y[8];
+  load8(a + (size_t)t * lda + c, x);
+  load8(g + (size_t)t * ldg + c, y);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) x[i] *= 1.f / (1.f + __expf(-y[i]));
+  store8(a + (size_t)t * lda + c, x);
+}
+
+// inclusive cumulative sum over the last dim (n <= 1024), one warp per row, fp32
+__global__ void cumsum_kernel(const float* __restrict__ x, float* __restrict__ y, int rows, int n) {
+  pdl_prologue();
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int lane = threadIdx.x & 31;
+  float carry = 0.f;
+  for (int base = 0; base < n; base += 32) {
+    const int i = base + lane;
+    float v = i < n ? x[(size_t)r * n + i] : 0.f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float u = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += u;
+    }
+    v += carry;
+    if (i < n) y[(size_t)r * n + i] = v;
+    carry = __shfl_sync(0xffffffffu, v, 31);
+  }
+}
+
+// X = (I - M)^-1 for a batch of n x n (n <= 64) blocks whose strict lower triangle is M
+// (everything on and above the diagonal of the input is ignored).  Forward substitution,
+// one CTA per block, one thread per column: X[i, :] = e_i + sum_{k<i} M[i, k] X[k, :].
+__global__ void unit_tril_inv_kernel(const float* __restrict__ m, float* __restrict__ out, int n) {
+  pdl_prologue();
+  __shared__ float M[64][65], X[64][65];
+  const float* mb = m + (size_t)blockIdx.x * n * n;
+  float* ob = out + (size_t)blockIdx.x * n * n;
+  for (int i = threadIdx.x; i < n * n; i += blockDim.x) {
+    M[i / n][i % n] = mb[i];
+    X[i / n][i % n] = 0.f;
+  }
+  __syncthreads();
+  const int c = threadIdx.x;
+  for (int i = 0; i < n; ++i) {
+    if (c < n) {
+      float acc = (c == i) ? 1.f : 0.f;
+      for (int k = 0; k < i; ++k) acc += M[i][k] * X[k][c];
+      X[i][c] = acc;
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < n * n; i += blockDim.x) ob[i] = X[i / n][i % n];
+}
+
+}  // namespace rf
+
+using namespace rf;
+
+#define RF_DISPATCH_T(dtype, ...)                      \
+  if ((dtype) == 0) { using T = __half; __VA_ARGS__; } \
+  else { using T = __nv_bfloat16; __VA_ARGS__; }
+
+extern "C" int rf_causal_conv1d(const RfConv1d* a, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(a && a->x && a->y && a->w && a->state, "conv1d: null argument");
+  RF_REQUIRE(a->K == 4, "conv1d: kernel size %d (only 4 is built)", a->K);
+  RF_REQUIRE(a->C % 8 == 0 && a->ldx % 8 == 0 && a->ldy % 8 == 0, "conv1d: channels and pitches must be multiples of 8");
+  RF_REQUIRE(a->num_seqs > 0, "conv1d: no sequences");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int threads = 128;
+  const int cblocks = (a->C / 8 + threads - 1) / threads;
+  const int max_len = a->q_len ? (a->max_q_len > 0 ? a->max_q_len : 1) : 1;
+  const int tpb = 32;
+  const int tblocks = (max_len + tpb - 1) / tpb;
+  RF_DISPATCH_T(a->dtype, {
+    RF_CUDA_CHECK(::rf::launch_k(conv1d_kernel<T, 4>, dim3(cblocks, tblocks, a->num_seqs), dim3(threads), 0, s, 1,
+                                 (const T*)a->x, a->ldx, (T*)a->y, a->ldy, (const T*)a->w, (const T*)a->state,
+                                 a->q_start, a->q_len, a->slot, a->C, tpb, a->silu));
+    ::rf::count_launch();
+    RF_CUDA_CHECK(::rf::launch_k(conv1d_state_kernel<T, 4>, dim3(cblocks, a->num_seqs), dim3(threads), 0, s, 1,
+                                 (const T*)a->x, a->ldx, (T*)a->state, a->q_start, a->q_len, a->slot, a->C));
+    ::rf::count_launch();
+  });
+  return RF_OK;
+}
+
+extern "C" int rf_gdn_recurrent(const RfGdn* a, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(a && a->qkv && a->b && a->a && a->out && a->state && a->A_log && a->dt_bias, "gdn: null argument");
+  RF_REQUIRE(a->Dk == 128, "gdn: key head dim %d (only 128 is built)", a->Dk);
+  RF_REQUIRE(a->Dv % kGdnCols == 0 && a->Hv % a->Hk == 0 && a->Hk > 0, "gdn: head geometry Hk=%d Hv=%d Dv=%d", a->Hk, a->Hv, a->Dv);
+  RF_REQUIRE(a->num_seqs > 0, "gdn: no sequences");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(a->Dv / kGdnCols, a->Hv, a->num_seqs);
+  if (a->dtype == 0) RF_CUDA_CHECK(::rf::launch_k(gdn_recurrent_kernel<__half, 128>, grid, dim3(kGdnThreads), 0, s, 1, *a));
+  else RF_CUDA_CHECK(::rf::launch_k(gdn_recurrent_kernel<__nv_bfloat16, 128>, grid, dim3(kGdnThreads), 0, s, 1, *a));
+  ::rf::count_launch();
+  return RF_OK;
+}
+
+extern "C" int rf_rmsnorm_gated(const void* x, int64_t ldx, const void* z, int64_t ldz, const void* w, void* y,
+                                int64_t ldy, int tokens, int heads, int D, float eps, int dtype, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(x && z && w && y, "rmsnorm_gated: null argument");
+  RF_REQUIRE(D % 32 == 0 && D <= 256, "rmsnorm_gated: width %d must be a multiple of 32, at most 256", D);
+  if (tokens == 0) return RF_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int rows = tokens * heads, wpb = 8;
+  RF_DISPATCH_T(dtype, RF_CUDA_CHECK(::rf::launch_k(rmsnorm_gated_kernel<T>, dim3((rows + wpb - 1) / wpb), dim3(wpb * 32), 0,
+                                                    s, 1, (const T*)x, ldx, (const T*)z, ldz, (const T*)w, (T*)y, ldy,
+                                                    rows, heads, D, eps)));
+  ::rf::count_launch();
+  return RF_OK;
+}
+
+extern "C" int rf_sigmoid_gate(void* a, int64_t lda, const void* g, int64_t ldg, int rows, int cols, int dtype,
+                               rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(a && g && cols % 8 == 0 && lda % 8 == 0 && ldg % 8 == 0, "sigmoid_gate arguments");
+  if (rows == 0) return RF_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t n = (int64_t)rows * (cols / 8);
+  RF_DISPATCH_T(dtype, RF_CUDA_CHECK(::rf::launch_k(sigmoid_gate_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s,
+                                                    1, (T*)a, lda, (const T*)g, ldg, rows, cols)));
+  ::rf::count_launch();
+  return RF_OK;
+}
+
+extern "C" int rf_cumsum_f32(const float* x, float* y, int rows, int n, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(x && y && n > 0, "cumsum arguments");
+  if (rows == 0) return RF_OK;
+  RF_CUDA_CHECK(::rf::launch_k(cumsum_kernel, dim3((rows + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream), 1, x, y,
+                               rows, n));
+  ::rf::count_launch();
+  return RF_OK;
+}
+
+extern "C" int rf_unit_tril_inv_f32(const float* m, float* out, int batch, int n, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(m && out && n > 0 && n <= 64, "unit_tril_inv: n=%d (1..64)", n);
+  if (batch == 0) return RF_OK;
+  RF_CUDA_CHECK(::rf::launch_k(unit_tril_inv_kernel, dim3(batch), dim3(64), 0, static_cast<cudaStream_t>(stream), 1, m, out, n));
+  ::rf::count_launch();
+  return RF_OK;
+}

@@ -42,6 +42,9 @@ struct GemmTcParams {
   int ar_world, ar_rank;
   void* const* ar_recv; uint32_t* const* ar_flags; uint32_t* ar_state;
   uint64_t ar_half_bytes;
+  const uint8_t* w_packed;  // tile-major weight image (null: row-major weights through the tensor maps)
+  int kb_total;             // k blocks of the whole weight (row-tile stride of the packed image)
+  int dual_tiles;           // row tiles of the first (gate) section
   int ar_two_shot;    // large-M path: 16-bit reduce-scatter to the tile's owner, then broadcast
   int ar_flag2_base;  // first flag of the "result has landed" range
 };
@@ -155,7 +158,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     auto load_weights = [&](int i, int s) {
       uint8_t* st = smem + (size_t)s * stage_bytes;
       const int kc = (kb0 + i) * kBK;
-      if (W8) {
+      if (p.w_packed) {
+        // contiguous 128-row x 64-column blocks: one bulk copy each
+        constexpr uint32_t kBlk = W8 ? (uint32_t)(kBM * kBK) : (uint32_t)kATileBytes;
+        const int rt0 = (SWAP ? a0 : b0) / kBM;
+        const int nsub = SWAP ? 1 : bn / kBM;
+#pragma unroll
+        for (int wt = 0; wt < kWTiles; ++wt) {
+          uint8_t* dst = W8 ? st + half_bytes + wt * q_tile_bytes
+                            : (SWAP ? st + wt * kATileBytes : st + kATiles * kATileBytes + wt * b_tile_bytes);
+          for (int sub = 0; sub < nsub; ++sub) {
+            const uint8_t* src = p.w_packed + ((size_t)(rt0 + sub + wt * p.dual_tiles) * p.kb_total + (kb0 + i)) * kBlk;
+            bulk_load_1d(dst + (size_t)sub * kBlk, src, kBlk, &ctl->full[s]);
+          }
+        }
+      } else if (W8) {
         const int r0 = SWAP ? a0 : b0;
         tma_load_2d(st + half_bytes, &tmW, &ctl->full[s], kc, r0);
         if (kWTiles == 2) tma_load_2d(st + half_bytes + q_tile_bytes, &tmW, &ctl->full[s], kc, p.dual_offset + r0);
@@ -654,7 +671,8 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
     pl->grid_y = ceil_div(g->M, bn);
   } else {
     int bn = g->force_bn > 0 ? g->force_bn : ((g->N % 256 == 0 && !dual) ? 256 : 128);
-    if (g->N < 128) bn = round_up(g->N, 16);
+    if (g->N < 128 && !g->w_packed) bn = round_up(g->N, 16);
+    if (g->w_packed && bn != 128 && bn != 256) bn = 128;   // packed weights come in 128-row blocks
     pl->bn = bn;
     pl->grid_x = ceil_div(g->M, kBM);
     pl->grid_y = ceil_div(g->N, bn);
@@ -719,7 +737,14 @@ static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream)
   const uint64_t w_rows = (uint64_t)(dual ? g->dual_offset + g->N : g->N);
   CUtensorMap tmA, tmB, tmW;
   int rc;
-  if (W8) {
+  if (g->w_packed) {
+    // only the activations go through a tensor map; the weight blocks are plain bulk copies
+    if (SWAP) rc = make_tmap_2d(&tmB, g->x, g->dtype, 2, g->K, g->M, g->ldx, kBK, pl.bn, true);
+    else rc = make_tmap_2d(&tmA, g->x, g->dtype, 2, g->K, g->M, g->ldx, kBK, kBM, true);
+    if (rc) return rc;
+    if (SWAP) tmA = tmB; else tmB = tmA;
+    tmW = tmA;
+  } else if (W8) {
     // int8 weights: their own byte-typed, unswizzled map; the 16-bit map of that operand is unused
     rc = make_tmap_2d(&tmW, g->w, 0, 1, g->K, w_rows, g->ldw, kBK, SWAP ? kBM : pl.bn, false);
     if (rc) return rc;
@@ -751,6 +776,9 @@ static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream)
   p.ar_world = g->ar_world; p.ar_rank = g->ar_rank;
   p.ar_recv = g->ar_recv; p.ar_flags = g->ar_flags; p.ar_state = g->ar_state;
   p.ar_half_bytes = g->ar_recv_bytes;
+  p.w_packed = g->w_packed ? reinterpret_cast<const uint8_t*>(g->w) : nullptr;
+  p.kb_total = pl.k_blocks;
+  p.dual_tiles = ceil_div(g->N, kBM);
   p.ar_two_shot = (g->ar_world > 1 && !SWAP && g->M > 256) ? 1 : 0;
   p.ar_flag2_base = g->ar_flag_count / 2;
   RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.grid_x, pl.grid_y, pl.splits), dim3(W8 ? 256 : 128), pl.smem_bytes, stream,
@@ -764,7 +792,8 @@ static int check_gemm(const RfGemm* g) {
   RF_REQUIRE(g->x && g->w && g->out, "GEMM needs x, w and out");
   RF_REQUIRE(g->M > 0 && g->N > 0 && g->K > 0, "GEMM shape %dx%dx%d", g->M, g->N, g->K);
   RF_REQUIRE(g->K % 8 == 0, "GEMM K=%d must be a multiple of 8 (16-byte rows)", g->K);
-  RF_REQUIRE(g->ldx % 8 == 0 && g->ldw % (g->w_int8 ? 16 : 8) == 0, "GEMM row pitches must be multiples of 16 bytes");
+  RF_REQUIRE(g->ldx % 8 == 0 && (g->w_packed || g->ldw % (g->w_int8 ? 16 : 8) == 0), "GEMM row pitches must be multiples of 16 bytes");
+  if (g->w_packed) RF_REQUIRE((reinterpret_cast<uintptr_t>(g->w) & 127) == 0, "packed weights must be 128-byte aligned");
   if (g->w_int8) RF_REQUIRE(g->scale != nullptr && g->K % 16 == 0, "int8 weights need a scale vector and K %% 16 == 0");
   RF_REQUIRE(g->dtype == 0 || g->dtype == 1, "GEMM dtype must be fp16 or bf16");
   const bool dual_act = g->act == kActSiluMul || g->act == kActGeluTanhMul;
@@ -783,6 +812,12 @@ static int check_gemm(const RfGemm* g) {
 }  // namespace rf
 
 using namespace rf;
+
+extern "C" uint64_t rf_pack_weight_bytes(int64_t rows, int64_t K, int32_t sections, int32_t elem_bytes) {
+  if (rows <= 0 || K <= 0 || sections <= 0 || rows % sections) return 0;
+  const int64_t tiles = ((rows / sections + kBM - 1) / kBM) * sections, kb = (K + kBK - 1) / kBK;
+  return (uint64_t)(tiles * kb) * kBM * kBK * (uint64_t)elem_bytes;
+}
 
 extern "C" int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem_count) {
   int rc = check_gemm(g);

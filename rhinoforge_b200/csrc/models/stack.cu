@@ -28,11 +28,17 @@ struct Stack {
   // arena
   uint8_t* base = nullptr;
   uint64_t bytes = 0;
-  uint64_t off_xn = 0, off_attn = 0, off_tmp = 0, off_wide = 0, off_head_xn = 0, off_logits = 0,
+  uint64_t off_xn = 0, off_attn = 0, off_tmp = 0, off_wide = 0, off_conv = 0, off_head_xn = 0, off_logits = 0,
            off_argmax = 0, off_attn_ws = 0, off_status = 0, total = 0;
   uint64_t attn_ws_bytes = 0, argmax_bytes = 0;
 
-  int qkv_dim() const { return (cfg.Hq + 2 * cfg.Hkv) * cfg.hd; }
+  int qkv_dim() const { return (cfg.Hq + 2 * cfg.Hkv) * cfg.hd + (cfg.attn_gate ? cfg.Hq * cfg.hd : 0); }
+  // Gated-DeltaNet geometry
+  int gdn_key_dim() const { return cfg.gdn_Hk * cfg.gdn_Dk; }
+  int gdn_value_dim() const { return cfg.gdn_Hv * cfg.gdn_Dv; }
+  int gdn_conv_dim() const { return 2 * gdn_key_dim() + gdn_value_dim(); }
+  int gdn_ba_pad() const { return (cfg.gdn_Hv + 7) / 8 * 8; }
+  int gdn_in_dim() const { return cfg.gdn_Hv > 0 ? gdn_conv_dim() + gdn_value_dim() + 2 * gdn_ba_pad() : 0; }
   bool glu() const { return cfg.mlp_kind == RF_MLP_SWIGLU || cfg.mlp_kind == RF_MLP_GEGLU_TANH; }
 
   void plan() {
@@ -40,9 +46,10 @@ struct Stack {
     const uint64_t T = (uint64_t)cfg.max_tokens, e = 2;
     uint64_t o = 0;
     off_xn = o; o += al(T * cfg.hidden * e);
-    off_attn = o; o += al(T * cfg.Hq * cfg.hd * e);
+    off_attn = o; o += al(T * std::max<uint64_t>(cfg.Hq * cfg.hd, gdn_value_dim()) * e);
     off_tmp = o; o += al(T * cfg.hidden * e);
-    off_wide = o; o += al(T * std::max<uint64_t>(qkv_dim(), cfg.inter) * e);
+    off_wide = o; o += al(T * std::max<uint64_t>(std::max(qkv_dim(), gdn_in_dim()), cfg.inter) * e);
+    off_conv = o; o += al(T * (uint64_t)(cfg.gdn_Hv > 0 ? gdn_conv_dim() : 0) * e);
     off_head_xn = o; o += al((uint64_t)cfg.max_seqs * cfg.hidden * e);
     off_logits = o; o += al((uint64_t)cfg.max_seqs * std::max(cfg.vocab_local, 1) * e);
     argmax_bytes = rf_argmax_scratch_bytes(cfg.max_seqs, std::max(cfg.vocab_local, 1));
@@ -81,6 +88,7 @@ static int linear(const Stack& s, const void* x, int64_t ldx, const void* w, con
   g.residual = residual; g.ldr = ldr; g.bias = bias; g.scale = scale;
   g.M = M; g.N = N; g.K = K; g.dtype = s.cfg.dtype; g.act = act; g.dual_offset = dual_offset;
   g.w_int8 = s.cfg.weights_int8 && scale != nullptr;
+  g.w_packed = s.cfg.weights_packed;
   g.status = s.status();
   g.force_swap = -1;
   const bool ar = all_reduce && s.cfg.tp_world > 1;
@@ -90,7 +98,7 @@ static int linear(const Stack& s, const void* x, int64_t ldx, const void* w, con
     g.ar_recv = s.comm.recv; g.ar_flags = s.comm.flags; g.ar_state = s.comm.state;
     g.ar_recv_bytes = s.comm.recv_half_bytes; g.ar_flag_count = s.comm.flag_count;
   }
-  if (!ar && M <= 8 && (M <= s.cfg.decode_gemv_max_m) && K % (g.w_int8 ? 16 : 8) == 0) return rf_gemv(&g, st);
+  if (!ar && !g.w_packed && M <= 8 && (M <= s.cfg.decode_gemv_max_m) && K % (g.w_int8 ? 16 : 8) == 0) return rf_gemv(&g, st);
   if (g.w_int8) return rf_gemm_w8a16(&g, st);
   return rf_gemm(&g, st);
 }
@@ -133,9 +141,39 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     const RfLayerWeights& w = s.layers[l];
     const uint8_t* mod1 = f.mod ? (const uint8_t*)f.mod + ((size_t)(l * 2 + 0) * nmods) * 3 * H * esz : nullptr;
     const uint8_t* mod2 = f.mod ? (const uint8_t*)f.mod + ((size_t)(l * 2 + 1) * nmods) * 3 * H * esz : nullptr;
-    // ---- attention block
+    // ---- token mixer: softmax attention or Gated-DeltaNet
     rc = norm(s, f.hidden, w.norm1_w, w.norm1_b, xn, T, mod1, f.rows_per_mod, st);
     if (rc) return rc;
+    const void* mix_out = attn;      // input of the output projection
+    int mix_dim = AD;
+    if (w.mixer == 1) {
+      RF_REQUIRE(c.gdn_Hv > 0 && w.gdn_conv_w && w.gdn_conv_state && w.gdn_rec_state, "layer %d: GDN weights/state missing", l);
+      const int CD = s.gdn_conv_dim(), VD = s.gdn_value_dim(), IN = s.gdn_in_dim(), BA = s.gdn_ba_pad();
+      void* conv = s.at(s.off_conv);
+      rc = linear(s, xn, H, w.wqkv, w.sqkv, nullptr, wide, IN, nullptr, 0, T, IN, H, kActNone, 0, false, st);
+      if (rc) return rc;
+      RfConv1d cv = {};
+      cv.x = wide; cv.ldx = IN; cv.y = conv; cv.ldy = CD; cv.w = w.gdn_conv_w; cv.state = w.gdn_conv_state;
+      cv.q_start = f.decode ? nullptr : f.q_start; cv.q_len = f.decode ? nullptr : f.q_len; cv.slot = f.state_slot;
+      cv.num_seqs = f.num_seqs; cv.max_q_len = f.decode ? 1 : f.max_q_len; cv.C = CD; cv.K = c.gdn_conv_k; cv.silu = 1;
+      cv.dtype = c.dtype;
+      rc = rf_causal_conv1d(&cv, st);
+      if (rc) return rc;
+      RfGdn g = {};
+      g.qkv = conv; g.ld = CD;
+      g.b = (const uint8_t*)wide + (size_t)(CD + VD) * esz; g.a = (const uint8_t*)wide + (size_t)(CD + VD + BA) * esz;
+      g.ld_ba = IN; g.out = attn; g.ldo = VD; g.state = w.gdn_rec_state; g.A_log = w.gdn_A_log; g.dt_bias = w.gdn_dt_bias;
+      g.q_start = cv.q_start; g.q_len = cv.q_len; g.slot = f.state_slot; g.fresh = f.state_fresh;
+      g.num_seqs = f.num_seqs; g.Hk = c.gdn_Hk; g.Hv = c.gdn_Hv; g.Dk = c.gdn_Dk; g.Dv = c.gdn_Dv; g.dtype = c.dtype;
+      rc = rf_gdn_recurrent(&g, st);
+      if (rc) return rc;
+      // gated RMSNorm over Dv: the conv buffer is free again and takes the result
+      rc = rf_rmsnorm_gated(attn, VD, (const uint8_t*)wide + (size_t)CD * esz, IN, w.gdn_norm_w, conv, VD, T, c.gdn_Hv,
+                            c.gdn_Dv, c.eps, c.dtype, st);
+      if (rc) return rc;
+      mix_out = conv;
+      mix_dim = VD;
+    } else {
     rc = linear(s, xn, H, w.wqkv, w.sqkv, w.bqkv, wide, QD, nullptr, 0, T, QD, H, kActNone, 0, false, st);
     if (rc) return rc;
     {
@@ -189,12 +227,17 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
         rc = rf_attn_prefill(&a, st);
       }
       if (rc) return rc;
+      if (c.attn_gate) {
+        rc = rf_sigmoid_gate(attn, AD, (const uint8_t*)wide + (size_t)(c.Hq + 2 * c.Hkv) * c.hd * esz, QD, T, AD, c.dtype, st);
+        if (rc) return rc;
+      }
+    }
     }
     if (!side) {
-      rc = linear(s, attn, AD, w.wo, w.so, w.bo, f.hidden, H, f.hidden, H, T, H, AD, kActNone, 0, true, st);
+      rc = linear(s, mix_out, mix_dim, w.wo, w.so, w.bo, f.hidden, H, f.hidden, H, T, H, mix_dim, kActNone, 0, true, st);
       if (rc) return rc;
     } else {
-      rc = linear(s, attn, AD, w.wo, w.so, w.bo, tmp, H, nullptr, 0, T, H, AD, kActNone, 0, true, st);
+      rc = linear(s, mix_out, mix_dim, w.wo, w.so, w.bo, tmp, H, nullptr, 0, T, H, mix_dim, kActNone, 0, true, st);
       if (rc) return rc;
       if (c.sandwich_norm) {
         rc = rf_rmsnorm(tmp, nullptr, w.post_attn_norm_w, tmp, nullptr, nullptr, 1, T, H, H, H, c.eps,
@@ -293,7 +336,10 @@ extern "C" int rf_stack_set_layer(int64_t h, int32_t layer, const RfLayerWeights
   RF_GET_STACK(h);
   RF_REQUIRE(w && layer >= 0 && layer < s.cfg.layers, "layer index %d out of range", layer);
   RF_REQUIRE(w->wqkv && w->wo && w->w_up && w->w_down, "layer %d: missing projection weights", layer);
-  if (s.cfg.paged_kv) RF_REQUIRE(w->k_pool && w->v_pool, "layer %d: missing KV pool", layer);
+  if (s.cfg.paged_kv && w->mixer == 0) RF_REQUIRE(w->k_pool && w->v_pool, "layer %d: missing KV pool", layer);
+  if (w->mixer == 1)
+    RF_REQUIRE(s.cfg.gdn_Hv > 0 && w->gdn_conv_w && w->gdn_A_log && w->gdn_dt_bias && w->gdn_norm_w && w->gdn_conv_state &&
+                   w->gdn_rec_state, "layer %d: incomplete Gated-DeltaNet weight set", layer);
   if (s.cfg.weights_int8) RF_REQUIRE(w->sqkv && w->so && w->s_up && w->s_down, "layer %d: int8 weights need scales", layer);
   s.layers[layer] = *w;
   return RF_OK;
@@ -304,6 +350,14 @@ extern "C" int rf_stack_set_kv(int64_t h, int32_t layer, void* k_pool, void* v_p
   RF_REQUIRE(layer >= 0 && layer < s.cfg.layers && k_pool && v_pool, "set_kv: layer %d", layer);
   s.layers[layer].k_pool = k_pool;
   s.layers[layer].v_pool = v_pool;
+  return RF_OK;
+}
+
+extern "C" int rf_stack_set_state(int64_t h, int32_t layer, void* conv_state, float* rec_state) {
+  RF_GET_STACK(h);
+  RF_REQUIRE(layer >= 0 && layer < s.cfg.layers && conv_state && rec_state, "set_state: layer %d", layer);
+  s.layers[layer].gdn_conv_state = conv_state;
+  s.layers[layer].gdn_rec_state = rec_state;
   return RF_OK;
 }
 
@@ -409,4 +463,5 @@ extern "C" void rf_struct_sizes(int32_t* out) {
   out[0] = (int32_t)sizeof(RfGemm); out[1] = (int32_t)sizeof(RfRopeKv); out[2] = (int32_t)sizeof(RfAttn);
   out[3] = (int32_t)sizeof(RfStackConfig); out[4] = (int32_t)sizeof(RfLayerWeights);
   out[5] = (int32_t)sizeof(RfStackComm); out[6] = (int32_t)sizeof(RfStackForward); out[7] = 0;
+  out[8] = (int32_t)sizeof(RfConv1d); out[9] = (int32_t)sizeof(RfGdn); out[10] = 0;
 }

@@ -42,6 +42,10 @@ typedef struct RfStackConfig {
   int32_t tp_world, tp_rank;
   int32_t weights_int8;         // linear weights are int8 + per-channel scale
   int32_t decode_gemv_max_m;    // use the CUDA-core GEMV for token counts up to this (0: never)
+  int32_t attn_gate;            // q_proj also yields a per-channel output gate: attn *= sigmoid(gate)
+  // Gated-DeltaNet layers (LOCAL head counts); gdn_Hv == 0: the stack has none
+  int32_t gdn_Hk, gdn_Hv, gdn_Dk, gdn_Dv, gdn_conv_k;
+  int32_t weights_packed;       // every linear weight (and the lm_head) is in the tile-major layout of RfGemm.w_packed
 } RfStackConfig;
 
 typedef struct RfLayerWeights {
@@ -54,6 +58,14 @@ typedef struct RfLayerWeights {
   const void* w_down; const void* b_down; const void* s_down;
   const void* post_attn_norm_w; const void* post_mlp_norm_w;   // sandwich norms
   void* k_pool; void* v_pool;                                  // this layer's KV pages
+  // mixer == 1: Gated-DeltaNet layer.  wqkv is then the fused input projection
+  // [q | k | v | z | b (padded to 8) | a (padded to 8)] and wo the output projection.
+  int64_t mixer;
+  const void* gdn_conv_w;        // [conv_dim, K]
+  const float* gdn_A_log; const float* gdn_dt_bias;            // [Hv] fp32
+  const void* gdn_norm_w;        // [Dv]
+  void* gdn_conv_state;          // [slots, K-1, conv_dim]
+  float* gdn_rec_state;          // [slots, Hv, Dk, Dv] fp32
 } RfLayerWeights;
 
 typedef struct RfStackComm {
@@ -83,6 +95,9 @@ typedef struct RfStackForward {
   const void* const* deepstack; const int32_t* deepstack_rows; int32_t n_deepstack, n_deepstack_rows;
   // tap: copy hidden after layer tap_layers[i] into taps[i] (vision DeepStack features)
   void* const* taps; const int32_t* tap_layers; int32_t n_taps;
+  // recurrent-state bookkeeping of Gated-DeltaNet layers: state slot of every sequence (null:
+  // sequence index) and whether the sequence starts from an empty state (null: continue)
+  const int32_t* state_slot; const int32_t* state_fresh;
 } RfStackForward;
 
 int64_t rf_stack_create(const RfStackConfig* cfg);
@@ -90,6 +105,8 @@ int rf_stack_destroy(int64_t h);
 int rf_stack_set_layer(int64_t h, int32_t layer, const RfLayerWeights* w);
 // Re-point one layer at another KV pool (binding a different cache object).
 int rf_stack_set_kv(int64_t h, int32_t layer, void* k_pool, void* v_pool);
+// Re-point a Gated-DeltaNet layer at other state tensors (binding a different cache object).
+int rf_stack_set_state(int64_t h, int32_t layer, void* conv_state, float* rec_state);
 int rf_stack_set_head(int64_t h, const void* final_norm_w, const void* final_norm_b, const void* w_lm,
                       const void* s_lm);
 int rf_stack_set_comm(int64_t h, const RfStackComm* c);

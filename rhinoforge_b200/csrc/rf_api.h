@@ -53,7 +53,14 @@ typedef struct RfGemm {
   int32_t force_splits;        // 0 = heuristic
   int32_t force_swap;          // -1 = heuristic, 0/1 forced
   int32_t force_bn;            // 0 = heuristic
+  // 1: w is in the tile-major layout (see rf_pack_weight_bytes): block (row tile rt, k block kb) of
+  // 128 rows x 64 columns is contiguous, 16-bit blocks already in the 128-byte-swizzled shared-memory
+  // image, so one 16 KB (int8: 8 KB) bulk copy per block streams HBM pages front to back.  Rows are
+  // padded to 128 per section (dual: gate section, then up section), K to 64; ldw is ignored.
+  int32_t w_packed;
 } RfGemm;
+// bytes of the tile-major image of a [rows, K] weight with `sections` equal row sections
+uint64_t rf_pack_weight_bytes(int64_t rows, int64_t K, int32_t sections, int32_t elem_bytes);
 
 int rf_gemm(const RfGemm* g, rf_stream_t stream);
 // Scratch a split-K launch of this shape would need (bytes of ws, number of sems).
@@ -144,6 +151,59 @@ typedef struct RfAttn {
 int rf_attn_prefill(const RfAttn* a, rf_stream_t stream);
 int rf_attn_decode(const RfAttn* a, rf_stream_t stream);
 uint64_t rf_attn_decode_scratch_bytes(int num_seqs, int Hq, int hd);
+
+
+// --------------------------------------------- linear attention (GDN) ----
+// Causal depthwise conv1d (kernel size 4) + optional SiLU over C channels of packed varlen rows,
+// with a carried state [slots, K-1, C] (oldest row first) that is read, then replaced by the last
+// K-1 inputs of every sequence.  q_start/q_len null: one token per sequence (decode), row = seq.
+// x and y must not alias.
+typedef struct RfConv1d {
+  const void* x; int64_t ldx;
+  void* y; int64_t ldy;
+  const void* w;            // [C, K]
+  void* state;              // [slots, K-1, C]
+  const int32_t* q_start; const int32_t* q_len; const int32_t* slot;   // device, [num_seqs]; slot null: seq
+  int32_t num_seqs, max_q_len, C, K, silu, dtype;
+} RfConv1d;
+int rf_causal_conv1d(const RfConv1d* a, rf_stream_t stream);
+
+// Gated delta rule over n tokens per sequence (n = 1: decode step):
+//   beta = sigmoid(b), g = -exp(A_log) * softplus(a + dt_bias), q,k L2-normalised, q /= sqrt(Dk)
+//   S *= exp(g);  kv = k^T S;  d = (v - kv) * beta;  S += k (x) d;  o = q^T S
+// qkv rows hold [q: Hk*Dk | k: Hk*Dk | v: Hv*Dv]; value head h reads key head h / (Hv/Hk).
+// state: fp32 [slots, Hv, Dk, Dv]; fresh[seq] != 0 starts that sequence from a zero state.
+typedef struct RfGdn {
+  const void* qkv; int64_t ld;
+  const void* b; const void* a; int64_t ld_ba;     // [rows, >= Hv] each
+  void* out; int64_t ldo;                           // [rows, Hv*Dv]
+  float* state;
+  const float* A_log; const float* dt_bias;         // [Hv] fp32
+  const int32_t* q_start; const int32_t* q_len; const int32_t* slot; const int32_t* fresh;
+  int32_t num_seqs, Hk, Hv, Dk, Dv, dtype;
+} RfGdn;
+int rf_gdn_recurrent(const RfGdn* a, rf_stream_t stream);
+// y[t, h, :] = (w * rmsnorm(x[t, h, :])) * silu(z[t, h, :]), D values per (token, head)
+int rf_rmsnorm_gated(const void* x, int64_t ldx, const void* z, int64_t ldz, const void* w, void* y, int64_t ldy,
+                     int tokens, int heads, int D, float eps, int dtype, rf_stream_t stream);
+// a[t, c] *= sigmoid(g[t, c]) (output gate of the gated full-attention layers)
+int rf_sigmoid_gate(void* a, int64_t lda, const void* g, int64_t ldg, int rows, int cols, int dtype, rf_stream_t stream);
+// helpers of the chunked delta-rule formulation
+int rf_cumsum_f32(const float* x, float* y, int rows, int n, rf_stream_t stream);
+int rf_unit_tril_inv_f32(const float* m, float* out, int batch, int n, rf_stream_t stream);
+
+
+// ------------------------------------------------- mixture of experts ----
+// Router: scores = sigmoid(logits) (score_fn 0) or softmax(logits) (1); the k experts with the largest
+// (score + bias) are selected, ties to the lower index; weights are the UNBIASED scores, divided by their
+// sum when norm_topk, times scale.  Any of out_ids [rows,k], out_w [rows,k], dense_w [rows,E] (zero for
+// unselected experts) may be null.  E <= 256, k <= 32.
+int rf_moe_select(const void* logits, int64_t ld, const float* bias, int rows, int E, int k, int score_fn,
+                  int norm_topk, float scale, int32_t* out_ids, float* out_w, void* dense_w, int64_t ldd, int dtype,
+                  rf_stream_t stream);
+// h[t, e*I + c] *= dense_w[t, e] for the E routed expert blocks of width I (dense-einsum expert MLP)
+int rf_moe_scale_blocks(void* h, int64_t ldh, const void* dense_w, int64_t ldd, int rows, int E, int I, int dtype,
+                        rf_stream_t stream);
 
 
 // ------------------------------------------------------------- KV pool ----

@@ -39,10 +39,21 @@ class DecoderConfig:
     rotary_dim: Optional[int] = None           # partial rotary; None = head_dim
     mrope_section: Optional[Tuple[int, int, int]] = None  # interleaved M-RoPE (Qwen3-VL)
     model_type: str = "qwen3"
+    # hybrid decoders (Qwen3.5): per-layer mixer kinds and the Gated-DeltaNet geometry
+    layer_types: Optional[Tuple[str, ...]] = None     # "full_attention" | "linear_attention"; None: all attention
+    attn_gate: bool = False                           # q_proj carries a sigmoid output gate per channel
+    gdn_heads_k: int = 0
+    gdn_heads_v: int = 0
+    gdn_dk: int = 0
+    gdn_dv: int = 0
+    gdn_conv: int = 4
 
     @property
     def rot_dim(self) -> int:
         return self.rotary_dim or self.head_dim
+
+    def is_linear(self, layer: int) -> bool:
+        return self.layer_types is not None and self.layer_types[layer] == "linear_attention"
 
     def profile(self) -> Tuple[int, int, int, int]:
         """(hidden, intermediate, layers, kv_heads): the admission key of the reference
@@ -68,19 +79,29 @@ class DecoderConfig:
         mrope = None
         if isinstance(rp, dict) and rp.get("mrope_section"):
             mrope = tuple(rp["mrope_section"])
-        return cls(
+        hybrid = {}
+        gemma_norm = mt.startswith("gemma")
+        if mt.startswith("qwen3_5"):
+            hd_ = g("head_dim", None) or hf.hidden_size // hf.num_attention_heads
+            prf = float(rp.get("partial_rotary_factor", 1.0)) if isinstance(rp, dict) else 1.0
+            hybrid = dict(layer_types=tuple(g("layer_types")), attn_gate=True, gdn_heads_k=g("linear_num_key_heads"),
+                          gdn_heads_v=g("linear_num_value_heads"), gdn_dk=g("linear_key_head_dim"),
+                          gdn_dv=g("linear_value_head_dim"), gdn_conv=g("linear_conv_kernel_dim", 4),
+                          rotary_dim=int(hd_ * prf))
+            gemma_norm = True           # Qwen3.5 RMSNorm stores (w - 1)
+        return cls(**hybrid, **dict(
             name=g("name_or_path", mt) or mt, vocab_size=hf.vocab_size, hidden_size=hf.hidden_size,
             intermediate_size=hf.intermediate_size, num_layers=hf.num_hidden_layers,
             num_heads=hf.num_attention_heads, num_kv_heads=g("num_key_value_heads", hf.num_attention_heads),
             head_dim=g("head_dim", None) or hf.hidden_size // hf.num_attention_heads,
             rms_eps=g("rms_norm_eps", 1e-6), rope_theta=float(rope_theta or 1e6),
             tie_embeddings=bool(g("tie_word_embeddings", False)),
-            qk_norm=mt in ("qwen3", "qwen3_vl_text", "qwen3_vl", "qwen3_moe"),
+            qk_norm=mt in ("qwen3", "qwen3_vl_text", "qwen3_vl", "qwen3_moe") or mt.startswith("qwen3_5"),
             attention_bias=bool(g("attention_bias", False)),
             mlp="geglu_tanh" if mt.startswith("gemma") else "swiglu",
-            norm="rms_gemma" if mt.startswith("gemma") else "rms",
+            norm="rms_gemma" if gemma_norm else "rms",
             embed_scale=math.sqrt(hf.hidden_size) if mt.startswith("gemma") else 1.0,
-            max_position=g("max_position_embeddings", 40960), mrope_section=mrope, model_type=mt)
+            max_position=g("max_position_embeddings", 40960), mrope_section=mrope, model_type=mt))
 
 
 def _q3(name, H, I, L, heads, kv, tie, vocab=151936):

@@ -137,17 +137,19 @@ def pi05_weight_shapes(cfg: Pi05Config) -> Iterator[Tuple[str, Tuple[int, ...], 
 def random_pi05_state_dict(cfg: Pi05Config, *, seed: int = 0, std: float = 0.02, dtype=torch.float16,
                            device="cpu") -> Dict[str, torch.Tensor]:
     """Random-init weights of the real architecture (synthetic benchmarks and tests)."""
-    g = torch.Generator(device="cpu").manual_seed(seed)
+    gen_dev = "cuda" if str(device).startswith("cuda") else "cpu"     # full-size models are drawn on the device
+    g = torch.Generator(device=gen_dev).manual_seed(seed)
     sd = {}
     for name, shape, kind in pi05_weight_shapes(cfg):
+        r = torch.randn(shape, generator=g, device=gen_dev)
         if kind == "matrix":
-            t = torch.randn(shape, generator=g) * std
+            t = r * std
         elif kind == "norm1":
-            t = 1.0 + 0.05 * torch.randn(shape, generator=g)
+            t = 1.0 + 0.05 * r
         elif kind == "norm0":                       # Gemma stores (w - 1)
-            t = 0.05 * torch.randn(shape, generator=g)
+            t = 0.05 * r
         else:
-            t = 0.02 * torch.randn(shape, generator=g)
+            t = 0.02 * r
         sd[name] = t.to(device, dtype)
     return sd
 
@@ -236,9 +238,12 @@ class TorchPi05:
         if past_kv is not None:
             k, v = torch.cat((past_kv[0], k), 2), torch.cat((past_kv[1], v), 2)
         G = g.heads // g.kv_heads
-        s = (q.float() @ k.repeat_interleave(G, 1).float().transpose(-1, -2)) / math.sqrt(g.head_dim)
-        s = s.masked_fill(~mask[:, None], float("-inf"))
-        a = (torch.softmax(s, -1) @ v.repeat_interleave(G, 1).float()).to(self.dtype)
+        if self.dtype != torch.float32:      # 16-bit baseline runs: the library's fused attention
+            a = F.scaled_dot_product_attention(q, k, v, attn_mask=mask[:, None], enable_gqa=True)
+        else:
+            s = (q.float() @ k.repeat_interleave(G, 1).float().transpose(-1, -2)) / math.sqrt(g.head_dim)
+            s = s.masked_fill(~mask[:, None], float("-inf"))
+            a = (torch.softmax(s, -1) @ v.repeat_interleave(G, 1).float()).to(self.dtype)
         o = F.linear(a.transpose(1, 2).reshape(B, S, -1), sd[b + "self_attn.o_proj.weight"])
         x = x + (o if gate is None else gate * o)
         h, gate = norm("post_attention_layernorm", x)

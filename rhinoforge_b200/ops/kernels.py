@@ -55,7 +55,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          act: Optional[str] = None, dual: bool = False, status: Optional[torch.Tensor] = None,
          force_splits: int = 0, force_swap: int = -1, force_bn: int = 0, use_gemv: bool = False,
          ws: Optional[torch.Tensor] = None, sem: Optional[torch.Tensor] = None,
-         comm=None) -> torch.Tensor:
+         comm=None, packed_shape: Optional[tuple] = None) -> torch.Tensor:
     """``out = epilogue(x @ w.T)`` on the tcgen05 kernel (or the CUDA-core GEMV).
 
     ``dual=True``: ``w`` stacks ``[gate; up]`` (2N rows) and ``act`` is a ``*_mul``
@@ -63,16 +63,21 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     ``w`` may be int8 with ``scale`` (per output channel) for the GEMV path.
     ``comm``: a :class:`rhinoforge_b200.parallel.symm.CommBuffers` for the fused all-reduce.
     """
-    assert x.is_cuda and x.dim() == 2 and w.dim() == 2 and x.stride(1) == 1 and w.stride(1) == 1
     M, K = x.shape
-    n_rows = w.shape[0]
-    assert w.shape[1] == K, (x.shape, w.shape)
+    if packed_shape is not None:          # ``w`` is the tile-major image made by pack_weight(); (rows, K) is its logical shape
+        n_rows, wk = packed_shape
+        assert wk == K and x.is_cuda and x.stride(1) == 1
+    else:
+        assert x.is_cuda and x.dim() == 2 and w.dim() == 2 and x.stride(1) == 1 and w.stride(1) == 1
+        n_rows = w.shape[0]
+        assert w.shape[1] == K, (x.shape, w.shape)
     Nn = n_rows // 2 if dual else n_rows
     if out is None:
         out = torch.empty((M, Nn), dtype=x.dtype, device=x.device)
     g = N.RfGemm()
     g.x, g.ldx = x.data_ptr(), x.stride(0)
-    g.w, g.ldw = w.data_ptr(), w.stride(0)
+    g.w, g.ldw = w.data_ptr(), (K if packed_shape is not None else w.stride(0))
+    g.w_packed = 1 if packed_shape is not None else 0
     g.out, g.ldo = out.data_ptr(), out.stride(0)
     if residual is not None:
         g.residual, g.ldr = residual.data_ptr(), residual.stride(0)
@@ -104,6 +109,29 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     else:
         N.check(lib.rf_gemm(C.byref(g), _stream()), "rf_gemm")
     return out
+
+
+def pack_weight(w: torch.Tensor, sections: int = 1) -> torch.Tensor:
+    """Tile-major image of a row-major ``[rows, K]`` weight (16-bit or int8) for ``gemm(..., packed_shape=)``.
+
+    Blocks of 128 rows x 64 columns are stored contiguously, ordered ``[row tile][k block]``; a 16-bit
+    block is the 128-byte-swizzled shared-memory image (16-byte chunk ``c`` of row ``r`` sits at chunk
+    ``c ^ (r % 8)``), an int8 block is plain row-major.  ``sections`` > 1 (GLU gate/up stacks) pads every
+    section to a multiple of 128 rows.  Rows/columns beyond the logical shape are zero."""
+    rows, Kd = w.shape
+    assert rows % sections == 0
+    per = rows // sections
+    rt, kb = (per + 127) // 128, (Kd + 63) // 64
+    out = torch.zeros((sections, rt * 128, kb * 64), dtype=w.dtype, device=w.device)
+    out[:, :per, :Kd] = w.view(sections, per, Kd)
+    out = out.view(sections * rt, 128, kb, 64).permute(0, 2, 1, 3).contiguous()        # [tile, kb, 128, 64]
+    if w.element_size() == 2:
+        blk = out.view(sections * rt, kb, 128, 8, 8)                                    # 8 chunks of 8 elements
+        r = torch.arange(128, device=w.device)[:, None]
+        c = torch.arange(8, device=w.device)[None, :]
+        src = (c ^ (r % 8)).view(1, 1, 128, 8, 1).expand_as(blk)                        # position p holds chunk p ^ (r%8)
+        out = torch.gather(blk, 3, src).contiguous()
+    return out.view(-1)
 
 
 def rmsnorm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, *, residual: Optional[torch.Tensor] = None,
@@ -314,3 +342,113 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, *, Hq: int, Hkv: int, h
 def attn_decode_scratch(num_seqs: int, Hq: int, hd: int, device) -> torch.Tensor:
     n = N.lib().rf_attn_decode_scratch_bytes(num_seqs, Hq, hd)
     return torch.empty(n // 4, dtype=torch.float32, device=device)
+
+
+# ----------------------------------------------------------------------------- linear attention (GDN)
+def causal_conv1d(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, *, q_start: Optional[torch.Tensor] = None,
+                  q_len: Optional[torch.Tensor] = None, max_q_len: int = 1, slot: Optional[torch.Tensor] = None,
+                  num_seqs: Optional[int] = None, silu: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Depthwise causal conv (kernel 4) + SiLU over packed rows ``x [T, >=C]`` (pitch = ``x.stride(0)``) with the
+    carried ``state [slots, K-1, C]`` (updated in place).  Without ``q_start``/``q_len``: one token per sequence."""
+    Cc, Kw = w.shape
+    a = N.RfConv1d()
+    if out is None:
+        out = torch.empty((x.shape[0], Cc), dtype=x.dtype, device=x.device)
+    a.x, a.ldx, a.y, a.ldy = x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0)
+    a.w, a.state = w.data_ptr(), state.data_ptr()
+    a.q_start, a.q_len, a.slot = _i32(q_start), _i32(q_len), _i32(slot)
+    a.num_seqs = int(num_seqs if num_seqs is not None else (q_len.numel() if q_len is not None else x.shape[0]))
+    a.max_q_len, a.C, a.K, a.silu, a.dtype = max_q_len, Cc, Kw, int(silu), dtype_code(x.dtype)
+    N.check(N.lib().rf_causal_conv1d(C.byref(a), _stream()), "rf_causal_conv1d")
+    return out
+
+
+def gdn_recurrent(qkv: torch.Tensor, b: torch.Tensor, a_: torch.Tensor, state: torch.Tensor, A_log: torch.Tensor,
+                  dt_bias: torch.Tensor, *, Hk: int, Hv: int, Dk: int, Dv: int, q_start: Optional[torch.Tensor] = None,
+                  q_len: Optional[torch.Tensor] = None, slot: Optional[torch.Tensor] = None,
+                  fresh: Optional[torch.Tensor] = None, num_seqs: Optional[int] = None,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gated delta rule; ``qkv [T, 2*Hk*Dk + Hv*Dv]``, ``b``/``a_`` ``[T, >=Hv]`` views with a common pitch,
+    ``state`` fp32 ``[slots, Hv, Dk, Dv]`` (updated in place).  Returns ``[T, Hv*Dv]``."""
+    assert state.dtype == torch.float32 and A_log.dtype == torch.float32 and dt_bias.dtype == torch.float32
+    assert b.stride(0) == a_.stride(0)
+    g = N.RfGdn()
+    if out is None:
+        out = torch.empty((qkv.shape[0], Hv * Dv), dtype=qkv.dtype, device=qkv.device)
+    g.qkv, g.ld = qkv.data_ptr(), qkv.stride(0)
+    g.b, g.a, g.ld_ba = b.data_ptr(), a_.data_ptr(), b.stride(0)
+    g.out, g.ldo, g.state = out.data_ptr(), out.stride(0), state.data_ptr()
+    g.A_log, g.dt_bias = A_log.data_ptr(), dt_bias.data_ptr()
+    g.q_start, g.q_len, g.slot, g.fresh = _i32(q_start), _i32(q_len), _i32(slot), _i32(fresh)
+    g.num_seqs = int(num_seqs if num_seqs is not None else (q_len.numel() if q_len is not None else qkv.shape[0]))
+    g.Hk, g.Hv, g.Dk, g.Dv, g.dtype = Hk, Hv, Dk, Dv, dtype_code(qkv.dtype)
+    N.check(N.lib().rf_gdn_recurrent(C.byref(g), _stream()), "rf_gdn_recurrent")
+    return out
+
+
+def rmsnorm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, heads: int, eps: float,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``(w * rmsnorm(x[t, h, :])) * silu(z[t, h, :])`` with ``x``/``z`` ``[T, heads*D]`` row views."""
+    D = w.numel()
+    if out is None:
+        out = torch.empty((x.shape[0], heads * D), dtype=x.dtype, device=x.device)
+    N.check(N.lib().rf_rmsnorm_gated(C.c_void_p(x.data_ptr()), C.c_int64(x.stride(0)), C.c_void_p(z.data_ptr()),
+                                     C.c_int64(z.stride(0)), C.c_void_p(w.data_ptr()), C.c_void_p(out.data_ptr()),
+                                     C.c_int64(out.stride(0)), x.shape[0], heads, D, C.c_float(eps), dtype_code(x.dtype),
+                                     _stream()), "rf_rmsnorm_gated")
+    return out
+
+
+def sigmoid_gate(a: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """In place ``a *= sigmoid(g)``; both ``[T, C]`` row views (pitches may differ)."""
+    N.check(N.lib().rf_sigmoid_gate(C.c_void_p(a.data_ptr()), C.c_int64(a.stride(0)), C.c_void_p(g.data_ptr()),
+                                    C.c_int64(g.stride(0)), a.shape[0], a.shape[1], dtype_code(a.dtype), _stream()),
+            "rf_sigmoid_gate")
+    return a
+
+
+def cumsum(x: torch.Tensor) -> torch.Tensor:
+    """Inclusive cumulative sum over the last dim (fp32, contiguous)."""
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    y = torch.empty_like(x)
+    n = x.shape[-1]
+    N.check(N.lib().rf_cumsum_f32(C.c_void_p(x.data_ptr()), C.c_void_p(y.data_ptr()), x.numel() // n, n, _stream()),
+            "rf_cumsum_f32")
+    return y
+
+
+def unit_tril_inv(m: torch.Tensor) -> torch.Tensor:
+    """``(I - tril(m, -1))^-1`` for a batch of ``[n, n]`` fp32 blocks, ``n <= 64``."""
+    assert m.dtype == torch.float32 and m.is_contiguous() and m.shape[-1] == m.shape[-2]
+    out = torch.empty_like(m)
+    n = m.shape[-1]
+    N.check(N.lib().rf_unit_tril_inv_f32(C.c_void_p(m.data_ptr()), C.c_void_p(out.data_ptr()), m.numel() // (n * n), n,
+                                         _stream()), "rf_unit_tril_inv_f32")
+    return out
+
+
+# ----------------------------------------------------------------------------- mixture of experts
+def moe_select(logits: torch.Tensor, k: int, *, bias: Optional[torch.Tensor] = None, score_fn: str = "sigmoid",
+               norm_topk: bool = True, scale: float = 1.0, dense: bool = False):
+    """Router top-k.  Returns ``(ids [T,k] int32, weights [T,k] fp32)`` and, with ``dense=True``, also the
+    ``[T, E]`` matrix of routing weights (zero for unselected experts) in the logits' dtype."""
+    T, E = logits.shape
+    ids = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    dw = torch.empty((T, E), dtype=logits.dtype, device=logits.device) if dense else None
+    if bias is not None:
+        assert bias.dtype == torch.float32
+    N.check(N.lib().rf_moe_select(C.c_void_p(logits.data_ptr()), C.c_int64(logits.stride(0)), C.c_void_p(_ptr(bias)), T, E, k,
+                                  {"sigmoid": 0, "softmax": 1}[score_fn], int(norm_topk), C.c_float(scale),
+                                  C.c_void_p(ids.data_ptr()), C.c_void_p(w.data_ptr()), C.c_void_p(_ptr(dw)),
+                                  C.c_int64(dw.stride(0) if dense else 0), dtype_code(logits.dtype), _stream()),
+            "rf_moe_select")
+    return (ids, w, dw) if dense else (ids, w)
+
+
+def moe_scale_blocks(h: torch.Tensor, dense_w: torch.Tensor, E: int, I: int) -> torch.Tensor:
+    """In place: expert block ``e`` (width ``I``) of every row of ``h`` times ``dense_w[:, e]``."""
+    N.check(N.lib().rf_moe_scale_blocks(C.c_void_p(h.data_ptr()), C.c_int64(h.stride(0)), C.c_void_p(dense_w.data_ptr()),
+                                        C.c_int64(dense_w.stride(0)), h.shape[0], E, I, dtype_code(h.dtype), _stream()),
+            "rf_moe_scale_blocks")
+    return h

@@ -14,6 +14,7 @@ This is the B200 counterpart of the reference's shared causal-decoder runtime
 from __future__ import annotations
 
 import ctypes as C
+import os
 import math
 from typing import Callable, Dict, List, Optional, Sequence
 
@@ -65,6 +66,7 @@ def quantize_per_channel(w: torch.Tensor, dtype=torch.float16):
     """Symmetric per-output-channel int8 (reference semantics: ``quant/_common.py:10-41``)."""
     amax = w.float().abs().amax(dim=1).clamp(min=1e-8)
     scale = (amax / 127.0).to(dtype)
+    scale = torch.where(scale > 0, scale, torch.ones_like(scale))     # all-zero rows (padding): q = 0, scale = 1
     q = torch.round(w.float() / scale.float()[:, None]).clamp(-127, 127).to(torch.int8)
     return q, scale
 
@@ -105,6 +107,20 @@ class DecoderEngine:
         sc.tp_world, sc.tp_rank = W, R
         sc.weights_int8 = 1 if quant == "w8a16" else 0
         sc.decode_gemv_max_m = decode_gemv_max_m
+        sc.attn_gate = int(cfg.attn_gate)
+        # linear weights live in the tile-major layout (contiguous 16 KB blocks): see ops.kernels.pack_weight
+        self.packed = os.environ.get("RF_PACKED_WEIGHTS", "1") != "0" and decode_gemv_max_m == 0
+        sc.weights_packed = int(self.packed)
+        # hybrid decoders: which layers own KV pages, and the local Gated-DeltaNet geometry
+        self.attn_layers = [l for l in range(cfg.num_layers) if not cfg.is_linear(l)]
+        self.kv_index = {l: i for i, l in enumerate(self.attn_layers)}
+        self.gdn_layers = [l for l in range(cfg.num_layers) if cfg.is_linear(l)]
+        if self.gdn_layers:
+            if cfg.gdn_heads_k % W or cfg.gdn_heads_v % W:
+                raise RPUBackendError(f"{cfg.name}: linear-attention heads do not split over {W} ranks")
+            self.gdn_Hk, self.gdn_Hv = cfg.gdn_heads_k // W, cfg.gdn_heads_v // W
+            sc.gdn_Hk, sc.gdn_Hv, sc.gdn_Dk, sc.gdn_Dv, sc.gdn_conv_k = (self.gdn_Hk, self.gdn_Hv, cfg.gdn_dk,
+                                                                        cfg.gdn_dv, cfg.gdn_conv)
         h = lib.rf_stack_create(C.byref(sc))
         if h < 0:
             N.check(-1, "rf_stack_create")
@@ -112,9 +128,17 @@ class DecoderEngine:
 
         # ---- KV cache: a PagedKV (or RPUCache) object; replaceable through bind_cache()
         from .kv_cache import PagedKV
-        self.cache = kv_cache if kv_cache is not None else PagedKV(cfg.num_layers, max_batch, max_seq_len, self.Hkv,
-                                                                     hd, device=self.device, dtype=dtype)
+        self.cache = kv_cache if kv_cache is not None else PagedKV(len(self.attn_layers), max_batch, max_seq_len,
+                                                                     self.Hkv, hd, device=self.device, dtype=dtype)
         self._check_cache(self.cache)
+        # recurrent + conv state of the linear-attention layers, one slot per sequence of the batch
+        self.gdn_conv_state: Dict[int, torch.Tensor] = {}
+        self.gdn_rec_state: Dict[int, torch.Tensor] = {}
+        for l in self.gdn_layers:
+            conv_dim = 2 * self.gdn_Hk * cfg.gdn_dk + self.gdn_Hv * cfg.gdn_dv
+            self.gdn_conv_state[l] = torch.zeros((max_batch, cfg.gdn_conv - 1, conv_dim), dtype=dtype, device=self.device)
+            self.gdn_rec_state[l] = torch.zeros((max_batch, self.gdn_Hv, cfg.gdn_dk, cfg.gdn_dv), dtype=torch.float32,
+                                                device=self.device)
 
         # ---- weights: packed once, kept alive here
         self._keep: List[torch.Tensor] = []
@@ -161,7 +185,16 @@ class DecoderEngine:
         self._keep.append(t)
         return t
 
-    def _lin(self, get: WeightGetter, parts, cols=None):
+    def _pack(self, w: torch.Tensor, sections: int) -> torch.Tensor:
+        if not self.packed:
+            return w
+        if self._keep and self._keep[-1] is w:
+            self._keep.pop()                 # only the packed image stays resident
+        p = K.pack_weight(w, sections)
+        self._keep.append(p)
+        return p
+
+    def _lin(self, get: WeightGetter, parts, cols=None, sections: int = 1):
         """One packed linear: ``parts`` is a list of (tensor name, row slice); the pieces are
         concatenated along the output dim, ``cols`` slices the input dim (row-parallel shards).
         Returns (device weight, device per-channel scale or None).  int8 checkpoints keep their
@@ -169,6 +202,11 @@ class DecoderEngine:
         scale_of = getattr(get, "scale", None)
         ws, ss = [], []
         for name, rows in parts:
+            if name is None:                     # ``rows`` all-zero output rows (alignment padding)
+                ref = ws[0]
+                ws.append(torch.zeros((rows, ref.shape[1]), dtype=ref.dtype, device=ref.device))
+                ss.append(None if ss[0] is None else torch.ones(rows, dtype=ss[0].dtype, device=ss[0].device))
+                continue
             w = get(name)
             sc = scale_of(name) if (scale_of is not None and w.dtype == torch.int8) else None
             w = w[rows]
@@ -183,11 +221,13 @@ class DecoderEngine:
             if self.quant != "w8a16":
                 raise RPUBackendError("int8 weights need quant='w8a16'")
             sc = ss[0] if len(ss) == 1 else torch.cat(ss, 0)
-            return self._dev(w), self._dev(sc.to(self.dtype))
+            sc_d = self._dev(sc.to(self.dtype))
+            return self._pack(self._dev(w), sections), sc_d
         if self.quant == "w8a16":
             q, sc = quantize_per_channel(w.to(self.device), self.dtype)
-            return self._dev(q), self._dev(sc)
-        return self._dev(w), None
+            sc_d = self._dev(sc)
+            return self._pack(self._dev(q), sections), sc_d
+        return self._pack(self._dev(w), sections), None
 
     def _pack_weights(self, get: WeightGetter, kv0: int, kv1: int) -> None:
         cfg, lib = self.cfg, N.lib()
@@ -206,10 +246,21 @@ class DecoderEngine:
                 bq, bk, bv = (get(p + f"self_attn.{n}_proj.bias") for n in "qkv")
                 bqkv = self._dev(torch.cat((bq[qs], bk[ks], bv[ks]), 0))
             lw = N.RfLayerWeights()
-            t_qkv, s_qkv = self._lin(get, [(p + "self_attn.q_proj.weight", qs), (p + "self_attn.k_proj.weight", ks),
-                                           (p + "self_attn.v_proj.weight", ks)])
-            t_o, s_o = self._lin(get, [(p + "self_attn.o_proj.weight", full)], cols=qs)
-            t_gu, s_gu = self._lin(get, [(p + "mlp.gate_proj.weight", isl), (p + "mlp.up_proj.weight", isl)])
+            if cfg.is_linear(l):
+                t_qkv, s_qkv, t_o, s_o = self._pack_gdn(get, l, lw)
+            else:
+                if cfg.attn_gate:
+                    # q_proj rows are [head][query hd | gate hd]: queries first, gates behind K and V
+                    idx = torch.arange(cfg.num_heads * 2 * hd).view(cfg.num_heads, 2, hd)[q0:q1]
+                    q_rows, g_rows = idx[:, 0].reshape(-1), idx[:, 1].reshape(-1)
+                    parts = [(p + "self_attn.q_proj.weight", q_rows), (p + "self_attn.k_proj.weight", ks),
+                             (p + "self_attn.v_proj.weight", ks), (p + "self_attn.q_proj.weight", g_rows)]
+                else:
+                    parts = [(p + "self_attn.q_proj.weight", qs), (p + "self_attn.k_proj.weight", ks),
+                             (p + "self_attn.v_proj.weight", ks)]
+                t_qkv, s_qkv = self._lin(get, parts)
+                t_o, s_o = self._lin(get, [(p + "self_attn.o_proj.weight", full)], cols=qs)
+            t_gu, s_gu = self._lin(get, [(p + "mlp.gate_proj.weight", isl), (p + "mlp.up_proj.weight", isl)], sections=2)
             t_d, s_d = self._lin(get, [(p + "mlp.down_proj.weight", full)], cols=isl)
             lw.wqkv, lw.sqkv, lw.bqkv = ptr(t_qkv), ptr(s_qkv), ptr(bqkv)
             lw.wo, lw.so = ptr(t_o), ptr(s_o)
@@ -217,10 +268,11 @@ class DecoderEngine:
             lw.w_down, lw.s_down = ptr(t_d), ptr(s_d)
             lw.norm1_w = ptr(self._dev(get(p + "input_layernorm.weight")))
             lw.norm2_w = ptr(self._dev(get(p + "post_attention_layernorm.weight")))
-            if cfg.qk_norm:
+            if cfg.qk_norm and not cfg.is_linear(l):
                 lw.q_norm_w = ptr(self._dev(get(p + "self_attn.q_norm.weight")))
                 lw.k_norm_w = ptr(self._dev(get(p + "self_attn.k_norm.weight")))
-            lw.k_pool, lw.v_pool = self.cache.layer_ptrs(l)
+            if not cfg.is_linear(l):
+                lw.k_pool, lw.v_pool = self.cache.layer_ptrs(self.kv_index[l])
             N.check(lib.rf_stack_set_layer(self.handle, l, C.byref(lw)), "rf_stack_set_layer")
         emb = get("model.embed_tokens.weight")
         self.embed_scale_rows = None
@@ -239,6 +291,41 @@ class DecoderEngine:
                                       C.c_void_p(t_lm.data_ptr()), C.c_void_p(ptr(s_lm))), "rf_stack_set_head")
         del emb
         torch.cuda.empty_cache()
+
+    def _pack_gdn(self, get: WeightGetter, l: int, lw) -> tuple:
+        """Gated-DeltaNet layer: fused input projection ``[q | k | v | z | b | a]`` (b and a padded to 8
+        rows), depthwise conv taps, decay parameters, gated-norm weight, state pointers."""
+        cfg = self.cfg
+        W, R = self.tp.world, self.tp.rank
+        p = f"model.layers.{l}.linear_attn."
+        Dk, Dv = cfg.gdn_dk, cfg.gdn_dv
+        k0, k1 = shard_range(cfg.gdn_heads_k, W, R)
+        v0, v1 = shard_range(cfg.gdn_heads_v, W, R)
+        key_dim = cfg.gdn_heads_k * Dk
+        q_rows = slice(k0 * Dk, k1 * Dk)
+        k_rows = slice(key_dim + k0 * Dk, key_dim + k1 * Dk)
+        v_rows = slice(2 * key_dim + v0 * Dv, 2 * key_dim + v1 * Dv)
+        z_rows, h_rows = slice(v0 * Dv, v1 * Dv), slice(v0, v1)
+        pad = (self.gdn_Hv + 7) // 8 * 8 - self.gdn_Hv
+        qkv = p + "in_proj_qkv.weight"
+        parts = [(qkv, q_rows), (qkv, k_rows), (qkv, v_rows), (p + "in_proj_z.weight", z_rows), (p + "in_proj_b.weight", h_rows)]
+        parts += [(None, pad)] if pad else []
+        parts += [(p + "in_proj_a.weight", h_rows)] + ([(None, pad)] if pad else [])
+        t_in, s_in = self._lin(get, parts)
+        t_o, s_o = self._lin(get, [(p + "out_proj.weight", slice(None))], cols=z_rows)
+        conv = get(p + "conv1d.weight")
+        conv = conv.reshape(conv.shape[0], -1)
+        conv = torch.cat((conv[q_rows], conv[k_rows], conv[v_rows]), 0)
+        f32 = lambda t: t.to(self.device, torch.float32).contiguous()
+        a_log, dtb = f32(get(p + "A_log")[h_rows]), f32(get(p + "dt_bias")[h_rows])
+        self._keep += [a_log, dtb]
+        lw.mixer = 1
+        lw.gdn_conv_w = self._dev(conv).data_ptr()
+        lw.gdn_A_log, lw.gdn_dt_bias = a_log.data_ptr(), dtb.data_ptr()
+        lw.gdn_norm_w = self._dev(get(p + "norm.weight")).data_ptr()
+        lw.gdn_conv_state = self.gdn_conv_state[l].data_ptr()
+        lw.gdn_rec_state = self.gdn_rec_state[l].data_ptr()
+        return t_in, s_in, t_o, s_o
 
     def advance_lengths(self, n_steps: int) -> None:
         """Account for ``n_steps`` graph replays issued outside :meth:`decode`."""
@@ -262,7 +349,7 @@ class DecoderEngine:
             raise RPUBackendError(f"peer wait timed out: {self.comm.status.tolist()[:4]}")
 
     def _check_cache(self, cache) -> None:
-        want = (self.cfg.num_layers, self.Hkv, self.cfg.head_dim)
+        want = (len(self.attn_layers), self.Hkv, self.cfg.head_dim)
         got = (cache.num_layers, cache.num_kv_heads, cache.head_dim)
         if want != got or cache.dtype != self.dtype or cache.batch_size > self.max_batch:
             raise RPUBackendError(f"KV cache geometry {got}/{cache.dtype}/batch {cache.batch_size} does not match the "
@@ -275,9 +362,16 @@ class DecoderEngine:
             return
         self._check_cache(cache)
         lib = N.lib()
-        for l in range(self.cfg.num_layers):
-            k, v = cache.layer_ptrs(l)
+        for l in self.attn_layers:
+            k, v = cache.layer_ptrs(self.kv_index[l])
             N.check(lib.rf_stack_set_kv(self.handle, l, C.c_void_p(k), C.c_void_p(v)), "rf_stack_set_kv")
+        states = getattr(cache, "linear_states", None)
+        if self.gdn_layers and states is not None:
+            for i, l in enumerate(self.gdn_layers):
+                conv, rec = states(i)
+                N.check(lib.rf_stack_set_state(self.handle, l, C.c_void_p(conv.data_ptr()), C.c_void_p(rec.data_ptr())),
+                        "rf_stack_set_state")
+                self.gdn_conv_state[l], self.gdn_rec_state[l] = conv, rec
         self.cache = cache
         self.graphs.clear()
 
@@ -381,7 +475,7 @@ class DecoderEngine:
                        deepstack=None) -> None:
         T = sum(c[2] for c in ch)
         n = len(ch)
-        meta = torch.empty((5, max(n, 1)), dtype=torch.int32)
+        meta = torch.empty((6, max(n, 1)), dtype=torch.int32)
         tokmeta = torch.empty((2, T), dtype=torch.int32)
         ids_host = torch.empty(T, dtype=torch.int32)
         o = 0
@@ -393,6 +487,7 @@ class DecoderEngine:
             meta[0, j], meta[1, j], meta[2, j] = o, cnt, base + off + cnt   # q_start, q_len, kv_len
             meta[3, j] = s
             meta[4, j] = o + cnt - 1
+            meta[5, j] = 1 if (base + off) == 0 else 0        # starts from an empty recurrent state
             tokmeta[0, o:o + cnt] = s
             tokmeta[1, o:o + cnt] = torch.arange(base + off, base + off + cnt, dtype=torch.int32)
             ids_host[o:o + cnt] = prompts[s][off:off + cnt].to("cpu", torch.int32)
@@ -439,6 +534,9 @@ class DecoderEngine:
         f.max_q_len = max(c[2] for c in ch)
         f.max_kv_len = max(starts[c[0]] + c[1] + c[2] for c in ch)
         f.page_table, f.pt_stride, f.pool_pages = pt.data_ptr(), pt.stride(0), self.cache.num_pages
+        if self.gdn_layers:
+            slot_d, fresh_d = meta_d[3].contiguous(), meta_d[5].contiguous()
+            f.state_slot, f.state_fresh = slot_d.data_ptr(), fresh_d.data_ptr()
         if ds_rows:
             ds_rows_d = torch.cat(ds_rows).to(torch.int32).pin_memory().to(self.device, non_blocking=True)
             ds_layers = [torch.cat(parts).contiguous() for parts in ds_feats]

@@ -51,6 +51,8 @@ class StackSpec:
     tp_rank: int = 0
     weights_int8: bool = False
     decode_gemv_max_m: int = 0
+    packed: bool = True        # linear weights in the tile-major layout of ops.kernels.pack_weight
+    attn_gate: bool = False
 
 
 LAYER_FIELDS = ("norm1_w", "norm1_b", "wqkv", "bqkv", "sqkv", "q_norm_w", "k_norm_w", "wo", "bo", "so", "norm2_w",
@@ -98,6 +100,7 @@ class NativeStack:
         sc.vocab_local, sc.vocab_offset = spec.vocab_local, spec.vocab_offset
         sc.tp_world, sc.tp_rank = spec.tp_world, spec.tp_rank
         sc.weights_int8, sc.decode_gemv_max_m = int(spec.weights_int8), spec.decode_gemv_max_m
+        sc.weights_packed, sc.attn_gate = int(spec.packed), int(spec.attn_gate)
         h = lib.rf_stack_create(C.byref(sc))
         if h < 0:
             N.check(-1, "rf_stack_create")
@@ -106,10 +109,16 @@ class NativeStack:
         self.cache = kv_cache
         for l, lw in enumerate(layer_weights):
             w = N.RfLayerWeights()
+            glu = spec.mlp in ("swiglu", "geglu_tanh")
             for f in LAYER_FIELDS:
                 t = lw.get(f)
                 if t is not None:
-                    setattr(w, f, self._dev(t).data_ptr())
+                    d = self._dev(t)
+                    if spec.packed and f in ("wqkv", "wo", "w_up", "w_down"):
+                        self._keep.pop()
+                        d = K.pack_weight(d, 2 if (f == "w_up" and glu) else 1)
+                        self._keep.append(d)
+                    setattr(w, f, d.data_ptr())
             if spec.paged_kv:
                 if kv_cache is None:
                     raise RPUBackendError("a paged-KV stack needs a kv_cache")
@@ -119,6 +128,10 @@ class NativeStack:
             fw = self._dev(final_norm_w)
             fb = self._dev(final_norm_b) if final_norm_b is not None else None
             lm = self._dev(lm_head) if lm_head is not None else None
+            if lm is not None and spec.packed:
+                self._keep.pop()
+                lm = K.pack_weight(lm)
+                self._keep.append(lm)
             ls = self._dev(lm_head_scale) if lm_head_scale is not None else None
             N.check(lib.rf_stack_set_head(self.handle, C.c_void_p(fw.data_ptr()),
                                           C.c_void_p(None if fb is None else fb.data_ptr()),

@@ -413,7 +413,8 @@ def test_engine_w8a16_matches_dequantised_oracle():
             deq[k] = dequantize_linear_per_channel(qq, s)
         else:
             deq[k] = v
-    deq["lm_head.weight"] = dequantize_linear_per_channel(*quantize_linear_per_channel(sd["model.embed_tokens.weight"]))
+    if "lm_head.weight" not in sd:            # tied embeddings: the head is the quantised embedding matrix
+        deq["lm_head.weight"] = dequantize_linear_per_channel(*quantize_linear_per_channel(sd["model.embed_tokens.weight"]))
     oracle = TorchDecoder(cfg, deq, dtype=torch.float32, device="cuda")
     eng = DecoderEngine(cfg, lambda n: sd[n] if n in sd else sd["model.embed_tokens.weight"], dtype=torch.float16,
                         max_batch=2, max_seq_len=96, quant="w8a16")
@@ -428,3 +429,36 @@ def test_engine_w8a16_matches_dequantised_oracle():
     assert toks.shape == (2, 6)
     eng.check_status()
     eng.close()
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M,N,K,swap,splits", [(16, 384, 1024, -1, 0), (64, 1000, 2048, 1, 4), (9, 200, 520, 1, 1),
+                                               (300, 640, 1024, 0, 1), (1024, 512, 2048, 0, 1), (700, 130, 264, 0, 1)])
+def test_gemm_packed_weights(dt, M, N, K, swap, splits, status):
+    """Tile-major (bulk-copy) weight layout gives the same result as row-major weights."""
+    from rhinoforge_b200.ops import kernels as K_
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(dt)
+    b = torch.randn(N, device="cuda").to(dt)
+    r = torch.randn(M, N, device="cuda").to(dt)
+    wp = K_.pack_weight(w)
+    y = K_.gemm(x, wp, packed_shape=(N, K), bias=b, residual=r, status=status, force_swap=swap, force_splits=splits)
+    ref = x.float() @ w.float().t() + b.float() + r.float()
+    _close(y, ref, dt, scale=max(1.0, ref.abs().max().item()))
+
+
+@pytest.mark.parametrize("M,swap", [(24, 1), (300, 0)])
+def test_gemm_packed_dual_and_int8(M, swap, status):
+    from rhinoforge_b200.ops import kernels as K_
+    dt, N, K = torch.float16, 200, 1024                    # N not a multiple of 128: sections are padded separately
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    w = (torch.randn(2 * N, K, device="cuda") * 0.05).to(dt)
+    y = K_.gemm(x, K_.pack_weight(w, 2), packed_shape=(2 * N, K), act="silu_mul", dual=True, status=status, force_swap=swap)
+    z = x.float() @ w.float().t()
+    _close(y, torch.nn.functional.silu(z[:, :N]) * z[:, N:], dt, scale=2.0)
+    q = torch.randint(-127, 128, (2 * N, K), device="cuda", dtype=torch.int8)
+    sc = (torch.rand(2 * N, device="cuda") * 0.002 + 0.0005).to(dt)
+    y = K_.gemm(x, K_.pack_weight(q, 2), packed_shape=(2 * N, K), scale=sc, act="silu_mul", dual=True, status=status,
+                force_swap=swap)
+    z = (x.float() @ q.float().t()) * sc.float()
+    _close(y, torch.nn.functional.silu(z[:, :N]) * z[:, N:], dt, scale=2.0)

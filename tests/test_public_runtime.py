@@ -158,8 +158,9 @@ def test_native_struct_layouts_match_ctypes():
     if not N.available():
         pytest.skip("native library not built")
     lib = N.lib()
-    sizes = (C.c_int32 * 8)()
+    sizes = (C.c_int32 * 16)()
     lib.rf_struct_sizes(sizes)
     got = [C.sizeof(t) for t in (N.RfGemm, N.RfRopeKv, N.RfAttn, N.RfStackConfig, N.RfLayerWeights, N.RfStackComm,
                                  N.RfStackForward)]
     assert list(sizes)[:7] == got
+    assert list(sizes)[8:10] == [C.sizeof(N.RfConv1d), C.sizeof(N.RfGdn)]

@@ -1,0 +1,198 @@
+"""Gated-DeltaNet kernels and the Qwen3.5 hybrid decoder against plain PyTorch / Hugging Face fp32."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+DT = [torch.float16, torch.bfloat16]
+
+
+def _rel(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).abs().max() / (b.abs().max() + 1e-6))
+
+
+@pytest.mark.parametrize("dt", DT)
+def test_causal_conv1d_varlen_and_decode(dt):
+    from rhinoforge_b200.ops import kernels as K
+    torch.manual_seed(0)
+    Cc, lens = 264, [5, 70, 1, 2]
+    T = sum(lens)
+    x = torch.randn(T, Cc + 24, device="cuda").to(dt)          # wider pitch than C
+    w = (torch.randn(Cc, 4, device="cuda") * 0.5).to(dt)
+    state = torch.randn(6, 3, Cc, device="cuda").to(dt)
+    slot = torch.tensor([4, 0, 2, 5], dtype=torch.int32, device="cuda")
+    ql = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    qs = (torch.cumsum(ql, 0) - ql).to(torch.int32)
+    st0 = state.clone()
+    y = K.causal_conv1d(x[:, :Cc], w, state, q_start=qs, q_len=ql, max_q_len=max(lens), slot=slot)
+    o = 0
+    for i, L in enumerate(lens):
+        full = torch.cat((st0[int(slot[i])].float(), x[o:o + L, :Cc].float()), 0)          # [3 + L, C]
+        ref = F.silu(F.conv1d(full.t()[None], w.float()[:, None], groups=Cc)[0].t())
+        assert _rel(y[o:o + L], ref) < (4e-3 if dt == torch.float16 else 2e-2)
+        assert torch.equal(state[int(slot[i])].float(), full[-3:].to(dt).float())
+        o += L
+    # decode: one token per sequence, slot = sequence index
+    xd = torch.randn(3, Cc, device="cuda").to(dt)
+    st1 = state[:3].clone()
+    yd = K.causal_conv1d(xd, w, state)
+    full = torch.cat((st1.float(), xd.float()[:, None]), 1)                                  # [3, 4, C]
+    ref = F.silu((full * w.float().t()[None]).sum(1))
+    assert _rel(yd, ref) < (4e-3 if dt == torch.float16 else 2e-2)
+    assert torch.equal(state[:3].float(), full[:, 1:].to(dt).float())
+
+
+def _delta_rule_ref(q, k, v, b, a, A_log, dt_bias, S):
+    """q,k [n,Hk,Dk], v [n,Hv,Dv], b,a [n,Hv], S [Hv,Dk,Dv] -> (o [n,Hv,Dv], S)."""
+    n, Hk, Dk = q.shape
+    Hv = v.shape[1]
+    rep = Hv // Hk
+    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) / Dk ** 0.5
+    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
+    beta = torch.sigmoid(b)
+    g = -torch.exp(A_log) * F.softplus(a + dt_bias)
+    out = []
+    for t in range(n):
+        S = S * torch.exp(g[t])[:, None, None]
+        kv = (S * k[t][:, :, None]).sum(1)
+        d = (v[t] - kv) * beta[t][:, None]
+        S = S + k[t][:, :, None] * d[:, None, :]
+        out.append((S * q[t][:, :, None]).sum(1))
+    return torch.stack(out), S
+
+
+@pytest.mark.parametrize("dt", DT)
+def test_gdn_recurrent_prefill_then_decode(dt):
+    from rhinoforge_b200.ops import kernels as K
+    torch.manual_seed(1)
+    Hk, Hv, Dk, Dv = 2, 4, 128, 64
+    lens = [37, 3]
+    T = sum(lens)
+    width = 2 * Hk * Dk + Hv * Dv
+    qkv = torch.randn(T, width, device="cuda").to(dt)
+    ba = torch.randn(T, 16, device="cuda").to(dt)
+    A_log = torch.log(torch.rand(Hv, device="cuda") * 4 + 0.5)
+    dtb = torch.rand(Hv, device="cuda")
+    state = torch.randn(3, Hv, Dk, Dv, device="cuda") * 0.1
+    st0 = state.clone()
+    slot = torch.tensor([2, 0], dtype=torch.int32, device="cuda")
+    fresh = torch.tensor([1, 0], dtype=torch.int32, device="cuda")
+    ql = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    qs = (torch.cumsum(ql, 0) - ql).to(torch.int32)
+    out = K.gdn_recurrent(qkv, ba[:, :8], ba[:, 8:], state, A_log, dtb, Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, q_start=qs, q_len=ql,
+                          slot=slot, fresh=fresh)
+    tol = 5e-3 if dt == torch.float16 else 3e-2
+    o = 0
+    for i, L in enumerate(lens):
+        r = qkv[o:o + L].float()
+        q, k = r[:, :Hk * Dk].view(L, Hk, Dk), r[:, Hk * Dk:2 * Hk * Dk].view(L, Hk, Dk)
+        v = r[:, 2 * Hk * Dk:].view(L, Hv, Dv)
+        S0 = torch.zeros_like(st0[0]) if int(fresh[i]) else st0[int(slot[i])]
+        ref, S = _delta_rule_ref(q, k, v, ba[o:o + L, :Hv].float(), ba[o:o + L, 8:8 + Hv].float(), A_log, dtb, S0)
+        assert _rel(out[o:o + L].view(L, Hv, Dv), ref) < tol
+        assert _rel(state[int(slot[i])], S) < 1e-3
+        o += L
+    assert torch.equal(state[1], st0[1])          # untouched slot
+    # decode step for two sequences, slots = sequence index
+    qd = torch.randn(2, width, device="cuda").to(dt)
+    bad = torch.randn(2, 16, device="cuda").to(dt)
+    st1 = state.clone()
+    od = K.gdn_recurrent(qd, bad[:, :8], bad[:, 8:], state, A_log, dtb, Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv)
+    for s in range(2):
+        r = qd[s:s + 1].float()
+        ref, S = _delta_rule_ref(r[:, :Hk * Dk].view(1, Hk, Dk), r[:, Hk * Dk:2 * Hk * Dk].view(1, Hk, Dk),
+                                 r[:, 2 * Hk * Dk:].view(1, Hv, Dv), bad[s:s + 1, :Hv].float(), bad[s:s + 1, 8:8 + Hv].float(),
+                                 A_log, dtb, st1[s])
+        assert _rel(od[s].view(Hv, Dv), ref[0]) < tol
+        assert _rel(state[s], S) < 1e-3
+
+
+def test_small_gdn_helpers():
+    from rhinoforge_b200.ops import kernels as K
+    torch.manual_seed(2)
+    x = torch.randn(7, 4, 128, device="cuda", dtype=torch.float16)
+    zfull = torch.randn(7, 4 * 128 + 64, device="cuda", dtype=torch.float16)
+    w = (1 + 0.1 * torch.randn(128, device="cuda")).half()
+    y = K.rmsnorm_gated(x.view(7, -1), zfull[:, 64:], w, 4, 1e-6)
+    xf = x.float()
+    n = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)).half().float()
+    ref = w.float() * n * F.silu(zfull[:, 64:].float().view(7, 4, 128))
+    assert _rel(y.view(7, 4, 128), ref) < 4e-3
+    a = torch.randn(9, 256, device="cuda", dtype=torch.float16)
+    g = torch.randn(9, 304, device="cuda", dtype=torch.float16)
+    want = a.float() * torch.sigmoid(g[:, 40:296].float())
+    K.sigmoid_gate(a, g[:, 40:296])
+    assert _rel(a, want) < 2e-3
+    c = torch.randn(5, 3, 64, device="cuda")
+    assert torch.allclose(K.cumsum(c), c.cumsum(-1), atol=1e-5)
+    c2 = torch.randn(6, 100, device="cuda")
+    assert torch.allclose(K.cumsum(c2), c2.cumsum(-1), atol=1e-4)
+    m = torch.randn(4, 64, 64, device="cuda") * 0.2
+    inv = K.unit_tril_inv(m)
+    eye = torch.eye(64, device="cuda")
+    assert torch.allclose((eye - m.tril(-1)) @ inv, eye.expand(4, 64, 64), atol=1e-4)
+
+
+def _tiny_hf():
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5TextConfig
+    from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5ForCausalLM
+    c = Qwen3_5TextConfig(
+        vocab_size=304, hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=2,
+        num_key_value_heads=1, head_dim=64, linear_conv_kernel_dim=4, linear_key_head_dim=128,
+        linear_value_head_dim=128, linear_num_key_heads=2, linear_num_value_heads=4,
+        layer_types=["linear_attention", "linear_attention", "full_attention", "linear_attention"],
+        rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.25,
+                         "mrope_section": [3, 3, 2], "mrope_interleaved": True},
+        max_position_embeddings=512, tie_word_embeddings=False)
+    c._attn_implementation = "eager"
+    m = Qwen3_5ForCausalLM(c).float().eval()
+    g = torch.Generator().manual_seed(3)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn(p.shape, generator=g) * 0.06)
+            elif n.endswith("A_log"):
+                p.copy_(torch.log(torch.rand(p.shape, generator=g) * 4 + 0.5))
+            elif n.endswith("dt_bias"):
+                p.copy_(torch.rand(p.shape, generator=g))
+            elif n.endswith("linear_attn.norm.weight"):
+                p.copy_(1 + 0.1 * torch.randn(p.shape, generator=g))
+            else:
+                p.copy_(0.1 * torch.randn(p.shape, generator=g))
+    return c, m
+
+
+def test_qwen3_5_engine_matches_hf():
+    from rhinoforge_b200.models.decoder import DecoderConfig
+    from rhinoforge_b200.runtime.engine import DecoderEngine
+    c, ref = _tiny_hf()
+    ref = ref.cuda()              # on a GPU box the Hugging Face module picks device kernels: keep it on the device
+    sd = ref.state_dict()
+    cfg = DecoderConfig.from_hf(c)
+    eng = DecoderEngine(cfg, lambda n: sd[n], max_batch=2, max_seq_len=128, max_prefill_tokens=32)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 304, (L,), generator=g) for L in (45, 9)]       # 45 > 32: chunked prefill carries state
+    steps = 5
+    want_tok, want_first = [], []
+    with torch.no_grad():
+        for p in prompts:
+            o = ref(input_ids=p[None].cuda(), use_cache=True)
+            want_first.append(o.logits[0, -1])
+            toks = [int(o.logits[0, -1].argmax())]
+            past = o.past_key_values
+            for _ in range(steps - 1):
+                o = ref(input_ids=torch.tensor([[toks[-1]]], device="cuda"), past_key_values=past, use_cache=True)
+                toks.append(int(o.logits[0, -1].argmax()))
+            want_tok.append(toks)
+    first, logits = eng.prefill(prompts, return_logits=True)
+    for b in range(2):
+        assert _rel(logits[b], want_first[b]) < 3e-2
+    rest = eng.decode(steps - 1)
+    eng.check_status()
+    for b in range(2):
+        mine = [int(first[b])] + rest[b].tolist()
+        assert mine[0] == want_tok[b][0]
+        assert sum(x == y for x, y in zip(mine, want_tok[b])) >= steps - 1, (mine, want_tok[b])
+    eng.close()
