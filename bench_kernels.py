@@ -1,0 +1,204 @@
+#!/usr/bin/env python
+"""Kernel micro-benchmarks with roofline fractions (device-timed, L2 flushed between iterations).
+
+    python bench_kernels.py gemm --m 64 --n 12288 --k 4096 --dual [--packed] [--int8]
+    python bench_kernels.py attn_prefill --seqs 4 --len 2048 --heads 32 --kv-heads 8 --hd 128
+    python bench_kernels.py attn_decode --seqs 64 --len 1024 --heads 32 --kv-heads 8 --hd 128
+    python bench_kernels.py gdn --seqs 1 --len 1024 --hk 16 --hv 32
+    python bench_kernels.py suite            # the shapes of one Qwen3-8B decode step and prefill chunk
+
+Every line is JSON: the achieved throughput and its fraction of the measured peaks in
+``MEASURED_PEAKS.json`` (copy bandwidth and cuBLAS bf16 throughput measured on this pool; the fallback
+values 6.65 TB/s and 1.59 PFLOP/s are used, and labelled, when the file is absent).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+
+
+def peaks() -> dict:
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.is_file():
+        d = json.loads(f.read_text())
+        return {"hbm_gbs": float(d.get("hbm_gbs", 6650.0)), "tflops": float(d.get("bf16_tflops", 1590.0)), "src": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "src": "fallback"}
+
+
+_flush = None
+
+
+def flush_l2() -> None:
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")      # 2x the 126 MB L2
+    _flush.zero_()
+
+
+def time_us(fn, iters: int = 20, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    return statistics.median(ts)
+
+
+def report(name: str, us: float, *, flops: float = 0.0, bytes_: float = 0.0, **extra) -> dict:
+    pk = peaks()
+    out = {"kernel": name, "us": round(us, 2), **extra}
+    if flops:
+        out["tflops"] = round(flops / us * 1e-6, 1)
+        out[f"frac_of_{pk['src']}_tflops"] = round(flops / us * 1e-6 / pk["tflops"], 3)
+    if bytes_:
+        out["gbs"] = round(bytes_ / us * 1e-3, 1)
+        out[f"frac_of_{pk['src']}_hbm"] = round(bytes_ / us * 1e-3 / pk["hbm_gbs"], 3)
+    print(json.dumps(out), flush=True)
+    return out
+
+
+def bench_gemm(m, n, k, *, dual=False, packed=False, int8=False, dtype=torch.float16, profile=False):
+    from rhinoforge_b200.ops import kernels as K
+    rows = 2 * n if dual else n
+    x = (torch.randn(m, k, device="cuda") * 0.5).to(dtype)
+    if int8:
+        w = torch.randint(-127, 128, (rows, k), device="cuda", dtype=torch.int8)
+        sc = (torch.rand(rows, device="cuda") * 0.004 + 0.001).to(dtype)
+    else:
+        w, sc = (torch.randn(rows, k, device="cuda") * 0.05).to(dtype), None
+    out = torch.empty(m, n, dtype=dtype, device="cuda")
+    kw = dict(out=out, scale=sc, act="silu_mul" if dual else None, dual=dual)
+    if packed:
+        wp = K.pack_weight(w, 2 if dual else 1)
+        fn = lambda: K.gemm(x, wp, packed_shape=(rows, k), **kw)
+    else:
+        fn = lambda: K.gemm(x, w, **kw)
+    if profile:
+        fn(); torch.cuda.synchronize()
+        torch.cuda.profiler.start(); fn(); torch.cuda.synchronize(); torch.cuda.profiler.stop()
+        return None
+    us = time_us(fn)
+    wbytes = rows * k * (1 if int8 else 2)
+    return report("gemm", us, flops=2.0 * m * rows * k, bytes_=wbytes + m * k * 2 + m * n * 2, m=m, n=n, k=k, dual=dual,
+                  packed=packed, int8=int8)
+
+
+def bench_attn_prefill(seqs, length, heads, kv_heads, hd, *, causal=True, dtype=torch.float16, profile=False):
+    from rhinoforge_b200.ops import kernels as K
+    T = seqs * length
+    qkv = (torch.randn(T, (heads + 2 * kv_heads) * hd, device="cuda") * 0.5).to(dtype)
+    out = torch.empty(T, heads * hd, dtype=dtype, device="cuda")
+    ql = torch.full((seqs,), length, dtype=torch.int32, device="cuda")
+    qs = (torch.arange(seqs, dtype=torch.int32, device="cuda") * length).contiguous()
+    q, k, v = qkv[:, :heads * hd], qkv[:, heads * hd:(heads + kv_heads) * hd], qkv[:, (heads + kv_heads) * hd:]
+    fn = lambda: K.attention_prefill(q, out, Hq=heads, Hkv=kv_heads, hd=hd, q_start=qs, q_len=ql, kv_len=ql, max_q_len=length,
+                                     k=k, v=v, kv_start=qs, causal=causal)
+    if profile:
+        fn(); torch.cuda.synchronize()
+        torch.cuda.profiler.start(); fn(); torch.cuda.synchronize(); torch.cuda.profiler.stop()
+        return None
+    us = time_us(fn)
+    flops = 4.0 * seqs * heads * length * length * hd * (0.5 if causal else 1.0)
+    return report("attn_prefill", us, flops=flops, seqs=seqs, len=length, heads=heads, kv_heads=kv_heads, hd=hd, causal=causal)
+
+
+def bench_attn_decode(seqs, length, heads, kv_heads, hd, *, dtype=torch.float16):
+    from rhinoforge_b200.ops import kernels as K
+    from rhinoforge_b200.runtime.kv_cache import PagedKV
+    cache = PagedKV(1, seqs, length + 16, kv_heads, hd, dtype=dtype)
+    cache.reserve_all()
+    cache.kv.normal_(0, 0.5)
+    q = (torch.randn(seqs, heads * hd, device="cuda") * 0.5).to(dtype)
+    out = torch.empty_like(q)
+    kl = torch.full((seqs,), length, dtype=torch.int32, device="cuda")
+    ws = K.attn_decode_scratch(seqs, heads, hd, q.device)
+    fn = lambda: K.attention_decode(q, out, Hq=heads, Hkv=kv_heads, hd=hd, kv_len=kl, max_kv_len=length, k_pool=cache.kv[0, 0],
+                                    v_pool=cache.kv[0, 1], page_table=cache.page_table, ws=ws)
+    us = time_us(fn)
+    r = report("attn_decode", us, bytes_=2.0 * seqs * length * kv_heads * hd * 2, seqs=seqs, len=length, heads=heads,
+               kv_heads=kv_heads, hd=hd)
+    cache.close()
+    return r
+
+
+def bench_gdn(seqs, length, hk, hv, *, dk=128, dv=128, dtype=torch.float16):
+    from rhinoforge_b200.ops import kernels as K
+    T = seqs * length
+    qkv = torch.randn(T, 2 * hk * dk + hv * dv, device="cuda").to(dtype)
+    ba = torch.randn(T, 2 * ((hv + 7) // 8 * 8), device="cuda").to(dtype)
+    half = ba.shape[1] // 2
+    state = torch.zeros(seqs, hv, dk, dv, device="cuda")
+    A, dtb = torch.zeros(hv, device="cuda"), torch.zeros(hv, device="cuda")
+    ql = torch.full((seqs,), length, dtype=torch.int32, device="cuda")
+    qs = (torch.arange(seqs, dtype=torch.int32, device="cuda") * length).contiguous()
+    if length == 1:
+        fn = lambda: K.gdn_recurrent(qkv, ba[:, :half], ba[:, half:], state, A, dtb, Hk=hk, Hv=hv, Dk=dk, Dv=dv)
+    else:
+        fn = lambda: K.gdn_recurrent(qkv, ba[:, :half], ba[:, half:], state, A, dtb, Hk=hk, Hv=hv, Dk=dk, Dv=dv, q_start=qs, q_len=ql)
+    us = time_us(fn, iters=10)
+    return report("gdn_recurrent", us, flops=6.0 * T * hv * dk * dv, bytes_=2.0 * seqs * hv * dk * dv * 4, seqs=seqs, len=length,
+                  hk=hk, hv=hv, us_per_token=round(us / length, 3))
+
+
+def suite() -> None:
+    """Qwen3-8B shapes: the four decode GEMMs at 64 tokens, the same at 2048 tokens, attention at both."""
+    for packed in (False, True):
+        for m in (64, 2048):
+            bench_gemm(m, 6144, 4096, packed=packed)                 # qkv
+            bench_gemm(m, 4096, 4096, packed=packed)                 # o_proj
+            bench_gemm(m, 12288, 4096, dual=True, packed=packed)     # gate/up + SwiGLU
+            bench_gemm(m, 4096, 12288, packed=packed)                # down
+    bench_gemm(64, 151936, 4096, packed=True)                        # lm_head
+    bench_gemm(64, 12288, 4096, dual=True, packed=True, int8=True)
+    bench_attn_decode(64, 1024, 32, 8, 128)
+    bench_attn_prefill(4, 2048, 32, 8, 128)
+    bench_attn_prefill(1, 968, 8, 1, 256, causal=False)              # Pi0.5 prefix
+    bench_attn_prefill(3, 256, 16, 16, 128, causal=False)            # SigLIP (72 padded to 128)
+    bench_gdn(1, 1, 16, 32)
+    bench_gdn(1, 1024, 16, 32)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("what", choices=["gemm", "attn_prefill", "attn_decode", "gdn", "suite"])
+    for name, d in (("m", 64), ("n", 4096), ("k", 4096), ("seqs", 4), ("len", 2048), ("heads", 32), ("kv-heads", 8),
+                    ("hd", 128), ("hk", 16), ("hv", 32)):
+        ap.add_argument(f"--{name}", type=int, default=d)
+    ap.add_argument("--dual", action="store_true")
+    ap.add_argument("--packed", action="store_true")
+    ap.add_argument("--int8", action="store_true")
+    ap.add_argument("--bidirectional", action="store_true")
+    ap.add_argument("--bf16", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="run the kernel once inside cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    a = ap.parse_args()
+    dt = torch.bfloat16 if a.bf16 else torch.float16
+    if a.what == "gemm":
+        bench_gemm(a.m, a.n, a.k, dual=a.dual, packed=a.packed, int8=a.int8, dtype=dt, profile=a.profile)
+    elif a.what == "attn_prefill":
+        bench_attn_prefill(a.seqs, a.len, a.heads, a.kv_heads, a.hd, causal=not a.bidirectional, dtype=dt, profile=a.profile)
+    elif a.what == "attn_decode":
+        bench_attn_decode(a.seqs, a.len, a.heads, a.kv_heads, a.hd, dtype=dt)
+    elif a.what == "gdn":
+        bench_gdn(a.seqs, a.len, a.hk, a.hv, dtype=dt)
+    else:
+        suite()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -339,16 +339,16 @@ class Pi05Engine:
                 out.append(d)
             return out
 
-        common = dict(mlp="geglu_tanh", paged_kv=True, causal=False, max_seqs=max_batch)
+        common = dict(mlp="geglu_tanh", paged_kv=True, causal=False)
         self.prefix_stack = NativeStack(
             StackSpec(layers=v.layers, hidden=v.hidden, heads=v.heads, kv_heads=v.kv_heads, head_dim=v.head_dim,
                       inter=v.inter, norm="rms_gemma", eps=v.eps, rot_dim=v.head_dim,
-                      max_tokens=max_batch * self.max_prefix, **common),
+                      max_tokens=max_batch * self.max_prefix, max_seqs=max_batch, **common),
             layers_of(VLM + "language_model.", v, False), device=device, dtype=dtype, kv_cache=self.cache)
         self.expert_stack = NativeStack(
             StackSpec(layers=e.layers, hidden=e.hidden, heads=e.heads, kv_heads=e.kv_heads, head_dim=e.head_dim,
                       inter=e.inter, norm="adarms", eps=e.eps, rot_dim=e.head_dim, gated_residual=True,
-                      max_tokens=max_batch * cfg.horizon, **common),
+                      max_tokens=max_batch * cfg.horizon, max_seqs=max_batch * cfg.horizon, **common),
             layers_of(EXP, e, True), device=device, dtype=dtype, kv_cache=self.cache)
         inv = 1.0 / (v.rope_theta ** (torch.arange(0, v.head_dim, 2, dtype=torch.float32) / v.head_dim))
         ang = torch.arange(self.max_seq, dtype=torch.float32)[:, None] * inv[None]
@@ -366,10 +366,12 @@ class Pi05Engine:
         self.h = torch.zeros(Bm * n, e.hidden, dtype=dtype, device=dev)
         self.hn = torch.zeros_like(self.h)
         self.s_pos = torch.zeros(Bm * n, **i32)
-        self.s_seq = torch.arange(Bm, **i32).repeat_interleave(n).contiguous()
-        self.s_qstart = (torch.arange(Bm, **i32) * n).contiguous()
-        self.s_qlen = torch.full((Bm,), n, **i32)
-        self.s_kvlen = torch.zeros(Bm, **i32)
+        # Every action row is its own one-query "sequence" for the split-KV decode attention kernel: it sees the
+        # whole prefix plus all action rows of its sample (their K/V are inserted before attention runs), which
+        # is exactly the bidirectional suffix mask, and the KV range is split over many CTAs instead of one.
+        self.s_seq = torch.arange(Bm * n, **i32)
+        self.s_kvlen = torch.zeros(Bm * n, **i32)
+        self.s_pt = torch.zeros((Bm * n, self.cache.pages_per_seq), **i32)
         self.prefix_hidden = torch.zeros(Bm * self.max_prefix, v.hidden, dtype=dtype, device=dev)
 
     # ------------------------------------------------------------------ conditioning schedule
@@ -435,10 +437,9 @@ class Pi05Engine:
         x, h, hn = self.x[:T], self.h[:T], self.hn[:T]
         for s in range(num_steps):
             K.gemm(x, self.in_w, bias=self.in_b, out=h)
-            self.expert_stack.forward(h, q_start=self.s_qstart[:B], q_len=self.s_qlen[:B], kv_len=self.s_kvlen[:B],
-                                      max_q_len=n, max_kv_len=self.max_seq, pos=self.s_pos[:T], cos=self.cos,
-                                      sin=self.sin, seq_of_tok=self.s_seq[:T], cache_pos=self.s_pos[:T],
-                                      page_table=self.cache.page_table, mod=sch["mod"][s], rows_per_mod=T)
+            self.expert_stack.forward(h, decode=True, kv_len=self.s_kvlen[:T], max_kv_len=self.max_seq, pos=self.s_pos[:T],
+                                      cos=self.cos, sin=self.sin, seq_of_tok=self.s_seq[:T], cache_pos=self.s_pos[:T],
+                                      page_table=self.s_pt[:T], mod=sch["mod"][s], rows_per_mod=T)
             K.rmsnorm(h, None, cfg.expert.eps, out=hn, mod=sch["final"][s:s + 1], rows_per_mod=T)
             K.gemm(hn, sch["out_w"], bias=sch["out_b"], residual=x, out=x)        # x <- x + dt * v
 
@@ -448,7 +449,8 @@ class Pi05Engine:
         B, n = noise.shape[0], cfg.horizon
         T = B * n
         pl = torch.tensor(list(prefix_lens), dtype=torch.int32)
-        self.s_kvlen[:B].copy_((pl + n).to(dev), non_blocking=True)
+        self.s_kvlen[:T].copy_((pl + n).repeat_interleave(n).to(dev), non_blocking=True)
+        self.s_pt[:T].copy_(self.cache.page_table[:B].repeat_interleave(n, 0))
         self.s_pos[:T].copy_((pl[:, None] + torch.arange(n, dtype=torch.int32)[None]).flatten().to(dev), non_blocking=True)
         self.x[:T].copy_(noise.reshape(T, -1).to(dev, self.dtype))
         if not use_graph:

@@ -72,6 +72,44 @@ class TPContext:
     def max_float(self, v: float) -> float:
         return max(self.all_gather_object(float(v)))
 
+    # -- host-side liveness ----------------------------------------------------------------------
+    # The fused kernels wait on flags that peers write; a peer that died would make every such wait
+    # run into its time limit.  Ranks therefore publish a heartbeat in the rendezvous store between
+    # steps, and check their peers' heartbeats BEFORE launching the next step: a missing rank is
+    # reported on the host, with no kernel in flight.
+    def _store(self):
+        import torch.distributed as dist
+        return dist.distributed_c10d._get_default_store()
+
+    def heartbeat(self, step: int) -> None:
+        """Publish "this rank has finished step ``step`` and is still alive"."""
+        if self.enabled:
+            self._store().set(f"rf_hb/{self.rank}", str(int(step)))
+
+    def check_peers(self, step: int, timeout_s: float = 5.0) -> None:
+        """Raise unless every rank has published a heartbeat for ``step`` (or later) within ``timeout_s``."""
+        if not self.enabled:
+            return
+        import time
+        from ..runtime.errors import RPUBackendError
+        store, deadline = self._store(), time.monotonic() + timeout_s
+        missing = list(range(self.world))
+        while missing:
+            still = []
+            for r in missing:
+                try:
+                    ok = store.check([f"rf_hb/{r}"]) and int(store.get(f"rf_hb/{r}")) >= step
+                except Exception:  # noqa: BLE001  (store gone: the rank hosting it died)
+                    ok = False
+                if not ok:
+                    still.append(r)
+            missing = still
+            if missing and time.monotonic() > deadline:
+                raise RPUBackendError(f"tensor-parallel rank(s) {missing} published no heartbeat for step {step} within "
+                                      f"{timeout_s:.1f} s; not launching (peer dead or hung)")
+            if missing:
+                time.sleep(0.01)
+
 
 def shard_range(total: int, world: int, rank: int) -> tuple[int, int]:
     """[begin, end) of an even split; ``total`` must divide."""

@@ -583,6 +583,8 @@ class DecoderEngine:
         if B in self.graphs:
             return
         snap = (self.pos.clone(), self.kv_len.clone(), self.ids.clone(), self.step.clone())
+        # recurrent layers are not idempotent: the eager build step must not advance their state
+        gdn_snap = {l: (self.gdn_conv_state[l].clone(), self.gdn_rec_state[l].clone()) for l in self.gdn_layers}
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
@@ -593,6 +595,9 @@ class DecoderEngine:
             self._decode_step(B)
         torch.cuda.synchronize()
         self.pos.copy_(snap[0]); self.kv_len.copy_(snap[1]); self.ids.copy_(snap[2]); self.step.copy_(snap[3])
+        for l, (cv, rc) in gdn_snap.items():
+            self.gdn_conv_state[l].copy_(cv)
+            self.gdn_rec_state[l].copy_(rc)
         self.graphs[B] = g
 
     def decode(self, n_steps: int, *, use_graph: bool = True) -> torch.Tensor:

@@ -164,8 +164,8 @@ class NativeStack:
     def _p(t: Optional[torch.Tensor]):
         return None if t is None else t.data_ptr()
 
-    def forward(self, hidden: torch.Tensor, *, q_start: torch.Tensor, q_len: torch.Tensor, kv_len: torch.Tensor,
-                max_q_len: int, max_kv_len: int, pos: Optional[torch.Tensor] = None,
+    def forward(self, hidden: torch.Tensor, *, kv_len: torch.Tensor, max_kv_len: int,
+                q_start: Optional[torch.Tensor] = None, q_len: Optional[torch.Tensor] = None, max_q_len: int = 1, pos: Optional[torch.Tensor] = None,
                 cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
                 axis_of_freq: Optional[torch.Tensor] = None, decode: bool = False,
                 seq_of_tok: Optional[torch.Tensor] = None, cache_pos: Optional[torch.Tensor] = None,
@@ -183,7 +183,7 @@ class NativeStack:
             f.pos, f.pos_stride = pos.data_ptr(), (1 if pos.dim() == 1 else pos.shape[1])
         f.cos, f.sin, f.axis_of_freq = self._p(cos), self._p(sin), self._p(axis_of_freq)
         f.seq_of_tok, f.cache_pos = self._p(seq_of_tok), self._p(cache_pos)
-        f.num_seqs = q_len.numel()
+        f.num_seqs = kv_len.numel()
         f.q_start, f.q_len, f.kv_len, f.kv_start = self._p(q_start), self._p(q_len), self._p(kv_len), self._p(kv_start)
         f.max_q_len, f.max_kv_len = max_q_len, max_kv_len
         if page_table is not None:
