@@ -42,6 +42,32 @@ def flush_l2() -> None:
     _flush.zero_()
 
 
+def time_graph_us(make_fn, nbuf: int, reps: int = 24) -> float:
+    """Back-to-back in-stream time per launch: ``reps`` launches captured in one CUDA graph, cycling over ``nbuf``
+    operand sets (``make_fn(i)`` returns the launch closure of set ``i``) so that no launch finds its weights in L2."""
+    fns = [make_fn(i) for i in range(nbuf)]
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        for i in range(reps):
+            fns[i % nbuf]()
+    ts = []
+    for _ in range(5):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3 / reps)
+    return statistics.median(ts)
+
+
 def time_us(fn, iters: int = 20, warmup: int = 3) -> float:
     for _ in range(warmup):
         fn()
@@ -71,30 +97,37 @@ def report(name: str, us: float, *, flops: float = 0.0, bytes_: float = 0.0, **e
     return out
 
 
-def bench_gemm(m, n, k, *, dual=False, packed=False, int8=False, dtype=torch.float16, profile=False):
+def bench_gemm(m, n, k, *, dual=False, packed=False, int8=False, dtype=torch.float16, profile=False, splits=0):
+    """In-stream time of one GEMM: launches are chained in a CUDA graph over enough weight copies to defeat L2."""
     from rhinoforge_b200.ops import kernels as K
     rows = 2 * n if dual else n
+    wbytes = rows * k * (1 if int8 else 2)
+    nbuf = 1 if profile else max(1, min(12, -(-(300 << 20) // wbytes)))
     x = (torch.randn(m, k, device="cuda") * 0.5).to(dtype)
-    if int8:
-        w = torch.randint(-127, 128, (rows, k), device="cuda", dtype=torch.int8)
-        sc = (torch.rand(rows, device="cuda") * 0.004 + 0.001).to(dtype)
-    else:
-        w, sc = (torch.randn(rows, k, device="cuda") * 0.05).to(dtype), None
     out = torch.empty(m, n, dtype=dtype, device="cuda")
-    kw = dict(out=out, scale=sc, act="silu_mul" if dual else None, dual=dual)
-    if packed:
-        wp = K.pack_weight(w, 2 if dual else 1)
-        fn = lambda: K.gemm(x, wp, packed_shape=(rows, k), **kw)
-    else:
-        fn = lambda: K.gemm(x, w, **kw)
+    sets = []
+    for _ in range(nbuf):
+        if int8:
+            w = torch.randint(-127, 128, (rows, k), device="cuda", dtype=torch.int8)
+            sc = (torch.rand(rows, device="cuda") * 0.004 + 0.001).to(dtype)
+        else:
+            w, sc = (torch.randn(rows, k, device="cuda") * 0.05).to(dtype), None
+        sets.append((K.pack_weight(w, 2 if dual else 1) if packed else w, sc))
+
+    def make(i):
+        w, sc = sets[i]
+        kw = dict(out=out, scale=sc, act="silu_mul" if dual else None, dual=dual, force_splits=splits)
+        if packed:
+            return lambda: K.gemm(x, w, packed_shape=(rows, k), **kw)
+        return lambda: K.gemm(x, w, **kw)
     if profile:
+        fn = make(0)
         fn(); torch.cuda.synchronize()
         torch.cuda.profiler.start(); fn(); torch.cuda.synchronize(); torch.cuda.profiler.stop()
         return None
-    us = time_us(fn)
-    wbytes = rows * k * (1 if int8 else 2)
+    us = time_graph_us(make, nbuf)
     return report("gemm", us, flops=2.0 * m * rows * k, bytes_=wbytes + m * k * 2 + m * n * 2, m=m, n=n, k=k, dual=dual,
-                  packed=packed, int8=int8)
+                  packed=packed, int8=int8, splits=splits or "auto")
 
 
 def bench_attn_prefill(seqs, length, heads, kv_heads, hd, *, causal=True, dtype=torch.float16, profile=False):
@@ -154,9 +187,20 @@ def bench_gdn(seqs, length, hk, hv, *, dk=128, dv=128, dtype=torch.float16):
                   hk=hk, hv=hv, us_per_token=round(us / length, 3))
 
 
+def sweep() -> None:
+    """Split-K factors around the planner's choice for the Qwen3-8B decode GEMMs and two mid-size GEMMs."""
+    for shape in ((64, 6144, 4096, False), (64, 4096, 4096, False), (64, 12288, 4096, True), (64, 4096, 12288, False),
+                  (1, 4096, 4096, False), (768, 6144, 1152, False), (768, 1152, 4304, False), (968, 2048, 16384, False)):
+        m, n, k, dual = shape
+        for sp in (0, 1, 2, 3, 4, 6, 8):
+            if sp > max(1, (k // 64) // 4):
+                continue
+            bench_gemm(m, n, k, dual=dual, packed=True, splits=sp)
+
+
 def suite() -> None:
     """Qwen3-8B shapes: the four decode GEMMs at 64 tokens, the same at 2048 tokens, attention at both."""
-    for packed in (False, True):
+    for packed in (True,):
         for m in (64, 2048):
             bench_gemm(m, 6144, 4096, packed=packed)                 # qkv
             bench_gemm(m, 4096, 4096, packed=packed)                 # o_proj
@@ -174,10 +218,11 @@ def suite() -> None:
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["gemm", "attn_prefill", "attn_decode", "gdn", "suite"])
+    ap.add_argument("what", choices=["gemm", "attn_prefill", "attn_decode", "gdn", "suite", "sweep"])
     for name, d in (("m", 64), ("n", 4096), ("k", 4096), ("seqs", 4), ("len", 2048), ("heads", 32), ("kv-heads", 8),
                     ("hd", 128), ("hk", 16), ("hv", 32)):
         ap.add_argument(f"--{name}", type=int, default=d)
+    ap.add_argument("--splits", type=int, default=0, help="force the split-K factor (0: planner)")
     ap.add_argument("--dual", action="store_true")
     ap.add_argument("--packed", action="store_true")
     ap.add_argument("--int8", action="store_true")
@@ -188,13 +233,15 @@ def main() -> int:
     a = ap.parse_args()
     dt = torch.bfloat16 if a.bf16 else torch.float16
     if a.what == "gemm":
-        bench_gemm(a.m, a.n, a.k, dual=a.dual, packed=a.packed, int8=a.int8, dtype=dt, profile=a.profile)
+        bench_gemm(a.m, a.n, a.k, dual=a.dual, packed=a.packed, int8=a.int8, dtype=dt, profile=a.profile, splits=a.splits)
     elif a.what == "attn_prefill":
         bench_attn_prefill(a.seqs, a.len, a.heads, a.kv_heads, a.hd, causal=not a.bidirectional, dtype=dt, profile=a.profile)
     elif a.what == "attn_decode":
         bench_attn_decode(a.seqs, a.len, a.heads, a.kv_heads, a.hd, dtype=dt)
     elif a.what == "gdn":
         bench_gdn(a.seqs, a.len, a.hk, a.hv, dtype=dt)
+    elif a.what == "sweep":
+        sweep()
     else:
         suite()
     return 0

@@ -20,6 +20,9 @@
 // SiLU/GELU + multiply launches and llama_reduce_sum (src/ops/rpu_linear.cpp:1047-1544,
 // src/ops/rpu_linear_gemv.cpp, src/core/fused_model_base.cpp:8515-8567,
 // src/core/rpu_runtime_extras.cpp:1035-1092).
+#include <map>
+#include <mutex>
+
 #include "../common/dtype.cuh"
 #include "../common/host_util.h"
 #include "../common/ptx.cuh"
@@ -381,6 +384,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t peer_part[8];
 #pragma unroll
       for (int s = 0; s < 8; ++s) peer_part[s] = dsmem_addr(my_part, (uint32_t)(s < p.splits ? s : 0));
+      if constexpr (!SWAP) {
+        // tokens on the rows: a thread owns one output row, so it takes EIGHT ADJACENT columns per
+        // round (column groups are dealt round-robin to the cluster's CTAs) and stores them as one
+        // 16-byte vector; single interleaved columns would make every store a lone 2-byte sector write
+        for (int g0 = (int)crank * 8; g0 < ncols; g0 += 8 * p.splits) {
+          float ag[8], au[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { ag[j] = 0.f; au[j] = 0.f; }
+          for (int s = 0; s < p.splits; ++s) {
+            float tg[8], tu[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int c = g0 + j;
+              tg[j] = (c < ncols && epi) ? ld_dsmem_f32(peer_part[s] + (uint32_t)(c * kBM + tid) * 4u) : 0.f;
+              tu[j] = (DUAL && c < ncols && epi) ? ld_dsmem_f32(peer_part[s] + (uint32_t)((bn + c) * kBM + tid) * 4u) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { ag[j] += tg[j]; au[j] += tu[j]; }
+          }
+          const int n0 = b0 + g0;
+          if (a_idx < M) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (n0 + j < N) ? finish(a_idx, n0 + j, ag[j], au[j]) : 0.f;
+            if (p.ar_world > 1) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (n0 + j < N) push_partial(a_idx, n0 + j, v[j]);
+            } else if (n0 + 8 <= N && (p.ldo & 7) == 0 && (!resid || (p.ldr & 7) == 0)) {
+              if (resid) {
+                float r8[8];
+                load8(resid + (size_t)a_idx * p.ldr + n0, r8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += r8[j];
+              }
+              store8(out + (size_t)a_idx * p.ldo + n0, v);
+            } else {
+              for (int j = 0; j < 8; ++j) {
+                if (n0 + j < N) {
+                  float r = v[j];
+                  if (resid) r += Num<T>::to_f(resid[(size_t)a_idx * p.ldr + n0 + j]);
+                  out[(size_t)a_idx * p.ldo + n0 + j] = Num<T>::from_f(r);
+                }
+              }
+            }
+          }
+        }
+      } else
       // four columns per round: all remote loads are issued before the first add
       for (int c0 = (int)crank; c0 < ncols; c0 += 4 * p.splits) {
         float pg[4][8], pu[4][8];
@@ -616,7 +667,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const float* rb = reinterpret_cast<const float*>(
           reinterpret_cast<const uint8_t*>(p.ar_recv[p.ar_rank]) + slot_off);
       const int cstep = p.splits > 1 ? p.splits : 1;
-      for (int c = (int)crank; c < ncols; c += cstep) {
+      for (int c = 0; c < ncols; ++c) {
+        // the columns this CTA pushed: single columns (swap) or groups of eight (tokens on rows)
+        if ((SWAP ? c : (c >> 3)) % cstep != (int)crank) continue;
         const int tok = SWAP ? (b0 + c) : a_idx;
         const int n = SWAP ? a_idx : (b0 + c);
         if (tok < M && n < N) {
@@ -656,6 +709,49 @@ struct GemmPlan {
   int sem_count;
 };
 
+// How many clusters of `cluster_z` CTAs with `smem` bytes each can be resident at once.  Cluster
+// placement is per GPC, so this is not simply SMs * CTAs-per-SM / cluster_z; the answer decides whether a
+// split-K grid runs as one wave or spills into a second one.  Queried once per (cluster size, smem) and
+// cached; the fp16 swap kernel stands in for all instantiations (shared memory is what limits residency).
+static int max_resident_clusters(int cluster_z, size_t smem) {
+  static std::mutex mu;
+  static std::map<std::pair<int, size_t>, int> cache;
+  const size_t key_smem = (smem + 8191) & ~size_t(8191);
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = cache.find({cluster_z, key_smem});
+  if (it != cache.end()) return it->second;
+  auto kfn = gemm_tc_kernel<__half, true, false, false>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(8, 8, (unsigned)cluster_z);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = key_smem > 227 * 1024 ? 227 * 1024 : key_smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)cluster_z;
+  cfg.attrs = attr;
+  cfg.numAttrs = cluster_z > 1 ? 1 : 0;
+  int n = 0;
+  int result;
+  if (cluster_z > 1 && cudaOccupancyMaxActiveClusters(&n, kfn, &cfg) == cudaSuccess && n > 0) {
+    result = n;
+  } else {
+    cudaGetLastError();
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kfn, 128, cfg.dynamicSmemBytes) != cudaSuccess || per_sm < 1) {
+      cudaGetLastError();
+      per_sm = cfg.dynamicSmemBytes > 113 * 1024 ? 1 : 2;
+    }
+    result = std::max(1, sm_count() * per_sm / cluster_z);
+  }
+  cache[{cluster_z, key_smem}] = result;
+  return result;
+}
+
 static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   const bool dual = g->dual_offset > 0;
   pl->k_blocks = ceil_div(g->K, kBK);
@@ -681,47 +777,84 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   if (pl->tmem_cols > 512) return fail(RF_ERR_BAD_ARG, "accumulator needs %d TMEM columns", pl->tmem_cols);
 
   const int tiles = pl->grid_x * pl->grid_y;
-  int splits = 1;
-  if (g->force_splits > 0) {
-    splits = g->force_splits;
-  } else {
-    const int target = 2 * sm_count();
-    if (tiles < target) {
-      splits = target / tiles;
-      const int max_by_k = std::max(1, pl->k_blocks / 4);
-      splits = std::min(std::min(splits, max_by_k), 8);
-      if (splits < 1) splits = 1;
-    }
-  }
-  // the two-shot all-reduce epilogue (large M, tensor parallel) works on whole tiles: no split-K there
-  if (g->ar_world > 1 && !swap && g->M > 256) splits = 1;
-  if (splits > 8) splits = 8;  // portable cluster size
-  if (splits > pl->k_blocks) splits = pl->k_blocks;
-  pl->splits = splits;
-  pl->ws_bytes = 0;
-  pl->sem_count = 0;
-
   const int a_tiles = (swap && dual) ? 2 : 1, b_tiles = (!swap && dual) ? 2 : 1;
   int stage_bytes = a_tiles * kATileBytes + b_tiles * pl->bn * kBK * 2;
   if (g->w_int8) stage_bytes += (dual ? 2 : 1) * (swap ? kBM : pl->bn) * kBK;   // int8 staging tiles
   const int ctl_bytes = (int)sizeof(GemmSmemCtl) + 1024 /*alignment slack*/ + 64;
-  // Two CTAs per SM whenever two stages fit in half the shared memory: bytes in flight per SM are
-  // what hides HBM latency, and a second resident CTA keeps a 2x148-CTA grid in a single wave.
-  int stages = (110 * 1024 - ctl_bytes) / stage_bytes;
-  if (stages < 2 || tiles * splits <= sm_count()) stages = (224 * 1024 - ctl_bytes) / stage_bytes;
-  stages = std::min(stages, kMaxStages);
-  stages = std::min(stages, std::max(2, ceil_div(pl->k_blocks, splits)));
+  static const int env_smem_kb = [] { const char* e = getenv("RF_GEMM_SMEM_KB"); return e ? atoi(e) : 0; }();
+
+  // shared-memory plan for a given split count and ring budget
+  auto layout = [&](int S, int budget, int* stages_out, int* part_out) -> size_t {
+    int st = (budget - ctl_bytes) / stage_bytes;
+    st = std::min(st, kMaxStages);
+    st = std::min(st, std::max(2, ceil_div(pl->k_blocks, S)));
+    // the split-K partial ([columns][128] fp32 per accumulator) reuses the stage ring
+    const int part = S > 1 ? pl->bn * (dual ? 2 : 1) * kBM * 4 : 0;
+    *stages_out = st;
+    *part_out = part;
+    return (size_t)round_up(std::max(st * stage_bytes, part), 1024) + ctl_bytes;
+  };
+
+  int splits = 1, budget = 224 * 1024;
+  const bool two_shot = g->ar_world > 1 && !swap && g->M > 256;   // its epilogue works on whole tiles
+  if (g->force_splits > 0) {
+    splits = std::min(std::min(g->force_splits, 8), pl->k_blocks);
+    if (two_shot) splits = 1;
+    int st, part;
+    if (layout(splits, 110 * 1024, &st, &part) && st >= 2 && tiles * splits > sm_count()) budget = 110 * 1024;
+  } else {
+    // Pick (splits, CTAs per SM) by a small cost model over what can actually be resident: a wave of
+    // `clusters` tiles costs its k-blocks at the slower of one CTA's own pace and its share of HBM,
+    // plus a fixed start/finish cost; a grid that does not fit pays for every extra wave.
+    const int max_by_k = std::max(1, pl->k_blocks / 4);
+    const double kblock_bytes = (double)stage_bytes;
+    // per-k-block time floors (microseconds): a CTA's own load/issue latency, its tensor-core time, and
+    // its share of HBM (only the bytes that are not re-reads of another tile's operand) and of L2
+    const double t_free_us = 0.22, hbm_bytes_per_us = 6.0e6, l2_bytes_per_us = 1.5e7, t_fixed_us = 4.0;
+    const double unique_bytes = ((double)g->M + (double)(dual ? 2 : 1) * g->N) * g->K * 2.0;
+    const double hbm_frac = std::min(1.0, unique_bytes / ((double)tiles * kblock_bytes * pl->k_blocks));
+    const double mma_us = 2.0 * kBM * pl->bn * (dual ? 2 : 1) * kBK / 15.2e6;
+    double best = 1e30;
+    for (int b : {224 * 1024, 110 * 1024}) {
+      for (int S = 1; S <= std::min(8, max_by_k); ++S) {
+        if (two_shot && S > 1) break;
+        int st, part;
+        const size_t smem = layout(S, b, &st, &part);
+        if (st < 2 || smem > 227 * 1024) continue;
+        const int clusters = max_resident_clusters(S, smem);
+        const int waves = ceil_div(tiles, clusters);
+        const int active = std::min(tiles, clusters) * S;
+        const int per_sm = std::max(1, ceil_div(active, sm_count()));
+        double t_kb = t_free_us * (st >= 4 ? 1.0 : (st == 3 ? 1.25 : 1.6));
+        t_kb = std::max(t_kb, mma_us * per_sm);
+        t_kb = std::max(t_kb, kblock_bytes * hbm_frac * active / hbm_bytes_per_us);
+        t_kb = std::max(t_kb, kblock_bytes * active / l2_bytes_per_us);
+        const double cost = waves * (ceil_div(pl->k_blocks, S) * t_kb + t_fixed_us + 0.35 * (S - 1));
+        if (cost < best) {
+          best = cost;
+          splits = S;
+          budget = b;
+        }
+      }
+    }
+  }
+  if (env_smem_kb > 0) budget = std::min(224, std::max(48, env_smem_kb)) * 1024;
+  pl->splits = splits;
+  pl->ws_bytes = 0;
+  pl->sem_count = 0;
+  int stages, part_bytes;
+  size_t smem_total = layout(splits, budget, &stages, &part_bytes);
+  if (stages < 2) smem_total = layout(splits, 224 * 1024, &stages, &part_bytes);
   if (stages < 2) return fail(RF_ERR_UNSUPPORTED, "GEMM tile does not fit in shared memory");
-  // the split-K partial ([columns][128] fp32 per accumulator) reuses the stage ring
-  int part_bytes = pl->splits > 1 ? pl->bn * (dual ? 2 : 1) * kBM * 4 : 0;
-  if ((size_t)std::max(stages * stage_bytes, part_bytes) + ctl_bytes > 227 * 1024) {
+  if (smem_total > 227 * 1024) {
     if (g->force_splits > 1) return fail(RF_ERR_UNSUPPORTED, "split-K partial does not fit in shared memory");
     pl->splits = 1;
-    part_bytes = 0;
+    smem_total = layout(1, budget, &stages, &part_bytes);
   }
   pl->stages = stages;
   pl->ctl_offset = round_up(std::max(stages * stage_bytes, part_bytes), 1024);
   pl->smem_bytes = (size_t)pl->ctl_offset + ctl_bytes;
+  (void)smem_total;
   return RF_OK;
 }
 

@@ -122,7 +122,7 @@ def test_environment_inventory_matches_sources():
     pattern = re.compile(r"[\"']((?:RPU|RF|QWEN3|LKN)_[A-Z0-9_]+)[\"']")
     used = set()
     files = list((ROOT / "rhinoforge_b200").rglob("*.py")) + [ROOT / "bench.py"]
-    files += list((ROOT / "rhinoforge_b200" / "csrc").rglob("*.cpp"))
+    files += list((ROOT / "rhinoforge_b200" / "csrc").rglob("*.cpp")) + list((ROOT / "rhinoforge_b200" / "csrc").rglob("*.cu"))
     for f in files:
         used |= set(pattern.findall(f.read_text(encoding="utf-8")))
     used |= {"RF_TP_REPORT", "RF_DEBUG_BOUNDS"}          # read by the test workers / the build script
