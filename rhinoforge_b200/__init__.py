@@ -52,6 +52,13 @@ from .runtime.registry import discover_all as _discover_all  # noqa: E402
 _discover_all(_BUILTINS)
 del _BUILTINS, _discover_all
 
+# torch.ops.rpu.*: the stand-alone operator surface (kernels are loaded lazily on first call)
+from .ops import torch_ops as _torch_ops  # noqa: E402
+
+with _warnings.catch_warnings():
+    _warnings.simplefilter("ignore")
+    _torch_ops.register()
+
 __all__ = ["__version__", "RPUCache", "RPUModelForCausalLM", "reset_graph_cache"]
 
 

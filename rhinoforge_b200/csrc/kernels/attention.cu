@@ -591,7 +591,9 @@ static int launch_prefill(const RfAttn* a, AttnParams& p, cudaStream_t s) {
   if (rc) return rc;
   constexpr int kStageBytes = 4 * 2 * (HD / 64) * kBoxBytes;
   constexpr int kQBytes = 4 * (HD / 64) * kBoxBytes;
-  p.stages = HD == 256 ? 2 : (HD == 128 ? 3 : 4);
+  // two resident CTAs per SM (registers allow two): their warps hide each other's MMA and ldmatrix latency,
+  // which matters more than a deeper K/V ring
+  p.stages = HD == 64 ? 3 : 2;
   const size_t smem = (size_t)kQBytes + (size_t)p.stages * kStageBytes + sizeof(AttnCtl) + 1024 + 64;
   auto kfn = attn_prefill_kernel<T, HD>;
   static bool attr = false;

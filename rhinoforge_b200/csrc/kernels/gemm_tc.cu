@@ -803,39 +803,33 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
     int st, part;
     if (layout(splits, 110 * 1024, &st, &part) && st >= 2 && tiles * splits > sm_count()) budget = 110 * 1024;
   } else {
-    // Pick (splits, CTAs per SM) by a small cost model over what can actually be resident: a wave of
-    // `clusters` tiles costs its k-blocks at the slower of one CTA's own pace and its share of HBM,
-    // plus a fixed start/finish cost; a grid that does not fit pays for every extra wave.
+    // Split rule from timing sweeps of decode and mid-size shapes on B200:
+    //  * power-of-two cluster sizes only (3 and 6 place badly on the GPCs and cost up to 2x);
+    //  * weight-streaming shapes (tokens on the MMA N axis) and 128-wide token-row tiles want about two CTAs per
+    //    SM in flight: more splits until tiles * splits would exceed 2 * SMs;
+    //  * 256-wide token-row tiles are tensor-core bound and want ONE CTA per SM with a deep ring, so they split
+    //    only up to tiles * splits <= SMs;
+    //  * the whole grid must be resident at once (cluster placement is checked, not assumed).
     const int max_by_k = std::max(1, pl->k_blocks / 4);
-    const double kblock_bytes = (double)stage_bytes;
-    // per-k-block time floors (microseconds): a CTA's own load/issue latency, its tensor-core time, and
-    // its share of HBM (only the bytes that are not re-reads of another tile's operand) and of L2
-    const double t_free_us = 0.22, hbm_bytes_per_us = 6.0e6, l2_bytes_per_us = 1.5e7, t_fixed_us = 4.0;
-    const double unique_bytes = ((double)g->M + (double)(dual ? 2 : 1) * g->N) * g->K * 2.0;
-    const double hbm_frac = std::min(1.0, unique_bytes / ((double)tiles * kblock_bytes * pl->k_blocks));
-    const double mma_us = 2.0 * kBM * pl->bn * (dual ? 2 : 1) * kBK / 15.2e6;
-    double best = 1e30;
-    for (int b : {224 * 1024, 110 * 1024}) {
-      for (int S = 1; S <= std::min(8, max_by_k); ++S) {
-        if (two_shot && S > 1) break;
+    const int cap = (!swap && pl->bn > 128) ? sm_count() : 2 * sm_count();
+    splits = 1;
+    if (!two_shot) {
+      for (int S = 8; S >= 2; S >>= 1) {
+        if (S > max_by_k || tiles * S > cap) continue;
         int st, part;
+        const int b = tiles * S > sm_count() ? 110 * 1024 : 224 * 1024;
         const size_t smem = layout(S, b, &st, &part);
         if (st < 2 || smem > 227 * 1024) continue;
-        const int clusters = max_resident_clusters(S, smem);
-        const int waves = ceil_div(tiles, clusters);
-        const int active = std::min(tiles, clusters) * S;
-        const int per_sm = std::max(1, ceil_div(active, sm_count()));
-        double t_kb = t_free_us * (st >= 4 ? 1.0 : (st == 3 ? 1.25 : 1.6));
-        t_kb = std::max(t_kb, mma_us * per_sm);
-        t_kb = std::max(t_kb, kblock_bytes * hbm_frac * active / hbm_bytes_per_us);
-        t_kb = std::max(t_kb, kblock_bytes * active / l2_bytes_per_us);
-        const double cost = waves * (ceil_div(pl->k_blocks, S) * t_kb + t_fixed_us + 0.35 * (S - 1));
-        if (cost < best) {
-          best = cost;
-          splits = S;
-          budget = b;
-        }
+        if (tiles > max_resident_clusters(S, smem)) continue;
+        splits = S;
+        break;
       }
+    }
+    {
+      int st, part;
+      layout(splits, 110 * 1024, &st, &part);
+      const int want = (!swap && pl->bn > 128) ? 3 : 2;          // stages needed to run two CTAs per SM
+      budget = (tiles * splits > sm_count() && st >= want) ? 110 * 1024 : 224 * 1024;
     }
   }
   if (env_smem_kb > 0) budget = std::min(224, std::max(48, env_smem_kb)) * 1024;

@@ -164,3 +164,24 @@ def test_native_struct_layouts_match_ctypes():
                                  N.RfStackForward)]
     assert list(sizes)[:7] == got
     assert list(sizes)[8:10] == [C.sizeof(N.RfConv1d), C.sizeof(N.RfGdn)]
+
+
+def test_torch_ops_rpu_namespace_is_registered_and_runs_on_cpu():
+    """The stand-alone operators exist by name; on CPU tensors they take the plain PyTorch path."""
+    import torch
+    import rhinoforge_b200  # noqa: F401
+    ops = torch.ops.rpu
+    for name in ("rms_norm", "apply_rotary_pos_emb", "scaled_dot_product_attention_unified", "gather_embedding",
+                 "assemble_inputs_embeds", "cast_uint8_fp16", "linear_into", "lm_head_logits_top1", "argmax_lastdim_host",
+                 "moe_select", "reset_graph_cache"):
+        assert hasattr(ops, name), name
+    x = torch.randn(3, 8)
+    y = ops.rms_norm(x, torch.ones(8), 1e-6)
+    assert torch.allclose(y, x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6), atol=1e-5)
+    q = torch.randn(2, 5, 4, 16)
+    kv = torch.randn(2, 5, 2, 16)
+    o = ops.scaled_dot_product_attention_unified(q, kv, kv, True, 0.0)
+    assert o.shape == q.shape
+    ids, w = ops.moe_select(torch.randn(4, 8), None, 2, 1.0)
+    assert ids.shape == (4, 2) and torch.allclose(w.sum(-1), torch.ones(4), atol=1e-5)
+    assert torch.equal(ops.argmax_lastdim_host(torch.tensor([[1.0, 3.0, 2.0]])), torch.tensor([1], dtype=torch.int32))
