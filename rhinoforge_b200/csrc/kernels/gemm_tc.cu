@@ -243,15 +243,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int wt = 0; wt < kWTiles; ++wt) {
         const uint8_t* src = st + half_bytes + wt * q_tile_bytes;
         uint8_t* dst = SWAP ? st + wt * kATileBytes : st + kATiles * kATileBytes + wt * b_tile_bytes;
-        for (int row = ct; row < w_rows; row += 128) {
-          const uint4* q4 = reinterpret_cast<const uint4*>(src + row * kBK);
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            const uint4 q = q4[h];
-            const int c0 = 2 * h, c1 = 2 * h + 1;
-            *reinterpret_cast<uint4*>(dst + row * 128 + ((c0 ^ (row & 7)) << 4)) = widen_i8x8<T>(make_uint2(q.x, q.y));
-            *reinterpret_cast<uint4*>(dst + row * 128 + ((c1 ^ (row & 7)) << 4)) = widen_i8x8<T>(make_uint2(q.z, q.w));
-          }
+        // 16 int8 (one 16-byte piece) per thread and round; consecutive threads take consecutive pieces, so a
+        // warp reads 512 contiguous bytes (8 rows x 64) without bank conflicts
+        for (int idx = ct; idx < w_rows * 4; idx += 128) {
+          const int row = idx >> 2, h = idx & 3;
+          const uint4 q = *reinterpret_cast<const uint4*>(src + row * kBK + h * 16);
+          const int c0 = 2 * h, c1 = 2 * h + 1;
+          *reinterpret_cast<uint4*>(dst + row * 128 + ((c0 ^ (row & 7)) << 4)) = widen_i8x8<T>(make_uint2(q.x, q.y));
+          *reinterpret_cast<uint4*>(dst + row * 128 + ((c1 ^ (row & 7)) << 4)) = widen_i8x8<T>(make_uint2(q.z, q.w));
         }
       }
       fence_proxy_async();   // generic-proxy writes -> visible to the tensor core's async-proxy reads
@@ -808,8 +807,9 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
     //  * weight-streaming shapes (tokens on the MMA N axis) and 128-wide token-row tiles want about two CTAs per
     //    SM in flight: more splits until tiles * splits would exceed 2 * SMs;
     //  * 256-wide token-row tiles are tensor-core bound and want ONE CTA per SM with a deep ring, so they split
-    //    only up to tiles * splits <= SMs;
-    //  * the whole grid must be resident at once (cluster placement is checked, not assumed).
+    //    only up to tiles * splits <= SMs (grids beyond that run two CTAs per SM with a two-stage ring each, which
+    //    measured faster than one CTA with four stages once there are several waves);
+    //  * a small second wave costs less than halving the split (measured), so residency is not required.
     const int max_by_k = std::max(1, pl->k_blocks / 4);
     const int cap = (!swap && pl->bn > 128) ? sm_count() : 2 * sm_count();
     splits = 1;
@@ -820,7 +820,6 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
         const int b = tiles * S > sm_count() ? 110 * 1024 : 224 * 1024;
         const size_t smem = layout(S, b, &st, &part);
         if (st < 2 || smem > 227 * 1024) continue;
-        if (tiles > max_resident_clusters(S, smem)) continue;
         splits = S;
         break;
       }
@@ -828,8 +827,7 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
     {
       int st, part;
       layout(splits, 110 * 1024, &st, &part);
-      const int want = (!swap && pl->bn > 128) ? 3 : 2;          // stages needed to run two CTAs per SM
-      budget = (tiles * splits > sm_count() && st >= want) ? 110 * 1024 : 224 * 1024;
+      budget = (tiles * splits > sm_count() && st >= 2) ? 110 * 1024 : 224 * 1024;
     }
   }
   if (env_smem_kb > 0) budget = std::min(224, std::max(48, env_smem_kb)) * 1024;
