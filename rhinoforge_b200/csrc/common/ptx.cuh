@@ -194,6 +194,35 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 
+// Each lane reads 32 consecutive 32-bit columns of its own TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+      " {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+      " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// Each lane writes 32 consecutive 32-bit columns of its own TMEM lane.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0],"
+      " {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16,"
+      " %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // 64-bit shared-memory matrix descriptor for a K-major operand tile whose rows
 // are 128 bytes (64 x 16-bit) laid out with the 128-byte swizzle that a TMA
 // box of inner extent 128 bytes produces: 8-row groups of 1024 bytes.
@@ -209,10 +238,25 @@ __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
   d |= static_cast<uint64_t>(2) << 61;             // SWIZZLE_128B
   return d;
 }
+// Descriptor of an MN-major operand (its M or N index is the contiguous one) in the 128-byte swizzle:
+// the tile is a stack of [k rows x 64 elements] slabs, row pitch 128 bytes, 8-row groups 1024 bytes apart
+// (stride byte offset); the next 64 elements along M/N start `mn_chunk_bytes` later (leading byte offset).
+// This is the image a TMA box of 64 elements x rows leaves for a row-major [k, mn] matrix, e.g. V[token, d]
+// used as the B operand of P.V.
+__device__ __forceinline__ uint64_t umma_desc_mn128(uint32_t smem_addr, uint32_t mn_chunk_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>((mn_chunk_bytes >> 4) & 0x3FFF) << 16;   // LBO: next 64-element chunk along M/N
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                        // SBO: next 8 k-rows
+  d |= static_cast<uint64_t>(1) << 46;                                // version
+  d |= static_cast<uint64_t>(2) << 61;                                // SWIZZLE_128B
+  return d;
+}
 // 32-bit instruction descriptor, kind::f16, fp32 accumulate, both operands
 // K-major.  ab_fmt: 0 = fp16, 1 = bf16.
-__host__ __device__ __forceinline__ uint32_t umma_idesc_f16(int m, int n, int ab_fmt) {
+__host__ __device__ __forceinline__ uint32_t umma_idesc_f16(int m, int n, int ab_fmt, int b_mn_major = 0) {
   uint32_t d = 0;
+  d |= static_cast<uint32_t>(b_mn_major & 1) << 16;  // B operand major-ness: 0 = K, 1 = M/N
   d |= 1u << 4;                                   // D format: fp32
   d |= static_cast<uint32_t>(ab_fmt) << 7;        // A format
   d |= static_cast<uint32_t>(ab_fmt) << 10;       // B format

@@ -23,28 +23,12 @@
 #include "../common/mma.cuh"
 #include "../common/ptx.cuh"
 #include "../rf_api.h"
+#include "attn_params.cuh"
 
 namespace rf {
 
 constexpr int kAttnMaxStages = 4;
 constexpr int kBoxBytes = 16 * 128;  // one TMA box: 16 rows x 64 x 16-bit
-
-struct AttnParams {
-  const void* q; int64_t ldq;
-  void* out; int64_t ldo;
-  const int32_t* page_table; int32_t pt_stride;
-  int32_t paged;
-  int32_t num_seqs, Hq, Hkv, G;
-  const int32_t* q_start; const int32_t* q_len; const int32_t* kv_start; const int32_t* kv_len;
-  int32_t max_q_len;
-  int32_t causal, window;
-  const uint8_t* mask; int64_t mask_ld, mask_seq_stride;
-  const int32_t* seg_q; const int32_t* seg_k;
-  float scale_log2;
-  float* ws_o; float* ws_lse;
-  int32_t splits, pages_per_split, stages;
-  int32_t* status;
-};
 
 struct alignas(8) AttnCtl {
   uint64_t full[kAttnMaxStages];
@@ -637,12 +621,19 @@ extern "C" int rf_attn_decode(const RfAttn* a, rf_stream_t stream) {
   RF_ATTN_DISPATCH(launch_decode)
 }
 
+namespace rf {
+int launch_prefill_tc(const RfAttn* a, const AttnParams& p, cudaStream_t s);   // attention_tc.cu
+}
+
 extern "C" int rf_attn_prefill(const RfAttn* a, rf_stream_t stream) {
   RF_SKIP_IF_REPLAYING();
   AttnParams p;
   int rc = fill_params(a, &p);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // tcgen05 kernel by default; RF_ATTN_TC=0 selects the mma.sync kernel (A/B timing)
+  static const bool use_tc = [] { const char* e = getenv("RF_ATTN_TC"); return !(e && e[0] == '0'); }();
+  if (use_tc) return rf::launch_prefill_tc(a, p, s);
   RF_ATTN_DISPATCH(launch_prefill)
 }
 
