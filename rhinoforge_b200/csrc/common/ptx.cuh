@@ -86,14 +86,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait on one phase of an mbarrier.  Returns false on timeout.
+// backoff_ns > 0: sleep between polls, for single-lane roles (TMA producer, MMA issuer) whose spinning would
+// otherwise take issue slots from the compute warps that share their scheduler.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          uint64_t limit_ns = kLocalWaitNs) {
+                                          uint64_t limit_ns = kLocalWaitNs, uint32_t backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   while (true) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
+      if (backoff_ns) __nanosleep(backoff_ns);
+    }
     if (global_timer_ns() - t0 > limit_ns) return false;
   }
 }

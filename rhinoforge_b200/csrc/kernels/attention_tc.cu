@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(kFaThreads)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   using G = FaGeom<HD>;
-  constexpr int J = G::J, KVB = G::KVB, PC = G::PC;
+  constexpr int J = G::J, KVB = G::KVB;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -118,7 +118,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       for (int j = 0; j < nblk; ++j) {
         const int s = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        if (!mbar_wait(&ctl->kv_empty[s], ph ^ 1u)) {
+        if (!mbar_wait(&ctl->kv_empty[s], ph ^ 1u, kLocalWaitNs, 64)) {
           report_status(p.status, kStatusTmaTimeout, kTagAttnPrefill, j);
           ctl->abort_flag = 1;
           break;
@@ -161,11 +161,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       const uint32_t idesc_qk = umma_idesc_f16(kFaRows, KVB, Num<T>::kFmt, 0);
       const uint32_t idesc_pv = umma_idesc_f16(kFaRows, HD, Num<T>::kFmt, 1);
       const uint32_t q_addr = smem_u32(qsm), p_addr = smem_u32(psm);
-      bool ok = mbar_wait(&ctl->q_full, 0);
+      bool ok = mbar_wait(&ctl->q_full, 0, kLocalWaitNs, 32);
       auto issue_qk = [&](int j) -> bool {
         const int s = j & 1, b = j & 1;
-        if (!mbar_wait(&ctl->kv_full[s], (uint32_t)(j >> 1) & 1u)) return false;
-        if (!mbar_wait(&ctl->s_empty[b], ((uint32_t)(j >> 1) & 1u) ^ 1u)) return false;
+        if (!mbar_wait(&ctl->kv_full[s], (uint32_t)(j >> 1) & 1u, kLocalWaitNs, 32)) return false;
+        if (!mbar_wait(&ctl->s_empty[b], ((uint32_t)(j >> 1) & 1u) ^ 1u, kLocalWaitNs, 32)) return false;
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(kvsm + (size_t)s * G::kStageBytes);
 #pragma unroll
@@ -181,7 +181,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       for (int j = 0; ok && j < nblk; ++j) {
         if (j + 1 < nblk) ok = issue_qk(j + 1);          // runs while the softmax warps work on block j
         if (!ok) break;
-        if (!mbar_wait(&ctl->p_full, (uint32_t)j & 1u)) { ok = false; break; }
+        if (!mbar_wait(&ctl->p_full, (uint32_t)j & 1u, kLocalWaitNs, 32)) { ok = false; break; }
         tc_fence_after_sync();
         const int s = j & 1;
         const uint32_t v_addr = smem_u32(kvsm + (size_t)s * G::kStageBytes + G::kKBytes);
@@ -210,31 +210,49 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     uint8_t* prow = psm + r * 128;
+    // bounds of the valid kv positions of this row that do not depend on data: [lo, hi]
+    const int hi_row = min(kvlen - 1, p.causal ? qpos0 + qi : 0x7fffffff);
+    const int lo_row = p.window > 0 ? qpos0 + qi - p.window + 1 : 0;
+    const bool data_mask = mrow != nullptr || p.seg_q != nullptr;
     for (int j = 0; j < nblk; ++j) {
       const int b = j & 1;
       if (!mbar_wait(&ctl->s_full[b], (uint32_t)(j >> 1) & 1u) || *abort_flag) { ok = false; break; }
       tc_fence_after_sync();
       const int t0 = kv_lo + j * KVB;
       const uint32_t s_addr = lane_base + (uint32_t)(b * KVB);
-      auto valid_at = [&](int col) -> bool {
-        const int tk = t0 + col;
-        bool v = tk < kvlen;
-        if (p.causal) v = v && tk <= qpos0 + qi;
-        if (p.window > 0) v = v && tk > qpos0 + qi - p.window;
-        if (mrow && v) v = mrow[tk] != 0;
-        if (p.seg_q && v) v = p.seg_k[kv0 + tk] == sq;
-        return v;
-      };
-      // pass 1: block maximum of this row
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < KVB; c0 += 32) {
-        uint32_t sv[32];
-        tmem_ld32(s_addr + c0, sv);
-        tmem_ld_wait();
+      // the whole row of S for this block: all loads in flight, one wait
+      uint32_t sv[KVB];
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (valid_at(c0 + i)) mx = fmaxf(mx, __uint_as_float(sv[i]) * p.scale_log2);
+      for (int c0 = 0; c0 < KVB; c0 += 32) tmem_ld32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
+      tmem_ld_wait();
+      // S[b] may now be overwritten by Q.K^T of block j+2
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->s_empty[b]);
+      // masking: interior blocks need none; edge blocks compare against the row's [lo, hi]; boolean
+      // masks and segment ids (rare) take the per-element path
+      const bool edge = __any_sync(0xffffffffu, t0 < lo_row || t0 + KVB - 1 > hi_row) || data_mask;
+      float mx = -INFINITY;
+      if (!edge) {
+#pragma unroll
+        for (int i = 0; i < KVB; ++i) {
+          const float v = __uint_as_float(sv[i]) * p.scale_log2;
+          sv[i] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < KVB; ++i) {
+          const int tk = t0 + i;
+          bool v = tk >= lo_row && tk <= hi_row;
+          if (data_mask && v) {
+            if (mrow) v = mrow[tk] != 0;
+            if (p.seg_q && v) v = p.seg_k[kv0 + tk] == sq;
+          }
+          const float x = v ? __uint_as_float(sv[i]) * p.scale_log2 : -INFINITY;
+          sv[i] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
+        }
       }
       // P and O belong to the tensor core until P.V of the previous block has finished
       if (j > 0 && !mbar_wait(&ctl->p_empty, (uint32_t)(j - 1) & 1u)) { ok = false; break; }
@@ -260,39 +278,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           m_ref = m_new;
         }
       }
-      // pass 2: probabilities against the reference maximum -> 16-bit P tile (K-major, 128-byte swizzle)
+      // probabilities against the reference maximum -> 16-bit P tile (K-major, 128-byte swizzle)
       const float mref = m_ref == -INFINITY ? 0.f : m_ref;
       float rs = 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < KVB; c0 += 32) {
-        uint32_t sv[32];
-        tmem_ld32(s_addr + c0, sv);
-        tmem_ld_wait();
-        float pv[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          pv[i] = valid_at(c0 + i) ? exp2f(__uint_as_float(sv[i]) * p.scale_log2 - mref) : 0.f;
-          rs += pv[i];
+      for (int u = 0; u < KVB / 8; ++u) {                 // 16-byte units of 8 values
+        float f8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          f8[i] = exp2f(__uint_as_float(sv[u * 8 + i]) - mref);   // masked entries are -inf -> 0
+          rs += f8[i];
         }
-        uint8_t* chunk_base = prow + (c0 >> 6) * (kFaRows * 128);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {                     // four 16-byte units of 8 values
-          float f8[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) f8[i] = pv[u * 8 + i];
-          const int unit = ((c0 & 63) >> 3) + u;           // unit index inside the 128-byte row
-          store8(reinterpret_cast<T*>(chunk_base + ((unit ^ (r & 7)) << 4)), f8);
-        }
+        uint8_t* chunk_base = prow + (u >> 3) * (kFaRows * 128);
+        store8(reinterpret_cast<T*>(chunk_base + (((u & 7) ^ (r & 7)) << 4)), f8);
       }
       l += rs;
-      // S[b] may be overwritten by Q.K^T of block j+2; P is ready for the tensor core
+      // P (and a rescaled O) are ready for the tensor core
       tc_fence_before_sync();
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&ctl->s_empty[b]);
-        mbar_arrive(&ctl->p_full);
-      }
+      if (lane == 0) mbar_arrive(&ctl->p_full);
     }
     // epilogue: O / l
     if (ok && nblk > 0) ok = mbar_wait(&ctl->o_full, 0);
