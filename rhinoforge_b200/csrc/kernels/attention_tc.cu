@@ -36,14 +36,15 @@ struct alignas(8) FaCtl {
 
 template <int HD> struct FaGeom {
   static constexpr int J = HD / 64;                      // 64-column chunks of the head dimension
-  static constexpr int KVB = HD == 256 ? 64 : 128;       // kv tokens per block
+  static constexpr int KVB = 64;                         // kv tokens per block: small enough for TWO CTAs per SM
+                                                         // (HD <= 128), whose softmax and MMA phases interleave
   static constexpr int PC = KVB / 64;                    // 64-token chunks of P
   static constexpr int kQBytes = J * kFaRows * 128;
   static constexpr int kKBytes = J * KVB * 128;          // K (and V) of one stage
   static constexpr int kStageBytes = 2 * kKBytes;
   static constexpr int kPBytes = PC * kFaRows * 128;
   static constexpr int kSmem = kQBytes + 2 * kStageBytes + kPBytes;
-  static constexpr int kTmemCols = 512;                  // 2 x KVB (S) + HD (O) <= 512
+  static constexpr int kTmemCols = HD == 256 ? 512 : 256; // 2 x KVB (S) + HD (O), rounded up to a power of two
   static constexpr int kOCol = 2 * KVB;
 };
 
@@ -53,9 +54,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                        const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   using G = FaGeom<HD>;
   constexpr int J = G::J, KVB = G::KVB;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw_addr = smem_u32(smem_raw);
-  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  // No alignment slack: two CTAs of the HD <= 128 configuration fill the SM's shared memory to within 2 KB.
+  // The swizzled tiles need a 1024-byte aligned base, which the runtime provides when the kernel has no
+  // static shared memory; a misaligned base is reported instead of being used.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0) report_status(p.status, kStatusBadArgument, kTagAttnPrefill, (int)(smem_u32(smem_raw) & 1023u));
+    return;
+  }
   uint8_t* qsm = smem;
   uint8_t* kvsm = smem + G::kQBytes;
   uint8_t* psm = kvsm + 2 * G::kStageBytes;
@@ -355,7 +362,7 @@ static int launch_prefill_tc_t(const RfAttn* a, const AttnParams& p, cudaStream_
   if (rc) return rc;
   rc = make_tmap_2d(&tmQ, a->q, a->dtype, 2, (uint64_t)a->Hq * a->hd, a->q_rows_total, a->ldq, 64, 16, true);
   if (rc) return rc;
-  const size_t smem = (size_t)G::kSmem + sizeof(FaCtl) + 1024 + 64;
+  const size_t smem = (size_t)G::kSmem + sizeof(FaCtl);
   auto kfn = attn_prefill_tc_kernel<T, HD>;
   static bool attr = false;
   if (!attr) {
