@@ -1,0 +1,121 @@
+"""Host-only checks of the weight layout rule, the chunk envelope, rotary table builders, the attribute guard,
+the tile-major packer and the Pi0.5 facade's input plumbing."""
+import pytest
+import torch
+
+
+def test_linear_partition_rule_and_shards():
+    from rhinoforge_b200.runtime import weights as W
+    assert W.get_linear_partition(4096, 12288, 2, 8, "model.layers.0.mlp.gate_proj") == W.PARTITION_COL
+    assert W.get_linear_partition(12288, 4096, 2, 8, "model.layers.0.mlp.down_proj") == W.PARTITION_ROW
+    assert W.get_linear_partition(4096, 4096, 2, 8, "model.layers.3.self_attn.o_proj") == W.PARTITION_ROW
+    assert W.get_linear_partition(100, 30, 2, 8, "head") == W.PARTITION_HOST
+    w = torch.arange(8 * 16, dtype=torch.float32).view(8, 16)
+    assert torch.equal(W.shard_linear(w, W.PARTITION_COL, 1, 4), w[2:4])
+    assert torch.equal(W.shard_linear(w, W.PARTITION_ROW, 3, 4), w[:, 12:16])
+    plan = W.partition_plan([("a.q_proj", (64, 32)), ("a.o_proj", (32, 64))], 8)
+    assert plan == {"a.q_proj": 1, "a.o_proj": 0}
+
+
+def test_pack_weight_layout_matches_the_swizzle_rule():
+    from rhinoforge_b200.ops.kernels import pack_weight
+    w = torch.arange(130 * 70, dtype=torch.float16).view(130, 70)
+    p = pack_weight(w).view(2, 2, 128, 64)                       # [row tile, k block, row, col]
+    for (r, c) in ((5, 9), (129, 67), (0, 0), (127, 63)):
+        rt, rr, kb, cc = r // 128, r % 128, c // 64, c % 64
+        chunk, within = cc // 8, cc % 8
+        assert p[rt, kb, rr, ((chunk ^ (rr % 8)) * 8) + within] == w[r, c]
+    assert float(p[1, 1, 5].abs().sum()) == 0.0                  # padding rows are zero
+    q = torch.randint(-127, 128, (256, 128), dtype=torch.int8)
+    pq = pack_weight(q, 2).view(2, 2, 128, 64)                    # int8: plain row-major blocks, two sections
+    assert torch.equal(pq[1, 1], q[128:256, 64:128])
+
+
+def test_chunk_envelope():
+    from rhinoforge_b200.runtime.chunk_envelope import ChunkEnvelope
+    e = ChunkEnvelope(4096, 512)
+    assert (e.pages, e.chunks_for(1000)) == (256, 2)
+    assert e.admits(4000, 96) and not e.admits(4000, 100)
+    with pytest.raises(ValueError):
+        ChunkEnvelope(4096, 100)
+    with pytest.raises(ValueError):
+        e.check(4096, 1)
+
+
+def test_rope_builders_agree_with_each_other():
+    from rhinoforge_b200.runtime import rope_partial as R
+    axis = R.mrope_axis_of_freq(64, (11, 11, 10))
+    assert axis.tolist()[:7] == [0, 1, 2, 0, 1, 2, 0] and int((axis == 0).sum()) == 11
+    assert int((axis == 1).sum()) == 11 and int((axis == 2).sum()) == 10
+    cos, sin = R.rope_tables(64, 50, 1e4)
+    pos3 = torch.stack((torch.arange(20), torch.arange(20) + 3, torch.arange(20) + 7))
+    bc, bs = R.baked_interleaved_tables(pos3, 64, (11, 11, 10), 1e4)
+    f = torch.arange(32)
+    want = cos[pos3[axis.long(), :].t(), f]
+    assert torch.allclose(bc, want, atol=1e-6)
+    assert R.partial_rotary_dim(256, 0.25) == 64
+    with pytest.raises(ValueError):
+        R.mrope_axis_of_freq(64, (10, 10, 10))
+
+
+def test_attribute_guard():
+    from rhinoforge_b200.runtime import hw_attrs
+    from rhinoforge_b200.runtime.errors import RPUConfigError
+
+    @hw_attrs.guard
+    class Handle:
+        pass
+    h = Handle()
+    h._rpu_execution = {"prefill": {"chunk_size": 512}}
+    h._rpu_last_execution_plan = {"stage": "prefill"}
+    h._rpu_freeze()
+    h._rpu_last_execution_plan = {"stage": "decode"}             # public: always writable
+    h._rpu_execution = {"prefill": {"chunk_size": 512}}          # same value: allowed
+    with pytest.raises(RPUConfigError):
+        h._rpu_execution = {"prefill": {"chunk_size": 256}}
+    with pytest.raises(RPUConfigError):
+        h._rpu_typo = 1
+    with pytest.raises(RPUConfigError):
+        h._rpu_is_ready = False
+    assert hw_attrs.classify("other") == "foreign"
+
+
+def test_pi05_image_preprocessing_and_checkpoint_names():
+    from rhinoforge_b200.adapters.pi05 import canonical_name, config_from_policy_config
+    from rhinoforge_b200.api.policy import resize_with_pad
+    img = torch.rand(2, 3, 100, 200)
+    out = resize_with_pad(img, 224)
+    assert out.shape == (2, 3, 224, 224)
+    assert float(out[:, :, :50].max()) == -1.0 and float(out[:, :, -50:].max()) == -1.0       # padded bands are black
+    assert -1.0 <= float(out.min()) and float(out.max()) <= 1.0
+    same = resize_with_pad(torch.rand(1, 3, 224, 224), 224)
+    assert same.shape == (1, 3, 224, 224)
+    assert canonical_name("model.paligemma_with_expert.gemma_expert.model.norm.dense.weight") == \
+        "paligemma_with_expert.gemma_expert.model.norm.dense.weight"
+    cfg, meta = config_from_policy_config({"chunk_size": 50, "max_action_dim": 32, "n_action_steps": 25,
+                                           "input_features": {"observation.images.a": {}, "observation.images.b": {},
+                                                              "observation.images.c": {}, "observation.state": {}},
+                                           "output_features": {"action": {"shape": [7]}}})
+    assert (cfg.num_views, cfg.horizon, cfg.action_dim) == (3, 50, 32)
+    assert meta == {"camera_keys": ["observation.images.a", "observation.images.b", "observation.images.c"],
+                    "n_action_steps": 25, "action_dim": 7}
+
+
+def test_pi05_oracle_runs_on_cpu_and_ignores_masked_inputs():
+    """The padded/masked reference is insensitive to what sits in masked cameras and padded tokens."""
+    from rhinoforge_b200.models.pi05 import TorchPi05, random_pi05_state_dict, tiny_pi05_config
+    cfg = tiny_pi05_config()
+    sd = random_pi05_state_dict(cfg, dtype=torch.float32, std=0.08, seed=1)
+    m = TorchPi05(cfg, sd)
+    g = torch.Generator().manual_seed(0)
+    img = torch.randn(1, cfg.num_views, 3, 56, 56, generator=g)
+    imask = torch.tensor([[True, False]])
+    tok = torch.randint(0, cfg.vocab_size, (1, 10), generator=g)
+    tmask = torch.arange(10)[None] < 7
+    noise = torch.randn(1, cfg.horizon, cfg.action_dim, generator=g)
+    a = m.sample_actions(img, imask, tok, tmask, noise, 3)
+    img2, tok2 = img.clone(), tok.clone()
+    img2[:, 1] = 5.0
+    tok2[:, 7:] = 3
+    b = m.sample_actions(img2, imask, tok2, tmask, noise, 3)
+    assert torch.allclose(a, b, atol=1e-5)
