@@ -119,3 +119,49 @@ def test_pi05_oracle_runs_on_cpu_and_ignores_masked_inputs():
     tok2[:, 7:] = 3
     b = m.sample_actions(img2, imask, tok2, tmask, noise, 3)
     assert torch.allclose(a, b, atol=1e-5)
+
+
+def test_action_denormalizer_and_runtime_env():
+    import numpy as np
+    from rhinoforge_b200.api._runtime_env import normalize_runtime_env
+    from rhinoforge_b200.api.action_denorm import ActionDenormalizer, ActionGroup
+    groups = [ActionGroup("arm", 3, "meanstd"), ActionGroup("grip", 1, "minmax"),
+              ActionGroup("base", 2, "bounds_99_woclip", subtract_state=True, state_key="observation.state.base")]
+    stats = {"arm": {"mean": np.array([1.0, 2.0, 3.0]), "std": np.array([0.5, 0.5, 2.0])},
+             "grip": {"min": np.array([0.0]), "max": np.array([0.08])},
+             "base": {"q01": np.array([-1.0, -2.0]), "q99": np.array([1.0, 2.0])}}
+    d = ActionDenormalizer(groups, stats)
+    a = torch.tensor([[1.0, -1.0, 0.0, 3.0, 0.5, -2.0, 9.0]])            # trailing padding column is ignored
+    out = d(a, {"observation.state.base": np.array([10.0, 20.0])})
+    assert out.shape == (1, 6)
+    assert np.allclose(out[0, :3], [1.5, 1.5, 3.0], atol=1e-5)
+    assert np.isclose(out[0, 3], 0.08, atol=1e-5)                        # clipped to +1 -> max
+    assert np.allclose(out[0, 4:], [10.5, 16.0], atol=1e-4)              # no clip, delta added
+    with pytest.raises(ValueError):
+        ActionDenormalizer([ActionGroup("x", 2, "sincos")], {})
+    with pytest.raises(KeyError):
+        ActionDenormalizer([ActionGroup("x", 2, "meanstd")], {"x": {"mean": np.zeros(2)}})
+    env = normalize_runtime_env({"RPU_WARMUP": 1}, owner="policy", allowed={"RPU_WARMUP"})
+    assert env == {"RPU_WARMUP": "1"}
+    with pytest.raises(ValueError, match="before importing"):
+        normalize_runtime_env({"RPU_LOG_LEVEL": 3}, owner="policy", allowed={"RPU_WARMUP"})
+    with pytest.raises(ValueError, match="unsupported"):
+        normalize_runtime_env({"PATH": "x"}, owner="policy", allowed={"RPU_WARMUP"})
+
+
+def test_rotation_6d_decode_roundtrip():
+    import numpy as np
+    from rhinoforge_b200.api import hy_action_decode as H
+    rng = np.random.default_rng(0)
+    q = rng.normal(size=(5, 4))
+    R = H.quat_xyzw_to_matrix(q)
+    assert np.allclose(R @ np.swapaxes(R, -1, -2), np.eye(3), atol=1e-9)
+    d6 = np.concatenate((R[..., 0], R[..., 1]), -1)
+    assert np.allclose(H.rotation_6d_to_matrix(d6), R, atol=1e-9)
+    q2 = H.matrix_to_quat_xyzw(R)
+    assert np.allclose(H.quat_xyzw_to_matrix(q2), R, atol=1e-9)
+    start = np.array([0.1, 0.2, 0.3, 0.0, 0.0, 0.0, 1.0])
+    rel = np.zeros((2, 10)); rel[:, 3] = 1.0; rel[:, 7] = 1.0; rel[1, :3] = [1, 0, 0]; rel[:, 9] = 0.5
+    poses = H.relative_to_absolute_poses(rel, start)
+    assert np.allclose(poses[0], [0.1, 0.2, 0.3, 0, 0, 0, 1, 0.5]) and np.allclose(poses[1, :3], [1.1, 0.2, 0.3])
+    assert H.relative_to_dual_arm_poses(np.concatenate((rel, rel), 1), np.concatenate((start, start))).shape == (2, 16)
