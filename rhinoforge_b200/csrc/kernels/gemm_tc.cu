@@ -955,12 +955,19 @@ extern "C" int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem
   return RF_OK;
 }
 
+namespace rf {
+bool gemm_ps_eligible(const RfGemm* g, bool swap, int splits);   // gemm_ps.cu: persistent kernel for large M
+int launch_gemm_ps(const RfGemm* g, cudaStream_t stream);
+}
+
 static int run_gemm(const RfGemm* g, cudaStream_t stream, bool w8) {
   int rc = check_gemm(g);
   if (rc) return rc;
   GemmPlan pl;
   rc = plan_gemm(g, &pl);
   if (rc) return rc;
+  if (!w8 && g->force_splits == 0 && g->force_bn == 0 && rf::gemm_ps_eligible(g, pl.swap != 0, pl.splits))
+    return rf::launch_gemm_ps(g, stream);
   if (g->ar_world > 1)
     RF_REQUIRE(pl.grid_x * pl.grid_y * 8 * g->ar_world <= g->ar_flag_count / 2,
                "all-reduce needs %d flags, have %d", pl.grid_x * pl.grid_y * 8 * g->ar_world, g->ar_flag_count / 2);

@@ -462,3 +462,30 @@ def test_gemm_packed_dual_and_int8(M, swap, status):
                 force_swap=swap)
     z = (x.float() @ q.float().t()) * sc.float()
     _close(y, torch.nn.functional.silu(z[:, :N]) * z[:, N:], dt, scale=2.0)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M,N,K,dual", [(2500, 2048, 520, False), (4100, 1280, 1024, False), (2304, 2560, 512, True),
+                                        (20000, 256, 128, False)])
+def test_gemm_persistent_kernel(dt, M, N, K, dual, status):
+    """Large token counts take the persistent kernel (one CTA per SM walking tiles, two accumulator buffers):
+    ragged M, N not a multiple of the tile, several tiles per CTA, bias + residual, GLU epilogue."""
+    from rhinoforge_b200.ops import kernels as K_
+    torch.manual_seed(M)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    rows = 2 * N if dual else N
+    w = (torch.randn(rows, K, device="cuda") * 0.05).to(dt)
+    wp = K_.pack_weight(w, 2 if dual else 1)
+    if dual:
+        y = K_.gemm(x, wp, packed_shape=(rows, K), act="silu_mul", dual=True, status=status)
+        z = x.float() @ w.float().t()
+        ref = torch.nn.functional.silu(z[:, :N]) * z[:, N:]
+    else:
+        b = torch.randn(N, device="cuda").to(dt)
+        r = torch.randn(M, N, device="cuda").to(dt)
+        y = K_.gemm(x, wp, packed_shape=(rows, K), bias=b, residual=r, status=status)
+        ref = x.float() @ w.float().t() + b.float() + r.float()
+    _close(y, ref, dt, scale=max(1.0, ref.abs().max().item()))
+    y2 = K_.gemm(x, wp, packed_shape=(rows, K), act="silu_mul", dual=True, status=status) if dual else \
+        K_.gemm(x, wp, packed_shape=(rows, K), bias=b, residual=r, status=status)
+    assert torch.equal(y, y2), "two launches of the same GEMM must agree bit for bit"
