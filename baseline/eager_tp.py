@@ -7,7 +7,7 @@ runtime is used.  It measures the same metric as ``bench.py`` on the same config
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P baseline/eager_tp.py --gpus N --batch 64 --steps 64 [--cuda-graph]
 
-``--cuda-graph`` additionally captures the eager decode step in a CUDA graph (a stronger baseline).
+``--cuda-graph`` (one GPU only) additionally captures the eager decode step in a CUDA graph (a stronger baseline).
 """
 from __future__ import annotations
 
@@ -135,6 +135,9 @@ def main() -> int:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     assert world == a.gpus
+    if a.cuda_graph and world > 1:
+        # capturing the NCCL all-reduces of a step inside a CUDA graph did not return on two GPUs here
+        raise SystemExit("--cuda-graph is a one-GPU baseline; run the multi-GPU baseline eagerly")
     dtype = torch.float16 if a.dtype == "fp16" else torch.bfloat16
     cfg = PROFILES[a.model]
     B, P = a.batch, a.prompt_len
