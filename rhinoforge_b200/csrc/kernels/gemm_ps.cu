@@ -1,15 +1,19 @@
 // Persistent tcgen05 GEMM for large token counts (prefill):  out[M,N] = epilogue( x[M,K] . w[N,K]^T ).
 //
-// One CTA per SM walks a list of 128 x BN output tiles.  Three roles run concurrently and never wait for
-// each other at tile boundaries:
-//   warp 0      TMA producer: the activation tile by tensor map, the weight blocks (tile-major layout) by
+// One CTA per SM walks a list of (128*MT) x BN output tiles.  Three roles run concurrently:
+//   warp 0      TMA producer: the activation tile(s) by tensor map, the weight blocks (tile-major layout) by
 //               bulk copy; its ring runs ahead into the next tile while the current one is still multiplying;
-//   warp 1      MMA issuer: accumulates a tile into one of TWO accumulator buffers in tensor memory;
-//   warps 2-5   epilogue: drain the other accumulator buffer (scale, bias, activation / GLU, residual, store)
-//               while the tensor core already works on the next tile.
-// This removes the per-tile start-up and epilogue bubbles of gemm_tc.cu's one-tile CTAs, which is what limits
-// that kernel on compute-bound shapes.  Tiles are numbered with the M index fastest, so the CTAs that run
-// side by side share one weight panel and the activation matrix stays in L2.
+//   warp 1      MMA issuer: accumulates a tile into an accumulator buffer in tensor memory;
+//   warps 2..   epilogue (four warps per 128-row half): scale, bias, activation / GLU, residual, store.
+// MT = 1: 128 x BN tiles and TWO accumulator buffers, so a tile's epilogue runs under the next tile's MMAs.
+// MT = 2: 256 x BN tiles; each weight tile in shared memory feeds two MMAs (rows 0-127 and 128-255), which
+//         cuts the shared-memory fill per FLOP by a third - the limit of the 128-row tile, whose operand
+//         stream (48 KB per 4.2 MFLOP) cannot be kept in flight deep enough to cover the L2 latency.  The two
+//         halves take all 512 tensor-memory columns, so the epilogue (eight warps) is not overlapped; the
+//         producer still runs ahead into the next tile meanwhile.
+// This removes the per-tile start-up bubbles of gemm_tc.cu's one-tile CTAs, which is what limits that kernel
+// on compute-bound shapes.  Tiles are numbered with the M index fastest, so the CTAs that run side by side
+// share one weight panel and the activation matrix stays in L2.
 // Scope: tokens on the MMA M axis, tile-major 16-bit weights, no split-K, no fused all-reduce (those shapes
 // stay with gemm_tc.cu).
 #include "../common/dtype.cuh"
@@ -22,7 +26,6 @@ namespace rf {
 constexpr int kPsBM = 128, kPsBK = 64;
 constexpr int kPsATile = kPsBM * kPsBK * 2;      // 16 KB
 constexpr int kPsBlock = 128 * kPsBK * 2;        // one packed weight block
-constexpr int kPsThreads = 192;
 constexpr int kPsMaxStages = 8;
 
 struct GemmPsParams {
@@ -32,7 +35,7 @@ struct GemmPsParams {
   const uint8_t* w_packed;
   int32_t* status;
   int M, N, k_blocks, bn, stages, act, dual_offset, dual_tiles;
-  int tiles_m, tiles_n;
+  int tiles_m, tiles_n;   // tiles_m counts tiles of 128*MT rows
 };
 
 struct alignas(8) GemmPsCtl {
@@ -41,8 +44,8 @@ struct alignas(8) GemmPsCtl {
   int32_t abort_flag;
 };
 
-template <typename T, bool DUAL>
-__global__ void __launch_bounds__(kPsThreads)
+template <typename T, bool DUAL, int MT>
+__global__ void __launch_bounds__(64 + 128 * MT)
 gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -51,8 +54,11 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
   const int bn = p.bn;
   constexpr int kW = DUAL ? 2 : 1;                         // weight tiles per stage
   const int b_bytes = bn * kPsBK * 2;
-  const int stage_bytes = kPsATile + kW * b_bytes;
-  const int acc_cols = kW * bn;                            // TMEM columns of one accumulator buffer
+  constexpr int kAStage = MT * kPsATile;                   // activation bytes of one stage
+  const int stage_bytes = kAStage + kW * b_bytes;
+  const int half_cols = kW * bn;                           // TMEM columns of one 128-row half
+  const int acc_cols = MT * half_cols;                     // ... of one accumulator buffer
+  const int nbuf = 2 * acc_cols <= 512 ? 2 : 1;
   GemmPsCtl* ctl = reinterpret_cast<GemmPsCtl*>(smem + (size_t)p.stages * stage_bytes);
   const int tiles = p.tiles_m * p.tiles_n;
 
@@ -63,7 +69,7 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&ctl->acc_full[b], 1);
-      mbar_init(&ctl->acc_empty[b], 4);
+      mbar_init(&ctl->acc_empty[b], 4 * MT);
     }
     ctl->abort_flag = 0;
     fence_barrier_init();
@@ -85,7 +91,7 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
     if (lane == 0) {
       const int nsub = bn / 128;
       auto load_w = [&](int tn, int kb, int s) {
-        uint8_t* sb = smem + (size_t)s * stage_bytes + kPsATile;
+        uint8_t* sb = smem + (size_t)s * stage_bytes + kAStage;
         const int rt0 = tn * nsub;
 #pragma unroll
         for (int wt = 0; wt < kW; ++wt)
@@ -95,7 +101,10 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
                          &ctl->full[s]);
       };
       auto load_x = [&](int tm, int kb, int s) {
-        tma_load_2d(smem + (size_t)s * stage_bytes, &tmA, &ctl->full[s], kb * kPsBK, tm * kPsBM);
+#pragma unroll
+        for (int h = 0; h < MT; ++h)   // a half wholly past the last row is zero-filled by the copy engine
+          tma_load_2d(smem + (size_t)s * stage_bytes + h * kPsATile, &tmA, &ctl->full[s], kb * kPsBK,
+                      (tm * MT + h) * kPsBM);
       };
       // weights never depend on the previous kernel: the first ring fill starts before the dependency wait
       int it = 0;
@@ -143,8 +152,8 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
       int it = 0, lt = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x, ++lt) {
-        const int b = lt & 1;
-        if (!mbar_wait(&ctl->acc_empty[b], (((uint32_t)(lt >> 1)) & 1u) ^ 1u, kLocalWaitNs, 32)) { ok = false; break; }
+        const int b = lt % nbuf;
+        if (!mbar_wait(&ctl->acc_empty[b], (((uint32_t)(lt / nbuf)) & 1u) ^ 1u, kLocalWaitNs, 32)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t acc = tmem_base + (uint32_t)(b * acc_cols);
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
@@ -152,13 +161,18 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
           if (!mbar_wait(&ctl->full[s], (uint32_t)(it / p.stages) & 1u, kLocalWaitNs, 0)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
-          const uint32_t b_addr = a_addr + kPsATile;
+          const uint32_t b_addr = a_addr + kAStage;
 #pragma unroll
           for (int k = 0; k < kPsBK / 16; ++k) {
             const uint32_t accum = (kb | k) ? 1u : 0u;
-            const uint64_t da = umma_desc_k128(a_addr + k * 32);
-            umma_f16(acc, da, umma_desc_k128(b_addr + k * 32), idesc, accum);
-            if (DUAL) umma_f16(acc + bn, da, umma_desc_k128(b_addr + b_bytes + k * 32), idesc, accum);
+            const uint64_t db = umma_desc_k128(b_addr + k * 32);
+            const uint64_t db2 = umma_desc_k128(b_addr + b_bytes + k * 32);
+#pragma unroll
+            for (int h = 0; h < MT; ++h) {
+              const uint64_t da = umma_desc_k128(a_addr + h * kPsATile + k * 32);
+              umma_f16(acc + h * half_cols, da, db, idesc, accum);
+              if (DUAL) umma_f16(acc + h * half_cols + bn, da, db2, idesc, accum);
+            }
           }
           umma_commit(&ctl->empty[s]);
         }
@@ -172,7 +186,8 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
   } else {
     // ------------------------------------------------------------------ epilogue ----
     pdl_wait();
-    const int quarter = warp & 3;
+    const int quarter = warp & 3;                          // the TMEM lanes a warp may read
+    const int half = (warp - 2) >> 2;                      // which 128-row half of the tile it drains
     const int r = quarter * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const T* bias = reinterpret_cast<const T*>(p.bias);
@@ -183,17 +198,17 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
     const bool vec_ok = (p.ldo & 7) == 0 && (!resid || (p.ldr & 7) == 0);
     int lt = 0;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++lt) {
-      const int b = lt & 1;
+      const int b = lt % nbuf;
       const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-      if (!mbar_wait(&ctl->acc_full[b], (uint32_t)(lt >> 1) & 1u) || *abort_flag) {
+      if (!mbar_wait(&ctl->acc_full[b], (uint32_t)(lt / nbuf) & 1u) || *abort_flag) {
         if (!*abort_flag) report_status(p.status, kStatusEpilogueTimeout, kTagGemmTc, tile);
         ctl->abort_flag = 1;
         break;
       }
       tc_fence_after_sync();
-      const int row = tm * kPsBM + r;
+      const int row = (tm * MT + half) * kPsBM + r;
       const int n_base = tn * bn;
-      const uint32_t acc = lane_base + (uint32_t)(b * acc_cols);
+      const uint32_t acc = lane_base + (uint32_t)(b * acc_cols + half * half_cols);
       const float rs = (p.row_scale && row < M) ? p.row_scale[row] : 1.f;
       for (int c = 0; c < bn; c += 16) {
         uint32_t rg[16], ru[16];
@@ -243,7 +258,7 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
           }
         }
       }
-      // this accumulator buffer may be overwritten by the tile after next
+      // this accumulator buffer may now be overwritten by a later tile
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->acc_empty[b]);
@@ -254,9 +269,9 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
   if (warp == 1) tmem_dealloc(tmem_base, 512u);
 }
 
-template <typename T, bool DUAL>
+template <typename T, bool DUAL, int MT>
 static int launch_ps(const RfGemm* g, int bn, cudaStream_t stream) {
-  auto kfn = gemm_ps_kernel<T, DUAL>;
+  auto kfn = gemm_ps_kernel<T, DUAL, MT>;
   static bool attr_set = false;
   if (!attr_set) {
     RF_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
@@ -272,15 +287,24 @@ static int launch_ps(const RfGemm* g, int bn, cudaStream_t stream) {
   p.status = g->status;
   p.M = g->M; p.N = g->N; p.k_blocks = ceil_div(g->K, kPsBK); p.bn = bn;
   p.act = g->act; p.dual_offset = g->dual_offset; p.dual_tiles = ceil_div(g->N, 128);
-  p.tiles_m = ceil_div(g->M, kPsBM); p.tiles_n = ceil_div(g->N, bn);
-  const int stage_bytes = kPsATile + (DUAL ? 2 : 1) * bn * kPsBK * 2;
+  p.tiles_m = ceil_div(g->M, kPsBM * MT); p.tiles_n = ceil_div(g->N, bn);
+  const int stage_bytes = MT * kPsATile + (DUAL ? 2 : 1) * bn * kPsBK * 2;
   const int ctl_bytes = (int)sizeof(GemmPsCtl) + 1024;
   p.stages = std::min(kPsMaxStages, (224 * 1024 - ctl_bytes) / stage_bytes);
   const size_t smem = (size_t)p.stages * stage_bytes + ctl_bytes;
   const int grid = std::min(p.tiles_m * p.tiles_n, sm_count());
-  RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(grid), dim3(kPsThreads), smem, stream, 1, tmA, p));
+  RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(grid), dim3(64 + 128 * MT), smem, stream, 1, tmA, p));
   ::rf::count_launch();
   return RF_OK;
+}
+
+// Rows per tile: 256 (MT = 2) once that still gives about one tile per SM, else 128; 0 = not a persistent shape.
+static int ps_rows_per_tile(const RfGemm* g, int bn) {
+  static const int forced = [] { const char* e = getenv("RF_GEMM_PS_ROWS"); return e ? atoi(e) : 0; }();
+  const int t1 = ceil_div(g->M, kPsBM) * ceil_div(g->N, bn), t2 = ceil_div(g->M, 2 * kPsBM) * ceil_div(g->N, bn);
+  if (forced == 128 || forced == 256) return (forced == 256 ? t2 : t1) >= sm_count() / 2 ? forced : 0;
+  if (t2 * 4 >= sm_count() * 3) return 256;
+  return t1 >= sm_count() ? 128 : 0;
 }
 
 // True when the persistent kernel takes this GEMM (called by rf_gemm after its argument checks).
@@ -289,14 +313,21 @@ bool gemm_ps_eligible(const RfGemm* g, bool swap, int splits) {
   if (!enabled || swap || splits != 1 || g->ar_world > 1 || !g->w_packed || g->w_int8) return false;
   const bool dual = g->dual_offset > 0;
   const int bn = (!dual && g->N % 256 == 0) ? 256 : 128;
-  return ceil_div(g->M, kPsBM) * ceil_div(g->N, bn) >= sm_count();
+  return ps_rows_per_tile(g, bn) != 0;
+}
+
+template <typename T>
+static int launch_ps_t(const RfGemm* g, bool dual, int bn, int rows, cudaStream_t stream) {
+  if (rows == 256) return dual ? launch_ps<T, true, 2>(g, bn, stream) : launch_ps<T, false, 2>(g, bn, stream);
+  return dual ? launch_ps<T, true, 1>(g, bn, stream) : launch_ps<T, false, 1>(g, bn, stream);
 }
 
 int launch_gemm_ps(const RfGemm* g, cudaStream_t stream) {
   const bool dual = g->dual_offset > 0;
   const int bn = (!dual && g->N % 256 == 0) ? 256 : 128;
-  if (g->dtype == 0) return dual ? launch_ps<__half, true>(g, bn, stream) : launch_ps<__half, false>(g, bn, stream);
-  return dual ? launch_ps<__nv_bfloat16, true>(g, bn, stream) : launch_ps<__nv_bfloat16, false>(g, bn, stream);
+  const int rows = ps_rows_per_tile(g, bn);
+  if (g->dtype == 0) return launch_ps_t<__half>(g, dual, bn, rows, stream);
+  return launch_ps_t<__nv_bfloat16>(g, dual, bn, rows, stream);
 }
 
 }  // namespace rf

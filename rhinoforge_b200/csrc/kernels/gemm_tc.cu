@@ -345,16 +345,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     return apply_act(p.act, vg, vu);
   };
+  // Peer buffer addresses are read ONCE: the table lives in global memory and nothing tells the compiler
+  // that the remote stores below cannot alias it, so a lookup per element would sit between every two stores.
+  uint8_t* peer_buf[8];
+#pragma unroll
+  for (int d = 0; d < 8; ++d)
+    peer_buf[d] = (p.ar_world > 1 && d < p.ar_world) ? reinterpret_cast<uint8_t*>(p.ar_recv[d]) + slot_off : nullptr;
   auto push_partial = [&](int tok, int n, float v) {
-    for (int dst = 0; dst < p.ar_world; ++dst) {
-      float* rb = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ar_recv[dst]) + slot_off) +
-                  (size_t)p.ar_rank * M * N;
-      rb[(size_t)tok * N + n] = v;
-    }
+    const size_t at = ((size_t)p.ar_rank * M + tok) * N + n;
+#pragma unroll
+    for (int d = 0; d < 8; ++d)
+      if (d < p.ar_world) reinterpret_cast<float*>(peer_buf[d])[at] = v;
   };
 
   bool aborted = __syncthreads_or(*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag) != 0);
   const int ncols = min(bn, (SWAP ? M : N) - b0);  // valid accumulator columns of this tile
+  uint8_t* owner_buf = nullptr;                    // two-shot: the buffer of this tile's owner rank
+  if (p.ar_world > 1 && p.ar_two_shot) {
+    const int owner = tile_id % p.ar_world;
+#pragma unroll
+    for (int d = 0; d < 8; ++d)
+      if (d == owner) owner_buf = peer_buf[d];
+  }
 
   if (p.splits > 1) {
     // ---- split-K: the CTAs of one output tile form a cluster (cluster dim z =
@@ -491,8 +503,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // reduce-scatter leg: the 16-bit partial of this tile goes to the tile's owner only
         if (!SWAP && a_idx < M) {
           const int owner = tile_id % p.ar_world;
-          T* pb = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(p.ar_recv[owner]) + slot_off) +
-                  ((size_t)p.ar_rank * M + a_idx) * N + b0 + c;
+          T* pb = reinterpret_cast<T*>(owner_buf) + ((size_t)p.ar_rank * M + a_idx) * N + b0 + c;
           if (b0 + c + 16 <= N && (N & 7) == 0) {
             float lo[8], hi[8];
 #pragma unroll
@@ -564,7 +575,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t want = call + 1u;
     const size_t fbase = ((size_t)tile_id * 8) * p.ar_world;
     const size_t f2 = (size_t)p.ar_flag2_base + tile_id;
-    const size_t result_off = slot_off + (uint64_t)p.ar_world * M * N * sizeof(T);
+    const size_t result_rel = (uint64_t)p.ar_world * M * N * sizeof(T);   // result region, after the partials
+    const size_t result_off = slot_off + result_rel;
     __threadfence_system();
     __syncthreads();
     if (tid == 0 && !aborted) st_release_sys(p.ar_flags[owner] + fbase + p.ar_rank, want);
@@ -582,33 +594,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int n0 = b0 + c;
           float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
           const bool vec = (n0 + 8 <= N) && ((N & 7) == 0) && (!resid || (p.ldr & 7) == 0);
-          for (int r = 0; r < p.ar_world; ++r) {
-            const T* src = part + ((size_t)r * M + a_idx) * N + n0;
-            if (vec) {
-              const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(src));
-              const typename Num<T>::T2* h = reinterpret_cast<const typename Num<T>::T2*>(&raw);
+          if (vec) {
+            // every rank's vector (and the residual's) is in flight before the first add
+            uint4 raw[8];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 f = Num<T>::to_f2(h[j]);
-                acc[2 * j] += f.x;
-                acc[2 * j + 1] += f.y;
+            for (int r = 0; r < 8; ++r)
+              raw[r] = r < p.ar_world ? __ldcg(reinterpret_cast<const uint4*>(part + ((size_t)r * M + a_idx) * N + n0))
+                                      : make_uint4(0u, 0u, 0u, 0u);
+            float r8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (resid) load8(resid + (size_t)a_idx * p.ldr + n0, r8);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              if (r < p.ar_world) {
+                const typename Num<T>::T2* h = reinterpret_cast<const typename Num<T>::T2*>(&raw[r]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f = Num<T>::to_f2(h[j]);
+                  acc[2 * j] += f.x;
+                  acc[2 * j + 1] += f.y;
+                }
               }
-            } else {
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += r8[j];
+          } else {
+            for (int r = 0; r < p.ar_world; ++r) {
+              const T* src = part + ((size_t)r * M + a_idx) * N + n0;
               for (int j = 0; j < 8; ++j)
                 if (n0 + j < N) acc[j] += Num<T>::to_f(src[j]);
             }
-          }
-          if (resid) {
-            for (int j = 0; j < 8; ++j)
-              if (n0 + j < N) acc[j] += Num<T>::to_f(resid[(size_t)a_idx * p.ldr + n0 + j]);
-          }
-          for (int dst = 0; dst < p.ar_world; ++dst) {
-            T* rp = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(p.ar_recv[dst]) + result_off) +
-                    (size_t)a_idx * N + n0;
-            if (vec) store8(rp, acc);
-            else
+            if (resid) {
               for (int j = 0; j < 8; ++j)
-                if (n0 + j < N) rp[j] = Num<T>::from_f(acc[j]);
+                if (n0 + j < N) acc[j] += Num<T>::to_f(resid[(size_t)a_idx * p.ldr + n0 + j]);
+            }
+          }
+#pragma unroll
+          for (int dst = 0; dst < 8; ++dst) {
+            if (dst < p.ar_world) {
+              T* rp = reinterpret_cast<T*>(peer_buf[dst] + result_rel) + (size_t)a_idx * N + n0;
+              if (vec) store8(rp, acc);
+              else
+                for (int j = 0; j < 8; ++j)
+                  if (n0 + j < N) rp[j] = Num<T>::from_f(acc[j]);
+            }
           }
         }
       }
@@ -626,14 +654,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (!aborted && !SWAP && a_idx < M) {
       const T* res = reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(p.ar_recv[p.ar_rank]) + result_off) +
                      (size_t)a_idx * N;
-      for (int c = 0; c < ncols; c += 8) {
-        const int n0 = b0 + c;
-        if (n0 + 8 <= N && (N & 7) == 0 && (p.ldo & 7) == 0) {
-          *reinterpret_cast<uint4*>(out + (size_t)a_idx * p.ldo + n0) = __ldcg(reinterpret_cast<const uint4*>(res + n0));
-        } else {
-          for (int j = 0; j < 8; ++j)
-            if (n0 + j < N) out[(size_t)a_idx * p.ldo + n0 + j] = res[n0 + j];
+      if ((N & 7) == 0 && (p.ldo & 7) == 0) {
+        // eight vector loads in flight per round: a store to `out` may alias `res` as far as the compiler
+        // knows, so a load-store pair per column group would run one memory latency at a time
+        for (int c = 0; c < ncols; c += 64) {
+          uint4 t[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int n0 = b0 + c + q * 8;
+            t[q] = (c + q * 8 < ncols && n0 + 8 <= N) ? __ldcg(reinterpret_cast<const uint4*>(res + n0)) : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int n0 = b0 + c + q * 8;
+            if (c + q * 8 < ncols && n0 + 8 <= N) *reinterpret_cast<uint4*>(out + (size_t)a_idx * p.ldo + n0) = t[q];
+          }
         }
+      } else {
+        for (int c = 0; c < ncols; ++c)
+          if (b0 + c < N) out[(size_t)a_idx * p.ldo + b0 + c] = res[b0 + c];
       }
     }
     __syncthreads();
@@ -666,16 +705,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const float* rb = reinterpret_cast<const float*>(
           reinterpret_cast<const uint8_t*>(p.ar_recv[p.ar_rank]) + slot_off);
       const int cstep = p.splits > 1 ? p.splits : 1;
-      for (int c = 0; c < ncols; ++c) {
-        // the columns this CTA pushed: single columns (swap) or groups of eight (tokens on rows)
-        if ((SWAP ? c : (c >> 3)) % cstep != (int)crank) continue;
-        const int tok = SWAP ? (b0 + c) : a_idx;
-        const int n = SWAP ? a_idx : (b0 + c);
-        if (tok < M && n < N) {
+      // the i-th column this CTA pushed: single columns (swap) or groups of eight (tokens on rows)
+      auto own_col = [&](int i) -> int {
+        return SWAP ? ((int)crank + i * cstep) : ((((int)crank + (i >> 3) * cstep) << 3) + (i & 7));
+      };
+      // four columns x every rank's partial are in flight before the first add
+      for (int i0 = 0; own_col(i0) < ncols; i0 += 4) {
+        float v[4][8], rs[4];
+        bool ok[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int c = own_col(i0 + q);
+          const int tok = SWAP ? (b0 + c) : a_idx;
+          const int n = SWAP ? a_idx : (b0 + c);
+          ok[q] = c < ncols && tok < M && n < N;
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+            v[q][r] = (ok[q] && r < p.ar_world) ? __ldcg(rb + ((size_t)r * M + tok) * N + n) : 0.f;
+          rs[q] = (ok[q] && resid) ? Num<T>::to_f(resid[(size_t)tok * p.ldr + n]) : 0.f;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (!ok[q]) continue;
+          const int c = own_col(i0 + q);
+          const int tok = SWAP ? (b0 + c) : a_idx;
+          const int n = SWAP ? a_idx : (b0 + c);
           float acc = 0.f;
-          for (int r = 0; r < p.ar_world; ++r) acc += __ldcg(rb + ((size_t)r * M + tok) * N + n);
-          if (resid) acc += Num<T>::to_f(resid[(size_t)tok * p.ldr + n]);
-          out[(size_t)tok * p.ldo + n] = Num<T>::from_f(acc);
+#pragma unroll
+          for (int r = 0; r < 8; ++r) acc += v[q][r];   // rank order; absent ranks contribute +0
+          out[(size_t)tok * p.ldo + n] = Num<T>::from_f(acc + rs[q]);
         }
       }
     }

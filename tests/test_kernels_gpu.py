@@ -466,10 +466,13 @@ def test_gemm_packed_dual_and_int8(M, swap, status):
 
 @pytest.mark.parametrize("dt", DT)
 @pytest.mark.parametrize("M,N,K,dual", [(2500, 2048, 520, False), (4100, 1280, 1024, False), (2304, 2560, 512, True),
-                                        (20000, 256, 128, False)])
+                                        (20000, 256, 128, False), (1152, 2560, 512, True), (5000, 2048, 520, False),
+                                        (4900, 1152, 256, False), (4900, 2048, 4096, False)])
 def test_gemm_persistent_kernel(dt, M, N, K, dual, status):
-    """Large token counts take the persistent kernel (one CTA per SM walking tiles, two accumulator buffers):
-    ragged M, N not a multiple of the tile, several tiles per CTA, bias + residual, GLU epilogue."""
+    """Large token counts take the persistent kernel (one CTA per SM walking tiles): 128-row tiles with two
+    accumulator buffers (the first, second, fourth and fifth shapes) and 256-row tiles (the others); ragged M
+    (a last half-tile partly or wholly past the end), N not a multiple of the tile, several tiles per CTA,
+    a ring shorter and longer than K, bias + residual, GLU epilogue."""
     from rhinoforge_b200.ops import kernels as K_
     torch.manual_seed(M)
     x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
