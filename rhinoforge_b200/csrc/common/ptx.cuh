@@ -146,6 +146,19 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
       "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
+// Fire-and-forget prefetch of a contiguous global range into L2 (16-byte aligned, bytes a multiple of 16).
+// Lets a kernel keep far more bytes in flight towards DRAM than its shared-memory ring can hold: the later
+// bulk copy of the same range then completes with L2 latency.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes)
+               : "memory");
+}
+// The same for one box of a 2-D tensor map.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* tm, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(tm)),
+               "r"(x), "r"(y)
+               : "memory");
+}
 
 // ------------------------------------------------------------- tcgen05 ----
 // TMEM allocation: whole warp executes; ncols a power of two in [32, 512].

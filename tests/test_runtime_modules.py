@@ -165,3 +165,22 @@ def test_rotation_6d_decode_roundtrip():
     poses = H.relative_to_absolute_poses(rel, start)
     assert np.allclose(poses[0], [0.1, 0.2, 0.3, 0, 0, 0, 1, 0.5]) and np.allclose(poses[1, :3], [1.1, 0.2, 0.3])
     assert H.relative_to_dual_arm_poses(np.concatenate((rel, rel), 1), np.concatenate((start, start))).shape == (2, 16)
+
+
+def test_qwen25vl_window_partition_matches_hf_index():
+    """The window-major unit order and window sizes equal the Hugging Face module's ``get_window_index`` (ragged
+    edge windows, several frames, several images)."""
+    import torch
+    from transformers.models.qwen2_5_vl.configuration_qwen2_5_vl import Qwen2_5_VLVisionConfig as HFConfig
+    from transformers.models.qwen2_5_vl.modeling_qwen2_5_vl import Qwen2_5_VisionTransformerPretrainedModel as HFModel
+    from rhinoforge_b200.models.qwen25_vl_vision import window_partition
+
+    hc = HFConfig(depth=1, hidden_size=32, num_heads=2, intermediate_size=32, patch_size=14, temporal_patch_size=2,
+                  spatial_merge_size=2, out_hidden_size=16, window_size=112, fullatt_block_indexes=[0])
+    ref = HFModel(hc)
+    for grid in ([[1, 6, 10]], [[2, 4, 4], [1, 18, 22]], [[3, 10, 26], [1, 2, 2]]):
+        idx, cu = ref.get_window_index(torch.tensor(grid))
+        cu = torch.unique_consecutive(torch.tensor(cu))
+        order, lens = window_partition([tuple(g) for g in grid], 2, 112 // 2 // 14)
+        assert order == [int(i) for i in idx]
+        assert [4 * n for n in lens] == (cu[1:] - cu[:-1]).tolist()

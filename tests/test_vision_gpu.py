@@ -99,3 +99,30 @@ def test_dinov3_matches_hf():
     assert _rel(last, o.last_hidden_state) < 2e-2
     assert _rel(pooled, o.pooler_output) < 2e-2
     enc.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_qwen25vl_vision_matches_hf(dtype):
+    """Window attention as varlen sequences in window-major order, full-attention blocks in between, head size 80 on
+    padded heads, SwiGLU with biases and a padded intermediate size, merger, raster order restored."""
+    from transformers.models.qwen2_5_vl.configuration_qwen2_5_vl import Qwen2_5_VLVisionConfig as HFConfig
+    from transformers.models.qwen2_5_vl.modeling_qwen2_5_vl import Qwen2_5_VisionTransformerPretrainedModel as HFModel
+    from rhinoforge_b200.models.qwen25_vl_vision import Qwen25VLVisionConfig, Qwen25VLVisionEncoder
+
+    hc = HFConfig(depth=5, hidden_size=160, num_heads=2, intermediate_size=216, patch_size=14, temporal_patch_size=2,
+                  spatial_merge_size=2, out_hidden_size=96, window_size=56, fullatt_block_indexes=[1, 4], hidden_act="silu")
+    hc._attn_implementation = "eager"
+    ref = HFModel(hc).float().eval()
+    _randomize(ref)
+    grid = torch.tensor([[1, 6, 10], [2, 4, 4], [1, 8, 8]])
+    T = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+    px = torch.randn(T, 3 * 2 * 14 * 14, generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = ref(px, grid_thw=grid).pooler_output
+    enc = Qwen25VLVisionEncoder(Qwen25VLVisionConfig.from_hf(hc), ref.state_dict(), dtype=dtype, max_patches=256)
+    assert enc.segments == [(0, 1, False), (1, 2, True), (2, 4, False), (4, 5, True)]
+    got = enc(px, grid)
+    enc.tower.stack.check_status()
+    assert got.shape == want.shape
+    assert _rel(got, want) < (2e-2 if dtype == torch.float16 else 6e-2)
+    enc.close()
