@@ -27,6 +27,7 @@ constexpr int kPsBM = 128, kPsBK = 64;
 constexpr int kPsATile = kPsBM * kPsBK * 2;      // 16 KB
 constexpr int kPsBlock = 128 * kPsBK * 2;        // one packed weight block
 constexpr int kPsMaxStages = 8;
+constexpr int kPsEpiBytes = 32 * 64 * 2;          // 32 rows x 64 columns of 16-bit results per epilogue warp
 
 struct GemmPsParams {
   void* out; int64_t ldo;
@@ -36,7 +37,21 @@ struct GemmPsParams {
   int32_t* status;
   int M, N, k_blocks, bn, stages, act, dual_offset, dual_tiles;
   int tiles_m, tiles_n;   // tiles_m counts tiles of 128*MT rows
+  int band;               // row tiles per band of the tile order
+  int pf_blocks;          // k blocks prefetched into L2 ahead of the ring
 };
+
+// Tile order: bands of `band` row tiles; inside a band the row index runs fastest and the weight panel
+// advances slowly.  The CTAs that run side by side then share a few weight panels and one band of the
+// activation matrix, and the band (sized to a fraction of L2) is reused from L2 by every panel of the sweep
+// instead of being streamed from DRAM once per wave.
+__device__ __forceinline__ void ps_tile_coords(const GemmPsParams& p, int tile, int* tm, int* tn) {
+  const int per_band = p.band * p.tiles_n;
+  const int b = tile / per_band, r = tile - b * per_band;
+  const int rows_here = min(p.band, p.tiles_m - b * p.band);
+  *tn = r / rows_here;
+  *tm = b * p.band + r % rows_here;
+}
 
 struct alignas(8) GemmPsCtl {
   uint64_t full[kPsMaxStages], empty[kPsMaxStages], acc_full[2], acc_empty[2];
@@ -59,7 +74,9 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
   const int half_cols = kW * bn;                           // TMEM columns of one 128-row half
   const int acc_cols = MT * half_cols;                     // ... of one accumulator buffer
   const int nbuf = 2 * acc_cols <= 512 ? 2 : 1;
-  GemmPsCtl* ctl = reinterpret_cast<GemmPsCtl*>(smem + (size_t)p.stages * stage_bytes);
+  // after the ring: one 4 KB transpose buffer per epilogue warp, then the control block
+  uint8_t* epi_stage = smem + (size_t)p.stages * stage_bytes;
+  GemmPsCtl* ctl = reinterpret_cast<GemmPsCtl*>(epi_stage + 4 * MT * kPsEpiBytes);
   const int tiles = p.tiles_m * p.tiles_n;
 
   if (tid == 0) {
@@ -106,20 +123,53 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
           tma_load_2d(smem + (size_t)s * stage_bytes + h * kPsATile, &tmA, &ctl->full[s], kb * kPsBK,
                       (tm * MT + h) * kPsBM);
       };
+      // L2 prefetch cursor: runs p.pf_blocks k blocks ahead of the ring (into the following tiles as well), so
+      // the ring's own copies complete with L2 latency and the bytes in flight towards DRAM are not limited by
+      // shared memory
+      int pf_tile = blockIdx.x, pf_kb = 0, pf_tm = 0, pf_tn = 0;
+      if (pf_tile < tiles) ps_tile_coords(p, pf_tile, &pf_tm, &pf_tn);
+      auto prefetch_next = [&](bool weights, bool acts) {
+        if (pf_tile >= tiles) return;
+        if (weights) {
+          const int rt0 = pf_tn * nsub;
+#pragma unroll
+          for (int wt = 0; wt < kW; ++wt)
+            for (int sub = 0; sub < nsub; ++sub)
+              bulk_prefetch_l2(p.w_packed + ((size_t)(rt0 + sub + wt * p.dual_tiles) * p.k_blocks + pf_kb) * kPsBlock,
+                               kPsBlock);
+        }
+        if (acts) {
+#pragma unroll
+          for (int h = 0; h < MT; ++h)
+            if ((pf_tm * MT + h) * kPsBM < p.M) tma_prefetch_2d(&tmA, pf_kb * kPsBK, (pf_tm * MT + h) * kPsBM);
+        }
+        if (++pf_kb == p.k_blocks) {
+          pf_kb = 0;
+          pf_tile += gridDim.x;
+          if (pf_tile < tiles) ps_tile_coords(p, pf_tile, &pf_tm, &pf_tn);
+        }
+      };
       // weights never depend on the previous kernel: the first ring fill starts before the dependency wait
       int it = 0;
       int tile = blockIdx.x;
+      int tm0 = 0, tn0 = 0;
+      if (tile < tiles) ps_tile_coords(p, tile, &tm0, &tn0);
       const int first_pre = tile < tiles ? min(p.stages, p.k_blocks) : 0;
       for (int i = 0; i < first_pre; ++i) {
         mbar_arrive_expect_tx(&ctl->full[i], (uint32_t)stage_bytes);
-        load_w(tile / p.tiles_m, i, i);
+        load_w(tn0, i, i);
       }
+      // the cursor passes the blocks the ring has just asked for, then takes its lead (weights only: the
+      // activations may still be written by the previous kernel)
+      const int lead = p.pf_blocks > 0 ? first_pre + p.pf_blocks : 0;
+      for (int i = 0; i < lead; ++i) prefetch_next(i >= first_pre, false);
       pdl_wait();
-      for (int i = 0; i < first_pre; ++i) load_x(tile % p.tiles_m, i, i);
+      for (int i = 0; i < first_pre; ++i) load_x(tm0, i, i);
       bool ok = true;
       int issued = first_pre;
       for (; ok && tile < tiles; tile += gridDim.x) {
-        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        int tm, tn;
+        ps_tile_coords(p, tile, &tm, &tn);
         for (int kb = (tile == (int)blockIdx.x ? first_pre : 0); kb < p.k_blocks; ++kb) {
           const int gi = it + kb;                          // global k-block index of this CTA
           const int s = gi % p.stages;
@@ -131,6 +181,7 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
           mbar_arrive_expect_tx(&ctl->full[s], (uint32_t)stage_bytes);
           load_w(tn, kb, s);
           load_x(tm, kb, s);
+          if (p.pf_blocks > 0) prefetch_next(true, true);
           issued = gi + 1;
         }
         it += p.k_blocks;
@@ -199,7 +250,8 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
     int lt = 0;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++lt) {
       const int b = lt % nbuf;
-      const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+      int tm, tn;
+      ps_tile_coords(p, tile, &tm, &tn);
       if (!mbar_wait(&ctl->acc_full[b], (uint32_t)(lt / nbuf) & 1u) || *abort_flag) {
         if (!*abort_flag) report_status(p.status, kStatusEpilogueTimeout, kTagGemmTc, tile);
         ctl->abort_flag = 1;
@@ -210,6 +262,79 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
       const int n_base = tn * bn;
       const uint32_t acc = lane_base + (uint32_t)(b * acc_cols + half * half_cols);
       const float rs = (p.row_scale && row < M) ? p.row_scale[row] : 1.f;
+      if (vec_ok) {
+        // Coalesced path.  A thread owns one accumulator row, so storing from its registers would write 16
+        // bytes to each of 32 different rows per instruction (one mostly empty 128-byte line each).  Instead
+        // the warp parks 64 columns of finished 16-bit results in shared memory (row r at r*128, its 16-byte
+        // chunks XOR-swizzled by r%8: conflict-free both ways) and writes them back transposed: eight lanes
+        // per row, four whole 128-byte lines per instruction; the residual is read the same way.
+        uint8_t* stg = epi_stage + (size_t)(warp - 2) * kPsEpiBytes;
+        const int row0 = (tm * MT + half) * kPsBM + quarter * 32;
+        for (int c0 = 0; c0 < bn; c0 += 64) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int c = c0 + q * 16;
+            uint32_t rg[16], ru[16];
+            tmem_ld16(acc + c, rg);
+            if (DUAL) tmem_ld16(acc + bn + c, ru);
+            tmem_ld_wait();
+            const int n0 = n_base + c;
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int n = n0 + j;
+              float vg = __uint_as_float(rg[j]) * rs, vu = DUAL ? __uint_as_float(ru[j]) * rs : 0.f;
+              if (n < N) {
+                if (scale) {
+                  vg *= Num<T>::to_f(scale[n]);
+                  if (DUAL) vu *= Num<T>::to_f(scale[p.dual_offset + n]);
+                }
+                if (bias) {
+                  vg += Num<T>::to_f(bias[n]);
+                  if (DUAL) vu += Num<T>::to_f(bias[p.dual_offset + n]);
+                }
+              }
+              v[j] = apply_act(p.act, vg, vu);
+            }
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              float w8[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) w8[j] = v[hh * 8 + j];
+              const int chunk = q * 2 + hh;
+              store8(reinterpret_cast<T*>(stg + lane * 128 + ((chunk ^ (lane & 7)) << 4)), w8);
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            const int rr = t * 4 + (lane >> 3), chunk = lane & 7;
+            const int grow = row0 + rr, n = n_base + c0 + chunk * 8;
+            if (grow < M && n < N) {
+              const T* sp = reinterpret_cast<const T*>(stg + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+              if (n + 8 <= N) {
+                if (resid) {
+                  float a8[8], r8[8];
+                  load8(sp, a8);
+                  load8(resid + (size_t)grow * p.ldr + n, r8);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) a8[j] += r8[j];
+                  store8(out + (size_t)grow * p.ldo + n, a8);
+                } else {
+                  *reinterpret_cast<uint4*>(out + (size_t)grow * p.ldo + n) = *reinterpret_cast<const uint4*>(sp);
+                }
+              } else {
+                for (int j = 0; n + j < N; ++j) {
+                  float x = Num<T>::to_f(sp[j]);
+                  if (resid) x += Num<T>::to_f(resid[(size_t)grow * p.ldr + n + j]);
+                  out[(size_t)grow * p.ldo + n + j] = Num<T>::from_f(x);
+                }
+              }
+            }
+          }
+          __syncwarp();
+        }
+      } else
       for (int c = 0; c < bn; c += 16) {
         uint32_t rg[16], ru[16];
         tmem_ld16(acc + c, rg);
@@ -234,27 +359,12 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
           }
           v[j] = apply_act(p.act, vg, vu);
         }
-        if (vec_ok && n0 + 16 <= N) {
-          if (resid) {
-            float r0[8], r1[8];
-            load8(resid + (size_t)row * p.ldr + n0, r0);
-            load8(resid + (size_t)row * p.ldr + n0 + 8, r1);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) { v[j] += r0[j]; v[8 + j] += r1[j]; }
-          }
-          float lo[8], hi[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
-          store8(out + (size_t)row * p.ldo + n0, lo);
-          store8(out + (size_t)row * p.ldo + n0 + 8, hi);
-        } else {
-          for (int j = 0; j < 16; ++j) {
-            const int n = n0 + j;
-            if (n < N) {
-              float x = v[j];
-              if (resid) x += Num<T>::to_f(resid[(size_t)row * p.ldr + n]);
-              out[(size_t)row * p.ldo + n] = Num<T>::from_f(x);
-            }
+        for (int j = 0; j < 16; ++j) {
+          const int n = n0 + j;
+          if (n < N) {
+            float x = v[j];
+            if (resid) x += Num<T>::to_f(resid[(size_t)row * p.ldr + n]);
+            out[(size_t)row * p.ldo + n] = Num<T>::from_f(x);
           }
         }
       }
@@ -289,8 +399,16 @@ static int launch_ps(const RfGemm* g, int bn, cudaStream_t stream) {
   p.act = g->act; p.dual_offset = g->dual_offset; p.dual_tiles = ceil_div(g->N, 128);
   p.tiles_m = ceil_div(g->M, kPsBM * MT); p.tiles_n = ceil_div(g->N, bn);
   const int stage_bytes = MT * kPsATile + (DUAL ? 2 : 1) * bn * kPsBK * 2;
-  const int ctl_bytes = (int)sizeof(GemmPsCtl) + 1024;
-  p.stages = std::min(kPsMaxStages, (224 * 1024 - ctl_bytes) / stage_bytes);
+  {
+    // a band of activation rows of about 16 MB: it and a weight matrix of a few tens of MB stay in L2 together
+    const int64_t row_tile_bytes = (int64_t)kPsBM * MT * g->K * 2;
+    p.band = (int)std::max<int64_t>(1, std::min<int64_t>(p.tiles_m, (16ll << 20) / std::max<int64_t>(1, row_tile_bytes)));
+    static const int pf_kb = [] { const char* e = getenv("RF_GEMM_L2_PREFETCH_KB"); return e ? atoi(e) : 0; }();
+    p.pf_blocks = std::min(16, pf_kb * 1024 / stage_bytes);
+  }
+  const int ctl_bytes = (int)sizeof(GemmPsCtl) + 1024 /*alignment slack*/ + 4 * MT * kPsEpiBytes;
+  p.stages = std::min(kPsMaxStages, (227 * 1024 - ctl_bytes) / stage_bytes);
+  RF_REQUIRE(p.stages >= 2, "persistent GEMM: a %d-byte stage does not fit twice in shared memory", stage_bytes);
   const size_t smem = (size_t)p.stages * stage_bytes + ctl_bytes;
   const int grid = std::min(p.tiles_m * p.tiles_n, sm_count());
   RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(grid), dim3(64 + 128 * MT), smem, stream, 1, tmA, p));

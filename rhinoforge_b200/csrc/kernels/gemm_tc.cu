@@ -48,7 +48,6 @@ struct GemmTcParams {
   const uint8_t* w_packed;  // tile-major weight image (null: row-major weights through the tensor maps)
   int kb_total;             // k blocks of the whole weight (row-tile stride of the packed image)
   int dual_tiles;           // row tiles of the first (gate) section
-  int pf_blocks;            // packed weights: k blocks prefetched into L2 ahead of the shared-memory ring
   int ar_two_shot;    // large-M path: 16-bit reduce-scatter to the tile's owner, then broadcast
   int ar_flag2_base;  // first flag of the "result has landed" range
 };
@@ -195,25 +194,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (SWAP) tma_load_2d(st + kATiles * kATileBytes, &tmB, &ctl->full[s], kc, b0);
       else tma_load_2d(st, &tmA, &ctl->full[s], kc, a0);
     };
-    // L2 prefetch of the weight blocks of k block i (packed layout only): a weight-streaming GEMM is bound by
-    // the bytes it keeps in flight towards DRAM, and the ring (two to four stages) is far too shallow for that
-    auto prefetch_weights = [&](int i) {
-      constexpr uint32_t kBlk = W8 ? (uint32_t)(kBM * kBK) : (uint32_t)kATileBytes;
-      const int rt0 = (SWAP ? a0 : b0) / kBM;
-      const int nsub = SWAP ? 1 : bn / kBM;
-#pragma unroll
-      for (int wt = 0; wt < kWTiles; ++wt)
-        for (int sub = 0; sub < nsub; ++sub)
-          bulk_prefetch_l2(p.w_packed + ((size_t)(rt0 + sub + wt * p.dual_tiles) * p.kb_total + (kb0 + i)) * kBlk, kBlk);
-    };
-    const int pf = p.w_packed ? p.pf_blocks : 0;
     // weights never depend on the previous kernel: fill the ring with them first
     const int pre = min(p.stages, kb_count);
     for (int i = 0; i < pre; ++i) {
       mbar_arrive_expect_tx(&ctl->full[i], tx);
       load_weights(i, i);
     }
-    for (int i = pre; i < min(pre + pf, kb_count); ++i) prefetch_weights(i);
     pdl_wait();
     for (int i = 0; i < pre; ++i) load_acts(i, i);
     issued = pre;
@@ -229,7 +215,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_arrive_expect_tx(&ctl->full[s], tx);
       load_weights(i, s);
       load_acts(i, s);
-      if (pf > 0 && i + pf < kb_count) prefetch_weights(i + pf);
       issued = i + 1;
     }
     if (!ok) {
@@ -977,14 +962,6 @@ static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream)
   p.w_packed = g->w_packed ? reinterpret_cast<const uint8_t*>(g->w) : nullptr;
   p.kb_total = pl.k_blocks;
   p.dual_tiles = ceil_div(g->N, kBM);
-  {
-    // weight-streaming shapes (tokens on the MMA N axis): up to 256 KB per CTA, 48 MB over the grid
-    static const int pf_kb = [] { const char* e = getenv("RF_GEMM_L2_PREFETCH_KB"); return e ? atoi(e) : 256; }();
-    const int64_t ctas = std::min<int64_t>((int64_t)pl.grid_x * pl.grid_y * pl.splits, 2 * sm_count());   // resident at once
-    const int64_t per_cta = std::min<int64_t>((int64_t)pf_kb * 1024, (48ll << 20) / std::max<int64_t>(1, ctas));
-    const int64_t kblock_bytes = (int64_t)(DUAL ? 2 : 1) * (W8 ? kBM * kBK : kATileBytes);
-    p.pf_blocks = (SWAP && g->w_packed) ? (int)std::min<int64_t>(64, per_cta / kblock_bytes) : 0;
-  }
   p.ar_two_shot = (g->ar_world > 1 && !SWAP && g->M > 256) ? 1 : 0;
   p.ar_flag2_base = g->ar_flag_count / 2;
   RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.grid_x, pl.grid_y, pl.splits), dim3(W8 ? 256 : 128), pl.smem_bytes, stream,
