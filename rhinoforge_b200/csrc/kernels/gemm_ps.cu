@@ -39,6 +39,7 @@ struct GemmPsParams {
   int tiles_m, tiles_n;   // tiles_m counts tiles of 128*MT rows
   int band;               // row tiles per band of the tile order
   int pf_blocks;          // k blocks prefetched into L2 ahead of the ring
+  int epi_direct;         // 1: store straight from registers (no shared-memory transpose)
 };
 
 // Tile order: bands of `band` row tiles; inside a band the row index runs fastest and the weight panel
@@ -262,7 +263,7 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
       const int n_base = tn * bn;
       const uint32_t acc = lane_base + (uint32_t)(b * acc_cols + half * half_cols);
       const float rs = (p.row_scale && row < M) ? p.row_scale[row] : 1.f;
-      if (vec_ok) {
+      if (vec_ok && !p.epi_direct) {
         // Coalesced path.  A thread owns one accumulator row, so storing from its registers would write 16
         // bytes to each of 32 different rows per instruction (one mostly empty 128-byte line each).  Instead
         // the warp parks 64 columns of finished 16-bit results in shared memory (row r at r*128, its 16-byte
@@ -359,12 +360,27 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
           }
           v[j] = apply_act(p.act, vg, vu);
         }
-        for (int j = 0; j < 16; ++j) {
-          const int n = n0 + j;
-          if (n < N) {
-            float x = v[j];
-            if (resid) x += Num<T>::to_f(resid[(size_t)row * p.ldr + n]);
-            out[(size_t)row * p.ldo + n] = Num<T>::from_f(x);
+        if (vec_ok && n0 + 16 <= N) {
+          if (resid) {
+            float r0[8], r1[8];
+            load8(resid + (size_t)row * p.ldr + n0, r0);
+            load8(resid + (size_t)row * p.ldr + n0 + 8, r1);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { v[j] += r0[j]; v[8 + j] += r1[j]; }
+          }
+          float lo[8], hi[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
+          store8(out + (size_t)row * p.ldo + n0, lo);
+          store8(out + (size_t)row * p.ldo + n0 + 8, hi);
+        } else {
+          for (int j = 0; j < 16; ++j) {
+            const int n = n0 + j;
+            if (n < N) {
+              float x = v[j];
+              if (resid) x += Num<T>::to_f(resid[(size_t)row * p.ldr + n]);
+              out[(size_t)row * p.ldo + n] = Num<T>::from_f(x);
+            }
           }
         }
       }
@@ -403,6 +419,10 @@ static int launch_ps(const RfGemm* g, int bn, cudaStream_t stream) {
     // a band of activation rows of about 16 MB: it and a weight matrix of a few tens of MB stay in L2 together
     const int64_t row_tile_bytes = (int64_t)kPsBM * MT * g->K * 2;
     p.band = (int)std::max<int64_t>(1, std::min<int64_t>(p.tiles_m, (16ll << 20) / std::max<int64_t>(1, row_tile_bytes)));
+    static const int band_env = [] { const char* e = getenv("RF_GEMM_PS_BAND"); return e ? atoi(e) : 0; }();
+    if (band_env > 0) p.band = std::min(p.tiles_m, band_env);
+    static const int epi_env = [] { const char* e = getenv("RF_GEMM_PS_EPI_DIRECT"); return e ? atoi(e) : 0; }();
+    p.epi_direct = epi_env;
     static const int pf_kb = [] { const char* e = getenv("RF_GEMM_L2_PREFETCH_KB"); return e ? atoi(e) : 0; }();
     p.pf_blocks = std::min(16, pf_kb * 1024 / stage_bytes);
   }

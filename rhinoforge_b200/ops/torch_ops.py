@@ -6,9 +6,10 @@ plain PyTorch implementation so that host-only tooling and tests can call the sa
 argument order follow the reference's schema list (``src/core/rpu_dispatch_registrations.inc:5-852``):
 ``rms_norm``, ``apply_rotary_pos_emb``, ``scaled_dot_product_attention_unified`` (layout ``[B, S, H, D]``),
 ``gather_embedding``, ``assemble_inputs_embeds``, ``cast_uint8_fp16``, ``linear_into``,
-``lm_head_logits_top1``, ``argmax_lastdim_host``, ``moe_select``, ``gdn_recurrent``, ``reset_graph_cache``.
-Model handle families (``causal_decoder_*`` ...) are Python objects here (``runtime.engine.DecoderEngine``,
-``runtime.stack.NativeStack``), not integer handles behind dispatcher ops.
+``assemble_inputs_embeds_rev``, ``cast_uint8_fp16_into``, ``conv2d_mc_nhwc``, ``lm_head_logits_top1``,
+``argmax_lastdim_host``, ``moe_select``, ``reset_graph_cache`` and the ``spm_alloc_*`` controls (the scratch-pad
+planner they steer does not exist on this hardware: they report the activation-arena figures instead).
+The model handle families (``causal_decoder_*`` ...) are registered by :mod:`rhinoforge_b200.ops.handle_ops`.
 """
 from __future__ import annotations
 
@@ -81,6 +82,60 @@ def _assemble_inputs_embeds(text: torch.Tensor, vision: torch.Tensor, rows: torc
     return out
 
 
+def _assemble_inputs_embeds_rev(embeds: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    """The inverse gather: rows ``rows[i]`` of ``embeds [T, H]`` as a ``[len(rows), H]`` tensor (vision rows read back)."""
+    if not embeds.is_cuda:
+        return embeds[rows.long()].clone()
+    return _k().embedding(embeds.contiguous(), rows.reshape(-1).to(torch.int32).contiguous())
+
+
+def _cast_uint8_fp16_into(x: torch.Tensor, out: torch.Tensor, scale: float = 1.0, shift: float = 0.0) -> torch.Tensor:
+    out.copy_(_cast_uint8_fp16(x, scale, shift).view_as(out))
+    return out
+
+
+def _conv2d_mc_nhwc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], stride: int = 1,
+                    padding: int = 0) -> torch.Tensor:
+    """``x [B, H, W, C]`` (channels last) with ``weight [O, C, kh, kw]`` -> ``[B, H', W', O]``.  A non-overlapping
+    convolution (stride == kernel, no padding: every patch embedding) is one GEMM over the patch matrix; other
+    geometries are off the hot path and go to the framework's convolution."""
+    O, Cc, kh, kw = weight.shape
+    B, Hh, Ww, _ = x.shape
+    if x.is_cuda and stride == kh == kw and padding == 0 and Hh % kh == 0 and Ww % kw == 0 and (Cc * kh * kw) % 8 == 0:
+        gh, gw = Hh // kh, Ww // kw
+        cols = x.reshape(B, gh, kh, gw, kw, Cc).permute(0, 1, 3, 5, 2, 4).reshape(B * gh * gw, Cc * kh * kw).contiguous()
+        y = _k().gemm(cols, weight.reshape(O, -1).to(x.dtype).contiguous(), bias=None if bias is None else bias.to(x.dtype))
+        return y.view(B, gh, gw, O)
+    y = torch.nn.functional.conv2d(x.permute(0, 3, 1, 2), weight.to(x.dtype), None if bias is None else bias.to(x.dtype),
+                                   stride=stride, padding=padding)
+    return y.permute(0, 2, 3, 1).contiguous()
+
+
+_SPM = {"initialised": False, "temporary_resets": 0, "full_resets": 0}
+
+
+def _spm_alloc_init() -> None:
+    _SPM["initialised"] = True
+
+
+def _spm_alloc_reset_temporary() -> None:
+    _SPM["temporary_resets"] += 1
+
+
+def _spm_alloc_reset_all() -> None:
+    _SPM["full_resets"] += 1
+
+
+def _spm_alloc_dump() -> str:
+    """One line of allocator state.  There is no scratch-pad planner here: activations live in one arena per native
+    handle, sized at creation, and the caching allocator owns device memory."""
+    import json
+    dev = {}
+    if torch.cuda.is_available():
+        dev = {"allocated_bytes": int(torch.cuda.memory_allocated()), "reserved_bytes": int(torch.cuda.memory_reserved())}
+    return json.dumps({**_SPM, **dev})
+
+
 def _cast_uint8_fp16(x: torch.Tensor, scale: float = 1.0, shift: float = 0.0) -> torch.Tensor:
     if not x.is_cuda:
         return (x.float() * scale + shift).half()
@@ -137,6 +192,13 @@ def register() -> bool:
         ("gather_embedding(Tensor table, Tensor ids) -> Tensor", _gather_embedding),
         ("assemble_inputs_embeds(Tensor text, Tensor vision, Tensor rows) -> Tensor", _assemble_inputs_embeds),
         ("cast_uint8_fp16(Tensor x, float scale=1.0, float shift=0.0) -> Tensor", _cast_uint8_fp16),
+        ("assemble_inputs_embeds_rev(Tensor embeds, Tensor rows) -> Tensor", _assemble_inputs_embeds_rev),
+        ("cast_uint8_fp16_into(Tensor x, Tensor(a!) out, float scale=1.0, float shift=0.0) -> Tensor(a!)", _cast_uint8_fp16_into),
+        ("conv2d_mc_nhwc(Tensor x, Tensor weight, Tensor? bias, int stride=1, int padding=0) -> Tensor", _conv2d_mc_nhwc),
+        ("spm_alloc_init() -> ()", _spm_alloc_init),
+        ("spm_alloc_reset_temporary() -> ()", _spm_alloc_reset_temporary),
+        ("spm_alloc_reset_all() -> ()", _spm_alloc_reset_all),
+        ("spm_alloc_dump() -> str", _spm_alloc_dump),
         ("linear_into(Tensor x, Tensor weight, Tensor? bias, Tensor(a!) out) -> Tensor(a!)", _linear_into),
         ("lm_head_logits_top1(Tensor hidden, Tensor weight) -> Tensor", _lm_head_logits_top1),
         ("argmax_lastdim_host(Tensor x) -> Tensor", _argmax_lastdim_host),
@@ -151,6 +213,8 @@ def register() -> bool:
         from ..graph import reset_graph_cache
         reset_graph_cache()
     lib.impl("reset_graph_cache", _reset, "CompositeExplicitAutograd")
+    from . import handle_ops
+    handle_ops.register(lib)
     _LIB = lib
     return True
 

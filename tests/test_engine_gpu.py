@@ -108,3 +108,44 @@ def test_qwen3_0p6b_shape_greedy_matches_fp32_oracle():
     _agree(toks, rt, rl, 0.02)
     eng.check_status()
     eng.close()
+
+
+def test_causal_decoder_handle_ops_match_the_engine():
+    """``torch.ops.rpu.causal_decoder_*``: create from an HF-style JSON config, install weights by name, feed input
+    embeddings at position 0 and then one more row at the cached position; logits equal the engine's own."""
+    import json
+    from rhinoforge_b200.models.decoder import random_state_dict, tiny_config
+    from rhinoforge_b200.runtime.engine import DecoderEngine
+    cfg = tiny_config()
+    sd = random_state_dict(cfg, seed=0, dtype=torch.float16, norm_jitter=0.05)
+    get = lambda n: sd[n] if n in sd else sd["model.embed_tokens.weight"]
+    eng = DecoderEngine(cfg, get, dtype=torch.float16, max_batch=2, max_seq_len=128)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab_size, (24,), generator=g) for _ in range(2)]
+    _, want = eng.prefill(prompts, return_logits=True)
+    nxt = [torch.randint(0, cfg.vocab_size, (1,), generator=g) for _ in range(2)]
+    _, want2 = eng.extend(nxt, return_logits=True)
+    want, want2 = want.clone(), want2.clone()
+    eng.close()
+
+    hf = dict(model_type="qwen3", vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
+              intermediate_size=cfg.intermediate_size, num_hidden_layers=cfg.num_layers, num_attention_heads=cfg.num_heads,
+              num_key_value_heads=cfg.num_kv_heads, head_dim=cfg.head_dim, rms_norm_eps=cfg.rms_eps, rope_theta=cfg.rope_theta,
+              tie_word_embeddings=cfg.tie_embeddings, max_position_embeddings=cfg.max_position, rpu_max_batch=2,
+              rpu_max_seq_len=128)
+    ops = torch.ops.rpu
+    h = ops.causal_decoder_create(json.dumps(hf))
+    names = list(sd)
+    if "lm_head.weight" not in sd:
+        names.append("lm_head.weight")
+    ops.causal_decoder_set_weights(h, names, [get(n) for n in names])
+    emb = sd["model.embed_tokens.weight"].cuda()
+    x = torch.stack([emb[p.cuda()] for p in prompts])
+    got = ops.causal_decoder_forward(h, x, [], [], None, 0, True, None, None, None, None)
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-3, atol=2e-3)
+    x2 = torch.stack([emb[p.cuda()] for p in nxt])
+    got2 = ops.causal_decoder_forward(h, x2, [], [], None, 24, True, None, None, None, None)
+    torch.testing.assert_close(got2.float(), want2.float(), rtol=2e-3, atol=2e-3)
+    with pytest.raises(Exception, match="does not match the cached lengths"):
+        ops.causal_decoder_forward(h, x2, [], [], None, 7, True, None, None, None, None)
+    ops.causal_decoder_destroy(h)

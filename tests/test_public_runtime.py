@@ -185,3 +185,49 @@ def test_torch_ops_rpu_namespace_is_registered_and_runs_on_cpu():
     ids, w = ops.moe_select(torch.randn(4, 8), None, 2, 1.0)
     assert ids.shape == (4, 2) and torch.allclose(w.sum(-1), torch.ones(4), atol=1e-5)
     assert torch.equal(ops.argmax_lastdim_host(torch.tensor([[1.0, 3.0, 2.0]])), torch.tensor([1], dtype=torch.int32))
+
+
+def test_handle_family_ops_exist_and_keep_their_books_on_cpu():
+    """Every in-scope handle family has create / set_weights / forward / destroy under ``torch.ops.rpu``; handles are
+    typed (a vision handle is refused by a decoder op), destroyed handles are gone, forward before weights fails."""
+    import json
+    import pytest
+    import torch
+    import rhinoforge_b200  # noqa: F401
+    from rhinoforge_b200.ops import handle_ops
+    from rhinoforge_b200.runtime.errors import RPUBackendError, RPUConfigError
+    ops = torch.ops.rpu
+    for fam in handle_ops.FAMILIES:
+        for suffix in ("create", "set_weights", "forward", "destroy"):
+            assert hasattr(ops, f"{fam}_{suffix}"), f"{fam}_{suffix}"
+    for name in ("causal_decoder_set_weights_w8a16", "qwen3_5_set_weights_w8a16", "pi05_denoise_loop_forward",
+                 "assemble_inputs_embeds_rev", "cast_uint8_fp16_into", "conv2d_mc_nhwc", "spm_alloc_init",
+                 "spm_alloc_reset_temporary", "spm_alloc_reset_all", "spm_alloc_dump"):
+        assert hasattr(ops, name), name
+    h = ops.siglip_create(json.dumps({"hidden_size": 64}))
+    d = ops.causal_decoder_create("{}")
+    assert handle_ops.live_handles()[h] == "siglip" and handle_ops.live_handles()[d] == "causal_decoder"
+    with pytest.raises(RPUBackendError, match="belongs to family"):
+        ops.causal_decoder_destroy(h)
+    with pytest.raises(RPUBackendError, match="no weights yet"):
+        ops.siglip_forward(h, torch.zeros(1, 3, 8, 8))
+    with pytest.raises(RPUConfigError):
+        ops.pi05_create("{not json")
+    ops.siglip_destroy(h)
+    ops.causal_decoder_destroy(d)
+    assert h not in handle_ops.live_handles() and d not in handle_ops.live_handles()
+    with pytest.raises(RPUBackendError, match="unknown or destroyed"):
+        ops.siglip_destroy(h)
+    # stand-alone additions on CPU tensors
+    x = torch.randn(2, 4, 4, 8)
+    w = torch.randn(6, 8, 2, 2)
+    y = ops.conv2d_mc_nhwc(x, w, None, 2, 0)
+    ref = torch.nn.functional.conv2d(x.permute(0, 3, 1, 2), w, stride=2).permute(0, 2, 3, 1)
+    assert torch.allclose(y, ref, atol=1e-5)
+    e = torch.randn(5, 3)
+    assert torch.equal(ops.assemble_inputs_embeds_rev(e, torch.tensor([4, 0])), e[[4, 0]])
+    out = torch.empty(2, 2, dtype=torch.float16)
+    ops.cast_uint8_fp16_into(torch.tensor([[0, 255], [1, 2]], dtype=torch.uint8), out, 1.0 / 255.0, 0.0)
+    assert abs(float(out[0, 1]) - 1.0) < 1e-3
+    ops.spm_alloc_init(); ops.spm_alloc_reset_temporary(); ops.spm_alloc_reset_all()
+    assert json.loads(ops.spm_alloc_dump())["initialised"] is True
