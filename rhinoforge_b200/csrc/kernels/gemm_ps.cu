@@ -27,7 +27,6 @@ constexpr int kPsBM = 128, kPsBK = 64;
 constexpr int kPsATile = kPsBM * kPsBK * 2;      // 16 KB
 constexpr int kPsBlock = 128 * kPsBK * 2;        // one packed weight block
 constexpr int kPsMaxStages = 8;
-constexpr int kPsEpiBytes = 32 * 64 * 2;          // 32 rows x 64 columns of 16-bit results per epilogue warp
 
 struct GemmPsParams {
   void* out; int64_t ldo;
@@ -39,7 +38,6 @@ struct GemmPsParams {
   int tiles_m, tiles_n;   // tiles_m counts tiles of 128*MT rows
   int band;               // row tiles per band of the tile order
   int pf_blocks;          // k blocks prefetched into L2 ahead of the ring
-  int epi_direct;         // 1: store straight from registers (no shared-memory transpose)
 };
 
 // Tile order: bands of `band` row tiles; inside a band the row index runs fastest and the weight panel
@@ -75,9 +73,7 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
   const int half_cols = kW * bn;                           // TMEM columns of one 128-row half
   const int acc_cols = MT * half_cols;                     // ... of one accumulator buffer
   const int nbuf = 2 * acc_cols <= 512 ? 2 : 1;
-  // after the ring: one 4 KB transpose buffer per epilogue warp, then the control block
-  uint8_t* epi_stage = smem + (size_t)p.stages * stage_bytes;
-  GemmPsCtl* ctl = reinterpret_cast<GemmPsCtl*>(epi_stage + 4 * MT * kPsEpiBytes);
+  GemmPsCtl* ctl = reinterpret_cast<GemmPsCtl*>(smem + (size_t)p.stages * stage_bytes);
   const int tiles = p.tiles_m * p.tiles_n;
 
   if (tid == 0) {
@@ -263,123 +259,62 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
       const int n_base = tn * bn;
       const uint32_t acc = lane_base + (uint32_t)(b * acc_cols + half * half_cols);
       const float rs = (p.row_scale && row < M) ? p.row_scale[row] : 1.f;
-      if (vec_ok && !p.epi_direct) {
-        // Coalesced path.  A thread owns one accumulator row, so storing from its registers would write 16
-        // bytes to each of 32 different rows per instruction (one mostly empty 128-byte line each).  Instead
-        // the warp parks 64 columns of finished 16-bit results in shared memory (row r at r*128, its 16-byte
-        // chunks XOR-swizzled by r%8: conflict-free both ways) and writes them back transposed: eight lanes
-        // per row, four whole 128-byte lines per instruction; the residual is read the same way.
-        uint8_t* stg = epi_stage + (size_t)(warp - 2) * kPsEpiBytes;
-        const int row0 = (tm * MT + half) * kPsBM + quarter * 32;
-        for (int c0 = 0; c0 < bn; c0 += 64) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int c = c0 + q * 16;
-            uint32_t rg[16], ru[16];
-            tmem_ld16(acc + c, rg);
-            if (DUAL) tmem_ld16(acc + bn + c, ru);
-            tmem_ld_wait();
-            const int n0 = n_base + c;
-            float v[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int n = n0 + j;
-              float vg = __uint_as_float(rg[j]) * rs, vu = DUAL ? __uint_as_float(ru[j]) * rs : 0.f;
-              if (n < N) {
-                if (scale) {
-                  vg *= Num<T>::to_f(scale[n]);
-                  if (DUAL) vu *= Num<T>::to_f(scale[p.dual_offset + n]);
-                }
-                if (bias) {
-                  vg += Num<T>::to_f(bias[n]);
-                  if (DUAL) vu += Num<T>::to_f(bias[p.dual_offset + n]);
-                }
-              }
-              v[j] = apply_act(p.act, vg, vu);
-            }
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              float w8[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) w8[j] = v[hh * 8 + j];
-              const int chunk = q * 2 + hh;
-              store8(reinterpret_cast<T*>(stg + lane * 128 + ((chunk ^ (lane & 7)) << 4)), w8);
-            }
-          }
-          __syncwarp();
-#pragma unroll
-          for (int t = 0; t < 8; ++t) {
-            const int rr = t * 4 + (lane >> 3), chunk = lane & 7;
-            const int grow = row0 + rr, n = n_base + c0 + chunk * 8;
-            if (grow < M && n < N) {
-              const T* sp = reinterpret_cast<const T*>(stg + rr * 128 + ((chunk ^ (rr & 7)) << 4));
-              if (n + 8 <= N) {
-                if (resid) {
-                  float a8[8], r8[8];
-                  load8(sp, a8);
-                  load8(resid + (size_t)grow * p.ldr + n, r8);
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) a8[j] += r8[j];
-                  store8(out + (size_t)grow * p.ldo + n, a8);
-                } else {
-                  *reinterpret_cast<uint4*>(out + (size_t)grow * p.ldo + n) = *reinterpret_cast<const uint4*>(sp);
-                }
-              } else {
-                for (int j = 0; n + j < N; ++j) {
-                  float x = Num<T>::to_f(sp[j]);
-                  if (resid) x += Num<T>::to_f(resid[(size_t)grow * p.ldr + n + j]);
-                  out[(size_t)grow * p.ldo + n + j] = Num<T>::from_f(x);
-                }
-              }
-            }
-          }
-          __syncwarp();
-        }
-      } else
-      for (int c = 0; c < bn; c += 16) {
-        uint32_t rg[16], ru[16];
-        tmem_ld16(acc + c, rg);
-        if (DUAL) tmem_ld16(acc + bn + c, ru);
+      // 64 accumulator columns (32 + 32 of the two GLU halves) per tensor-memory round trip: a load's latency
+      // is long while the tensor core is accumulating into the other buffer, so few large loads beat many small
+      // ones.  Results are stored straight from registers; a shared-memory transpose for wider stores measured
+      // 35 % slower (this loop is bound by its own instruction chain, not by store efficiency).
+      constexpr int kLd = DUAL ? 32 : 64;                  // output columns per round trip
+      for (int c0 = 0; c0 < bn; c0 += kLd) {
+        uint32_t ra[32], rb[32];
+        tmem_ld32(acc + c0, ra);
+        if (DUAL) tmem_ld32(acc + bn + c0, rb);
+        else tmem_ld32(acc + c0 + 32, rb);
         tmem_ld_wait();
-        const int n0 = n_base + c;
-        if (row >= M || n0 >= N) continue;
-        float v[16];
+        if (row >= M) continue;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int n = n0 + j;
-          float vg = __uint_as_float(rg[j]) * rs, vu = DUAL ? __uint_as_float(ru[j]) * rs : 0.f;
-          if (n < N) {
-            if (scale) {
-              vg *= Num<T>::to_f(scale[n]);
-              if (DUAL) vu *= Num<T>::to_f(scale[p.dual_offset + n]);
-            }
-            if (bias) {
-              vg += Num<T>::to_f(bias[n]);
-              if (DUAL) vu += Num<T>::to_f(bias[p.dual_offset + n]);
-            }
-          }
-          v[j] = apply_act(p.act, vg, vu);
-        }
-        if (vec_ok && n0 + 16 <= N) {
-          if (resid) {
-            float r0[8], r1[8];
-            load8(resid + (size_t)row * p.ldr + n0, r0);
-            load8(resid + (size_t)row * p.ldr + n0 + 8, r1);
+        for (int q = 0; q < kLd / 16; ++q) {
+          const int n0 = n_base + c0 + q * 16;
+          if (n0 >= N) break;
+          float v[16];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { v[j] += r0[j]; v[8 + j] += r1[j]; }
-          }
-          float lo[8], hi[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
-          store8(out + (size_t)row * p.ldo + n0, lo);
-          store8(out + (size_t)row * p.ldo + n0 + 8, hi);
-        } else {
           for (int j = 0; j < 16; ++j) {
             const int n = n0 + j;
+            const int i = q * 16 + j;                      // column inside this round trip
+            float vg = __uint_as_float(DUAL ? ra[i & 31] : (i < 32 ? ra[i & 31] : rb[i & 31])) * rs;
+            float vu = DUAL ? __uint_as_float(rb[i & 31]) * rs : 0.f;
             if (n < N) {
-              float x = v[j];
-              if (resid) x += Num<T>::to_f(resid[(size_t)row * p.ldr + n]);
-              out[(size_t)row * p.ldo + n] = Num<T>::from_f(x);
+              if (scale) {
+                vg *= Num<T>::to_f(scale[n]);
+                if (DUAL) vu *= Num<T>::to_f(scale[p.dual_offset + n]);
+              }
+              if (bias) {
+                vg += Num<T>::to_f(bias[n]);
+                if (DUAL) vu += Num<T>::to_f(bias[p.dual_offset + n]);
+              }
+            }
+            v[j] = apply_act(p.act, vg, vu);
+          }
+          if (vec_ok && n0 + 16 <= N) {
+            if (resid) {
+              float r0[8], r1[8];
+              load8(resid + (size_t)row * p.ldr + n0, r0);
+              load8(resid + (size_t)row * p.ldr + n0 + 8, r1);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { v[j] += r0[j]; v[8 + j] += r1[j]; }
+            }
+            float lo[8], hi[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
+            store8(out + (size_t)row * p.ldo + n0, lo);
+            store8(out + (size_t)row * p.ldo + n0 + 8, hi);
+          } else {
+            for (int j = 0; j < 16; ++j) {
+              const int n = n0 + j;
+              if (n < N) {
+                float x = v[j];
+                if (resid) x += Num<T>::to_f(resid[(size_t)row * p.ldr + n]);
+                out[(size_t)row * p.ldo + n] = Num<T>::from_f(x);
+              }
             }
           }
         }
@@ -421,12 +356,10 @@ static int launch_ps(const RfGemm* g, int bn, cudaStream_t stream) {
     p.band = (int)std::max<int64_t>(1, std::min<int64_t>(p.tiles_m, (16ll << 20) / std::max<int64_t>(1, row_tile_bytes)));
     static const int band_env = [] { const char* e = getenv("RF_GEMM_PS_BAND"); return e ? atoi(e) : 0; }();
     if (band_env > 0) p.band = std::min(p.tiles_m, band_env);
-    static const int epi_env = [] { const char* e = getenv("RF_GEMM_PS_EPI_DIRECT"); return e ? atoi(e) : 0; }();
-    p.epi_direct = epi_env;
     static const int pf_kb = [] { const char* e = getenv("RF_GEMM_L2_PREFETCH_KB"); return e ? atoi(e) : 0; }();
     p.pf_blocks = std::min(16, pf_kb * 1024 / stage_bytes);
   }
-  const int ctl_bytes = (int)sizeof(GemmPsCtl) + 1024 /*alignment slack*/ + 4 * MT * kPsEpiBytes;
+  const int ctl_bytes = (int)sizeof(GemmPsCtl) + 1024 /*alignment slack*/;
   p.stages = std::min(kPsMaxStages, (227 * 1024 - ctl_bytes) / stage_bytes);
   RF_REQUIRE(p.stages >= 2, "persistent GEMM: a %d-byte stage does not fit twice in shared memory", stage_bytes);
   const size_t smem = (size_t)p.stages * stage_bytes + ctl_bytes;
