@@ -375,16 +375,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // over distributed shared memory in split order and finishes them.
     float* part = reinterpret_cast<float*>(smem);
     if (!aborted) {
-      for (int c = 0; c < bn; c += 16) {
-        uint32_t rg[16], ru[16];
-        tmem_ld16(trow + c, rg);
-        if (DUAL) tmem_ld16(trow + bn + c, ru);
-        tmem_ld_wait();
-        if (epi) {
+      if ((bn & 31) == 0) {
+        // 32 columns (of each accumulator) per tensor-memory round trip: the round trip, not the copy, is the cost
+        for (int c = 0; c < bn; c += 32) {
+          uint32_t rg[32], ru[32];
+          tmem_ld32(trow + c, rg);
+          if (DUAL) tmem_ld32(trow + bn + c, ru);
+          tmem_ld_wait();
+          if (epi) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            part[(c + j) * kBM + tid] = __uint_as_float(rg[j]);
-            if (DUAL) part[(bn + c + j) * kBM + tid] = __uint_as_float(ru[j]);
+            for (int j = 0; j < 32; ++j) {
+              part[(c + j) * kBM + tid] = __uint_as_float(rg[j]);
+              if (DUAL) part[(bn + c + j) * kBM + tid] = __uint_as_float(ru[j]);
+            }
+          }
+        }
+      } else {
+        for (int c = 0; c < bn; c += 16) {
+          uint32_t rg[16], ru[16];
+          tmem_ld16(trow + c, rg);
+          if (DUAL) tmem_ld16(trow + bn + c, ru);
+          tmem_ld_wait();
+          if (epi) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              part[(c + j) * kBM + tid] = __uint_as_float(rg[j]);
+              if (DUAL) part[(bn + c + j) * kBM + tid] = __uint_as_float(ru[j]);
+            }
           }
         }
       }
