@@ -259,29 +259,22 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
       const int n_base = tn * bn;
       const uint32_t acc = lane_base + (uint32_t)(b * acc_cols + half * half_cols);
       const float rs = (p.row_scale && row < M) ? p.row_scale[row] : 1.f;
-      // 64 accumulator columns (32 + 32 of the two GLU halves) per tensor-memory round trip: a load's latency
-      // is long while the tensor core is accumulating into the other buffer, so few large loads beat many small
-      // ones.  Results are stored straight from registers; a shared-memory transpose for wider stores measured
-      // 35 % slower (this loop is bound by its own instruction chain, not by store efficiency).
-      constexpr int kLd = DUAL ? 32 : 64;                  // output columns per round trip
-      for (int c0 = 0; c0 < bn; c0 += kLd) {
-        uint32_t ra[32], rb[32];
-        tmem_ld32(acc + c0, ra);
-        if (DUAL) tmem_ld32(acc + bn + c0, rb);
-        else tmem_ld32(acc + c0 + 32, rb);
-        tmem_ld_wait();
-        if (row >= M) continue;
+      // Results go straight from registers to global memory, 16 columns (of each accumulator) per tensor-memory
+      // round trip for one accumulator and 32 for the GLU pair.  Measured alternatives on 8192 x 4096 x 4096:
+      // 64-column round trips 30 % slower, a shared-memory transpose for full-line stores 35 % slower - long
+      // instruction bursts of the epilogue warps delay the single MMA-issuing lane that shares their schedulers,
+      // so the loop is kept short and, where the epilogue is a plain conversion, free of per-element math.
+      const bool plain = !DUAL && !scale && !bias && !p.row_scale && p.act == kActNone;
+      auto finish16 = [&](int n0, const uint32_t* g16, const uint32_t* u16) {
+        float v[16];
+        if (plain) {
 #pragma unroll
-        for (int q = 0; q < kLd / 16; ++q) {
-          const int n0 = n_base + c0 + q * 16;
-          if (n0 >= N) break;
-          float v[16];
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(g16[j]);
+        } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int n = n0 + j;
-            const int i = q * 16 + j;                      // column inside this round trip
-            float vg = __uint_as_float(DUAL ? ra[i & 31] : (i < 32 ? ra[i & 31] : rb[i & 31])) * rs;
-            float vu = DUAL ? __uint_as_float(rb[i & 31]) * rs : 0.f;
+            float vg = __uint_as_float(g16[j]) * rs, vu = DUAL ? __uint_as_float(u16[j]) * rs : 0.f;
             if (n < N) {
               if (scale) {
                 vg *= Num<T>::to_f(scale[n]);
@@ -294,29 +287,51 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
             }
             v[j] = apply_act(p.act, vg, vu);
           }
-          if (vec_ok && n0 + 16 <= N) {
-            if (resid) {
-              float r0[8], r1[8];
-              load8(resid + (size_t)row * p.ldr + n0, r0);
-              load8(resid + (size_t)row * p.ldr + n0 + 8, r1);
+        }
+        if (vec_ok && n0 + 16 <= N) {
+          if (resid) {
+            float r0[8], r1[8];
+            load8(resid + (size_t)row * p.ldr + n0, r0);
+            load8(resid + (size_t)row * p.ldr + n0 + 8, r1);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) { v[j] += r0[j]; v[8 + j] += r1[j]; }
-            }
-            float lo[8], hi[8];
+            for (int j = 0; j < 8; ++j) { v[j] += r0[j]; v[8 + j] += r1[j]; }
+          }
+          float lo[8], hi[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
-            store8(out + (size_t)row * p.ldo + n0, lo);
-            store8(out + (size_t)row * p.ldo + n0 + 8, hi);
-          } else {
-            for (int j = 0; j < 16; ++j) {
-              const int n = n0 + j;
-              if (n < N) {
-                float x = v[j];
-                if (resid) x += Num<T>::to_f(resid[(size_t)row * p.ldr + n]);
-                out[(size_t)row * p.ldo + n] = Num<T>::from_f(x);
-              }
+          for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
+          store8(out + (size_t)row * p.ldo + n0, lo);
+          store8(out + (size_t)row * p.ldo + n0 + 8, hi);
+        } else {
+          for (int j = 0; j < 16; ++j) {
+            const int n = n0 + j;
+            if (n < N) {
+              float x = v[j];
+              if (resid) x += Num<T>::to_f(resid[(size_t)row * p.ldr + n]);
+              out[(size_t)row * p.ldo + n] = Num<T>::from_f(x);
             }
           }
+        }
+      };
+      if constexpr (DUAL) {
+        for (int c0 = 0; c0 < bn; c0 += 32) {
+          uint32_t ra[32], rb[32];
+          tmem_ld32(acc + c0, ra);
+          tmem_ld32(acc + bn + c0, rb);
+          tmem_ld_wait();
+          if (row >= M) continue;
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int n0 = n_base + c0 + q * 16;
+            if (n0 < N) finish16(n0, ra + q * 16, rb + q * 16);
+          }
+        }
+      } else {
+        for (int c0 = 0; c0 < bn; c0 += 16) {
+          uint32_t ra[16];
+          tmem_ld16(acc + c0, ra);
+          tmem_ld_wait();
+          const int n0 = n_base + c0;
+          if (row < M && n0 < N) finish16(n0, ra, ra);
         }
       }
       // this accumulator buffer may now be overwritten by a later tile
