@@ -57,11 +57,20 @@ __device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
   *reinterpret_cast<Vec8<T>*>(p) = x;
 }
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+// Activations run inside GEMM epilogues whose instruction count is on the critical path (the epilogue warps
+// share schedulers with the MMA-issuing lane), so they use the approximate special-function units: results are
+// rounded to 16 bits afterwards and the approximation error (2^-11 relative for tanh, 2 ulp for the division)
+// is below that rounding.
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float tanh_approx_f(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float gelu_tanh_f(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float u = k0 * (x + k1 * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(u));
+  return 0.5f * x * (1.0f + tanh_approx_f(u));
 }
 __device__ __forceinline__ float gelu_erf_f(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
@@ -84,6 +93,36 @@ __device__ __forceinline__ float apply_act(int act, float g, float u) {
     case kActGeluErf: return gelu_erf_f(g);
     case kActSilu: return silu_f(g);
     default: return g;
+  }
+}
+
+// The same on N values with the activation switch outside the element loop.
+template <int N>
+__device__ __forceinline__ void apply_act_n(int act, const float (&g)[N], const float (&u)[N], float (&v)[N]) {
+  switch (act) {
+    case kActSiluMul:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = silu_f(g[j]) * u[j];
+      break;
+    case kActGeluTanhMul:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = gelu_tanh_f(g[j]) * u[j];
+      break;
+    case kActGeluTanh:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = gelu_tanh_f(g[j]);
+      break;
+    case kActGeluErf:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = gelu_erf_f(g[j]);
+      break;
+    case kActSilu:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = silu_f(g[j]);
+      break;
+    default:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = g[j];
   }
 }
 

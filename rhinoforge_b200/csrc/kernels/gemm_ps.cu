@@ -263,31 +263,34 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
       // round trip for one accumulator and 32 for the GLU pair.  Measured alternatives on 8192 x 4096 x 4096:
       // 64-column round trips 30 % slower, a shared-memory transpose for full-line stores 35 % slower - long
       // instruction bursts of the epilogue warps delay the single MMA-issuing lane that shares their schedulers,
-      // so the loop is kept short and, where the epilogue is a plain conversion, free of per-element math.
-      const bool plain = !DUAL && !scale && !bias && !p.row_scale && p.act == kActNone;
+      // so the loop is kept short: scale / bias work and the activation switch are hoisted out of the element loop.
+      const bool affine = scale || bias || p.row_scale;   // per-element scale / bias work, hoisted out of the loop
       auto finish16 = [&](int n0, const uint32_t* g16, const uint32_t* u16) {
-        float v[16];
-        if (plain) {
+        float g[16], u[16], v[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(g16[j]);
-        } else {
+        for (int j = 0; j < 16; ++j) {
+          g[j] = __uint_as_float(g16[j]);
+          u[j] = DUAL ? __uint_as_float(u16[j]) : 0.f;
+        }
+        if (affine) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int n = n0 + j;
-            float vg = __uint_as_float(g16[j]) * rs, vu = DUAL ? __uint_as_float(u16[j]) * rs : 0.f;
+            g[j] *= rs;
+            if (DUAL) u[j] *= rs;
             if (n < N) {
               if (scale) {
-                vg *= Num<T>::to_f(scale[n]);
-                if (DUAL) vu *= Num<T>::to_f(scale[p.dual_offset + n]);
+                g[j] *= Num<T>::to_f(scale[n]);
+                if (DUAL) u[j] *= Num<T>::to_f(scale[p.dual_offset + n]);
               }
               if (bias) {
-                vg += Num<T>::to_f(bias[n]);
-                if (DUAL) vu += Num<T>::to_f(bias[p.dual_offset + n]);
+                g[j] += Num<T>::to_f(bias[n]);
+                if (DUAL) u[j] += Num<T>::to_f(bias[p.dual_offset + n]);
               }
             }
-            v[j] = apply_act(p.act, vg, vu);
           }
         }
+        apply_act_n<16>(p.act, g, u, v);
         if (vec_ok && n0 + 16 <= N) {
           if (resid) {
             float r0[8], r1[8];

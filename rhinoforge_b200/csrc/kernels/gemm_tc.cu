@@ -329,7 +329,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t crank = p.splits > 1 ? cluster_ctarank() : 0u;
 
   // per-element epilogue math shared by both paths
+  const bool affine = p.row_scale || scale || use_bias;
   auto finish = [&](int tok, int n, float vg, float vu) -> float {
+    if (!affine) return apply_act(p.act, vg, vu);
     if (p.row_scale) {
       const float rs = p.row_scale[tok];
       vg *= rs;

@@ -2,8 +2,11 @@
 from ._runtime import (GraphCache, GraphHandle, GraphSignature, backend_loaded, configure_backend,  # noqa: F401
                        get_default_graph_cache, install_torch_namespace, reset_graph_cache)
 
+from .admission import EntryRegistry, GraphPlan, SignaturePlanner  # noqa: E402,F401
+from .manual_capture import GraphCapture, capture  # noqa: E402,F401
+
 GraphSignature.__module__ = "rpu_backend.graph"
 GraphCache.__module__ = "rpu_backend.graph"
 
 __all__ = ["GraphCache", "GraphSignature", "GraphHandle", "configure_backend", "get_default_graph_cache",
-           "reset_graph_cache"]
+           "reset_graph_cache", "SignaturePlanner", "GraphPlan", "EntryRegistry", "GraphCapture", "capture"]

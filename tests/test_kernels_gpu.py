@@ -492,3 +492,31 @@ def test_gemm_persistent_kernel(dt, M, N, K, dual, status):
     y2 = K_.gemm(x, wp, packed_shape=(rows, K), act="silu_mul", dual=True, status=status) if dual else \
         K_.gemm(x, wp, packed_shape=(rows, K), bias=b, residual=r, status=status)
     assert torch.equal(y, y2), "two launches of the same GEMM must agree bit for bit"
+
+
+def test_manual_graph_capture_replays_with_refilled_inputs(status):
+    """``graph.capture``: one recording run, then replays that refill the static input buffers; a changed shape is refused."""
+    from rhinoforge_b200.graph import capture
+    from rhinoforge_b200.ops import kernels as K_
+    w = (1.0 + 0.1 * torch.randn(256, device="cuda")).half()
+    x = torch.randn(40, 256, device="cuda").half()
+    out = torch.empty_like(x)
+
+    def fn(inp):
+        K_.rmsnorm(inp, w, 1e-6, out=out)
+        return out
+
+    g = capture(fn, x)
+    assert g.replayable, g.non_replayable_reason
+    ref = lambda t: (w.float() * (t.float() * torch.rsqrt(t.float().pow(2).mean(-1, keepdim=True) + 1e-6)))
+    torch.cuda.synchronize()
+    _close(g.cached_output, ref(x), torch.float16)
+    x2 = torch.randn(40, 256, device="cuda").half()
+    y = g.replay(x2)
+    torch.cuda.synchronize()
+    _close(y, ref(x2), torch.float16)
+    st = g.stats()
+    assert st["replays"] == 1 and st["build_count"] == 1 and st["node_count"] >= 1
+    with pytest.raises(RuntimeError, match="shape_bucket"):
+        g.replay(torch.randn(41, 256, device="cuda").half())
+    g.invalidate()

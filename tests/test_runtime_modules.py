@@ -184,3 +184,101 @@ def test_qwen25vl_window_partition_matches_hf_index():
         order, lens = window_partition([tuple(g) for g in grid], 2, 112 // 2 // 14)
         assert order == [int(i) for i in idx]
         assert [4 * n for n in lens] == (cu[1:] - cu[:-1]).tolist()
+
+
+def test_signature_planner_layers_and_miss_attribution():
+    import torch
+    from rhinoforge_b200.graph.admission import SignaturePlanner
+
+    P = SignaturePlanner()
+    x = torch.zeros(2, 5, 8)
+
+    def f(a):
+        return a
+
+    base = P.layers_for_call("op", (x, 3), {"flag": True}, branch=f)
+    assert P.layers_for_call("op", (torch.zeros(2, 5, 8), 3), {"flag": True}, branch=f) == base
+    cases = {
+        "gm_id": P.layers_for_call("other", (x, 3), {"flag": True}, branch=f),
+        "tensor_struct": P.layers_for_call("op", ((x, x), 3), {"flag": True}, branch=f),
+        "shape_bucket": P.layers_for_call("op", (torch.zeros(2, 6, 8), 3), {"flag": True}, branch=f),
+        "dtype_layout": P.layers_for_call("op", (x.half(), 3), {"flag": True}, branch=f),
+        "scalar_flags": P.layers_for_call("op", (x, 4), {"flag": True}, branch=f),
+        "branch_key": P.layers_for_call("op", (x, 3), {"flag": True}, branch=len),
+        "segment_key": P.layers_for_call("op", (x, 3), {"flag": True}, branch=f, segment=2),
+    }
+    for reason, layers in cases.items():
+        assert P.attribute_miss_reason(layers, [base]) == reason, reason
+    assert P.attribute_miss_reason(base, []) == "no_entry"
+    # the closest entry decides: one entry differs in the op, another only in a scalar
+    assert P.attribute_miss_reason(cases["scalar_flags"], [cases["gm_id"], base]) == "scalar_flags"
+    assert P.infer_workload_kind((torch.zeros(4, 1, 8),)) == "decode"
+    assert P.infer_workload_kind((torch.zeros(4, 7, 8),)) == "prefill"
+    assert P.infer_workload_kind((3, "x")) == "generic"
+    assert P.stable_branch_key(f) == P.stable_branch_key(f) != P.stable_branch_key(len)
+    assert P.stable_branch_key(None) == 0
+
+
+def test_entry_registry_lru_and_plans_without_a_device():
+    import torch
+    from rhinoforge_b200.graph.admission import EntryRegistry, GraphPlan
+
+    class FakeCache:          # the registry only needs this much of a GraphCache
+        def __init__(self):
+            self.evicted, self.frozen = [], False
+        def is_frozen(self): return self.frozen
+        def evict(self, sig): self.evicted.append(sig)
+        def capture(self, sig): return ("scope", sig)
+        def explain_miss(self, sig): return "miss"
+        def size(self): return 0
+        def clear(self): pass
+
+    fc = FakeCache()
+    reg = EntryRegistry(fc, max_entries=2)
+    # without the native backend every signature hashes alike, so give each plan its own key object
+    class Sig:
+        def __init__(self, k): self.k, self._impl = k, (k,)
+        def __hash__(self): return hash(self.k)
+        def __eq__(self, o): return self.k == o.k
+    L = reg.planner.layers_for_call("op", (torch.zeros(1, 1),))
+    plans = [GraphPlan(Sig(i), L) for i in range(3)]
+    for p in plans[:2]:
+        assert reg.admit_for_call(p)[0] == "scope" and p.admission == "record"
+    assert reg.admit_for_call(plans[0]) and plans[0].admission == "replay"
+    reg.admit_for_call(plans[2])                       # evicts plans[1] (least recently used)
+    assert fc.evicted == [plans[1].signature] and plans[2].lifecycle == "evict"
+    st = reg.stats()
+    assert (st["hits"], st["misses"], st["evictions"], st["entries"]) == (1, 3, 1, 2)
+    fc.frozen = True
+    import pytest
+    with pytest.raises(RuntimeError, match="frozen"):
+        reg.admit_for_call(GraphPlan(Sig(9), L))
+    assert "plan[" in plans[2].to_log_str()
+
+
+def test_manual_capture_passes_through_without_a_device_and_refuses_drift():
+    import pytest
+    import torch
+    from rhinoforge_b200.graph import capture
+
+    calls = []
+
+    def fn(a, b, *, k=2):
+        calls.append(1)
+        return a * k + b
+
+    a, b = torch.ones(3), torch.arange(3.0)
+    g = capture(fn, a, b, k=2)
+    if not torch.cuda.is_available():
+        assert not g.replayable and g.non_replayable_reason
+        assert torch.equal(g.replay(a, b, k=2), a * 2 + b)
+        assert g.stats()["passthrough_calls"] == 1 and len(calls) == 2
+    with pytest.raises(RuntimeError, match="shape_bucket"):
+        g.replay(torch.ones(4), torch.ones(4), k=2)
+    with pytest.raises(RuntimeError, match="scalar_flags"):
+        g.replay(a, b, k=3)
+    with pytest.raises(NotImplementedError):
+        capture(fn, a, b, dynamic_inputs=("a",))
+    g.invalidate()
+    with pytest.raises(RuntimeError, match="invalidated"):
+        g.replay(a, b, k=2)
