@@ -101,3 +101,79 @@ def test_w8a16_loader_keeps_int8_parameters(tmp_path):
     assert get("model.layers.1.mlp.up_proj.weight").dtype == torch.int8
     assert get.scale("model.layers.1.mlp.up_proj.weight").shape == (512,)
     assert get.scale("model.norm.weight") is None
+
+
+def test_verify_accepts_a_converted_checkpoint_and_flags_a_corrupted_one(tmp_path):
+    from safetensors.torch import load_file, save_file
+    from rpu_backend.quant.convert_qwen3 import convert_checkpoint
+    from rpu_backend.quant.verify_qwen3_w8a16 import main, verify
+    _tiny_ckpt(tmp_path / "src", tie=False)
+    convert_checkpoint(tmp_path / "src", tmp_path / "q", ["lm_head"])
+    rep = verify(tmp_path / "src", tmp_path / "q")
+    assert rep["ok"] and rep["quantized"] > 0 and rep["worst_cosine"] > 0.999 and rep["worst_rel_product_error"] < 0.02
+    assert main(["--src", str(tmp_path / "src"), "--quant", str(tmp_path / "q")]) == 0
+    t = load_file(str(tmp_path / "q" / "model.safetensors"))
+    name = "model.layers.0.self_attn.q_proj.weight"
+    t[name] = t[name].clone()
+    t[name][0, :8] = 127                                     # corrupt one row
+    save_file(t, str(tmp_path / "q" / "model.safetensors"), metadata={"format": "pt"})
+    rep = verify(tmp_path / "src", tmp_path / "q")
+    assert not rep["ok"] and any(name in p for p in rep["problems"])
+    assert main(["--src", str(tmp_path / "src"), "--quant", str(tmp_path / "q")]) == 1
+
+
+def test_w4a16_converter_packs_projections_with_group_scales(tmp_path):
+    from safetensors.torch import load_file
+    from rpu_backend.quant.convert_qwen3_w4a16 import convert_checkpoint, main
+    from rpu_backend.quant.int4_pgrp_pack import dequantize_int4_pgrp
+    from rpu_backend.quant._common import cosine
+    cfg, sd = _tiny_ckpt(tmp_path / "src", tie=False)
+    st = convert_checkpoint(tmp_path / "src", tmp_path / "w4", group_size=32)
+    assert st["n_quantized"] == 7 * cfg.num_layers
+    out = load_file(str(tmp_path / "w4" / "model.safetensors"))
+    name = "model.layers.1.mlp.up_proj.weight"
+    w = sd[name]
+    assert out[name].dtype == torch.uint8 and tuple(out[name].shape) == (w.shape[0], w.shape[1] // 2)
+    sc = out[name[:-7] + ".weight_scale"]
+    assert sc.dtype == torch.float16 and tuple(sc.shape) == (w.shape[0], w.shape[1] // 32)
+    assert cosine(dequantize_int4_pgrp(out[name], sc, 32), w) > 0.99
+    qc = json.loads((tmp_path / "w4" / "config.json").read_text())["quant_config"]
+    assert qc["method"] == "w4a16" and qc["group_size"] == 32
+    assert main(["--src", str(tmp_path / "src"), "--dst", str(tmp_path / "w4")]) == 1      # never overwrites
+
+
+def test_pi05_converter_quantises_only_gemma_projections_and_writes_the_sidecar(tmp_path):
+    from safetensors.torch import load_file, save_file
+    from rpu_backend.quant.convert_pi05 import SIDECAR, convert_checkpoint, target_of
+    g = torch.Generator().manual_seed(0)
+    r = lambda *s: torch.randn(*s, generator=g) * 0.05
+    vlm = "model.paligemma_with_expert.paligemma.model.language_model.layers.0."
+    exp = "model.paligemma_with_expert.gemma_expert.model.layers.0."
+    sd = {vlm + "self_attn.q_proj.weight": r(32, 16), vlm + "mlp.down_proj.weight": r(16, 64),
+          exp + "self_attn.o_proj.weight": r(16, 32), exp + "input_layernorm.dense.weight": r(48, 16),
+          "model.paligemma_with_expert.paligemma.model.vision_tower.vision_model.encoder.layers.0.self_attn.q_proj.weight": r(16, 16),
+          "model.action_in_proj.weight": r(16, 8)}
+    src = tmp_path / "src"
+    src.mkdir()
+    save_file(sd, str(src / "model.safetensors"), metadata={"format": "pt"})
+    (src / "config.json").write_text(json.dumps({"type": "pi05"}))
+    (src / "model_remapped.safetensors").write_bytes(b"stale")
+    assert target_of(vlm + "self_attn.q_proj.weight") == "vlm" and target_of(exp + "self_attn.o_proj.weight") == "expert"
+    assert target_of(exp + "input_layernorm.dense.weight") is None
+    st = convert_checkpoint(src, tmp_path / "q8")
+    assert (st["vlm"], st["expert"], st["int8"]) == (2, 1, 3)
+    out = load_file(str(tmp_path / "q8" / "model.safetensors"))
+    assert out[vlm + "self_attn.q_proj.weight"].dtype == torch.int8
+    assert out[vlm + "self_attn.q_proj.weight_scale"].dtype == torch.float16
+    assert out[exp + "input_layernorm.dense.weight"].dtype == torch.float32          # untouched
+    assert out["model.action_in_proj.weight"].dtype == torch.float32
+    assert not (tmp_path / "q8" / "model_remapped.safetensors").exists()
+    side = json.loads((tmp_path / "q8" / SIDECAR).read_text())
+    assert side["method"] == "w8a16" and side["targets"] == ["vlm", "expert"]
+    st4 = convert_checkpoint(src, tmp_path / "q4", bits=4, targets=["expert"], keep_int8_suffixes=["self_attn.o_proj"])
+    out4 = load_file(str(tmp_path / "q4" / "model.safetensors"))
+    assert (st4["expert"], st4["vlm"], st4["int8"], st4["int4"]) == (1, 0, 1, 0)     # the only expert tensor is exempt
+    assert out4[vlm + "self_attn.q_proj.weight"].dtype == torch.float32
+    st4b = convert_checkpoint(src, tmp_path / "q4b", bits=4)
+    q = load_file(str(tmp_path / "q4b" / "model.safetensors"))[vlm + "mlp.down_proj.weight"]
+    assert st4b["int4"] == 3 and int(q.max()) <= 7 and int(q.min()) >= -8
