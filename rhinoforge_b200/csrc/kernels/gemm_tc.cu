@@ -101,9 +101,15 @@ template <typename T, bool SWAP, bool DUAL, bool W8>
 __global__ void __launch_bounds__(W8 ? 256 : 128)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmW, const GemmTcParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw_addr = smem_u32(smem_raw);
-  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  // No alignment slack: the W8A16 decode configuration fits two CTAs per SM only without it.  The swizzled
+  // tiles need a 1024-byte aligned base, which the runtime provides when the kernel has no static shared
+  // memory; a misaligned base is reported instead of being used.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0) report_status(p.status, kStatusBadArgument, kTagGemmTc, (int)(smem_u32(smem_raw) & 1023u));
+    return;
+  }
+  uint8_t* smem = smem_raw;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -519,21 +525,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         v[j] = (tok < M && n < N) ? finish(tok, n, vg, vu) : 0.f;
       }
       if (p.ar_world > 1 && p.ar_two_shot) {
-        // reduce-scatter leg: the 16-bit partial of this tile goes to the tile's owner only
-        if (!SWAP && a_idx < M) {
-          const int owner = tile_id % p.ar_world;
-          T* pb = reinterpret_cast<T*>(owner_buf) + ((size_t)p.ar_rank * M + a_idx) * N + b0 + c;
-          if (b0 + c + 16 <= N && (N & 7) == 0) {
-            float lo[8], hi[8];
+        // The 16-bit partial of this tile is parked in the operand ring (idle once the accumulator is
+        // complete): row r at r * bn elements, its 16-byte chunks XOR-swizzled by r so that both this
+        // row-per-thread write and the row-per-warp reads below are free of bank conflicts.  It leaves the
+        // CTA as whole rows, because 16-byte stores scattered over 32 rows cross NVLink at a fraction of
+        // the link rate.
+        if (!SWAP && epi) {
+          T* srow = reinterpret_cast<T*>(smem) + (size_t)tid * bn;
+          const int cmask = min(bn >> 3, 32) - 1;
+          float lo[8], hi[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
-            store8(pb, lo);
-            store8(pb + 8, hi);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (b0 + c + j < N) pb[j] = Num<T>::from_f(v[j]);
-          }
+          for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
+          store8(srow + ((((c >> 3)) ^ (tid & cmask)) << 3), lo);
+          store8(srow + ((((c >> 3) + 1) ^ (tid & cmask)) << 3), hi);
         }
       } else if (p.ar_world > 1) {
 #pragma unroll
@@ -586,16 +590,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 
   if (p.ar_world > 1 && p.ar_two_shot) {
-    // Two-shot all-reduce for large M.  Leg 1 (above): every rank stored its 16-bit partial of
-    // this tile in the owner's buffer.  The owner waits for all ranks, sums in rank order in
-    // fp32, adds the residual and stores the finished tile into every rank's result region
-    // (leg 2); every rank then copies the tile into its own output.
+    // Two-shot all-reduce for large M, one output tile per CTA.  Leg 1: every rank copies its 16-bit partial
+    // tile (parked in shared memory above) into the buffer of the tile's owner rank.  The owner waits for all
+    // ranks, sums in rank order in fp32, adds the residual and writes the finished tile into every rank's
+    // result region (leg 2); every rank then copies the tile into its own output.  All global traffic is
+    // row-per-warp: the lanes of a warp cover whole rows of the tile with 16 bytes each.
     const int owner = tile_id % p.ar_world;
     const uint32_t want = call + 1u;
     const size_t fbase = ((size_t)tile_id * 8) * p.ar_world;
     const size_t f2 = (size_t)p.ar_flag2_base + tile_id;
     const size_t result_rel = (uint64_t)p.ar_world * M * N * sizeof(T);   // result region, after the partials
     const size_t result_off = slot_off + result_rel;
+    const bool vecio = (N & 7) == 0 && (p.ldo & 7) == 0 && (!resid || (p.ldr & 7) == 0);
+    const int cpr = bn >> 3;                       // 16-byte chunks per tile row (a power of two, <= 32)
+    const int rpi = 32 / cpr;                      // tile rows one warp instruction covers
+    const int cmask = cpr - 1;
+    const int nwarps = (int)blockDim.x >> 5;
+    const int lrow = lane_id() / cpr, lchunk = lane_id() % cpr;
+    const int ncol0 = b0 + lchunk * 8;             // first output column of this lane
+    const T* tile_s = reinterpret_cast<const T*>(smem);
+    __syncthreads();                               // the parked tile is complete
+    if (!aborted && !SWAP && ncol0 < N) {
+      T* pdst = reinterpret_cast<T*>(owner_buf) + (size_t)p.ar_rank * M * N;
+      for (int r0 = warp * rpi; r0 < kBM; r0 += nwarps * rpi) {
+        const int r = r0 + lrow, grow = a0 + r;
+        if (grow >= M) continue;
+        const T* sp = tile_s + (size_t)r * bn + ((lchunk ^ (r & cmask)) << 3);
+        T* gp = pdst + (size_t)grow * N + ncol0;
+        if (vecio && ncol0 + 8 <= N) {
+          *reinterpret_cast<uint4*>(gp) = *reinterpret_cast<const uint4*>(sp);
+        } else {
+          for (int j = 0; j < 8; ++j)
+            if (ncol0 + j < N) gp[j] = sp[j];
+        }
+      }
+    }
     __threadfence_system();
     __syncthreads();
     if (tid == 0 && !aborted) st_release_sys(p.ar_flags[owner] + fbase + p.ar_rank, want);
@@ -607,25 +636,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       }
       aborted = __syncthreads_or(*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag) != 0);
-      if (!aborted && !SWAP && a_idx < M) {
+      if (!aborted && !SWAP && ncol0 < N) {
         const T* part = reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(p.ar_recv[p.ar_rank]) + slot_off);
-        for (int c = 0; c < ncols; c += 8) {
-          const int n0 = b0 + c;
+        for (int r0 = warp * rpi; r0 < kBM; r0 += nwarps * rpi) {
+          const int grow = a0 + r0 + lrow;
+          if (grow >= M) continue;
           float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          const bool vec = (n0 + 8 <= N) && ((N & 7) == 0) && (!resid || (p.ldr & 7) == 0);
+          const bool vec = vecio && ncol0 + 8 <= N;
           if (vec) {
             // every rank's vector (and the residual's) is in flight before the first add
             uint4 raw[8];
 #pragma unroll
-            for (int r = 0; r < 8; ++r)
-              raw[r] = r < p.ar_world ? __ldcg(reinterpret_cast<const uint4*>(part + ((size_t)r * M + a_idx) * N + n0))
-                                      : make_uint4(0u, 0u, 0u, 0u);
+            for (int rr = 0; rr < 8; ++rr)
+              raw[rr] = rr < p.ar_world
+                            ? __ldcg(reinterpret_cast<const uint4*>(part + ((size_t)rr * M + grow) * N + ncol0))
+                            : make_uint4(0u, 0u, 0u, 0u);
             float r8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (resid) load8(resid + (size_t)a_idx * p.ldr + n0, r8);
+            if (resid) load8(resid + (size_t)grow * p.ldr + ncol0, r8);
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-              if (r < p.ar_world) {
-                const typename Num<T>::T2* h = reinterpret_cast<const typename Num<T>::T2*>(&raw[r]);
+            for (int rr = 0; rr < 8; ++rr) {
+              if (rr < p.ar_world) {
+                const typename Num<T>::T2* h = reinterpret_cast<const typename Num<T>::T2*>(&raw[rr]);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   const float2 f = Num<T>::to_f2(h[j]);
@@ -637,24 +668,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] += r8[j];
           } else {
-            for (int r = 0; r < p.ar_world; ++r) {
-              const T* src = part + ((size_t)r * M + a_idx) * N + n0;
+            for (int rr = 0; rr < p.ar_world; ++rr) {
+              const T* src = part + ((size_t)rr * M + grow) * N + ncol0;
               for (int j = 0; j < 8; ++j)
-                if (n0 + j < N) acc[j] += Num<T>::to_f(src[j]);
+                if (ncol0 + j < N) acc[j] += Num<T>::to_f(src[j]);
             }
             if (resid) {
               for (int j = 0; j < 8; ++j)
-                if (n0 + j < N) acc[j] += Num<T>::to_f(resid[(size_t)a_idx * p.ldr + n0 + j]);
+                if (ncol0 + j < N) acc[j] += Num<T>::to_f(resid[(size_t)grow * p.ldr + ncol0 + j]);
             }
           }
 #pragma unroll
           for (int dst = 0; dst < 8; ++dst) {
             if (dst < p.ar_world) {
-              T* rp = reinterpret_cast<T*>(peer_buf[dst] + result_rel) + (size_t)a_idx * N + n0;
+              T* rp = reinterpret_cast<T*>(peer_buf[dst] + result_rel) + (size_t)grow * N + ncol0;
               if (vec) store8(rp, acc);
               else
                 for (int j = 0; j < 8; ++j)
-                  if (n0 + j < N) rp[j] = Num<T>::from_f(acc[j]);
+                  if (ncol0 + j < N) rp[j] = Num<T>::from_f(acc[j]);
             }
           }
         }
@@ -670,28 +701,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
     aborted = __syncthreads_or(*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag) != 0);
-    if (!aborted && !SWAP && a_idx < M) {
-      const T* res = reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(p.ar_recv[p.ar_rank]) + result_off) +
-                     (size_t)a_idx * N;
-      if ((N & 7) == 0 && (p.ldo & 7) == 0) {
-        // eight vector loads in flight per round: a store to `out` may alias `res` as far as the compiler
-        // knows, so a load-store pair per column group would run one memory latency at a time
-        for (int c = 0; c < ncols; c += 64) {
-          uint4 t[8];
+    if (!aborted && !SWAP && ncol0 < N) {
+      const T* res = reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(p.ar_recv[p.ar_rank]) + result_off);
+      if (vecio && ncol0 + 8 <= N) {
+        // four row groups per round: a store to `out` may alias `res` as far as the compiler knows, so a
+        // load-store pair per row would run one memory latency at a time
+        for (int r0 = warp * rpi; r0 < kBM; r0 += 4 * nwarps * rpi) {
+          uint4 t[4];
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const int n0 = b0 + c + q * 8;
-            t[q] = (c + q * 8 < ncols && n0 + 8 <= N) ? __ldcg(reinterpret_cast<const uint4*>(res + n0)) : make_uint4(0u, 0u, 0u, 0u);
+          for (int q = 0; q < 4; ++q) {
+            const int grow = a0 + r0 + q * nwarps * rpi + lrow;
+            t[q] = (r0 + q * nwarps * rpi < kBM && grow < M)
+                       ? __ldcg(reinterpret_cast<const uint4*>(res + (size_t)grow * N + ncol0)) : make_uint4(0u, 0u, 0u, 0u);
           }
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const int n0 = b0 + c + q * 8;
-            if (c + q * 8 < ncols && n0 + 8 <= N) *reinterpret_cast<uint4*>(out + (size_t)a_idx * p.ldo + n0) = t[q];
+          for (int q = 0; q < 4; ++q) {
+            const int grow = a0 + r0 + q * nwarps * rpi + lrow;
+            if (r0 + q * nwarps * rpi < kBM && grow < M)
+              *reinterpret_cast<uint4*>(out + (size_t)grow * p.ldo + ncol0) = t[q];
           }
         }
       } else {
-        for (int c = 0; c < ncols; ++c)
-          if (b0 + c < N) out[(size_t)a_idx * p.ldo + b0 + c] = res[b0 + c];
+        for (int r0 = warp * rpi; r0 < kBM; r0 += nwarps * rpi) {
+          const int grow = a0 + r0 + lrow;
+          if (grow >= M) continue;
+          for (int j = 0; j < 8; ++j)
+            if (ncol0 + j < N) out[(size_t)grow * p.ldo + ncol0 + j] = res[(size_t)grow * N + ncol0 + j];
+        }
       }
     }
     __syncthreads();
@@ -856,7 +892,7 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   const int a_tiles = (swap && dual) ? 2 : 1, b_tiles = (!swap && dual) ? 2 : 1;
   int stage_bytes = a_tiles * kATileBytes + b_tiles * pl->bn * kBK * 2;
   if (g->w_int8) stage_bytes += (dual ? 2 : 1) * (swap ? kBM : pl->bn) * kBK;   // int8 staging tiles
-  const int ctl_bytes = (int)sizeof(GemmSmemCtl) + 1024 /*alignment slack*/ + 64;
+  const int ctl_bytes = (int)sizeof(GemmSmemCtl) + 64;
   static const int env_smem_kb = [] { const char* e = getenv("RF_GEMM_SMEM_KB"); return e ? atoi(e) : 0; }();
 
   // shared-memory plan for a given split count and ring budget
@@ -871,13 +907,15 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
     return (size_t)round_up(std::max(st * stage_bytes, part), 1024) + ctl_bytes;
   };
 
+  // largest dynamic shared memory with which two CTAs share an SM: (228 KB - 1 KB reserved per CTA) / 2
+  constexpr int kTwoCtaSmem = 113 * 1024;
   int splits = 1, budget = 224 * 1024;
   const bool two_shot = g->ar_world > 1 && !swap && g->M > 256;   // its epilogue works on whole tiles
   if (g->force_splits > 0) {
     splits = std::min(std::min(g->force_splits, 8), pl->k_blocks);
     if (two_shot) splits = 1;
     int st, part;
-    if (layout(splits, 110 * 1024, &st, &part) && st >= 2 && tiles * splits > sm_count()) budget = 110 * 1024;
+    if (layout(splits, kTwoCtaSmem, &st, &part) && st >= 2 && tiles * splits > sm_count()) budget = kTwoCtaSmem;
   } else {
     // Split rule from timing sweeps of decode and mid-size shapes on B200:
     //  * power-of-two cluster sizes only (3 and 6 place badly on the GPCs and cost up to 2x);
@@ -894,7 +932,7 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
       for (int S = 8; S >= 2; S >>= 1) {
         if (S > max_by_k || tiles * S > cap) continue;
         int st, part;
-        const int b = tiles * S > sm_count() ? 110 * 1024 : 224 * 1024;
+        const int b = tiles * S > sm_count() ? kTwoCtaSmem : 224 * 1024;
         const size_t smem = layout(S, b, &st, &part);
         if (st < 2 || smem > 227 * 1024) continue;
         splits = S;
@@ -903,8 +941,8 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
     }
     {
       int st, part;
-      layout(splits, 110 * 1024, &st, &part);
-      budget = (tiles * splits > sm_count() && st >= 2) ? 110 * 1024 : 224 * 1024;
+      layout(splits, kTwoCtaSmem, &st, &part);
+      budget = (tiles * splits > sm_count() && st >= 2) ? kTwoCtaSmem : 224 * 1024;
     }
   }
   if (env_smem_kb > 0) budget = std::min(224, std::max(48, env_smem_kb)) * 1024;
