@@ -40,6 +40,7 @@ class RfGemm(C.Structure):
         ("ar_recv", C.c_void_p), ("ar_flags", C.c_void_p), ("ar_state", C.c_void_p),
         ("ar_recv_bytes", C.c_uint64), ("ar_flag_count", C.c_int32),
         ("force_splits", C.c_int32), ("force_swap", C.c_int32), ("force_bn", C.c_int32), ("w_packed", C.c_int32),
+        ("w_scratch", C.c_void_p), ("w_scratch_bytes", C.c_uint64),
     ]
 
 

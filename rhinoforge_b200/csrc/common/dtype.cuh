@@ -96,6 +96,40 @@ __device__ __forceinline__ float apply_act(int act, float g, float u) {
   }
 }
 
+// Eight int8 values (two 32-bit words) -> eight 16-bit floats, exactly.
+// fp16: byte b = x + 128 is dropped into the mantissa of 1024.0 (0x6400 | b = 1024 + b), then 1152 is
+// subtracted -- two integer permutes and one half2 subtract per four values, no int->float convert.
+template <typename T> __device__ __forceinline__ uint4 widen_i8x8(uint2 q);
+template <> __device__ __forceinline__ uint4 widen_i8x8<__half>(uint2 q) {
+  const uint32_t bias = 0x64806480u;  // half2(1152, 1152)
+  uint4 r;
+  uint32_t x = q.x ^ 0x80808080u;
+  uint32_t lo = __byte_perm(x, 0x64646464u, 0x5140), hi = __byte_perm(x, 0x64646464u, 0x5342);
+  __half2 a = __hsub2(*reinterpret_cast<__half2*>(&lo), *reinterpret_cast<const __half2*>(&bias));
+  __half2 b = __hsub2(*reinterpret_cast<__half2*>(&hi), *reinterpret_cast<const __half2*>(&bias));
+  r.x = *reinterpret_cast<uint32_t*>(&a);
+  r.y = *reinterpret_cast<uint32_t*>(&b);
+  x = q.y ^ 0x80808080u;
+  lo = __byte_perm(x, 0x64646464u, 0x5140);
+  hi = __byte_perm(x, 0x64646464u, 0x5342);
+  a = __hsub2(*reinterpret_cast<__half2*>(&lo), *reinterpret_cast<const __half2*>(&bias));
+  b = __hsub2(*reinterpret_cast<__half2*>(&hi), *reinterpret_cast<const __half2*>(&bias));
+  r.z = *reinterpret_cast<uint32_t*>(&a);
+  r.w = *reinterpret_cast<uint32_t*>(&b);
+  return r;
+}
+template <> __device__ __forceinline__ uint4 widen_i8x8<__nv_bfloat16>(uint2 q) {
+  const int8_t* b = reinterpret_cast<const int8_t*>(&q);
+  uint4 r;
+  __nv_bfloat162 t;
+  t = __floats2bfloat162_rn((float)b[0], (float)b[1]); r.x = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn((float)b[2], (float)b[3]); r.y = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn((float)b[4], (float)b[5]); r.z = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn((float)b[6], (float)b[7]); r.w = *reinterpret_cast<uint32_t*>(&t);
+  return r;
+}
+
+
 // The same on N values with the activation switch outside the element loop.
 template <int N>
 __device__ __forceinline__ void apply_act_n(int act, const float (&g)[N], const float (&u)[N], float (&v)[N]) {

@@ -419,4 +419,30 @@ int launch_gemm_ps(const RfGemm* g, cudaStream_t stream) {
   return launch_ps_t<__nv_bfloat16>(g, dual, bn, rows, stream);
 }
 
+// int8 tile-major weight image -> 16-bit tile-major image (the 128-byte-swizzled block layout the MMA reads).
+// One thread widens eight values: 8 bytes in, 16 bytes out.  Exact in fp16 and bf16 (|q| <= 127).
+template <typename T>
+__global__ void widen_packed_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t pieces) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < pieces; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t block = i >> 10;                     // 128 rows x 8 pieces
+    const int row = (int)(i & 1023) >> 3, c = (int)(i & 7);
+    const uint2 q = *reinterpret_cast<const uint2*>(src + block * 8192 + row * 64 + c * 8);
+    *reinterpret_cast<uint4*>(dst + block * 16384 + row * 128 + ((c ^ (row & 7)) << 4)) = widen_i8x8<T>(q);
+  }
+}
+
+int widen_packed(const void* src, void* dst, int64_t blocks, int dtype, cudaStream_t stream) {
+  const int64_t pieces = blocks * 1024;
+  const int grid = (int)std::min<int64_t>((pieces + 255) / 256, (int64_t)sm_count() * 16);
+  if (dtype == 0)
+    widen_packed_kernel<__half><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(src),
+                                                          reinterpret_cast<uint8_t*>(dst), pieces);
+  else
+    widen_packed_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(src),
+                                                                 reinterpret_cast<uint8_t*>(dst), pieces);
+  RF_CUDA_CHECK(cudaGetLastError());
+  ::rf::count_launch();
+  return RF_OK;
+}
+
 }  // namespace rf

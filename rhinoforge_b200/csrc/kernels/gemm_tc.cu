@@ -56,43 +56,12 @@ struct alignas(8) GemmSmemCtl {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
   uint64_t ready[kMaxStages];  // W8A16: the converter warps have written the 16-bit weight tile
+  uint64_t qfull[kMaxStages];  // W8A16: the int8 staging tile has landed
+  uint64_t qempty[kMaxStages]; // W8A16: the converter warps have read the int8 staging tile
   uint64_t accum;
   uint32_t tmem_base;
   int32_t abort_flag;
 };
-
-// Eight int8 values (two 32-bit words) -> eight 16-bit floats, exactly.
-// fp16: byte b = x + 128 is dropped into the mantissa of 1024.0 (0x6400 | b = 1024 + b), then 1152 is
-// subtracted -- two integer permutes and one half2 subtract per four values, no int->float convert.
-template <typename T> __device__ __forceinline__ uint4 widen_i8x8(uint2 q);
-template <> __device__ __forceinline__ uint4 widen_i8x8<__half>(uint2 q) {
-  const uint32_t bias = 0x64806480u;  // half2(1152, 1152)
-  uint4 r;
-  uint32_t x = q.x ^ 0x80808080u;
-  uint32_t lo = __byte_perm(x, 0x64646464u, 0x5140), hi = __byte_perm(x, 0x64646464u, 0x5342);
-  __half2 a = __hsub2(*reinterpret_cast<__half2*>(&lo), *reinterpret_cast<const __half2*>(&bias));
-  __half2 b = __hsub2(*reinterpret_cast<__half2*>(&hi), *reinterpret_cast<const __half2*>(&bias));
-  r.x = *reinterpret_cast<uint32_t*>(&a);
-  r.y = *reinterpret_cast<uint32_t*>(&b);
-  x = q.y ^ 0x80808080u;
-  lo = __byte_perm(x, 0x64646464u, 0x5140);
-  hi = __byte_perm(x, 0x64646464u, 0x5342);
-  a = __hsub2(*reinterpret_cast<__half2*>(&lo), *reinterpret_cast<const __half2*>(&bias));
-  b = __hsub2(*reinterpret_cast<__half2*>(&hi), *reinterpret_cast<const __half2*>(&bias));
-  r.z = *reinterpret_cast<uint32_t*>(&a);
-  r.w = *reinterpret_cast<uint32_t*>(&b);
-  return r;
-}
-template <> __device__ __forceinline__ uint4 widen_i8x8<__nv_bfloat16>(uint2 q) {
-  const int8_t* b = reinterpret_cast<const int8_t*>(&q);
-  uint4 r;
-  __nv_bfloat162 t;
-  t = __floats2bfloat162_rn((float)b[0], (float)b[1]); r.x = *reinterpret_cast<uint32_t*>(&t);
-  t = __floats2bfloat162_rn((float)b[2], (float)b[3]); r.y = *reinterpret_cast<uint32_t*>(&t);
-  t = __floats2bfloat162_rn((float)b[4], (float)b[5]); r.z = *reinterpret_cast<uint32_t*>(&t);
-  t = __floats2bfloat162_rn((float)b[6], (float)b[7]); r.w = *reinterpret_cast<uint32_t*>(&t);
-  return r;
-}
 
 // W8 = int8 weights (W8A16): TMA brings the int8 tile into a staging area of the stage, four extra
 // converter warps widen it into the 128-byte-swizzled 16-bit tile the MMA reads, and the
@@ -137,6 +106,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(&ctl->full[s], 1);
       mbar_init(&ctl->empty[s], 1);
       mbar_init(&ctl->ready[s], 4);
+      mbar_init(&ctl->qfull[s], 1);
+      mbar_init(&ctl->qempty[s], 4);
     }
     mbar_init(&ctl->accum, 1);
     ctl->abort_flag = 0;
@@ -161,10 +132,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   // ------------------------------------------------------- TMA producer ----
   if (warp == 0 && lane_id() == 0) {
-    const uint32_t tx = W8 ? (uint32_t)(act_bytes + kWTiles * q_tile_bytes) : (uint32_t)stage_bytes;
-    int issued = 0;
+    // W8A16 splits a stage's traffic over two barriers: the int8 staging tile (qfull) is refilled as soon as
+    // the converter warps have widened it (qempty), without waiting for the MMAs that still read the 16-bit
+    // tile of the same stage, so the DRAM latency of the next weights hides behind conversion and MMA.
+    const uint32_t tx = W8 ? (uint32_t)act_bytes : (uint32_t)stage_bytes;
+    const uint32_t txq = (uint32_t)(kWTiles * q_tile_bytes);
+    int issued = 0, issued_q = 0;
     bool ok = true;
     auto load_weights = [&](int i, int s) {
+      uint64_t* wbar = W8 ? &ctl->qfull[s] : &ctl->full[s];
       uint8_t* st = smem + (size_t)s * stage_bytes;
       const int kc = (kb0 + i) * kBK;
       if (p.w_packed) {
@@ -178,13 +154,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             : (SWAP ? st + wt * kATileBytes : st + kATiles * kATileBytes + wt * b_tile_bytes);
           for (int sub = 0; sub < nsub; ++sub) {
             const uint8_t* src = p.w_packed + ((size_t)(rt0 + sub + wt * p.dual_tiles) * p.kb_total + (kb0 + i)) * kBlk;
-            bulk_load_1d(dst + (size_t)sub * kBlk, src, kBlk, &ctl->full[s]);
+            bulk_load_1d(dst + (size_t)sub * kBlk, src, kBlk, wbar);
           }
         }
       } else if (W8) {
         const int r0 = SWAP ? a0 : b0;
-        tma_load_2d(st + half_bytes, &tmW, &ctl->full[s], kc, r0);
-        if (kWTiles == 2) tma_load_2d(st + half_bytes + q_tile_bytes, &tmW, &ctl->full[s], kc, p.dual_offset + r0);
+        tma_load_2d(st + half_bytes, &tmW, wbar, kc, r0);
+        if (kWTiles == 2) tma_load_2d(st + half_bytes + q_tile_bytes, &tmW, wbar, kc, p.dual_offset + r0);
       } else if (SWAP) {
         tma_load_2d(st, &tmA, &ctl->full[s], kc, a0);
         if (kATiles == 2) tma_load_2d(st + kATileBytes, &tmA, &ctl->full[s], kc, p.dual_offset + a0);
@@ -203,15 +179,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // weights never depend on the previous kernel: fill the ring with them first
     const int pre = min(p.stages, kb_count);
     for (int i = 0; i < pre; ++i) {
-      mbar_arrive_expect_tx(&ctl->full[i], tx);
+      if (W8) mbar_arrive_expect_tx(&ctl->qfull[i], txq);
+      else mbar_arrive_expect_tx(&ctl->full[i], tx);
       load_weights(i, i);
     }
+    issued_q = pre;
     pdl_wait();
-    for (int i = 0; i < pre; ++i) load_acts(i, i);
+    for (int i = 0; i < pre; ++i) {
+      if (W8) mbar_arrive_expect_tx(&ctl->full[i], tx);
+      load_acts(i, i);
+    }
     issued = pre;
     for (int i = pre; i < kb_count; ++i) {
       const int s = i % p.stages;
       const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
+      if (W8) {
+        if (!mbar_wait(&ctl->qempty[s], ph ^ 1u)) {
+          report_status(p.status, kStatusTmaTimeout, kTagW8A16, i);
+          ok = false;
+          break;
+        }
+        if (*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag)) { ok = false; break; }
+        mbar_arrive_expect_tx(&ctl->qfull[s], txq);
+        load_weights(i, s);
+        issued_q = i + 1;
+      }
       if (!mbar_wait(&ctl->empty[s], ph ^ 1u)) {
         report_status(p.status, kStatusTmaTimeout, kTagGemmTc, i);
         ok = false;
@@ -219,7 +211,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       if (*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag)) { ok = false; break; }
       mbar_arrive_expect_tx(&ctl->full[s], tx);
-      load_weights(i, s);
+      if (!W8) load_weights(i, s);
       load_acts(i, s);
       issued = i + 1;
     }
@@ -229,6 +221,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int first = issued > p.stages ? issued - p.stages : 0;
       for (int i = first; i < issued; ++i)
         mbar_wait(&ctl->full[i % p.stages], (uint32_t)(i / p.stages) & 1u, 20ull * 1000 * 1000);
+      if (W8) {
+        const int firstq = issued_q > p.stages ? issued_q - p.stages : 0;
+        for (int i = firstq; i < issued_q; ++i)
+          mbar_wait(&ctl->qfull[i % p.stages], (uint32_t)(i / p.stages) & 1u, 20ull * 1000 * 1000);
+      }
     }
   } else {
     pdl_wait();
@@ -239,11 +236,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int i = 0; i < kb_count; ++i) {
       const int s = i % p.stages;
       const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
-      if (!mbar_wait(&ctl->full[s], ph)) {
+      // the int8 tile has landed, and the MMAs that read this stage's 16-bit tile one ring turn ago are done
+      if (!mbar_wait(&ctl->qfull[s], ph) || !mbar_wait(&ctl->empty[s], ph ^ 1u)) {
         report_status(p.status, kStatusMmaTimeout, kTagW8A16, i);
         ctl->abort_flag = 1;
         break;
       }
+      if (*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag)) break;
       uint8_t* st = smem + (size_t)s * stage_bytes;
 #pragma unroll
       for (int wt = 0; wt < kWTiles; ++wt) {
@@ -261,7 +260,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       fence_proxy_async();   // generic-proxy writes -> visible to the tensor core's async-proxy reads
       __syncwarp();
-      if (lane_id() == 0) mbar_arrive(&ctl->ready[s]);
+      if (lane_id() == 0) {
+        mbar_arrive(&ctl->ready[s]);
+        mbar_arrive(&ctl->qempty[s]);
+      }
     }
   }
   // --------------------------------------------------------- MMA issuer ----
@@ -1073,6 +1075,7 @@ extern "C" int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem
 namespace rf {
 bool gemm_ps_eligible(const RfGemm* g, bool swap, int splits);   // gemm_ps.cu: persistent kernel for large M
 int launch_gemm_ps(const RfGemm* g, cudaStream_t stream);
+int widen_packed(const void* src, void* dst, int64_t blocks, int dtype, cudaStream_t stream);   // gemm_ps.cu
 }
 
 static int run_gemm(const RfGemm* g, cudaStream_t stream, bool w8) {
@@ -1083,6 +1086,20 @@ static int run_gemm(const RfGemm* g, cudaStream_t stream, bool w8) {
   if (rc) return rc;
   if (!w8 && g->force_splits == 0 && g->force_bn == 0 && rf::gemm_ps_eligible(g, pl.swap != 0, pl.splits))
     return rf::launch_gemm_ps(g, stream);
+  if (w8 && !pl.swap && g->M > 256 && g->w_packed && g->w_scratch && g->force_splits == 0 && g->force_bn == 0) {
+    // Large token counts are compute-bound: widen the int8 weight image once into the caller's scratch (a pass
+    // over the weights costs a few per cent of the GEMM) and run the 16-bit kernels, whose main loop has no
+    // converter stage; the per-channel scale stays in the epilogue, so the result is (X . Q^T) * s as before.
+    const int64_t blocks = (int64_t)(g->dual_offset > 0 ? 2 : 1) * ceil_div(g->N, kBM) * ceil_div(g->K, kBK);
+    if ((uint64_t)blocks * kATileBytes <= g->w_scratch_bytes) {
+      rc = rf::widen_packed(g->w, g->w_scratch, blocks, g->dtype, stream);
+      if (rc) return rc;
+      RfGemm g2 = *g;
+      g2.w = g->w_scratch;
+      g2.w_int8 = 0;
+      return run_gemm(&g2, stream, false);
+    }
+  }
   if (g->ar_world > 1)
     RF_REQUIRE(pl.grid_x * pl.grid_y * 8 * g->ar_world <= g->ar_flag_count / 2,
                "all-reduce needs %d flags, have %d", pl.grid_x * pl.grid_y * 8 * g->ar_world, g->ar_flag_count / 2);

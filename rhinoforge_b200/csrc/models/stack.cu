@@ -29,8 +29,8 @@ struct Stack {
   uint8_t* base = nullptr;
   uint64_t bytes = 0;
   uint64_t off_xn = 0, off_attn = 0, off_tmp = 0, off_wide = 0, off_conv = 0, off_head_xn = 0, off_logits = 0,
-           off_argmax = 0, off_attn_ws = 0, off_status = 0, total = 0;
-  uint64_t attn_ws_bytes = 0, argmax_bytes = 0;
+           off_argmax = 0, off_attn_ws = 0, off_wscratch = 0, off_status = 0, total = 0;
+  uint64_t attn_ws_bytes = 0, argmax_bytes = 0, wscratch_bytes = 0;
 
   int qkv_dim() const { return (cfg.Hq + 2 * cfg.Hkv) * cfg.hd + (cfg.attn_gate ? cfg.Hq * cfg.hd : 0); }
   // Gated-DeltaNet geometry
@@ -56,6 +56,17 @@ struct Stack {
     off_argmax = o; o += al(argmax_bytes);
     attn_ws_bytes = cfg.paged_kv ? rf_attn_decode_scratch_bytes(cfg.max_seqs, cfg.Hq, cfg.hd) : 0;
     off_attn_ws = o; o += al(attn_ws_bytes);
+    // W8A16 with prefill-sized token counts: room for the largest weight widened to 16 bits (tile-major image)
+    wscratch_bytes = 0;
+    if (cfg.weights_int8 && cfg.weights_packed && cfg.max_tokens > 256) {
+      auto img = [](uint64_t rows, uint64_t K, uint64_t sections) {
+        return sections * ((rows + 127) / 128) * 128 * ((K + 63) / 64) * 64 * 2;
+      };
+      const uint64_t H = (uint64_t)cfg.hidden, I = (uint64_t)cfg.inter;
+      wscratch_bytes = std::max(std::max(img(qkv_dim(), H, 1), img(H, (uint64_t)cfg.Hq * cfg.hd, 1)),
+                                std::max(glu() ? img(I, H, 2) : img(I, H, 1), img(H, I, 1)));
+    }
+    off_wscratch = o; o += al(wscratch_bytes);
     off_status = o; o += al(kStatusWords * sizeof(int32_t));
     total = o;
   }
@@ -89,6 +100,10 @@ static int linear(const Stack& s, const void* x, int64_t ldx, const void* w, con
   g.M = M; g.N = N; g.K = K; g.dtype = s.cfg.dtype; g.act = act; g.dual_offset = dual_offset;
   g.w_int8 = s.cfg.weights_int8 && scale != nullptr;
   g.w_packed = s.cfg.weights_packed;
+  if (g.w_int8 && s.wscratch_bytes) {
+    g.w_scratch = s.at(s.off_wscratch);
+    g.w_scratch_bytes = s.wscratch_bytes;
+  }
   g.status = s.status();
   g.force_swap = -1;
   const bool ar = all_reduce && s.cfg.tp_world > 1;

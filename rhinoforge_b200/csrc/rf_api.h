@@ -58,6 +58,10 @@ typedef struct RfGemm {
   // image, so one 16 KB (int8: 8 KB) bulk copy per block streams HBM pages front to back.  Rows are
   // padded to 128 per section (dual: gate section, then up section), K to 64; ldw is ignored.
   int32_t w_packed;
+  // W8A16 with more than 256 tokens: device scratch for the widened (16-bit, tile-major) weight image, twice
+  // the bytes of the int8 image.  Null: the int8 tile is widened inside the main loop for every token count.
+  void* w_scratch;
+  uint64_t w_scratch_bytes;
 } RfGemm;
 // bytes of the tile-major image of a [rows, K] weight with `sections` equal row sections
 uint64_t rf_pack_weight_bytes(int64_t rows, int64_t K, int32_t sections, int32_t elem_bytes);

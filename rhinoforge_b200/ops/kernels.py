@@ -55,13 +55,15 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          act: Optional[str] = None, dual: bool = False, status: Optional[torch.Tensor] = None,
          force_splits: int = 0, force_swap: int = -1, force_bn: int = 0, use_gemv: bool = False,
          ws: Optional[torch.Tensor] = None, sem: Optional[torch.Tensor] = None,
-         comm=None, packed_shape: Optional[tuple] = None) -> torch.Tensor:
+         comm=None, packed_shape: Optional[tuple] = None, w_scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out = epilogue(x @ w.T)`` on the tcgen05 kernel (or the CUDA-core GEMV).
 
     ``dual=True``: ``w`` stacks ``[gate; up]`` (2N rows) and ``act`` is a ``*_mul``
     activation, giving ``act(x@gate.T) * (x@up.T)`` with N columns.
     ``w`` may be int8 with ``scale`` (per output channel) for the GEMV path.
     ``comm``: a :class:`rhinoforge_b200.parallel.symm.CommBuffers` for the fused all-reduce.
+    ``w_scratch``: device bytes (twice the packed int8 image) that let a W8A16 GEMM of more than 256 tokens widen the
+    weights once and run the 16-bit kernels.
     """
     M, K = x.shape
     if packed_shape is not None:          # ``w`` is the tile-major image made by pack_weight(); (rows, K) is its logical shape
@@ -89,6 +91,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     g.w_int8 = 1 if w.dtype == torch.int8 else 0
     g.status = _ptr(status)
     g.force_splits, g.force_swap, g.force_bn = force_splits, force_swap, force_bn
+    if w_scratch is not None:
+        g.w_scratch, g.w_scratch_bytes = w_scratch.data_ptr(), w_scratch.numel() * w_scratch.element_size()
     lib = N.lib()
     if use_gemv:
         N.check(lib.rf_gemv(C.byref(g), _stream()), "rf_gemv")

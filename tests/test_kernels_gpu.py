@@ -520,3 +520,28 @@ def test_manual_graph_capture_replays_with_refilled_inputs(status):
     with pytest.raises(RuntimeError, match="shape_bucket"):
         g.replay(torch.randn(41, 256, device="cuda").half())
     g.invalidate()
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("dual", [False, True])
+def test_gemm_w8a16_large_m_widens_once_and_matches(dt, dual, status):
+    """W8A16 with a prefill-sized token count and caller scratch: the int8 image is widened once and the 16-bit
+    (persistent) kernel runs; the result equals ``(x . q^T) * scale`` like the in-loop path without scratch."""
+    from rhinoforge_b200.ops import kernels as K_
+    torch.manual_seed(3)
+    M, N, K = 2304, 2560, 512
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    rows = 2 * N if dual else N
+    q = torch.randint(-127, 128, (rows, K), device="cuda", dtype=torch.int8)
+    sc = (torch.rand(rows, device="cuda") * 0.002 + 0.0005).to(dt)
+    qp = K_.pack_weight(q, 2 if dual else 1)
+    scratch = torch.empty(2 * qp.numel(), dtype=torch.uint8, device="cuda")
+    kw = dict(packed_shape=(rows, K), scale=sc, status=status)
+    if dual:
+        kw.update(act="silu_mul", dual=True)
+    y = K_.gemm(x, qp, w_scratch=scratch, **kw)
+    y0 = K_.gemm(x, qp, **kw)
+    z = (x.float() @ q.float().t()) * sc.float()
+    ref = torch.nn.functional.silu(z[:, :N]) * z[:, N:] if dual else z
+    _close(y, ref, dt, scale=max(1.0, ref.abs().max().item()))
+    _close(y0, ref, dt, scale=max(1.0, ref.abs().max().item()))
