@@ -57,7 +57,7 @@ class ClockSampler:
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.proc, self.lines, self.first = index, None, [], 0
 
     def start(self):
         try:
@@ -71,6 +71,17 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def wait_first(self, timeout_s: float = 8.0) -> None:
+        """Block until the first sample has arrived (nvidia-smi takes a while to start on an 8-GPU box), so that a
+        short timed region is not over before sampling begins."""
+        t0 = time.time()
+        while self.proc is not None and not self.lines and time.time() - t0 < timeout_s:
+            time.sleep(0.01)
+
+    def mark(self) -> None:
+        """Start of the timed region: only samples taken from here on are reported."""
+        self.first = len(self.lines)
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -80,7 +91,10 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
-        for ln in self.lines:
+        lines = self.lines[self.first:]
+        if len(lines) < 2:       # region shorter than two sampling periods: include the warm-up samples just before it
+            lines = self.lines[max(0, self.first - 4):]
+        for ln in lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -141,7 +155,9 @@ def run(args) -> dict:
         sampler = ClockSampler(dev.index or 0)
         sampler.start()
         eng.decode(args.warmup)
+        sampler.wait_first()
         tp.barrier(); torch.cuda.synchronize()
+        sampler.mark()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         g = eng.graphs[B]
@@ -209,11 +225,13 @@ def run(args) -> dict:
 def _timed(fn, steps: int, warmup: int):
     """(per-call device ms list, clocks): CUDA events around every call, clocks sampled meanwhile."""
     import torch
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
+    sampler.wait_first()
+    sampler.mark()
     ms = []
     for _ in range(steps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
