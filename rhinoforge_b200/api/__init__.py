@@ -8,10 +8,10 @@ _LAZY = {
     "RPUModelForConditionalGeneration": ("conditional_generation", "RPUModelForConditionalGeneration"),
     "Qwen3_5Cache": ("qwen3_5_cache", "Qwen3_5Cache"),
     "Pi05Policy": ("policy", "Pi05Policy"),
-    "WallOssPolicy": ("wall_oss", "WallOssPolicy"),
-    "Lingbot2Policy": ("lingbot2", "Lingbot2Policy"),
-    "HyEmbodiedPolicy": ("hy_embodied", "HyEmbodiedPolicy"),
-    "RhinoVLAPolicy": ("rhinovla", "RhinoVLAPolicy"),
+    "WallOssPolicy": ("_unbuilt", "WallOssPolicy"),
+    "Lingbot2Policy": ("_unbuilt", "Lingbot2Policy"),
+    "HyEmbodiedPolicy": ("_unbuilt", "HyEmbodiedPolicy"),
+    "RhinoVLAPolicy": ("_unbuilt", "RhinoVLAPolicy"),
 }
 
 

@@ -1,0 +1,41 @@
+"""Policy facades of model families that this framework does not run yet.
+
+The classes exist so that ``rpu_backend.api.WallOssPolicy`` and its siblings import and fail in a defined way: every
+constructor path raises :class:`UnsupportedModelError` naming the family, what it would need and what is available
+instead, before any checkpoint is read (the reference's facades: ``python/rpu_backend/api/wall_oss.py``,
+``lingbot2.py``, ``hy_embodied.py``, ``rhinovla.py``).  The shared pieces those policies use - runtime-environment
+validation, action de-normalisation, 6-D rotation decoding - are built (``_runtime_env``, ``action_denorm``,
+``hy_action_decode``), and so are the towers they start from (Qwen2.5-VL ViT, SigLIP, the Qwen2.5 / Qwen3 decoder stack).
+"""
+from __future__ import annotations
+
+from typing import Any
+
+from .errors import UnsupportedModelError
+
+
+def _facade(name: str, family: str, needs: str):
+    def refuse(cls, *args: Any, **kwargs: Any):
+        raise UnsupportedModelError(f"{family} is not built in this framework ({needs}); "
+                                    "the policy that runs today is Pi05Policy")
+
+    body = {
+        "__doc__": f"{family}: defined, not runnable (see :mod:`rhinoforge_b200.api._unbuilt`).",
+        "FAMILY": family,
+        "from_checkpoint": classmethod(refuse),
+        "from_pretrained": classmethod(refuse),
+        "__init__": lambda self, *a, **k: refuse(type(self)),
+    }
+    return type(name, (), body)
+
+
+WallOssPolicy = _facade("WallOssPolicy", "Wall-OSS (Qwen2.5-VL backbone with a flow-matching action expert)",
+                        "needs the mixture-of-transformers action step and its denoise loop")
+Lingbot2Policy = _facade("Lingbot2Policy", "LingBot-VLA v2 (sparse-MoE action expert)",
+                         "needs the MoE expert MLP inside the native stack")
+HyEmbodiedPolicy = _facade("HyEmbodiedPolicy", "HunYuan embodied VLA (HYViT2 tower, twin-weight prefill, action expert)",
+                           "needs the HYViT2 tower and row-routed twin weights")
+RhinoVLAPolicy = _facade("RhinoVLAPolicy", "RhinoVLA (adaRMS + QK-norm + M-RoPE action expert over a prefix KV)",
+                         "needs its action expert recipe on the native stack")
+
+__all__ = ["WallOssPolicy", "Lingbot2Policy", "HyEmbodiedPolicy", "RhinoVLAPolicy"]
