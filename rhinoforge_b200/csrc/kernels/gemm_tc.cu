@@ -48,6 +48,7 @@ struct GemmTcParams {
   const uint8_t* w_packed;  // tile-major weight image (null: row-major weights through the tensor maps)
   int kb_total;             // k blocks of the whole weight (row-tile stride of the packed image)
   int dual_tiles;           // row tiles of the first (gate) section
+  int k_rotate;             // 1: every output tile starts its K loop at a different block
   int ar_two_shot;    // large-M path: 16-bit reduce-scatter to the tile's owner, then broadcast
   int ar_flag2_base;  // first flag of the "result has landed" range
 };
@@ -139,10 +140,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t txq = (uint32_t)(kWTiles * q_tile_bytes);
     int issued = 0, issued_q = 0;
     bool ok = true;
+    // Weight-streaming CTAs would otherwise all walk their (power-of-two sized) weight panels in lock step and
+    // present DRAM with one address offset at a time; each output tile starts its K loop at a different block
+    // and wraps around (the accumulation order changes, deterministically per shape).
+    const int rot = (SWAP && p.k_rotate) ? (int)((blockIdx.x * 11u + blockIdx.y * 7u) % (uint32_t)kb_count) : 0;
+    auto kblock = [&](int i) { const int j = i + rot; return kb0 + (j >= kb_count ? j - kb_count : j); };
     auto load_weights = [&](int i, int s) {
       uint64_t* wbar = W8 ? &ctl->qfull[s] : &ctl->full[s];
       uint8_t* st = smem + (size_t)s * stage_bytes;
-      const int kc = (kb0 + i) * kBK;
+      const int kc = kblock(i) * kBK;
       if (p.w_packed) {
         // contiguous 128-row x 64-column blocks: one bulk copy each
         constexpr uint32_t kBlk = W8 ? (uint32_t)(kBM * kBK) : (uint32_t)kATileBytes;
@@ -153,7 +159,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint8_t* dst = W8 ? st + half_bytes + wt * q_tile_bytes
                             : (SWAP ? st + wt * kATileBytes : st + kATiles * kATileBytes + wt * b_tile_bytes);
           for (int sub = 0; sub < nsub; ++sub) {
-            const uint8_t* src = p.w_packed + ((size_t)(rt0 + sub + wt * p.dual_tiles) * p.kb_total + (kb0 + i)) * kBlk;
+            const uint8_t* src = p.w_packed + ((size_t)(rt0 + sub + wt * p.dual_tiles) * p.kb_total + kblock(i)) * kBlk;
             bulk_load_1d(dst + (size_t)sub * kBlk, src, kBlk, wbar);
           }
         }
@@ -172,7 +178,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     };
     auto load_acts = [&](int i, int s) {
       uint8_t* st = smem + (size_t)s * stage_bytes;
-      const int kc = (kb0 + i) * kBK;
+      const int kc = kblock(i) * kBK;
       if (SWAP) tma_load_2d(st + kATiles * kATileBytes, &tmB, &ctl->full[s], kc, b0);
       else tma_load_2d(st, &tmA, &ctl->full[s], kc, a0);
     };
@@ -1021,6 +1027,10 @@ static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream)
   p.w_packed = g->w_packed ? reinterpret_cast<const uint8_t*>(g->w) : nullptr;
   p.kb_total = pl.k_blocks;
   p.dual_tiles = ceil_div(g->N, kBM);
+  {
+    static const int rot_env = [] { const char* e = getenv("RF_GEMM_K_ROTATE"); return e ? atoi(e) : 1; }();
+    p.k_rotate = rot_env;
+  }
   p.ar_two_shot = (g->ar_world > 1 && !SWAP && g->M > 256) ? 1 : 0;
   p.ar_flag2_base = g->ar_flag_count / 2;
   RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.grid_x, pl.grid_y, pl.splits), dim3(W8 ? 256 : 128), pl.smem_bytes, stream,
