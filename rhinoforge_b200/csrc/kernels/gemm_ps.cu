@@ -27,6 +27,7 @@ constexpr int kPsBM = 128, kPsBK = 64;
 constexpr int kPsATile = kPsBM * kPsBK * 2;      // 16 KB
 constexpr int kPsBlock = 128 * kPsBK * 2;        // one packed weight block
 constexpr int kPsMaxStages = 8;
+constexpr int kPsEpiBytes = 32 * 64 * 2;          // staging of one epilogue warp: 32 rows x 64 columns, 16-bit
 
 struct GemmPsParams {
   void* out; int64_t ldo;
@@ -38,6 +39,7 @@ struct GemmPsParams {
   int tiles_m, tiles_n;   // tiles_m counts tiles of 128*MT rows
   int band;               // row tiles per band of the tile order
   int pf_blocks;          // k blocks prefetched into L2 ahead of the ring
+  int tma_out;            // 1: results leave through shared-memory staging and tiled bulk stores
 };
 
 // Tile order: bands of `band` row tiles; inside a band the row index runs fastest and the weight panel
@@ -60,7 +62,7 @@ struct alignas(8) GemmPsCtl {
 
 template <typename T, bool DUAL, int MT>
 __global__ void __launch_bounds__(64 + 128 * MT)
-gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
+gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmO, const GemmPsParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -73,7 +75,9 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
   const int half_cols = kW * bn;                           // TMEM columns of one 128-row half
   const int acc_cols = MT * half_cols;                     // ... of one accumulator buffer
   const int nbuf = 2 * acc_cols <= 512 ? 2 : 1;
-  GemmPsCtl* ctl = reinterpret_cast<GemmPsCtl*>(smem + (size_t)p.stages * stage_bytes);
+  // after the ring: one 4 KB output staging buffer per epilogue warp, then the control block
+  uint8_t* epi_stage = smem + (size_t)p.stages * stage_bytes;
+  GemmPsCtl* ctl = reinterpret_cast<GemmPsCtl*>(epi_stage + 4 * MT * kPsEpiBytes);
   const int tiles = p.tiles_m * p.tiles_n;
 
   if (tid == 0) {
@@ -88,6 +92,7 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
     ctl->abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
+    if (p.tma_out) tma_prefetch_desc(&tmO);
   }
   if (warp == 1) {
     tmem_alloc(&ctl->tmem_base, 512u);
@@ -265,6 +270,25 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
       // instruction bursts of the epilogue warps delay the single MMA-issuing lane that shares their schedulers,
       // so the loop is kept short: scale / bias work and the activation switch are hoisted out of the element loop.
       const bool affine = scale || bias || p.row_scale;   // per-element scale / bias work, hoisted out of the loop
+      // Output path without a residual: 64 finished columns of the warp's 32 rows are parked in a swizzled
+      // staging tile and leave as ONE tiled bulk store issued by lane 0 - whole 128-byte lines, asynchronous,
+      // no store instructions on the epilogue warps (16-byte stores to 32 rows per instruction kept the store
+      // queue saturated: 537 MB on the L1->L2 path for 67 MB of output).
+      const bool tma_out = p.tma_out != 0;
+      uint8_t* stg = epi_stage + (size_t)(warp - 2) * kPsEpiBytes;
+      const int row0 = (tm * MT + half) * kPsBM + quarter * 32;
+      auto chunk_begin = [&]() {                       // the previous bulk store has read the staging tile
+        if (lane == 0) bulk_wait_read_all();
+        __syncwarp();
+      };
+      auto chunk_end = [&](int c_first) {              // c_first: first column of the 64-column chunk in the tile
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && row0 < M && n_base + c_first < N) {
+          tma_store_2d(&tmO, stg, n_base + c_first, row0);
+          bulk_commit_group();
+        }
+      };
       auto finish16 = [&](int n0, const uint32_t* g16, const uint32_t* u16) {
         float g[16], u[16], v[16];
 #pragma unroll
@@ -291,7 +315,15 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
           }
         }
         apply_act_n<16>(p.act, g, u, v);
-        if (vec_ok && n0 + 16 <= N) {
+        if (tma_out) {
+          // row `lane` of the warp's staging tile, 128-byte swizzled as the bulk store expects it
+          const int ch = ((n0 - n_base) >> 3) & 7;
+          float lo[8], hi[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
+          store8(reinterpret_cast<T*>(stg + lane * 128 + ((ch ^ (lane & 7)) << 4)), lo);
+          store8(reinterpret_cast<T*>(stg + lane * 128 + (((ch + 1) ^ (lane & 7)) << 4)), hi);
+        } else if (vec_ok && n0 + 16 <= N) {
           if (resid) {
             float r0[8], r1[8];
             load8(resid + (size_t)row * p.ldr + n0, r0);
@@ -321,12 +353,15 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
           tmem_ld32(acc + c0, ra);
           tmem_ld32(acc + bn + c0, rb);
           tmem_ld_wait();
-          if (row >= M) continue;
+          if (tma_out && (c0 & 63) == 0) chunk_begin();
+          if (row < M || tma_out) {
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const int n0 = n_base + c0 + q * 16;
-            if (n0 < N) finish16(n0, ra + q * 16, rb + q * 16);
+            for (int q = 0; q < 2; ++q) {
+              const int n0 = n_base + c0 + q * 16;
+              if (n0 < N || tma_out) finish16(n0, ra + q * 16, rb + q * 16);
+            }
           }
+          if (tma_out && (c0 & 63) == 32) chunk_end(c0 - 32);
         }
       } else {
         for (int c0 = 0; c0 < bn; c0 += 16) {
@@ -334,7 +369,9 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
           tmem_ld16(acc + c0, ra);
           tmem_ld_wait();
           const int n0 = n_base + c0;
-          if (row < M && n0 < N) finish16(n0, ra, ra);
+          if (tma_out && (c0 & 63) == 0) chunk_begin();
+          if ((row < M && n0 < N) || tma_out) finish16(n0, ra, ra);
+          if (tma_out && (c0 & 63) == 48) chunk_end(c0 - 48);
         }
       }
       // this accumulator buffer may now be overwritten by a later tile
@@ -342,6 +379,7 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const GemmPsParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->acc_empty[b]);
     }
+    if (p.tma_out && lane == 0) bulk_wait_all();       // the last stores are complete before the CTA retires
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -356,14 +394,24 @@ static int launch_ps(const RfGemm* g, int bn, cudaStream_t stream) {
     RF_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
-  CUtensorMap tmA;
+  CUtensorMap tmA, tmO;
   int rc = make_tmap_2d(&tmA, g->x, g->dtype, 2, g->K, g->M, g->ldx, kPsBK, kPsBM, true);
   if (rc) return rc;
+  static const bool tma_out_enabled = [] { const char* e = getenv("RF_GEMM_PS_TMA_OUT"); return !(e && e[0] == '0'); }();
+  const bool tma_out = tma_out_enabled && !g->residual && (g->ldo & 7) == 0 &&
+                       (reinterpret_cast<uintptr_t>(g->out) & 15) == 0;
+  if (tma_out) {
+    rc = make_tmap_2d(&tmO, g->out, g->dtype, 2, g->N, g->M, g->ldo, 64, 32, true);
+    if (rc) return rc;
+  } else {
+    tmO = tmA;
+  }
   GemmPsParams p = {};
   p.out = g->out; p.ldo = g->ldo; p.residual = g->residual; p.ldr = g->ldr;
   p.bias = g->bias; p.scale = g->scale; p.row_scale = g->row_scale;
   p.w_packed = reinterpret_cast<const uint8_t*>(g->w);
   p.status = g->status;
+  p.tma_out = tma_out ? 1 : 0;
   p.M = g->M; p.N = g->N; p.k_blocks = ceil_div(g->K, kPsBK); p.bn = bn;
   p.act = g->act; p.dual_offset = g->dual_offset; p.dual_tiles = ceil_div(g->N, 128);
   p.tiles_m = ceil_div(g->M, kPsBM * MT); p.tiles_n = ceil_div(g->N, bn);
@@ -377,12 +425,12 @@ static int launch_ps(const RfGemm* g, int bn, cudaStream_t stream) {
     static const int pf_kb = [] { const char* e = getenv("RF_GEMM_L2_PREFETCH_KB"); return e ? atoi(e) : 0; }();
     p.pf_blocks = std::min(16, pf_kb * 1024 / stage_bytes);
   }
-  const int ctl_bytes = (int)sizeof(GemmPsCtl) + 1024 /*alignment slack*/;
+  const int ctl_bytes = (int)sizeof(GemmPsCtl) + 1024 /*alignment slack*/ + 4 * MT * kPsEpiBytes;
   p.stages = std::min(kPsMaxStages, (227 * 1024 - ctl_bytes) / stage_bytes);
   RF_REQUIRE(p.stages >= 2, "persistent GEMM: a %d-byte stage does not fit twice in shared memory", stage_bytes);
   const size_t smem = (size_t)p.stages * stage_bytes + ctl_bytes;
   const int grid = std::min(p.tiles_m * p.tiles_n, sm_count());
-  RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(grid), dim3(64 + 128 * MT), smem, stream, 1, tmA, p));
+  RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(grid), dim3(64 + 128 * MT), smem, stream, 1, tmA, tmO, p));
   ::rf::count_launch();
   return RF_OK;
 }

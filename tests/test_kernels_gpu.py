@@ -492,6 +492,14 @@ def test_gemm_persistent_kernel(dt, M, N, K, dual, status):
     y2 = K_.gemm(x, wp, packed_shape=(rows, K), act="silu_mul", dual=True, status=status) if dual else \
         K_.gemm(x, wp, packed_shape=(rows, K), bias=b, residual=r, status=status)
     assert torch.equal(y, y2), "two launches of the same GEMM must agree bit for bit"
+    if not dual:
+        # without a residual the results leave through staging tiles and tiled bulk stores
+        y3 = K_.gemm(x, wp, packed_shape=(rows, K), bias=b, status=status)
+        _close(y3, x.float() @ w.float().t() + b.float(), dt, scale=max(1.0, ref.abs().max().item()))
+        view = torch.zeros(M, N + 8, device="cuda", dtype=dt)           # strided output rows
+        K_.gemm(x, wp, packed_shape=(rows, K), out=view[:, :N], status=status)
+        _close(view[:, :N], x.float() @ w.float().t(), dt, scale=max(1.0, ref.abs().max().item()))
+        assert float(view[:, N:].abs().max()) == 0.0, "columns past N must stay untouched"
 
 
 def test_manual_graph_capture_replays_with_refilled_inputs(status):
