@@ -39,7 +39,8 @@ struct GemmPsParams {
   int tiles_m, tiles_n;   // tiles_m counts tiles of 128*MT rows
   int band;               // row tiles per band of the tile order
   int pf_blocks;          // k blocks prefetched into L2 ahead of the ring
-  int tma_out;            // 1: results leave through shared-memory staging and tiled bulk stores
+  int tma_out;            // results leave through shared-memory staging: 1 tiled bulk stores, 2 bulk reduce-adds
+                          // into an output that already holds the residual (out == residual)
 };
 
 // Tile order: bands of `band` row tiles; inside a band the row index runs fastest and the weight panel
@@ -270,10 +271,12 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       // instruction bursts of the epilogue warps delay the single MMA-issuing lane that shares their schedulers,
       // so the loop is kept short: scale / bias work and the activation switch are hoisted out of the element loop.
       const bool affine = scale || bias || p.row_scale;   // per-element scale / bias work, hoisted out of the loop
-      // Output path without a residual: 64 finished columns of the warp's 32 rows are parked in a swizzled
-      // staging tile and leave as ONE tiled bulk store issued by lane 0 - whole 128-byte lines, asynchronous,
-      // no store instructions on the epilogue warps (16-byte stores to 32 rows per instruction kept the store
-      // queue saturated: 537 MB on the L1->L2 path for 67 MB of output).
+      // Output path without a residual, or with the residual already in place (out == residual, the decoder's
+      // out-projection and down-projection): 64 finished columns of the warp's 32 rows are parked in a swizzled
+      // staging tile and leave as ONE tiled bulk store (or bulk reduce-add, which makes the residual add an L2
+      // operation) issued by lane 0 - whole 128-byte lines, asynchronous, no load or store instructions on the
+      // epilogue warps (16-byte stores to 32 rows per instruction kept the store queue saturated: 537 MB on the
+      // L1->L2 path for 67 MB of output).
       const bool tma_out = p.tma_out != 0;
       uint8_t* stg = epi_stage + (size_t)(warp - 2) * kPsEpiBytes;
       const int row0 = (tm * MT + half) * kPsBM + quarter * 32;
@@ -285,7 +288,8 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         fence_proxy_async();
         __syncwarp();
         if (lane == 0 && row0 < M && n_base + c_first < N) {
-          tma_store_2d(&tmO, stg, n_base + c_first, row0);
+          if (p.tma_out == 2) tma_reduce_add_2d(&tmO, stg, n_base + c_first, row0);
+          else tma_store_2d(&tmO, stg, n_base + c_first, row0);
           bulk_commit_group();
         }
       };
@@ -398,7 +402,8 @@ static int launch_ps(const RfGemm* g, int bn, cudaStream_t stream) {
   int rc = make_tmap_2d(&tmA, g->x, g->dtype, 2, g->K, g->M, g->ldx, kPsBK, kPsBM, true);
   if (rc) return rc;
   static const bool tma_out_enabled = [] { const char* e = getenv("RF_GEMM_PS_TMA_OUT"); return !(e && e[0] == '0'); }();
-  const bool tma_out = tma_out_enabled && !g->residual && (g->ldo & 7) == 0 &&
+  const bool inplace_resid = g->residual == g->out && g->ldr == g->ldo;
+  const bool tma_out = tma_out_enabled && (!g->residual || inplace_resid) && (g->ldo & 7) == 0 &&
                        (reinterpret_cast<uintptr_t>(g->out) & 15) == 0;
   if (tma_out) {
     rc = make_tmap_2d(&tmO, g->out, g->dtype, 2, g->N, g->M, g->ldo, 64, 32, true);
@@ -411,7 +416,7 @@ static int launch_ps(const RfGemm* g, int bn, cudaStream_t stream) {
   p.bias = g->bias; p.scale = g->scale; p.row_scale = g->row_scale;
   p.w_packed = reinterpret_cast<const uint8_t*>(g->w);
   p.status = g->status;
-  p.tma_out = tma_out ? 1 : 0;
+  p.tma_out = tma_out ? (g->residual ? 2 : 1) : 0;
   p.M = g->M; p.N = g->N; p.k_blocks = ceil_div(g->K, kPsBK); p.bn = bn;
   p.act = g->act; p.dual_offset = g->dual_offset; p.dual_tiles = ceil_div(g->N, 128);
   p.tiles_m = ceil_div(g->M, kPsBM * MT); p.tiles_n = ceil_div(g->N, bn);

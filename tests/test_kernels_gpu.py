@@ -500,6 +500,10 @@ def test_gemm_persistent_kernel(dt, M, N, K, dual, status):
         K_.gemm(x, wp, packed_shape=(rows, K), out=view[:, :N], status=status)
         _close(view[:, :N], x.float() @ w.float().t(), dt, scale=max(1.0, ref.abs().max().item()))
         assert float(view[:, N:].abs().max()) == 0.0, "columns past N must stay untouched"
+        # residual already in the output buffer (out == residual): the add happens in the bulk reduce
+        acc = r.clone()
+        K_.gemm(x, wp, packed_shape=(rows, K), residual=acc, out=acc, status=status)
+        _close(acc, x.float() @ w.float().t() + r.float(), dt, scale=max(1.0, ref.abs().max().item()))
 
 
 def test_manual_graph_capture_replays_with_refilled_inputs(status):
