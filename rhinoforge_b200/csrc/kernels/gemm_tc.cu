@@ -829,49 +829,6 @@ struct GemmPlan {
   int sem_count;
 };
 
-// How many clusters of `cluster_z` CTAs with `smem` bytes each can be resident at once.  Cluster
-// placement is per GPC, so this is not simply SMs * CTAs-per-SM / cluster_z; the answer decides whether a
-// split-K grid runs as one wave or spills into a second one.  Queried once per (cluster size, smem) and
-// cached; the fp16 swap kernel stands in for all instantiations (shared memory is what limits residency).
-static int max_resident_clusters(int cluster_z, size_t smem) {
-  static std::mutex mu;
-  static std::map<std::pair<int, size_t>, int> cache;
-  const size_t key_smem = (smem + 8191) & ~size_t(8191);
-  std::lock_guard<std::mutex> lk(mu);
-  auto it = cache.find({cluster_z, key_smem});
-  if (it != cache.end()) return it->second;
-  auto kfn = gemm_tc_kernel<__half, true, false, false>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    attr_set = true;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(8, 8, (unsigned)cluster_z);
-  cfg.blockDim = dim3(128);
-  cfg.dynamicSmemBytes = key_smem > 227 * 1024 ? 227 * 1024 : key_smem;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)cluster_z;
-  cfg.attrs = attr;
-  cfg.numAttrs = cluster_z > 1 ? 1 : 0;
-  int n = 0;
-  int result;
-  if (cluster_z > 1 && cudaOccupancyMaxActiveClusters(&n, kfn, &cfg) == cudaSuccess && n > 0) {
-    result = n;
-  } else {
-    cudaGetLastError();
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kfn, 128, cfg.dynamicSmemBytes) != cudaSuccess || per_sm < 1) {
-      cudaGetLastError();
-      per_sm = cfg.dynamicSmemBytes > 113 * 1024 ? 1 : 2;
-    }
-    result = std::max(1, sm_count() * per_sm / cluster_z);
-  }
-  cache[{cluster_z, key_smem}] = result;
-  return result;
-}
-
 static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   const bool dual = g->dual_offset > 0;
   pl->k_blocks = ceil_div(g->K, kBK);
