@@ -88,7 +88,9 @@ class RfStackConfig(C.Structure):
                                          "causal", "window")] + [("attn_scale", C.c_float)] + \
                [(n, C.c_int32) for n in ("true_hd", "dtype", "max_tokens", "max_seqs", "vocab_local", "vocab_offset",
                                          "tp_world", "tp_rank", "weights_int8", "decode_gemv_max_m", "attn_gate",
-                                         "gdn_Hk", "gdn_Hv", "gdn_Dk", "gdn_Dv", "gdn_conv_k", "weights_packed")]
+                                         "gdn_Hk", "gdn_Hv", "gdn_Dk", "gdn_Dv", "gdn_conv_k", "weights_packed",
+                                         "moe_experts", "moe_top_k", "moe_expert_inter", "moe_score_fn",
+                                         "moe_norm_topk")] + [("moe_routed_scale", C.c_float)]
 
 
 class RfLayerWeights(C.Structure):
@@ -96,7 +98,8 @@ class RfLayerWeights(C.Structure):
         "norm1_w", "norm1_b", "wqkv", "bqkv", "sqkv", "q_norm_w", "k_norm_w", "wo", "bo", "so", "norm2_w", "norm2_b",
         "w_up", "b_up", "s_up", "w_down", "b_down", "s_down", "post_attn_norm_w", "post_mlp_norm_w", "k_pool",
         "v_pool")] + [("mixer", C.c_int64)] + [(n, C.c_void_p) for n in (
-        "gdn_conv_w", "gdn_A_log", "gdn_dt_bias", "gdn_norm_w", "gdn_conv_state", "gdn_rec_state")]
+        "gdn_conv_w", "gdn_A_log", "gdn_dt_bias", "gdn_norm_w", "gdn_conv_state", "gdn_rec_state",
+        "moe_router_w", "moe_router_bias")]
 
 
 class RfStackComm(C.Structure):

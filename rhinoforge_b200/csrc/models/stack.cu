@@ -29,7 +29,7 @@ struct Stack {
   uint8_t* base = nullptr;
   uint64_t bytes = 0;
   uint64_t off_xn = 0, off_attn = 0, off_tmp = 0, off_wide = 0, off_conv = 0, off_head_xn = 0, off_logits = 0,
-           off_argmax = 0, off_attn_ws = 0, off_wscratch = 0, off_status = 0, total = 0;
+           off_argmax = 0, off_attn_ws = 0, off_wscratch = 0, off_moe = 0, off_status = 0, total = 0;
   uint64_t attn_ws_bytes = 0, argmax_bytes = 0, wscratch_bytes = 0;
 
   int qkv_dim() const { return (cfg.Hq + 2 * cfg.Hkv) * cfg.hd + (cfg.attn_gate ? cfg.Hq * cfg.hd : 0); }
@@ -40,6 +40,7 @@ struct Stack {
   int gdn_ba_pad() const { return (cfg.gdn_Hv + 7) / 8 * 8; }
   int gdn_in_dim() const { return cfg.gdn_Hv > 0 ? gdn_conv_dim() + gdn_value_dim() + 2 * gdn_ba_pad() : 0; }
   bool glu() const { return cfg.mlp_kind == RF_MLP_SWIGLU || cfg.mlp_kind == RF_MLP_GEGLU_TANH; }
+  int moe_ld() const { return (cfg.moe_experts + 7) / 8 * 8; }   // row pitch of the router buffers
 
   void plan() {
     auto al = [](uint64_t v) { return (v + 1023) & ~uint64_t(1023); };
@@ -67,6 +68,10 @@ struct Stack {
                                 std::max(glu() ? img(I, H, 2) : img(I, H, 1), img(H, I, 1)));
     }
     off_wscratch = o; o += al(wscratch_bytes);
+    // MoE router: logits and dense routing weights [tokens, experts] (16-bit each), ids + weights of the picks
+    off_moe = o;
+    if (cfg.moe_experts > 0)
+      o += al(T * (uint64_t)moe_ld() * e * 2) + al(T * (uint64_t)std::max(cfg.moe_top_k, 1) * 8);
     off_status = o; o += al(kStatusWords * sizeof(int32_t));
     total = o;
   }
@@ -266,9 +271,31 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     // ---- MLP block
     rc = norm(s, f.hidden, w.norm2_w, w.norm2_b, xn, T, mod2, f.rows_per_mod, st);
     if (rc) return rc;
+    const bool moe = c.moe_experts > 0 && w.moe_router_w != nullptr;
+    void* moe_dense = nullptr;
+    if (moe) {
+      // router: 16-bit logits -> top-k -> dense [tokens, experts] routing weights (zero where not picked)
+      const int E = c.moe_experts, ldE = s.moe_ld();
+      auto al = [](uint64_t v) { return (v + 1023) & ~uint64_t(1023); };
+      uint8_t* mb = s.at<uint8_t>(s.off_moe);
+      void* logits = mb;
+      moe_dense = mb + (uint64_t)c.max_tokens * ldE * esz;
+      uint8_t* picks = mb + al((uint64_t)c.max_tokens * ldE * esz * 2);
+      rc = linear(s, xn, H, w.moe_router_w, nullptr, nullptr, logits, ldE, nullptr, 0, T, E, H, kActNone, 0, false, st);
+      if (rc) return rc;
+      rc = rf_moe_select(logits, ldE, w.moe_router_bias, T, E, c.moe_top_k, c.moe_score_fn, c.moe_norm_topk,
+                         c.moe_routed_scale, reinterpret_cast<int32_t*>(picks),
+                         reinterpret_cast<float*>(picks + (uint64_t)c.max_tokens * c.moe_top_k * 4), moe_dense, ldE,
+                         c.dtype, st);
+      if (rc) return rc;
+    }
     rc = linear(s, xn, H, w.w_up, w.s_up, w.b_up, wide, I, nullptr, 0, T, I, H, act_of(c.mlp_kind),
                 s.glu() ? I : 0, false, st);
     if (rc) return rc;
+    if (moe) {
+      rc = rf_moe_scale_blocks(wide, I, moe_dense, s.moe_ld(), T, c.moe_experts, c.moe_expert_inter, c.dtype, st);
+      if (rc) return rc;
+    }
     if (!side) {
       rc = linear(s, wide, I, w.w_down, w.s_down, w.b_down, f.hidden, H, f.hidden, H, T, H, I, kActNone, 0, true, st);
       if (rc) return rc;
@@ -329,6 +356,13 @@ extern "C" int64_t rf_stack_create(const RfStackConfig* cfg) {
       cfg->tp_world < 1 || cfg->tp_world > 8 || cfg->tp_rank < 0 || cfg->tp_rank >= cfg->tp_world) {
     fail(RF_ERR_BAD_ARG, "invalid stack config (layers=%d hidden=%d Hq=%d Hkv=%d hd=%d inter=%d)", cfg->layers,
          cfg->hidden, cfg->Hq, cfg->Hkv, cfg->hd, cfg->inter);
+    return -1;
+  }
+  if (cfg->moe_experts > 0 &&
+      (cfg->moe_top_k < 1 || cfg->moe_top_k > cfg->moe_experts || cfg->moe_expert_inter <= 0 ||
+       (int64_t)cfg->moe_experts * cfg->moe_expert_inter > cfg->inter || cfg->weights_int8)) {
+    fail(RF_ERR_BAD_ARG, "invalid MoE config (experts=%d top_k=%d expert_inter=%d inter=%d int8=%d)", cfg->moe_experts,
+         cfg->moe_top_k, cfg->moe_expert_inter, cfg->inter, cfg->weights_int8);
     return -1;
   }
   auto s = std::make_unique<Stack>();

@@ -46,6 +46,14 @@ typedef struct RfStackConfig {
   // Gated-DeltaNet layers (LOCAL head counts); gdn_Hv == 0: the stack has none
   int32_t gdn_Hk, gdn_Hv, gdn_Dk, gdn_Dv, gdn_conv_k;
   int32_t weights_packed;       // every linear weight (and the lm_head) is in the tile-major layout of RfGemm.w_packed
+  // Sparse MoE MLP in the dense-einsum form (moe_experts == 0: dense MLP).  `inter` is then the LOCAL width of the
+  // whole expert bank, moe_experts * moe_expert_inter plus the always-on shared expert's columns behind it: w_up /
+  // w_down hold every expert side by side, the router picks moe_top_k experts per token and the routing weight
+  // (zero for an expert that was not picked) scales that expert's column block between the two GEMMs.
+  int32_t moe_experts, moe_top_k, moe_expert_inter;
+  int32_t moe_score_fn;         // 0 sigmoid (+ selection-only bias), 1 softmax
+  int32_t moe_norm_topk;        // picked weights are normalised to sum 1 before the routed scale
+  float moe_routed_scale;
 } RfStackConfig;
 
 typedef struct RfLayerWeights {
@@ -66,6 +74,8 @@ typedef struct RfLayerWeights {
   const void* gdn_norm_w;        // [Dv]
   void* gdn_conv_state;          // [slots, K-1, conv_dim]
   float* gdn_rec_state;          // [slots, Hv, Dk, Dv] fp32
+  const void* moe_router_w;      // [experts, hidden]; null: this layer's MLP is dense
+  const float* moe_router_bias;  // [experts] fp32 selection bias (optional)
 } RfLayerWeights;
 
 typedef struct RfStackComm {

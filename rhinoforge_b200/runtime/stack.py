@@ -53,10 +53,18 @@ class StackSpec:
     decode_gemv_max_m: int = 0
     packed: bool = True        # linear weights in the tile-major layout of ops.kernels.pack_weight
     attn_gate: bool = False
+    # sparse MoE MLP (dense-einsum form): `inter` is then experts * expert_inter + the shared expert's width
+    moe_experts: int = 0
+    moe_top_k: int = 0
+    moe_expert_inter: int = 0
+    moe_score_fn: str = "sigmoid"
+    moe_norm_topk: bool = True
+    moe_routed_scale: float = 1.0
 
 
 LAYER_FIELDS = ("norm1_w", "norm1_b", "wqkv", "bqkv", "sqkv", "q_norm_w", "k_norm_w", "wo", "bo", "so", "norm2_w",
-                "norm2_b", "w_up", "b_up", "s_up", "w_down", "b_down", "s_down", "post_attn_norm_w", "post_mlp_norm_w")
+                "norm2_b", "w_up", "b_up", "s_up", "w_down", "b_down", "s_down", "post_attn_norm_w", "post_mlp_norm_w",
+                "moe_router_w", "moe_router_bias")
 
 
 def pad_heads(w: torch.Tensor, heads: int, hd: int, hd_pad: int, dim: int) -> torch.Tensor:
@@ -101,6 +109,9 @@ class NativeStack:
         sc.tp_world, sc.tp_rank = spec.tp_world, spec.tp_rank
         sc.weights_int8, sc.decode_gemv_max_m = int(spec.weights_int8), spec.decode_gemv_max_m
         sc.weights_packed, sc.attn_gate = int(spec.packed), int(spec.attn_gate)
+        sc.moe_experts, sc.moe_top_k, sc.moe_expert_inter = spec.moe_experts, spec.moe_top_k, spec.moe_expert_inter
+        sc.moe_score_fn = {"sigmoid": 0, "softmax": 1}[spec.moe_score_fn]
+        sc.moe_norm_topk, sc.moe_routed_scale = int(spec.moe_norm_topk), spec.moe_routed_scale
         h = lib.rf_stack_create(C.byref(sc))
         if h < 0:
             N.check(-1, "rf_stack_create")
@@ -114,7 +125,11 @@ class NativeStack:
                 t = lw.get(f)
                 if t is not None:
                     d = self._dev(t)
-                    if spec.packed and f in ("wqkv", "wo", "w_up", "w_down"):
+                    if f == "moe_router_bias":          # fp32 whatever the stack's dtype
+                        self._keep.pop()
+                        d = t.to(self.device, torch.float32).contiguous()
+                        self._keep.append(d)
+                    if spec.packed and f in ("wqkv", "wo", "w_up", "w_down", "moe_router_w"):
                         self._keep.pop()
                         d = K.pack_weight(d, 2 if (f == "w_up" and glu) else 1)
                         self._keep.append(d)

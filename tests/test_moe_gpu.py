@@ -43,3 +43,45 @@ def test_moe_mlp_dense_einsum_equals_sparse_reference():
     want = moe_reference(cfg, sd, x)
     rel = float((got.float() - want).abs().max() / want.abs().max())
     assert rel < 2e-2, rel
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_native_stack_layer_with_moe_mlp(dtype):
+    """The stack executor's MoE branch (router GEMM, top-k, expert bank as one GLU GEMM, routing-weight block scale, one
+    down GEMM with the residual) against the sparse fp32 evaluation.  The attention output projection is zero, so the
+    layer reduces to ``x + moe(rmsnorm(x))``."""
+    from rhinoforge_b200.models.moe import MoEConfig, MoEMLP, moe_reference
+    from rhinoforge_b200.runtime.stack import NativeStack, StackSpec
+    torch.manual_seed(2)
+    H, E, I, S, T = 128, 16, 64, 64, 70
+    cfg = MoEConfig(hidden=H, experts=E, top_k=4, expert_inter=I, shared_inter=S, routed_scale=2.5)
+    sd = {"router.weight": torch.randn(E, H) * 0.3, "router.bias": torch.randn(E) * 0.05}
+    for e in range(E):
+        for n, shape in (("gate_proj", (I, H)), ("up_proj", (I, H)), ("down_proj", (H, I))):
+            sd[f"experts.{e}.{n}.weight"] = torch.randn(shape) * 0.08
+    for n, shape in (("gate_proj", (S, H)), ("up_proj", (S, H)), ("down_proj", (H, S))):
+        sd[f"shared.{n}.weight"] = torch.randn(shape) * 0.08
+    sd = {k: v.cuda().to(dtype) for k, v in sd.items()}
+    sd["router.bias"] = sd["router.bias"].float()
+    bank = MoEMLP(cfg, sd, dtype=dtype)                     # builds the side-by-side expert bank
+    norm_w = (1.0 + 0.1 * torch.randn(H, device="cuda")).to(dtype)
+    inter = E * I + S
+    lw = dict(norm1_w=torch.ones(H), wqkv=torch.randn(3 * 2 * 64, H) * 0.05, wo=torch.zeros(H, 2 * 64), norm2_w=norm_w,
+              w_up=bank.w_gate_up, w_down=bank.w_down, moe_router_w=sd["router.weight"], moe_router_bias=sd["router.bias"])
+    spec = StackSpec(layers=1, hidden=H, heads=2, kv_heads=2, head_dim=64, inter=inter, norm="rms", mlp="swiglu",
+                     paged_kv=False, causal=False, max_tokens=128, max_seqs=4, moe_experts=E, moe_top_k=4,
+                     moe_expert_inter=I, moe_routed_scale=2.5)
+    stack = NativeStack(spec, [lw], dtype=dtype)
+    x = (torch.randn(T, H, device="cuda") * 0.5).to(dtype)
+    hidden = x.clone()
+    lens = torch.tensor([40, 30], dtype=torch.int32, device="cuda")
+    starts = torch.tensor([0, 40], dtype=torch.int32, device="cuda")
+    stack.forward(hidden, q_start=starts, q_len=lens, kv_len=lens, max_q_len=40, max_kv_len=40,
+                  pos=torch.zeros(T, dtype=torch.int32, device="cuda"))
+    stack.check_status()
+    xf = x.float()
+    xn = (norm_w.float() * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6))).to(dtype)
+    want = xf + moe_reference(cfg, sd, xn)
+    rel = float((hidden.float() - want).abs().max() / want.abs().max())
+    assert rel < (2e-2 if dtype == torch.float16 else 6e-2), rel
+    stack.close()
