@@ -78,6 +78,23 @@ inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Launch WITHOUT programmatic dependent launch: the kernel starts after everything before it in the stream has
+// completed, and a later kernel (even one launched with launch_k, whose prologue runs before its dependency wait)
+// cannot start before this one has completed.  For kernels that write data which the next kernel reads in its
+// prologue (a widened weight image that the GEMM prefetches before its dependency wait).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_serial(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = nullptr;
+  cfg.numAttrs = 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // True while this thread is inside a graph scope in REPLAY mode: launchers return at once.
 bool replay_mode();
 #define RF_SKIP_IF_REPLAYING()             \

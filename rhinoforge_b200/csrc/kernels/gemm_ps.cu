@@ -487,13 +487,11 @@ __global__ void widen_packed_kernel(const uint8_t* __restrict__ src, uint8_t* __
 int widen_packed(const void* src, void* dst, int64_t blocks, int dtype, cudaStream_t stream) {
   const int64_t pieces = blocks * 1024;
   const int grid = (int)std::min<int64_t>((pieces + 255) / 256, (int64_t)sm_count() * 16);
-  if (dtype == 0)
-    widen_packed_kernel<__half><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(src),
-                                                          reinterpret_cast<uint8_t*>(dst), pieces);
-  else
-    widen_packed_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(src),
-                                                                 reinterpret_cast<uint8_t*>(dst), pieces);
-  RF_CUDA_CHECK(cudaGetLastError());
+  // no programmatic dependent launch here: the GEMM that follows prefetches this image before its dependency wait
+  const uint8_t* sp = reinterpret_cast<const uint8_t*>(src);
+  uint8_t* dp = reinterpret_cast<uint8_t*>(dst);
+  if (dtype == 0) RF_CUDA_CHECK(::rf::launch_serial(widen_packed_kernel<__half>, dim3(grid), dim3(256), 0, stream, sp, dp, pieces));
+  else RF_CUDA_CHECK(::rf::launch_serial(widen_packed_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, sp, dp, pieces));
   ::rf::count_launch();
   return RF_OK;
 }

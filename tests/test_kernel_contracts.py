@@ -55,7 +55,10 @@ def test_waiting_kernels_report_and_release():
     g = _text(CSRC / "kernels" / "gemm_tc.cu")
     assert g.count("report_status") >= 5
     assert g.rindex("tmem_dealloc") > g.rindex("report_status")
-    assert "return;" not in g[g.index("gemm_tc_kernel("):g.index("// ------------------------------------------------------------ host side")]
+    # the only early exit allowed is the shared-memory alignment check, which runs before anything is acquired
+    kernel = g[g.index("gemm_tc_kernel("):g.index("// ------------------------------------------------------------ host side")]
+    assert "return;" not in kernel[kernel.index("tmem_alloc("):], "an early return after the TMEM allocation leaks it"
+    assert kernel[:kernel.index("tmem_alloc(")].count("return;") <= 1
 
 
 def test_qwen3_5_geometry_guard_fires_from_the_config_alone():
