@@ -1,4 +1,4 @@
-"""Vision towers on the native transformer stack: Qwen3-VL ViT, SigLIP and DINOv3.
+"""Vision towers on the native transformer stack: Qwen3-VL ViT, SigLIP, HYViT2 and DINOv3.
 
 All three are a pre-norm LayerNorm ViT with a plain (non-gated) GELU MLP; they differ in patch
 embedding, position information (interpolated learned table + 2-D RoPE / learned table / 2-D
@@ -279,7 +279,8 @@ class SiglipVisionEncoder:
     to 128 so that the attention kernels apply; the softmax scale stays 1/sqrt(72)."""
 
     def __init__(self, cfg: SiglipConfig, sd: Dict[str, torch.Tensor], *, prefix: str = "vision_model.", device="cuda",
-                 dtype=torch.float16, max_images: int = 8, projector: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+                 dtype=torch.float16, max_images: int = 8, projector: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                 post_norm: bool = True):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         H, heads = cfg.hidden_size, cfg.num_attention_heads
         hd = H // heads
@@ -306,8 +307,10 @@ class SiglipVisionEncoder:
         geo = TowerGeometry(H, cfg.num_hidden_layers, heads, hd, cfg.intermediate_size, cfg.layer_norm_eps, act)
         self.tower = VisionTower(geo, layers, max_tokens=max_images * self.tokens_per_image, max_seqs=max_images,
                                  device=device, dtype=dtype)
-        self.post_w = g("post_layernorm.weight").to(self.device, dtype).contiguous()
-        self.post_b = g("post_layernorm.bias").to(self.device, dtype).contiguous()
+        self.post_norm = post_norm       # HYViT2 feeds the last block's output straight to its projector
+        if post_norm:
+            self.post_w = g("post_layernorm.weight").to(self.device, dtype).contiguous()
+            self.post_b = g("post_layernorm.bias").to(self.device, dtype).contiguous()
         self.projector = None
         if projector is not None:
             self.projector = tuple(t.to(self.device, dtype).contiguous() for t in projector)
@@ -320,7 +323,7 @@ class SiglipVisionEncoder:
             raise RPUBackendError(f"SigLIP expects {self.cfg.image_size}x{self.cfg.image_size} images")
         hidden = K.gemm(x, self.patch_w, bias=self.patch_b, residual=self.pos.repeat(B, 1) if B > 1 else self.pos)
         self.tower.run(hidden, [n] * B)
-        out = K.layernorm(hidden, self.post_w, self.post_b, self.cfg.layer_norm_eps)
+        out = K.layernorm(hidden, self.post_w, self.post_b, self.cfg.layer_norm_eps) if self.post_norm else hidden
         if self.projector is not None:
             out = K.gemm(out, self.projector[0], bias=self.projector[1])
         return out.view(B, n, -1)
@@ -329,6 +332,42 @@ class SiglipVisionEncoder:
 
     def close(self):
         self.tower.close()
+
+
+# ----------------------------------------------------------------------------- HYViT2
+def hyvit2_to_siglip_names(sd: Dict[str, torch.Tensor], layers: int, prefix: str = "") -> Dict[str, torch.Tensor]:
+    """timm-style ViT names (``patch_embed.proj``, ``pos_embed``, ``blocks.{i}.norm1 / attn.qkv / attn.proj / norm2 /
+    mlp.fc1 / mlp.fc2``) -> the SigLIP names :class:`SiglipVisionEncoder` reads.  The fused ``qkv`` ``[3H, H]`` is split
+    into q / k / v; a leading class / register token row of ``pos_embed`` is not expected (HYViT2 has none)."""
+    g = lambda n: sd[prefix + n]
+    out = {"embeddings.patch_embedding.weight": g("patch_embed.proj.weight"),
+           "embeddings.patch_embedding.bias": g("patch_embed.proj.bias")}
+    pos = g("pos_embed")
+    out["embeddings.position_embedding.weight"] = pos.reshape(-1, pos.shape[-1])
+    for i in range(layers):
+        b, o = f"blocks.{i}.", f"encoder.layers.{i}."
+        qkv_w, qkv_b = g(b + "attn.qkv.weight"), g(b + "attn.qkv.bias")
+        H = qkv_w.shape[1]
+        for j, n in enumerate(("q_proj", "k_proj", "v_proj")):
+            out[o + f"self_attn.{n}.weight"] = qkv_w[j * H:(j + 1) * H]
+            out[o + f"self_attn.{n}.bias"] = qkv_b[j * H:(j + 1) * H]
+        out[o + "self_attn.out_proj.weight"], out[o + "self_attn.out_proj.bias"] = g(b + "attn.proj.weight"), g(b + "attn.proj.bias")
+        for src, dst in (("norm1", "layer_norm1"), ("norm2", "layer_norm2"), ("mlp.fc1", "mlp.fc1"), ("mlp.fc2", "mlp.fc2")):
+            out[o + dst + ".weight"], out[o + dst + ".bias"] = g(b + src + ".weight"), g(b + src + ".bias")
+    return out
+
+
+class HYViT2Encoder(SiglipVisionEncoder):
+    """HunYuan HYViT2-400M tower: the SigLIP-So400m geometry and block (hidden 1152, 27 layers, 16 heads of 72, MLP 4304,
+    LayerScale and drop-path are identities) **without** the post-LayerNorm: the last block's output goes straight to
+    the per-token projector, the first linear of the merger (``proj1``); the merger's pooling and second projection stay
+    with the caller.  Checkpoints use timm-style names.  Reference: ``src/fused/rpu_hyvit2_vision_model.cpp:1-30``."""
+
+    def __init__(self, cfg: SiglipConfig, sd: Dict[str, torch.Tensor], *, prefix: str = "", device="cuda",
+                 dtype=torch.float16, max_images: int = 1, projector: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+        mapped = hyvit2_to_siglip_names(sd, cfg.num_hidden_layers, prefix)
+        super().__init__(cfg, mapped, prefix="", device=device, dtype=dtype, max_images=max_images, projector=projector,
+                         post_norm=False)
 
 
 # ----------------------------------------------------------------------------- DINOv3

@@ -10,7 +10,8 @@ pool (the ``k_caches`` / ``v_caches`` lists of ``causal_decoder_forward`` are ac
 and not read), and the decoder returns last-row logits of each sequence (the reference's fused-lm-head mode).
 
 Families: ``causal_decoder`` and ``qwen3_5`` (``runtime.engine.DecoderEngine``), ``qwen3vl_vision`` /
-``qwen3_5_vision`` (``models.vision.Qwen3VLVisionEncoder``), ``qwen25vl_vision``, ``siglip``, ``dinov3_vision``,
+``qwen3_5_vision`` (``models.vision.Qwen3VLVisionEncoder``), ``qwen25vl_vision``, ``siglip``, ``hyvit2`` (optional
+projector passed as ``rpu_projector.weight`` / ``rpu_projector.bias``), ``dinov3_vision``,
 and the Pi0.5 set ``pi05`` / ``gemma`` / ``adarms`` / ``pi05_denoise_step`` (+ ``pi05_denoise_loop_forward``), which
 share one ``models.pi05.Pi05Engine`` per handle: ``gemma_forward`` is the prefix pass, ``adarms_forward`` /
 ``pi05_denoise_step_forward`` / ``pi05_denoise_loop_forward`` integrate the action expert over the stored prefix.
@@ -165,6 +166,13 @@ def _vision_set_weights(family: str, handle: int, names: List[str], tensors: Lis
         from ..models.vision import SiglipConfig, SiglipVisionEncoder
         e.runtime = SiglipVisionEncoder(SiglipConfig.from_hf(cfg), sd, prefix=str(cfg.get("rpu_prefix", "vision_model.")),
                                         dtype=dt, max_images=int(cfg.get("rpu_max_images", 8)))
+    elif family == "hyvit2":
+        from ..models.vision import HYViT2Encoder, SiglipConfig
+        proj = None
+        if "rpu_projector.weight" in sd:
+            proj = (sd.pop("rpu_projector.weight"), sd.pop("rpu_projector.bias"))
+        e.runtime = HYViT2Encoder(SiglipConfig.from_hf(cfg), sd, prefix=str(cfg.get("rpu_prefix", "")), dtype=dt,
+                                  max_images=int(cfg.get("rpu_max_images", 1)), projector=proj)
     elif family == "dinov3_vision":
         from ..models.vision import DINOv3Config, DINOv3Encoder
         e.runtime = DINOv3Encoder(DINOv3Config.from_hf(cfg), sd, dtype=dt)
@@ -258,7 +266,7 @@ def register(lib: "torch.library.Library") -> None:
         family(name, (name,), lambda handle, names, tensors, _n=name: _vision_set_weights(_n, handle, names, tensors),
                "(int handle, Tensor pixel_values, Tensor grid_thw) -> Tensor[]",
                lambda handle, pixel_values, grid_thw, _n=name: _grid_vision_forward(_n, handle, pixel_values, grid_thw))
-    for name in ("siglip", "dinov3_vision"):
+    for name in ("siglip", "hyvit2", "dinov3_vision"):
         family(name, (name,), lambda handle, names, tensors, _n=name: _vision_set_weights(_n, handle, names, tensors),
                "(int handle, Tensor pixel_values) -> Tensor[]",
                lambda handle, pixel_values, _n=name: _image_vision_forward(_n, handle, pixel_values))
@@ -273,6 +281,6 @@ def register(lib: "torch.library.Library") -> None:
     op("pi05_denoise_loop_forward(int handle, Tensor? prefix_lens, Tensor noise, int num_steps=10) -> Tensor", _denoise_forward)
 
 
-FAMILIES = _DECODERS + ("qwen3vl_vision", "qwen3_5_vision", "qwen25vl_vision", "siglip", "dinov3_vision") + _PI05
+FAMILIES = _DECODERS + ("qwen3vl_vision", "qwen3_5_vision", "qwen25vl_vision", "siglip", "hyvit2", "dinov3_vision") + _PI05
 
 __all__ = ["register", "live_handles", "FAMILIES"]

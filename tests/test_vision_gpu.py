@@ -126,3 +126,37 @@ def test_qwen25vl_vision_matches_hf(dtype):
     assert got.shape == want.shape
     assert _rel(got, want) < (2e-2 if dtype == torch.float16 else 6e-2)
     enc.close()
+
+
+def test_hyvit2_is_siglip_without_post_norm_from_timm_names():
+    """HYViT2: timm-style checkpoint names, fused qkv, no post-LayerNorm, per-token projector on the last block's
+    output.  Oracle: the Hugging Face SigLIP encoder's last hidden state *before* its post-LayerNorm."""
+    from transformers import SiglipVisionConfig, SiglipVisionModel
+    from rhinoforge_b200.models.vision import HYViT2Encoder, SiglipConfig
+
+    hc = SiglipVisionConfig(hidden_size=144, intermediate_size=272, num_hidden_layers=3, num_attention_heads=2,
+                            image_size=56, patch_size=14)
+    hc._attn_implementation = "eager"
+    ref = SiglipVisionModel(hc).float().eval()
+    _randomize(ref)
+    px = torch.randn(1, 3, 56, 56, generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        want = ref(pixel_values=px, output_hidden_states=True).hidden_states[-1]
+    s = ref.state_dict()
+    sd = {"patch_embed.proj.weight": s["vision_model.embeddings.patch_embedding.weight"],
+          "patch_embed.proj.bias": s["vision_model.embeddings.patch_embedding.bias"],
+          "pos_embed": s["vision_model.embeddings.position_embedding.weight"][None]}
+    for i in range(3):
+        a, b = f"vision_model.encoder.layers.{i}.", f"blocks.{i}."
+        sd[b + "attn.qkv.weight"] = torch.cat([s[a + f"self_attn.{n}.weight"] for n in ("q_proj", "k_proj", "v_proj")])
+        sd[b + "attn.qkv.bias"] = torch.cat([s[a + f"self_attn.{n}.bias"] for n in ("q_proj", "k_proj", "v_proj")])
+        sd[b + "attn.proj.weight"], sd[b + "attn.proj.bias"] = s[a + "self_attn.out_proj.weight"], s[a + "self_attn.out_proj.bias"]
+        for src, dst in (("layer_norm1", "norm1"), ("layer_norm2", "norm2"), ("mlp.fc1", "mlp.fc1"), ("mlp.fc2", "mlp.fc2")):
+            sd[b + dst + ".weight"], sd[b + dst + ".bias"] = s[a + src + ".weight"], s[a + src + ".bias"]
+    proj_w = torch.randn(64, 144, generator=torch.Generator().manual_seed(6)) * 0.05
+    proj_b = torch.randn(64, generator=torch.Generator().manual_seed(7)) * 0.1
+    enc = HYViT2Encoder(SiglipConfig.from_hf(hc), sd, projector=(proj_w, proj_b))
+    got = enc(px)
+    enc.tower.stack.check_status()
+    assert _rel(got, want @ proj_w.T + proj_b) < 2e-2
+    enc.close()
