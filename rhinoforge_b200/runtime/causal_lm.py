@@ -82,9 +82,14 @@ class RPUCausalLM:
             parts = [torch.empty_like(logits) for _ in range(self.engine.tp.world)]
             dist.all_gather(parts, logits, group=self.engine.tp.group)
             logits = torch.cat(parts, -1)
-        self._rpu_last_execution_plan = {"stage": "prefill" if rows[0].numel() > 1 else "decode",
-                                         "logical_len": int(rows[0].numel()), "execution_len": int(rows[0].numel()),
-                                         "chunk_size": self.engine.max_tokens, "padding_rows": 0, "position": start}
+        # the resolved plan of this call (variable-length launches run every length as it is: no padding rows)
+        from .decoder import default_chunk_resolver, plan_bounded_prefill_execution
+        n_rows = int(rows[0].numel())
+        exec_len, chunk = plan_bounded_prefill_execution(n_rows, max(start + n_rows, 1), 0,
+                                                         default_chunk_resolver(self.engine.max_tokens), start)
+        self._rpu_last_execution_plan = {"stage": "prefill" if n_rows > 1 else "decode", "logical_len": n_rows,
+                                         "execution_len": exec_len, "chunk_size": chunk,
+                                         "padding_rows": exec_len - n_rows, "position": start}
         logits = logits[:, None, :]
         if not return_dict:
             return (logits, past_key_values)

@@ -282,3 +282,34 @@ def test_manual_capture_passes_through_without_a_device_and_refuses_drift():
     g.invalidate()
     with pytest.raises(RuntimeError, match="invalidated"):
         g.replay(a, b, k=2)
+
+
+def test_bounded_prefill_planner_orders_launches_then_padding_then_deficit():
+    import pytest
+    from rhinoforge_b200.runtime.decoder import (chunk_policy_key, default_chunk_resolver, plan_bounded_prefill_execution,
+                                                 prefill_position_key)
+    res = default_chunk_resolver(256)
+    assert plan_bounded_prefill_execution(100, 4096, 64, res) == (100, 112)            # one launch, no padding needed
+    assert plan_bounded_prefill_execution(300, 4096, 64, res) == (300, 256)            # two launches either way: keep raw rows
+    assert plan_bounded_prefill_execution(100, 4096, 64, res, alignment=64) == (128, 128)
+    assert plan_bounded_prefill_execution(100, 4096, 0, res, padding_rows=12) == (112, 112)
+    # a resolver with a coarse grid: padding is taken only because it saves a launch
+    grid = lambda n: 128 if n % 128 == 0 else 64
+    assert plan_bounded_prefill_execution(120, 4096, 16, grid) == (128, 128)
+    assert plan_bounded_prefill_execution(120, 4096, 4, grid) == (120, 64)
+    # exact chunk requests, the padding-only launch rule, limits and bad arguments
+    assert plan_bounded_prefill_execution(120, 4096, 16, grid, exact_chunk_size=128) == (128, 128)
+    with pytest.raises(ValueError, match="not the requested"):
+        plan_bounded_prefill_execution(100, 4096, 0, res, exact_chunk_size=256)
+    with pytest.raises(ValueError, match="padding only"):
+        plan_bounded_prefill_execution(60, 4096, 0, lambda n: 64, padding_rows=68)
+    with pytest.raises(ValueError, match="physical limit"):
+        plan_bounded_prefill_execution(100, 150, 0, res, position=100)
+    with pytest.raises(ValueError, match="multiple of 16"):
+        plan_bounded_prefill_execution(100, 4096, 0, res, exact_chunk_size=100)
+    with pytest.raises(ValueError, match="alignment"):
+        plan_bounded_prefill_execution(100, 4096, 0, res, alignment=64, padding_rows=1)
+    score = lambda n, c, launches, pad, deficit: (pad, launches)                        # caller prefers no padding at all
+    assert plan_bounded_prefill_execution(120, 4096, 16, grid, candidate_score=score) == (120, 64)
+    assert chunk_policy_key("auto") == 0 and chunk_policy_key(None) == 0 and chunk_policy_key(512) == 512
+    assert prefill_position_key(1, 900) == 0 and prefill_position_key(32, 0) == 0 and prefill_position_key(32, 64) == 64
