@@ -890,7 +890,10 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
     //    only up to tiles * splits <= SMs (grids beyond that run two CTAs per SM with a two-stage ring each, which
     //    measured faster than one CTA with four stages once there are several waves);
     //  * a small second wave costs less than halving the split (measured), so residency is not required.
-    const int max_by_k = std::max(1, pl->k_blocks / 4);
+    // at least one k block per split: short-K shapes (tensor-parallel out-projections, K = 512) measured 16.3 us
+    // unsplit-ish (S <= k_blocks / 4) against 8.8 us at one block per CTA - the fixed cost of a CTA is paid in
+    // parallel, its streaming time is not
+    const int max_by_k = std::max(1, pl->k_blocks);
     const int cap = (!swap && pl->bn > 128) ? sm_count() : 2 * sm_count();
     splits = 1;
     if (!two_shot) {
