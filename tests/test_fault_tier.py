@@ -89,3 +89,56 @@ def test_native_errors_become_python_exceptions_with_the_message():
     rc = lib.rf_gemm(C.byref(g), None)
     with pytest.raises(RPUBackendError, match="GEMM needs x, w and out"):
         N.check(rc, "rf_gemm")
+
+
+def test_allreduce_protocol_model_sums_in_rank_order_and_survives_a_rank_one_call_ahead():
+    """Host model of the in-kernel protocol: both variants give every rank the same bits, over several back-to-back
+    calls (slot alternation), with one rank deliberately slow."""
+    import time
+    import numpy as np
+    from rhinoforge_b200.parallel.protocol_sim import SimWorld, run_ranks
+    rng = np.random.default_rng(0)
+    for two_shot in (False, True):
+        W = 4
+        world = SimWorld(W, rows=6, cols=16, tile_cols=4, wait_s=2.0)
+        for call in range(3):
+            parts = [rng.standard_normal((6, 16)).astype(np.float32) for _ in range(W)]
+            resid = rng.standard_normal((6, 16)).astype(np.float32)
+
+            def one(rank):
+                if rank == 2:
+                    time.sleep(0.05)                      # a slow rank: the others wait on its flags
+                return world.all_reduce(rank, parts[rank], resid, two_shot=two_shot)
+            outs = run_ranks(world, one)
+            if two_shot:
+                want = sum(p.astype(np.float16).astype(np.float32) for p in parts) + resid
+                tol = 2e-2
+            else:
+                want = ((parts[0] + parts[1]) + parts[2]) + parts[3] + resid
+                tol = 1e-6
+            for o in outs:
+                assert o is not None and np.allclose(o, want, atol=tol)
+                assert np.array_equal(o, outs[0]), "every rank must hold the same bits"
+        assert all(m.status == 0 and m.call == 3 for m in world.mem)
+
+
+def test_allreduce_protocol_model_times_out_instead_of_hanging_when_a_flag_is_withheld():
+    """A flag write that never arrives (dropped on the host) ends the waiters' call with the peer-timeout status
+    within the wait bound; the other tiles still complete and the next call works again."""
+    import time
+    import numpy as np
+    from rhinoforge_b200.parallel.protocol_sim import STATUS_PEER_TIMEOUT, SimWorld, run_ranks
+    W = 2
+    world = SimWorld(W, rows=2, cols=8, tile_cols=4, wait_s=0.2)
+    world.allow_flag = lambda kind, src, dst, tile: not (kind == 0 and src == 1 and dst == 0 and tile == 1)
+    parts = [np.full((2, 8), float(r + 1), np.float32) for r in range(W)]
+    t0 = time.monotonic()
+    outs = run_ranks(world, lambda r: world.all_reduce(r, parts[r], None, two_shot=False))
+    assert time.monotonic() - t0 < 2.0
+    assert outs[0] is None and world.mem[0].status == STATUS_PEER_TIMEOUT and world.mem[0].status_detail == 1
+    assert outs[1] is not None and np.allclose(outs[1], 3.0)          # rank 1 got every flag
+    world.allow_flag = lambda *a: True
+    for m in world.mem:
+        m.status = 0
+    outs = run_ranks(world, lambda r: world.all_reduce(r, parts[r], None, two_shot=True))
+    assert all(o is not None and np.allclose(o, 3.0) for o in outs)
