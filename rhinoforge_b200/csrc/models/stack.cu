@@ -253,8 +253,17 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
       }
     }
     }
+    // Gated residual with ONE modulation row for all tokens (a single sample's action rows): the gate is a
+    // per-column vector, so hidden += gate * sublayer(x) is the GEMM's own epilogue (column scale, then the in-place
+    // residual) and the separate gated-residual launch disappears.
+    const bool fuse_gate = c.gated_residual && !c.sandwich_norm && f.rows_per_mod >= T && !c.weights_int8 &&
+                           c.tp_world == 1 && f.mod != nullptr;
     if (!side) {
       rc = linear(s, mix_out, mix_dim, w.wo, w.so, w.bo, f.hidden, H, f.hidden, H, T, H, mix_dim, kActNone, 0, true, st);
+      if (rc) return rc;
+    } else if (fuse_gate && !w.bo) {
+      rc = linear(s, mix_out, mix_dim, w.wo, mod1 + (size_t)2 * H * esz, nullptr, f.hidden, H, f.hidden, H, T, H, mix_dim,
+                  kActNone, 0, true, st);
       if (rc) return rc;
     } else {
       rc = linear(s, mix_out, mix_dim, w.wo, w.so, w.bo, tmp, H, nullptr, 0, T, H, mix_dim, kActNone, 0, true, st);
@@ -298,6 +307,10 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     }
     if (!side) {
       rc = linear(s, wide, I, w.w_down, w.s_down, w.b_down, f.hidden, H, f.hidden, H, T, H, I, kActNone, 0, true, st);
+      if (rc) return rc;
+    } else if (fuse_gate && !w.b_down) {
+      rc = linear(s, wide, I, w.w_down, mod2 + (size_t)2 * H * esz, nullptr, f.hidden, H, f.hidden, H, T, H, I, kActNone,
+                  0, true, st);
       if (rc) return rc;
     } else {
       rc = linear(s, wide, I, w.w_down, w.s_down, w.b_down, tmp, H, nullptr, 0, T, H, I, kActNone, 0, true, st);
