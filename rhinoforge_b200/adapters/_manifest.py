@@ -7,7 +7,7 @@ BUILTIN_ADAPTERS = (
     ("Qwen3ForCausalLM", "rhinoforge_b200.adapters.qwen3", "Qwen3Adapter"),
     ("LlamaForCausalLM", "rhinoforge_b200.adapters.llama", "LlamaAdapter"),
     ("DINOv3ViTModel", "rhinoforge_b200.adapters.dinov3", "DINOv3Adapter"),
-    ("Gemma4ForConditionalGeneration", "rhinoforge_b200.adapters.gemma4", "Gemma4Adapter"),
+    ("SiglipVisionModel", "rhinoforge_b200.adapters.siglip", "SiglipAdapter"),
     ("Qwen3_5ForConditionalGeneration", "rhinoforge_b200.adapters.qwen3_5", "Qwen3_5Adapter"),
     ("Qwen3VLForConditionalGeneration", "rhinoforge_b200.adapters.qwen3_vl", "Qwen3VLAdapter"),
 )

@@ -13,7 +13,8 @@ from .errors import UnsupportedModelError
 
 _ROUTES = {
     "DINOv3ViTModel": "use DINOv3Adapter with the direct vision-model path",
-    "Gemma4ForConditionalGeneration": "use Gemma4Adapter(model).to_rpu()",
+    "Gemma4ForConditionalGeneration": "Gemma4 is not built in this framework",
+    "SiglipVisionModel": "use SiglipAdapter(model).to_rpu()",
     "Qwen3_5ForConditionalGeneration": "use Qwen3_5Adapter(model).to_rpu() with Qwen3_5Cache",
     "Qwen3VLForConditionalGeneration": "use RPUModelForConditionalGeneration.from_pretrained(...)",
     "LlamaForCausalLM": "use RPUModelForCausalLM.from_pretrained(...) and .to('rpu')",

@@ -313,3 +313,13 @@ def test_bounded_prefill_planner_orders_launches_then_padding_then_deficit():
     assert plan_bounded_prefill_execution(120, 4096, 16, grid, candidate_score=score) == (120, 64)
     assert chunk_policy_key("auto") == 0 and chunk_policy_key(None) == 0 and chunk_policy_key(512) == 512
     assert prefill_position_key(1, 900) == 0 and prefill_position_key(32, 0) == 0 and prefill_position_key(32, 64) == 64
+
+
+def test_every_builtin_adapter_in_the_manifest_imports():
+    """The manifest is data only; every row must resolve to a class (a row for a family that is not built would make
+    ``get_adapter`` fail with an import error instead of a model error)."""
+    from rhinoforge_b200.adapters._manifest import BUILTIN_ADAPTERS
+    from rhinoforge_b200.runtime.registry import get_adapter
+    for arch, module, cls in BUILTIN_ADAPTERS:
+        got = get_adapter(arch)
+        assert got.__name__ == cls and got.__module__.startswith(module)
