@@ -323,3 +323,20 @@ def test_every_builtin_adapter_in_the_manifest_imports():
     for arch, module, cls in BUILTIN_ADAPTERS:
         got = get_adapter(arch)
         assert got.__name__ == cls and got.__module__.startswith(module)
+
+
+def test_vision_tower_adapters_preflight_from_the_config_alone():
+    import pytest
+    from rhinoforge_b200.adapters.hyvit2 import HYViT2Adapter
+    from rhinoforge_b200.adapters.qwen25_vl_vision import Qwen25VLVisionAdapter
+    from rhinoforge_b200.runtime.errors import UnsupportedModelError
+    ok = dict(depth=32, hidden_size=1280, num_heads=16, intermediate_size=3420, patch_size=14, spatial_merge_size=2,
+              window_size=112, fullatt_block_indexes=[7, 15, 23, 31], hidden_act="silu")
+    Qwen25VLVisionAdapter.preflight(ok)
+    for bad in (dict(ok, hidden_act="gelu"), dict(ok, window_size=100), dict(ok, fullatt_block_indexes=[40]),
+                dict(ok, hidden_size=8192, num_heads=16)):
+        with pytest.raises(UnsupportedModelError):
+            Qwen25VLVisionAdapter.preflight(bad)
+    HYViT2Adapter.preflight(dict(hidden_size=1152, num_attention_heads=16, image_size=224, patch_size=14))
+    with pytest.raises(UnsupportedModelError):
+        HYViT2Adapter.preflight(dict(hidden_size=1152, num_attention_heads=16, image_size=230, patch_size=14))
