@@ -557,3 +557,25 @@ def test_gemm_w8a16_large_m_widens_once_and_matches(dt, dual, status):
     ref = torch.nn.functional.silu(z[:, :N]) * z[:, N:] if dual else z
     _close(y, ref, dt, scale=max(1.0, ref.abs().max().item()))
     _close(y0, ref, dt, scale=max(1.0, ref.abs().max().item()))
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 512), (64, 4096, 1024), (50, 1024, 192), (8, 2048, 64)])
+def test_gemm_short_k_splits_down_to_one_block_per_cta(dt, M, N, K, status):
+    """Short-K weight-streaming shapes (tensor-parallel out-projections): the planner may give every CTA of the
+    cluster a single k block (or fewer splits than blocks when K is tiny); bias, residual and the rotated K start are
+    all in play."""
+    from rhinoforge_b200.ops import kernels as K_
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(dt)
+    b = torch.randn(N, device="cuda").to(dt)
+    r = torch.randn(M, N, device="cuda").to(dt)
+    ref = x.float() @ w.float().t() + b.float() + r.float()
+    y = K_.gemm(x, K_.pack_weight(w), packed_shape=(N, K), bias=b, residual=r, status=status)
+    _close(y, ref, dt, scale=max(1.0, ref.abs().max().item()))
+    y2 = K_.gemm(x, w, bias=b, residual=r, status=status)                  # row-major weights, same planner
+    _close(y2, ref, dt, scale=max(1.0, ref.abs().max().item()))
+    for s in (1, 8):
+        if s * 64 <= max(K, 64) or s == 1:
+            y3 = K_.gemm(x, K_.pack_weight(w), packed_shape=(N, K), bias=b, residual=r, status=status, force_splits=s)
+            _close(y3, ref, dt, scale=max(1.0, ref.abs().max().item()))
