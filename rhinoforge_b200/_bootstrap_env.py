@@ -1,32 +1,32 @@
-"""Process-environment set-up that must happen before PyTorch is imported.
-
-Only the standard library is imported at module load (reference behaviour:
-``python/rpu_backend/_bootstrap_env.py:1-33``).
-"""
+"""What has to be arranged in the process before PyTorch is imported (standard library only at import time;
+the reference does the same in ``python/rpu_backend/_bootstrap_env.py:1-33``)."""
 from __future__ import annotations
 
 import resource
 
-_TARGET_NOFILE = 1_048_576
+WANTED_OPEN_FILES = 1 << 20
 
 
-def ensure_nofile_limit() -> None:
-    """Raise the soft open-file limit towards the hard limit; silent, best effort.
+def ensure_nofile_limit(wanted: int = WANTED_OPEN_FILES) -> int:
+    """Lift the soft ``RLIMIT_NOFILE`` as far as the hard limit allows and return the soft limit now in force.
 
-    Sharded checkpoints are memory-mapped one file per shard and CUDA IPC keeps one
-    descriptor per peer mapping, so large tensor-parallel loads can exceed 1024."""
+    A sharded checkpoint is one memory-mapped file per shard and every CUDA-IPC peer mapping holds a descriptor, so an
+    8-way tensor-parallel load of a large model runs past the usual 1024.  Failing to raise the limit is not an error."""
     soft, hard = resource.getrlimit(resource.RLIMIT_NOFILE)
-    if soft >= _TARGET_NOFILE:
-        return
-    try:
-        resource.setrlimit(resource.RLIMIT_NOFILE, (min(_TARGET_NOFILE, hard), hard))
-    except (ValueError, OSError):
-        return
+    goal = wanted if hard == resource.RLIM_INFINITY else min(wanted, hard)
+    if soft < goal:
+        try:
+            resource.setrlimit(resource.RLIMIT_NOFILE, (goal, hard))
+            soft = goal
+        except (ValueError, OSError):
+            pass
+    return soft
 
 
 def configure_hf_cache() -> None:
-    from . import model_registry
-    model_registry.set_hf_home_env()
+    """Point the Hugging Face cache variables at the model cache unless the user already set them."""
+    from .model_registry import set_hf_home_env
+    set_hf_home_env()
 
 
-__all__ = ["configure_hf_cache", "ensure_nofile_limit"]
+__all__ = ["ensure_nofile_limit", "configure_hf_cache", "WANTED_OPEN_FILES"]

@@ -1,34 +1,19 @@
-"""Public error hierarchy (reference: ``python/rpu_backend/api/errors.py:1-40``).
+"""Public error hierarchy: everything derives from ``RPUBackendError`` (names as in the reference,
+``python/rpu_backend/api/errors.py:1-40``, so that ``except`` clauses written against it keep working).
 
-``RPUBackendError`` is the base; ``SPMExhaustionError`` keeps its name for API
-compatibility and is raised here when a plan exceeds the static device arena or
-the paged KV pool.
+``SPMExhaustionError`` keeps its historical name; here it means that an execution plan exceeds the static
+activation arena or the paged KV pool.
 """
 from ..runtime.errors import RPUBackendError, RPUConfigError, UnsupportedModelError
 
+_DERIVED = {
+    "RPUUnsupportedDtypeError": "The requested dtype is not supported on the selected path.",
+    "RPUSingleHandleError": "A second live model or policy handle was requested in one process.",
+    "SPMExhaustionError": "The execution plan does not fit the activation arena / KV pool.",
+    "WeightShapeMismatchError": "A weight tensor violates the layout constraints of its adapter.",
+}
+for _name, _doc in _DERIVED.items():
+    globals()[_name] = type(_name, (RPUBackendError,), {"__doc__": _doc, "__module__": __name__})
+del _name, _doc
 
-class RPUUnsupportedDtypeError(RPUBackendError):
-    """The requested dtype is not supported on the selected path."""
-
-
-class RPUSingleHandleError(RPUBackendError):
-    """A second live model or policy handle was requested in one process."""
-
-
-class SPMExhaustionError(RPUBackendError):
-    """The execution plan does not fit the activation arena / KV pool."""
-
-
-class WeightShapeMismatchError(RPUBackendError):
-    """A weight tensor violates the layout constraints of its adapter."""
-
-
-__all__ = [
-    "RPUBackendError",
-    "RPUConfigError",
-    "UnsupportedModelError",
-    "RPUUnsupportedDtypeError",
-    "RPUSingleHandleError",
-    "SPMExhaustionError",
-    "WeightShapeMismatchError",
-]
+__all__ = ["RPUBackendError", "RPUConfigError", "UnsupportedModelError", *_DERIVED]
