@@ -421,7 +421,8 @@ def run_qwen3vl(args) -> dict:
 def main(argv=None) -> int:
     args = parse_args(argv)
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        if int(os.environ.get("RANK", "0")) == 0:          # one line per job, also under torch.distributed.run
+            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
     out = {"decode": run, "pi05": run_pi05, "qwen3vl": run_qwen3vl}[args.workload](args)
     if out is not None:
