@@ -213,7 +213,8 @@ def register() -> bool:
         from ..graph import reset_graph_cache
         reset_graph_cache()
     lib.impl("reset_graph_cache", _reset, "CompositeExplicitAutograd")
-    from . import handle_ops
+    from . import fake_ops, handle_ops
+    fake_ops.register(lib)
     handle_ops.register(lib)
     _LIB = lib
     return True

@@ -231,3 +231,28 @@ def test_handle_family_ops_exist_and_keep_their_books_on_cpu():
     assert abs(float(out[0, 1]) - 1.0) < 1e-3
     ops.spm_alloc_init(); ops.spm_alloc_reset_temporary(); ops.spm_alloc_reset_all()
     assert json.loads(ops.spm_alloc_dump())["initialised"] is True
+
+
+def test_standalone_ops_propagate_shapes_on_meta_and_fake_tensors():
+    """Shape-only implementations: the operators trace on ``device='meta'`` and under ``FakeTensorMode`` with fake CUDA
+    tensors (no GPU, no data pointers)."""
+    import torch
+    import rhinoforge_b200  # noqa: F401
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    ops = torch.ops.rpu
+    m = lambda *s, dtype=torch.float16: torch.empty(*s, device="meta", dtype=dtype)
+    assert ops.rms_norm(m(3, 8), m(8), 1e-6).shape == (3, 8)
+    assert ops.gather_embedding(m(100, 16), m(2, 5, dtype=torch.int64)).shape == (2, 5, 16)
+    assert ops.assemble_inputs_embeds_rev(m(9, 4), m(3, dtype=torch.int64)).shape == (3, 4)
+    assert ops.cast_uint8_fp16(m(2, 3, dtype=torch.uint8), 1.0, 0.0).dtype == torch.float16
+    assert ops.conv2d_mc_nhwc(m(1, 28, 28, 3), m(16, 3, 14, 14), None, 14, 0).shape == (1, 2, 2, 16)
+    assert ops.lm_head_logits_top1(m(4, 8), m(32, 8)).shape == (4,)
+    ids, w = ops.moe_select(m(4, 8), None, 2, 1.0)
+    assert ids.dtype == torch.int32 and w.dtype == torch.float32 and ids.shape == w.shape == (4, 2)
+    with FakeTensorMode():
+        a = torch.empty(7, 16, device="cuda", dtype=torch.float16)
+        y = ops.rms_norm(a, torch.empty(16, device="cuda", dtype=torch.float16), 1e-6)
+        q = torch.empty(2, 5, 4, 16, device="cuda", dtype=torch.float16)
+        kv = torch.empty(2, 5, 2, 16, device="cuda", dtype=torch.float16)
+        o = ops.scaled_dot_product_attention_unified(q, kv, kv, True, 0.0)
+    assert y.shape == (7, 16) and y.device.type == "cuda" and o.shape == q.shape
