@@ -256,3 +256,20 @@ def test_standalone_ops_propagate_shapes_on_meta_and_fake_tensors():
         kv = torch.empty(2, 5, 2, 16, device="cuda", dtype=torch.float16)
         o = ops.scaled_dot_product_attention_unified(q, kv, kv, True, 0.0)
     assert y.shape == (7, 16) and y.device.type == "cuda" and o.shape == q.shape
+
+
+def test_handle_ops_build_model_configs_from_json():
+    """The JSON a ``*_create`` op receives becomes the runtime's config object: nested Pi0.5 geometry, dtype names."""
+    import torch
+    from rhinoforge_b200.ops import handle_ops as H
+    c = H._pi05_config({"action_dim": 7, "horizon": 16, "num_views": 2,
+                        "vlm": {"hidden": 128, "inter": 256, "layers": 2, "heads": 2, "kv_heads": 1, "head_dim": 64},
+                        "expert": {"hidden": 64, "inter": 128, "layers": 2, "heads": 2, "kv_heads": 1, "head_dim": 64},
+                        "vision": {"hidden_size": 128, "intermediate_size": 256, "num_hidden_layers": 2,
+                                   "num_attention_heads": 2, "image_size": 56, "patch_size": 14}})
+    assert (c.action_dim, c.horizon, c.num_views, c.vlm.hidden, c.expert.inter, c.vision.patch_size) == (7, 16, 2, 128, 128, 14)
+    assert c.tokens_per_image == 16
+    d = H._pi05_config({})
+    assert (d.vlm.hidden, d.expert.hidden, d.horizon) == (2048, 1024, 50)
+    assert H._dtype_of({"torch_dtype": "bfloat16"}) == torch.bfloat16 and H._dtype_of({}) == torch.float16
+    assert H._dtype_of({"dtype": "torch.float16"}) == torch.float16
