@@ -153,6 +153,10 @@ class DecoderEngine:
         self.status = self.arena[off:off + 32].view(torch.int32)
         self.comm: Optional[CommBuffers] = None
         if self.tp.enabled:
+            from .control import tp_comm_mode
+            if tp_comm_mode() == "nccl":
+                raise RPUBackendError("RPU_TP_COMM=nccl: the engine's step has no NCCL path (its all-reduce is the GEMM "
+                                      "epilogue); the NCCL implementation of the same models is baseline/eager_tp.py")
             # one-shot fp32 partials for <= 256 rows, two-shot 16-bit partials + result region above
             need = max(W * min(self.max_tokens, 256) * H * 4, (W + 1) * self.max_tokens * H * 2)
             self.comm = CommBuffers(self.tp, need)
