@@ -36,6 +36,10 @@ def main() -> int:
     inputs = tok(config["generation"]["prompt"], return_tensors="pt")
     n = config["generation"]["max_new_tokens"]
     cache = RPUCache.from_model(model, input_ids=inputs.input_ids, max_new_tokens=n)
+    from rpu_backend.runtime.control import warmup_iters
+    for _ in range(warmup_iters()):          # RPU_WARMUP untimed runs (graph capture, allocator warm-up) before the real one
+        model.generate(inputs.input_ids, past_key_values=cache, max_new_tokens=n, do_sample=False, use_cache=True)
+        cache.reset()
     out = model.generate(inputs.input_ids, past_key_values=cache, max_new_tokens=n, do_sample=False, use_cache=True)
     print(tok.decode(out[0, inputs.input_ids.shape[1]:].cpu(), skip_special_tokens=True))
     return 0

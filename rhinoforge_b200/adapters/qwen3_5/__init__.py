@@ -38,6 +38,12 @@ class Qwen3_5Adapter:
         cfg = DecoderConfig.from_hf(tc)
         if cfg.layer_types is None:
             raise UnsupportedModelError("Qwen3.5 config carries no layer_types")
+        from ...runtime.control import rpu_env_exact1
+        if getattr(config, "vision_config", None) is not None and getattr(config, "rpu_use_vision", False) \
+                and not rpu_env_exact1("QWEN3_5_VISION_ALLOW_NUMERIC_BLOCKED"):
+            # fail-closed evaluation gate: the Qwen3.5 vision path has no numeric sign-off here
+            raise UnsupportedModelError("the Qwen3.5 vision path is evaluation-gated: set "
+                                        "QWEN3_5_VISION_ALLOW_NUMERIC_BLOCKED=1 (exactly 1) to admit it")
         if cfg.gdn_dk != 128 or cfg.gdn_dv % 32 or cfg.gdn_conv != 4:
             raise UnsupportedModelError(f"Qwen3.5 linear-attention geometry (Dk={cfg.gdn_dk}, Dv={cfg.gdn_dv}, "
                                         f"conv={cfg.gdn_conv}) is not built (Dk 128, Dv multiple of 32, conv 4)")
@@ -98,7 +104,15 @@ class Qwen3_5Adapter:
         from ...runtime.engine import DecoderEngine
         cfg = DecoderConfig.from_hf(_text(self.config))
         ex = self._rpu_execution or {}
+        from ...runtime.control import rpu_env_int
         chunk = (ex.get("prefill") or {}).get("chunk_size", "auto")
+        if chunk in ("auto", None):
+            env_chunk = rpu_env_int("QWEN3_5_TEXT_CHUNK", 0)          # process-wide default when the config says auto
+            if env_chunk % 64:
+                raise RPUConfigError(f"QWEN3_5_TEXT_CHUNK must be a multiple of 64, got {env_chunk}")
+            chunk = env_chunk or "auto"
+        self.padding_budget = (ex.get("prefill") or {}).get("padding_budget",
+                                                            rpu_env_int("QWEN3_5_TEXT_PADDING_BUDGET", 64))
         max_prefill = min(max_seq_len, 8192) if chunk in ("auto", None) else int(chunk)
         live_handle.claim(self)
         try:

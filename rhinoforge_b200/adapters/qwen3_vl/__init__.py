@@ -23,6 +23,12 @@ class Qwen3VLAdapter:
     @classmethod
     def preflight(cls, config) -> None:
         Q.preflight(config, strict=os.environ.get("RPU_QWEN3_VL_ALLOW_ANY_PROFILE", "0") != "1")
+        from ...runtime.control import rpu_env_exact1
+        prof32 = Q.TEXT_PROFILES.get(Q.text_config_of(config).profile()) == "qwen3-vl-32b"
+        if prof32 and not rpu_env_exact1("QWEN3_VL_32B_ALLOW_GRAPH_BLOCKED"):
+            # fail-closed evaluation gate: the 32B profile has not been run end to end on this backend
+            raise UnsupportedModelError("the Qwen3-VL 32B profile is evaluation-gated: set QWEN3_VL_32B_ALLOW_GRAPH_BLOCKED=1 "
+                                        "(exactly 1) to admit it")
         from ..causal_base import config_is_w8a16
         if config_is_w8a16(config):
             prof = Q.text_config_of(config).profile()

@@ -208,7 +208,11 @@ class Pi05Policy:
         if self._frozen and (args[0].shape[0], steps) not in self._prepared:
             raise RPUBackendError(f"{ep}: graphs are frozen for {sorted(self._prepared)}; (batch, num_steps)="
                                   f"{(args[0].shape[0], steps)} was not prepared")
-        out = self.engine.predict(*args, num_steps=steps)
+        # RPU_PI05_FUSED_DENOISE=0 / RPU_PI05_DENOISE_UNROLL=0: launch the Euler steps one by one instead of replaying the
+        # whole loop from one captured graph (debugging and A/B timing)
+        from ..runtime.control import rpu_env_bool
+        one_graph = rpu_env_bool("RPU_PI05_FUSED_DENOISE", True) and rpu_env_bool("RPU_PI05_DENOISE_UNROLL", True)
+        out = self.engine.predict(*args, num_steps=steps, use_graph=one_graph)
         return out[:, :, :self.action_dim].float().clone()
 
     @torch.no_grad()

@@ -340,3 +340,32 @@ def test_vision_tower_adapters_preflight_from_the_config_alone():
     HYViT2Adapter.preflight(dict(hidden_size=1152, num_attention_heads=16, image_size=224, patch_size=14))
     with pytest.raises(UnsupportedModelError):
         HYViT2Adapter.preflight(dict(hidden_size=1152, num_attention_heads=16, image_size=230, patch_size=14))
+
+
+def test_evaluation_gates_and_model_switches_read_their_environment(monkeypatch):
+    """Fail-closed gates admit only the exact literal 1; per-model switches use the strict boolean parser."""
+    import pytest
+    from types import SimpleNamespace as NS
+    from rhinoforge_b200.adapters.qwen3_vl import Qwen3VLAdapter
+    from rhinoforge_b200.runtime.errors import UnsupportedModelError
+    text = dict(model_type="qwen3_vl_text", vocab_size=151936, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64,
+                num_attention_heads=64, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6,
+                rope_parameters={"rope_theta": 5e6, "mrope_section": [24, 20, 20]}, max_position_embeddings=262144)
+    vision = dict(hidden_size=1024, intermediate_size=4096, depth=24, num_heads=16, patch_size=16, temporal_patch_size=2,
+                  spatial_merge_size=2, out_hidden_size=5120, num_position_embeddings=2304,
+                  deepstack_visual_indexes=[5, 11, 17], hidden_act="gelu_pytorch_tanh")
+    cfg = NS(text_config=NS(**text), vision_config=NS(**vision), architectures=["Qwen3VLForConditionalGeneration"])
+    monkeypatch.delenv("QWEN3_VL_32B_ALLOW_GRAPH_BLOCKED", raising=False)
+    with pytest.raises(UnsupportedModelError, match="evaluation-gated"):
+        Qwen3VLAdapter.preflight(cfg)
+    monkeypatch.setenv("QWEN3_VL_32B_ALLOW_GRAPH_BLOCKED", "true")          # not the exact literal
+    with pytest.raises(UnsupportedModelError, match="evaluation-gated"):
+        Qwen3VLAdapter.preflight(cfg)
+    monkeypatch.setenv("QWEN3_VL_32B_ALLOW_GRAPH_BLOCKED", "1")
+    Qwen3VLAdapter.preflight(cfg)
+    from rhinoforge_b200.runtime.control import rpu_env_bool, warmup_iters
+    monkeypatch.setenv("RPU_PI05_DENOISE_UNROLL", "maybe")
+    with pytest.raises(ValueError):
+        rpu_env_bool("RPU_PI05_DENOISE_UNROLL", True)
+    monkeypatch.setenv("RPU_WARMUP", "2")
+    assert warmup_iters() == 2
