@@ -46,7 +46,7 @@ def parse_args(argv=None):
 
 
 REFERENCE_UNAVAILABLE = ("reference needs the restricted 'rhino_launch 1.0.0' CMake package, the rhinoOpLib operator "
-                         "asset and an RPU board; pip install of /root/reference fails at CMake configure")
+                         "asset and an RPU board; pip install of the reference source fails at CMake configure")
 
 
 class ClockSampler:
