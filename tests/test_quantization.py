@@ -177,3 +177,50 @@ def test_pi05_converter_quantises_only_gemma_projections_and_writes_the_sidecar(
     st4b = convert_checkpoint(src, tmp_path / "q4b", bits=4)
     q = load_file(str(tmp_path / "q4b" / "model.safetensors"))[vlm + "mlp.down_proj.weight"]
     assert st4b["int4"] == 3 and int(q.max()) <= 7 and int(q.min()) >= -8
+
+
+def test_wall_oss_converters_scope_and_sidecars(tmp_path):
+    """W8A16: every 2-D weight but the token embedding.  W4A16: only the fused expert projections of the decoder, as
+    4-bit values in int8 containers or packed groups; `--keep-int8` retreats a suffix to 8 bits."""
+    from safetensors.torch import load_file, save_file
+    from rpu_backend.quant.convert_wall_oss import convert_checkpoint as to_w4
+    from rpu_backend.quant.convert_wall_oss_w8a16 import convert_checkpoint as to_w8, main as main_w8
+    from rpu_backend.quant.int4_pgrp_pack import dequantize_int4_pgrp
+    from rpu_backend.quant._common import cosine, dequantize_linear_per_channel
+    g = torch.Generator().manual_seed(0)
+    r = lambda *s: torch.randn(*s, generator=g) * 0.05
+    L = "model.layers.0."
+    sd = {"model.embed_tokens.weight": r(40, 32), L + "self_attn.qkv_proj_experts.0.weight": r(96, 32),
+          L + "self_attn.o_proj_experts.1.weight": r(32, 32), L + "moe.experts.0.gate_up_proj.weight": r(128, 32),
+          L + "moe.experts.1.down_proj.weight": r(32, 64), L + "input_layernorm.weight": r(32),
+          "visual.blocks.0.attn.qkv.weight": r(96, 32), "visual.blocks.0.attn.qkv.bias": r(96),
+          "action_preprocessor.proj.weight": r(32, 16)}
+    src = tmp_path / "src"
+    src.mkdir()
+    save_file(sd, str(src / "model.safetensors"), metadata={"format": "pt"})
+    (src / "config.json").write_text("{}")
+    (src / "norm_stats.json").write_text("{}")
+    st = to_w8(src, tmp_path / "w8")
+    out = load_file(str(tmp_path / "w8" / "model.safetensors"))
+    assert st["n_quantized"] == 6                                        # all 2-D weights except the embedding
+    assert out["model.embed_tokens.weight"].dtype == torch.float32 and out["visual.blocks.0.attn.qkv.weight"].dtype == torch.int8
+    assert out["visual.blocks.0.attn.qkv.bias"].dtype == torch.float32
+    name = "action_preprocessor.proj.weight"
+    assert cosine(dequantize_linear_per_channel(out[name], out[name[:-7] + ".weight_scale"]), sd[name]) > 0.999
+    side = json.loads((tmp_path / "w8" / "rpu_quant_config.json").read_text())
+    assert side["method"] == "w8a16" and side["skip_modules"] == ["embed_tokens"]
+    assert (tmp_path / "w8" / "norm_stats.json").is_file()
+    assert main_w8(["--src", str(src), "--dst", str(tmp_path / "w8")]) == 1                  # never overwrites
+    st4 = to_w4(src, tmp_path / "w4", keep_int8=["self_attn.o_proj_experts.1"])
+    o4 = load_file(str(tmp_path / "w4" / "model.safetensors"))
+    assert (st4["int4"], st4["int8"]) == (3, 1)
+    q = o4[L + "moe.experts.0.gate_up_proj.weight"]
+    assert q.dtype == torch.int8 and int(q.max()) <= 7 and int(q.min()) >= -8
+    assert int(o4[L + "self_attn.o_proj_experts.1.weight"].abs().max()) > 8            # kept at 8 bits
+    assert o4["visual.blocks.0.attn.qkv.weight"].dtype == torch.float32                  # vision untouched
+    stg = to_w4(src, tmp_path / "w4g", group_size=32)
+    og = load_file(str(tmp_path / "w4g" / "model.safetensors"))
+    name = L + "moe.experts.1.down_proj.weight"
+    assert og[name].dtype == torch.uint8 and tuple(og[name].shape) == (32, 32) and stg["int4"] == 4
+    assert cosine(dequantize_int4_pgrp(og[name], og[name[:-7] + ".weight_scale"], 32), sd[name]) > 0.99
+    assert json.loads((tmp_path / "w4g" / "rpu_quant_config.json").read_text())["group_size"] == 32
