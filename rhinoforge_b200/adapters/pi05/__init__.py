@@ -119,7 +119,9 @@ def load_checkpoint(path: str):
     if pc.get("type", "pi05") != "pi05":
         raise UnsupportedModelError(f"checkpoint policy type {pc.get('type')!r} is not pi05")
     cfg, meta = config_from_policy_config(pc)
-    files = sorted(root.glob("model*.safetensors"))
+    # names are canonicalised while reading, so the reference's derived `model_remapped.safetensors` (a cache that can be
+    # stale with respect to the shards beside it) is never read
+    files = sorted(f for f in root.glob("model*.safetensors") if f.name != "model_remapped.safetensors")
     if not files:
         raise UnsupportedModelError(f"no model*.safetensors under {path!r}")
     return cfg, _LazyStateDict(files), meta

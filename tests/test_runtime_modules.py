@@ -369,3 +369,15 @@ def test_evaluation_gates_and_model_switches_read_their_environment(monkeypatch)
         rpu_env_bool("RPU_PI05_DENOISE_UNROLL", True)
     monkeypatch.setenv("RPU_WARMUP", "2")
     assert warmup_iters() == 2
+
+
+def test_pi05_loader_ignores_a_stale_remapped_cache_file(tmp_path):
+    import json
+    import torch
+    from safetensors.torch import save_file
+    from rhinoforge_b200.adapters.pi05 import load_checkpoint
+    (tmp_path / "config.json").write_text(json.dumps({"type": "pi05"}))
+    save_file({"model.action_in_proj.weight": torch.ones(2, 2)}, str(tmp_path / "model.safetensors"))
+    save_file({"action_in_proj.weight": torch.zeros(2, 2)}, str(tmp_path / "model_remapped.safetensors"))   # stale copy
+    _, sd, _ = load_checkpoint(str(tmp_path))
+    assert torch.equal(sd["action_in_proj.weight"], torch.ones(2, 2))
