@@ -381,3 +381,32 @@ def test_pi05_loader_ignores_a_stale_remapped_cache_file(tmp_path):
     save_file({"action_in_proj.weight": torch.zeros(2, 2)}, str(tmp_path / "model_remapped.safetensors"))   # stale copy
     _, sd, _ = load_checkpoint(str(tmp_path))
     assert torch.equal(sd["action_in_proj.weight"], torch.ones(2, 2))
+
+
+def test_chunked_gated_delta_rule_equals_the_recurrence():
+    """The block-parallel form (triangular solve per chunk) reproduces the token-by-token recurrence: ragged last chunk,
+    carried-in state, strong and weak decay, and agreement with the Hugging Face recurrent reference."""
+    import torch
+    from rhinoforge_b200.models.gdn_chunked import chunked_gated_delta_rule, recurrent_gated_delta_rule
+    torch.manual_seed(0)
+    T, H, Dk, Dv = 150, 3, 16, 24
+    q = torch.nn.functional.normalize(torch.randn(T, H, Dk), dim=-1)
+    k = torch.nn.functional.normalize(torch.randn(T, H, Dk), dim=-1)
+    v = torch.randn(T, H, Dv)
+    g = -torch.rand(T, H) * 0.5
+    g[40:60] *= 8.0                                         # a stretch of strong forgetting
+    beta = torch.rand(T, H)
+    s0 = torch.randn(H, Dk, Dv) * 0.3
+    o_ref, s_ref = recurrent_gated_delta_rule(q, k, v, g, beta, state=s0)
+    for chunk in (64, 32, 7):
+        o, s = chunked_gated_delta_rule(q, k, v, g, beta, state=s0, chunk=chunk)
+        assert torch.allclose(o, o_ref, atol=2e-4, rtol=2e-4), chunk
+        assert torch.allclose(s, s_ref, atol=2e-4, rtol=2e-4), chunk
+    try:
+        from transformers.models.qwen3_next.modeling_qwen3_next import torch_recurrent_gated_delta_rule as hf
+    except Exception:  # noqa: BLE001
+        return
+    o_hf, s_hf = hf(q[None], k[None], v[None], g[None], beta[None], initial_state=s0[None], output_final_state=True,
+                    use_qk_l2norm_in_kernel=False)
+    assert torch.allclose(o_hf[0].float(), o_ref, atol=2e-4, rtol=2e-4)
+    assert torch.allclose(s_hf[0].float(), s_ref, atol=2e-4, rtol=2e-4)
