@@ -67,8 +67,9 @@ class RPUModelForCausalLM:
         from ..quant.load import is_w8a16_config, load_w8a16_model
         if to_rpu and os.path.isdir(hf_repo_or_path):
             # streamed load: safetensors -> packed device weights, no host-side model object
-            from ..quant.load import w8a16_tensor_getter
+            from ..quant.load import is_w4a16_config, w4a16_tensor_getter, w8a16_tensor_getter
             get = (w8a16_tensor_getter(hf_repo_or_path, config) if is_w8a16_config(config)
+                   else w4a16_tensor_getter(hf_repo_or_path, config) if is_w4a16_config(config)
                    else checkpoint_tensor_getter(hf_repo_or_path))
             adapter = adapter_cls(None, config=config, get_weight=get, rpu_execution=execution, dtype=dtype)
             return adapter.to_rpu(max_batch=max_batch, tp=tp)

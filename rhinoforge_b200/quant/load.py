@@ -30,6 +30,34 @@ def is_w8a16_config(config) -> bool:
     return isinstance(qc, dict) and qc.get("method") == W8A16_METHOD
 
 
+def is_w4a16_config(config) -> bool:
+    qc = getattr(config, "quant_config", None)
+    if qc is None and isinstance(config, dict):
+        qc = config.get("quant_config")
+    return isinstance(qc, dict) and qc.get("method") == "w4a16"
+
+
+def w4a16_tensor_getter(ckpt_dir: str, config) -> Callable[[str], torch.Tensor]:
+    """``get(name)`` over a packed W4A16 checkpoint (``quant/convert_qwen3_w4a16.py``): a packed projection
+    (``uint8 [out, in/2]`` with group-wise fp16 scales) is dequantised to fp16 when it is read, so the 16-bit kernels run
+    it; there is no 4-bit device GEMM.  Every other tensor is returned as stored; scale tensors are not listed."""
+    from ..api._loading import checkpoint_tensor_getter
+    from .int4_pgrp_pack import dequantize_int4_pgrp
+    qc = getattr(config, "quant_config", None) or (config.get("quant_config") if isinstance(config, dict) else {})
+    group = int(qc.get("group_size", 32))
+    base = checkpoint_tensor_getter(ckpt_dir)
+    scale_of = lambda n: n[:-len(".weight")] + ".weight_scale"
+
+    def get(name: str) -> torch.Tensor:
+        t = base(name)
+        if t.dtype == torch.uint8 and name.endswith(".weight") and scale_of(name) in base.names:
+            return dequantize_int4_pgrp(t, base(scale_of(name)), group)
+        return t
+
+    get.names = frozenset(n for n in base.names if not n.endswith(".weight_scale"))  # type: ignore[attr-defined]
+    return get
+
+
 def _shards(ckpt: Path) -> List[Path]:
     idx = ckpt / "model.safetensors.index.json"
     if idx.is_file():

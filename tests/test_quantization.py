@@ -224,3 +224,19 @@ def test_wall_oss_converters_scope_and_sidecars(tmp_path):
     assert og[name].dtype == torch.uint8 and tuple(og[name].shape) == (32, 32) and stg["int4"] == 4
     assert cosine(dequantize_int4_pgrp(og[name], og[name[:-7] + ".weight_scale"], 32), sd[name]) > 0.99
     assert json.loads((tmp_path / "w4g" / "rpu_quant_config.json").read_text())["group_size"] == 32
+
+
+def test_w4a16_checkpoint_is_dequantised_when_read(tmp_path):
+    from rpu_backend.quant._common import cosine
+    from rpu_backend.quant.convert_qwen3_w4a16 import convert_checkpoint
+    from rpu_backend.quant.load import is_w4a16_config, w4a16_tensor_getter
+    cfg, sd = _tiny_ckpt(tmp_path / "src", tie=False)
+    convert_checkpoint(tmp_path / "src", tmp_path / "w4", group_size=32)
+    config = json.loads((tmp_path / "w4" / "config.json").read_text())
+    assert is_w4a16_config(config) and not is_w4a16_config({"quant_config": {"method": "w8a16"}})
+    get = w4a16_tensor_getter(str(tmp_path / "w4"), config)
+    name = "model.layers.0.self_attn.q_proj.weight"
+    w = get(name)
+    assert w.dtype == torch.float16 and w.shape == sd[name].shape and cosine(w, sd[name]) > 0.99
+    assert get("model.layers.0.input_layernorm.weight").dtype == torch.float16
+    assert not any(n.endswith(".weight_scale") for n in get.names) and name in get.names
