@@ -1042,6 +1042,11 @@ extern "C" int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem
   return RF_OK;
 }
 
+// The launch plan rf_gemm / rf_gemm_w8a16 would use for this shape, without launching (host-only; usable without
+// a GPU, where 148 SMs are assumed): out = {swap, bn, splits, stages, grid_x, grid_y, shared-memory bytes, k_blocks,
+// persistent kernel?, two-shot all-reduce?}.  For tests of the planner's invariants and for diagnostics.
+extern "C" int rf_gemm_plan_info(const RfGemm* g, int32_t* out);
+
 namespace rf {
 bool gemm_ps_eligible(const RfGemm* g, bool swap, int splits);   // gemm_ps.cu: persistent kernel for large M
 int launch_gemm_ps(const RfGemm* g, cudaStream_t stream);
@@ -1089,6 +1094,20 @@ static int run_gemm(const RfGemm* g, cudaStream_t stream, bool w8) {
   if (g->dtype == 0) { RF_GEMM_DISPATCH(__half, false) }
   RF_GEMM_DISPATCH(__nv_bfloat16, false)
 #undef RF_GEMM_DISPATCH
+}
+
+extern "C" int rf_gemm_plan_info(const RfGemm* g, int32_t* out) {
+  RF_REQUIRE(g && out, "rf_gemm_plan_info: null argument");
+  int rc = check_gemm(g);
+  if (rc) return rc;
+  GemmPlan pl;
+  rc = plan_gemm(g, &pl);
+  if (rc) return rc;
+  out[0] = pl.swap; out[1] = pl.bn; out[2] = pl.splits; out[3] = pl.stages; out[4] = pl.grid_x; out[5] = pl.grid_y;
+  out[6] = (int32_t)pl.smem_bytes; out[7] = pl.k_blocks;
+  out[8] = (!g->w_int8 && g->force_splits == 0 && g->force_bn == 0 && rf::gemm_ps_eligible(g, pl.swap != 0, pl.splits)) ? 1 : 0;
+  out[9] = (g->ar_world > 1 && !pl.swap && g->M > 256) ? 1 : 0;
+  return RF_OK;
 }
 
 extern "C" int rf_gemm(const RfGemm* g, rf_stream_t stream) {

@@ -67,6 +67,9 @@ typedef struct RfGemm {
 uint64_t rf_pack_weight_bytes(int64_t rows, int64_t K, int32_t sections, int32_t elem_bytes);
 
 int rf_gemm(const RfGemm* g, rf_stream_t stream);
+// Launch plan of a shape without launching: out[10] = {swap, bn, splits, stages, grid_x, grid_y, smem bytes, k_blocks,
+// persistent kernel, two-shot all-reduce}.  Host-only.
+int rf_gemm_plan_info(const RfGemm* g, int32_t* out);
 // Scratch a split-K launch of this shape would need (bytes of ws, number of sems).
 int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem_count);
 // Same contract with int8 weights [N,K] and a per-output-channel scale (W8A16):

@@ -410,3 +410,101 @@ def test_chunked_gated_delta_rule_equals_the_recurrence():
                     use_qk_l2norm_in_kernel=False)
     assert torch.allclose(o_hf[0].float(), o_ref, atol=2e-4, rtol=2e-4)
     assert torch.allclose(s_hf[0].float(), s_ref, atol=2e-4, rtol=2e-4)
+
+
+def test_widened_int8_image_equals_the_packed_16bit_image_index_for_index():
+    """The device pass that widens a tile-major int8 weight image writes piece ``c`` (8 values) of row ``r`` of a block
+    to byte ``r*128 + ((c ^ (r & 7)) << 4)`` of the 16 KB block.  Replayed on the host, that must give exactly the image
+    ``pack_weight`` builds from the 16-bit weight (ragged rows / K, two GLU sections)."""
+    import torch
+    from rhinoforge_b200.ops.kernels import pack_weight
+    g = torch.Generator().manual_seed(0)
+    for rows, K, sections in ((200, 150, 1), (256, 64, 2), (130, 200, 2)):
+        q = torch.randint(-127, 128, (rows, K), generator=g, dtype=torch.int8)
+        want = pack_weight(q.to(torch.float16), sections).view(torch.uint8)
+        src = pack_weight(q, sections).view(torch.uint8)
+        blocks = src.numel() // 8192
+        assert want.numel() == blocks * 16384
+        got = torch.zeros(blocks * 16384, dtype=torch.uint8)
+        s8 = src.view(blocks, 128, 8, 8).view(torch.int8)                    # [block, row, piece, 8 values]
+        wide = s8.to(torch.float16).view(torch.uint8).view(blocks, 128, 8, 16)   # 16 bytes per piece
+        out = got.view(blocks, 128, 8, 16)
+        r = torch.arange(128)[:, None]
+        c = torch.arange(8)[None, :]
+        pos = (c ^ (r & 7))                                                   # physical chunk of logical piece c in row r
+        out[:, r.expand(128, 8), pos] = wide[:, r.expand(128, 8), c.expand(128, 8)]
+        assert torch.equal(got, want.view(-1))
+
+
+def test_persistent_tile_order_visits_every_tile_once_in_bands():
+    """Host mirror of the persistent GEMM's tile order (bands of row tiles, rows fastest inside a band): a permutation
+    of all tiles for any band size, with the short last band handled."""
+    def coords(tile, tiles_m, tiles_n, band):
+        per_band = band * tiles_n
+        b, r = divmod(tile, per_band)
+        rows_here = min(band, tiles_m - b * band)
+        return b * band + r % rows_here, r // rows_here
+
+    for tiles_m, tiles_n, band in ((64, 16, 16), (20, 8, 16), (7, 3, 2), (5, 5, 1), (9, 4, 100), (33, 5, 8)):
+        band = min(band, tiles_m)
+        seen = [coords(t, tiles_m, tiles_n, band) for t in range(tiles_m * tiles_n)]
+        assert sorted(seen) == [(m, n) for m in range(tiles_m) for n in range(tiles_n)], (tiles_m, tiles_n, band)
+        # consecutive tiles of a full band walk down the rows of one weight panel
+        if tiles_m >= 2 * band:
+            assert [c[0] for c in seen[:band]] == list(range(band)) and len({c[1] for c in seen[:band]}) == 1
+
+
+def test_gemm_planner_invariants_over_decode_prefill_and_tensor_parallel_shapes():
+    """Host-only launch plans (148 SMs assumed without a GPU): splits are powers of two and never exceed the k blocks,
+    grids stay within two CTAs per SM times the cluster size for weight-streaming shapes, shared memory fits, two-shot
+    all-reduce shapes do not split, big shapes go to the persistent kernel, and the all-reduce flag budget holds for every
+    Qwen3-8B shard shape at TP 1/2/4/8."""
+    import ctypes as C
+    from rhinoforge_b200 import _native as N
+    lib = N.lib()
+    names = "swap bn splits stages gx gy smem kb ps twoshot".split()
+
+    def plan(M, Nn, K, dual=False, int8=False, ar=0):
+        g = N.RfGemm()
+        g.M, g.N, g.K, g.dtype, g.force_swap, g.w_packed = M, Nn, K, 0, -1, 1
+        g.x = g.w = g.out = 4096
+        g.ldx, g.ldw, g.ldo = K, K, Nn
+        if dual:
+            g.dual_offset, g.act = Nn, 1
+        if int8:
+            g.w_int8, g.scale = 1, 4096
+        if ar:
+            g.ar_world, g.ar_rank, g.ar_recv, g.ar_flags, g.ar_state = ar, 0, 4096, 4096, 4096
+            g.ar_recv_bytes, g.ar_flag_count = 1 << 40, (1 << 20) - 64
+        out = (C.c_int32 * 10)()
+        assert lib.rf_gemm_plan_info(C.byref(g), out) == 0, (M, Nn, K, lib.rf_last_error())
+        return dict(zip(names, out))
+
+    H = 4096
+    for tp in (1, 2, 4, 8):
+        I, QD, AD = 12288 // tp, 48 * 128 // tp, 32 * 128 // tp
+        ar = tp if tp > 1 else 0
+        for M in (1, 8, 64, 256):
+            for (Nn, K, dual, a) in ((QD, H, False, 0), (H, AD, False, ar), (I, H, True, 0), (H, I, False, ar)):
+                for int8 in (False, True):
+                    p = plan(M, Nn, K, dual, int8, a)
+                    S = p["splits"]
+                    assert p["swap"] == 1 and S in (1, 2, 4, 8) and S <= p["kb"] and p["stages"] >= 2
+                    assert p["gx"] * p["gy"] * S <= 2 * 148 or S == 1
+                    assert p["smem"] <= 227 * 1024
+                    if a:
+                        assert p["gx"] * p["gy"] * 8 * a <= ((1 << 20) - 64) // 2
+        for M in (2048, 8192):
+            for (Nn, K, dual, a) in ((QD, H, False, 0), (H, AD, False, ar), (I, H, True, 0), (H, I, False, ar)):
+                p = plan(M, Nn, K, dual, False, a)
+                assert p["swap"] == 0 and p["smem"] <= 227 * 1024 and p["stages"] >= 2
+                if a:
+                    assert p["twoshot"] == 1 and p["splits"] == 1 and p["ps"] == 0
+                    assert p["gx"] * p["gy"] * 8 * a <= ((1 << 20) - 64) // 2
+                elif p["gx"] * p["gy"] >= 148:
+                    assert p["ps"] == 1
+    # the W8A16 gate/up decode shape fits two CTAs per SM
+    p = plan(64, 12288, 4096, True, True)
+    assert p["smem"] <= (228 * 1024 - 2048) // 2 and p["stages"] == 2 and p["splits"] == 2
+    # short K: one k block per split is allowed
+    assert plan(64, 4096, 512)["splits"] == 8 and plan(64, 4096, 128)["splits"] == 2
