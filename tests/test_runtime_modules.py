@@ -508,3 +508,32 @@ def test_gemm_planner_invariants_over_decode_prefill_and_tensor_parallel_shapes(
     assert p["smem"] <= (228 * 1024 - 2048) // 2 and p["stages"] == 2 and p["splits"] == 2
     # short K: one k block per split is allowed
     assert plan(64, 4096, 512)["splits"] == 8 and plan(64, 4096, 128)["splits"] == 2
+
+
+def test_bench_clock_sampler_reports_the_timed_region_only():
+    """The sampler parses nvidia-smi CSV lines, reports samples taken after mark() (falling back to the last warm-up
+    samples when the region is shorter than two sampling periods) and collects the throttle reasons it saw."""
+    import importlib.util
+    from pathlib import Path
+    spec = importlib.util.spec_from_file_location("bench_mod", Path(__file__).resolve().parents[1] / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+
+    class Done:
+        def terminate(self): pass
+        def wait(self, timeout=None): return 0
+
+    def sampler(lines, first):
+        s = bench.ClockSampler(0)
+        s.proc, s.lines, s.first = Done(), list(lines), first
+        return s.stop()
+
+    idle = "0, 345, 1965, 140.2, 0x0000000000000001, Not Active, Not Active, Not Active, Not Active"
+    busy = "0, 1965, 1965, 960.5, 0x0000000000000004, Not Active, Not Active, Not Active, Active"
+    hot = "0, 1500, 1965, 990.0, 0x0000000000000040, Not Active, Active, Not Active, Active"
+    r = sampler([idle, idle, busy, busy, busy], first=2)
+    assert r["sm_mhz"] == 1965.0 and r["sm_max_mhz"] == 1965.0 and r["samples"] == 3 and r["reasons"] == ["sw_power_cap"]
+    r = sampler([idle, busy, busy, busy, hot], first=4)          # one sample in the region: the warm-up tail is included
+    assert r["samples"] == 5 and "hw_thermal_slowdown" in r["reasons"]
+    r = sampler(["garbage", busy], first=0)
+    assert r["samples"] == 1
