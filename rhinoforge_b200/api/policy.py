@@ -13,15 +13,13 @@ Reference: ``python/rpu_backend/api/policy.py:57-119,164-190,193-289``.
 """
 from __future__ import annotations
 
-import json
 from collections import deque
-from pathlib import Path
 from typing import Any, Dict, Optional
 
 import torch
 
 from ._execution import normalize_rpu_execution
-from .errors import RPUBackendError, RPUUnsupportedDtypeError, UnsupportedModelError
+from .errors import RPUBackendError, RPUUnsupportedDtypeError
 
 IMAGE_PREFIX = "observation.images."
 TOKENS_KEY = "observation.language.tokens"

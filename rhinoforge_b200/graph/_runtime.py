@@ -12,7 +12,6 @@ Semantics follow ``python/rpu_backend/graph/_runtime.py:49-340``; the native hal
 from __future__ import annotations
 
 import ctypes as C
-import os
 import threading
 import warnings
 import weakref

@@ -14,7 +14,7 @@ Without a CUDA device or the native library the object degrades to *pass-through
 """
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Callable, Dict, List, Optional, Sequence
 
 import torch
 

@@ -10,7 +10,7 @@ reference (``src/fused/rpu_lingbot_v2_moe_model.h:29-49``, ``.cpp:1029-1213,1215
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Optional
+from typing import Dict
 
 import torch
 import torch.nn.functional as F

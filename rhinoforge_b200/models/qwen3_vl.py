@@ -13,7 +13,7 @@ M-RoPE tables), ``src/fused/rpu_qwen3_model.h:3594-3623`` (DeepStack add after t
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Callable, List, Optional, Sequence
 
 import torch
 

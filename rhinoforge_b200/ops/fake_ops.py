@@ -7,7 +7,6 @@ which hand pointers to the native library, cannot run there.  The reference keep
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 

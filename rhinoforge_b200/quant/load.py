@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import json
 from pathlib import Path
-from typing import Callable, Dict, List
+from typing import Callable, List
 
 import torch
 from torch import nn

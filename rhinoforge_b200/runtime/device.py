@@ -4,7 +4,7 @@ The reference accepts only device index 0 (``python/rpu_backend/runtime/device.p
 index selects the CUDA ordinal, and tensor-parallel ranks use their local GPU."""
 from __future__ import annotations
 
-from typing import Optional, Union
+from typing import Union
 
 
 def resolve_device(device: Union[str, "object", None]):

@@ -15,7 +15,6 @@ from __future__ import annotations
 
 import ctypes as C
 import os
-import math
 from typing import Callable, Dict, List, Optional, Sequence
 
 import torch

@@ -3,7 +3,7 @@
 ``[positions, rot_dim/2]`` plus an optional per-frequency axis selector; these helpers produce both."""
 from __future__ import annotations
 
-from typing import Optional, Sequence, Tuple
+from typing import Sequence, Tuple
 
 import torch
 

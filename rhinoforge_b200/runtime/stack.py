@@ -9,7 +9,7 @@ paged vs in-buffer KV), which is how the reference's one-class-per-family fused 
 from __future__ import annotations
 
 import ctypes as C
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
 import torch

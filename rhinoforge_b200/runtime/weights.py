@@ -9,7 +9,7 @@ swizzled shared-memory image, loaded by one bulk copy per block.
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, Optional, Tuple
+from typing import Dict, Iterable, Tuple
 
 import torch
 
