@@ -11,7 +11,7 @@ _LAZY = {
     "WallOssPolicy": ("_unbuilt", "WallOssPolicy"),
     "Lingbot2Policy": ("_unbuilt", "Lingbot2Policy"),
     "HyEmbodiedPolicy": ("_unbuilt", "HyEmbodiedPolicy"),
-    "RhinoVLAPolicy": ("_unbuilt", "RhinoVLAPolicy"),
+    "RhinoVLAPolicy": ("rhinovla", "RhinoVLAPolicy"),
 }
 
 
