@@ -14,6 +14,7 @@ from typing import Optional
 
 import torch
 
+from ..graph.lazy_init_guard import mark_install_checked, verify_lazy_init
 from .errors import RPUBackendError
 from .engine import DecoderEngine
 
@@ -29,6 +30,9 @@ class RPUCausalLM:
         self._owner = owner
         self._rpu_last_execution_plan = None
         self.generation_config = getattr(owner, "generation_config", None)
+        # everything the decode path reads exists from here on; nothing is created at the first forward
+        mark_install_checked(self, ("engine", "_rpu_execution", "_rpu_dtype", "_rpu_tp_world"))
+        verify_lazy_init(self)
 
     # -- module-like surface --------------------------------------------------------------------
     @property

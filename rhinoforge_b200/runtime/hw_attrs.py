@@ -13,7 +13,9 @@ from .errors import RPUConfigError
 PUBLIC = frozenset({"_rpu_last_execution_plan", "_rpu_debug_tag"})
 COLD = frozenset({"_rpu_execution", "_rpu_dtype", "_rpu_tp_world", "_rpu_max_seq_len", "_rpu_chunk_envelope",
                   "_rpu_vlm_chunk_size", "_rpu_linear_partition"})
-INTERNAL = frozenset({"_rpu_is_ready", "_rpu_handle", "_rpu_graph_caches", "_rpu_swizzle_started", "_rpu_frozen"})
+INTERNAL = frozenset({"_rpu_is_ready", "_rpu_handle", "_rpu_graph_caches", "_rpu_swizzle_started", "_rpu_frozen",
+                      # the install-completeness guard's opt-in marker (two spellings) and its attribute list
+                      "_rpu_lazy_init_checked", "_rpu_dynamo_safe", "_rpu_required_attrs"})
 
 
 def classify(name: str) -> str:

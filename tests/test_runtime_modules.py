@@ -537,3 +537,48 @@ def test_bench_clock_sampler_reports_the_timed_region_only():
     assert r["samples"] == 5 and "hw_thermal_slowdown" in r["reasons"]
     r = sampler(["garbage", busy], first=0)
     assert r["samples"] == 1
+
+
+# ----------------------------------------------------------------------------- install-completeness guard
+def test_lazy_init_guard_finds_missing_declared_state():
+    import torch.nn as nn
+    from rhinoforge_b200.graph import (DynamoUnsafeLazyStateError, UninitializedLazyStateError, freeze_for_dynamo,
+                                       mark_install_checked, verify_lazy_init)
+    from rhinoforge_b200.graph.lazy_init_guard import missing_state, verify_graph_module_best_effort
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.proj = nn.Linear(4, 4)
+
+    model = nn.Sequential(Block(), Block(), nn.ReLU())
+    verify_lazy_init(model)                                          # nobody opted in: nothing to check
+    mark_install_checked(model[0], ("_rpu_handle_x",))
+    model[1]._rpu_dynamo_safe = True                                 # the older marker spelling
+    model[1]._rpu_required_attrs = ("_rpu_cos_sin", "proj")
+    assert missing_state(model) == [("0", "Block", ["_rpu_handle_x"]), ("1", "Block", ["_rpu_cos_sin"])]
+    with pytest.raises(UninitializedLazyStateError, match=r"0 \(Block\): missing \['_rpu_handle_x'\]"):
+        verify_lazy_init(model)
+    assert DynamoUnsafeLazyStateError is UninitializedLazyStateError and freeze_for_dynamo is verify_lazy_init
+    model[0]._rpu_handle_x = object()
+    model[1]._rpu_cos_sin = None                                     # present, even if None
+    verify_lazy_init(model)
+    mark_install_checked(model[0], ("_rpu_handle_x", "_rpu_other"))  # extends, no duplicates
+    assert model[0]._rpu_required_attrs == ("_rpu_handle_x", "_rpu_other")
+    with pytest.raises(UninitializedLazyStateError):
+        verify_graph_module_best_effort(model)                       # walks direct children
+    verify_graph_module_best_effort(object())                        # nothing with _modules: no-op
+
+    class Handle:                                                    # runtime handles are not nn.Modules
+        pass
+    h = mark_install_checked(Handle(), ("engine",))
+    with pytest.raises(UninitializedLazyStateError, match="<root>"):
+        verify_lazy_init(h)
+    h.engine = 1
+    verify_lazy_init(h)
+
+
+def test_guard_marker_names_are_known_runtime_attributes():
+    from rhinoforge_b200.runtime import hw_attrs
+    for name in ("_rpu_lazy_init_checked", "_rpu_dynamo_safe", "_rpu_required_attrs"):
+        assert hw_attrs.classify(name) == "internal"
