@@ -582,3 +582,53 @@ def test_guard_marker_names_are_known_runtime_attributes():
     from rhinoforge_b200.runtime import hw_attrs
     for name in ("_rpu_lazy_init_checked", "_rpu_dynamo_safe", "_rpu_required_attrs"):
         assert hw_attrs.classify(name) == "internal"
+
+
+# ----------------------------------------------------------------------------- adapter template
+def test_adapter_template_refuses_until_filled_then_behaves_like_a_family(monkeypatch):
+    from types import SimpleNamespace
+    import torch
+    from rhinoforge_b200.adapters._template import MinimalCausalLMAdapter, TemplateNotFilledError, register
+    from rhinoforge_b200.api.errors import UnsupportedModelError
+    from rhinoforge_b200.runtime import live_handle, registry
+
+    cfg = SimpleNamespace(model_type="llama", hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                          num_attention_heads=2, num_key_value_heads=1, head_dim=64, vocab_size=64, rms_norm_eps=1e-5,
+                          rope_theta=1e4, tie_word_embeddings=True)
+    with pytest.raises(TemplateNotFilledError, match="ARCH, FAMILY, SUPPORTED_PROFILES"):
+        MinimalCausalLMAdapter.preflight(cfg)
+    with pytest.raises(TemplateNotFilledError):
+        register()
+
+    class TinyAdapter(MinimalCausalLMAdapter):
+        ARCH, FAMILY = "TinyForCausalLM", "Tiny"
+        SUPPORTED_PROFILES = frozenset({(128, 256, 2, 1)})
+        RENAMES = (("transformer.h.", "model.layers."), ("transformer.wte.", "model.embed_tokens."))
+
+    TinyAdapter.preflight(cfg)
+    with pytest.raises(UnsupportedModelError, match="deny by default"):
+        TinyAdapter.preflight(SimpleNamespace(**{**vars(cfg), "hidden_size": 256}))
+    with pytest.raises(UnsupportedModelError, match="head_dim"):
+        TinyAdapter.preflight(SimpleNamespace(**{**vars(cfg), "head_dim": 80}))
+
+    sd = {"transformer.wte.weight": torch.zeros(64, 128), "transformer.h.0.self_attn.q_proj.weight": torch.ones(128, 128),
+          "model.norm.weight": torch.ones(128)}
+    get_raw = lambda n: sd[n]
+    get_raw.names = frozenset(sd)
+    ad = TinyAdapter(config=cfg, get_weight=get_raw, rpu_execution={"prefill": {"chunk_size": 64}})
+    try:
+        dc = ad.decoder_config()
+        assert (dc.hidden_size, dc.num_layers, dc.num_kv_heads, dc.qk_norm, dc.tie_embeddings) == (128, 2, 1, False, True)
+        get = ad._weights()
+        assert get("model.layers.0.self_attn.q_proj.weight").sum() == 128 * 128
+        assert get("model.embed_tokens.weight").shape == (64, 128) and get("model.norm.weight").shape == (128,)
+        assert "model.layers.0.self_attn.q_proj.weight" in get.names and "transformer.wte.weight" not in get.names
+        ad._validate_shapes(dc, get)                                # the names the engine asks for are all present
+        with pytest.raises(ValueError, match="not supported"):
+            TinyAdapter(config=cfg, get_weight=get_raw, rpu_execution={"vision": {"chunk_size": 64}})
+    finally:
+        live_handle.release(ad) if hasattr(live_handle, "release") else None
+
+    monkeypatch.setattr(registry, "ADAPTERS", dict(registry.ADAPTERS))
+    register(TinyAdapter)
+    assert registry.get_adapter("TinyForCausalLM") is TinyAdapter
