@@ -54,7 +54,9 @@ def convert_checkpoint(src, dst, *, keep_int8: Sequence[str] = (), group_size: i
         n["int4" if b == 4 else "int8"] += 1
         return {name: q, scale_name(name): s}
 
-    sidecar = {"method": "w4a16", "mode": "per_group_symmetric" if group_size else "per_channel_symmetric", "qaxis": 0,
+    # "source" is the directory name only: converted checkpoints sit beside their source, and a build host's path must
+    # not leak into the artifact; checkpoint_pair.validate_* resolves it relative to the converted directory's parent
+    sidecar = {"source": Path(src).name, "method": "w4a16", "mode": "per_group_symmetric" if group_size else "per_channel_symmetric", "qaxis": 0,
                "group_size": group_size, "container": "uint8x2" if group_size else "int8",
                "int4_suffixes": [s for s in QUANT_SUFFIXES if s not in keep], "int8_suffixes": list(keep)}
     stats = rewrite_checkpoint(src, dst, transform, sidecars={SIDECAR: sidecar}, drop_files=(SIDECAR,),

@@ -41,7 +41,7 @@ def convert_checkpoint(src, dst, *, skip_modules: Sequence[str] = DEFAULT_SKIP_M
         n["quantized"] += 1
         return {name: q, scale_name(name): s}
 
-    sidecar = {"method": "w8a16", "mode": "per_channel_symmetric", "qaxis": 0, "skip_modules": list(skip),
+    sidecar = {"source": Path(src).name, "method": "w8a16", "mode": "per_channel_symmetric", "qaxis": 0, "skip_modules": list(skip),
                "scope": "all_2d_weights"}
     stats = rewrite_checkpoint(src, dst, transform, sidecars={SIDECAR: sidecar}, drop_files=(SIDECAR,),
                                tag="convert_wall_oss_w8a16")

@@ -240,3 +240,79 @@ def test_w4a16_checkpoint_is_dequantised_when_read(tmp_path):
     assert w.dtype == torch.float16 and w.shape == sd[name].shape and cosine(w, sd[name]) > 0.99
     assert get("model.layers.0.input_layernorm.weight").dtype == torch.float16
     assert not any(n.endswith(".weight_scale") for n in get.names) and name in get.names
+
+
+def test_wall_oss_checkpoint_pair_validation(tmp_path):
+    """A converted directory is accepted only with the 16-bit directory it was converted from."""
+    from safetensors.torch import save_file
+    from rpu_backend.quant.checkpoint_pair import (validate_checkpoint_pair, validate_rtc_w4_checkpoint_pair,
+                                                   validate_w8_nvfp4_checkpoint_pair)
+    from rpu_backend.quant.convert_wall_oss import QUANT_SUFFIXES, convert_checkpoint as to_w4
+    from rpu_backend.quant.convert_wall_oss_w8a16 import convert_checkpoint as to_w8
+    g = torch.Generator().manual_seed(1)
+    L = "model.layers.0."
+    sd = {L + s: torch.randn(64, 64, generator=g) * 0.05 for s in QUANT_SUFFIXES}
+    sd["model.embed_tokens.weight"] = torch.randn(16, 64, generator=g)
+
+    def make_src(path, **cfg):
+        path.mkdir()
+        save_file(sd, str(path / "model.safetensors"), metadata={"format": "pt"})
+        (path / "config.json").write_text(json.dumps({"hidden_size": 64, "num_hidden_layers": 1, "torch_dtype": "bfloat16",
+                                                      **cfg}))
+        return path
+
+    src = make_src(tmp_path / "wall-oss")
+    other = make_src(tmp_path / "wall-oss-finetune")
+    bigger = make_src(tmp_path / "wall-oss-big", hidden_size=128)
+    to_w8(src, tmp_path / "w8")
+    cfg = json.loads((tmp_path / "w8" / "config.json").read_text())
+    cfg["torch_dtype"] = "float16"                                     # a representation field may differ
+    (tmp_path / "w8" / "config.json").write_text(json.dumps(cfg))
+    qcfg, fcfg = validate_w8_nvfp4_checkpoint_pair(tmp_path / "w8", src)
+    assert qcfg["hidden_size"] == fcfg["hidden_size"] == 64
+    assert json.loads((tmp_path / "w8" / "rpu_quant_config.json").read_text())["source"] == "wall-oss"   # name, not a path
+
+    with pytest.raises(ValueError, match="not a declared source pair"):
+        validate_w8_nvfp4_checkpoint_pair(tmp_path / "w8", other)
+    with pytest.raises(ValueError, match="got unquantized"):
+        validate_w8_nvfp4_checkpoint_pair(src, src)                     # arguments of the wrong kind
+    with pytest.raises(ValueError, match="must be an unquantized source"):
+        validate_w8_nvfp4_checkpoint_pair(tmp_path / "w8", tmp_path / "w8")
+    with pytest.raises(ValueError, match="method='w4a16'; got w8a16"):
+        validate_rtc_w4_checkpoint_pair(tmp_path / "w8", src)
+
+    # a converted directory that was moved away from its source cannot be resolved
+    moved = tmp_path / "elsewhere"
+    moved.mkdir()
+    (tmp_path / "w8").rename(moved / "w8")
+    with pytest.raises(ValueError, match="cannot be resolved exactly"):
+        validate_w8_nvfp4_checkpoint_pair(moved / "w8", src)
+    side = json.loads((moved / "w8" / "rpu_quant_config.json").read_text())
+    (moved / "w8" / "rpu_quant_config.json").write_text(json.dumps({**side, "source": str(src)}))  # absolute is allowed
+    validate_w8_nvfp4_checkpoint_pair(moved / "w8", src)
+    (moved / "w8" / "rpu_quant_config.json").write_text(json.dumps({k: v for k, v in side.items() if k != "source"}))
+    with pytest.raises(ValueError, match="no source provenance"):
+        validate_w8_nvfp4_checkpoint_pair(moved / "w8", src)
+
+    # same provenance, different architecture fields
+    to_w8(bigger, tmp_path / "w8big")
+    cfgb = json.loads((tmp_path / "w8big" / "config.json").read_text())
+    (tmp_path / "w8big" / "config.json").write_text(json.dumps({**cfgb, "hidden_size": 64, "rope_theta": 5.0}))
+    with pytest.raises(ValueError, match=r"mismatched config fields: \['hidden_size', 'rope_theta'\]"):
+        validate_w8_nvfp4_checkpoint_pair(tmp_path / "w8big", bigger)
+
+    # sidecar and embedded record must agree
+    (tmp_path / "w8big" / "config.json").write_text(json.dumps({**cfgb, "quant_config": {"method": "w4a16"}}))
+    with pytest.raises(ValueError, match="conflicting quantization metadata"):
+        validate_w8_nvfp4_checkpoint_pair(tmp_path / "w8big", bigger)
+
+    # the real-time-chunking composition: group 32, expert-0 down projection kept at 8 bits, nothing else
+    to_w4(src, tmp_path / "rtc", keep_int8=["moe.experts.0.down_proj"], group_size=32)
+    validate_rtc_w4_checkpoint_pair(tmp_path / "rtc", src)
+    to_w4(src, tmp_path / "w4_plain", group_size=32)
+    with pytest.raises(ValueError, match="exact seven group-wise INT4"):
+        validate_rtc_w4_checkpoint_pair(tmp_path / "w4_plain", src)
+    to_w4(src, tmp_path / "w4_g64", keep_int8=["moe.experts.0.down_proj"], group_size=64)
+    with pytest.raises(ValueError, match="group_size=32"):
+        validate_rtc_w4_checkpoint_pair(tmp_path / "w4_g64", src)
+    assert validate_checkpoint_pair(tmp_path / "w4_plain", src, expected_method="w4a16", label="W4A16")[2]["group_size"] == 32
