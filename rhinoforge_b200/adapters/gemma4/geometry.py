@@ -42,47 +42,58 @@ class LayerGeom:
         return (self.head_dim, self.num_kv_heads, self.layer_type_id, int(self.is_kv_shared), self.kv_source_layer)
 
 
-def _field(cfg: Any, name: str, default: Any = None) -> Any:
-    return cfg.get(name, default) if isinstance(cfg, dict) else getattr(cfg, name, default)
+class _Cfg:
+    """Uniform reader over a config object or the plain dict of a ``config.json``."""
+
+    def __init__(self, raw: Any):
+        self._get = raw.get if isinstance(raw, dict) else (lambda k, d=None: getattr(raw, k, d))
+
+    def __call__(self, key: str, default: Any = None) -> Any:
+        return self._get(key, default)
+
+    def integer(self, key: str, default: int = 0) -> int:
+        return int(self._get(key, None) or default)
 
 
 def layer_geometry(text_config: Any) -> List[LayerGeom]:
     """The table for a ``Gemma4TextConfig`` or the plain ``text_config`` dict of a ``config.json``."""
-    n_layers = int(_field(text_config, "num_hidden_layers"))
-    types = list(_field(text_config, "layer_types"))
-    if len(types) != n_layers:
-        raise ValueError(f"layer_types length {len(types)} != num_hidden_layers {n_layers}")
-    first_shared = n_layers - int(_field(text_config, "num_kv_shared_layers", 0) or 0)
-    hd_sliding = int(_field(text_config, "head_dim"))
-    hd_global = int(_field(text_config, "global_head_dim") or hd_sliding)
-    n_q = int(_field(text_config, "num_attention_heads"))
-    n_kv = int(_field(text_config, "num_key_value_heads"))
-    n_kv_global = _field(text_config, "num_global_key_value_heads")
-    k_is_v = bool(_field(text_config, "attention_k_eq_v", False))
-    window = _field(text_config, "sliding_window")
+    cfg = _Cfg(text_config)
+    depth = cfg.integer("num_hidden_layers")
+    kinds = list(cfg("layer_types"))
+    if len(kinds) != depth:
+        raise ValueError(f"layer_types length {len(kinds)} != num_hidden_layers {depth}")
+    owners_end = depth - cfg.integer("num_kv_shared_layers")
+    width = {False: cfg.integer("head_dim")}
+    width[True] = cfg.integer("global_head_dim", width[False])
+    kv_heads = {False: cfg.integer("num_key_value_heads")}
+    kv_heads[True] = (cfg.integer("num_global_key_value_heads", kv_heads[False])
+                      if cfg("attention_k_eq_v", False) else kv_heads[False])
+    window = cfg.integer("sliding_window") or None
+    q_heads = cfg.integer("num_attention_heads")
 
-    source_of_type: Dict[str, int] = {t: i for i, t in enumerate(types[:first_shared])}    # last owner wins
+    donor: Dict[str, int] = {}                      # per layer type: the last layer that still owns its K/V
+    for i in range(owners_end):
+        donor[kinds[i]] = i
     table: List[LayerGeom] = []
-    for i, t in enumerate(types):
-        glob = t == GLOBAL_LAYER_TYPE
-        shared = i >= first_shared
-        if shared and t not in source_of_type:
-            raise ValueError(f"layer {i} ({t}) is KV-shared but no non-shared source layer of that type exists in "
-                             f"[0,{first_shared})")
-        table.append(LayerGeom(
-            idx=i, layer_type=t, is_global=glob, head_dim=hd_global if glob else hd_sliding, num_q_heads=n_q,
-            num_kv_heads=int(n_kv_global) if (glob and k_is_v and n_kv_global) else n_kv,
-            rope_type="proportional" if glob else "default",
-            sliding_window=None if glob or not window else int(window),
-            is_kv_shared=shared, kv_source_layer=source_of_type[t] if shared else i, has_kv_proj=not shared))
+    for i, kind in enumerate(kinds):
+        wide, borrows = kind == GLOBAL_LAYER_TYPE, i >= owners_end
+        if borrows and kind not in donor:
+            raise ValueError(f"layer {i} ({kind}) is KV-shared but no non-shared source layer of that type exists in "
+                             f"[0,{owners_end})")
+        table.append(LayerGeom(i, kind, wide, width[wide], q_heads, kv_heads[wide],
+                               "proportional" if wide else "default", None if wide else window,
+                               borrows, donor[kind] if borrows else i, not borrows))
     return table
+
+
+_NATIVE_COLUMNS = (("layer_type_ids", "layer_type_id"), ("head_dim_per_layer", "head_dim"),
+                   ("num_kv_heads_per_layer", "num_kv_heads"), ("kv_source_layer", "kv_source_layer"),
+                   ("is_kv_shared", "is_kv_shared"), ("has_kv_proj", "has_kv_proj"))
 
 
 def native_layer_arrays(geo: List[LayerGeom]) -> Dict[str, List[int]]:
     """The per-layer integer arrays a native stack takes verbatim."""
-    return {"layer_type_ids": [g.layer_type_id for g in geo], "head_dim_per_layer": [g.head_dim for g in geo],
-            "num_kv_heads_per_layer": [g.num_kv_heads for g in geo], "kv_source_layer": [g.kv_source_layer for g in geo],
-            "is_kv_shared": [int(g.is_kv_shared) for g in geo], "has_kv_proj": [int(g.has_kv_proj) for g in geo]}
+    return {column: [int(getattr(g, attr)) for g in geo] for column, attr in _NATIVE_COLUMNS}
 
 
 cpp_layer_arrays = native_layer_arrays          # the reference's name for the same table
