@@ -216,6 +216,7 @@ def register() -> bool:
     from . import fake_ops, handle_ops
     fake_ops.register(lib)
     handle_ops.register(lib)
+    fake_ops.register_handle_families(lib)
     _LIB = lib
     return True
 

@@ -258,6 +258,56 @@ def test_standalone_ops_propagate_shapes_on_meta_and_fake_tensors():
     assert y.shape == (7, 16) and y.device.type == "cuda" and o.shape == q.shape
 
 
+def test_handle_forward_ops_propagate_shapes_from_the_handle_config():
+    """A handle's configuration is host data, so ``*_forward`` can be shape-traced with fake tensors; the grid-driven
+    towers, whose length depends on tensor values, refuse instead of guessing."""
+    import json
+    import logging
+    import torch
+    import rhinoforge_b200  # noqa: F401
+    from rhinoforge_b200.runtime.errors import RPUBackendError
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    ops = torch.ops.rpu
+    made = {"causal_decoder": ops.causal_decoder_create(json.dumps({"vocab_size": 1000, "hidden_size": 64,
+                                                                   "torch_dtype": "bfloat16"})),
+            "siglip": ops.siglip_create(json.dumps({"hidden_size": 96, "patch_size": 14, "image_size": 224})),
+            "hyvit2": ops.hyvit2_create(json.dumps({"hidden_size": 96, "patch_size": 16, "image_size": 64,
+                                                    "rpu_projector_dim": 40})),
+            "dinov3_vision": ops.dinov3_vision_create(json.dumps({"hidden_size": 64, "patch_size": 16})),
+            "pi05": ops.pi05_create("{}"), "qwen3vl_vision": ops.qwen3vl_vision_create("{}")}
+    try:
+        cu = lambda *s, dtype=torch.float16: torch.empty(*s, device="cuda", dtype=dtype)
+        with FakeTensorMode():
+            logits = ops.causal_decoder_forward(made["causal_decoder"], cu(2, 5, 64, dtype=torch.bfloat16), [], [], None, 0,
+                                                True, None, None, None, None)
+            sig, = ops.siglip_forward(made["siglip"], cu(3, 3, 224, 224))
+            hy, = ops.hyvit2_forward(made["hyvit2"], cu(1, 3, 64, 64))
+            tokens, cls = ops.dinov3_vision_forward(made["dinov3_vision"], cu(1, 3, 224, 224))
+            img, msk, tok = cu(2, 3, 3, 224, 224), cu(2, 3), cu(2, 48, dtype=torch.int64)
+            act = ops.pi05_forward(made["pi05"], img, msk, tok, cu(2, 48), cu(2, 50, 32, dtype=torch.float32))
+            lens = ops.gemma_forward(made["pi05"], img, msk, tok, cu(2, 48))
+            step = ops.pi05_denoise_loop_forward(made["pi05"], None, cu(2, 50, 32), 10)
+            logging.disable(logging.ERROR)                           # torch logs the refusal before re-raising it
+            try:
+                with pytest.raises(RPUBackendError, match="data-dependent output length"):
+                    ops.qwen3vl_vision_forward(made["qwen3vl_vision"], cu(16, 1536), cu(1, 3, dtype=torch.int64))
+            finally:
+                logging.disable(logging.NOTSET)
+        assert (tuple(logits.shape), logits.dtype, logits.device.type) == ((2, 1000), torch.bfloat16, "cuda")
+        assert tuple(sig.shape) == (3, 256, 96) and tuple(hy.shape) == (1, 16, 40)
+        assert tuple(tokens.shape) == (1, 1 + 4 + 196, 64) and tuple(cls.shape) == (1, 64)
+        assert tuple(act.shape) == (2, 50, 32) and act.dtype == torch.float16 and tuple(step.shape) == (2, 50, 32)
+        assert tuple(lens.shape) == (2,) and lens.dtype == torch.int32
+        on_meta = ops.causal_decoder_forward(made["causal_decoder"], torch.empty(5, 64, device="meta"), [], [], None, 0, True,
+                                             None, None, None, None)
+        assert tuple(on_meta.shape) == (1, 1000)
+        with pytest.raises(RPUBackendError, match="belongs to family"):
+            ops.siglip_forward(made["pi05"], torch.empty(1, 3, 224, 224, device="meta"))
+    finally:
+        for fam, h in made.items():
+            getattr(ops, fam + "_destroy")(h)
+
+
 def test_handle_ops_build_model_configs_from_json():
     """The JSON a ``*_create`` op receives becomes the runtime's config object: nested Pi0.5 geometry, dtype names."""
     import torch
