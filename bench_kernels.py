@@ -132,23 +132,9 @@ def bench_gemm(m, n, k, *, dual=False, packed=False, int8=False, dtype=torch.flo
 
 def _plan(m, n, k, dual, packed, int8, dtype, splits):
     """The launch plan the library picks for this shape (swap-AB, tile width, splits, stages, grid, shared memory)."""
-    import ctypes as C
-    from rhinoforge_b200 import _native as N
+    from rhinoforge_b200.ops.kernels import gemm_plan
     try:
-        g = N.RfGemm()
-        g.M, g.N, g.K, g.dtype, g.force_swap, g.force_splits = m, n, k, 0 if dtype == torch.float16 else 1, -1, splits
-        g.w_packed = int(packed)
-        g.x = g.w = g.out = 4096
-        g.ldx, g.ldw, g.ldo = k, k, n
-        if dual:
-            g.dual_offset, g.act = n, 1
-        if int8:
-            g.w_int8, g.scale = 1, 4096
-        out = (C.c_int32 * 10)()
-        if N.lib().rf_gemm_plan_info(C.byref(g), out) != 0:
-            return None
-        keys = ("swap", "bn", "splits", "stages", "grid_x", "grid_y", "smem", "k_blocks", "persistent", "two_shot")
-        return dict(zip(keys, (int(v) for v in out)))
+        return gemm_plan(m, n, k, dtype=dtype, dual=dual, packed=packed, int8=int8, force_splits=splits)
     except Exception:  # noqa: BLE001  (diagnostic only)
         return None
 

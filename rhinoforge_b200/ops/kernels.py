@@ -49,6 +49,31 @@ def _splitk_scratch(device: torch.device, ws_bytes: int, sems: int):
     return ws, sem
 
 
+GEMM_PLAN_KEYS = ("swap", "bn", "splits", "stages", "grid_x", "grid_y", "smem", "k_blocks", "persistent", "two_shot")
+
+
+def gemm_plan(M: int, N_out: int, K: int, *, dtype: torch.dtype = torch.float16, dual: bool = False, packed: bool = True,
+              int8: bool = False, force_splits: int = 0) -> Optional[dict]:
+    """The launch plan the library would pick for ``[M, K] x [N_out, K]^T`` - swap-AB, tile width, K splits, ring stages,
+    grid, shared memory, persistent / two-shot form.  A host-side query (no device, no launch); ``None`` when the native
+    library is not built."""
+    if not N.available():
+        return None
+    g = N.RfGemm()
+    g.M, g.N, g.K, g.dtype, g.force_swap, g.force_splits = M, N_out, K, 0 if dtype == torch.float16 else 1, -1, force_splits
+    g.w_packed = int(packed)
+    g.x = g.w = g.out = 4096                                  # placeholders: the planner checks alignment only
+    g.ldx, g.ldw, g.ldo = K, K, N_out
+    if dual:
+        g.dual_offset, g.act = N_out, 1
+    if int8:
+        g.w_int8, g.scale = 1, 4096
+    out = (C.c_int32 * len(GEMM_PLAN_KEYS))()
+    if N.lib().rf_gemm_plan_info(C.byref(g), out) != 0:
+        return None
+    return dict(zip(GEMM_PLAN_KEYS, (int(v) for v in out)))
+
+
 def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
          bias: Optional[torch.Tensor] = None, scale: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,

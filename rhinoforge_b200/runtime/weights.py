@@ -9,7 +9,7 @@ swizzled shared-memory image, loaded by one bulk copy per block.
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, Tuple
+from typing import Any, Dict, Iterable, Sequence, Tuple
 
 import torch
 
@@ -87,5 +87,55 @@ def load_rpu_model(path: str) -> dict:
     return art
 
 
+_STATUS = {PARTITION_ROW: "row", PARTITION_COL: "col", PARTITION_HOST: "fallback"}
+
+
+def check_model_rpu_compatible(model: torch.nn.Module, *, tp_degrees: Sequence[int] = (1, 2, 4, 8),
+                               decode_rows: int = 64) -> Dict[str, Dict[str, Any]]:
+    """What would happen to each ``nn.Linear`` of ``model`` on the accelerator, without touching a weight.
+
+    Per module name: ``in_features``, ``out_features``, ``partition`` / ``status`` at the widest tensor-parallel group
+    (``row`` | ``col`` | ``fallback`` - the reference's report, ``python/rpu_backend/runtime/weights.py:654-680``), plus
+    ``tp`` - the widest group in ``tp_degrees`` whose shards stay 16-byte aligned - ``shard`` (the ``(N, K)`` one rank
+    holds at that width), ``tma_ok`` (K rows start on 16-byte boundaries, the condition for tensor-map loads) and, when
+    the native library is built, ``decode_plan``: the GEMM launch plan for ``decode_rows`` tokens on that shard."""
+    from ..ops.kernels import gemm_plan
+    report: Dict[str, Dict[str, Any]] = {}
+    for name, mod in model.named_modules():
+        if not isinstance(mod, torch.nn.Linear):
+            continue
+        K, N = mod.in_features, mod.out_features
+        width = mod.weight.element_size() if mod.weight.is_floating_point() else 2
+        widest = get_linear_partition(K, N, width, max(tp_degrees), name)
+        fit = 1
+        for degree in sorted(tp_degrees):
+            if get_linear_partition(K, N, width, degree, name) != PARTITION_HOST:
+                fit = degree
+        part = get_linear_partition(K, N, width, fit, name)
+        shard = (N // fit, K) if part == PARTITION_COL else (N, K // fit) if part == PARTITION_ROW else (N, K)
+        row = {"in_features": K, "out_features": N, "partition": widest, "status": _STATUS[widest], "tp": fit,
+               "shard": shard, "tma_ok": (shard[1] * width) % 16 == 0}
+        if row["tma_ok"]:
+            plan = gemm_plan(decode_rows, shard[0], shard[1])
+            if plan is not None:
+                row["decode_plan"] = plan
+        report[name] = row
+    return report
+
+
+def print_rpu_compatibility_report(model: torch.nn.Module, **kwargs: Any) -> None:
+    """One summary line through the runtime logger (level INFO), then one line per Linear that cannot be accelerated."""
+    import logging
+    log = logging.getLogger("rpu_backend")
+    info = check_model_rpu_compatible(model, **kwargs)
+    count = lambda status: sum(1 for r in info.values() if r["status"] == status)
+    log.info("Compatibility: %d Linear layers (accelerated: %d, col: %d, row: %d, fallback: %d)", len(info),
+             len(info) - count("fallback"), count("col"), count("row"), count("fallback"))
+    for name, r in info.items():
+        if r["status"] == "fallback" or not r["tma_ok"]:
+            log.info("  %s [%d x %d]: %s", name, r["out_features"], r["in_features"],
+                     "no aligned tensor-parallel split" if r["tma_ok"] else "K rows are not 16-byte aligned")
+
+
 __all__ = ["ROW_PARTITION_NAMES", "NUM_CORES", "get_linear_partition", "shard_linear", "swizzle_linear", "partition_plan",
-           "convert_model_for_rpu", "load_rpu_model"]
+           "convert_model_for_rpu", "load_rpu_model", "check_model_rpu_compatible", "print_rpu_compatibility_report"]

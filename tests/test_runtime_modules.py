@@ -632,3 +632,49 @@ def test_adapter_template_refuses_until_filled_then_behaves_like_a_family(monkey
     monkeypatch.setattr(registry, "ADAPTERS", dict(registry.ADAPTERS))
     register(TinyAdapter)
     assert registry.get_adapter("TinyForCausalLM") is TinyAdapter
+
+
+# ----------------------------------------------------------------------------- compatibility report
+def test_compatibility_report_classifies_linears_and_plans_their_decode_gemm(caplog):
+    import logging
+    import torch.nn as nn
+    from rhinoforge_b200 import _native
+    from rhinoforge_b200.runtime.weights import check_model_rpu_compatible, print_rpu_compatibility_report
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj = nn.Linear(4096, 4096, bias=False)
+            self.o_proj = nn.Linear(4096, 4096, bias=False)
+            self.gate = nn.Linear(4096, 12288, bias=False)
+            self.head = nn.Linear(100, 6, bias=False)            # 6 outputs split over 2 ranks at most
+            self.odd = nn.Linear(37, 5, bias=False)              # splits nowhere; 74-byte rows are not TMA-aligned
+
+    with torch.device("meta"):
+        model = Block()
+    info = check_model_rpu_compatible(model)
+    assert (info["q_proj"]["status"], info["o_proj"]["status"], info["gate"]["status"]) == ("col", "row", "col")
+    assert info["q_proj"]["tp"] == 8 and info["q_proj"]["shard"] == (512, 4096)
+    assert info["o_proj"]["shard"] == (4096, 512) and info["gate"]["shard"] == (1536, 4096)
+    assert info["head"]["status"] == "fallback" and info["head"]["tp"] == 2 and info["head"]["shard"] == (3, 100)
+    assert info["odd"]["status"] == "fallback" and info["odd"]["tp"] == 1 and not info["odd"]["tma_ok"]
+    assert "decode_plan" not in info["odd"]
+    if _native.available():
+        plan = info["o_proj"]["decode_plan"]                      # the tensor-parallel o_proj shard: short K, split fully
+        assert plan["swap"] == 1 and plan["k_blocks"] == 8 and plan["splits"] == 8
+        assert info["q_proj"]["decode_plan"]["swap"] == 1
+    one = check_model_rpu_compatible(model, tp_degrees=(1,))
+    assert one["head"]["status"] == "col" and one["head"]["shard"] == (6, 100)
+    logger = logging.getLogger("rpu_backend")
+    old_level, old_propagate = logger.level, logger.propagate
+    logger.setLevel(logging.INFO)
+    logger.propagate = True
+    try:
+        with caplog.at_level(logging.INFO, logger="rpu_backend"):
+            print_rpu_compatibility_report(model)
+    finally:
+        logger.setLevel(old_level)
+        logger.propagate = old_propagate
+    text = caplog.text
+    assert "5 Linear layers (accelerated: 3, col: 2, row: 1, fallback: 2)" in text
+    assert "odd [5 x 37]: K rows are not 16-byte aligned" in text and "head [6 x 100]: no aligned" in text
