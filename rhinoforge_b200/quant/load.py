@@ -37,6 +37,51 @@ def is_w4a16_config(config) -> bool:
     return isinstance(qc, dict) and qc.get("method") == "w4a16"
 
 
+# The one image-text profile admitted in W8A16: Qwen3-VL-32B with the decoder projections quantised, the lm_head, the
+# embeddings and the whole vision tower left in 16 bits (reference: ``python/rpu_backend/quant/load.py:29-103``).
+QWEN3_VL_32B_W8A16 = {
+    "top": {"model_type": "qwen3_vl", "tie_word_embeddings": False},
+    "quant_config": {"method": W8A16_METHOD, "mode": "per_channel_symmetric", "qaxis": 0, "skip_modules": ["lm_head"],
+                     "quantized_lm_head": False, "quantized_embed_tokens": False, "lm_head_untied": False,
+                     "embed_tokens_untied": False},
+    "text_config": {"model_type": "qwen3_vl_text", "hidden_size": 5120, "intermediate_size": 25600,
+                    "num_hidden_layers": 64, "num_attention_heads": 64, "num_key_value_heads": 8, "head_dim": 128,
+                    "vocab_size": 151936, "hidden_act": "silu", "rms_norm_eps": 1e-6},
+    "vision_config": {"model_type": "qwen3_vl", "hidden_size": 1152, "intermediate_size": 4304, "depth": 27,
+                      "num_heads": 16, "patch_size": 16, "temporal_patch_size": 2, "spatial_merge_size": 2,
+                      "deepstack_visual_indexes": [8, 16, 24], "out_hidden_size": 5120,
+                      "hidden_act": "gelu_pytorch_tanh"},
+}
+
+
+def is_qwen3_vl_32b_w8a16_config(config) -> bool:
+    """True only for the exact profile above; anything missing, extra-quantised or differently sized is False."""
+    read = (lambda o, k: o.get(k)) if isinstance(config, dict) else (lambda o, k: getattr(o, k, None))
+
+    def matches(obj, want: dict) -> bool:
+        if obj is None:
+            return False
+        get = (lambda k: obj.get(k)) if isinstance(obj, dict) else (lambda k: getattr(obj, k, None))
+        for key, value in want.items():
+            got = get(key)
+            if isinstance(value, float):
+                if not isinstance(got, (int, float)) or abs(float(got) - value) > 1e-12:
+                    return False
+            elif isinstance(value, list):
+                if got is None or list(got) != value:
+                    return False
+            elif got != value or isinstance(got, bool) != isinstance(value, bool):
+                return False
+        return True
+
+    arch = read(config, "architectures")
+    return (arch is not None and tuple(arch) == ("Qwen3VLForConditionalGeneration",)
+            and matches(config, QWEN3_VL_32B_W8A16["top"])
+            and read(config, "quant_config") == QWEN3_VL_32B_W8A16["quant_config"]
+            and matches(read(config, "text_config"), QWEN3_VL_32B_W8A16["text_config"])
+            and matches(read(config, "vision_config"), QWEN3_VL_32B_W8A16["vision_config"]))
+
+
 def w4a16_tensor_getter(ckpt_dir: str, config) -> Callable[[str], torch.Tensor]:
     """``get(name)`` over a packed W4A16 checkpoint (``quant/convert_qwen3_w4a16.py``): a packed projection
     (``uint8 [out, in/2]`` with group-wise fp16 scales) is dequantised to fp16 when it is read, so the 16-bit kernels run

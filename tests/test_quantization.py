@@ -316,3 +316,112 @@ def test_wall_oss_checkpoint_pair_validation(tmp_path):
     with pytest.raises(ValueError, match="group_size=32"):
         validate_rtc_w4_checkpoint_pair(tmp_path / "w4_g64", src)
     assert validate_checkpoint_pair(tmp_path / "w4_plain", src, expected_method="w4a16", label="W4A16")[2]["group_size"] == 32
+
+
+def test_w8a16_inventory_is_checked_from_headers_alone(tmp_path):
+    """The real converter's output passes; each way of being almost right is named."""
+    from safetensors.torch import load_file, save_file
+    from rpu_backend.quant.convert_qwen3 import convert_checkpoint
+    from rpu_backend.quant.inventory import inspect_w8a16_checkpoint, is_decoder_projection
+    cfg, sd = _tiny_ckpt(tmp_path / "src", tie=False)
+    convert_checkpoint(tmp_path / "src", tmp_path / "w8", ["lm_head"])
+    plan = inspect_w8a16_checkpoint(tmp_path / "w8")
+    assert len(plan["int8"]) == len(plan["scales"]) == 7 * cfg.num_layers and not plan["unquantized"]
+    assert len(plan["layers"]) == cfg.num_layers and "model.embed_tokens.weight" in plan["nondecoder"]
+    assert all(any(n.endswith("q_proj.weight_scale") for n in names) for names in plan["layers"])
+    assert set(plan["tensor_shards"].values()) == {"model.safetensors"} and plan["bytes"] > 0
+    assert is_decoder_projection("model.language_model.layers.3.mlp.up_proj.weight")
+    assert not is_decoder_projection("model.visual.blocks.3.mlp.up_proj.weight")
+    assert not is_decoder_projection("visual.layers.3.self_attn.q_proj.weight") and not is_decoder_projection("lm_head.weight")
+
+    good = load_file(str(tmp_path / "w8" / "model.safetensors"))
+    q = "model.layers.1.self_attn.k_proj.weight"
+
+    def variant(name, edit, index=None):
+        d = tmp_path / name
+        d.mkdir()
+        t = dict(good)
+        edit(t)
+        save_file({k: v.contiguous() for k, v in t.items()}, str(d / "model.safetensors"), metadata={"format": "pt"})
+        if index is not None:
+            (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": index(t)}))
+        return d
+
+    d = variant("float_proj", lambda t: (t.__setitem__(q, sd[q]), t.pop(q + "_scale")))
+    with pytest.raises(TypeError, match="k_proj.weight' must be int8, got F16"):
+        inspect_w8a16_checkpoint(d)
+    # even when floating projections are tolerated, layers that differ in what they quantise are refused
+    with pytest.raises(KeyError, match="different numbers of int8"):
+        inspect_w8a16_checkpoint(d, require_all=False)
+    d = variant("all_float", lambda t: [(t.__setitem__(n, t[n].half()), t.pop(n + "_scale")) for n in list(t)
+                                        if n.endswith("proj.weight")])
+    assert len(inspect_w8a16_checkpoint(d, require_all=False)["unquantized"]) == 7 * cfg.num_layers
+    with pytest.raises(KeyError, match="has no 'model.layers.1.self_attn.k_proj.weight_scale'"):
+        inspect_w8a16_checkpoint(variant("no_scale", lambda t: t.pop(q + "_scale")))
+    with pytest.raises(KeyError, match="unexpected scale 'model.norm.weight_scale'"):
+        inspect_w8a16_checkpoint(variant("stray_scale", lambda t: t.__setitem__("model.norm.weight_scale", torch.ones(4).half())))
+    with pytest.raises(TypeError, match="must be fp16, got F32"):
+        inspect_w8a16_checkpoint(variant("f32_scale", lambda t: t.__setitem__(q + "_scale", t[q + "_scale"].float())))
+    with pytest.raises(ValueError, match="has shape"):
+        inspect_w8a16_checkpoint(variant("short_scale", lambda t: t.__setitem__(q + "_scale", t[q + "_scale"][:-1])))
+    with pytest.raises(TypeError, match="not a decoder projection"):
+        inspect_w8a16_checkpoint(variant("int8_embed", lambda t: (t.__setitem__("model.embed_tokens.weight", t[q].clone()),
+                                                                   t.__setitem__("model.embed_tokens.weight_scale", t[q + "_scale"].clone()))))
+    with pytest.raises(TypeError, match="must be floating, got I64"):
+        inspect_w8a16_checkpoint(variant("int_buffer", lambda t: t.__setitem__("model.position_ids", torch.arange(4))))
+    d = variant("int_buffer_ok", lambda t: t.__setitem__("model.position_ids", torch.arange(4)))
+    assert "model.position_ids" in inspect_w8a16_checkpoint(d, allow_integer=["model.position_ids"])["nondecoder"]
+    with pytest.raises(KeyError, match="only in index \\['ghost.weight'\\]"):
+        inspect_w8a16_checkpoint(variant("ghost", lambda t: None,
+                                         index=lambda t: {**{n: "model.safetensors" for n in t}, "ghost.weight": "model.safetensors"}))
+    lm = variant("int8_head", lambda t: (t.__setitem__("lm_head.weight", t[q].clone()),
+                                         t.__setitem__("lm_head.weight_scale", t[q + "_scale"].clone())),
+                 index=lambda t: {n: "model.safetensors" for n in t})
+    with pytest.raises(TypeError, match="not a decoder projection"):
+        inspect_w8a16_checkpoint(lm)
+    assert "lm_head.weight" in inspect_w8a16_checkpoint(lm, extra_int8=["lm_head.weight"])["int8"]
+
+    # two shards: a duplicate tensor and an index that points to the wrong shard
+    two = tmp_path / "two"
+    two.mkdir()
+    names = sorted(good)
+    a, b = {n: good[n] for n in names[::2]}, {n: good[n] for n in names[1::2]}
+    save_file(a, str(two / "model-00001-of-00002.safetensors"), metadata={"format": "pt"})
+    save_file(b, str(two / "model-00002-of-00002.safetensors"), metadata={"format": "pt"})
+    wm = {**{n: "model-00001-of-00002.safetensors" for n in a}, **{n: "model-00002-of-00002.safetensors" for n in b}}
+    (two / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wm}))
+    assert len(set(inspect_w8a16_checkpoint(two)["tensor_shards"].values())) == 2
+    wrong = dict(wm)
+    wrong[names[0]] = "model-00002-of-00002.safetensors"
+    (two / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wrong}))
+    with pytest.raises(KeyError, match="wrong shard"):
+        inspect_w8a16_checkpoint(two)
+    (two / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wm}))
+    save_file({**b, names[0]: good[names[0]]}, str(two / "model-00002-of-00002.safetensors"), metadata={"format": "pt"})
+    with pytest.raises(KeyError, match="appears more than once"):
+        inspect_w8a16_checkpoint(two)
+
+
+def test_qwen3_vl_32b_w8a16_profile_predicate():
+    import copy
+    from types import SimpleNamespace
+    from rpu_backend.quant.load import QWEN3_VL_32B_W8A16 as P, is_qwen3_vl_32b_w8a16_config
+    base = {"architectures": ["Qwen3VLForConditionalGeneration"], **P["top"], "quant_config": dict(P["quant_config"]),
+            "text_config": dict(P["text_config"]), "vision_config": dict(P["vision_config"])}
+    assert is_qwen3_vl_32b_w8a16_config(base)
+    as_object = SimpleNamespace(**{**base, "text_config": SimpleNamespace(**base["text_config"]),
+                                   "vision_config": SimpleNamespace(**{**base["vision_config"],
+                                                                       "deepstack_visual_indexes": (8, 16, 24)})})
+    assert is_qwen3_vl_32b_w8a16_config(as_object)
+    for path, value in ((("text_config", "num_hidden_layers"), 36), (("vision_config", "depth"), 24),
+                        (("quant_config", "quantized_lm_head"), True), (("tie_word_embeddings",), True),
+                        (("architectures",), ["Qwen3VLMoeForConditionalGeneration"]), (("text_config",), None),
+                        (("vision_config", "deepstack_visual_indexes"), [8, 16]), (("text_config", "rms_norm_eps"), 1e-5),
+                        (("quant_config", "extra"), 1)):
+        c = copy.deepcopy(base)
+        target = c
+        for k in path[:-1]:
+            target = target[k]
+        target[path[-1]] = value
+        assert not is_qwen3_vl_32b_w8a16_config(c), path
+    assert not is_qwen3_vl_32b_w8a16_config({}) and not is_qwen3_vl_32b_w8a16_config(SimpleNamespace())
