@@ -25,6 +25,7 @@ from pathlib import Path
 from typing import Any, Dict, Iterable, List, Sequence, Tuple
 
 from .convert_qwen3 import QUANT_PROJ_SUFFIXES, scale_name
+from .load import _shards
 
 FLOAT_DTYPES = frozenset({"F64", "F32", "F16", "BF16"})
 ELEMENT_BYTES = {"F64": 8, "F32": 4, "F16": 2, "BF16": 2, "I8": 1, "U8": 1, "I32": 4, "I64": 8, "BOOL": 1, "I16": 2}
@@ -60,7 +61,6 @@ def inspect_w8a16_checkpoint(ckpt_dir, *, suffixes: Sequence[str] = QUANT_PROJ_S
 
     ``extra_int8`` names tensors outside the decoder layers that are quantised as well (an untied ``lm_head.weight``).
     Raises ``FileNotFoundError`` / ``KeyError`` / ``TypeError`` / ``ValueError`` with the offending tensor names."""
-    from .load import _shards
     root = Path(ckpt_dir)
     meta = _headers(_shards(root))
     extra = set(extra_int8)
