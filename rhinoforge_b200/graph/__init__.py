@@ -1,4 +1,5 @@
-"""Graph namespace: signature-keyed CUDA-graph caches and the manual capture helper."""
+"""Graph namespace: signature-keyed CUDA-graph caches, the manual capture helper, the install-completeness guard and
+(imported on demand: ``graph.dynamo_backend``, ``graph.dynamo_partitioner``) the TorchDynamo front-end."""
 from ._runtime import (GraphCache, GraphHandle, GraphSignature, backend_loaded, configure_backend,  # noqa: F401
                        get_default_graph_cache, install_torch_namespace, reset_graph_cache)
 

@@ -678,3 +678,75 @@ def test_compatibility_report_classifies_linears_and_plans_their_decode_gemm(cap
     text = caplog.text
     assert "5 Linear layers (accelerated: 3, col: 2, row: 1, fallback: 2)" in text
     assert "odd [5 x 37]: K rows are not 16-byte aligned" in text and "head [6 x 100]: no aligned" in text
+
+
+# ----------------------------------------------------------------------------- Dynamo front-end
+def test_partitioner_cuts_at_host_nodes_and_preserves_results():
+    import torch.fx
+    from rhinoforge_b200.graph.dynamo_partitioner import default_is_capturable, partition_for_capture
+
+    class M(torch.nn.Module):
+        def forward(self, x, w):
+            y = torch.relu(x @ w)
+            rows = y.sum(1).nonzero()                     # data-dependent shape: the host has to look
+            z = y * 2 + rows.shape[0]
+            return z, y.to("cpu"), z.to(torch.float64)    # a host copy is cut out, a dtype cast is not
+
+    gm = torch.fx.symbolic_trace(M())
+    parts = partition_for_capture(gm)
+    assert [s.capturable for s in parts.segments] == [True, False, True, False, True]
+    assert [s.n_nodes for s in parts.segments if not s.capturable] == [1, 1]
+    x, w = torch.randn(4, 8), torch.randn(8, 8)
+    got, want = parts.run((x, w)), M()(x, w)
+    assert all(torch.equal(a, b) for a, b in zip(got, want))
+    seen = []
+    parts.run((x, w), lambda i, seg, fn, args: (seen.append((i, seg.capturable)), fn(*args))[1])
+    assert seen == [(0, True), (1, False), (2, True), (3, False), (4, True)]
+    names = {n.name: default_is_capturable(n) for n in gm.graph.nodes}
+    assert not names["nonzero"] and names["relu"] and not names["to"] and names["to_1"]
+
+    class Pure(torch.nn.Module):
+        def forward(self, x):
+            return torch.tanh(x) * 3
+    one = partition_for_capture(torch.fx.symbolic_trace(Pure()))
+    assert [s.capturable for s in one.segments] == [True] and torch.equal(one.run((x,)), torch.tanh(x) * 3)
+    everything_host = partition_for_capture(torch.fx.symbolic_trace(Pure()), lambda n: False)
+    assert [s.capturable for s in everything_host.segments] == [False]
+
+
+def test_dynamo_backend_records_once_replays_after_and_bounds_its_table():
+    from rhinoforge_b200.graph.dynamo_backend import RpuDynamoBackend, dynamo_backend
+    from rhinoforge_b200.graph.lazy_init_guard import UninitializedLazyStateError, mark_install_checked
+    torch._dynamo.reset()
+    be = RpuDynamoBackend(max_entries=1)
+    w = torch.randn(8, 8)
+
+    @torch.compile(backend=be)
+    def f(x):
+        return torch.relu(x @ w) + 1
+
+    x = torch.randn(4, 8)
+    for _ in range(3):
+        out = f(x)
+    assert torch.allclose(out, torch.relu(x @ w) + 1)
+    s = be.stats()
+    assert (s["graphs"], s["records"], s["replays"], s["evictions"], s["entries"]) == (1, 1, 2, 0, 1)
+    f(torch.randn(6, 8))                                    # another shape: re-trace, new signature, the old entry goes
+    s = be.stats()
+    assert s["records"] == 2 and s["evictions"] == 1 and s["entries"] == 1
+    be.clear()
+    assert be.stats()["entries"] == 0
+    with pytest.raises(ValueError, match="max_entries"):
+        RpuDynamoBackend(max_entries=0)
+    assert isinstance(dynamo_backend, RpuDynamoBackend)
+
+    # a module that still creates state in forward is refused when its graph reaches the backend
+    class Lazy(torch.nn.Module):
+        def forward(self, x):
+            return x + 1
+    lazy = mark_install_checked(Lazy(), ("_rpu_table",))
+    holder = torch.nn.Module()
+    holder.child = lazy
+    with pytest.raises(UninitializedLazyStateError):
+        be(holder, ())
+    torch._dynamo.reset()
