@@ -29,13 +29,17 @@ def configure_torch_rpu(torch, mod: types.ModuleType):
     mod.get_device_name = lambda i=None: torch.cuda.get_device_name(i) if torch.cuda.is_available() else "cpu"
     for name in ("set_caching_allocator", "get_caching_allocator", "empty_cache", "memory_stats",
                  "reset_peak_memory_stats", "set_ddr_flush", "set_ddr_flush_force", "set_cross_layer_batch_size",
-                 "set_cross_layer_batch_prefill", "get_cross_layer_batch_size", "shutdown"):
+                 "set_cross_layer_batch_prefill", "get_cross_layer_batch_size", "shutdown", "get_ddr_flush",
+                 "get_ddr_flush_force", "get_amp_supported_dtype", "is_autocast_available", "get_spm_mode",
+                 "get_allreduce_twostage", "get_linear_acc32", "get_memory_stats", "reset_accumulated_memory_stats",
+                 "get_cross_layer_batch_prefill", "spm_alloc_reset_temporary", "reset_temporary_spm", "reset_all_spm"):
         setattr(mod, name, getattr(control, name))
     for name in ("set_debug_level", "get_debug_level"):
         setattr(mod, name, getattr(log, name))
     for name in ("set_debug", "get_debug", "set_profile", "get_profile", "reset_profile_accumulators",
                  "set_debug_export", "get_debug_export", "get_debug_tensor", "set_spm_debug", "spm_alloc_dump",
-                 "set_hw_perf_trace", "hw_perf_trace", "profile_counters"):
+                 "set_hw_perf_trace", "hw_perf_trace", "profile_counters", "get_hw_perf_trace", "list_debug_tensors",
+                 "clear_debug_tensors", "get_spm_debug"):
         setattr(mod, name, getattr(debug, name))
     return control
 

@@ -124,8 +124,78 @@ def set_ddr_flush(enabled: bool) -> None:
     _flush = bool(enabled)
 
 
+def get_ddr_flush() -> bool:
+    return _flush
+
+
 def set_ddr_flush_force(enabled: bool) -> None:
     set_ddr_flush(enabled)
+
+
+def get_ddr_flush_force() -> bool:
+    """Always true in effect: every device-to-host read goes through a stream synchronisation."""
+    return True
+
+
+def is_available() -> bool:
+    """A CUDA device is visible and the native kernel library is built."""
+    import torch
+    from .. import _native
+    return bool(torch.cuda.is_available()) and _native.available()
+
+
+def get_amp_supported_dtype() -> list:
+    """Compute dtypes of the kernels (accumulation is fp32 in tensor memory either way)."""
+    import torch
+    return [torch.float16, torch.bfloat16]
+
+
+def is_autocast_available() -> bool:
+    return True
+
+
+def get_spm_mode() -> bool:
+    """There is no scratch-pad mode to switch: operators place their tiles in shared / tensor memory themselves."""
+    return False
+
+
+def get_allreduce_twostage() -> bool:
+    """The fused tensor-parallel all-reduce has a two-shot (reduce-scatter + all-gather) form, which the GEMM picks by
+    itself for outputs above 256 rows; there is no process-wide switch, so this reports that the form is available."""
+    return True
+
+
+def get_linear_acc32() -> bool:
+    """Linear layers always accumulate in fp32 (tensor-memory accumulators)."""
+    return True
+
+
+def get_memory_stats() -> dict:
+    return memory_stats()
+
+
+def reset_accumulated_memory_stats() -> None:
+    import torch
+    if torch.cuda.is_available():
+        torch.cuda.reset_accumulated_memory_stats()
+
+
+def get_cross_layer_batch_prefill() -> int:
+    return _cross_layer_batch
+
+
+def spm_alloc_reset_temporary() -> None:
+    """Release the transient scratch of the stand-alone operators (split-K workspaces)."""
+    import torch
+    torch.ops.rpu.spm_alloc_reset_temporary()
+
+
+reset_temporary_spm = spm_alloc_reset_temporary
+
+
+def reset_all_spm() -> None:
+    import torch
+    torch.ops.rpu.spm_alloc_reset_all()
 
 
 def set_cross_layer_batch_size(n: int) -> None:

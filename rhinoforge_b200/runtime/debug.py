@@ -85,9 +85,22 @@ def get_debug_tensor(name: str):
     return _tensors.get(name)
 
 
+def list_debug_tensors() -> list:
+    """Names of the probe tensors held since export was switched on, in export order."""
+    return list(_tensors)
+
+
+def clear_debug_tensors() -> None:
+    _tensors.clear()
+
+
 def set_spm_debug(enabled: bool) -> None:
     global _spm_debug
     _spm_debug = bool(enabled)
+
+
+def get_spm_debug() -> bool:
+    return _spm_debug
 
 
 def spm_alloc_dump() -> str:
@@ -103,6 +116,12 @@ def set_hw_perf_trace(output_dir: Optional[str], max_dumps: int = 8) -> None:
         _hw["dir"], _hw["max_dumps"], _hw["seq"] = (str(output_dir) if output_dir else None), int(max_dumps), 0
         if output_dir:
             os.makedirs(output_dir, exist_ok=True)
+
+
+def get_hw_perf_trace() -> dict:
+    """``{"dir", "max_dumps", "seq"}`` of the trace configuration in force (``dir`` is None when tracing is off)."""
+    with _lock:
+        return {"dir": _hw.get("dir"), "max_dumps": _hw.get("max_dumps", 0), "seq": _hw.get("seq", 0)}
 
 
 @contextlib.contextmanager

@@ -323,3 +323,50 @@ def test_handle_ops_build_model_configs_from_json():
     assert (d.vlm.hidden, d.expert.hidden, d.horizon) == (2048, 1024, 50)
     assert H._dtype_of({"torch_dtype": "bfloat16"}) == torch.bfloat16 and H._dtype_of({}) == torch.float16
     assert H._dtype_of({"dtype": "torch.float16"}) == torch.float16
+
+
+def test_torch_rpu_controls_and_debug_surface(tmp_path):
+    """Setters are reflected by their getters; fixed properties of the design answer as documented; the probe-tensor
+    store and the trace configuration can be inspected and cleared."""
+    import torch
+    import rhinoforge_b200  # noqa: F401
+    r = torch.rpu
+    assert r.get_ddr_flush() is False
+    r.set_ddr_flush(True)
+    assert r.get_ddr_flush() is True
+    r.set_ddr_flush(False)
+    assert r.get_ddr_flush_force() is True and r.get_spm_mode() is False
+    assert r.get_linear_acc32() is True and r.get_allreduce_twostage() is True and r.is_autocast_available() is True
+    assert r.get_amp_supported_dtype() == [torch.float16, torch.bfloat16]
+    before = r.get_cross_layer_batch_size()
+    r.set_cross_layer_batch_prefill(4)
+    assert r.get_cross_layer_batch_prefill() == r.get_cross_layer_batch_size() == 4
+    r.set_cross_layer_batch_size(before)
+    with pytest.raises(ValueError):
+        r.set_cross_layer_batch_size(-1)
+    assert set(r.get_memory_stats()) == {"allocated_bytes", "reserved_bytes", "peak_allocated_bytes"}
+    assert r.get_memory_stats() == r.memory_stats()
+    r.reset_peak_memory_stats(); r.reset_accumulated_memory_stats()          # no device: no-ops
+    r.reset_temporary_spm(); r.spm_alloc_reset_temporary(); r.reset_all_spm()
+    assert r.is_available() == (torch.cuda.is_available() and rhinoforge_b200._native.available())
+
+    from rhinoforge_b200.runtime import debug
+    r.set_debug_export(True)
+    try:
+        debug.export_debug_tensor("layer0.attn_out", torch.arange(4.0))
+        debug.export_debug_tensor("layer0.mlp_out", torch.ones(2))
+        assert r.list_debug_tensors() == ["layer0.attn_out", "layer0.mlp_out"]
+        assert torch.equal(r.get_debug_tensor("layer0.attn_out"), torch.arange(4.0))
+        r.clear_debug_tensors()
+        assert r.list_debug_tensors() == [] and r.get_debug_tensor("layer0.attn_out") is None
+    finally:
+        r.set_debug_export(False)
+    assert r.get_spm_debug() is False
+    r.set_spm_debug(True)
+    assert r.get_spm_debug() is True
+    r.set_spm_debug(False)
+    assert r.get_hw_perf_trace()["dir"] is None
+    r.set_hw_perf_trace(str(tmp_path / "trace"), 3)
+    assert r.get_hw_perf_trace() == {"dir": str(tmp_path / "trace"), "max_dumps": 3, "seq": 0}
+    r.set_hw_perf_trace(None, 0)
+    assert r.get_hw_perf_trace()["dir"] is None
