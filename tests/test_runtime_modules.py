@@ -750,3 +750,62 @@ def test_dynamo_backend_records_once_replays_after_and_bounds_its_table():
     with pytest.raises(UninitializedLazyStateError):
         be(holder, ())
     torch._dynamo.reset()
+
+
+def test_action_denormalizer_config_constructors_and_unapply(tmp_path):
+    import json
+    import numpy as np
+    from rhinoforge_b200.api.action_denorm import EPS, ActionDenormalizer, ActionGroup
+    stats = {"norm_stats": {"action.arm.position": {"mean": [1.0, 2.0, 3.0], "std": [0.5, 0.5, 2.0]},
+                            "action.gripper": {"min": [0.0], "max": [0.08], "mean": [0.04], "std": [0.01]},
+                            "observation.state.arm.position": {"mean": [0.0] * 3, "std": [1.0] * 3}}}
+    path = tmp_path / "norm.json"
+    path.write_text(json.dumps(stats))
+    train = {"data": {"joints": ["{'arm.position': 3}", {"gripper": 1}],
+                      "norm_type": ["{'arm.position': 'meanstd'}", "{'gripper': 'minmax'}"]}}
+    robot = {"actions": [{"action.arm.position": {"subtract_state": True}}, {"action.gripper": {"subtract_state": False}}]}
+    d = ActionDenormalizer.from_training_config(str(path), train, robot_config=robot)
+    assert [(g.key, g.dim, g.norm_type, g.subtract_state) for g in d.groups] == [
+        ("action.arm.position", 3, "meanstd", True), ("action.gripper", 1, "minmax", False)]
+    assert d.groups[0].state_key == "observation.state.arm.position" and d.real_dim == 4
+    a = torch.tensor([[[0.0, 1.0, -1.0, 0.0, 9.0, 9.0], [2.0, 0.0, 0.0, 5.0, 9.0, 9.0]]])     # [1, H, padded D]
+    state = [10.0, 20.0, 30.0, 99.0]
+    out = d.unapply(a, state)
+    assert out.dtype == torch.float32 and out.shape == (2, 4)
+    want_arm0 = np.array([0.0, 1.0, -1.0]) * (np.array([0.5, 0.5, 2.0]) + EPS) + [1, 2, 3] + np.array(state[:3])
+    assert np.allclose(out[0, :3].numpy(), want_arm0, atol=1e-5)
+    assert abs(float(out[0, 3]) - 0.04) < 1e-5 and abs(float(out[1, 3]) - 0.08) < 1e-5      # clipped to +1 before scaling
+    with pytest.raises(ValueError, match="no state was provided"):
+        d.unapply(a)
+    with pytest.raises(ValueError, match="state has 2 dims"):
+        d.unapply(a, [1.0, 2.0])
+    with pytest.raises(ValueError, match="non-finite"):
+        d.unapply(torch.tensor([[float("nan"), 0, 0, 0]]), state)
+    with pytest.raises(ValueError, match="non-finite"):
+        d.unapply(a, [float("inf"), 0, 0, 0])
+    with pytest.raises(ValueError, match="expected batch 1"):
+        d.unapply(torch.zeros(2, 3, 4), state)
+    with pytest.raises(ValueError, match="< real_dim 4"):
+        d.unapply(torch.zeros(3, 2), state)
+    absolute = ActionDenormalizer.from_training_config(str(path), train["data"])             # no robot config: absolute
+    assert not any(g.subtract_state for g in absolute.groups)
+    assert np.allclose(absolute.unapply(a)[0, :3].numpy(), want_arm0 - np.array(state[:3]), atol=1e-5)
+    with pytest.raises(ValueError, match=r"missing explicit norm_type entries for action groups \['gripper'\]"):
+        ActionDenormalizer.from_training_config(str(path), {"joints": train["data"]["joints"],
+                                                            "norm_type": ["{'arm.position': 'meanstd'}"]})
+
+    auto = ActionDenormalizer.from_norm_json(str(path), robot_config=robot)
+    assert [(g.key, g.dim, g.norm_type) for g in auto.groups] == [("action.arm.position", 3, "meanstd"),
+                                                                  ("action.gripper", 1, "meanstd")]
+    assert auto.groups[0].subtract_state and auto.groups[1].state_key == "observation.state.gripper"
+    only_state = tmp_path / "state_only.json"
+    only_state.write_text(json.dumps({"observation.state.x": {"mean": [0.0], "std": [1.0]}}))
+    with pytest.raises(ValueError, match="no 'action.\\*' keys"):
+        ActionDenormalizer.from_norm_json(str(only_state))
+    spec = ActionDenormalizer.from_spec(str(path), [ActionGroup("action.gripper", 1, "minmax")])
+    assert abs(float(spec.unapply([[-1.0]])[0, 0])) < 1e-6
+
+    yaml_path = tmp_path / "train.yaml"
+    yaml_path.write_text("data:\n  joints:\n    - \"{'arm.position': 3}\"\n  norm_type:\n    - \"{'arm.position': 'std'}\"\n")
+    from_yaml = ActionDenormalizer.from_training_config(str(path), str(yaml_path))
+    assert from_yaml.groups[0].norm_type == "std" and from_yaml.real_dim == 3
