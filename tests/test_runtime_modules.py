@@ -156,8 +156,8 @@ def test_rotation_6d_decode_roundtrip():
     q = rng.normal(size=(5, 4))
     R = H.quat_xyzw_to_matrix(q)
     assert np.allclose(R @ np.swapaxes(R, -1, -2), np.eye(3), atol=1e-9)
-    d6 = np.concatenate((R[..., 0], R[..., 1]), -1)
-    assert np.allclose(H.rotation_6d_to_matrix(d6), R, atol=1e-9)
+    d6 = np.concatenate((R[..., 0, :], R[..., 1, :]), -1)             # the encoding is the first two ROWS
+    assert np.allclose(H.rotation_6d_to_matrix(d6), R, atol=1e-9) and np.allclose(H.matrix_to_rotation_6d(R), d6)
     q2 = H.matrix_to_quat_xyzw(R)
     assert np.allclose(H.quat_xyzw_to_matrix(q2), R, atol=1e-9)
     start = np.array([0.1, 0.2, 0.3, 0.0, 0.0, 0.0, 1.0])
@@ -165,6 +165,100 @@ def test_rotation_6d_decode_roundtrip():
     poses = H.relative_to_absolute_poses(rel, start)
     assert np.allclose(poses[0], [0.1, 0.2, 0.3, 0, 0, 0, 1, 0.5]) and np.allclose(poses[1, :3], [1.1, 0.2, 0.3])
     assert H.relative_to_dual_arm_poses(np.concatenate((rel, rel), 1), np.concatenate((start, start))).shape == (2, 16)
+    sixteen = np.concatenate((start, [0.0], start + [1.0, 1.0, 1.0, 0, 0, 0, 0], [0.0]))
+    dual = H.relative_to_dual_arm_poses(np.concatenate((rel, rel), 1), sixteen)
+    assert np.allclose(dual[1, :3], [1.1, 0.2, 0.3]) and np.allclose(dual[1, 8:11], [2.1, 1.2, 1.3])
+    with pytest.raises(ValueError, match="16 wide"):
+        H.relative_to_dual_arm_poses(np.concatenate((rel, rel), 1), np.zeros(15))
+
+
+def test_hy_vla_action_decoder_matches_a_scipy_statement_of_the_contract():
+    import numpy as np
+    from scipy.spatial.transform import Rotation as Rot
+    from rhinoforge_b200.api.hy_action_decode import HyVlaActionDecoder, convert_frame, quat_wxyz_to_xyzw, quat_xyzw_to_wxyz
+    rng = np.random.default_rng(3)
+    H = 6
+    stats = {"action_mean": rng.normal(size=(H, 20)) * 0.01, "action_std": rng.uniform(0.5, 1.5, size=(H, 20)),
+             "qpos_mean": rng.normal(size=20) * 0.1, "qpos_std": rng.uniform(0.5, 1.5, size=20)}
+    W = np.array([[0, 1, 0], [-1, 0, 0], [0, 0, 1.0]])
+    P = np.array([[0, 0, 1], [1, 0, 0], [0, 1, 0.0]])
+
+    def unit(q):
+        return q / np.linalg.norm(q)
+    start_wxyz = np.concatenate(([0.3, -0.1, 0.5], unit(rng.normal(size=4)), [0.7],
+                                 [-0.2, 0.4, 0.6], unit(rng.normal(size=4)), [0.2]))
+    act = rng.normal(size=(1, H, 32)) * 0.3
+    for arm in (3, 13):                                               # keep the two encoded rows far from parallel
+        act[0, :, arm:arm + 6] += np.array([3.0, 0, 0, 0, 3.0, 0])
+
+    def by_scipy(umi: bool, grip: bool, drop: bool):
+        rel = act[0, :, :20] * stats["action_std"] + stats["action_mean"]
+        out = np.zeros((H, 16))
+        for a_off, p_off in ((0, 0), (10, 8)):
+            t0 = start_wxyz[p_off:p_off + 3]
+            R0 = Rot.from_quat(start_wxyz[p_off + 3:p_off + 7][[1, 2, 3, 0]]).as_matrix()
+            g0 = start_wxyz[p_off + 7]
+            if umi:
+                t0, R0 = W @ t0, W @ R0 @ P
+            for h in range(H):
+                r1 = rel[h, a_off + 3:a_off + 6]; r2 = rel[h, a_off + 6:a_off + 9]
+                b1 = r1 / np.linalg.norm(r1); b2 = r2 - (b1 @ r2) * b1; b2 /= np.linalg.norm(b2)
+                dR = np.stack((b1, b2, np.cross(b1, b2)))              # rows
+                R, t, g = R0 @ dR, t0 + R0 @ rel[h, a_off:a_off + 3], rel[h, a_off + 9]
+                if umi:
+                    t, R = W.T @ t, W.T @ R @ P.T
+                    if grip:
+                        g = 1.0 - g / 90.0
+                out[h, p_off:p_off + 3] = t
+                out[h, p_off + 3:p_off + 7] = Rot.from_matrix(R).as_quat()[[3, 0, 1, 2]]
+                out[h, p_off + 7] = g
+        return out[1:] if drop else out
+
+    def same_pose(a, b):
+        a, b = a.copy(), b.copy()
+        for s in (3, 11):                                             # q and -q are the same rotation
+            flip = np.sign((a[:, s:s + 4] * b[:, s:s + 4]).sum(-1, keepdims=True))
+            b[:, s:s + 4] *= flip
+        return np.allclose(a, b, atol=1e-9)
+
+    for umi, grip, drop in ((True, False, True), (False, False, False), (True, True, True)):
+        dec = HyVlaActionDecoder.from_norm_stats_mapping(stats, umi_coord_frame=umi, umi_gripper_space=grip, drop_first=drop)
+        got = dec.decode(act, start_wxyz)
+        assert got.shape == ((H - 1) if drop else H, 16) and same_pose(got, by_scipy(umi, grip, drop)), (umi, grip, drop)
+    dec = HyVlaActionDecoder.from_norm_stats_mapping(stats)
+    assert dec.horizon == H and dec.decode(act[0, :3, :20], start_wxyz).shape == (2, 16)
+
+    # state encoding: frame change, rows of the rotation, then (x - mean) / (std + 1e-8)
+    st = dec.encode_state(start_wxyz)
+    assert st.shape == (1, 20)
+    raw = st[0] * (stats["qpos_std"] + 1e-8) + stats["qpos_mean"]
+    Rl = W @ Rot.from_quat(start_wxyz[3:7][[1, 2, 3, 0]]).as_matrix() @ P
+    assert np.allclose(raw[:3], W @ start_wxyz[:3]) and np.allclose(raw[3:9], np.concatenate((Rl[0], Rl[1])), atol=1e-9)
+    assert np.isclose(raw[9], 0.7) and np.isclose(raw[19], 0.2)
+
+    # frame change and quaternion order are invertible
+    p = quat_wxyz_to_xyzw(start_wxyz)[None]
+    back = convert_frame(convert_frame(p, to_umi=True, convert_gripper=True), to_umi=False, convert_gripper=True)
+    assert same_pose(back, p) and np.allclose(quat_xyzw_to_wxyz(p)[0], start_wxyz)
+    assert np.isclose(convert_frame(p, to_umi=True, convert_gripper=True)[0, 7], (1 - 0.7) * 90)
+
+    for bad, exc, msg in ((dict(action_mean=np.zeros((4, 19)), action_std=np.zeros((4, 19))), ValueError, r"\[H, 20\]"),
+                          (dict(action_mean=np.zeros((4, 20)), action_std=np.zeros((5, 20))), ValueError, "differ in shape"),
+                          (dict(action_mean=np.zeros((4, 20))), KeyError, "action_std"),
+                          ({**stats, "action_mean_abs": 1, "action_std_abs": 1}, NotImplementedError, "absolute and relative")):
+        with pytest.raises(exc, match=msg):
+            HyVlaActionDecoder.from_norm_stats_mapping(bad)
+    with pytest.raises(TypeError):
+        HyVlaActionDecoder.from_norm_stats_mapping([1, 2])
+    with pytest.raises(ValueError, match="requires umi_coord_frame"):
+        HyVlaActionDecoder(stats["action_mean"], stats["action_std"], umi_coord_frame=False, umi_gripper_space=True)
+    for bad_act, msg in ((np.zeros((2, H, 20)), "batch 1"), (np.zeros((H + 1, 20)), "exceed"), (np.zeros((H, 19)), "at least 20")):
+        with pytest.raises(ValueError, match=msg):
+            dec.decode(bad_act, start_wxyz)
+    with pytest.raises(ValueError, match="16 entries"):
+        dec.decode(act, start_wxyz[:14])
+    with pytest.raises(ValueError, match="cannot be encoded"):
+        HyVlaActionDecoder(stats["action_mean"], stats["action_std"]).encode_state(start_wxyz)
 
 
 def test_qwen25vl_window_partition_matches_hf_index():
