@@ -903,3 +903,40 @@ def test_action_denormalizer_config_constructors_and_unapply(tmp_path):
     yaml_path.write_text("data:\n  joints:\n    - \"{'arm.position': 3}\"\n  norm_type:\n    - \"{'arm.position': 'std'}\"\n")
     from_yaml = ActionDenormalizer.from_training_config(str(path), str(yaml_path))
     assert from_yaml.groups[0].norm_type == "std" and from_yaml.real_dim == 3
+
+
+def test_mrope_table_builders_match_the_hugging_face_formulations():
+    """Interleaved (Qwen3-VL) and chunked (Qwen2.5-VL) M-RoPE, stated the way the Hugging Face modules compute them."""
+    from rhinoforge_b200.runtime.rope_partial import build_chunked_mrope_cos_sin, build_interleaved_mrope_cos_sin
+    hd, theta, section = 128, 1e6, [24, 20, 20]
+    g = torch.Generator().manual_seed(0)
+    pos = torch.randint(0, 500, (37, 3), generator=g)
+    inv = 1.0 / (theta ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))
+    freqs = pos.t().double()[:, :, None] * inv[None, None, :]                        # [3, seq, half]
+    # Qwen3-VL apply_interleaved_mrope: start from T, overwrite slice(offset, section*3, 3) with H / W
+    inter = freqs[0].clone()
+    for dim, off in ((1, 1), (2, 2)):
+        idx = slice(off, section[dim] * 3, 3)
+        inter[:, idx] = freqs[dim][:, idx]
+    cos, sin = build_interleaved_mrope_cos_sin(pos, head_dim=hd, rope_theta=theta, mrope_section=section)
+    assert cos.dtype == sin.dtype == torch.float16 and cos.shape == (37, 64) and cos.device.type == "cpu"
+    assert torch.equal(cos, inter.cos().half()) and torch.equal(sin, inter.sin().half())
+    # Qwen2.5-VL: split the frequency axis by section, take chunk i from axis i % 3
+    chunks = torch.cat([part[i % 3] for i, part in enumerate(freqs.split(section, dim=-1))], dim=-1)
+    cos_c, sin_c = build_chunked_mrope_cos_sin(pos, head_dim=hd, rope_theta=theta, mrope_section=section)
+    assert torch.equal(cos_c, chunks.cos().half()) and torch.equal(sin_c, chunks.sin().half())
+    assert not torch.equal(cos, cos_c)
+    # partial rotary: tables cover rotary_dim only
+    part, _ = build_interleaved_mrope_cos_sin(pos, head_dim=256, rope_theta=theta, mrope_section=[11, 11, 10], rotary_dim=64)
+    assert part.shape == (37, 32)
+    text_only = torch.arange(9)[:, None].expand(9, 3).contiguous()                   # equal axes: plain 1-D RoPE
+    c1, _ = build_interleaved_mrope_cos_sin(text_only, head_dim=hd, rope_theta=theta, mrope_section=section)
+    assert torch.equal(c1, (torch.arange(9).double()[:, None] * inv[None]).cos().half())
+    for kw, exc in ((dict(mrope_section=[24, 20, 19]), ValueError), (dict(rotary_dim=130), ValueError),
+                    (dict(rotary_dim=63), ValueError), (dict(rope_theta=0.0), ValueError)):
+        with pytest.raises(exc):
+            build_interleaved_mrope_cos_sin(pos, **{**dict(head_dim=hd, rope_theta=theta, mrope_section=section), **kw})
+    with pytest.raises(ValueError, match=r"\[seq, 3\]"):
+        build_chunked_mrope_cos_sin(pos.t(), head_dim=hd, rope_theta=theta, mrope_section=section)
+    with pytest.raises(TypeError, match="integer"):
+        build_chunked_mrope_cos_sin(pos.float(), head_dim=hd, rope_theta=theta, mrope_section=section)
