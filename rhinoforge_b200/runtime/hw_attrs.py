@@ -59,4 +59,105 @@ def guard(cls):
     return cls
 
 
-__all__ = ["PUBLIC", "COLD", "INTERNAL", "classify", "validate_write", "guard"]
+# ---------------------------------------------------------------------------------------------- whole-tree API
+# The same policy applied to an object tree that this package does not own (a Hugging Face module tree an integrator
+# installs by hand): scans before and after the install, then a per-instance stamp that routes later ``_rpu_*`` writes
+# through ``validate_write``.  Reference counterpart: ``python/rpu_backend/runtime/hw_attrs.py:334-472``.
+import weakref
+
+USER_SETTABLE_BEFORE_INSTALL = PUBLIC | frozenset({"_rpu_execution", "_rpu_max_seq_len", "_rpu_chunk_envelope",
+                                                   "_rpu_vlm_chunk_size"})
+
+
+class TreeState:
+    """Shared by every stamped member of one tree: flipping it on the root is seen by all of them."""
+
+    __slots__ = ("first_forward_done", "__weakref__")
+
+    def __init__(self) -> None:
+        self.first_forward_done = False
+
+
+_STATE_OF: "weakref.WeakKeyDictionary[Any, TreeState]" = weakref.WeakKeyDictionary()
+_STAMPED_CLASS: dict = {}
+
+
+def _members(root: Any):
+    walk = getattr(root, "modules", None)
+    return list(walk()) if callable(walk) else [root]
+
+
+def _own_rpu_names(obj: Any):
+    return [n for n in list(vars(obj)) if n.startswith("_rpu_")] if hasattr(obj, "__dict__") else []
+
+
+def validate_preinstall(root: Any) -> None:
+    """Before an install: only names a user may set ahead of time can be present; anything the runtime owns is stale
+    state from an earlier install and is refused."""
+    for m in _members(root):
+        for name in _own_rpu_names(m):
+            if name not in USER_SETTABLE_BEFORE_INSTALL:
+                raise RPUConfigError(f"unexpected attribute {name!r} on {type(m).__name__} before the install; only "
+                                     f"{sorted(USER_SETTABLE_BEFORE_INSTALL)} may be set ahead of it - clear the stale "
+                                     "state or load a fresh model instance")
+
+
+def validate_postinstall(root: Any) -> None:
+    """After an install: every ``_rpu_*`` name in the tree must be a known one (a typo must not silently do nothing)."""
+    for m in _members(root):
+        for name in _own_rpu_names(m):
+            if classify(name) == "unknown":
+                raise RPUConfigError(f"unexpected attribute {name!r} on {type(m).__name__} after the install "
+                                     f"(known: {sorted(PUBLIC | COLD | INTERNAL)})")
+
+
+validate_existing_hw_attrs = validate_postinstall
+
+
+def _stamped(cls: type) -> type:
+    hit = _STAMPED_CLASS.get(cls)
+    if hit is None:
+        def __setattr__(self, name, value, _base=cls):
+            if name.startswith("_rpu_"):
+                st = _STATE_OF.get(self)
+                frozen = bool(st and st.first_forward_done)
+                validate_write(self, name, value, frozen=frozen, internal_ok=not frozen)
+            _base.__setattr__(self, name, value)
+        hit = type(f"Validated_{cls.__name__}", (cls,), {"__setattr__": __setattr__, "__module__": cls.__module__,
+                                                         "_rpu_validated_base": cls})
+        _STAMPED_CLASS[cls] = hit
+    return hit
+
+
+def install_hw_attr_validator(root: Any) -> None:
+    """Stamp every member of the tree (idempotent): later ``_rpu_*`` writes are checked, and after
+    :func:`mark_first_forward_done` cold names cannot change and runtime-owned names cannot be written.  The tree is
+    scanned before anything is stamped, so a failure leaves it untouched."""
+    validate_postinstall(root)
+    if root in _STATE_OF:
+        return
+    members = _members(root)
+    state = TreeState()
+    for m in members:
+        base = type(m)
+        if getattr(base, "_rpu_validated_base", None) is None:
+            try:
+                m.__class__ = _stamped(base)
+            except TypeError as e:
+                raise RPUConfigError(f"{base.__name__} does not allow the validator to be installed: {e}") from None
+        _STATE_OF[m] = state
+
+
+def mark_first_forward_done(root: Any) -> None:
+    """Start the cold period of a stamped tree; a no-op for objects that were never stamped."""
+    try:
+        st = _STATE_OF.get(root)
+    except TypeError:
+        return
+    if st is not None:
+        st.first_forward_done = True
+
+
+__all__ = ["PUBLIC", "COLD", "INTERNAL", "classify", "validate_write", "guard", "validate_preinstall",
+           "validate_postinstall", "validate_existing_hw_attrs", "install_hw_attr_validator", "mark_first_forward_done",
+           "USER_SETTABLE_BEFORE_INSTALL", "TreeState"]

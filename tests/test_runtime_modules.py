@@ -940,3 +940,57 @@ def test_mrope_table_builders_match_the_hugging_face_formulations():
         build_chunked_mrope_cos_sin(pos.t(), head_dim=hd, rope_theta=theta, mrope_section=section)
     with pytest.raises(TypeError, match="integer"):
         build_chunked_mrope_cos_sin(pos.float(), head_dim=hd, rope_theta=theta, mrope_section=section)
+
+
+def test_hw_attr_validator_over_a_module_tree():
+    import torch.nn as nn
+    from rhinoforge_b200.runtime import hw_attrs as H
+    from rhinoforge_b200.runtime.errors import RPUConfigError
+
+    def tree():
+        return nn.Sequential(nn.Linear(4, 4), nn.Sequential(nn.Linear(4, 4), nn.ReLU()))
+
+    m = tree()
+    m._rpu_execution = {"prefill": {"chunk_size": 64}}           # a user may set this ahead of the install
+    m[0]._rpu_debug_tag = "first"
+    H.validate_preinstall(m)
+    m[1][0]._rpu_handle = 7                                      # runtime-owned: stale before an install
+    with pytest.raises(RPUConfigError, match="'_rpu_handle' on Linear before the install"):
+        H.validate_preinstall(m)
+    H.validate_postinstall(m)                                    # ... but legitimate after one
+    m[1]._rpu_chunksize = 64                                     # a typo
+    with pytest.raises(RPUConfigError, match="'_rpu_chunksize' on Sequential after the install"):
+        H.validate_existing_hw_attrs(m)
+    with pytest.raises(RPUConfigError):
+        H.install_hw_attr_validator(m)                           # scanned first: nothing was stamped
+    assert type(m) is nn.Sequential and type(m[0]) is nn.Linear
+    del m[1]._rpu_chunksize
+
+    H.install_hw_attr_validator(m)
+    H.install_hw_attr_validator(m)                               # idempotent
+    assert type(m).__name__ == "Validated_Sequential" and type(m[0]).__name__ == "Validated_Linear"
+    assert isinstance(m[0], nn.Linear) and type(m[0]) is type(m[1][0])       # one cached subclass per class
+    assert m(torch.zeros(2, 4)).shape == (2, 4)                  # forward is untouched
+    m[0]._rpu_dtype = torch.float16                              # cold names can still be set before the first forward
+    m[0]._rpu_is_ready = True                                    # so can runtime-owned ones
+    with pytest.raises(RPUConfigError, match="not a known runtime attribute"):
+        m[1][1]._rpu_typo = 1
+    m[0].some_user_field = 3                                     # foreign names are nobody's business
+
+    H.mark_first_forward_done(m)
+    m[0]._rpu_dtype = torch.float16                              # same value: fine
+    with pytest.raises(RPUConfigError, match="cannot change afterwards"):
+        m[0]._rpu_dtype = torch.bfloat16
+    with pytest.raises(RPUConfigError, match="owned by the runtime"):
+        m[1][0]._rpu_handle = 8
+    m[1][1]._rpu_debug_tag = "hot"                               # public names stay writable
+    other = tree()
+    H.install_hw_attr_validator(other)
+    other[0]._rpu_dtype = torch.bfloat16                         # another tree has its own state
+    H.mark_first_forward_done(object())                          # never stamped: no-op
+    H.mark_first_forward_done(3)
+
+    class Slotted:
+        __slots__ = ("x",)
+    with pytest.raises(RPUConfigError, match="does not allow the validator"):
+        H.install_hw_attr_validator(Slotted())                   # a class whose layout forbids the swap is reported
