@@ -132,3 +132,17 @@ def test_environment_inventory_matches_sources():
     assert project_documented - used == set(), f"documented but unused: {sorted(project_documented - used)}"
     for d in dropped:
         assert f"`{d}`" in doc
+
+
+def test_rhinovla_example_runs_the_whole_lifecycle_with_its_stand_in_factory(tmp_path):
+    """construct -> prepare graphs -> predict, with the execution handshake, on a machine without a GPU; a request that
+    the runtime cannot honour is reported by the policy, not swallowed."""
+    script = ROOT / "examples" / "rhinovla.py"
+    r = subprocess.run([sys.executable, str(script)], cwd=ROOT, text=True, capture_output=True, timeout=300)
+    assert r.returncode == 0, (r.stdout, r.stderr)
+    assert "shape=(32, 7)" in r.stdout and "'chunk_size': 256" in r.stdout and "'execution_alignment': 16" in r.stdout
+    bad = tmp_path / "vision.toml"
+    bad.write_text((ROOT / "examples" / "configs" / "rhinovla.toml").read_text().replace(
+        "[rpu_execution.action]", "[rpu_execution.vision]"))
+    r = subprocess.run([sys.executable, str(script), "--config", str(bad)], cwd=ROOT, text=True, capture_output=True, timeout=300)
+    assert r.returncode != 0 and "not supported by this model entry point" in r.stderr
