@@ -994,3 +994,16 @@ def test_hw_attr_validator_over_a_module_tree():
         __slots__ = ("x",)
     with pytest.raises(RPUConfigError, match="does not allow the validator"):
         H.install_hw_attr_validator(Slotted())                   # a class whose layout forbids the swap is reported
+
+
+def test_runtime_handle_opts_into_the_install_check():
+    from types import SimpleNamespace
+    from rhinoforge_b200.graph.lazy_init_guard import verify_lazy_init
+    from rhinoforge_b200.runtime.causal_lm import RPUCausalLM
+    engine = SimpleNamespace(dtype=torch.float16, tp=SimpleNamespace(world=1), device=torch.device("cpu"))
+    handle = RPUCausalLM(engine, SimpleNamespace(), execution={"prefill": {"chunk_size": 64}})
+    assert handle._rpu_lazy_init_checked and set(handle._rpu_required_attrs) >= {"engine", "_rpu_execution", "_rpu_dtype"}
+    verify_lazy_init(handle)
+    del handle._rpu_dtype
+    with pytest.raises(RuntimeError, match="_rpu_dtype"):
+        verify_lazy_init(handle)
