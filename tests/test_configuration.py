@@ -146,3 +146,11 @@ def test_rhinovla_example_runs_the_whole_lifecycle_with_its_stand_in_factory(tmp
         "[rpu_execution.action]", "[rpu_execution.vision]"))
     r = subprocess.run([sys.executable, str(script), "--config", str(bad)], cwd=ROOT, text=True, capture_output=True, timeout=300)
     assert r.returncode != 0 and "not supported by this model entry point" in r.stderr
+
+
+def test_version_comes_from_the_project_table():
+    import rhinoforge_b200
+    from rhinoforge_b200._version import API_VERSION, DISTRIBUTION_VERSION
+    project = tomllib.loads((ROOT / "pyproject.toml").read_text(encoding="utf-8"))["project"]
+    assert DISTRIBUTION_VERSION == project["version"] == rhinoforge_b200.__version__
+    assert API_VERSION.split(".")[0] == "5"
