@@ -4,8 +4,11 @@ Nothing about a robot is hard-coded: groups, their normalisation kind and the st
 configuration (reference: ``python/rpu_backend/api/action_denorm.py:50-300``).
 
 Kinds: ``meanstd`` ``x*(std+eps)+mean``; ``std`` ``x*(std+eps)``; ``minmax`` / ``bounds_98`` / ``bounds_99``
-``(clip(x,-1,1)+1)/2*(hi-lo+eps)+lo`` with (min,max) / (q02,q98) / (q01,q99); the ``*_woclip`` forms skip the
-clip; ``identity``.  ``eps = 1e-6`` as in the normaliser that produced the statistics.
+``(x+1)/2*(hi-lo+eps)+lo`` with (min,max) / (q02,q98) / (q01,q99); ``identity``.  The clip of the ``minmax`` /
+``bounds_*`` kinds belongs to the forward (normalising) direction only: the inverse never clips, so a kind and its
+``*_woclip`` twin de-normalise identically, exactly as in the reference (``_unnormalize_group``).  Statistics are
+``[dim]`` or per-step ``[chunk, dim]``; the latter are cut to the action horizon.  ``eps = 1e-6`` as in the
+normaliser that produced the statistics.
 """
 from __future__ import annotations
 
@@ -56,6 +59,10 @@ class ActionDenormalizer:
                     v = np.asarray(self.norm_stats[g.key][name], dtype=np.float64)
                     if v.ndim not in (1, 2) or v.shape[-1] != int(g.dim):
                         raise ValueError(f"{g.key}.{name} has shape {v.shape}, expected [..., {int(g.dim)}]")
+                    if v.ndim == 2 and v.shape[0] == 0:
+                        raise ValueError(f"{g.key}.{name} has an empty horizon")
+                    if not np.isfinite(v).all():
+                        raise ValueError(f"{g.key}.{name} contains non-finite statistics")
             if g.subtract_state and not g.state_key:
                 raise ValueError(f"delta action group {g.key!r} needs a state_key")
             self._offsets.append((acc, acc + int(g.dim)))
@@ -158,18 +165,26 @@ class ActionDenormalizer:
             raise ValueError("de-normalized action contains non-finite values")
         return result
 
+    def _stat(self, key: str, name: str, horizon: int) -> np.ndarray:
+        """Statistic ``name`` of group ``key`` for an action of ``horizon`` steps: per-step ``[chunk, dim]`` tables
+        are cut to the first ``horizon`` rows (a shorter table is an error), ``[dim]`` vectors broadcast."""
+        s = np.asarray(self.norm_stats[key][name], dtype=np.float64)
+        if s.ndim == 2:
+            if s.shape[0] < horizon:
+                raise ValueError(f"{key}.{name} horizon {s.shape[0]} < action horizon {horizon}")
+            s = s[:horizon]
+        return s
+
     def _unnorm(self, g: ActionGroup, x: np.ndarray) -> np.ndarray:
         if g.norm_type == "identity":
             return x
-        s = {k: np.asarray(v, dtype=np.float64) for k, v in self.norm_stats[g.key].items()}
+        H = x.shape[0]
         if g.norm_type == "meanstd":
-            return x * (s["std"] + EPS) + s["mean"]
+            return x * (self._stat(g.key, "std", H) + EPS) + self._stat(g.key, "mean", H)
         if g.norm_type == "std":
-            return x * (s["std"] + EPS)
-        lo, hi = (s[k] for k in _RANGE_KEYS[g.norm_type])
-        if not g.norm_type.endswith("_woclip"):
-            x = np.clip(x, -1.0, 1.0)
-        return (x + 1.0) / 2.0 * (hi - lo + EPS) + lo
+            return x * (self._stat(g.key, "std", H) + EPS)
+        lo, hi = (self._stat(g.key, k, H) for k in _RANGE_KEYS[g.norm_type])
+        return (x + 1.0) / 2.0 * (hi - lo + EPS) + lo      # no clip on the way back (see the module docstring)
 
     def __call__(self, actions, state: Optional[Mapping[str, np.ndarray]] = None) -> np.ndarray:
         """``actions [H, >= total_dim]`` (tensor or array) -> physical ``[H, total_dim]`` float64."""

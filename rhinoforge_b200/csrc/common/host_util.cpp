@@ -84,14 +84,27 @@ bool pdl_enabled() {
   return v == 1;
 }
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 148;
+int device_ordinal() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    (void)cudaGetLastError();   // no device: not an error of the caller's
+    return -1;
   }
+  return dev;
+}
+
+int sm_count() {
+  constexpr int kMaxDev = 64;
+  static std::atomic<int> cache[kMaxDev];   // zero-initialised: 0 = not looked up yet
+  const int dev = device_ordinal();
+  if (dev < 0) return 148;
+  if (dev < kMaxDev) {
+    const int c = cache[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
+  }
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  if (dev < kMaxDev) cache[dev].store(n, std::memory_order_relaxed);
   return n;
 }
 

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <atomic>
 #include <string>
 
 #include "../rf_api.h"
@@ -44,7 +45,25 @@ inline uint32_t next_pow2(uint32_t v) {
   return p;
 }
 
+// SM count of the CURRENT device (cached per device ordinal; 148 when no device answers).
 int sm_count();
+
+// Ordinal of the current device, or -1 when there is none.
+int device_ordinal();
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device property of a kernel: a process that uses several
+// GPUs must set it on each of them.  This sets it the first time the call site runs on each device (one bit per
+// ordinal; ordinals >= 64 set it on every call).
+#define RF_ALLOW_SMEM_PER_DEVICE(kfn, bytes)                                                               \
+  do {                                                                                                     \
+    static std::atomic<uint64_t> _rf_done{0};                                                              \
+    const int _rf_dev = ::rf::device_ordinal();                                                            \
+    const bool _rf_track = _rf_dev >= 0 && _rf_dev < 64;                                                   \
+    if (!_rf_track || !((_rf_done.load(std::memory_order_acquire) >> _rf_dev) & 1ull)) {                   \
+      RF_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes))); \
+      if (_rf_track) _rf_done.fetch_or(1ull << _rf_dev, std::memory_order_release);                        \
+    }                                                                                                      \
+  } while (0)
 
 // Whether kernels are launched with programmatic stream serialization (RF_PDL=0 turns it off).
 bool pdl_enabled();

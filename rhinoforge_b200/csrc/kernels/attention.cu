@@ -233,7 +233,19 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     }
   }
   __syncthreads();
-  if (ctl->abort_flag) return;
+  if (ctl->abort_flag) {
+    // A bounded wait ran out (the status word says where).  The merge pass still runs after this kernel, so this
+    // CTA's slots must not keep an earlier call's partials: mark them empty (weight 0 in the merge).
+    if (p.splits > 1) {
+      for (int idx = tid; idx < G * HD; idx += blockDim.x) {
+        const int g = idx / HD, col = idx % HD;
+        const size_t base = ((size_t)seq * p.Hq + (size_t)kvh * G + g) * p.splits + split;
+        p.ws_o[base * HD + col] = 0.f;
+        if (col == 0) p.ws_lse[base] = -INFINITY;
+      }
+    }
+    return;
+  }
   for (int idx = tid; idx < G * HD; idx += blockDim.x) {
     const int g = idx / HD, col = idx % HD;
     float M = -INFINITY;
@@ -516,6 +528,28 @@ static int kv_tmaps(const RfAttn* a, CUtensorMap* tmK, CUtensorMap* tmV) {
   return make_tmap_2d(tmV, a->v, a->dtype, 2, (uint64_t)a->Hkv * a->hd, a->kv_rows_total, a->ldv, 64, 16, true);
 }
 
+// Split-KV plan of the decode kernel: how many CTAs share one (sequence, kv head)'s KV range and how many pages each
+// takes.  Small batches are split until about two CTAs per SM exist; a split covers at least 8 pages and a multiple
+// of 4 (one ring stage).  `allow_split` is false when the caller gave no scratch for the partials.
+struct DecodeSplitPlan {
+  int splits, pages_per_split;
+  uint64_t scratch_bytes;   // fp32 partial outputs + one log-sum-exp per (sequence, head, split); 0 when unsplit
+};
+static DecodeSplitPlan plan_decode_split(int num_seqs, int Hq, int Hkv, int hd, int max_kv_len, bool allow_split) {
+  const int max_pages = std::max(1, (max_kv_len + 15) / 16);
+  const int ctas = num_seqs * Hkv;
+  int splits = 1;
+  if (allow_split && ctas < 2 * sm_count()) {
+    splits = std::min(std::max(1, (2 * sm_count()) / ctas), std::max(1, max_pages / 8));
+    splits = std::min(splits, 64);
+  }
+  DecodeSplitPlan pl;
+  pl.pages_per_split = round_up(ceil_div(max_pages, splits), 4);
+  pl.splits = std::max(1, ceil_div(max_pages, pl.pages_per_split));
+  pl.scratch_bytes = pl.splits > 1 ? (uint64_t)num_seqs * Hq * pl.splits * (hd + 1) * sizeof(float) : 0;
+  return pl;
+}
+
 template <typename T, int HD>
 static int launch_decode(const RfAttn* a, AttnParams& p, cudaStream_t s) {
   CUtensorMap tmK, tmV;
@@ -528,30 +562,18 @@ static int launch_decode(const RfAttn* a, AttnParams& p, cudaStream_t s) {
   p.stages = stages;
   const size_t smem = (size_t)stages * kStageBytes + sizeof(AttnCtl) + 1024 + 64;
   auto kfn = attn_decode_kernel<T, HD>;
-  static bool attr = false;
-  if (!attr) {
-    RF_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr = true;
-  }
+  RF_ALLOW_SMEM_PER_DEVICE(kfn, 200 * 1024);
   // split the KV range so that small batches still fill the machine
-  const int max_pages = (a->max_kv_len + 15) / 16;
-  const int ctas = a->num_seqs * a->Hkv;
-  int splits = 1;
-  if (a->ws && ctas < 2 * sm_count()) {
-    splits = std::min(std::max(1, (2 * sm_count()) / ctas), std::max(1, max_pages / 8));
-    splits = std::min(splits, 64);
-  }
-  int pps = ceil_div(std::max(1, max_pages), splits);
-  pps = round_up(pps, 4);
-  splits = std::max(1, ceil_div(std::max(1, max_pages), pps));
+  const DecodeSplitPlan pl = plan_decode_split(a->num_seqs, a->Hq, a->Hkv, HD, a->max_kv_len, a->ws != nullptr);
+  const int splits = pl.splits;
   if (splits > 1) {
-    const uint64_t need = (uint64_t)a->num_seqs * a->Hq * splits * (HD + 1) * sizeof(float);
-    RF_REQUIRE(need <= a->ws_bytes, "decode attention scratch too small: need %llu B", (unsigned long long)need);
+    RF_REQUIRE(pl.scratch_bytes <= a->ws_bytes, "decode attention scratch too small: need %llu B",
+               (unsigned long long)pl.scratch_bytes);
     p.ws_o = a->ws;
     p.ws_lse = a->ws + (size_t)a->num_seqs * a->Hq * splits * HD;
   }
   p.splits = splits;
-  p.pages_per_split = pps;
+  p.pages_per_split = pl.pages_per_split;
   dim3 grid(splits, a->Hkv, a->num_seqs);
   RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(grid), dim3(160), smem, s, 1, tmK, tmV, p));
   RF_CUDA_CHECK(cudaGetLastError());
@@ -580,11 +602,7 @@ static int launch_prefill(const RfAttn* a, AttnParams& p, cudaStream_t s) {
   p.stages = HD == 64 ? 3 : 2;
   const size_t smem = (size_t)kQBytes + (size_t)p.stages * kStageBytes + sizeof(AttnCtl) + 1024 + 64;
   auto kfn = attn_prefill_kernel<T, HD>;
-  static bool attr = false;
-  if (!attr) {
-    RF_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr = true;
-  }
+  RF_ALLOW_SMEM_PER_DEVICE(kfn, 200 * 1024);
   dim3 grid(ceil_div(a->max_q_len, 64), a->Hq, a->num_seqs);
   RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(grid), dim3(160), smem, s, 1, tmQ, tmK, tmV, p));
   RF_CUDA_CHECK(cudaGetLastError());
@@ -617,6 +635,8 @@ extern "C" int rf_attn_decode(const RfAttn* a, rf_stream_t stream) {
   if (rc) return rc;
   RF_REQUIRE(a->Hq / a->Hkv <= 16, "decode attention handles GQA groups up to 16, got %d", a->Hq / a->Hkv);
   RF_REQUIRE(a->max_kv_len > 0, "decode attention needs max_kv_len");
+  RF_REQUIRE(a->window <= 0, "decode attention has no sliding-window form (window=%d): every query would see the whole "
+             "context", a->window);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   RF_ATTN_DISPATCH(launch_decode)
 }
@@ -671,19 +691,9 @@ static int static_scratch_ptr(void** out) {
   return RF_OK;
 }
 
-// Bytes of split-KV partials the launcher will ask for (mirrors its split choice).
+// Bytes of split-KV partials the launcher will ask for: the launcher's own plan, with splitting allowed.
 static uint64_t decode_scratch_need(const RfAttn* a) {
-  const int max_pages = (a->max_kv_len + 15) / 16;
-  const int ctas = a->num_seqs * a->Hkv;
-  int splits = 1;
-  if (ctas < 2 * sm_count()) {
-    splits = std::min(std::max(1, (2 * sm_count()) / ctas), std::max(1, max_pages / 8));
-    splits = std::min(splits, 64);
-  }
-  int pps = round_up(ceil_div(std::max(1, max_pages), splits), 4);
-  splits = std::max(1, ceil_div(std::max(1, max_pages), pps));
-  if (splits <= 1) return 0;
-  return (uint64_t)a->num_seqs * a->Hq * splits * (a->hd + 1) * sizeof(float);
+  return plan_decode_split(a->num_seqs, a->Hq, a->Hkv, a->hd, a->max_kv_len, true).scratch_bytes;
 }
 
 }  // namespace rf

@@ -364,11 +364,7 @@ static int launch_prefill_tc_t(const RfAttn* a, const AttnParams& p, cudaStream_
   if (rc) return rc;
   const size_t smem = (size_t)G::kSmem + sizeof(FaCtl);
   auto kfn = attn_prefill_tc_kernel<T, HD>;
-  static bool attr = false;
-  if (!attr) {
-    RF_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr = true;
-  }
+  RF_ALLOW_SMEM_PER_DEVICE(kfn, 227 * 1024);
   dim3 grid(ceil_div(a->max_q_len, kFaRows), a->Hq, a->num_seqs);
   RF_CUDA_CHECK(::rf::launch_k(kfn, grid, dim3(kFaThreads), smem, s, 1, tmQ, tmK, tmV, p));
   ::rf::count_launch();

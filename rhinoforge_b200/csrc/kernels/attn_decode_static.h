@@ -30,10 +30,17 @@ extern "C" {
 //    per device, with that device current).  Make that first call outside any
 //    stream capture.
 //  * Every call on a device shares the one buffer, and the buffer keeps whatever
-//    the previous call left in it.  Nothing has to be cleared between calls --
-//    each slot the merge pass reads is rewritten by the same call first -- but
-//    two calls that overlap on the GPU (different streams, or the same stream
-//    from concurrent graph launches) race on it.  Serialise them.
+//    the previous call left in it.  Nothing has to be cleared between calls:
+//    each slot the merge pass reads is rewritten by the same call first, with a
+//    partial result or -- when a bounded wait inside the kernel ran out -- with an
+//    "empty" marker, so a timed-out call never blends an earlier call's partials
+//    into `out`.  After a reported timeout (non-zero status word) `out` is still
+//    not a valid result: check the status before using it.
+//  * Two calls that overlap on the GPU (different streams, or the same stream
+//    from concurrent graph launches) race on the buffer.  Serialise them.
+//  * The entry point may be used on several devices of one process: the buffer's
+//    address, the kernels' shared-memory limits and the SM count that sizes the
+//    split are all kept per device.
 int rf_attn_decode_static(const RfAttn* a, rf_stream_t stream);
 
 #ifdef __cplusplus

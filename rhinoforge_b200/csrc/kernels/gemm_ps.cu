@@ -393,11 +393,7 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 template <typename T, bool DUAL, int MT>
 static int launch_ps(const RfGemm* g, int bn, cudaStream_t stream) {
   auto kfn = gemm_ps_kernel<T, DUAL, MT>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    RF_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr_set = true;
-  }
+  RF_ALLOW_SMEM_PER_DEVICE(kfn, 227 * 1024);
   CUtensorMap tmA, tmO;
   int rc = make_tmap_2d(&tmA, g->x, g->dtype, 2, g->K, g->M, g->ldx, kPsBK, kPsBM, true);
   if (rc) return rc;

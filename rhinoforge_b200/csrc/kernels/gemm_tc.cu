@@ -935,12 +935,8 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
 
 template <typename T, bool SWAP, bool DUAL, bool W8>
 static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream) {
-  static bool attr_set = false;
   auto kfn = gemm_tc_kernel<T, SWAP, DUAL, W8>;
-  if (!attr_set) {
-    RF_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr_set = true;
-  }
+  RF_ALLOW_SMEM_PER_DEVICE(kfn, 227 * 1024);
   const bool dual = DUAL;
   const uint64_t w_rows = (uint64_t)(dual ? g->dual_offset + g->N : g->N);
   CUtensorMap tmA, tmB, tmW;

@@ -237,6 +237,8 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
       }
       if (f.decode) {
         RF_REQUIRE(c.paged_kv, "decode needs a paged KV pool");
+        RF_REQUIRE(c.window <= 0, "decode attention has no sliding-window form: a stack with window=%d would prefill "
+                   "with the window and decode over the whole context", c.window);
         a.ws = s.at<float>(s.off_attn_ws); a.ws_bytes = s.attn_ws_bytes;
         rc = rf_attn_decode(&a, st);
       } else {

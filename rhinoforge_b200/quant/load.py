@@ -141,14 +141,40 @@ def w8a16_tensor_getter(ckpt_dir: str, config=None) -> Callable[[str], torch.Ten
 
 
 def _set_tensor(model: nn.Module, name: str, tensor: torch.Tensor) -> None:
+    """Install a checkpoint tensor over the skeleton's parameter or buffer of the same name; the shapes must agree
+    (a mis-sized checkpoint is an error here, not wrong numbers later)."""
     mod_name, _, leaf = name.rpartition(".")
     mod = model.get_submodule(mod_name) if mod_name else model
     if leaf in mod._parameters:
-        mod._parameters[leaf] = nn.Parameter(tensor, requires_grad=False)
+        old = mod._parameters[leaf]
     elif leaf in mod._buffers:
-        mod._buffers[leaf] = tensor
+        old = mod._buffers[leaf]
     else:
         raise KeyError(f"checkpoint tensor {name!r} has no destination in the model")
+    if old is not None and tuple(old.shape) != tuple(tensor.shape):
+        raise ValueError(f"checkpoint tensor {name!r} has shape {tuple(tensor.shape)}, the model expects {tuple(old.shape)}")
+    if leaf in mod._parameters:
+        mod._parameters[leaf] = nn.Parameter(tensor, requires_grad=False)
+    else:
+        mod._buffers[leaf] = tensor
+
+
+def _skipped(name: str, skip_modules) -> bool:
+    """True when ``name`` belongs to a module the converter was told to leave in 16 bits."""
+    return any(s and (name == s + ".weight" or name.startswith(s + ".") or ("." + s + ".") in ("." + name))
+               for s in (skip_modules or ()))
+
+
+def _rope_init(mod):
+    """The function a Hugging Face rotary-embedding module derives its ``inv_freq`` with (by rope type)."""
+    fn = getattr(mod, "rope_init_fn", None)
+    if fn is not None:
+        return fn
+    rope_type = getattr(mod, "rope_type", "default")
+    if rope_type != "default":
+        from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+        return ROPE_INIT_FUNCTIONS[rope_type]
+    return mod.compute_default_rope_parameters
 
 
 def load_w8a16_model(config, ckpt_dir: str, *, dtype: torch.dtype = torch.float16, **_ignored) -> nn.Module:
@@ -157,14 +183,21 @@ def load_w8a16_model(config, ckpt_dir: str, *, dtype: torch.dtype = torch.float1
     from safetensors.torch import load_file
     from transformers import AutoModelForCausalLM
     ckpt = Path(ckpt_dir)
+    qc = getattr(config, "quant_config", None) or {}
+    skip = tuple(qc.get("skip_modules") or ())
     with torch.device("meta"):
         model = AutoModelForCausalLM.from_config(config)
     seen: set = set()
     for shard in _shards(ckpt):
         for name, t in load_file(str(shard)).items():
             if name.endswith(".weight_scale"):
-                owner = model.get_submodule(name[:-len(".weight_scale")])
-                owner.register_buffer("weight_scale", t.to(torch.float16))
+                owner_name = name[:-len(".weight_scale")]
+                owner = model.get_submodule(owner_name)
+                rows = getattr(owner, "weight").shape[0]
+                if t.dtype != torch.float16 or t.numel() != rows:
+                    raise ValueError(f"{name!r} must be fp16 with one entry per output row ({rows}), got {t.dtype} "
+                                     f"x {t.numel()}")
+                owner.register_buffer("weight_scale", t)
                 seen.add(name)
                 continue
             if t.dtype == torch.int8:
@@ -172,6 +205,8 @@ def load_w8a16_model(config, ckpt_dir: str, *, dtype: torch.dtype = torch.float1
                     raise TypeError(f"unexpected int8 tensor {name!r} in a W8A16 checkpoint")
                 _set_tensor(model, name, t)
             else:
+                if name.endswith(PROJECTION_SUFFIXES) and t.is_floating_point() and not _skipped(name, skip):
+                    raise TypeError(f"W8A16 projection {name!r} must be int8, got {t.dtype}")
                 _set_tensor(model, name, t.to(dtype) if t.is_floating_point() else t)
             seen.add(name)
     if getattr(config, "tie_word_embeddings", False) and LM_HEAD not in seen:
@@ -181,15 +216,21 @@ def load_w8a16_model(config, ckpt_dir: str, *, dtype: torch.dtype = torch.float1
             raise RuntimeError(f"W8A16 checkpoint left {n!r} unloaded")
         if p.dtype == torch.int8 and scale_name(n) not in seen:
             raise RuntimeError(f"W8A16 tensor {n!r} has no {scale_name(n)!r}")
-    # rotary buffers created on meta need real storage
-    for mod in model.modules():
+    # Buffers the checkpoint does not carry were created on meta and need real storage.  Only the rotary
+    # frequencies can be rebuilt from the configuration (with the attention scaling of non-default rope types);
+    # anything else left on meta is an error rather than a zero fill.
+    for mname, mod in model.named_modules():
         for bn, b in list(mod._buffers.items()):
-            if b is not None and b.is_meta:
-                if bn == "inv_freq" and hasattr(mod, "rope_init_fn"):
-                    inv, _ = mod.rope_init_fn(mod.config, torch.device("cpu"))
-                    mod._buffers[bn] = inv
-                else:
-                    mod._buffers[bn] = torch.zeros(b.shape, dtype=b.dtype)
+            if b is None or not b.is_meta:
+                continue
+            if bn in ("inv_freq", "original_inv_freq") and hasattr(mod, "config"):
+                inv, scaling = _rope_init(mod)(mod.config, torch.device("cpu"))
+                mod._buffers[bn] = inv.clone()
+                if hasattr(mod, "attention_scaling"):
+                    mod.attention_scaling = scaling
+            else:
+                raise KeyError(f"buffer {mname + '.' if mname else ''}{bn} is neither in the checkpoint nor derivable "
+                               "from the configuration")
     model._rpu_w8a16 = True
     return model.eval()
 

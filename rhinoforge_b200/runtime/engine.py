@@ -74,7 +74,7 @@ class DecoderEngine:
     def __init__(self, cfg: DecoderConfig, get_weight: WeightGetter, *, device="cuda", dtype=torch.float16,
                  max_batch: int = 1, max_seq_len: int = 2048, max_prefill_tokens: int = 8192,
                  tp: Optional[TPContext] = None, quant: Optional[str] = None, decode_gemv_max_m: int = 0,
-                 hist_steps: int = 4096, kv_cache=None):
+                 hist_steps: int = 4096, kv_cache=None, kv_pool_tokens: Optional[int] = None):
         if not torch.cuda.is_available():
             raise RPUBackendError("DecoderEngine needs a CUDA device")
         self.cfg, self.dtype = cfg, dtype
@@ -128,7 +128,8 @@ class DecoderEngine:
         # ---- KV cache: a PagedKV (or RPUCache) object; replaceable through bind_cache()
         from .kv_cache import PagedKV
         self.cache = kv_cache if kv_cache is not None else PagedKV(len(self.attn_layers), max_batch, max_seq_len,
-                                                                     self.Hkv, hd, device=self.device, dtype=dtype)
+                                                                     self.Hkv, hd, device=self.device, dtype=dtype,
+                                                                     pool_tokens=kv_pool_tokens)
         self._check_cache(self.cache)
         # recurrent + conv state of the linear-attention layers, one slot per sequence of the batch
         self.gdn_conv_state: Dict[int, torch.Tensor] = {}
@@ -181,6 +182,11 @@ class DecoderEngine:
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.batch = 0
         self.launches_per_step = 0
+        self._hb = 0                         # host heartbeat counter (tensor parallel only)
+        self._host_steps = 0
+        self.heartbeat_every = int(os.environ.get("RPU_TP_HEARTBEAT_STEPS", "64"))
+        if self.tp.enabled:
+            self._check_plan_agreement()
 
     # ------------------------------------------------------------------ weights
     def _dev(self, t: torch.Tensor) -> torch.Tensor:
@@ -332,8 +338,39 @@ class DecoderEngine:
 
     def advance_lengths(self, n_steps: int) -> None:
         """Account for ``n_steps`` graph replays issued outside :meth:`decode`."""
-        for s in range(self.batch):
-            self.cache.lengths[s] += n_steps
+        self.cache.lengths[:self.batch] += n_steps
+
+    def reserve_steps(self, n_steps: int) -> None:
+        """Give every sequence of the batch KV pages for ``n_steps`` more decode steps (a caller that replays
+        the captured graph itself calls this first; :meth:`decode` does it on its own)."""
+        self.cache.ensure_batch(self.batch, n_steps + 1)
+
+    def _liveness(self) -> None:
+        """Tensor-parallel ranks confirm on the host, between steps and with no kernel of this call in flight yet,
+        that every peer is still there: a dead peer is then an exception here, not a one-second in-kernel flag
+        timeout per waiting kernel."""
+        if self.tp.enabled:
+            self._hb += 1
+            self.tp.heartbeat(self._hb)
+            self.tp.check_peers(self._hb)
+
+    def _check_plan_agreement(self) -> None:
+        """Every rank must launch the same grids on the shared flag arrays: compare a digest of what decides the launch
+        plans (model geometry, dtype, quantisation, batch / token envelope, weight layout, planner environment) across
+        ranks once, at construction.  A mismatch (say an environment override on one rank) would otherwise only show
+        up as a peer-wait timeout inside a kernel."""
+        import hashlib
+        c = self.cfg
+        # every kernel-selection switch of this library starts with RF_ (RF_TP_REPORT only names a test's report file)
+        env = {k: v for k, v in os.environ.items() if k.startswith("RF_") and k != "RF_TP_REPORT"}
+        desc = repr((c.name, c.num_layers, c.hidden_size, c.num_heads, c.num_kv_heads, c.head_dim, c.intermediate_size,
+                     c.vocab_size, str(self.dtype), self.quant, self.max_batch, self.max_tokens, self.packed,
+                     self.tp.world, sorted(env.items())))
+        digest = hashlib.sha256(desc.encode()).hexdigest()[:16]
+        seen = self.tp.all_gather_object(digest)
+        if len(set(seen)) != 1:
+            raise RPUBackendError(f"tensor-parallel ranks disagree on the launch plan inputs (digests by rank: {seen}); "
+                                  "check per-rank environment overrides and constructor arguments")
 
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._keep)
@@ -388,7 +425,7 @@ class DecoderEngine:
 
     def reset(self) -> None:
         for s in range(self.cache.batch_size):
-            self.cache.lengths[s] = 0
+            self.cache.release(s)
         self.step.zero_()
         self.batch = 0
 
@@ -429,13 +466,16 @@ class DecoderEngine:
         cache = self.cache
         if B > cache.batch_size:
             raise RPUBackendError(f"batch {B} exceeds the cache's batch_size {cache.batch_size}")
-        starts = [cache.lengths[s] for s in range(B)]
+        self._liveness()
+        starts = [int(cache.lengths[s]) for s in range(B)]
         lens = [int(p.numel()) for p in tokens]
         for s, L in enumerate(lens):
             if L < 1:
                 raise RPUBackendError("every sequence needs at least one new token")
             cache.check_fits(s, L + 1)
-        cache.reserve_all()
+        for s, L in enumerate(lens):              # pages for the new tokens and the first decode step
+            cache.ensure(s, starts[s] + L + 1)
+        cache.sync_table()
         logits_all = torch.empty((B, self.vocab_local), dtype=self.dtype, device=self.device) if return_logits else None
         first = torch.zeros(B, dtype=torch.int32, device=self.device)
         chunk: List[tuple] = []
@@ -461,7 +501,7 @@ class DecoderEngine:
             cache.lengths[s] = starts[s] + L
         # decode state: the token to feed next is `first`, at position = new length
         self.ids[:B].copy_(first)
-        new_len = torch.tensor([cache.lengths[s] for s in range(B)], dtype=torch.int32)
+        new_len = torch.from_numpy(cache.lengths[:B].astype("int32"))
         if self.device.type == "cuda":
             new_len = new_len.pin_memory()
         new_len = new_len.to(self.device, non_blocking=True)
@@ -611,6 +651,8 @@ class DecoderEngine:
             raise RPUBackendError("decode() before prefill()")
         for s in range(B):
             self.cache.check_fits(s, n_steps + 1)
+        self._liveness()
+        self.reserve_steps(n_steps)
         start = int(self.step.item())
         if start + n_steps > self.hist_steps:
             self.step.zero_()
@@ -623,19 +665,21 @@ class DecoderEngine:
         else:
             for _ in range(n_steps):
                 self._decode_step(B)
-        for s in range(B):
-            self.cache.lengths[s] += n_steps
+        self.cache.lengths[:B] += n_steps
         return self.hist[start:start + n_steps, :B].t()
 
     def step_from_host(self, host_ids: torch.Tensor, host_out: torch.Tensor) -> None:
         """One decode step driven from the host: copy this step's input ids from pinned host
         memory, replay the graph, copy the produced ids back (asynchronous; the caller syncs)."""
         B = self.batch
+        self._host_steps += 1
+        if self.tp.enabled and self.heartbeat_every > 0 and self._host_steps % self.heartbeat_every == 0:
+            self._liveness()
+        self.cache.ensure_batch(B, 2)            # one vector comparison unless a sequence crosses a page boundary
         self.ids[:B].copy_(host_ids, non_blocking=True)
         self.graphs[B].replay()
         host_out.copy_(self.out_ids[:B], non_blocking=True)
-        for s in range(B):
-            self.cache.lengths[s] += 1
+        self.cache.lengths[:B] += 1
 
     @torch.no_grad()
     def generate(self, prompts: Sequence[torch.Tensor], max_new_tokens: int, *, use_graph: bool = True) -> torch.Tensor:

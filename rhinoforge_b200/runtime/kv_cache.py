@@ -6,12 +6,19 @@ page table instead of a fixed 7-D view.  Page ownership is kept by the native ``
 (``csrc/runtime/kv_pool.cpp``); ``position`` per sequence is host state and the only source of
 truth for lengths.  The pool is zero-filled at creation and must never hold NaN/Inf: masked
 tokens still pass through the attention MMAs.
+
+Pages are handed out ON DEMAND: a sequence owns only the pages its tokens (plus the step about to
+run) need, ``ensure(seq, tokens)`` grows it, ``release(seq)`` returns its pages.  The pool may
+therefore be smaller than ``batch_size * max_seq_len`` (``pool_tokens``): short sequences leave room
+for long ones, and a request the pool cannot serve raises ``SPMExhaustionError`` before anything
+runs.  Because sequences grow interleaved, the page table is in general not the identity map.
 """
 from __future__ import annotations
 
 import ctypes as C
-from typing import List, Optional
+from typing import Optional
 
+import numpy as np
 import torch
 
 from .. import _native as N
@@ -22,7 +29,7 @@ PAGE_TOKENS = 16
 
 class PagedKV:
     def __init__(self, num_layers: int, batch_size: int, max_seq_len: int, num_kv_heads: int, head_dim: int, *,
-                 device="cuda", dtype=torch.float16):
+                 device="cuda", dtype=torch.float16, pool_tokens: Optional[int] = None):
         for name, v in (("num_layers", num_layers), ("batch_size", batch_size), ("max_seq_len", max_seq_len),
                         ("num_kv_heads", num_kv_heads), ("head_dim", head_dim)):
             if isinstance(v, bool) or not isinstance(v, int) or v <= 0:
@@ -35,49 +42,83 @@ class PagedKV:
         self.device = torch.device(device)
         self.pages_per_seq = (max_seq_len + PAGE_TOKENS - 1) // PAGE_TOKENS
         self.num_pages = batch_size * self.pages_per_seq
+        if pool_tokens is not None:
+            if isinstance(pool_tokens, bool) or not isinstance(pool_tokens, int) or pool_tokens <= 0:
+                raise ValueError(f"RPUCache pool_tokens must be a positive integer, got {pool_tokens!r}")
+            self.num_pages = min(self.num_pages, (pool_tokens + PAGE_TOKENS - 1) // PAGE_TOKENS)
         self.kv = torch.zeros((num_layers, 2, self.num_pages, num_kv_heads, PAGE_TOKENS, head_dim), dtype=dtype,
                               device=self.device)
         self.page_table = torch.zeros((batch_size, self.pages_per_seq), dtype=torch.int32, device=self.device)
         self._pt_host = torch.zeros((batch_size, self.pages_per_seq), dtype=torch.int32)
         if self.device.type == "cuda":
             self._pt_host = self._pt_host.pin_memory()
-        self.lengths: List[int] = [0] * batch_size
+        # cached length and page capacity (in tokens) of every sequence slot: numpy so that a decode step
+        # advances / checks the whole batch with one vector operation
+        self.lengths = np.zeros(batch_size, dtype=np.int64)
+        self._capacity = np.zeros(batch_size, dtype=np.int64)
+        self._dirty = False
         self._pool = None
         if N.available() or self.device.type == "cuda":
             self._pool = C.c_int64(N.lib().rf_kvpool_create(self.num_pages, batch_size, self.pages_per_seq))
         else:  # host-only sizing without the native library: identity mapping
+            if self.num_pages < batch_size * self.pages_per_seq:
+                raise ValueError("an over-subscribed pool (pool_tokens) needs the native library")
             for s in range(batch_size):
                 self._pt_host[s] = torch.arange(s * self.pages_per_seq, (s + 1) * self.pages_per_seq)
-        self._reserved = [False] * batch_size
+            self._capacity[:] = self.pages_per_seq * PAGE_TOKENS
 
     # -- page ownership ----------------------------------------------------------------------
-    def reserve(self, seq: int, tokens: Optional[int] = None) -> None:
-        """Give sequence ``seq`` pages for ``tokens`` tokens (default: the full ``max_seq_len``)."""
-        tokens = self.max_seq_len if tokens is None else tokens
+    def ensure(self, seq: int, tokens: int) -> bool:
+        """Grow sequence ``seq`` until it owns pages for ``tokens`` tokens; True when pages were added (the device
+        table is then stale until :meth:`sync_table`).  Raises ``SPMExhaustionError`` when the pool has no free
+        page left or ``tokens`` exceeds ``max_seq_len``; nothing is changed then."""
+        if tokens <= self._capacity[seq]:
+            return False
         if self._pool is None:
-            self._reserved[seq] = True
-            return
+            raise RPUBackendError(f"sequence {seq} needs {tokens} tokens, the host-only cache holds {self._capacity[seq]}")
         row = self._pt_host[seq]
-        rc = N.lib().rf_kvpool_reserve(self._pool, seq, tokens, C.c_void_p(row.data_ptr()))
+        rc = N.lib().rf_kvpool_reserve(self._pool, seq, int(tokens), C.c_void_p(row.data_ptr()))
         if rc != 0:
             from ..api.errors import SPMExhaustionError
             raise SPMExhaustionError(N.lib().rf_last_error().decode(errors="replace"))
-        self._reserved[seq] = True
+        self._capacity[seq] = (int(tokens) + PAGE_TOKENS - 1) // PAGE_TOKENS * PAGE_TOKENS
+        self._dirty = True
+        return True
+
+    def ensure_batch(self, n_seqs: int, extra: int) -> None:
+        """Every sequence ``0..n_seqs-1`` gets room for ``extra`` more tokens; the device table is refreshed when
+        a page was added.  The common case (room is there) costs one vector comparison."""
+        need = self.lengths[:n_seqs] + extra
+        short = np.nonzero(need > self._capacity[:n_seqs])[0]
+        for s in short:
+            self.ensure(int(s), int(need[s]))
+        if self._dirty:
+            self.sync_table()
+
+    def reserve(self, seq: int, tokens: Optional[int] = None) -> None:
+        """Give sequence ``seq`` pages for ``tokens`` tokens up front (default: the full ``max_seq_len``)."""
+        self.ensure(seq, self.max_seq_len if tokens is None else tokens)
 
     def reserve_all(self) -> None:
+        """Reserve ``max_seq_len`` for every slot up front (the fixed-envelope behaviour; needs a full-size pool)."""
         for s in range(self.batch_size):
-            if not self._reserved[s]:
-                self.reserve(s)
+            self.reserve(s)
         self.sync_table()
 
     def sync_table(self) -> None:
         self.page_table.copy_(self._pt_host, non_blocking=True)
+        self._dirty = False
 
     def release(self, seq: int) -> None:
         if self._pool is not None:
             N.lib().rf_kvpool_release(self._pool, seq)
-        self._reserved[seq] = False
+            self._capacity[seq] = 0
+            self._pt_host[seq].zero_()
+            self._dirty = True
         self.lengths[seq] = 0
+
+    def owned_pages(self, seq: int) -> int:
+        return int(self._capacity[seq]) // PAGE_TOKENS
 
     def free_pages(self) -> int:
         return N.lib().rf_kvpool_free_pages(self._pool) if self._pool is not None else 0
@@ -88,7 +129,7 @@ class PagedKV:
     # -- contents ------------------------------------------------------------------------------
     def gather(self, layer: int, seq: int, length: Optional[int] = None):
         """Dense ``(K, V)`` of one sequence: ``[kv_heads, length, head_dim]`` each."""
-        L = self.lengths[seq] if length is None else length
+        L = int(self.lengths[seq] if length is None else length)
         npg = (L + PAGE_TOKENS - 1) // PAGE_TOKENS
         pages = self._pt_host[seq, :npg].long().to(self.device)
         k = self.kv[layer, 0][pages]  # [npg, H, 16, hd]

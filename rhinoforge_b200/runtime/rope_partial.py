@@ -54,6 +54,8 @@ def _mrope_tables(position_ids: torch.Tensor, head_dim: int, rope_theta: float, 
                          f"{tuple(getattr(position_ids, 'shape', ()))}")
     if position_ids.is_floating_point() or position_ids.dtype == torch.bool:
         raise TypeError(f"{builder}: position_ids must be an integer tensor, got {position_ids.dtype}")
+    if position_ids.numel() and int(position_ids.min()) < 0:
+        raise ValueError(f"{builder}: position_ids must be non-negative, got minimum {int(position_ids.min())}")
     rot = head_dim if rotary_dim is None else int(rotary_dim)
     if rot <= 0 or rot % 2 or rot > head_dim:
         raise ValueError(f"{builder}: rotary_dim {rot} must be even and within head_dim {head_dim}")

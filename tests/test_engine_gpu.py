@@ -149,3 +149,36 @@ def test_causal_decoder_handle_ops_match_the_engine():
     with pytest.raises(Exception, match="does not match the cached lengths"):
         ops.causal_decoder_forward(h, x2, [], [], None, 7, True, None, None, None, None)
     ops.causal_decoder_destroy(h)
+
+
+def test_engine_over_an_interleaved_oversubscribed_page_table():
+    """KV pages are handed out on demand: three sequences that grow in turns end up with interleaved page ids in a
+    pool smaller than ``batch * max_seq_len``; greedy tokens still follow the fp32 oracle, and a request the pool
+    cannot hold is refused on the host before anything runs."""
+    from rhinoforge_b200.api.errors import SPMExhaustionError
+    from rhinoforge_b200.models.decoder import tiny_config
+    cfg = tiny_config()
+    oracle, eng = _oracle_and_engine(cfg, torch.float16, max_batch=3, max_seq_len=256, kv_pool_tokens=3 * 96)
+    assert eng.cache.num_pages == 18 < 3 * eng.cache.pages_per_seq
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, cfg.vocab_size, (L,), generator=g) for L in (17, 40, 5)]
+    first = eng.prefill(prompts)
+    parts = [first[:, None]]
+    for _ in range(4):                       # four decode calls of 9 steps: every call adds pages to some sequence
+        parts.append(eng.decode(9).clone())
+    toks = torch.cat(parts, 1)
+    table = eng.cache._pt_host[:, :4].tolist()
+    owned = [eng.cache.owned_pages(s) for s in range(3)]
+    assert owned == [(17 + 36 + 1 + 15) // 16, (40 + 36 + 1 + 15) // 16, (5 + 36 + 1 + 15) // 16]
+    rows = [table[s][:owned[s]] for s in range(3)]
+    assert any(r != list(range(r[0], r[0] + len(r))) for r in rows), rows      # not the identity / contiguous map
+    assert len({p for r in rows for p in r}) == sum(owned)                       # no page is shared
+    for b, p in enumerate(prompts):
+        rt, rl = oracle.greedy(p[None].cuda(), 37)
+        _agree(toks[b:b + 1], rt, rl, 0.01)
+    eng.check_status()
+    free = eng.cache.free_pages()
+    with pytest.raises(SPMExhaustionError):
+        eng.decode(40)                        # 6 + 8 + 6 pages would be needed, the pool has 18
+    assert eng.cache.free_pages() <= free
+    eng.close()

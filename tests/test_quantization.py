@@ -40,9 +40,26 @@ def test_int4_and_nvfp4_packers_round_trip():
     assert p.shape == (32, 64) and s.shape == (32,)
     pg, sg = quantize_pack_int4_pgrp(w, 32)
     assert sg.shape == (32, 4) and cosine(dequantize_int4_pgrp(pg, sg, 32), w) > 0.98
-    pk, bs, ts = quantize_nvfp4(w)
-    assert pk.shape == (32, 64) and bs.shape == (32, 8) and bs.dtype == torch.uint8
-    assert cosine(dequantize_nvfp4(pk, bs, ts), w) > 0.97
+    codes, bs, ts = quantize_nvfp4(w)
+    assert codes.shape == (32, 128) and bs.shape == (8, 32) and bs.dtype == torch.uint8     # scales are [K/16, N]
+    deq = dequantize_nvfp4(codes, bs, ts)
+    assert deq.dtype == torch.float32 and cosine(deq, w) > 0.97
+
+
+def test_nvfp4_encoder_rounds_ties_to_the_even_code_and_keeps_signed_zero():
+    from rpu_backend.quant.nvfp4_pack import (fp4_e2m1_decode, fp4_e2m1_encode, pack_nibbles, quantize_nvfp4,
+                                              unpack_nibbles)
+    ties = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+    assert fp4_e2m1_decode(fp4_e2m1_encode(ties)).tolist() == [0.0, 1.0, 1.0, 2.0, 2.0, 4.0, 4.0]
+    assert fp4_e2m1_decode(fp4_e2m1_encode(-ties)).tolist() == [-0.0, -1.0, -1.0, -2.0, -2.0, -4.0, -4.0]
+    off = torch.tensor([0.26, 0.74, 1.26, 1.74, 2.51, 3.49, 5.01, 100.0])
+    assert fp4_e2m1_decode(fp4_e2m1_encode(off)).tolist() == [0.5, 0.5, 1.5, 1.5, 3.0, 3.0, 6.0, 6.0]
+    assert int(fp4_e2m1_encode(torch.tensor([-0.0]))[0]) == 8                      # sign bit survives on -0.0
+    zero = torch.zeros(2, 32)
+    codes, scales, ts = quantize_nvfp4(zero)
+    assert float(ts) == 2.0 ** -24 and int(codes.max()) == 0 and int(scales.max()) == 0
+    c = torch.randint(0, 16, (3, 32), dtype=torch.uint8)
+    assert torch.equal(unpack_nibbles(pack_nibbles(c)), c)
 
 
 def _tiny_ckpt(path: Path, tie=True):
@@ -101,6 +118,36 @@ def test_w8a16_loader_keeps_int8_parameters(tmp_path):
     assert get("model.layers.1.mlp.up_proj.weight").dtype == torch.int8
     assert get.scale("model.layers.1.mlp.up_proj.weight").shape == (512,)
     assert get.scale("model.norm.weight") is None
+
+
+def test_w8a16_loader_refuses_mis_sized_half_converted_and_mis_scaled_checkpoints(tmp_path):
+    from safetensors.torch import load_file, save_file
+    from transformers import AutoConfig
+    from rpu_backend.quant.convert_qwen3 import convert_checkpoint
+    from rpu_backend.quant.load import load_w8a16_model
+    _tiny_ckpt(tmp_path / "src", tie=False)
+    convert_checkpoint(tmp_path / "src", tmp_path / "dst", ["lm_head"])
+    config = AutoConfig.from_pretrained(tmp_path / "dst")
+    good = load_file(str(tmp_path / "dst" / "model.safetensors"))
+    qname = "model.layers.0.self_attn.q_proj.weight"
+
+    def variant(tag, edit):
+        d = tmp_path / tag
+        d.mkdir()
+        (d / "config.json").write_text((tmp_path / "dst" / "config.json").read_text())
+        t = {k: v.clone() for k, v in good.items()}
+        edit(t)
+        save_file(t, str(d / "model.safetensors"), metadata={"format": "pt"})
+        return str(d)
+
+    with pytest.raises(ValueError, match="the model expects"):                     # a row short
+        load_w8a16_model(config, variant("short", lambda t: t.__setitem__(qname, t[qname][:-1].contiguous())))
+    with pytest.raises(TypeError, match="must be int8"):                           # projection left in 16 bits
+        load_w8a16_model(config, variant("half", lambda t: t.__setitem__(qname, t[qname].to(torch.float16))))
+    with pytest.raises(ValueError, match="one entry per output row"):              # scale of the wrong length
+        load_w8a16_model(config, variant("scale", lambda t: t.__setitem__(qname + "_scale", t[qname + "_scale"][:-1].contiguous())))
+    with pytest.raises(ValueError, match="must be fp16"):                          # scale of the wrong dtype
+        load_w8a16_model(config, variant("sdtype", lambda t: t.__setitem__(qname + "_scale", t[qname + "_scale"].float())))
 
 
 def test_verify_accepts_a_converted_checkpoint_and_flags_a_corrupted_one(tmp_path):

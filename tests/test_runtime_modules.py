@@ -135,7 +135,7 @@ def test_action_denormalizer_and_runtime_env():
     out = d(a, {"observation.state.base": np.array([10.0, 20.0])})
     assert out.shape == (1, 6)
     assert np.allclose(out[0, :3], [1.5, 1.5, 3.0], atol=1e-5)
-    assert np.isclose(out[0, 3], 0.08, atol=1e-5)                        # clipped to +1 -> max
+    assert np.isclose(out[0, 3], (3.0 + 1) / 2 * 0.08, atol=1e-5)        # the inverse never clips: 3.0 maps past max
     assert np.allclose(out[0, 4:], [10.5, 16.0], atol=1e-4)              # no clip, delta added
     with pytest.raises(ValueError):
         ActionDenormalizer([ActionGroup("x", 2, "sincos")], {})
@@ -868,7 +868,21 @@ def test_action_denormalizer_config_constructors_and_unapply(tmp_path):
     assert out.dtype == torch.float32 and out.shape == (2, 4)
     want_arm0 = np.array([0.0, 1.0, -1.0]) * (np.array([0.5, 0.5, 2.0]) + EPS) + [1, 2, 3] + np.array(state[:3])
     assert np.allclose(out[0, :3].numpy(), want_arm0, atol=1e-5)
-    assert abs(float(out[0, 3]) - 0.04) < 1e-5 and abs(float(out[1, 3]) - 0.08) < 1e-5      # clipped to +1 before scaling
+    assert abs(float(out[0, 3]) - 0.04) < 1e-5 and abs(float(out[1, 3]) - 0.24) < 1e-5      # 5.0 is not clipped: (5+1)/2*0.08
+    # the reference's own example: x=[1.5,-2.0], min=[0,0], max=[2,4] -> [2.5,-2.0]; minmax == minmax_woclip on the way back
+    for kind in ("minmax", "minmax_woclip"):
+        mm = ActionDenormalizer([ActionGroup("g", 2, kind)], {"g": {"min": np.zeros(2), "max": np.array([2.0, 4.0])}})
+        assert np.allclose(mm.unapply([[1.5, -2.0]]).numpy(), [[2.5, -2.0]], atol=1e-5)
+    # per-step [chunk, dim] statistics are cut to the action horizon; a shorter table is refused
+    per_step = {"g": {"mean": np.arange(8.0).reshape(4, 2), "std": np.ones((4, 2))}}
+    ps = ActionDenormalizer([ActionGroup("g", 2, "meanstd")], per_step)
+    assert np.allclose(ps.unapply(np.zeros((3, 2))).numpy(), np.arange(6.0).reshape(3, 2), atol=1e-5)
+    with pytest.raises(ValueError, match="horizon 4 < action horizon 5"):
+        ps.unapply(np.zeros((5, 2)))
+    with pytest.raises(ValueError, match="non-finite statistics"):
+        ActionDenormalizer([ActionGroup("g", 2, "std")], {"g": {"std": np.array([1.0, np.inf])}})
+    with pytest.raises(ValueError, match="empty horizon"):
+        ActionDenormalizer([ActionGroup("g", 2, "std")], {"g": {"std": np.zeros((0, 2))}})
     with pytest.raises(ValueError, match="no state was provided"):
         d.unapply(a)
     with pytest.raises(ValueError, match="state has 2 dims"):
