@@ -113,34 +113,21 @@ class EagerTPDecoder:
         return idx
 
 
-def main() -> int:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--model", default="qwen3-8b")
-    ap.add_argument("--batch", type=int, default=64)
-    ap.add_argument("--prompt-len", type=int, default=1024)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--dtype", default="fp16")
-    ap.add_argument("--cuda-graph", action="store_true")
-    a = ap.parse_args()
+def run_baseline(model: str = "qwen3-8b", batch: int = 64, prompt_len: int = 1024, steps: int = 64, warmup: int = 8,
+                 dtype_name: str = "fp16", cuda_graph: bool = False) -> dict:
+    """Measure the eager baseline in the calling process (one rank of the job when WORLD_SIZE > 1; the process group
+    must then exist already).  Returns the record rank 0 prints; every rank gets the same numbers."""
     import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    assert world == a.gpus
-    if a.cuda_graph and world > 1:
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    dev = torch.device("cuda", torch.cuda.current_device())
+    if cuda_graph and world > 1:
         # capturing the NCCL all-reduces of a step inside a CUDA graph did not return on two GPUs here
         raise SystemExit("--cuda-graph is a one-GPU baseline; run the multi-GPU baseline eagerly")
-    dtype = torch.float16 if a.dtype == "fp16" else torch.bfloat16
-    cfg = PROFILES[a.model]
-    B, P = a.batch, a.prompt_len
-    max_len = P + a.steps + a.warmup + 8
+    dtype = torch.float16 if dtype_name == "fp16" else torch.bfloat16
+    cfg = PROFILES[model]
+    B, P = batch, prompt_len
+    max_len = P + steps + warmup + 8
     m = EagerTPDecoder(cfg, world, rank, dev, dtype, B, max_len)
     gen = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab_size, (B, P), generator=gen).to(dev)
@@ -174,10 +161,10 @@ def main() -> int:
         step_pos = torch.full((B, 1), P, device=dev, dtype=torch.long)
         graph = None
         kv = P
-        if a.cuda_graph:
+        if cuda_graph:
             # eager SDPA takes the KV length as a host value, so one captured step has a fixed length:
             # the graph variant replays a step at the final length (an upper bound on the work)
-            kv = P + a.warmup + a.steps
+            kv = P + warmup + steps
             static_ids = cur.clone()
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
@@ -186,7 +173,7 @@ def main() -> int:
             torch.cuda.current_stream().wait_stream(s)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                out = m.forward(static_ids, step_pos, kv)
+                m.forward(static_ids, step_pos, kv)
 
         def step():
             nonlocal cur, kv
@@ -196,24 +183,51 @@ def main() -> int:
                 kv += 1
                 cur = m.forward(cur, step_pos + (kv - 1 - P), kv)[:, None]
 
-        for _ in range(a.warmup):
+        for _ in range(warmup):
             step()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(a.steps):
+        for _ in range(steps):
             step()
         e1.record()
         torch.cuda.synchronize()
-        ms = sync_max(e0.elapsed_time(e1)) / a.steps
+        ms = sync_max(e0.elapsed_time(e1)) / steps
+    del m, graph
+    torch.cuda.empty_cache()
+    return {"impl": "baseline-eager-nccl" + ("-cudagraph" if cuda_graph else ""),
+            "metric": "decode_tokens_per_s", "value": B * 1000.0 / ms, "unit": "tokens/s",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+            "ttft_ms_p50": statistics.median(ttft), "dtype": dtype_name, "data": "synthetic",
+            "config": {"model": cfg.name, "global_batch": B, "seq_len": P, "parallelism": f"tp{world}"}}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--model", default="qwen3-8b")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--dtype", default="fp16")
+    ap.add_argument("--cuda-graph", action="store_true")
+    a = ap.parse_args()
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    assert world == a.gpus
+    rec = run_baseline(a.model, a.batch, a.prompt_len, a.steps, a.warmup, a.dtype, a.cuda_graph)
     if rank == 0:
-        print(json.dumps({"impl": "baseline-eager-nccl" + ("-cudagraph" if a.cuda_graph else ""),
-                          "metric": "decode_tokens_per_s", "value": B * 1000.0 / ms, "unit": "tokens/s",
-                          "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms,
-                          "ttft_ms_p50": statistics.median(ttft), "dtype": a.dtype, "data": "synthetic",
-                          "config": {"model": cfg.name, "global_batch": B, "seq_len": P, "parallelism": f"tp{world}"}}))
+        print(json.dumps(rec))
     if world > 1:
         dist.destroy_process_group()
     return 0

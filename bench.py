@@ -37,7 +37,11 @@ def parse_args(argv=None):
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16"])
     ap.add_argument("--quant", default=None, choices=[None, "w8a16"])
-    ap.add_argument("--sweep", default="", help="extra batch sizes to report, e.g. 1,8,32")
+    ap.add_argument("--sweep", default="1,8,32", help="extra batch sizes reported in by_batch ('' = only --batch)")
+    ap.add_argument("--no-baseline", action="store_true",
+                    help="skip the same-box PyTorch eager (+NCCL) baseline run that fills vs_baseline")
+    ap.add_argument("--no-tokens-check", action="store_true",
+                    help="skip the greedy-token check of a 4-layer truncation against the fp32 oracle / the TP=1 engine")
     ap.add_argument("--ttft-samples", type=int, default=3)
     ap.add_argument("--no-graph", action="store_true", help="launch decode steps eagerly (kernel profiling only)")
     ap.add_argument("--profiler-range", action="store_true",
@@ -109,6 +113,60 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def tokens_check(args, tp, dtype) -> dict:
+    """Correctness bit of the benchmarked configuration: a 4-layer truncation of the benchmarked model (same widths,
+    same random weights, same tensor-parallel degree, same kernels and graph path) decodes 16 greedy tokens for 4
+    prompts of 64 tokens; rank 0 compares them with (a) the plain-PyTorch fp32 forward of the same weights - tokens
+    must agree until the oracle's own top-2 margin is inside 16-bit noise, after which sequences legitimately part
+    ways - and, under tensor parallelism, (b) a TP=1 engine on rank 0 (exact match count reported)."""
+    import dataclasses
+    import torch
+    from rhinoforge_b200.models.decoder import PROFILES, TorchDecoder
+    from rhinoforge_b200.parallel.tp import TPContext
+    from rhinoforge_b200.runtime.engine import DecoderEngine, random_weight_getter
+    cfg = dataclasses.replace(PROFILES[args.model], num_layers=4, name=PROFILES[args.model].name + "-4layer")
+    dev = tp.device
+    get = random_weight_getter(cfg, seed=0, std=0.02, dtype=dtype, device=dev)
+    gen = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, cfg.vocab_size, (64,), generator=gen) for _ in range(4)]
+    n_new = 16
+    eng = DecoderEngine(cfg, get, dtype=dtype, max_batch=4, max_seq_len=128, max_prefill_tokens=512, tp=tp,
+                        quant=args.quant)
+    toks = eng.generate(prompts, n_new).cpu()
+    eng.close()
+    out = {"layers": 4, "prompts": 4, "new_tokens": n_new}
+    if tp.rank == 0:
+        if args.quant is None:
+            from rhinoforge_b200.models.decoder import weight_shapes
+            sd = {name: get(name) for name, _, _ in weight_shapes(cfg)}
+            oracle = TorchDecoder(cfg, sd, dtype=torch.float32, device=dev)
+            agree, compared = True, 0
+            for b, p in enumerate(prompts):
+                oracle.reset()
+                rt, rl = oracle.greedy(p[None].to(dev), n_new)
+                for t in range(n_new):
+                    compared += 1
+                    if int(toks[b, t]) != int(rt[0, t]):
+                        lg = rl[0, t].float()
+                        margin = float(lg[int(rt[0, t])] - lg[int(toks[b, t])])
+                        out.setdefault("first_mismatches", []).append({"seq": b, "step": t, "margin": margin})
+                        agree &= margin < 0.02
+                        break
+            del oracle, sd
+            out.update({"vs_fp32_oracle": bool(agree), "oracle_tokens_compared": compared})
+        if tp.enabled:
+            e1 = DecoderEngine(cfg, get, device=dev, dtype=dtype, max_batch=4, max_seq_len=128, max_prefill_tokens=512,
+                               tp=TPContext.single(dev), quant=args.quant)
+            t1 = e1.generate(prompts, n_new).cpu()
+            e1.close()
+            out["tp1_equal_tokens"] = f"{int((t1 == toks).sum())}/{t1.numel()}"
+            out["vs_tp1_engine"] = bool((t1 == toks).all())
+        out["ok"] = bool(out.get("vs_fp32_oracle", True) and (out.get("vs_tp1_engine", True) or out.get("vs_fp32_oracle", False)))
+    torch.cuda.empty_cache()
+    tp.barrier()
+    return out
+
+
 def run(args) -> dict:
     import torch
     from rhinoforge_b200 import _native as N
@@ -155,6 +213,7 @@ def run(args) -> dict:
         sampler = ClockSampler(dev.index or 0)
         sampler.start()
         eng.decode(args.warmup)
+        eng.reserve_steps(args.steps)             # KV pages for the raw graph replays below
         sampler.wait_first()
         tp.barrier(); torch.cuda.synchronize()
         sampler.mark()
@@ -200,11 +259,32 @@ def run(args) -> dict:
             headline = res
     wbytes = eng.weight_bytes()
     eng.close()
+    del eng
+    torch.cuda.empty_cache()
     B = args.batch
+    check = None if args.no_tokens_check else tokens_check(args, tp, dtype)
+    # ---- same-box baseline: the same model in plain PyTorch eager (cuBLAS, SDPA, NCCL all-reduce), same batch, prompt
+    # length, steps and warm-up; on one GPU additionally with its decode step captured in a CUDA graph (the stronger
+    # baseline, used for vs_baseline there; NCCL collectives inside a graph capture did not return on this pool).
+    base = None
+    if not args.no_baseline:
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+        from eager_tp import run_baseline
+        eager = run_baseline(args.model, B, args.prompt_len, args.steps, args.warmup, args.dtype, cuda_graph=False)
+        base = {"impl": eager["impl"], "decode_tok_s": eager["value"], "ms_per_step": eager["ms_per_step"],
+                "ttft_ms_p50": eager["ttft_ms_p50"]}
+        if tp.world == 1:
+            graphed = run_baseline(args.model, B, args.prompt_len, args.steps, args.warmup, args.dtype, cuda_graph=True)
+            base.update({"impl": graphed["impl"], "decode_tok_s": graphed["value"], "ms_per_step": graphed["ms_per_step"],
+                         "eager_decode_tok_s": eager["value"], "eager_ms_per_step": eager["ms_per_step"]})
+        base["ttft_speedup"] = base["ttft_ms_p50"] / headline["ttft_ms_p50"]
     out = {
         "metric": "decode_tokens_per_s", "value": headline["tok_s"], "unit": "tokens/s", "n_gpus": tp.world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": headline["ms_per_step"],
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": (headline["tok_s"] / base["decode_tok_s"]) if base else None,
+        "baseline": base, "tokens_check": (check or {}).get("ok") if tp.rank == 0 else None,
+        "tokens_check_detail": check,
         "dtype": args.dtype if not args.quant else f"{args.dtype}+int8w", "data": "synthetic",
         "impl": "ours",
         "config": {"model": f"{cfg.name}-architecture random-init (std 0.02, seed 0)", "global_batch": B,
@@ -334,9 +414,11 @@ def run_pi05(args) -> dict:
 
 
 def run_qwen3vl(args) -> dict:
-    """Qwen3-VL-2B-architecture: one prompt of 2 images (448x448 -> 28x28 patches each) + 256 text tokens;
+    """Qwen3-VL-2B-architecture: batch 4, every sample 2 images (448x448 -> 28x28 patches each) + 256 text tokens;
     reports multimodal prefill ms (vision tower + text prefill with DeepStack) and greedy decode tokens/s."""
+    import ctypes
     import torch
+    from rhinoforge_b200 import _native as N
     from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLConfig
     from rhinoforge_b200.models.decoder import PROFILES, weight_shapes
     from rhinoforge_b200.models.qwen3_vl import Qwen3VLEngine
@@ -375,8 +457,9 @@ def run_qwen3vl(args) -> dict:
         else:
             shape_of[n] = (lambda s=shp: torch.zeros(s, device=dev, dtype=dtype))
     t0 = time.time()
-    eng = Qwen3VLEngine(hf, get, names=set(shape_of), dtype=dtype, max_seq_len=2048, max_patches=2 * 28 * 28,
-                        max_prefill_tokens=2048)
+    BATCH = 4
+    eng = Qwen3VLEngine(hf, get, names=set(shape_of), dtype=dtype, max_seq_len=2048, max_batch=BATCH,
+                        max_patches=BATCH * 2 * 28 * 28, max_prefill_tokens=BATCH * 1024)
     cache.clear()
     torch.cuda.synchronize()
     startup_s = time.time() - t0
@@ -386,19 +469,30 @@ def run_qwen3vl(args) -> dict:
     text = torch.randint(0, 150000, (256,), generator=g)
     ids = torch.cat((text[:8], torch.full((n_img // 2,), eng.image_token_id), text[8:16],
                      torch.full((n_img // 2,), eng.image_token_id), text[16:]))
-    px = torch.randn(2 * 28 * 28, 3 * 2 * 16 * 16, generator=g).pin_memory()
+    # uniform [0,1] pixels normalised with mean/std 0.5, one pinned host tensor per sample
+    pxs = [torch.rand(2 * 28 * 28, 3 * 2 * 16 * 16, generator=g).sub_(0.5).div_(0.5).pin_memory() for _ in range(BATCH)]
+    idss = [ids.clone() for _ in range(BATCH)]
+    lib = N.lib()
+    lib.rf_launch_count.restype = ctypes.c_uint64
 
     def prefill():
-        eng.prefill(ids, px.to(dev, non_blocking=True), grid)
+        eng.prefill_batch(idss, [p.to(dev, non_blocking=True) for p in pxs], [grid] * BATCH)
+    prefill()
+    c0 = lib.rf_launch_count()
+    prefill()
+    prefill_launches = int(lib.rf_launch_count() - c0)
     ms, clocks = _timed(prefill, max(3, args.ttft_samples), 3)
     prefill()
-    eng.text.capture(1)
+    c0 = lib.rf_launch_count()
+    eng.text.capture(BATCH)
+    step_launches = int(lib.rf_launch_count() - c0) // 2        # one eager + one captured step
     eng.decode(max(args.warmup, 3))
+    eng.text.reserve_steps(args.steps)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        eng.text.graphs[1].replay()
+        eng.text.graphs[BATCH].replay()
     e1.record()
     torch.cuda.synchronize()
     dec_ms = e0.elapsed_time(e1) / args.steps
@@ -406,15 +500,16 @@ def run_qwen3vl(args) -> dict:
     eng.text.check_status()
     eng.close()
     return {
-        "metric": "qwen3vl_decode_tokens_per_s", "value": 1000.0 / dec_ms, "unit": "tokens/s", "n_gpus": 1,
+        "metric": "qwen3vl_decode_tokens_per_s", "value": BATCH * 1000.0 / dec_ms, "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dec_ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "impl": "ours",
-        "config": {"model": "qwen3-vl-2b-architecture random-init", "global_batch": 1, "images": "2 x 448x448",
+        "config": {"model": "qwen3-vl-2b-architecture random-init", "global_batch": BATCH, "images": "2 x 448x448 per sample",
                    "seq_len": int(ids.numel()), "parallelism": "tp1", "l2": "weights (4 GB) exceed L2"},
         "prefill_ms_p50": statistics.median(ms), "clocks": clocks, "startup_s": startup_s,
-        "e2e": {"value": statistics.median(ms), "unit": "ms (prefill incl. pixel H2D)", "h2d_bytes_per_step": px.numel() * 4,
-                "d2h_bytes_per_step": 4},
-        "gpu_launches": args.steps * 300,
+        "e2e": {"value": statistics.median(ms), "unit": "ms (batch prefill incl. pixel H2D)",
+                "h2d_bytes_per_step": sum(p.numel() for p in pxs) * 4, "d2h_bytes_per_step": 4 * BATCH},
+        "gpu_launches": args.steps * step_launches, "launches_per_decode_step": step_launches,
+        "launches_per_prefill": prefill_launches,
     }
 
 

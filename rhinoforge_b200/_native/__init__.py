@@ -41,6 +41,18 @@ class RfGemm(C.Structure):
         ("ar_recv_bytes", C.c_uint64), ("ar_flag_count", C.c_int32),
         ("force_splits", C.c_int32), ("force_swap", C.c_int32), ("force_bn", C.c_int32), ("w_packed", C.c_int32),
         ("w_scratch", C.c_void_p), ("w_scratch_bytes", C.c_uint64),
+        ("ar_publish", C.c_int32), ("ar_cnt_base", C.c_int32),
+    ]
+
+
+class RfArConsume(C.Structure):
+    _fields_ = [
+        ("M", C.c_int32), ("N", C.c_int32), ("world", C.c_int32), ("rank", C.c_int32),
+        ("ar_recv", C.c_void_p), ("ar_flags", C.c_void_p), ("ar_state", C.c_void_p),
+        ("ar_recv_bytes", C.c_uint64), ("ar_cnt_base", C.c_int32), ("pub_ctas", C.c_int32),
+        ("residual", C.c_void_p), ("ldr", C.c_int64), ("out", C.c_void_p), ("ldo", C.c_int64),
+        ("norm_w", C.c_void_p), ("norm_out", C.c_void_p), ("ldn", C.c_int64),
+        ("eps", C.c_float), ("norm_mode", C.c_int32), ("status", C.c_void_p), ("dtype", C.c_int32),
     ]
 
 
@@ -104,7 +116,7 @@ class RfLayerWeights(C.Structure):
 
 class RfStackComm(C.Structure):
     _fields_ = [("recv", C.c_void_p), ("flags", C.c_void_p), ("state", C.c_void_p),
-                ("recv_half_bytes", C.c_uint64), ("flag_count", C.c_int32)]
+                ("recv_half_bytes", C.c_uint64), ("flag_count", C.c_int32), ("cnt_base", C.c_int32)]
 
 
 class RfStackForward(C.Structure):

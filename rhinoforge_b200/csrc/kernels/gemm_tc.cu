@@ -51,6 +51,9 @@ struct GemmTcParams {
   int k_rotate;             // 1: every output tile starts its K loop at a different block
   int ar_two_shot;    // large-M path: 16-bit reduce-scatter to the tile's owner, then broadcast
   int ar_flag2_base;  // first flag of the "result has landed" range
+  int ar_publish;     // small-M path: push the partial rows to every rank, bump the arrival counters, exit
+  int ar_cnt_base;    // first arrival counter in every rank's flag array
+  int ar_stage_off;   // shared-memory offset of the staging rows of the publish path
 };
 
 struct alignas(8) GemmSmemCtl {
@@ -374,6 +377,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (d < p.ar_world) reinterpret_cast<float*>(peer_buf[d])[at] = v;
   };
 
+  // Publish path (swap mode): finished values are parked as rows [token][128 features] in shared memory and leave
+  // the CTA as 16-byte vectors, one contiguous 256- or 512-byte row segment per group of 16 or 32 threads.
+  const bool pub = SWAP && p.ar_world > 1 && p.ar_publish;
+  const bool pub_f32 = M <= RF_AR_F32_MAX_ROWS;
+  uint8_t* pub_stage = smem + p.ar_stage_off;
+  auto stage_put = [&](int j, float v) {   // j: row of the staging area (this CTA's j-th token)
+    if (pub_f32) reinterpret_cast<float*>(pub_stage)[j * kBM + tid] = v;
+    else reinterpret_cast<T*>(pub_stage)[j * kBM + tid] = Num<T>::from_f(v);
+  };
+
   bool aborted = __syncthreads_or(*reinterpret_cast<volatile int32_t*>(&ctl->abort_flag) != 0);
   const int ncols = min(bn, (SWAP ? M : N) - b0);  // valid accumulator columns of this tile
   uint8_t* owner_buf = nullptr;                    // two-shot: the buffer of this tile's owner rank
@@ -504,7 +517,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           const int tok = SWAP ? (b0 + c) : a_idx;
           const int n = SWAP ? a_idx : (b0 + c);
-          if (tok < M && n < N) {
+          if (pub) {
+            if (epi) stage_put((c - (int)crank) / p.splits, (tok < M && n < N) ? finish(tok, n, g, u) : 0.f);
+          } else if (tok < M && n < N) {
             const float v = finish(tok, n, g, u);
             if (p.ar_world > 1) {
               push_partial(tok, n, v);
@@ -546,6 +561,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
           store8(srow + ((((c >> 3)) ^ (tid & cmask)) << 3), lo);
           store8(srow + ((((c >> 3) + 1) ^ (tid & cmask)) << 3), hi);
+        }
+      } else if (pub) {
+        if (epi) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) stage_put(c + j, v[j]);
         }
       } else if (p.ar_world > 1) {
 #pragma unroll
@@ -748,6 +768,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         p.ar_state[0] = call + 1u;
       }
     }
+  } else if (pub) {
+    // Publish and exit: copy the staged rows into slot [rank] of every rank's receive buffer, make the copies
+    // visible system-wide, bump this rank's arrival counter on every rank.  Nothing here waits for a peer; the
+    // reduction, the residual and the following norm belong to rf_ar_consume.
+    __syncthreads();                                       // the staging rows are complete
+    if (!aborted) {
+      const int vpr = pub_f32 ? 32 : 16;                   // 16-byte vectors per staged row
+      const int epv = pub_f32 ? 4 : 8;                     // elements per vector
+      const int esz = pub_f32 ? 4 : 2;
+      const int nfeat = min(kBM, N - a0);                  // valid features of this tile (N % 8 == 0)
+      const int nst = p.splits > 1 ? (ncols > (int)crank ? (ncols - (int)crank + p.splits - 1) / p.splits : 0) : ncols;
+      for (int idx = tid; idx < nst * vpr; idx += (int)blockDim.x) {
+        const int j = idx / vpr, ch = idx - j * vpr;
+        if (ch * epv >= nfeat) continue;
+        const int tok = b0 + (p.splits > 1 ? (int)crank + j * p.splits : j);
+        if (tok >= M) continue;
+        const uint4 val = *reinterpret_cast<const uint4*>(pub_stage + ((size_t)j * kBM * esz) + ch * 16);
+        const size_t off = (((size_t)p.ar_rank * M + tok) * N + a0) * esz + (size_t)ch * 16;
+#pragma unroll
+        for (int d = 0; d < 8; ++d)
+          if (d < p.ar_world) *reinterpret_cast<uint4*>(peer_buf[d] + off) = val;
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < p.ar_world && !aborted) red_release_sys_add(p.ar_flags[tid] + p.ar_cnt_base + p.ar_rank, 1u);
   } else if (p.ar_world > 1) {
     // Publish this CTA's share of the tile to every rank, wait (bounded) for
     // every rank's share, then reduce in rank order and add the residual.
@@ -858,6 +904,7 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   int stage_bytes = a_tiles * kATileBytes + b_tiles * pl->bn * kBK * 2;
   if (g->w_int8) stage_bytes += (dual ? 2 : 1) * (swap ? kBM : pl->bn) * kBK;   // int8 staging tiles
   const int ctl_bytes = (int)sizeof(GemmSmemCtl) + 64;
+  const bool publish = g->ar_world > 1 && g->ar_publish && swap;
   static const int env_smem_kb = [] { const char* e = getenv("RF_GEMM_SMEM_KB"); return e ? atoi(e) : 0; }();
 
   // shared-memory plan for a given split count and ring budget
@@ -865,8 +912,10 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
     int st = (budget - ctl_bytes) / stage_bytes;
     st = std::min(st, kMaxStages);
     st = std::min(st, std::max(2, ceil_div(pl->k_blocks, S)));
-    // the split-K partial ([columns][128] fp32 per accumulator) reuses the stage ring
-    const int part = S > 1 ? pl->bn * (dual ? 2 : 1) * kBM * 4 : 0;
+    // the split-K partial ([columns][128] fp32 per accumulator) reuses the stage ring; the publish path parks this
+    // CTA's finished rows behind it (peers still read the partial over DSMEM while the rows are pushed)
+    int part = S > 1 ? pl->bn * (dual ? 2 : 1) * kBM * 4 : 0;
+    if (S > 1 && publish) part += ceil_div(pl->bn, S) * kBM * (g->M <= RF_AR_F32_MAX_ROWS ? 4 : 2);
     *stages_out = st;
     *part_out = part;
     return (size_t)round_up(std::max(st * stage_bytes, part), 1024) + ctl_bytes;
@@ -989,6 +1038,9 @@ static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream)
   }
   p.ar_two_shot = (g->ar_world > 1 && !SWAP && g->M > 256) ? 1 : 0;
   p.ar_flag2_base = g->ar_flag_count / 2;
+  p.ar_publish = (g->ar_world > 1 && g->ar_publish && SWAP) ? 1 : 0;
+  p.ar_cnt_base = g->ar_cnt_base;
+  p.ar_stage_off = pl.splits > 1 ? pl.bn * (DUAL ? 2 : 1) * kBM * 4 : 0;
   RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.grid_x, pl.grid_y, pl.splits), dim3(W8 ? 256 : 128), pl.smem_bytes, stream,
                                pl.splits, tmA, tmB, tmW, p));
   ::rf::count_launch();
@@ -1013,6 +1065,13 @@ static int check_gemm(const RfGemm* g) {
                                      : (uint64_t)g->ar_world * g->M * g->N * sizeof(float);
     RF_REQUIRE(need <= g->ar_recv_bytes, "all-reduce receive buffer too small for %dx%d: need %llu B, have %llu B",
                g->M, g->N, (unsigned long long)need, (unsigned long long)g->ar_recv_bytes);
+    if (g->ar_publish) {
+      RF_REQUIRE(g->M <= 256 && g->force_swap != 0, "ar_publish is the path for at most 256 tokens (got %d)", g->M);
+      RF_REQUIRE(g->N % 8 == 0 && g->dual_offset == 0, "ar_publish needs N %% 8 == 0 and a single accumulator");
+      RF_REQUIRE(g->ar_cnt_base >= 0 && g->ar_cnt_base + g->ar_world <= g->ar_flag_count + 64,
+                 "ar_publish arrival counters [%d, %d) lie outside the flag array", g->ar_cnt_base,
+                 g->ar_cnt_base + g->ar_world);
+    }
   }
   return RF_OK;
 }
@@ -1027,14 +1086,21 @@ extern "C" uint64_t rf_pack_weight_bytes(int64_t rows, int64_t K, int32_t sectio
   return (uint64_t)(tiles * kb) * kBM * kBK * (uint64_t)elem_bytes;
 }
 
+namespace rf { void gemm_sk_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* flags); }
+
 extern "C" int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem_count) {
   int rc = check_gemm(g);
   if (rc) return rc;
   GemmPlan pl;
   rc = plan_gemm(g, &pl);
   if (rc) return rc;
-  if (ws_bytes) *ws_bytes = pl.ws_bytes;
-  if (sem_count) *sem_count = pl.sem_count;
+  // the persistent stream-K kernel (small token counts) parks partial tiles in global scratch, one slot and one
+  // flag per CTA; a caller that provides them gets that kernel
+  uint64_t sk_ws = 0;
+  int32_t sk_flags = 0;
+  if (!g->w_int8) rf::gemm_sk_scratch(g, &sk_ws, &sk_flags);
+  if (ws_bytes) *ws_bytes = std::max<uint64_t>(pl.ws_bytes, sk_ws);
+  if (sem_count) *sem_count = std::max<int32_t>(pl.sem_count, sk_flags);
   return RF_OK;
 }
 
@@ -1044,6 +1110,9 @@ extern "C" int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem
 extern "C" int rf_gemm_plan_info(const RfGemm* g, int32_t* out);
 
 namespace rf {
+bool gemm_sk_eligible(const RfGemm* g, int* ctas);               // gemm_sk.cu: persistent stream-K kernel for small M
+void gemm_sk_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* flags);
+int launch_gemm_sk(const RfGemm* g, cudaStream_t stream);
 bool gemm_ps_eligible(const RfGemm* g, bool swap, int splits);   // gemm_ps.cu: persistent kernel for large M
 int launch_gemm_ps(const RfGemm* g, cudaStream_t stream);
 int widen_packed(const void* src, void* dst, int64_t blocks, int dtype, cudaStream_t stream);   // gemm_ps.cu
@@ -1052,6 +1121,7 @@ int widen_packed(const void* src, void* dst, int64_t blocks, int dtype, cudaStre
 static int run_gemm(const RfGemm* g, cudaStream_t stream, bool w8) {
   int rc = check_gemm(g);
   if (rc) return rc;
+  if (!w8 && rf::gemm_sk_eligible(g, nullptr)) return rf::launch_gemm_sk(g, stream);
   GemmPlan pl;
   rc = plan_gemm(g, &pl);
   if (rc) return rc;
@@ -1102,8 +1172,20 @@ extern "C" int rf_gemm_plan_info(const RfGemm* g, int32_t* out) {
   out[0] = pl.swap; out[1] = pl.bn; out[2] = pl.splits; out[3] = pl.stages; out[4] = pl.grid_x; out[5] = pl.grid_y;
   out[6] = (int32_t)pl.smem_bytes; out[7] = pl.k_blocks;
   out[8] = (!g->w_int8 && g->force_splits == 0 && g->force_bn == 0 && rf::gemm_ps_eligible(g, pl.swap != 0, pl.splits)) ? 1 : 0;
+  if (!g->w_int8 && rf::gemm_sk_eligible(g, nullptr)) out[8] = 2;   // persistent stream-K kernel
   out[9] = (g->ar_world > 1 && !pl.swap && g->M > 256) ? 1 : 0;
   return RF_OK;
+}
+
+extern "C" int rf_gemm_grid_ctas(const RfGemm* g) {
+  int rc = check_gemm(g);
+  if (rc) return rc;
+  int sk_ctas = 0;
+  if (!g->w_int8 && rf::gemm_sk_eligible(g, &sk_ctas)) return sk_ctas;
+  GemmPlan pl;
+  rc = plan_gemm(g, &pl);
+  if (rc) return rc;
+  return pl.grid_x * pl.grid_y * pl.splits;
 }
 
 extern "C" int rf_gemm(const RfGemm* g, rf_stream_t stream) {

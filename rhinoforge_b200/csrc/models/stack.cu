@@ -2,8 +2,11 @@
 // operation is one of the kernels in ../kernels, enqueued on the caller's stream.
 #include "stack.h"
 
+#include <stdlib.h>
+
 #include <algorithm>
 #include <memory>
+#include <string>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -29,8 +32,10 @@ struct Stack {
   uint8_t* base = nullptr;
   uint64_t bytes = 0;
   uint64_t off_xn = 0, off_attn = 0, off_tmp = 0, off_wide = 0, off_conv = 0, off_head_xn = 0, off_logits = 0,
-           off_argmax = 0, off_attn_ws = 0, off_wscratch = 0, off_moe = 0, off_status = 0, total = 0;
-  uint64_t attn_ws_bytes = 0, argmax_bytes = 0, wscratch_bytes = 0;
+           off_argmax = 0, off_attn_ws = 0, off_wscratch = 0, off_moe = 0, off_sk_ws = 0, off_sk_flags = 0,
+           off_status = 0, total = 0;
+  uint64_t attn_ws_bytes = 0, argmax_bytes = 0, wscratch_bytes = 0, sk_ws_bytes = 0;
+  static constexpr int kSkFlags = 1024;
 
   int qkv_dim() const { return (cfg.Hq + 2 * cfg.Hkv) * cfg.hd + (cfg.attn_gate ? cfg.Hq * cfg.hd : 0); }
   // Gated-DeltaNet geometry
@@ -72,6 +77,14 @@ struct Stack {
     off_moe = o;
     if (cfg.moe_experts > 0)
       o += al(T * (uint64_t)moe_ld() * e * 2) + al(T * (uint64_t)std::max(cfg.moe_top_k, 1) * 8);
+    // persistent stream-K GEMM (at most 256 tokens): one fp32 partial slot (two accumulators of up to 256 token
+    // columns x 128 features) and one flag per CTA; the flags start at zero and every launch leaves them at zero
+    {
+      const uint64_t bn = (uint64_t)((std::min(cfg.max_tokens, 256) + 15) / 16 * 16);
+      sk_ws_bytes = (uint64_t)sm_count() * 2 * bn * 128 * sizeof(float);
+    }
+    off_sk_ws = o; o += al(sk_ws_bytes);
+    off_sk_flags = o; o += al(kSkFlags * sizeof(uint32_t));
     off_status = o; o += al(kStatusWords * sizeof(int32_t));
     total = o;
   }
@@ -95,10 +108,21 @@ static int act_of(int mlp_kind) {
   return kActNone;
 }
 
-// One linear layer: picks GEMV / tcgen05 GEMM / W8A16 and wires the fused all-reduce.
+// Tensor-parallel all-reduce form for at most 256 tokens: "publish" (default) = the row-parallel GEMM pushes its
+// partial rows and exits, rf_ar_consume waits, reduces, adds the residual and applies the next RMSNorm;
+// RF_TP_AR=inkernel keeps wait + reduction inside the GEMM's epilogue (A/B timing).
+static bool tp_publish_enabled() {
+  static const bool v = [] { const char* e = getenv("RF_TP_AR"); return !(e && std::string(e) == "inkernel"); }();
+  return v;
+}
+
+// One linear layer: picks GEMV / tcgen05 GEMM / W8A16 and wires the fused all-reduce.  pub_ctas != null asks for
+// the publish-and-exit form: *pub_ctas receives the CTA count the consumer must wait for, or 0 when the shape took
+// the in-kernel form after all (more than 256 tokens), in which case `out` and `residual` were used as given.
 static int linear(const Stack& s, const void* x, int64_t ldx, const void* w, const void* scale,
                   const void* bias, void* out, int64_t ldo, const void* residual, int64_t ldr, int M,
-                  int N, int K, int act, int dual_offset, bool all_reduce, cudaStream_t st) {
+                  int N, int K, int act, int dual_offset, bool all_reduce, cudaStream_t st,
+                  int* pub_ctas = nullptr) {
   RfGemm g = {};
   g.x = x; g.ldx = ldx; g.w = w; g.ldw = K; g.out = out; g.ldo = ldo;
   g.residual = residual; g.ldr = ldr; g.bias = bias; g.scale = scale;
@@ -111,16 +135,69 @@ static int linear(const Stack& s, const void* x, int64_t ldx, const void* w, con
   }
   g.status = s.status();
   g.force_swap = -1;
+  g.ws = s.at<float>(s.off_sk_ws); g.ws_bytes = s.sk_ws_bytes;
+  g.sem = s.at<uint32_t>(s.off_sk_flags); g.sem_count = Stack::kSkFlags;
   const bool ar = all_reduce && s.cfg.tp_world > 1;
   if (ar) {
     if (!s.has_comm) return fail(RF_ERR_STATE, "tensor-parallel stack has no comm buffers bound");
     g.ar_world = s.cfg.tp_world; g.ar_rank = s.cfg.tp_rank;
     g.ar_recv = s.comm.recv; g.ar_flags = s.comm.flags; g.ar_state = s.comm.state;
     g.ar_recv_bytes = s.comm.recv_half_bytes; g.ar_flag_count = s.comm.flag_count;
+    if (pub_ctas) {
+      *pub_ctas = 0;
+      if (M <= 256 && N % 8 == 0 && dual_offset == 0) {
+        g.ar_publish = 1;
+        g.ar_cnt_base = s.comm.cnt_base;
+        const int ctas = rf_gemm_grid_ctas(&g);
+        if (ctas < 0) return ctas;
+        *pub_ctas = ctas;
+      }
+    }
+  } else if (pub_ctas) {
+    *pub_ctas = 0;
   }
   if (!ar && !g.w_packed && M <= 8 && (M <= s.cfg.decode_gemv_max_m) && K % (g.w_int8 ? 16 : 8) == 0) return rf_gemv(&g, st);
   if (g.w_int8) return rf_gemm_w8a16(&g, st);
   return rf_gemm(&g, st);
+}
+
+// Finish a published all-reduce: out = sum of the ranks' partial rows (+ residual), and when norm_w is given the
+// RMSNorm of the finished rows into norm_out (the stack's plain or Gemma-style RMSNorm).
+static int consume(const Stack& s, int pub_ctas, const void* residual, void* out, int M, const void* norm_w,
+                   void* norm_out, cudaStream_t st) {
+  RfArConsume a = {};
+  a.M = M; a.N = s.cfg.hidden; a.world = s.cfg.tp_world; a.rank = s.cfg.tp_rank;
+  a.ar_recv = s.comm.recv; a.ar_flags = s.comm.flags; a.ar_state = s.comm.state;
+  a.ar_recv_bytes = s.comm.recv_half_bytes; a.ar_cnt_base = s.comm.cnt_base; a.pub_ctas = pub_ctas;
+  a.residual = residual; a.ldr = s.cfg.hidden; a.out = out; a.ldo = s.cfg.hidden;
+  if (norm_w) {
+    a.norm_w = norm_w; a.norm_out = norm_out; a.ldn = s.cfg.hidden; a.eps = s.cfg.eps;
+    a.norm_mode = s.cfg.norm_kind == RF_NORM_RMS_GEMMA ? 2 : 1;
+  }
+  a.status = s.status(); a.dtype = s.cfg.dtype;
+  return rf_ar_consume(&a, st);
+}
+
+// Row-parallel projection + all-reduce (+ residual into `out` when residual != null).  With tensor parallelism and
+// at most 256 tokens this is GEMM(publish) + consume, and the RMSNorm that follows in the layer (next_norm_w, result
+// in next_xn) rides in the consumer: *normed tells the caller that next_xn is valid.
+static int linear_ar(const Stack& s, const void* x, int64_t ldx, const void* w, const void* scale, const void* bias,
+                     void* out, const void* residual, int M, int K, const void* next_norm_w, void* next_xn,
+                     bool* normed, cudaStream_t st) {
+  const int H = s.cfg.hidden;
+  if (normed) *normed = false;
+  if (s.cfg.tp_world > 1 && tp_publish_enabled()) {
+    int ctas = 0;
+    int rc = linear(s, x, ldx, w, scale, bias, out, H, residual, residual ? H : 0, M, H, K, kActNone, 0, true, st, &ctas);
+    if (rc) return rc;
+    if (ctas > 0) {
+      rc = consume(s, ctas, residual, out, M, next_norm_w, next_xn, st);
+      if (rc) return rc;
+      if (normed && next_norm_w) *normed = true;
+    }
+    return RF_OK;
+  }
+  return linear(s, x, ldx, w, scale, bias, out, H, residual, residual ? H : 0, M, H, K, kActNone, 0, true, st);
 }
 
 static int norm(const Stack& s, const void* x, const void* w, const void* b, void* y, int rows,
@@ -157,13 +234,21 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
   const bool side = c.gated_residual || c.sandwich_norm;  // sublayer output goes to tmp first
   int rc;
 
+  // A plain RMSNorm that follows an all-reduce can ride in the all-reduce's consumer (linear_ar)
+  const bool norm_rides = !side && (c.norm_kind == RF_NORM_RMS || c.norm_kind == RF_NORM_RMS_GEMMA);
+  bool have_xn = false;     // xn already holds this layer's first norm (written by the previous layer's consumer)
+
   for (int l = lb; l < le; ++l) {
     const RfLayerWeights& w = s.layers[l];
     const uint8_t* mod1 = f.mod ? (const uint8_t*)f.mod + ((size_t)(l * 2 + 0) * nmods) * 3 * H * esz : nullptr;
     const uint8_t* mod2 = f.mod ? (const uint8_t*)f.mod + ((size_t)(l * 2 + 1) * nmods) * 3 * H * esz : nullptr;
     // ---- token mixer: softmax attention or Gated-DeltaNet
-    rc = norm(s, f.hidden, w.norm1_w, w.norm1_b, xn, T, mod1, f.rows_per_mod, st);
-    if (rc) return rc;
+    if (!have_xn) {
+      rc = norm(s, f.hidden, w.norm1_w, w.norm1_b, xn, T, mod1, f.rows_per_mod, st);
+      if (rc) return rc;
+    }
+    have_xn = false;
+    bool have_xn2 = false;  // xn holds the second norm (written by the attention all-reduce's consumer)
     const void* mix_out = attn;      // input of the output projection
     int mix_dim = AD;
     if (w.mixer == 1) {
@@ -261,14 +346,15 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     const bool fuse_gate = c.gated_residual && !c.sandwich_norm && f.rows_per_mod >= T && !c.weights_int8 &&
                            c.tp_world == 1 && f.mod != nullptr;
     if (!side) {
-      rc = linear(s, mix_out, mix_dim, w.wo, w.so, w.bo, f.hidden, H, f.hidden, H, T, H, mix_dim, kActNone, 0, true, st);
+      rc = linear_ar(s, mix_out, mix_dim, w.wo, w.so, w.bo, f.hidden, f.hidden, T, mix_dim,
+                     norm_rides ? w.norm2_w : nullptr, xn, &have_xn2, st);
       if (rc) return rc;
     } else if (fuse_gate && !w.bo) {
       rc = linear(s, mix_out, mix_dim, w.wo, mod1 + (size_t)2 * H * esz, nullptr, f.hidden, H, f.hidden, H, T, H, mix_dim,
                   kActNone, 0, true, st);
       if (rc) return rc;
     } else {
-      rc = linear(s, mix_out, mix_dim, w.wo, w.so, w.bo, tmp, H, nullptr, 0, T, H, mix_dim, kActNone, 0, true, st);
+      rc = linear_ar(s, mix_out, mix_dim, w.wo, w.so, w.bo, tmp, nullptr, T, mix_dim, nullptr, nullptr, nullptr, st);
       if (rc) return rc;
       if (c.sandwich_norm) {
         rc = rf_rmsnorm(tmp, nullptr, w.post_attn_norm_w, tmp, nullptr, nullptr, 1, T, H, H, H, c.eps,
@@ -280,8 +366,10 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
       if (rc) return rc;
     }
     // ---- MLP block
-    rc = norm(s, f.hidden, w.norm2_w, w.norm2_b, xn, T, mod2, f.rows_per_mod, st);
-    if (rc) return rc;
+    if (!have_xn2) {
+      rc = norm(s, f.hidden, w.norm2_w, w.norm2_b, xn, T, mod2, f.rows_per_mod, st);
+      if (rc) return rc;
+    }
     const bool moe = c.moe_experts > 0 && w.moe_router_w != nullptr;
     void* moe_dense = nullptr;
     if (moe) {
@@ -307,15 +395,18 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
       rc = rf_moe_scale_blocks(wide, I, moe_dense, s.moe_ld(), T, c.moe_experts, c.moe_expert_inter, c.dtype, st);
       if (rc) return rc;
     }
+    // the next layer's first norm can ride in this all-reduce unless something still changes hidden in between
+    const bool hook_after = (f.deepstack && l < f.n_deepstack && f.deepstack[l]);
+    const void* next_w = (norm_rides && l + 1 < le && !hook_after) ? s.layers[l + 1].norm1_w : nullptr;
     if (!side) {
-      rc = linear(s, wide, I, w.w_down, w.s_down, w.b_down, f.hidden, H, f.hidden, H, T, H, I, kActNone, 0, true, st);
+      rc = linear_ar(s, wide, I, w.w_down, w.s_down, w.b_down, f.hidden, f.hidden, T, I, next_w, xn, &have_xn, st);
       if (rc) return rc;
     } else if (fuse_gate && !w.b_down) {
       rc = linear(s, wide, I, w.w_down, mod2 + (size_t)2 * H * esz, nullptr, f.hidden, H, f.hidden, H, T, H, I, kActNone,
                   0, true, st);
       if (rc) return rc;
     } else {
-      rc = linear(s, wide, I, w.w_down, w.s_down, w.b_down, tmp, H, nullptr, 0, T, H, I, kActNone, 0, true, st);
+      rc = linear_ar(s, wide, I, w.w_down, w.s_down, w.b_down, tmp, nullptr, T, I, nullptr, nullptr, nullptr, st);
       if (rc) return rc;
       if (c.sandwich_norm) {
         rc = rf_rmsnorm(tmp, nullptr, w.post_mlp_norm_w, tmp, nullptr, nullptr, 1, T, H, H, H, c.eps,
@@ -527,5 +618,5 @@ extern "C" void rf_struct_sizes(int32_t* out) {
   out[0] = (int32_t)sizeof(RfGemm); out[1] = (int32_t)sizeof(RfRopeKv); out[2] = (int32_t)sizeof(RfAttn);
   out[3] = (int32_t)sizeof(RfStackConfig); out[4] = (int32_t)sizeof(RfLayerWeights);
   out[5] = (int32_t)sizeof(RfStackComm); out[6] = (int32_t)sizeof(RfStackForward); out[7] = 0;
-  out[8] = (int32_t)sizeof(RfConv1d); out[9] = (int32_t)sizeof(RfGdn); out[10] = 0;
+  out[8] = (int32_t)sizeof(RfConv1d); out[9] = (int32_t)sizeof(RfGdn); out[10] = (int32_t)sizeof(RfArConsume);
 }

@@ -84,6 +84,7 @@ typedef struct RfStackComm {
   uint32_t* state;         // local [4]
   uint64_t recv_half_bytes;
   int32_t flag_count;
+  int32_t cnt_base;        // first of `world` arrival counters in every rank's flag array (publish / consume all-reduce)
 } RfStackComm;
 
 typedef struct RfStackForward {

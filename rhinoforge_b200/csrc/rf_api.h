@@ -62,6 +62,11 @@ typedef struct RfGemm {
   // the bytes of the int8 image.  Null: the int8 tile is widened inside the main loop for every token count.
   void* w_scratch;
   uint64_t w_scratch_bytes;
+  // Tensor parallel, at most 256 tokens: 1 = "publish and exit".  The epilogue only pushes this rank's partial
+  // rows (16-byte vectors) into every rank's receive buffer and bumps counter ar_cnt_base + ar_rank on every rank;
+  // it does not wait, reduce, add the residual or write `out`.  rf_ar_consume() finishes the all-reduce.
+  int32_t ar_publish;
+  int32_t ar_cnt_base;         // first of `world` arrival counters in every rank's flag array
 } RfGemm;
 // bytes of the tile-major image of a [rows, K] weight with `sections` equal row sections
 uint64_t rf_pack_weight_bytes(int64_t rows, int64_t K, int32_t sections, int32_t elem_bytes);
@@ -77,6 +82,32 @@ int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem_count);
 int rf_gemm_w8a16(const RfGemm* g, rf_stream_t stream);
 // CUDA-core skinny GEMM (M <= 8): reference path and small-batch decode.
 int rf_gemv(const RfGemm* g, rf_stream_t stream);
+// CTAs of the launch rf_gemm / rf_gemm_w8a16 would make for this shape (each bumps the arrival counters once when
+// ar_publish is set); negative RfError on a bad shape.  Host-only.
+int rf_gemm_grid_ctas(const RfGemm* g);
+
+// Second half of the tensor-parallel all-reduce of a row-parallel GEMM launched with ar_publish: waits (bounded)
+// until every rank's arrival counter shows that all `pub_ctas` CTAs of its GEMM have published, sums the ranks'
+// partial rows in rank order in fp32, adds the residual, writes `out`, and optionally applies the RMSNorm that
+// follows in the layer (norm_mode 1: w * norm(x), 2: (1 + w) * norm(x)) into norm_out.  out may alias residual.
+// Partials are fp32 up to RF_AR_F32_MAX_ROWS rows and the activation dtype above.
+#define RF_AR_F32_MAX_ROWS 16
+typedef struct RfArConsume {
+  int32_t M, N;                // rows (tokens) and columns (hidden size); N a multiple of 8
+  int32_t world, rank;
+  void* const* ar_recv;        // device array [world] of receive-buffer bases (only [rank] is read here)
+  uint32_t* const* ar_flags;   // device array [world] of flag-array bases (only [rank] is read here)
+  uint32_t* ar_state;          // local state words: [0] call counter, [4] counter value consumed so far, [5] finished CTAs
+  uint64_t ar_recv_bytes;      // bytes of one half of the double-buffered receive buffer
+  int32_t ar_cnt_base;
+  int32_t pub_ctas;            // rf_gemm_grid_ctas() of the producing GEMM
+  const void* residual; int64_t ldr;   // optional
+  void* out; int64_t ldo;
+  const void* norm_w; void* norm_out; int64_t ldn;   // optional fused RMSNorm of the finished rows
+  float eps; int32_t norm_mode;
+  int32_t* status; int32_t dtype;
+} RfArConsume;
+int rf_ar_consume(const RfArConsume* a, rf_stream_t stream);
 
 
 // ------------------------------------------------------ norms / glue ----

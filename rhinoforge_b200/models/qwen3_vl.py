@@ -179,6 +179,38 @@ class Qwen3VLEngine:
         self._next_pos = int(pos3.max()) + 1
         return self.text.extend([ids], return_logits=return_logits, positions3=[pos3])
 
+    @torch.no_grad()
+    def prefill_batch(self, input_ids: Sequence[torch.Tensor], pixel_values: Sequence[torch.Tensor],
+                      image_grid_thw: Sequence, *, return_logits: bool = False):
+        """Start sequences ``0..B-1`` from empty, each with its own multimodal prompt: the images of the whole batch go
+        through the vision tower as ONE packed pass, every sequence gets its own embeddings, three-axis positions
+        and DeepStack rows, and the text decoder prefills all of them as one packed varlen launch.  Returns the greedy
+        next token of every sequence (with ``return_logits`` also the last-row logits)."""
+        self.text.reset()
+        B = len(input_ids)
+        merge2 = self.vcfg.spatial_merge_size ** 2
+        grids = [[tuple(int(v) for v in g) for g in torch.as_tensor(gr).tolist()] for gr in image_grid_thw]
+        img, feats = self.vision(torch.cat([p.to(self.device) for p in pixel_values]), [g for gr in grids for g in gr])
+        embeds, pos3s, deeps, o = [], [], [], 0
+        for s in range(B):
+            ids = input_ids[s].flatten().to("cpu")
+            is_vis = ids == self.image_token_id
+            n_img = sum(t * h * w for t, h, w in grids[s]) // merge2
+            rows = is_vis.nonzero().flatten()
+            if rows.numel() != n_img:
+                raise RPUBackendError(f"sequence {s}: {rows.numel()} image placeholder tokens but {n_img} image embeddings")
+            e = torch.empty((ids.numel(), self.cfg.hidden_size), dtype=self.dtype, device=self.device)
+            K.embedding(self.text.embed, ids.to(self.device, torch.int32), out=e, scale=self.cfg.embed_scale,
+                        row_scale=self.text.embed_scale_rows)
+            K.scatter_rows(e, img[o:o + n_img], rows.to(self.device, torch.int32))
+            embeds.append(e)
+            pos3s.append(rope_index(is_vis.to(torch.int32).tolist(), grids[s], self.vcfg.spatial_merge_size))
+            deeps.append((rows, [f[o:o + n_img] for f in feats]))
+            o += n_img
+        self._next_pos = max(int(p.max()) for p in pos3s) + 1
+        return self.text.extend([t.flatten() for t in input_ids], return_logits=return_logits, inputs_embeds=embeds,
+                                positions3=pos3s, deepstack=deeps)
+
     def decode(self, n_steps: int, **kw) -> torch.Tensor:
         out = self.text.decode(n_steps, **kw)
         self._next_pos += n_steps

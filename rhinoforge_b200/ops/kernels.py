@@ -80,7 +80,9 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          act: Optional[str] = None, dual: bool = False, status: Optional[torch.Tensor] = None,
          force_splits: int = 0, force_swap: int = -1, force_bn: int = 0, use_gemv: bool = False,
          ws: Optional[torch.Tensor] = None, sem: Optional[torch.Tensor] = None,
-         comm=None, packed_shape: Optional[tuple] = None, w_scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+         comm=None, packed_shape: Optional[tuple] = None, w_scratch: Optional[torch.Tensor] = None,
+         publish: bool = False, norm_w: Optional[torch.Tensor] = None, norm_out: Optional[torch.Tensor] = None,
+         norm_eps: float = 1e-6, norm_gemma: bool = False) -> torch.Tensor:
     """``out = epilogue(x @ w.T)`` on the tcgen05 kernel (or the CUDA-core GEMV).
 
     ``dual=True``: ``w`` stacks ``[gate; up]`` (2N rows) and ``act`` is a ``*_mul``
@@ -89,6 +91,9 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     ``comm``: a :class:`rhinoforge_b200.parallel.symm.CommBuffers` for the fused all-reduce.
     ``w_scratch``: device bytes (twice the packed int8 image) that let a W8A16 GEMM of more than 256 tokens widen the
     weights once and run the 16-bit kernels.
+    ``publish`` (with ``comm``, at most 256 rows): the GEMM only pushes its partial rows to the peers and exits;
+    ``rf_ar_consume`` then waits, reduces, adds ``residual`` and, with ``norm_w`` / ``norm_out``, writes the RMSNorm of
+    the finished rows (``norm_gemma``: ``(1 + w)`` weights).
     """
     M, K = x.shape
     if packed_shape is not None:          # ``w`` is the tile-major image made by pack_weight(); (rows, K) is its logical shape
@@ -124,6 +129,13 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
         return out
     if comm is not None:
         comm.fill(g)
+    if publish:
+        if comm is None:
+            raise ValueError("publish=True needs comm buffers")
+        g.ar_publish = 1
+        ctas = lib.rf_gemm_grid_ctas(C.byref(g))
+        if ctas <= 0:
+            N.check(ctas, "rf_gemm_grid_ctas")
     need_ws, need_sem = C.c_uint64(0), C.c_int32(0)
     g.ws_bytes = 2 ** 64 - 1
     N.check(lib.rf_gemm_scratch(C.byref(g), C.byref(need_ws), C.byref(need_sem)), "rf_gemm_scratch")
@@ -137,6 +149,10 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
         N.check(lib.rf_gemm_w8a16(C.byref(g), _stream()), "rf_gemm_w8a16")
     else:
         N.check(lib.rf_gemm(C.byref(g), _stream()), "rf_gemm")
+    if publish:
+        a = comm.consume_args(M, Nn, ctas, out, residual=residual, norm_w=norm_w, norm_out=norm_out, eps=norm_eps,
+                              norm_mode=0 if norm_w is None else (2 if norm_gemma else 1), status=status)
+        N.check(lib.rf_ar_consume(C.byref(a), _stream()), "rf_ar_consume")
     return out
 
 

@@ -18,6 +18,7 @@ from typing import Optional
 import torch
 
 from .. import _native as N
+from .. import _native as N_    # the same module under a name that an argument called N cannot shadow
 
 
 @dataclass
@@ -138,7 +139,8 @@ class CommBuffers:
     """
 
     FLAG_COUNT = 1 << 20
-    BARRIER_FLAGS = 64  # the last flags are reserved for the stand-alone barrier and the arg-max merge
+    BARRIER_FLAGS = 64  # the last flags are reserved: barrier [0, 8), arg-max merge [16, 24), arrival counters [32, 40)
+    CNT_OFFSET = 32     # arrival counters of the publish / consume all-reduce, one per source rank
     AUX_ROWS = 1024     # rows of (value, id) pairs per rank in the aux area
 
     def __init__(self, tp: TPContext, recv_half_bytes: int):
@@ -182,13 +184,36 @@ class CommBuffers:
         g.ar_state = self.state_ptr
         g.ar_recv_bytes = self.recv_half_bytes
         g.ar_flag_count = self.FLAG_COUNT - self.BARRIER_FLAGS
+        g.ar_cnt_base = self.cnt_base
 
     def stack_comm(self) -> "N.RfStackComm":
         c = N.RfStackComm()
         c.recv, c.flags, c.state = self.recv_ptrs.data_ptr(), self.flag_ptrs.data_ptr(), self.state_ptr
         c.recv_half_bytes = self.recv_half_bytes
         c.flag_count = self.FLAG_COUNT - self.BARRIER_FLAGS
+        c.cnt_base = self.cnt_base
         return c
+
+    @property
+    def cnt_base(self) -> int:
+        return self.FLAG_COUNT - self.BARRIER_FLAGS + self.CNT_OFFSET
+
+    def consume_args(self, M: int, N: int, pub_ctas: int, out: torch.Tensor, residual=None, norm_w=None,
+                     norm_out=None, eps: float = 1e-6, norm_mode: int = 0, status=None) -> "N.RfArConsume":
+        """Argument block of ``rf_ar_consume`` for a GEMM launched with ``ar_publish`` on these buffers."""
+        a = N_.RfArConsume()
+        a.M, a.N, a.world, a.rank = M, N, self.tp.world, self.tp.rank
+        a.ar_recv, a.ar_flags, a.ar_state = self.recv_ptrs.data_ptr(), self.flag_ptrs.data_ptr(), self.state_ptr
+        a.ar_recv_bytes, a.ar_cnt_base, a.pub_ctas = self.recv_half_bytes, self.cnt_base, pub_ctas
+        if residual is not None:
+            a.residual, a.ldr = residual.data_ptr(), residual.stride(0)
+        a.out, a.ldo = out.data_ptr(), out.stride(0)
+        if norm_w is not None:
+            a.norm_w, a.norm_out, a.ldn = norm_w.data_ptr(), norm_out.data_ptr(), norm_out.stride(0)
+            a.eps, a.norm_mode = eps, norm_mode
+        a.status = (status if status is not None else self.status).data_ptr()
+        a.dtype = 0 if out.dtype == torch.float16 else 1
+        return a
 
     def device_barrier(self) -> None:
         """Bounded device-side barrier over the peer flags (set-up and tests)."""

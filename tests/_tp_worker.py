@@ -47,6 +47,41 @@ def main() -> int:
     same = all(torch.equal(y_all[0], t) for t in y_all)
     ok &= same
     report["bit_identical_across_ranks"] = same
+    # ---- 1b. publish-and-exit GEMM + consumer kernel (wait, rank-order sum, residual, fused RMSNorm), mixed with the
+    # in-kernel form on the same buffers: both advance the one call counter / double-buffered slot
+    for (M, Nn, Kd, splits, packed, gemma) in [(1, 512, 1024, 0, False, False), (7, 384, 2048, 4, True, False),
+                                               (16, 1024, 1024, 0, True, True), (17, 1024, 1024, 2, True, False),
+                                               (64, 4096, 512, 0, True, False), (33, 256, 4096, 8, False, True),
+                                               (200, 640, 512, 1, True, False), (64, 5120, 1024, 0, True, False)]:
+        x = (torch.randn(M, Kd, device=dev, generator=g) * 0.5).half()
+        w = (torch.randn(Nn, Kd, device=dev, generator=g) * 0.05).half()
+        r = torch.randn(M, Nn, device=dev, generator=g).half()
+        b = torch.randn(Nn, device=dev, generator=g).half()
+        nw = (torch.randn(Nn, device=dev, generator=g) * 0.1 + (0.0 if gemma else 1.0)).half()
+        k0, k1 = R * Kd // W, (R + 1) * Kd // W
+        xs, ws_ = x[:, k0:k1].contiguous(), w[:, k0:k1].contiguous()
+        wk = dict(packed_shape=(Nn, k1 - k0)) if packed else {}
+        wt = K.pack_weight(ws_) if packed else ws_
+        for rep in range(3):
+            xn = torch.zeros(M, Nn, device=dev, dtype=torch.float16)
+            y = K.gemm(xs, wt, residual=r, bias=b, comm=comm, status=status, force_splits=splits, publish=True,
+                       norm_w=nw, norm_out=xn, norm_eps=1e-6, norm_gemma=gemma, **wk)
+            if rep == 1:   # an in-kernel all-reduce in between must not disturb the publish / consume bookkeeping
+                K.gemm(xs, ws_, residual=r, comm=comm, status=status)
+            torch.cuda.synchronize()
+            ref = x.float() @ w.float().t() + r.float() + b.float()
+            err = (y.float() - ref).abs().max().item()
+            hq = y.float()
+            nref = hq * torch.rsqrt(hq.pow(2).mean(-1, keepdim=True) + 1e-6) * ((1.0 + nw.float()) if gemma else nw.float())
+            nerr = (xn.float() - nref).abs().max().item()
+            good = err < 2e-2 and nerr < 2e-2 and int(status[0]) == 0 and int(comm.status[0]) == 0
+            ok &= good
+            report["cases"].append({"publish": True, "M": M, "N": Nn, "K": Kd, "splits": splits, "rep": rep, "err": err,
+                                    "norm_err": nerr, "ok": good, "status": status.tolist()[:4]})
+        y_all = tp.all_gather_object((y.cpu(), xn.cpu()))
+        same = all(torch.equal(y_all[0][0], t[0]) and torch.equal(y_all[0][1], t[1]) for t in y_all)
+        ok &= same
+        report["cases"][-1]["bit_identical_across_ranks"] = same
     comm.device_barrier()
     torch.cuda.synchronize()
     ok &= int(comm.status[0]) == 0
@@ -67,8 +102,8 @@ def main() -> int:
     eN.close()
     toks = tp.all_gather_object(tN)
     ranks_agree = all(torch.equal(toks[0], t) for t in toks)
-    # fp32 partial sums in a different order can flip a near-tie; require the first 8 tokens of every sequence
-    match = bool((t1[:, :8] == tN[:, :8]).all())
+    # all 16 tokens of every sequence must equal the single-GPU engine's
+    match = bool((t1 == tN).all())
     report.update({"ranks_agree": ranks_agree, "tp_matches_single": match, "replay_stable": bool(torch.equal(tN, tN2)),
                    "t1": t1.tolist(), "tN": tN.tolist()})
     ok &= ranks_agree and match and torch.equal(tN, tN2)

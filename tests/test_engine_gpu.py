@@ -167,7 +167,7 @@ def test_engine_over_an_interleaved_oversubscribed_page_table():
     for _ in range(4):                       # four decode calls of 9 steps: every call adds pages to some sequence
         parts.append(eng.decode(9).clone())
     toks = torch.cat(parts, 1)
-    table = eng.cache._pt_host[:, :4].tolist()
+    table = eng.cache._pt_host[:, :8].tolist()
     owned = [eng.cache.owned_pages(s) for s in range(3)]
     assert owned == [(17 + 36 + 1 + 15) // 16, (40 + 36 + 1 + 15) // 16, (5 + 36 + 1 + 15) // 16]
     rows = [table[s][:owned[s]] for s in range(3)]

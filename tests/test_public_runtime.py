@@ -163,7 +163,7 @@ def test_native_struct_layouts_match_ctypes():
     got = [C.sizeof(t) for t in (N.RfGemm, N.RfRopeKv, N.RfAttn, N.RfStackConfig, N.RfLayerWeights, N.RfStackComm,
                                  N.RfStackForward)]
     assert list(sizes)[:7] == got
-    assert list(sizes)[8:10] == [C.sizeof(N.RfConv1d), C.sizeof(N.RfGdn)]
+    assert list(sizes)[8:11] == [C.sizeof(N.RfConv1d), C.sizeof(N.RfGdn), C.sizeof(N.RfArConsume)]
 
 
 def test_torch_ops_rpu_namespace_is_registered_and_runs_on_cpu():
