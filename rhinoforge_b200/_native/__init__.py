@@ -56,6 +56,16 @@ class RfArConsume(C.Structure):
     ]
 
 
+class RfMoeGroupedGemm(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("ldx", C.c_int64), ("w", C.c_void_p), ("out", C.c_void_p), ("ldo", C.c_int64),
+        ("row_scale", C.c_void_p), ("tiles", C.c_void_p),
+        ("max_rows", C.c_int32), ("N", C.c_int32), ("K", C.c_int32), ("dual", C.c_int32), ("act", C.c_int32),
+        ("bank_section_row_tiles", C.c_int32), ("bank_kb_total", C.c_int32),
+        ("rt_per_expert", C.c_int32), ("kb_per_expert", C.c_int32), ("dtype", C.c_int32), ("status", C.c_void_p),
+    ]
+
+
 class RfRopeKv(C.Structure):
     _fields_ = [
         ("qkv", C.c_void_p), ("ld", C.c_int64),

@@ -16,6 +16,13 @@
 // share one weight panel and the activation matrix stays in L2.
 // Scope: tokens on the MMA M axis, tile-major 16-bit weights, no split-K, no fused all-reduce (those shapes
 // stay with gemm_tc.cu).
+//
+// Grouped form (mixture of experts, rf_moe_grouped_gemm): the rows are (token, pick) pairs sorted by expert and
+// the tile list comes from device memory - one entry {expert, first row, end row} per 128-row block of one
+// expert's rows.  A tile reads its rows from the sorted activation matrix and its weight blocks from that
+// expert's row tiles (up / gate projections) or k blocks (down projection) of the one packed expert bank; rows
+// of the block that belong to the next expert are multiplied but never stored.  The number of tiles is only
+// known on the device, so every CTA reads it there: the launch itself is shape-independent and graph-capturable.
 #include "../common/dtype.cuh"
 #include "../common/host_util.h"
 #include "../common/ptx.cuh"
@@ -41,6 +48,11 @@ struct GemmPsParams {
   int pf_blocks;          // k blocks prefetched into L2 ahead of the ring
   int tma_out;            // results leave through shared-memory staging: 1 tiled bulk stores, 2 bulk reduce-adds
                           // into an output that already holds the residual (out == residual)
+  // grouped form: grp[0] = number of row blocks, then {expert, row0, row_end, 0} per block (device memory)
+  const int32_t* grp;
+  int grp_rt_per_expert;  // row tiles of the weight image between two experts (projection whose N axis is split by expert)
+  int grp_kb_per_expert;  // k blocks of the weight image between two experts (projection whose K axis is split by expert)
+  int kb_total;           // k blocks of a row tile of the whole weight image (stride between row tiles)
 };
 
 // Tile order: bands of `band` row tiles; inside a band the row index runs fastest and the weight panel
@@ -53,6 +65,31 @@ __device__ __forceinline__ void ps_tile_coords(const GemmPsParams& p, int tile, 
   const int rows_here = min(p.band, p.tiles_m - b * p.band);
   *tn = r / rows_here;
   *tm = b * p.band + r % rows_here;
+}
+
+// Coordinates of one tile: first activation row, end of the valid rows, weight column tile, and the offsets of
+// the tile's expert inside the packed weight image (zero in the plain form).
+struct PsTile { int row0, row_end, tm, tn, rt_add, kb_add; };
+template <int MT>
+__device__ __forceinline__ PsTile ps_tile(const GemmPsParams& p, int tile) {
+  PsTile t;
+  if (p.grp) {
+    const int entry = tile / p.tiles_n;
+    t.tn = tile - entry * p.tiles_n;
+    const int e = p.grp[1 + 4 * entry];
+    t.row0 = p.grp[2 + 4 * entry];
+    t.row_end = p.grp[3 + 4 * entry];
+    t.tm = 0;
+    t.rt_add = e * p.grp_rt_per_expert;
+    t.kb_add = e * p.grp_kb_per_expert;
+  } else {
+    ps_tile_coords(p, tile, &t.tm, &t.tn);
+    t.row0 = t.tm * MT * kPsBM;
+    t.row_end = p.M;
+    t.rt_add = 0;
+    t.kb_add = 0;
+  }
+  return t;
 }
 
 struct alignas(8) GemmPsCtl {
@@ -79,7 +116,6 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // after the ring: one 4 KB output staging buffer per epilogue warp, then the control block
   uint8_t* epi_stage = smem + (size_t)p.stages * stage_bytes;
   GemmPsCtl* ctl = reinterpret_cast<GemmPsCtl*>(epi_stage + 4 * MT * kPsEpiBytes);
-  const int tiles = p.tiles_m * p.tiles_n;
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -105,30 +141,34 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t tmem_base = ctl->tmem_base;
   pdl_launch_dependents();         // after this CTA owns its TMEM columns
   volatile int32_t* abort_flag = &ctl->abort_flag;
+  // Plain form: the tile count is a launch constant.  Grouped form: it (and the list) was written by the kernel
+  // before this one, so it may only be read after the dependency wait; nothing of a tile is touched before that.
+  auto tile_count = [&]() { return p.grp ? p.grp[0] * p.tiles_n : p.tiles_m * p.tiles_n; };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer ----
     if (lane == 0) {
       const int nsub = bn / 128;
-      auto load_w = [&](int tn, int kb, int s) {
+      auto load_w = [&](const PsTile& t, int kb, int s) {
         uint8_t* sb = smem + (size_t)s * stage_bytes + kAStage;
-        const int rt0 = tn * nsub;
+        const int rt0 = t.tn * nsub + t.rt_add;
 #pragma unroll
         for (int wt = 0; wt < kW; ++wt)
           for (int sub = 0; sub < nsub; ++sub)
             bulk_load_1d(sb + wt * b_bytes + sub * kPsBlock,
-                         p.w_packed + ((size_t)(rt0 + sub + wt * p.dual_tiles) * p.k_blocks + kb) * kPsBlock, kPsBlock,
-                         &ctl->full[s]);
+                         p.w_packed + ((size_t)(rt0 + sub + wt * p.dual_tiles) * p.kb_total + t.kb_add + kb) * kPsBlock,
+                         kPsBlock, &ctl->full[s]);
       };
-      auto load_x = [&](int tm, int kb, int s) {
+      auto load_x = [&](const PsTile& t, int kb, int s) {
 #pragma unroll
         for (int h = 0; h < MT; ++h)   // a half wholly past the last row is zero-filled by the copy engine
           tma_load_2d(smem + (size_t)s * stage_bytes + h * kPsATile, &tmA, &ctl->full[s], kb * kPsBK,
-                      (tm * MT + h) * kPsBM);
+                      t.row0 + h * kPsBM);
       };
       // L2 prefetch cursor: runs p.pf_blocks k blocks ahead of the ring (into the following tiles as well), so
       // the ring's own copies complete with L2 latency and the bytes in flight towards DRAM are not limited by
       // shared memory
+      const int tiles = p.grp ? 0 : p.tiles_m * p.tiles_n;   // the prefetch cursor and the early ring fill are plain-form only
       int pf_tile = blockIdx.x, pf_kb = 0, pf_tm = 0, pf_tn = 0;
       if (pf_tile < tiles) ps_tile_coords(p, pf_tile, &pf_tm, &pf_tn);
       auto prefetch_next = [&](bool weights, bool acts) {
@@ -155,24 +195,24 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       // weights never depend on the previous kernel: the first ring fill starts before the dependency wait
       int it = 0;
       int tile = blockIdx.x;
-      int tm0 = 0, tn0 = 0;
-      if (tile < tiles) ps_tile_coords(p, tile, &tm0, &tn0);
+      PsTile t0 = {};
+      if (tile < tiles) t0 = ps_tile<MT>(p, tile);
       const int first_pre = tile < tiles ? min(p.stages, p.k_blocks) : 0;
       for (int i = 0; i < first_pre; ++i) {
         mbar_arrive_expect_tx(&ctl->full[i], (uint32_t)stage_bytes);
-        load_w(tn0, i, i);
+        load_w(t0, i, i);
       }
       // the cursor passes the blocks the ring has just asked for, then takes its lead (weights only: the
       // activations may still be written by the previous kernel)
       const int lead = p.pf_blocks > 0 ? first_pre + p.pf_blocks : 0;
       for (int i = 0; i < lead; ++i) prefetch_next(i >= first_pre, false);
       pdl_wait();
-      for (int i = 0; i < first_pre; ++i) load_x(tm0, i, i);
+      for (int i = 0; i < first_pre; ++i) load_x(t0, i, i);
       bool ok = true;
       int issued = first_pre;
-      for (; ok && tile < tiles; tile += gridDim.x) {
-        int tm, tn;
-        ps_tile_coords(p, tile, &tm, &tn);
+      const int ntiles = tile_count();
+      for (; ok && tile < ntiles; tile += gridDim.x) {
+        const PsTile t = ps_tile<MT>(p, tile);
         for (int kb = (tile == (int)blockIdx.x ? first_pre : 0); kb < p.k_blocks; ++kb) {
           const int gi = it + kb;                          // global k-block index of this CTA
           const int s = gi % p.stages;
@@ -182,8 +222,8 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             break;
           }
           mbar_arrive_expect_tx(&ctl->full[s], (uint32_t)stage_bytes);
-          load_w(tn, kb, s);
-          load_x(tm, kb, s);
+          load_w(t, kb, s);
+          load_x(t, kb, s);
           if (p.pf_blocks > 0) prefetch_next(true, true);
           issued = gi + 1;
         }
@@ -205,6 +245,7 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t idesc = umma_idesc_f16(kPsBM, bn, Num<T>::kFmt);
       int it = 0, lt = 0;
       bool ok = true;
+      const int tiles = tile_count();
       for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x, ++lt) {
         const int b = lt % nbuf;
         if (!mbar_wait(&ctl->acc_empty[b], (((uint32_t)(lt / nbuf)) & 1u) ^ 1u, kLocalWaitNs, 32)) { ok = false; break; }
@@ -248,20 +289,22 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const T* scale = reinterpret_cast<const T*>(p.scale);
     const T* resid = reinterpret_cast<const T*>(p.residual);
     T* out = reinterpret_cast<T*>(p.out);
-    const int M = p.M, N = p.N;
+    const int N = p.N;
     const bool vec_ok = (p.ldo & 7) == 0 && (!resid || (p.ldr & 7) == 0);
     int lt = 0;
+    const int tiles = tile_count();
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++lt) {
       const int b = lt % nbuf;
-      int tm, tn;
-      ps_tile_coords(p, tile, &tm, &tn);
+      const PsTile pt = ps_tile<MT>(p, tile);
+      const int tn = pt.tn;
+      const int M = pt.row_end;                            // rows at and past it are not this tile's to store
       if (!mbar_wait(&ctl->acc_full[b], (uint32_t)(lt / nbuf) & 1u) || *abort_flag) {
         if (!*abort_flag) report_status(p.status, kStatusEpilogueTimeout, kTagGemmTc, tile);
         ctl->abort_flag = 1;
         break;
       }
       tc_fence_after_sync();
-      const int row = (tm * MT + half) * kPsBM + r;
+      const int row = pt.row0 + half * kPsBM + r;
       const int n_base = tn * bn;
       const uint32_t acc = lane_base + (uint32_t)(b * acc_cols + half * half_cols);
       const float rs = (p.row_scale && row < M) ? p.row_scale[row] : 1.f;
@@ -279,7 +322,7 @@ gemm_ps_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       // L1->L2 path for 67 MB of output).
       const bool tma_out = p.tma_out != 0;
       uint8_t* stg = epi_stage + (size_t)(warp - 2) * kPsEpiBytes;
-      const int row0 = (tm * MT + half) * kPsBM + quarter * 32;
+      const int row0 = pt.row0 + half * kPsBM + quarter * 32;
       auto chunk_begin = [&]() {                       // the previous bulk store has read the staging tile
         if (lane == 0) bulk_wait_read_all();
         __syncwarp();
@@ -414,6 +457,7 @@ static int launch_ps(const RfGemm* g, int bn, cudaStream_t stream) {
   p.status = g->status;
   p.tma_out = tma_out ? (g->residual ? 2 : 1) : 0;
   p.M = g->M; p.N = g->N; p.k_blocks = ceil_div(g->K, kPsBK); p.bn = bn;
+  p.kb_total = p.k_blocks;
   p.act = g->act; p.dual_offset = g->dual_offset; p.dual_tiles = ceil_div(g->N, 128);
   p.tiles_m = ceil_div(g->M, kPsBM * MT); p.tiles_n = ceil_div(g->N, bn);
   const int stage_bytes = MT * kPsATile + (DUAL ? 2 : 1) * bn * kPsBK * 2;
@@ -469,6 +513,40 @@ int launch_gemm_ps(const RfGemm* g, cudaStream_t stream) {
   return launch_ps_t<__nv_bfloat16>(g, dual, bn, rows, stream);
 }
 
+// Grouped (mixture-of-experts) launch: see the file comment.  One accumulator or a GLU pair, 128-row tiles.
+template <typename T, bool DUAL>
+static int launch_ps_grouped(const RfMoeGroupedGemm* a, cudaStream_t stream) {
+  auto kfn = gemm_ps_kernel<T, DUAL, 1>;
+  RF_ALLOW_SMEM_PER_DEVICE(kfn, 227 * 1024);
+  CUtensorMap tmA;
+  int rc = make_tmap_2d(&tmA, a->x, a->dtype, 2, a->K, a->max_rows, a->ldx, kPsBK, kPsBM, true);
+  if (rc) return rc;
+  const int bn = (!DUAL && a->N % 256 == 0) ? 256 : 128;
+  GemmPsParams p = {};
+  p.out = a->out; p.ldo = a->ldo;
+  p.row_scale = a->row_scale;
+  p.w_packed = reinterpret_cast<const uint8_t*>(a->w);
+  p.status = a->status;
+  p.M = a->max_rows; p.N = a->N; p.k_blocks = ceil_div(a->K, kPsBK); p.bn = bn;
+  p.act = a->act; p.dual_offset = DUAL ? a->N : 0; p.dual_tiles = a->bank_section_row_tiles;
+  p.tiles_m = 0; p.tiles_n = ceil_div(a->N, bn);
+  p.band = 1;
+  p.grp = a->tiles; p.grp_rt_per_expert = a->rt_per_expert; p.grp_kb_per_expert = a->kb_per_expert;
+  p.kb_total = a->bank_kb_total;
+  const int stage_bytes = kPsATile + (DUAL ? 2 : 1) * bn * kPsBK * 2;
+  const int ctl_bytes = (int)sizeof(GemmPsCtl) + 1024 + 4 * kPsEpiBytes;
+  p.stages = std::min(kPsMaxStages, (227 * 1024 - ctl_bytes) / stage_bytes);
+  const size_t smem = (size_t)p.stages * stage_bytes + ctl_bytes;
+  RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(sm_count()), dim3(64 + 128), smem, stream, 1, tmA, tmA, p));
+  ::rf::count_launch();
+  return RF_OK;
+}
+
+int launch_moe_grouped(const RfMoeGroupedGemm* a, cudaStream_t stream) {
+  if (a->dtype == 0) return a->dual ? launch_ps_grouped<__half, true>(a, stream) : launch_ps_grouped<__half, false>(a, stream);
+  return a->dual ? launch_ps_grouped<__nv_bfloat16, true>(a, stream) : launch_ps_grouped<__nv_bfloat16, false>(a, stream);
+}
+
 // int8 tile-major weight image -> 16-bit tile-major image (the 128-byte-swizzled block layout the MMA reads).
 // One thread widens eight values: 8 bytes in, 16 bytes out.  Exact in fp16 and bf16 (|q| <= 127).
 template <typename T>
@@ -494,3 +572,16 @@ int widen_packed(const void* src, void* dst, int64_t blocks, int dtype, cudaStre
 }
 
 }  // namespace rf
+
+extern "C" int rf_moe_grouped_gemm(const RfMoeGroupedGemm* a, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(a && a->x && a->w && a->out && a->tiles, "moe_grouped_gemm needs x, w, out and the tile list");
+  RF_REQUIRE(a->max_rows > 0 && a->N > 0 && a->K > 0 && a->K % 8 == 0 && a->ldx % 8 == 0, "moe_grouped_gemm shape %d x %d x %d",
+             a->max_rows, a->N, a->K);
+  RF_REQUIRE(a->dtype == 0 || a->dtype == 1, "moe_grouped_gemm dtype");
+  RF_REQUIRE(a->bank_kb_total > 0 && a->rt_per_expert >= 0 && a->kb_per_expert >= 0, "moe_grouped_gemm bank geometry");
+  RF_REQUIRE((reinterpret_cast<uintptr_t>(a->w) & 127) == 0, "packed expert bank must be 128-byte aligned");
+  if (a->dual) RF_REQUIRE(a->bank_section_row_tiles > 0 && (a->act == rf::kActSiluMul || a->act == rf::kActGeluTanhMul),
+                          "a GLU grouped GEMM needs the section size and a *_mul activation");
+  return rf::launch_moe_grouped(a, static_cast<cudaStream_t>(stream));
+}

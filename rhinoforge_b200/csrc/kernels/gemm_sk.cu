@@ -26,6 +26,7 @@
 // Replaces the reference's parallel_linear_* tile family at small M, llama_gemv and the ring-buffered K pipeline
 // of src/ops/rpu_linear_gemv.cpp:1-275 (src/ops/rpu_linear.cpp:1047-1544, src/fused/rpu_qwen3_model.h:3653-3700).
 #include <algorithm>
+#include <atomic>
 
 #include "../common/dtype.cuh"
 #include "../common/host_util.h"
@@ -51,6 +52,7 @@ struct GemmSkParams {
   long long units;
   int stage_off;             // shared-memory offset of the [token][128] staging rows
   int ctl_off;
+  int tmem_cols;             // tensor-memory columns this CTA allocates (a power of two covering its accumulator buffers)
   // tensor-parallel publish (see gemm_tc.cu / ar_consume.cu)
   int ar_world, ar_rank, ar_publish, ar_cnt_base;
   void* const* ar_recv; uint32_t* const* ar_flags; uint32_t* ar_state; uint64_t ar_half_bytes;
@@ -109,7 +111,7 @@ gemm_sk_kernel(const __grid_constant__ CUtensorMap tmX, const GemmSkParams p) {
     tma_prefetch_desc(&tmX);
   }
   if (warp == 1) {
-    tmem_alloc(&ctl->tmem_base, 512u);
+    tmem_alloc(&ctl->tmem_base, (uint32_t)p.tmem_cols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -379,27 +381,41 @@ gemm_sk_kernel(const __grid_constant__ CUtensorMap tmX, const GemmSkParams p) {
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 512u);
+  if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
 }
 
 // ------------------------------------------------------------------ host side ----
 struct SkPlan {
-  int bn, stages, ctas, stage_off, ctl_off, tiles, k_blocks;
+  int bn, stages, ctas, stage_off, ctl_off, tiles, k_blocks, tmem_cols;
   long long units;
   size_t smem;
   uint64_t ws_bytes;
 };
 
-static bool sk_enabled() {
-  static const bool v = [] { const char* e = getenv("RF_GEMM_STREAMK"); return !(e && e[0] == '0'); }();
-  return v;
+// 0: never; 1 (default): shapes with at least four output tiles per SM, where almost every tile is streamed whole by
+// one CTA and the partial-tile fix-up is noise (measured on B200 at 64 tokens: the 151936-row vocabulary projection
+// 244 -> 203 us, 0.97 of the copy bandwidth; with fewer tiles than SMs - 32 to 96 for the projections of a decoder
+// layer - every tile is cut into 4 to 8 pieces, the fix-up through global memory is a serial tail, and the cluster
+// split-K kernel of gemm_tc.cu with its on-chip reduction is 1.1x to 1.9x faster); 2: every shape that fits (tests).
+static std::atomic<int> g_sk_mode{-1};
+static int sk_mode() {
+  int m = g_sk_mode.load(std::memory_order_relaxed);
+  if (m < 0) {
+    const char* e = getenv("RF_GEMM_STREAMK");
+    m = e ? atoi(e) : 1;
+    if (m < 0 || m > 2) m = 1;
+    g_sk_mode.store(m, std::memory_order_relaxed);
+  }
+  return m;
 }
 
 // Shapes the stream-K kernel takes: tokens on the MMA N axis (at most 256), tile-major 16-bit weights, enough
 // (tile, k block) units that every CTA streams a few.
 static bool sk_plan(const RfGemm* g, SkPlan* pl) {
-  if (!sk_enabled() || !g->w_packed || g->w_int8 || g->M > 256 || g->force_swap == 0 || g->force_splits > 0 || g->force_bn > 0)
+  const int mode = sk_mode();
+  if (mode == 0 || !g->w_packed || g->w_int8 || g->M > 256 || g->force_swap == 0 || g->force_splits > 0 || g->force_bn > 0)
     return false;
+  if (mode == 1 && ceil_div(g->N, kSkBM) < 4 * sm_count()) return false;
   if (g->ar_world > 1 && !g->ar_publish) return false;     // the in-kernel all-reduce form stays with gemm_tc.cu
   const bool dual = g->dual_offset > 0;
   const int bn = round_up(std::max(g->M, 16), 16);
@@ -410,14 +426,22 @@ static bool sk_plan(const RfGemm* g, SkPlan* pl) {
   pl->units = (long long)pl->tiles * pl->k_blocks;
   static const int min_units = [] { const char* e = getenv("RF_GEMM_STREAMK_MIN_UNITS"); return e ? atoi(e) : 2; }();
   if (pl->units < (long long)min_units * 16) return false;  // tiny GEMMs: set-up dominates either way
-  pl->ctas = (int)std::min<long long>(sm_count(), std::max<long long>(1, pl->units / std::max(1, min_units)));
-  // a tile's k range may spread over at most kSkMaxPartners + 1 shares
-  if ((long long)pl->k_blocks > (kSkMaxPartners) * (pl->units / pl->ctas)) return false;
+  // a tile's k range may spread over at most kSkMaxPartners + 1 shares: a share holds at least k_blocks / kSkMaxPartners units
+  const long long per_cta = std::max<long long>(std::max(1, min_units), ceil_div(pl->k_blocks, kSkMaxPartners));
+  // CTAs per SM: 2 (default) = two half-size rings with their own producer and MMA issuer, and a CTA of the next
+  // kernel can move in as soon as one of them retires (vocabulary projection at 64 tokens: 203 us against 248 us
+  // with one CTA per SM); 1 = the whole shared memory is one deep ring (RF_GEMM_STREAMK_PER_SM=1, A/B timing)
+  static const int per_sm = [] { const char* e = getenv("RF_GEMM_STREAMK_PER_SM"); const int v = e ? atoi(e) : 2; return v == 1 ? 1 : 2; }();
+  const int acc_cols = (dual ? 2 : 1) * bn;
+  pl->tmem_cols = (int)next_pow2((uint32_t)std::max(32, (2 * acc_cols <= 512 ? 2 : 1) * acc_cols));
+  const int ctas_per_sm = (per_sm == 2 && pl->tmem_cols <= 256) ? 2 : 1;
+  pl->ctas = (int)std::min<long long>((long long)sm_count() * ctas_per_sm, std::max<long long>(1, pl->units / per_cta));
+  if ((long long)pl->k_blocks > (long long)kSkMaxPartners * (pl->units / pl->ctas)) return false;
   const int stage_bytes = (dual ? 2 : 1) * kSkWBlock + bn * kSkBK * 2;
   const bool pub_f32 = g->ar_world > 1 && g->ar_publish && g->M <= RF_AR_F32_MAX_ROWS;
   const int staging = bn * kSkBM * (pub_f32 ? 4 : 2);
   const int ctl_bytes = (int)sizeof(GemmSkCtl) + 64;
-  const int budget = 227 * 1024 - 1024 /*alignment slack*/ - round_up(staging, 1024) - ctl_bytes;
+  const int budget = (ctas_per_sm == 2 ? 113 : 227) * 1024 - 1024 /*alignment slack*/ - round_up(staging, 1024) - ctl_bytes;
   pl->stages = std::min(kSkMaxStages, budget / stage_bytes);
   if (pl->stages < 2) return false;
   pl->stage_off = round_up(pl->stages * stage_bytes, 1024);
@@ -459,7 +483,7 @@ static int launch_sk(const RfGemm* g, const SkPlan& pl, cudaStream_t stream) {
   p.ws = g->ws; p.flags = g->sem; p.status = g->status;
   p.M = g->M; p.N = g->N; p.k_blocks = pl.k_blocks; p.bn = pl.bn; p.stages = pl.stages; p.act = g->act;
   p.dual_offset = g->dual_offset; p.dual_tiles = pl.tiles; p.tiles = pl.tiles; p.units = pl.units;
-  p.stage_off = pl.stage_off; p.ctl_off = pl.ctl_off;
+  p.stage_off = pl.stage_off; p.ctl_off = pl.ctl_off; p.tmem_cols = pl.tmem_cols;
   p.ar_world = g->ar_world; p.ar_rank = g->ar_rank; p.ar_publish = g->ar_publish; p.ar_cnt_base = g->ar_cnt_base;
   p.ar_recv = g->ar_recv; p.ar_flags = g->ar_flags; p.ar_state = g->ar_state; p.ar_half_bytes = g->ar_recv_bytes;
   RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.ctas), dim3(kSkThreads), pl.smem, stream, 1, tmX, p));
@@ -476,3 +500,10 @@ int launch_gemm_sk(const RfGemm* g, cudaStream_t stream) {
 }
 
 }  // namespace rf
+
+// 0 never, 1 automatic (large N only), 2 every eligible shape; returns the previous mode.  For tests and A/B timing.
+extern "C" int rf_gemm_streamk_mode(int mode) {
+  const int old = rf::sk_mode();
+  if (mode >= 0 && mode <= 2) rf::g_sk_mode.store(mode, std::memory_order_relaxed);
+  return old;
+}

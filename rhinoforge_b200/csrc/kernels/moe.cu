@@ -145,6 +145,70 @@ __global__ void moe_scale_blocks_kernel(T* __restrict__ h, int64_t ldh, const T*
   store8(p, f);
 }
 
+// Counting sort of the (token, pick) pairs by expert, one CTA.  The order of an expert's rows among themselves
+// is whatever the atomics give; every row is computed independently of its neighbours and the combine step adds
+// a token's picks in pick order, so results do not depend on it.
+__global__ void moe_group_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w, int pairs, int E,
+                                 int32_t* __restrict__ slot_of, int32_t* __restrict__ token_of_slot,
+                                 float* __restrict__ slot_w, int32_t* __restrict__ tiles, int k) {
+  pdl_prologue();
+  __shared__ int32_t count[256], start[257], cursor[256];
+  const int tid = threadIdx.x;
+  for (int e = tid; e < 256; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int i = tid; i < pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int acc = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = acc;
+      cursor[e] = acc;
+      for (int r0 = 0; r0 < count[e]; r0 += 128) {     // one tile entry per 128-row block of this expert
+        tiles[1 + 4 * nt + 0] = e;
+        tiles[1 + 4 * nt + 1] = acc + r0;
+        tiles[1 + 4 * nt + 2] = acc + count[e];
+        tiles[1 + 4 * nt + 3] = 0;
+        ++nt;
+      }
+      acc += count[e];
+    }
+    start[E] = acc;
+    tiles[0] = nt;
+  }
+  __syncthreads();
+  for (int i = tid; i < pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e < 0 || e >= E) { slot_of[i] = -1; continue; }
+    const int s = atomicAdd(&cursor[e], 1);
+    slot_of[i] = s;
+    token_of_slot[s] = i / k;
+    slot_w[s] = w[i];
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(T* __restrict__ out, int64_t ldo, const T* __restrict__ y, int64_t ldy,
+                                   const int32_t* __restrict__ slot_of, int k, int H) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+    float acc[8];
+    load8(out + (size_t)t * ldo + c, acc);
+    for (int j = 0; j < k; ++j) {
+      const int s = slot_of[(size_t)t * k + j];
+      if (s < 0) continue;
+      float f[8];
+      load8(y + (size_t)s * ldy + c, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    store8(out + (size_t)t * ldo + c, acc);
+  }
+}
+
 }  // namespace rf
 
 using namespace rf;
@@ -177,6 +241,29 @@ extern "C" int rf_moe_scale_blocks(void* h, int64_t ldh, const void* dense_w, in
   RF_DISPATCH_T(dtype, RF_CUDA_CHECK(::rf::launch_k(moe_scale_blocks_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
                                                     static_cast<cudaStream_t>(stream), 1, (T*)h, ldh, (const T*)dense_w, ldd,
                                                     rows, E, I)));
+  ::rf::count_launch();
+  return RF_OK;
+}
+
+extern "C" int rf_moe_group(const int32_t* ids, const float* w, int rows, int k, int E, int32_t* slot_of,
+                            int32_t* token_of_slot, float* slot_w, int32_t* tiles, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(ids && w && slot_of && token_of_slot && slot_w && tiles, "moe_group arguments");
+  RF_REQUIRE(rows > 0 && k > 0 && E > 0 && E <= 256 && (int64_t)rows * k <= (1 << 20), "moe_group: rows=%d k=%d E=%d", rows, k, E);
+  RF_CUDA_CHECK(::rf::launch_k(moe_group_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream), 1, ids, w,
+                               rows * k, E, slot_of, token_of_slot, slot_w, tiles, k));
+  ::rf::count_launch();
+  return RF_OK;
+}
+
+extern "C" int rf_moe_combine(void* out, int64_t ldo, const void* y, int64_t ldy, const int32_t* slot_of, int rows, int k,
+                              int H, int dtype, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(out && y && slot_of && H % 8 == 0 && ldo % 8 == 0 && ldy % 8 == 0, "moe_combine: widths and pitches must be multiples of 8");
+  if (rows == 0) return RF_OK;
+  RF_DISPATCH_T(dtype, RF_CUDA_CHECK(::rf::launch_k(moe_combine_kernel<T>, dim3(rows), dim3(128), 0,
+                                                    static_cast<cudaStream_t>(stream), 1, (T*)out, ldo, (const T*)y, ldy,
+                                                    slot_of, k, H)));
   ::rf::count_launch();
   return RF_OK;
 }

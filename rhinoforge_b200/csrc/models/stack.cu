@@ -81,7 +81,7 @@ struct Stack {
     // columns x 128 features) and one flag per CTA; the flags start at zero and every launch leaves them at zero
     {
       const uint64_t bn = (uint64_t)((std::min(cfg.max_tokens, 256) + 15) / 16 * 16);
-      sk_ws_bytes = (uint64_t)sm_count() * 2 * bn * 128 * sizeof(float);
+      sk_ws_bytes = (uint64_t)sm_count() * 2 /*CTAs per SM*/ * 2 /*accumulators*/ * bn * 128 * sizeof(float);
     }
     off_sk_ws = o; o += al(sk_ws_bytes);
     off_sk_flags = o; o += al(kSkFlags * sizeof(uint32_t));

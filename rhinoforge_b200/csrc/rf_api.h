@@ -244,6 +244,36 @@ int rf_moe_scale_blocks(void* h, int64_t ldh, const void* dense_w, int64_t ldd, 
                         rf_stream_t stream);
 
 
+// Grouped expert GEMM.  The (token, pick) pairs of a batch are bucketed by expert (rf_moe_group), their rows are
+// gathered in that order, and ONE persistent launch multiplies every 128-row block of one expert's rows with that
+// expert's weights out of the packed expert bank: out[s, :] = act(x[s, :] . W_e^T) (* row_scale[s]) for every sorted
+// row s of expert e.  Only the experts that were picked are read, and only for as many row blocks as they have rows.
+//   up / gate projections: the bank stacks the experts along N (rt_per_expert row tiles apart, kb_per_expert = 0);
+//   down projection:       the bank concatenates the experts along K (kb_per_expert k blocks apart, rt_per_expert = 0).
+typedef struct RfMoeGroupedGemm {
+  const void* x; int64_t ldx;          // sorted rows [max_rows, K]
+  const void* w;                       // tile-major image of the whole expert bank (rf_pack_weight_bytes layout)
+  void* out; int64_t ldo;              // [max_rows, N]
+  const float* row_scale;              // optional [max_rows] (routing weight of the row)
+  const int32_t* tiles;                // device: [0] number of row blocks, then {expert, first row, end row, 0} per block
+  int32_t max_rows, N, K;              // upper bound of sorted rows; per-expert GEMM shape
+  int32_t dual, act;                   // dual = 1: GLU pair (gate section, then up section of the bank)
+  int32_t bank_section_row_tiles;      // 128-row tiles of one section of the bank image
+  int32_t bank_kb_total;               // 64-column k blocks of one row tile of the bank image
+  int32_t rt_per_expert, kb_per_expert;
+  int32_t dtype; int32_t* status;
+} RfMoeGroupedGemm;
+int rf_moe_grouped_gemm(const RfMoeGroupedGemm* a, rf_stream_t stream);
+// Bucket the picks by expert.  ids / w: [rows, k] (rf_moe_select).  Outputs (device): slot_of [rows*k] = sorted row
+// of pick (t, j); token_of_slot [rows*k]; slot_w [rows*k] (fp32 routing weight per sorted row); tiles = the list
+// rf_moe_grouped_gemm takes (1 + 4 * (rows*k/128 + E) int32).  One CTA; rows * k <= 1 << 20, E <= 256.
+int rf_moe_group(const int32_t* ids, const float* w, int rows, int k, int E, int32_t* slot_of, int32_t* token_of_slot,
+                 float* slot_w, int32_t* tiles, rf_stream_t stream);
+// out[t, :] += sum_j y[slot_of[t, j], :]  (fp32, picks in order j = 0..k-1, one rounding)
+int rf_moe_combine(void* out, int64_t ldo, const void* y, int64_t ldy, const int32_t* slot_of, int rows, int k, int H,
+                   int dtype, rf_stream_t stream);
+
+
 // ------------------------------------------------------------- KV pool ----
 int64_t rf_kvpool_create(int32_t num_pages, int32_t max_seqs, int32_t pages_per_seq);
 int rf_kvpool_destroy(int64_t h);

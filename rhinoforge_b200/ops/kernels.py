@@ -497,3 +497,53 @@ def moe_scale_blocks(h: torch.Tensor, dense_w: torch.Tensor, E: int, I: int) -> 
                                         C.c_int64(dense_w.stride(0)), h.shape[0], E, I, dtype_code(h.dtype), _stream()),
             "rf_moe_scale_blocks")
     return h
+
+
+def moe_group(ids: torch.Tensor, w: torch.Tensor, E: int):
+    """Bucket the router's picks by expert.  ``ids`` / ``w``: ``[T, k]`` from :func:`moe_select`.  Returns
+    ``(slot_of [T*k] int32, token_of_slot [T*k] int32, slot_w [T*k] fp32, tiles int32)``: the sorted row of every
+    pick, the token of every sorted row, its routing weight, and the device-side tile list of
+    :func:`moe_grouped_gemm` (``tiles[0]`` = number of 128-row blocks)."""
+    T, k = ids.shape
+    dev = ids.device
+    slot_of = torch.empty(T * k, dtype=torch.int32, device=dev)
+    token_of_slot = torch.zeros(T * k, dtype=torch.int32, device=dev)
+    slot_w = torch.zeros(T * k, dtype=torch.float32, device=dev)
+    tiles = torch.zeros(1 + 4 * (T * k // 128 + E + 1), dtype=torch.int32, device=dev)
+    N.check(N.lib().rf_moe_group(C.c_void_p(ids.data_ptr()), C.c_void_p(w.data_ptr()), T, k, E, C.c_void_p(slot_of.data_ptr()),
+                                 C.c_void_p(token_of_slot.data_ptr()), C.c_void_p(slot_w.data_ptr()),
+                                 C.c_void_p(tiles.data_ptr()), _stream()), "rf_moe_group")
+    return slot_of, token_of_slot, slot_w, tiles
+
+
+def moe_grouped_gemm(x: torch.Tensor, bank: torch.Tensor, tiles: torch.Tensor, *, n: int, k: int, bank_rows: int,
+                     bank_k: int, expert_rows: int = 0, expert_k: int = 0, dual: bool = False, act: Optional[str] = None,
+                     row_scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                     status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[s] = act(x[s] @ W_e.T) * row_scale[s]`` for every sorted row ``s`` of every expert ``e`` (see
+    :func:`moe_group`).  ``bank`` is the ``pack_weight`` image of the whole expert bank: ``bank_rows`` rows per section
+    (GLU banks have two sections: gates, then ups) and ``bank_k`` columns.  Experts are ``expert_rows`` rows apart
+    (up / gate projection: a multiple of 128) or ``expert_k`` columns apart (down projection: a multiple of 64)."""
+    S = x.shape[0]
+    assert x.stride(1) == 1 and (expert_rows % 128 == 0) and (expert_k % 64 == 0)
+    if out is None:
+        out = torch.zeros((S, n), dtype=x.dtype, device=x.device)
+    a = N.RfMoeGroupedGemm()
+    a.x, a.ldx, a.w, a.out, a.ldo = x.data_ptr(), x.stride(0), bank.data_ptr(), out.data_ptr(), out.stride(0)
+    a.row_scale, a.tiles = _ptr(row_scale), tiles.data_ptr()
+    a.max_rows, a.N, a.K, a.dual, a.act = S, n, k, int(dual), ACT[act]
+    a.bank_section_row_tiles = (bank_rows + 127) // 128
+    a.bank_kb_total = (bank_k + 63) // 64
+    a.rt_per_expert, a.kb_per_expert = expert_rows // 128, expert_k // 64
+    a.dtype, a.status = dtype_code(x.dtype), _ptr(status)
+    N.check(N.lib().rf_moe_grouped_gemm(C.byref(a), _stream()), "rf_moe_grouped_gemm")
+    return out
+
+
+def moe_combine(out: torch.Tensor, y: torch.Tensor, slot_of: torch.Tensor, k: int) -> torch.Tensor:
+    """In place: ``out[t] += sum_j y[slot_of[t*k + j]]`` (fp32 sum in pick order, one rounding)."""
+    T, H = out.shape
+    N.check(N.lib().rf_moe_combine(C.c_void_p(out.data_ptr()), C.c_int64(out.stride(0)), C.c_void_p(y.data_ptr()),
+                                   C.c_int64(y.stride(0)), C.c_void_p(slot_of.data_ptr()), T, k, H, dtype_code(out.dtype),
+                                   _stream()), "rf_moe_combine")
+    return out

@@ -579,3 +579,62 @@ def test_gemm_short_k_splits_down_to_one_block_per_cta(dt, M, N, K, status):
         if s * 64 <= max(K, 64) or s == 1:
             y3 = K_.gemm(x, K_.pack_weight(w), packed_shape=(N, K), bias=b, residual=r, status=status, force_splits=s)
             _close(y3, ref, dt, scale=max(1.0, ref.abs().max().item()))
+
+
+def _close_elementwise(y, ref, dt):
+    """Every element within fp16 / bf16 rounding of ITS OWN reference value (plus a small absolute floor), so a
+    wrong low-magnitude column cannot hide behind the largest entry of the matrix."""
+    rel = 2.0 ** -7 if dt == torch.bfloat16 else 2.0 ** -10
+    err = (y.float() - ref.float()).abs()
+    bound = rel * ref.float().abs() * 2.0 + (6e-2 if dt == torch.bfloat16 else 6e-3)
+    bad = (err > bound).nonzero()
+    assert bad.numel() == 0, f"{bad.shape[0]} elements off; first {bad[0].tolist()}: {y[tuple(bad[0])].item()} vs {ref[tuple(bad[0])].item()}"
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M,N,K,dual", [(1, 4096, 4096, False), (7, 384, 2048, False), (16, 1000, 1024, False),
+                                        (64, 2048, 4096, True), (64, 4096, 12288, False), (33, 1280, 512, True),
+                                        (200, 640, 2560, False), (256, 1152, 1024, False), (96, 8192, 1024, True),
+                                        (64, 151936, 1024, False)])
+def test_gemm_stream_k(dt, M, N, K, dual, status):
+    """The persistent stream-K kernel (tile-major weights, at most 256 tokens): shares that start and end inside a
+    tile (partials parked in scratch and added by the tile's finisher), several tiles per CTA, ragged N, one token,
+    a full 256-token tile, GLU pairs, a vocabulary-sized N; bias, per-channel scale, per-row scale and residual;
+    two launches agree bit for bit."""
+    from rhinoforge_b200 import _native as N_
+    from rhinoforge_b200.ops import kernels as K_
+    old_mode = N_.lib().rf_gemm_streamk_mode(2)          # every shape that fits, not only the large-N ones
+    try:
+        _stream_k_case(dt, M, N, K, dual, status)
+    finally:
+        N_.lib().rf_gemm_streamk_mode(old_mode)
+
+
+def _stream_k_case(dt, M, N, K, dual, status):
+    from rhinoforge_b200.ops import kernels as K_
+    torch.manual_seed(M * 7 + N)
+    rows = 2 * N if dual else N
+    plan = K_.gemm_plan(M, N, K, dtype=dt, dual=dual, packed=True)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    w = (torch.randn(rows, K, device="cuda") * (1.0 / math.sqrt(K))).to(dt)
+    wp = K_.pack_weight(w, 2 if dual else 1)
+    z = x.float() @ w.float().t()
+    if dual:
+        y = K_.gemm(x, wp, packed_shape=(rows, K), act="silu_mul", dual=True, status=status)
+        ref = torch.nn.functional.silu(z[:, :N]) * z[:, N:]
+        y2 = K_.gemm(x, wp, packed_shape=(rows, K), act="silu_mul", dual=True, status=status)
+    else:
+        b = torch.randn(N, device="cuda").to(dt)
+        sc = (torch.rand(N, device="cuda") + 0.5).to(dt)
+        rs = torch.rand(M, device="cuda") + 0.5
+        r = torch.randn(M, N, device="cuda").to(dt)
+        y = K_.gemm(x, wp, packed_shape=(rows, K), bias=b, scale=sc, row_scale=rs, residual=r, status=status)
+        ref = z * rs[:, None] * sc.float() + b.float() + r.float()
+        y2 = K_.gemm(x, wp, packed_shape=(rows, K), bias=b, scale=sc, row_scale=rs, residual=r, status=status)
+        # in place: the residual already sits in the output buffer
+        acc = r.clone()
+        K_.gemm(x, wp, packed_shape=(rows, K), residual=acc, out=acc, status=status)
+        _close_elementwise(acc, z + r.float(), dt)
+    _close_elementwise(y, ref, dt)
+    assert torch.equal(y, y2), "two launches of the same GEMM must agree bit for bit"
+    assert plan is None or plan["persistent"] in (0, 2)
