@@ -126,7 +126,19 @@ class RfLayerWeights(C.Structure):
 
 class RfStackComm(C.Structure):
     _fields_ = [("recv", C.c_void_p), ("flags", C.c_void_p), ("state", C.c_void_p),
-                ("recv_half_bytes", C.c_uint64), ("flag_count", C.c_int32), ("cnt_base", C.c_int32)]
+                ("recv_half_bytes", C.c_uint64), ("flag_count", C.c_int32), ("cnt_base", C.c_int32),
+                ("sym_rows", C.c_int32), ("rows_flag_base", C.c_int32),
+                ("sym_hidden", C.c_void_p), ("sym_xn", C.c_void_p), ("sym_tmp", C.c_void_p), ("sym_partial", C.c_void_p),
+                ("hidden_tab", C.c_void_p), ("xn_tab", C.c_void_p), ("tmp_tab", C.c_void_p), ("partial_tab", C.c_void_p)]
+
+
+class RfArRows(C.Structure):
+    _fields_ = [
+        ("M", C.c_int32), ("N", C.c_int32), ("world", C.c_int32), ("rank", C.c_int32),
+        ("partial_tab", C.c_void_p), ("out_tab", C.c_void_p), ("norm_tab", C.c_void_p), ("ar_flags", C.c_void_p),
+        ("ar_state", C.c_void_p), ("flag_base", C.c_int32), ("add_residual", C.c_int32),
+        ("norm_w", C.c_void_p), ("eps", C.c_float), ("norm_mode", C.c_int32), ("status", C.c_void_p), ("dtype", C.c_int32),
+    ]
 
 
 class RfStackForward(C.Structure):

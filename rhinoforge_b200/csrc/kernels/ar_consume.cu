@@ -158,6 +158,160 @@ __global__ void __launch_bounds__(kArThreads) ar_consume_kernel(const ArConsumeP
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Two-shot all-reduce of whole rows for prefill-sized token counts (see RfArRows in rf_api.h).
+struct ArRowsParams {
+  void* const* partial_tab; void* const* out_tab; void* const* norm_tab;
+  uint32_t* const* flag_tab; uint32_t* state;
+  int world, rank, M, N, flag_base, add_residual;
+  const void* norm_w; float eps; int norm_mode;
+  int32_t* status;
+};
+
+template <typename T, int VPT>
+__global__ void __launch_bounds__(kArThreads) ar_rows_kernel(const ArRowsParams p) {
+  pdl_prologue();
+  __shared__ float red[kArThreads / 32 + 1];
+  __shared__ int bad;
+  __shared__ unsigned last_cta;
+  const int tid = threadIdx.x;
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.state + 6) + 1u;
+  uint32_t* my_flags = p.flag_tab[p.rank] + p.flag_base;
+  if (tid == 0) bad = 0;
+  // this rank's partial (written by the kernel before this one) is complete: tell every peer, once
+  if (blockIdx.x == 0 && tid < p.world) {
+    __threadfence_system();
+    st_release_sys(p.flag_tab[tid] + p.flag_base + p.rank, epoch);
+  }
+  __syncthreads();
+  if (tid < p.world) {
+    const bool poisoned = p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0;
+    if (poisoned || !wait_flag_ge_sys(my_flags + tid, epoch)) {
+      if (!poisoned) report_status(p.status, kStatusPeerTimeout, kTagGemmAr, 300 + tid);
+      bad = 1;
+    }
+  }
+  __syncthreads();
+  const int per = (p.M + p.world - 1) / p.world;
+  const int row_begin = p.rank * per, row_end = min(p.M, row_begin + per);
+  const int nvec = p.N >> 3;
+  if (!bad) {
+    const T* parts[8];
+    T* outs[8];
+    T* norms[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      parts[r] = r < p.world ? reinterpret_cast<const T*>(p.partial_tab[r]) : nullptr;
+      outs[r] = r < p.world ? reinterpret_cast<T*>(p.out_tab[r]) : nullptr;
+      norms[r] = (r < p.world && p.norm_mode != 0) ? reinterpret_cast<T*>(p.norm_tab[r]) : nullptr;
+    }
+    const T* resid = p.add_residual ? outs[0] : nullptr;
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      if (r == p.rank && p.add_residual) resid = outs[r];
+    const T* w = reinterpret_cast<const T*>(p.norm_w);
+    for (int row = row_begin + blockIdx.x; row < row_end; row += gridDim.x) {
+      float h[VPT][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int v = tid + k * kArThreads;
+        if (v < nvec) {
+          const size_t at = (size_t)row * p.N + (size_t)v * 8;
+          uint4 raw[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+            raw[r] = r < p.world ? __ldcg(reinterpret_cast<const uint4*>(parts[r] + at)) : make_uint4(0u, 0u, 0u, 0u);
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          float r8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (resid) load8(resid + at, r8);
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            if (r < p.world) {
+              const typename Num<T>::T2* hh = reinterpret_cast<const typename Num<T>::T2*>(&raw[r]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = Num<T>::to_f2(hh[j]);
+                acc[2 * j] += f.x;
+                acc[2 * j + 1] += f.y;
+              }
+            }
+          }
+          Vec8<T> packed;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            packed.v[j] = Num<T>::from_f2(acc[2 * j] + r8[2 * j], acc[2 * j + 1] + r8[2 * j + 1]);
+            const float2 back = Num<T>::to_f2(packed.v[j]);
+            h[k][2 * j] = back.x;
+            h[k][2 * j + 1] = back.y;
+            ss += back.x * back.x + back.y * back.y;
+          }
+#pragma unroll
+          for (int d = 0; d < 8; ++d)
+            if (d < p.world) *reinterpret_cast<Vec8<T>*>(outs[d] + at) = packed;
+        }
+      }
+      if (p.norm_mode != 0) {
+        ss = warp_sum(ss);
+        __syncthreads();                       // red[] of the previous row has been read
+        if ((tid & 31) == 0) red[tid >> 5] = ss;
+        __syncthreads();
+        if (tid < 32) {
+          float t = tid < (int)(blockDim.x >> 5) ? red[tid] : 0.f;
+          t = warp_sum(t);
+          if (tid == 0) red[kArThreads / 32] = t;
+        }
+        __syncthreads();
+        const float rstd = rsqrtf(red[kArThreads / 32] / (float)p.N + p.eps);
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          const int v = tid + k * kArThreads;
+          if (v < nvec) {
+            const size_t at = (size_t)row * p.N + (size_t)v * 8;
+            float wf[8], o[8];
+            load8(w + (size_t)v * 8, wf);
+            if (p.norm_mode == 2) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[j] = h[k][j] * rstd * (1.f + wf[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[j] = wf[j] * Num<T>::to_f(Num<T>::from_f(h[k][j] * rstd));
+            }
+            Vec8<T> packed;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) packed.v[j] = Num<T>::from_f2(o[2 * j], o[2 * j + 1]);
+#pragma unroll
+            for (int d = 0; d < 8; ++d)
+              if (d < p.world) *reinterpret_cast<Vec8<T>*>(norms[d] + at) = packed;
+          }
+        }
+      }
+    }
+  }
+  // Every row this rank owns is written on every rank: the last CTA says so to every peer and then waits until
+  // every peer has said the same, so that the kernel after this one finds all rows of its buffers complete.
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned done = atomicAdd(p.state + 7, 1u);
+    last_cta = (done == gridDim.x - 1u) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (last_cta) {
+    __threadfence_system();
+    if (tid < p.world && !bad) st_release_sys(p.flag_tab[tid] + p.flag_base + 8 + p.rank, epoch);
+    if (tid < p.world && !bad) {
+      if (!wait_flag_ge_sys(my_flags + 8 + tid, epoch)) report_status(p.status, kStatusPeerTimeout, kTagGemmAr, 400 + tid);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      p.state[7] = 0u;
+      __threadfence();
+      p.state[6] = epoch;
+    }
+  }
+}
+
 template <typename T, bool F32>
 static int launch_consume(const RfArConsume* a, const ArConsumeParams& p, cudaStream_t st) {
   const int nvec = a->N / 8;
@@ -205,4 +359,37 @@ extern "C" int rf_ar_consume(const RfArConsume* a, rf_stream_t stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->dtype == 0) return f32 ? launch_consume<__half, true>(a, p, st) : launch_consume<__half, false>(a, p, st);
   return f32 ? launch_consume<__nv_bfloat16, true>(a, p, st) : launch_consume<__nv_bfloat16, false>(a, p, st);
+}
+
+extern "C" int rf_ar_rows(const RfArRows* a, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(a != nullptr, "null RfArRows");
+  RF_REQUIRE(a->M > 0 && a->N > 0 && a->N % 8 == 0 && a->N <= kArThreads * kArMaxVec * 8, "ar_rows shape %dx%d", a->M, a->N);
+  RF_REQUIRE(a->world >= 2 && a->world <= 8 && a->rank >= 0 && a->rank < a->world, "ar_rows rank %d of %d", a->rank, a->world);
+  RF_REQUIRE(a->partial_tab && a->out_tab && a->ar_flags && a->ar_state && a->flag_base >= 0, "ar_rows needs the buffer tables, flags and state");
+  RF_REQUIRE(a->dtype == 0 || a->dtype == 1, "ar_rows dtype");
+  if (a->norm_mode != 0) RF_REQUIRE(a->norm_w && a->norm_tab && (a->norm_mode == 1 || a->norm_mode == 2), "ar_rows fused norm arguments");
+  ArRowsParams p;
+  p.partial_tab = a->partial_tab; p.out_tab = a->out_tab; p.norm_tab = a->norm_tab;
+  p.flag_tab = a->ar_flags; p.state = a->ar_state;
+  p.world = a->world; p.rank = a->rank; p.M = a->M; p.N = a->N; p.flag_base = a->flag_base; p.add_residual = a->add_residual;
+  p.norm_w = a->norm_w; p.eps = a->eps; p.norm_mode = a->norm_mode; p.status = a->status;
+  const int nvec = a->N / 8;
+  const int vpt = ceil_div(nvec, kArThreads);
+  const int threads = vpt > 1 ? kArThreads : std::max(32, round_up(nvec, 32));
+  const int own = ceil_div(a->M, a->world);
+  const int grid = std::max(1, std::min(own, 8 * sm_count()));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+#define RF_AR_ROWS(T)                                                                                        \
+  switch (vpt) {                                                                                             \
+    case 1: e = launch_k(ar_rows_kernel<T, 1>, dim3(grid), dim3(threads), 0, st, 1, p); break;               \
+    case 2: e = launch_k(ar_rows_kernel<T, 2>, dim3(grid), dim3(threads), 0, st, 1, p); break;               \
+    default: e = launch_k(ar_rows_kernel<T, kArMaxVec>, dim3(grid), dim3(threads), 0, st, 1, p); break;      \
+  }
+  if (a->dtype == 0) { RF_AR_ROWS(__half) } else { RF_AR_ROWS(__nv_bfloat16) }
+#undef RF_AR_ROWS
+  RF_CUDA_CHECK(e);
+  count_launch();
+  return RF_OK;
 }

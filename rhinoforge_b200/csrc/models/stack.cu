@@ -186,6 +186,28 @@ static int linear_ar(const Stack& s, const void* x, int64_t ldx, const void* w, 
                      bool* normed, cudaStream_t st) {
   const int H = s.cfg.hidden;
   if (normed) *normed = false;
+  if (s.cfg.tp_world > 1 && tp_publish_enabled() && M > 256 && s.comm.sym_rows >= M &&
+      (out == s.comm.sym_hidden || out == s.comm.sym_tmp) && (!residual || residual == out)) {
+    // Prefill-sized rows: the GEMM (persistent kernel, no collective in it) writes this rank's partial into its
+    // symmetric buffer; rf_ar_rows reduces the rows this rank owns over NVLink, adds the residual, applies the
+    // following RMSNorm and stores the finished rows into every rank's buffers.  Only rank 0 adds the bias.
+    int rc = linear(s, x, ldx, w, scale, s.cfg.tp_rank == 0 ? bias : nullptr, s.comm.sym_partial, H, nullptr, 0, M, H, K,
+                    kActNone, 0, false, st);
+    if (rc) return rc;
+    RfArRows a = {};
+    a.M = M; a.N = H; a.world = s.cfg.tp_world; a.rank = s.cfg.tp_rank;
+    a.partial_tab = s.comm.partial_tab;
+    a.out_tab = out == s.comm.sym_hidden ? s.comm.hidden_tab : s.comm.tmp_tab;
+    a.ar_flags = s.comm.flags; a.ar_state = s.comm.state; a.flag_base = s.comm.rows_flag_base;
+    a.add_residual = residual ? 1 : 0;
+    if (next_norm_w && next_xn == s.comm.sym_xn) {
+      a.norm_tab = s.comm.xn_tab; a.norm_w = next_norm_w; a.eps = s.cfg.eps;
+      a.norm_mode = s.cfg.norm_kind == RF_NORM_RMS_GEMMA ? 2 : 1;
+      if (normed) *normed = true;
+    }
+    a.status = s.status(); a.dtype = s.cfg.dtype;
+    return rf_ar_rows(&a, st);
+  }
   if (s.cfg.tp_world > 1 && tp_publish_enabled()) {
     int ctas = 0;
     int rc = linear(s, x, ldx, w, scale, bias, out, H, residual, residual ? H : 0, M, H, K, kActNone, 0, true, st, &ctas);
@@ -225,9 +247,12 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
   if (c.norm_kind == RF_NORM_ADARMS) RF_REQUIRE(f.mod && f.rows_per_mod > 0, "adaRMS stack needs mod");
   const int T = f.tokens, H = c.hidden, QD = s.qkv_dim(), AD = c.Hq * c.hd, I = c.inter;
   const int lb = f.layer_end > 0 ? f.layer_begin : 0, le = f.layer_end > 0 ? f.layer_end : c.layers;
-  void* xn = s.at(s.off_xn);
+  // under tensor parallelism with symmetric buffers the normalised rows and the side result live there, so that
+  // the owner rank of a row can store them into every rank's copy
+  const bool sym = s.has_comm && s.comm.sym_rows >= T && s.comm.sym_xn && s.comm.sym_tmp;
+  void* xn = sym ? s.comm.sym_xn : s.at(s.off_xn);
   void* attn = s.at(s.off_attn);
-  void* tmp = s.at(s.off_tmp);
+  void* tmp = sym ? s.comm.sym_tmp : s.at(s.off_tmp);
   void* wide = s.at(s.off_wide);
   const size_t esz = 2;
   const int nmods = c.norm_kind == RF_NORM_ADARMS ? T / f.rows_per_mod : 0;

@@ -85,6 +85,15 @@ typedef struct RfStackComm {
   uint64_t recv_half_bytes;
   int32_t flag_count;
   int32_t cnt_base;        // first of `world` arrival counters in every rank's flag array (publish / consume all-reduce)
+  // Symmetric activation buffers (optional; sym_rows == 0: none): every rank allocated [sym_rows, hidden] buffers for
+  // the residual stream, the normalised rows, a side result and the row-parallel GEMM's partial at the same offsets
+  // of its peer-mapped region.  *_tab are device arrays [world] of the ranks' bases, sym_* this rank's own bases.
+  // With them a prefill-sized all-reduce runs as GEMM -> rf_ar_rows (reduce-scatter by peer loads, all-gather by peer
+  // stores); the caller must then pass sym_hidden as RfStackForward.hidden.
+  int32_t sym_rows;
+  int32_t rows_flag_base;  // first of the 16 flags of rf_ar_rows in every rank's flag array
+  void* sym_hidden; void* sym_xn; void* sym_tmp; void* sym_partial;
+  void* const* hidden_tab; void* const* xn_tab; void* const* tmp_tab; void* const* partial_tab;
 } RfStackComm;
 
 typedef struct RfStackForward {

@@ -109,6 +109,28 @@ typedef struct RfArConsume {
 } RfArConsume;
 int rf_ar_consume(const RfArConsume* a, rf_stream_t stream);
 
+// Two-shot all-reduce for large token counts (prefill), over buffers that every rank allocated at the same offsets
+// of its peer-mapped communication region ("symmetric" buffers; the tables hold one base pointer per rank).
+// Every rank's row-parallel GEMM has written its partial result [M, N] into its own `partial` buffer.  Rank r owns
+// rows [r * ceil(M / world), ...): it reads those rows of EVERY rank's partial over NVLink (reduce-scatter by peer
+// loads, summed in rank order in fp32), adds the residual, and writes the finished rows -- and, when norm_mode != 0,
+// the RMSNorm of them -- into every rank's `out` (and `norm_out`) buffer (all-gather by peer stores).  The residual is
+// read from this rank's own `out` buffer when add_residual is set (the residual stream lives there).  Flags:
+// world "partial ready" + world "rows written" words per rank at flag_base; state word 6 is the epoch.
+typedef struct RfArRows {
+  int32_t M, N, world, rank;
+  void* const* partial_tab;    // device array [world]: every rank's partial [M, N]
+  void* const* out_tab;        // device array [world]: every rank's destination [M, N]
+  void* const* norm_tab;       // device array [world]: every rank's normalised destination (optional)
+  uint32_t* const* ar_flags;   // device array [world] of flag-array bases
+  uint32_t* ar_state;
+  int32_t flag_base;
+  int32_t add_residual;
+  const void* norm_w; float eps; int32_t norm_mode;
+  int32_t* status; int32_t dtype;
+} RfArRows;
+int rf_ar_rows(const RfArRows* a, rf_stream_t stream);
+
 
 // ------------------------------------------------------ norms / glue ----
 int rf_rmsnorm(const void* x, const void* residual, const void* w, void* y, void* residual_out,

@@ -139,18 +139,28 @@ class CommBuffers:
     """
 
     FLAG_COUNT = 1 << 20
-    BARRIER_FLAGS = 64  # the last flags are reserved: barrier [0, 8), arg-max merge [16, 24), arrival counters [32, 40)
+    BARRIER_FLAGS = 64  # the last flags are reserved: barrier [0, 8), arg-max merge [16, 24), arrival counters [32, 40),
+    #                     row all-reduce [40, 56)
     CNT_OFFSET = 32     # arrival counters of the publish / consume all-reduce, one per source rank
+    ROWS_OFFSET = 40    # "partial ready" and "rows written" flags of the row all-reduce, eight each
+    SYM_NAMES = ("hidden", "xn", "tmp", "partial")
     AUX_ROWS = 1024     # rows of (value, id) pairs per rank in the aux area
 
-    def __init__(self, tp: TPContext, recv_half_bytes: int):
+    def __init__(self, tp: TPContext, recv_half_bytes: int, *, sym_rows: int = 0, sym_cols: int = 0, sym_elem_bytes: int = 2):
+        """``sym_rows`` / ``sym_cols`` > 0 additionally lays out four symmetric ``[sym_rows, sym_cols]`` activation
+        buffers (residual stream, normalised rows, side result, GEMM partial) behind the flags: every rank has them at
+        the same offsets, so a rank can load the rows it owns from every peer's partial and store finished rows into
+        every peer's buffers (the prefill-sized all-reduce)."""
         assert tp.enabled
         self.tp = tp
         lib = N.lib()
         self.recv_half_bytes = (recv_half_bytes + 1023) // 1024 * 1024
         self.flag_bytes = self.FLAG_COUNT * 4
         self.aux_bytes = 2 * 8 * self.AUX_ROWS * 8
-        self.total = 2 * self.recv_half_bytes + self.flag_bytes + 1024 + self.aux_bytes
+        self.sym_rows, self.sym_cols, self.sym_elem_bytes = sym_rows, sym_cols, sym_elem_bytes
+        self.sym_bytes = (sym_rows * sym_cols * sym_elem_bytes + 1023) // 1024 * 1024
+        self.sym_off = 2 * self.recv_half_bytes + self.flag_bytes + 1024 + self.aux_bytes
+        self.total = self.sym_off + len(self.SYM_NAMES) * self.sym_bytes
         p = C.c_void_p()
         N.check(lib.rf_comm_alloc(C.c_uint64(self.total), C.byref(p)), "rf_comm_alloc")
         self.local = p.value
@@ -176,7 +186,28 @@ class CommBuffers:
         aux_off = flag_off + self.flag_bytes + 1024
         self.aux_ptrs = torch.tensor([b + aux_off for b in self.peers], dtype=torch.int64, device=dev)
         self.status = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.sym_tabs = {}
+        if self.sym_bytes:
+            for i, name in enumerate(self.SYM_NAMES):
+                self.sym_tabs[name] = torch.tensor([b + self.sym_off + i * self.sym_bytes for b in self.peers],
+                                                   dtype=torch.int64, device=dev)
         tp.barrier()
+
+    def sym_ptr(self, name: str) -> int:
+        """Device address of this rank's symmetric buffer ``name`` (``hidden``, ``xn``, ``tmp`` or ``partial``)."""
+        return self.local + self.sym_off + self.SYM_NAMES.index(name) * self.sym_bytes
+
+    def sym_tensor(self, name: str, dtype: torch.dtype) -> torch.Tensor:
+        """This rank's symmetric buffer ``name`` as a ``[sym_rows, sym_cols]`` tensor over the communication region
+        (no copy; the region outlives the tensor only as long as this object is open)."""
+        class _Raw:
+            pass
+        raw = _Raw()
+        typestr = {torch.float16: "<f2", torch.bfloat16: "<u2", torch.float32: "<f4"}[dtype]
+        raw.__cuda_array_interface__ = {"shape": (self.sym_rows, self.sym_cols), "typestr": typestr,
+                                        "data": (self.sym_ptr(name), False), "version": 2}
+        t = torch.as_tensor(raw, device=self.tp.device)
+        return t.view(dtype) if dtype == torch.bfloat16 else t
 
     def fill(self, g) -> None:
         g.ar_world, g.ar_rank = self.tp.world, self.tp.rank
@@ -192,6 +223,13 @@ class CommBuffers:
         c.recv_half_bytes = self.recv_half_bytes
         c.flag_count = self.FLAG_COUNT - self.BARRIER_FLAGS
         c.cnt_base = self.cnt_base
+        if self.sym_bytes:
+            c.sym_rows = self.sym_rows
+            c.rows_flag_base = self.FLAG_COUNT - self.BARRIER_FLAGS + self.ROWS_OFFSET
+            c.sym_hidden, c.sym_xn = self.sym_ptr("hidden"), self.sym_ptr("xn")
+            c.sym_tmp, c.sym_partial = self.sym_ptr("tmp"), self.sym_ptr("partial")
+            c.hidden_tab, c.xn_tab = self.sym_tabs["hidden"].data_ptr(), self.sym_tabs["xn"].data_ptr()
+            c.tmp_tab, c.partial_tab = self.sym_tabs["tmp"].data_ptr(), self.sym_tabs["partial"].data_ptr()
         return c
 
     @property

@@ -157,9 +157,13 @@ class DecoderEngine:
             if tp_comm_mode() == "nccl":
                 raise RPUBackendError("RPU_TP_COMM=nccl: the engine's step has no NCCL path (its all-reduce is the GEMM "
                                       "epilogue); the NCCL implementation of the same models is baseline/eager_tp.py")
-            # one-shot fp32 partials for <= 256 rows, two-shot 16-bit partials + result region above
-            need = max(W * min(self.max_tokens, 256) * H * 4, (W + 1) * self.max_tokens * H * 2)
-            self.comm = CommBuffers(self.tp, need)
+            # receive slots of the publish / consume all-reduce (<= 256 rows, fp32 partials at most) and four symmetric
+            # [max_tokens, hidden] activation buffers for the prefill-sized row all-reduce; RF_TP_AR=inkernel (the
+            # all-reduce inside the GEMM epilogue, A/B timing) needs room for 16-bit partials + results of all rows
+            need = W * min(self.max_tokens, 256) * H * 4
+            if os.environ.get("RF_TP_AR") == "inkernel":
+                need = max(need, (W + 1) * self.max_tokens * H * 2)
+            self.comm = CommBuffers(self.tp, need, sym_rows=self.max_tokens, sym_cols=H, sym_elem_bytes=2)
             cc = self.comm.stack_comm()
             N.check(lib.rf_stack_set_comm(self.handle, C.byref(cc)), "rf_stack_set_comm")
 
@@ -170,7 +174,10 @@ class DecoderEngine:
         self.axis = ax.to(self.device) if ax is not None else None
         self.pos_stride = 3 if ax is not None else 1
         i32 = dict(dtype=torch.int32, device=self.device)
-        self.hidden = torch.zeros((self.max_tokens, H), dtype=dtype, device=self.device)
+        # the residual stream: under tensor parallelism it lives in the peer-mapped region, where the owner rank of a
+        # row stores the all-reduced row into every rank's copy
+        self.hidden = (self.comm.sym_tensor("hidden", dtype) if self.comm is not None
+                       else torch.zeros((self.max_tokens, H), dtype=dtype, device=self.device))
         self.ids = torch.zeros(max_batch, **i32)
         self.out_ids = torch.zeros(max_batch, **i32)
         self.out_vals = torch.zeros(max_batch, dtype=torch.float32, device=self.device)

@@ -107,6 +107,25 @@ def main() -> int:
     report.update({"ranks_agree": ranks_agree, "tp_matches_single": match, "replay_stable": bool(torch.equal(tN, tN2)),
                    "t1": t1.tolist(), "tN": tN.tolist()})
     ok &= ranks_agree and match and torch.equal(tN, tN2)
+    # ---- 3. prefill-sized rows: one packed chunk of 8192 tokens goes through GEMM -> row all-reduce (reduce-scatter by
+    # peer loads, all-gather by peer stores, residual and RMSNorm in the same kernel); last-row logits and the greedy
+    # continuation must match the single-GPU engine
+    long_prompts = [torch.randint(0, cfg.vocab_size, (L,), generator=gen) for L in (3000, 5192)]
+    e1 = DecoderEngine(cfg, get, device=dev, max_batch=2, max_seq_len=5248, max_prefill_tokens=8192)
+    f1, l1 = e1.prefill(long_prompts, return_logits=True)
+    l1 = l1.float().cpu()
+    d1 = e1.decode(8).cpu()
+    e1.close()
+    eN = DecoderEngine(cfg, get, max_batch=2, max_seq_len=5248, tp=tp, max_prefill_tokens=8192)
+    fN, lN = eN.prefill(long_prompts, return_logits=True)
+    lN_all = torch.cat(tp.all_gather_object(lN.float().cpu()), 1)        # vocab shards side by side
+    dN = eN.decode(8).cpu()
+    eN.check_status()
+    eN.close()
+    logit_err = float((lN_all - l1).abs().max())
+    long_ok = logit_err < 3e-2 and bool((f1.cpu() == fN.cpu()).all()) and bool((d1 == dN).all())
+    report.update({"rows_allreduce_logit_err": logit_err, "rows_allreduce_ok": long_ok, "d1": d1.tolist(), "dN": dN.tolist()})
+    ok &= long_ok
     report["ok"] = bool(ok)
     out = os.environ.get("RF_TP_REPORT")
     if out:
