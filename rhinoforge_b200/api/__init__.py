@@ -9,7 +9,8 @@ _LAZY = {
     "Qwen3_5Cache": ("qwen3_5_cache", "Qwen3_5Cache"),
     "Pi05Policy": ("policy", "Pi05Policy"),
     "WallOssPolicy": ("_unbuilt", "WallOssPolicy"),
-    "Lingbot2Policy": ("_unbuilt", "Lingbot2Policy"),
+    "Lingbot2Policy": ("lingbot2", "Lingbot2Policy"),
+    "Lingbot2ActionOutput": ("lingbot2", "Lingbot2ActionOutput"),
     "HyEmbodiedPolicy": ("_unbuilt", "HyEmbodiedPolicy"),
     "RhinoVLAPolicy": ("rhinovla", "RhinoVLAPolicy"),
 }

@@ -3,7 +3,7 @@
 The classes exist so that ``rpu_backend.api.WallOssPolicy`` and its siblings import and fail in a defined way: every
 constructor path raises :class:`UnsupportedModelError` naming the family, what it would need and what is available
 instead, before any checkpoint is read (the reference's facades: ``python/rpu_backend/api/wall_oss.py``,
-``lingbot2.py``, ``hy_embodied.py``).  ``RhinoVLAPolicy`` is not among them: it wraps an externally assembled runtime
+``hy_embodied.py``).  ``RhinoVLAPolicy`` is not among them: it wraps an externally assembled runtime
 and is built in :mod:`rhinoforge_b200.api.rhinovla`.  The shared pieces those policies use - runtime-environment
 validation, action de-normalisation, 6-D rotation decoding - are built (``_runtime_env``, ``action_denorm``,
 ``hy_action_decode``), and so are the towers they start from (Qwen2.5-VL ViT, SigLIP, the Qwen2.5 / Qwen3 decoder stack).
@@ -32,9 +32,7 @@ def _facade(name: str, family: str, needs: str):
 
 WallOssPolicy = _facade("WallOssPolicy", "Wall-OSS (Qwen2.5-VL backbone with a flow-matching action expert)",
                         "needs the mixture-of-transformers action step and its denoise loop")
-Lingbot2Policy = _facade("Lingbot2Policy", "LingBot-VLA v2 (sparse-MoE action expert)",
-                         "needs the MoE expert MLP inside the native stack")
 HyEmbodiedPolicy = _facade("HyEmbodiedPolicy", "HunYuan embodied VLA (HYViT2 tower, twin-weight prefill, action expert)",
                            "needs the HYViT2 tower and row-routed twin weights")
 
-__all__ = ["WallOssPolicy", "Lingbot2Policy", "HyEmbodiedPolicy"]
+__all__ = ["WallOssPolicy", "HyEmbodiedPolicy"]

@@ -37,7 +37,8 @@ class DecoderConfig:
     embed_scale: float = 1.0     # Gemma multiplies embeddings by sqrt(hidden)
     max_position: int = 40960
     rotary_dim: Optional[int] = None           # partial rotary; None = head_dim
-    mrope_section: Optional[Tuple[int, int, int]] = None  # interleaved M-RoPE (Qwen3-VL)
+    mrope_section: Optional[Tuple[int, int, int]] = None  # M-RoPE: frequency pairs per (T, H, W) axis
+    mrope_interleaved: bool = True   # True: THWTHW... (Qwen3-VL); False: contiguous T.., H.., W.. ranges (Qwen2.5-VL)
     model_type: str = "qwen3"
     # hybrid decoders (Qwen3.5): per-layer mixer kinds and the Gated-DeltaNet geometry
     layer_types: Optional[Tuple[str, ...]] = None     # "full_attention" | "linear_attention"; None: all attention
@@ -77,8 +78,10 @@ class DecoderConfig:
             rope_theta = rp.get("rope_theta", 1e6)
         mt = g("model_type", "qwen3")
         mrope = None
+        mrope_il = True
         if isinstance(rp, dict) and rp.get("mrope_section"):
             mrope = tuple(rp["mrope_section"])
+            mrope_il = bool(rp.get("mrope_interleaved", mt.startswith("qwen3")))
         hybrid = {}
         gemma_norm = mt.startswith("gemma")
         if mt.startswith("qwen3_5"):
@@ -101,7 +104,8 @@ class DecoderConfig:
             mlp="geglu_tanh" if mt.startswith("gemma") else "swiglu",
             norm="rms_gemma" if gemma_norm else "rms",
             embed_scale=math.sqrt(hf.hidden_size) if mt.startswith("gemma") else 1.0,
-            max_position=g("max_position_embeddings", 40960), mrope_section=mrope, model_type=mt))
+            max_position=g("max_position_embeddings", 40960), mrope_section=mrope, mrope_interleaved=mrope_il,
+            model_type=mt))
 
 
 def _q3(name, H, I, L, heads, kv, tie, vocab=151936):
@@ -194,13 +198,19 @@ def rope_tables(cfg: DecoderConfig, max_pos: int, device="cpu") -> Tuple[torch.T
 
 
 def mrope_axis_of_freq(cfg: DecoderConfig) -> Optional[torch.Tensor]:
-    """Position axis (0=T, 1=H, 2=W) used by each rotary frequency under interleaved M-RoPE
-    (reference kernel semantics: ``src/ops/rpu_mrope.cpp:37-124``)."""
+    """Position axis (0=T, 1=H, 2=W) used by each rotary frequency under M-RoPE: interleaved ``THWTHW...TT``
+    (reference kernel semantics: ``src/ops/rpu_mrope.cpp:37-124``) or contiguous ranges ``T.. H.. W..``
+    (Qwen2.5-VL; ``python/rpu_backend/runtime/rope_partial.py:129,176``)."""
     if cfg.mrope_section is None:
         return None
     axis = torch.zeros(cfg.rot_dim // 2, dtype=torch.int8)
-    for dim, off in ((1, 1), (2, 2)):
-        axis[off:cfg.mrope_section[dim] * 3:3] = dim
+    if cfg.mrope_interleaved:
+        for dim, off in ((1, 1), (2, 2)):
+            axis[off:cfg.mrope_section[dim] * 3:3] = dim
+    else:
+        t, h = cfg.mrope_section[0], cfg.mrope_section[1]
+        axis[t:t + h] = 1
+        axis[t + h:] = 2
     return axis
 
 
