@@ -117,6 +117,7 @@ class Lingbot2Policy:
         self._lock = threading.RLock()
         self._prepare_ms: Dict[str, float] = {}
         self._graph_profile: Optional[dict] = None
+        self._one_graph = True
         return self
 
     @classmethod
@@ -131,6 +132,7 @@ class Lingbot2Policy:
         self._closed = False
         self._lock = threading.RLock()
         self._prepare_ms, self._graph_profile = {}, None
+        self._one_graph = True
         return self
 
     @property
@@ -191,6 +193,8 @@ class Lingbot2Policy:
         old_env = {k: os.environ.get(k) for k in self._runtime_env}
         os.environ.update(self._runtime_env)
         try:
+            from ..runtime.control import rpu_env_bool
+            self._one_graph = rpu_env_bool("RPU_LINGBOT2_DENOISE_UNROLL", True)     # 0: one launch sequence per Euler step
             self._engine = build_engine(config, get, device=dev, dtype=torch.float16 if self._dtype == "fp16" else torch.bfloat16,
                                         max_lang_tokens=self._max_lang_tokens, n_cameras=self._n_cameras,
                                         image_size=self._image_size, qwen3vl_base=self._qwen3vl_base)
@@ -242,7 +246,7 @@ class Lingbot2Policy:
         per_image = [int(t * h * w) // merge2 for t, h, w in grid.tolist()]
         ids = eng.build_input_ids(per_image, torch.as_tensor(obs["lang_tokens"]))
         return eng.predict(ids, obs["pixel_values"], grid, torch.as_tensor(obs["state"], dtype=torch.float32),
-                           torch.as_tensor(obs["noise"], dtype=torch.float32))
+                           torch.as_tensor(obs["noise"], dtype=torch.float32), use_graph=self._one_graph)
 
     # ------------------------------------------------------------------ graphs
     @_serialized

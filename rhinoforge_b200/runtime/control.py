@@ -23,6 +23,8 @@ KEPT_ENV: Dict[str, tuple] = {
     "RPU_TP_COMM": ("enum:fused,nccl", "fused", "MODEL"),
     "RPU_PI05_FUSED_DENOISE": ("bool", True, "MODEL"),
     "RPU_PI05_DENOISE_UNROLL": ("bool", True, "MODEL"),
+    "RPU_LINGBOT2_DENOISE_UNROLL": ("bool", True, "MODEL"),
+    "RPU_WALL_OSS_FUSED_DENOISE": ("bool", True, "MODEL"),
     "RPU_QWEN3_5_FREE_HF_WEIGHTS": ("bool", False, "MODEL"),
     "QWEN3_5_TEXT_CHUNK": ("int", 0, "MODEL"),
     "QWEN3_5_TEXT_PADDING_BUDGET": ("int", 64, "MODEL"),

@@ -26,7 +26,7 @@ class _FakeEngine:
     def build_input_ids(self, per_image, lang):
         return torch.cat([torch.full((n,), 150) for n in per_image] + [lang.flatten()])
 
-    def predict(self, ids, px, grid, state, noise):
+    def predict(self, ids, px, grid, state, noise, use_graph=True):
         self.calls += 1
         out = noise * 0.5 + state[:1]
         return torch.full_like(out, float("nan")) if self.nan else out
