@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """Wall-OSS vision-language-action policy: action chunk from camera images, an instruction and proprioception.
 
-This entry point validates its configuration; the model family itself is not part of this build yet, so a
-real run stops with UnsupportedModelError before any checkpoint is read."""
+The checkpoint directory must hold config.json, the safetensors shards, the Qwen2.5-VL processor files and the
+normalizer_action.pth / normalizer_propri.pth sidecars."""
 from __future__ import annotations
 
 import sys
@@ -26,6 +26,11 @@ def load_config(path) -> dict:
         raise ValueError("[request].images must be a list of path strings")
     if not isinstance(req.get("instruction"), str):
         raise ValueError("[request].instruction must be a string")
+    prop = req.get("proprioception")
+    if not isinstance(prop, list) or not prop or not all(isinstance(v, (int, float)) and not isinstance(v, bool) for v in prop):
+        raise ValueError("[request].proprioception must be a non-empty list of numbers")
+    if len(req["images"]) != len(model.get("camera_names", ["face_view"])):
+        raise ValueError("[request].images needs one path per entry of [model].camera_names")
     check_execution(config, {"prefill", "vision", "action"})
     return config
 
@@ -36,8 +41,22 @@ def main() -> int:
     if args.check_config:
         return ok(args.config, require_model(config))
     sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
-    from rpu_backend.api.errors import UnsupportedModelError
-    raise UnsupportedModelError(f"{FAMILY} is not built in this release; supported policies: Pi0.5 (examples/pi05.py)")
+    from _config import load_image, resolve_checkpoint
+    from rpu_backend.api import WallOssPolicy
+    model, req = config["model"], config["request"]
+    images = [load_image(p) for p in req["images"]]
+    policy = WallOssPolicy.from_pretrained(
+        resolve_checkpoint(config), dataset_key=model.get("dataset_key", "berkeley_autolab_ur5"),
+        camera_names=tuple(model.get("camera_names", ["face_view"])), action_horizon=int(model.get("action_horizon", 32)),
+        num_steps=int(model.get("num_steps", 10)), max_seq_len=int(model.get("max_seq_len", 2048)),
+        rpu_execution=config.get("rpu_execution")).to("rpu")
+    try:
+        out = policy.infer(images=images, instruction=req["instruction"], proprioception=req["proprioception"],
+                           noise_seed=int(req.get("noise_seed", 0)))
+    finally:
+        policy.close()
+    print(f"actions={tuple(out.actions.shape)} action_hz={out.action_hz:g} latency_ms={out.latency_ms:.3f}")
+    return 0
 
 
 if __name__ == "__main__":

@@ -8,7 +8,8 @@ _LAZY = {
     "RPUModelForConditionalGeneration": ("conditional_generation", "RPUModelForConditionalGeneration"),
     "Qwen3_5Cache": ("qwen3_5_cache", "Qwen3_5Cache"),
     "Pi05Policy": ("policy", "Pi05Policy"),
-    "WallOssPolicy": ("_unbuilt", "WallOssPolicy"),
+    "WallOssPolicy": ("wall_oss", "WallOssPolicy"),
+    "WallOssActionOutput": ("wall_oss", "WallOssActionOutput"),
     "Lingbot2Policy": ("lingbot2", "Lingbot2Policy"),
     "Lingbot2ActionOutput": ("lingbot2", "Lingbot2ActionOutput"),
     "HyEmbodiedPolicy": ("_unbuilt", "HyEmbodiedPolicy"),

@@ -1,10 +1,10 @@
 """Policy facades of model families that this framework does not run yet.
 
-The classes exist so that ``rpu_backend.api.WallOssPolicy`` and its siblings import and fail in a defined way: every
+The classes exist so that ``rpu_backend.api.HyEmbodiedPolicy`` imports and fails in a defined way: every
 constructor path raises :class:`UnsupportedModelError` naming the family, what it would need and what is available
-instead, before any checkpoint is read (the reference's facades: ``python/rpu_backend/api/wall_oss.py``,
-``hy_embodied.py``).  ``RhinoVLAPolicy`` is not among them: it wraps an externally assembled runtime
-and is built in :mod:`rhinoforge_b200.api.rhinovla`.  The shared pieces those policies use - runtime-environment
+instead, before any checkpoint is read (the reference's facade: ``python/rpu_backend/api/hy_embodied.py``).
+``WallOssPolicy``, ``Lingbot2Policy`` and ``RhinoVLAPolicy`` are not among them: they are built in
+:mod:`rhinoforge_b200.api.wall_oss`, :mod:`rhinoforge_b200.api.lingbot2` and :mod:`rhinoforge_b200.api.rhinovla`.  The shared pieces those policies use - runtime-environment
 validation, action de-normalisation, 6-D rotation decoding - are built (``_runtime_env``, ``action_denorm``,
 ``hy_action_decode``), and so are the towers they start from (Qwen2.5-VL ViT, SigLIP, the Qwen2.5 / Qwen3 decoder stack).
 """
@@ -18,7 +18,7 @@ from .errors import UnsupportedModelError
 def _facade(name: str, family: str, needs: str):
     def refuse(cls, *args: Any, **kwargs: Any):
         raise UnsupportedModelError(f"{family} is not built in this framework ({needs}); "
-                                    "the policy that runs today is Pi05Policy")
+                                    "the policies that run today are Pi05Policy, Lingbot2Policy and WallOssPolicy")
 
     body = {
         "__doc__": f"{family}: defined, not runnable (see :mod:`rhinoforge_b200.api._unbuilt`).",
@@ -30,9 +30,7 @@ def _facade(name: str, family: str, needs: str):
     return type(name, (), body)
 
 
-WallOssPolicy = _facade("WallOssPolicy", "Wall-OSS (Qwen2.5-VL backbone with a flow-matching action expert)",
-                        "needs the mixture-of-transformers action step and its denoise loop")
 HyEmbodiedPolicy = _facade("HyEmbodiedPolicy", "HunYuan embodied VLA (HYViT2 tower, twin-weight prefill, action expert)",
                            "needs the HYViT2 tower and row-routed twin weights")
 
-__all__ = ["WallOssPolicy", "HyEmbodiedPolicy"]
+__all__ = ["HyEmbodiedPolicy"]

@@ -341,6 +341,8 @@ class Lingbot2Engine:
         self.s_kvlen = torch.zeros(1, **i32)
         self.mask = torch.zeros(n, self.max_seq, dtype=torch.uint8, device=dev)
         self.image_token_id = self.vlm.image_token_id
+        cg = lambda k, d: hf_vlm_config.get(k, d) if isinstance(hf_vlm_config, dict) else getattr(hf_vlm_config, k, d)
+        self.vision_start_id, self.vision_end_id = int(cg("vision_start_token_id", 151652)), int(cg("vision_end_token_id", 151653))
 
     # ------------------------------------------------------------------ per-num_steps constants
     def schedule(self, num_steps: int) -> dict:
@@ -364,10 +366,21 @@ class Lingbot2Engine:
         return hit
 
     # ------------------------------------------------------------------ prefix
-    def build_input_ids(self, tokens_per_image: Sequence[int], lang_tokens: torch.Tensor) -> torch.Tensor:
-        """Prefix id sequence: one run of image placeholders per camera, then the instruction tokens."""
-        parts = [torch.full((int(t),), self.image_token_id, dtype=torch.long) for t in tokens_per_image]
-        return torch.cat(parts + [lang_tokens.flatten().to(torch.long)])
+    def build_input_ids(self, tokens_per_image: Sequence[int], lang_tokens: torch.Tensor, *,
+                        vision_boundaries: bool = False, tail_token_id: Optional[int] = None) -> torch.Tensor:
+        """Prefix id sequence: one run of image placeholders per camera (with ``vision_boundaries`` each run sits
+        between a vision-start and a vision-end token), then the instruction tokens and, when ``tail_token_id`` is
+        given, ``blocked_tail`` filler rows that stand in for learned query tokens the action rows must not see."""
+        parts = []
+        for t in tokens_per_image:
+            run = torch.full((int(t),), self.image_token_id, dtype=torch.long)
+            if vision_boundaries:
+                run = torch.cat((torch.tensor([self.vision_start_id]), run, torch.tensor([self.vision_end_id])))
+            parts.append(run)
+        parts.append(lang_tokens.flatten().to(torch.long))
+        if self.cfg.blocked_tail and tail_token_id is not None:
+            parts.append(torch.full((self.cfg.blocked_tail,), int(tail_token_id), dtype=torch.long))
+        return torch.cat(parts)
 
     @torch.no_grad()
     def prefill(self, input_ids: torch.Tensor, pixel_values: Optional[torch.Tensor], image_grid_thw) -> Tuple[int, int]:

@@ -62,7 +62,8 @@ def rope_index(token_types: Sequence[int], image_grids: Sequence[Sequence[int]],
     ``token_types[i]`` is 0 for text, 1 for an image placeholder row and 2 for a video-frame
     placeholder row; every maximal run of one non-zero type consumes the next grid ``(t, h, w)`` (in
     patches) of that kind -- a video of ``t`` frames counts as ``t`` grids ``(1, h, w)``, one per
-    timestamp-separated run.  Text advances all three axes together; a vision run occupies
+    timestamp-separated run -- and, when images follow each other without a separator token, as many
+    further grids as it takes to cover the run.  Text advances all three axes together; a vision run occupies
     ``t = start``, ``h = start + row``, ``w = start + col`` and the following text resumes at
     ``start + max(h, w) / merge``."""
     frames = [(1, int(h), int(w)) for t, h, w in video_grids for _ in range(int(t))]
@@ -78,17 +79,20 @@ def rope_index(token_types: Sequence[int], image_grids: Sequence[Sequence[int]],
             out.append(torch.arange(cur, cur + (j - i)).view(1, -1).expand(3, -1))
             cur += j - i
         else:
-            if not queues[kind]:
-                raise RPUBackendError("more vision placeholder runs than grids")
-            t, h, w = (int(v) for v in queues[kind].pop(0))
-            gh, gw = h // merge, w // merge
-            if t * gh * gw != j - i:
-                raise RPUBackendError(f"vision placeholder run of {j - i} rows does not match grid {(t, h, w)}")
-            pw = torch.arange(cur, cur + gw).repeat(gh * t)
-            ph = torch.arange(cur, cur + gh).repeat_interleave(gw * t)
-            pt = torch.full((t * gh * gw,), cur)
-            out.append(torch.stack((pt, ph, pw)))
-            cur += max(h, w) // merge
+            left = j - i
+            while left > 0:
+                if not queues[kind]:
+                    raise RPUBackendError("more vision placeholder rows than the grids cover")
+                t, h, w = (int(v) for v in queues[kind].pop(0))
+                gh, gw = h // merge, w // merge
+                if t * gh * gw > left:
+                    raise RPUBackendError(f"vision placeholder run of {j - i} rows does not match grid {(t, h, w)}")
+                pw = torch.arange(cur, cur + gw).repeat(gh * t)
+                ph = torch.arange(cur, cur + gh).repeat_interleave(gw * t)
+                pt = torch.full((t * gh * gw,), cur)
+                out.append(torch.stack((pt, ph, pw)))
+                cur += max(h, w) // merge
+                left -= t * gh * gw
         i = j
     return torch.cat(out, 1).to(torch.int32)
 

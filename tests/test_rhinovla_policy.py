@@ -5,7 +5,7 @@ import types
 
 import pytest
 
-from rhinoforge_b200.api import RhinoVLAPolicy, UnsupportedModelError, WallOssPolicy
+from rhinoforge_b200.api import HyEmbodiedPolicy, RhinoVLAPolicy, UnsupportedModelError
 from rhinoforge_b200.api.rhinovla import StagePlan, declared_capabilities, resolve_runtime_factory
 
 CAPS = {"prefill": ("chunk_size", "padding_rows", "padding_budget"), "action": ("chunk_size",)}
@@ -54,7 +54,7 @@ def test_constructor_is_closed_and_other_families_still_refuse():
     with pytest.raises(RuntimeError, match="not a public constructor"):
         RhinoVLAPolicy()
     with pytest.raises(UnsupportedModelError):
-        WallOssPolicy.from_pretrained("x")
+        HyEmbodiedPolicy.from_pretrained("x")
 
 
 def test_from_runtime_without_execution_config_is_a_plain_wrapper():
