@@ -51,7 +51,7 @@ def test_lingbot2_action_chunk_matches_fp32(blocked_tail, use_graph):
     g = torch.Generator().manual_seed(5)
     px = torch.randn(int((grid[:, 1] * grid[:, 2]).sum()), 3 * 2 * 16 * 16, generator=g)
     lang = torch.tensor([3, 9, 27, 81, 43, 129, 11])
-    ids = eng.build_input_ids([6, 4], lang)
+    ids = eng.build_input_ids([6, 4], lang, vision_boundaries=True)
     state = torch.randn(cfg.state_dim, generator=g)
     noise = torch.randn(cfg.horizon, cfg.action_dim, generator=g)
     got = eng.predict(ids, px, grid, state, noise, use_graph=use_graph).float().cpu().clone()

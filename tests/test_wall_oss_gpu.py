@@ -97,7 +97,7 @@ def test_qwen25vl_prompt_decoder_matches_hf_tokens_and_logits():
     grid, px, ids, _ = _inputs()
     tok, logits = eng.vlm.prefill(ids, px, grid, return_logits=True)
     with torch.no_grad():
-        o = ref(input_ids=ids[None], pixel_values=px, image_grid_thw=grid)
+        o = ref(input_ids=ids[None], pixel_values=px, image_grid_thw=grid, mm_token_type_ids=(ids[None] == IMG).int())
     want = o.logits[0, -1]
     got = logits.float().cpu().reshape(-1)[:VOCAB]
     assert float((got - want).abs().max()) < 3e-2 * max(1.0, float(want.abs().max()))
@@ -124,7 +124,8 @@ def test_wall_oss_action_chunk_matches_fp32(causal, masked, use_graph):
     got2 = eng.predict(ids, px, grid, noise, dof, padding_action=pad, use_graph=use_graph).float().cpu().clone()
     eng.check_status()
     with torch.no_grad():
-        o = ref(input_ids=ids[None], pixel_values=px, image_grid_thw=grid, use_cache=True)
+        o = ref(input_ids=ids[None], pixel_values=px, image_grid_thw=grid, mm_token_type_ids=(ids[None] == IMG).int(),
+                use_cache=True)
     past = o.past_key_values
     layers = getattr(past, "layers", None)
     kv = [(layers[i].keys[0], layers[i].values[0]) if layers is not None else (past[i][0][0], past[i][1][0])
