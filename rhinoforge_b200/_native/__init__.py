@@ -42,6 +42,7 @@ class RfGemm(C.Structure):
         ("force_splits", C.c_int32), ("force_swap", C.c_int32), ("force_bn", C.c_int32), ("w_packed", C.c_int32),
         ("w_scratch", C.c_void_p), ("w_scratch_bytes", C.c_uint64),
         ("ar_publish", C.c_int32), ("ar_cnt_base", C.c_int32),
+        ("prefetch", C.c_void_p), ("prefetch_bytes", C.c_uint64),
     ]
 
 

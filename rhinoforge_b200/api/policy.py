@@ -13,6 +13,7 @@ Reference: ``python/rpu_backend/api/policy.py:57-119,164-190,193-289``.
 """
 from __future__ import annotations
 
+import dataclasses
 from collections import deque
 from typing import Any, Dict, Optional
 
@@ -57,6 +58,13 @@ def resize_with_pad(img: torch.Tensor, size: int) -> torch.Tensor:
     return img * 2.0 - 1.0
 
 
+@dataclasses.dataclass(frozen=True)
+class Pi05ActionOutput:
+    actions: torch.Tensor            # [B, horizon, action_dim] fp32
+    latency_ms: float                # wall time of the call: pre-processing, prefill, denoise loop, result materialised
+    phase_ms: Dict[str, float]
+
+
 class Pi05Policy:
     def __init__(self) -> None:
         raise RuntimeError("Pi05Policy() is not a public constructor. Use Pi05Policy.from_pretrained(...) or "
@@ -72,6 +80,7 @@ class Pi05Policy:
         self._vlm_chunk_size = 0 if chunk == "auto" else chunk
         self._engine = None
         self._frozen = False
+        self.last_latency_ms = 0.0
         self._prepared: Dict[tuple, bool] = {}
         self.camera_keys = list(camera_keys) if camera_keys else None
         self.n_action_steps = n_action_steps or cfg.horizon
@@ -188,14 +197,16 @@ class Pi05Policy:
         args = self._inputs(batch)
         key = (args[0].shape[0], steps)
         eng._graphs.pop(key, None)
-        a = eng.predict(*args, num_steps=steps).clone()
-        b = eng.predict(*args, num_steps=steps).clone()
+        eng._prefill_graphs.clear()                       # vision + prefix prefill graph of this geometry is rebuilt too
+        a = eng.predict(*args, num_steps=steps).clone()   # BUILD: prefill graph (vision tower + prefix) and denoise graph
+        b = eng.predict(*args, num_steps=steps).clone()   # REPLAY of both
         eng.check_status()
         if not torch.equal(a, b):
-            raise RPUBackendError("Pi0.5 graph BUILD and REPLAY disagree: the captured loop is not deterministic")
+            raise RPUBackendError("Pi0.5 graph BUILD and REPLAY disagree: the captured stages are not deterministic")
         self._prepared[key] = True
         self._frozen = True
-        return {"batch_size": key[0], "num_steps": steps, "graphs": len(eng._graphs), "deterministic": True}
+        return {"batch_size": key[0], "num_steps": steps, "graphs": len(eng._graphs) + len(eng._prefill_graphs),
+                "stages": ["vision+prefix", "denoise"], "deterministic": True}
 
     @torch.no_grad()
     def predict_action_chunk(self, batch: dict, num_steps: Optional[int] = None) -> torch.Tensor:
@@ -210,8 +221,23 @@ class Pi05Policy:
         # whole loop from one captured graph (debugging and A/B timing)
         from ..runtime.control import rpu_env_bool
         one_graph = rpu_env_bool("RPU_PI05_FUSED_DENOISE", True) and rpu_env_bool("RPU_PI05_DENOISE_UNROLL", True)
+        import time
+        t0 = time.perf_counter()
         out = self.engine.predict(*args, num_steps=steps, use_graph=one_graph)
-        return out[:, :, :self.action_dim].float().clone()
+        out = out[:, :, :self.action_dim].float().clone()
+        if out.is_cuda:
+            torch.cuda.current_stream(out.device).synchronize()
+        self.last_latency_ms = (time.perf_counter() - t0) * 1000.0       # device work of the chunk, result materialised
+        return out
+
+    @torch.no_grad()
+    def infer(self, batch: dict, num_steps: Optional[int] = None) -> "Pi05ActionOutput":
+        """``predict_action_chunk`` with the wall time of the call attached (pre-processing included)."""
+        import time
+        t0 = time.perf_counter()
+        actions = self.predict_action_chunk(batch, num_steps)
+        return Pi05ActionOutput(actions=actions, latency_ms=(time.perf_counter() - t0) * 1000.0,
+                                phase_ms={"device_ms": self.last_latency_ms})
 
     @torch.no_grad()
     def select_action(self, batch: dict) -> torch.Tensor:
@@ -231,4 +257,4 @@ class Pi05Policy:
             self._engine = None
 
 
-__all__ = ["Pi05Policy", "resize_with_pad"]
+__all__ = ["Pi05Policy", "Pi05ActionOutput", "resize_with_pad"]

@@ -54,7 +54,10 @@ struct GemmTcParams {
   int ar_publish;     // small-M path: push the partial rows to every rank, bump the arrival counters, exit
   int ar_cnt_base;    // first arrival counter in every rank's flag array
   int ar_stage_off;   // shared-memory offset of the staging rows of the publish path
+  const uint8_t* pf_ptr;   // L2 prefetch hint: memory the next kernel will read
+  uint32_t pf_chunks;      // number of kPrefetchChunk-byte pieces of it, dealt out over the CTAs
 };
+constexpr uint32_t kPrefetchChunk = 8192;
 
 struct alignas(8) GemmSmemCtl {
   uint64_t full[kMaxStages];
@@ -223,6 +226,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (!W8) load_weights(i, s);
       load_acts(i, s);
       issued = i + 1;
+    }
+    if (ok && p.pf_chunks) {
+      // this CTA's own weight loads are all in flight: spend the rest of its life keeping HBM busy for the next kernel
+      const uint32_t ncta = gridDim.x * gridDim.y * gridDim.z;
+      const uint32_t cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+      for (uint32_t c = cta; c < p.pf_chunks; c += ncta) bulk_prefetch_l2(p.pf_ptr + (size_t)c * kPrefetchChunk, kPrefetchChunk);
     }
     if (!ok) {
       ctl->abort_flag = 1;
@@ -1041,6 +1050,12 @@ static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream)
   p.ar_publish = (g->ar_world > 1 && g->ar_publish && SWAP) ? 1 : 0;
   p.ar_cnt_base = g->ar_cnt_base;
   p.ar_stage_off = pl.splits > 1 ? pl.bn * (DUAL ? 2 : 1) * kBM * 4 : 0;
+  p.pf_ptr = nullptr; p.pf_chunks = 0;
+  if (SWAP && g->prefetch && g->prefetch_bytes >= kPrefetchChunk && g->M <= 256 &&
+      (reinterpret_cast<uintptr_t>(g->prefetch) & 15u) == 0) {
+    p.pf_ptr = reinterpret_cast<const uint8_t*>(g->prefetch);
+    p.pf_chunks = (uint32_t)std::min<uint64_t>(g->prefetch_bytes / kPrefetchChunk, 1u << 20);
+  }
   RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.grid_x, pl.grid_y, pl.splits), dim3(W8 ? 256 : 128), pl.smem_bytes, stream,
                                pl.splits, tmA, tmB, tmW, p));
   ::rf::count_launch();

@@ -116,6 +116,29 @@ static bool tp_publish_enabled() {
   return v;
 }
 
+// L2 prefetch hint for the next linear() call on this thread (set by the layer loop right before the call, consumed
+// by it): the weights of the linear layer that FOLLOWS, so that a weight-streaming GEMM hands HBM over to its
+// successor without an idle gap.  RF_GEMM_L2_PREFETCH_MB caps the bytes asked for (0: off).
+static thread_local const void* t_pf_ptr = nullptr;
+static thread_local uint64_t t_pf_bytes = 0;
+static uint64_t prefetch_cap_bytes() {
+  static const uint64_t v = [] {
+    const char* e = getenv("RF_GEMM_L2_PREFETCH_MB");
+    const long mb = e ? atol(e) : 0;
+    return (uint64_t)(mb < 0 ? 0 : mb) << 20;
+  }();
+  return v;
+}
+static void hint_next_weights(const Stack& s, const void* w, const void* scale, int64_t rows, int64_t K, int sections,
+                              int tokens) {
+  t_pf_ptr = nullptr; t_pf_bytes = 0;
+  if (!w || tokens > 256 || prefetch_cap_bytes() == 0) return;
+  const int eb = (s.cfg.weights_int8 && scale) ? 1 : 2;
+  const uint64_t bytes = s.cfg.weights_packed ? rf_pack_weight_bytes(rows, K, sections, eb) : (uint64_t)rows * K * eb;
+  t_pf_ptr = w;
+  t_pf_bytes = bytes < prefetch_cap_bytes() ? bytes : prefetch_cap_bytes();
+}
+
 // One linear layer: picks GEMV / tcgen05 GEMM / W8A16 and wires the fused all-reduce.  pub_ctas != null asks for
 // the publish-and-exit form: *pub_ctas receives the CTA count the consumer must wait for, or 0 when the shape took
 // the in-kernel form after all (more than 256 tokens), in which case `out` and `residual` were used as given.
@@ -135,6 +158,8 @@ static int linear(const Stack& s, const void* x, int64_t ldx, const void* w, con
   }
   g.status = s.status();
   g.force_swap = -1;
+  g.prefetch = t_pf_ptr; g.prefetch_bytes = t_pf_bytes;
+  t_pf_ptr = nullptr; t_pf_bytes = 0;
   g.ws = s.at<float>(s.off_sk_ws); g.ws_bytes = s.sk_ws_bytes;
   g.sem = s.at<uint32_t>(s.off_sk_flags); g.sem_count = Stack::kSkFlags;
   const bool ar = all_reduce && s.cfg.tp_world > 1;
@@ -304,6 +329,7 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
       mix_out = conv;
       mix_dim = VD;
     } else {
+    hint_next_weights(s, w.wo, w.so, H, AD, 1, T);
     rc = linear(s, xn, H, w.wqkv, w.sqkv, w.bqkv, wide, QD, nullptr, 0, T, QD, H, kActNone, 0, false, st);
     if (rc) return rc;
     {
@@ -370,6 +396,7 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     // residual) and the separate gated-residual launch disappears.
     const bool fuse_gate = c.gated_residual && !c.sandwich_norm && f.rows_per_mod >= T && !c.weights_int8 &&
                            c.tp_world == 1 && f.mod != nullptr;
+    hint_next_weights(s, w.w_up, w.s_up, s.glu() ? 2 * (int64_t)I : I, H, s.glu() ? 2 : 1, T);
     if (!side) {
       rc = linear_ar(s, mix_out, mix_dim, w.wo, w.so, w.bo, f.hidden, f.hidden, T, mix_dim,
                      norm_rides ? w.norm2_w : nullptr, xn, &have_xn2, st);
@@ -413,6 +440,7 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
                          c.dtype, st);
       if (rc) return rc;
     }
+    hint_next_weights(s, w.w_down, w.s_down, H, I, 1, T);
     rc = linear(s, xn, H, w.w_up, w.s_up, w.b_up, wide, I, nullptr, 0, T, I, H, act_of(c.mlp_kind),
                 s.glu() ? I : 0, false, st);
     if (rc) return rc;
@@ -423,6 +451,7 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     // the next layer's first norm can ride in this all-reduce unless something still changes hidden in between
     const bool hook_after = (f.deepstack && l < f.n_deepstack && f.deepstack[l]);
     const void* next_w = (norm_rides && l + 1 < le && !hook_after) ? s.layers[l + 1].norm1_w : nullptr;
+    if (l + 1 < le && s.layers[l + 1].mixer != 1) hint_next_weights(s, s.layers[l + 1].wqkv, s.layers[l + 1].sqkv, QD, H, 1, T);
     if (!side) {
       rc = linear_ar(s, wide, I, w.w_down, w.s_down, w.b_down, f.hidden, f.hidden, T, I, next_w, xn, &have_xn, st);
       if (rc) return rc;

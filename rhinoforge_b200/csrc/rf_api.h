@@ -67,6 +67,12 @@ typedef struct RfGemm {
   // it does not wait, reduce, add the residual or write `out`.  rf_ar_consume() finishes the all-reduce.
   int32_t ar_publish;
   int32_t ar_cnt_base;         // first of `world` arrival counters in every rank's flag array
+  // Optional hint (weight-streaming shapes of at most 256 tokens): device memory the NEXT kernel on the stream will
+  // read - normally the next linear layer's weights.  Once a CTA has issued its own last weight load it asks for its
+  // share of the first prefetch_bytes of that memory to be brought into L2, so HBM keeps streaming through this
+  // kernel's epilogue, the launch gap and the next kernel's prologue.  Never dereferenced; 16-byte aligned.
+  const void* prefetch;
+  uint64_t prefetch_bytes;
 } RfGemm;
 // bytes of the tile-major image of a [rows, K] weight with `sections` equal row sections
 uint64_t rf_pack_weight_bytes(int64_t rows, int64_t K, int32_t sections, int32_t elem_bytes);

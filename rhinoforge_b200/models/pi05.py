@@ -373,6 +373,12 @@ class Pi05Engine:
         self.s_kvlen = torch.zeros(Bm * n, **i32)
         self.s_pt = torch.zeros((Bm * n, self.cache.pages_per_seq), **i32)
         self.prefix_hidden = torch.zeros(Bm * self.max_prefix, v.hidden, dtype=dtype, device=dev)
+        # static inputs of the captured prefill: the valid cameras' pixels and the valid language token ids
+        S = cfg.vision.image_size
+        self.img_in = torch.zeros(Bm * cfg.num_views, 3, S, S, dtype=dtype, device=dev)
+        self.ids_in = torch.zeros(Bm * cfg.max_lang_tokens, **i32)
+        self._prefill_meta: Dict[tuple, dict] = {}
+        self._prefill_graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
 
     # ------------------------------------------------------------------ conditioning schedule
     def schedule(self, num_steps: int) -> dict:
@@ -397,38 +403,82 @@ class Pi05Engine:
         return hit
 
     # ------------------------------------------------------------------ prefix
+    def _prefill_geometry(self, im: torch.Tensor, tm: torch.Tensor) -> dict:
+        """Device index tensors of one input geometry (which cameras are valid, how many language tokens each sample
+        has): built once per geometry, so a repeated geometry copies nothing but pixels and token ids."""
+        key = (tuple(im.flatten().tolist()), tuple(tm.sum(1).tolist()))
+        hit = self._prefill_meta.get(key)
+        if hit is not None:
+            return hit
+        cfg, dev = self.cfg, self.device
+        B = im.shape[0]
+        n_img = im.sum(1) * cfg.tokens_per_image
+        n_lang = tm.sum(1)
+        lens = (n_img + n_lang).to(torch.int32)
+        starts = torch.cumsum(lens, 0, dtype=torch.int32) - lens
+        lang_rows = torch.cat([torch.arange(int(n_lang[b])) + int(starts[b]) + int(n_img[b]) for b in range(B)])
+        img_dst = torch.cat([torch.arange(int(n_img[b])) + int(starts[b]) for b in range(B)])
+        pos = torch.cat([torch.arange(int(l), dtype=torch.int32) for l in lens]).to(dev)
+        seq = torch.repeat_interleave(torch.arange(B, dtype=torch.int32), lens.long())
+        hit = dict(key=key, B=B, T=int(lens.sum()), n_valid=int(im.sum()), n_ids=int(n_lang.sum()), lens=lens.tolist(),
+                   longest=int(lens.max()), starts=starts.to(dev), q_len=lens.to(dev), pos=pos, seq=seq.to(dev),
+                   lang_rows=lang_rows.to(dev, torch.int32), img_dst=img_dst.to(dev, torch.int32))
+        if len(self._prefill_meta) >= 32:
+            self._prefill_meta.clear()
+            self._prefill_graphs.clear()
+        self._prefill_meta[key] = hit
+        return hit
+
+    def _prefill_run(self, m: dict) -> None:
+        """Vision tower, embedding, packed prefix prefill over the static inputs (device work only)."""
+        cfg, K = self.cfg, self.K
+        hidden = self.prefix_hidden[:m["T"]]
+        if m["n_valid"]:
+            img_rows = self.vision(self.img_in[:m["n_valid"]])                         # [n_valid, tok, H]
+            K.scatter_rows(hidden, img_rows.reshape(-1, cfg.vlm.hidden), m["img_dst"])
+        if m["n_ids"]:
+            lang = K.embedding(self.embed, self.ids_in[:m["n_ids"]], scale=math.sqrt(cfg.vlm.hidden))
+            K.scatter_rows(hidden, lang, m["lang_rows"])
+        self.prefix_stack.forward(hidden, q_start=m["starts"], q_len=m["q_len"], kv_len=m["q_len"], max_q_len=m["longest"],
+                                  max_kv_len=m["longest"], pos=m["pos"], cos=self.cos, sin=self.sin, seq_of_tok=m["seq"],
+                                  cache_pos=m["pos"], page_table=self.cache.page_table)
+
     @torch.no_grad()
-    def prefill(self, images: torch.Tensor, image_mask: torch.Tensor, tokens: torch.Tensor, token_mask: torch.Tensor):
-        """Encode the valid cameras and language tokens of every sample and fill the KV cache.
-        Returns the per-sample prefix lengths (host list)."""
-        cfg, K, dev = self.cfg, self.K, self.device
-        B, V = images.shape[:2]
+    def prefill(self, images: torch.Tensor, image_mask: torch.Tensor, tokens: torch.Tensor, token_mask: torch.Tensor, *,
+                use_graph: bool = True):
+        """Encode the valid cameras and language tokens of every sample and fill the KV cache; returns the per-sample
+        prefix lengths (host list).  The device work of one input geometry is captured in a CUDA graph on its first
+        use and replayed afterwards; only pixels and token ids are copied per call."""
+        B = images.shape[0]
         if B > self.max_batch:
             raise ValueError(f"batch {B} exceeds max_batch {self.max_batch}")
         im = torch.as_tensor(image_mask).bool().cpu()
         tm = torch.as_tensor(token_mask).bool().cpu()
-        keep = im.flatten().nonzero().flatten()
-        img_rows = self.vision(images.flatten(0, 1)[keep.to(images.device)])          # [n_valid, tok, H]
-        n_img = im.sum(1) * cfg.tokens_per_image
-        n_lang = tm.sum(1)
-        lens = (n_img + n_lang).to(torch.int32)
-        T = int(lens.sum())
-        starts = torch.cumsum(lens, 0, dtype=torch.int32) - lens
-        hidden = self.prefix_hidden[:T]
-        ids = tokens.cpu()[tm].to(torch.int32)
-        lang_rows = torch.cat([torch.arange(int(n_lang[b])) + int(starts[b]) + int(n_img[b]) for b in range(B)])
-        img_dst = torch.cat([torch.arange(int(n_img[b])) + int(starts[b]) for b in range(B)])
-        lang = K.embedding(self.embed, ids.to(dev), scale=math.sqrt(cfg.vlm.hidden))
-        K.scatter_rows(hidden, lang, lang_rows.to(dev, torch.int32))
-        K.scatter_rows(hidden, img_rows.reshape(-1, cfg.vlm.hidden), img_dst.to(dev, torch.int32))
-        pos = torch.cat([torch.arange(int(l), dtype=torch.int32) for l in lens])
-        seq = torch.repeat_interleave(torch.arange(B, dtype=torch.int32), lens.long())
-        pos_d = pos.to(dev)
-        q_len = lens.to(dev)
-        self.prefix_stack.forward(hidden, q_start=starts.to(dev), q_len=q_len, kv_len=q_len, max_q_len=int(lens.max()),
-                                  max_kv_len=int(lens.max()), pos=pos_d, cos=self.cos, sin=self.sin,
-                                  seq_of_tok=seq.to(dev), cache_pos=pos_d, page_table=self.cache.page_table)
-        return lens.tolist()
+        m = self._prefill_geometry(im, tm)
+        if m["n_valid"]:
+            flat = images.flatten(0, 1)
+            if m["n_valid"] != flat.shape[0]:
+                flat = flat[im.flatten().nonzero().flatten().to(flat.device)]
+            self.img_in[:m["n_valid"]].copy_(flat, non_blocking=True)
+        if m["n_ids"]:
+            ids = tokens.cpu()[tm].to(torch.int32)
+            self.ids_in[:m["n_ids"]].copy_(ids)
+        if not use_graph:
+            self._prefill_run(m)
+            return m["lens"]
+        gph = self._prefill_graphs.get(m["key"])
+        if gph is None:
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._prefill_run(m)                                     # warm-up: load kernels, fill metadata caches
+            torch.cuda.current_stream().wait_stream(s)
+            gph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gph, stream=s):
+                self._prefill_run(m)
+            self._prefill_graphs[m["key"]] = gph
+        gph.replay()
+        return m["lens"]
 
     # ------------------------------------------------------------------ denoise
     def _denoise_loop(self, B: int, num_steps: int) -> None:
@@ -477,7 +527,7 @@ class Pi05Engine:
 
     @torch.no_grad()
     def predict(self, images, image_mask, tokens, token_mask, noise, num_steps: int = 10, *, use_graph: bool = True):
-        lens = self.prefill(images, image_mask, tokens, token_mask)
+        lens = self.prefill(images, image_mask, tokens, token_mask, use_graph=use_graph)
         return self.denoise(lens, noise, num_steps, use_graph=use_graph)
 
     def check_status(self) -> None:
@@ -487,6 +537,7 @@ class Pi05Engine:
 
     def close(self) -> None:
         self._graphs.clear()
+        self._prefill_graphs.clear()
         self.vision.close()
         self.prefix_stack.close()
         self.expert_stack.close()

@@ -86,6 +86,7 @@ class VisionTower:
                          true_head_dim=geo.head_dim, max_tokens=max_tokens, max_seqs=max_seqs)
         self.max_tokens, self.max_seqs = max_tokens, max_seqs
         self.stack = NativeStack(spec, layer_weights, device=device, dtype=dtype)
+        self._meta: Dict[tuple, tuple] = {}
 
     def run(self, hidden: torch.Tensor, seq_lens: Sequence[int], *, pos: Optional[torch.Tensor] = None,
             cos=None, sin=None, axis_of_freq=None, taps: Optional[Dict[int, torch.Tensor]] = None) -> torch.Tensor:
@@ -93,14 +94,19 @@ class VisionTower:
         if T > self.max_tokens or len(seq_lens) > self.max_seqs or sum(seq_lens) != T:
             raise RPUBackendError(f"vision tower: {T} tokens / {len(seq_lens)} sequences exceed the planned "
                                   f"{self.max_tokens} / {self.max_seqs} (or lengths do not add up)")
-        lens = torch.tensor(list(seq_lens), dtype=torch.int32)
-        starts = torch.cumsum(lens, 0, dtype=torch.int32) - lens
-        dev = self.device
-        q_len, q_start = lens.to(dev), starts.to(dev)
-        if pos is None:
-            pos = torch.zeros(T, dtype=torch.int32, device=dev)
-        self.stack.forward(hidden, q_start=q_start, q_len=q_len, kv_len=q_len, max_q_len=int(lens.max()),
-                           max_kv_len=int(lens.max()), pos=pos, cos=cos, sin=sin, axis_of_freq=axis_of_freq, taps=taps)
+        # sequence metadata is cached per partition: a repeated geometry launches no copy (and can be graph-captured)
+        key = tuple(int(v) for v in seq_lens)
+        meta = self._meta.get(key)
+        if meta is None:
+            lens = torch.tensor(list(key), dtype=torch.int32)
+            starts = torch.cumsum(lens, 0, dtype=torch.int32) - lens
+            dev = self.device
+            meta = (starts.to(dev), lens.to(dev), int(lens.max()), torch.zeros(T, dtype=torch.int32, device=dev))
+            if len(self._meta) < 64:
+                self._meta[key] = meta
+        q_start, q_len, longest, zero_pos = meta
+        self.stack.forward(hidden, q_start=q_start, q_len=q_len, kv_len=q_len, max_q_len=longest, max_kv_len=longest,
+                           pos=zero_pos if pos is None else pos, cos=cos, sin=sin, axis_of_freq=axis_of_freq, taps=taps)
         return hidden
 
     def close(self):

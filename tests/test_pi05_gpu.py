@@ -41,8 +41,23 @@ def test_actions_match_fp32_reference(B, steps):
     # a different prompt through the same graph: metadata buffers are updated in place
     args2 = _inputs(cfg, B, seed=5)
     want2 = TorchPi05(cfg, sd, device="cuda").sample_actions(*args2, num_steps=steps).cpu()
+    import ctypes
+    from rhinoforge_b200 import _native as N
+    lib = N.lib()
+    lib.rf_launch_count.restype = ctypes.c_uint64
+    c0 = lib.rf_launch_count()
     got2 = eng.predict(*args2, num_steps=steps).float().cpu()
+    assert lib.rf_launch_count() == c0, "vision tower, prefix prefill and denoise loop all replay from graphs"
+    assert len(eng._prefill_graphs) == 1 and len(eng._graphs) == 1
     assert float((got2 - want2).abs().max() / want2.abs().max()) < 3e-2
+    # another input geometry (camera 1 of sample 0 missing) builds its own prefill graph and stays correct
+    im3 = args2[1].clone()
+    im3[0, 1] = False
+    args3 = (args2[0], im3, *args2[2:])
+    want3 = TorchPi05(cfg, sd, device="cuda").sample_actions(*args3, num_steps=steps).cpu()
+    got3 = eng.predict(*args3, num_steps=steps).float().cpu()
+    assert len(eng._prefill_graphs) == 2
+    assert float((got3 - want3).abs().max() / want3.abs().max()) < 3e-2
     eng.close()
 
 
