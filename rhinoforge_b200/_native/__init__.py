@@ -43,6 +43,9 @@ class RfGemm(C.Structure):
         ("w_scratch", C.c_void_p), ("w_scratch_bytes", C.c_uint64),
         ("ar_publish", C.c_int32), ("ar_cnt_base", C.c_int32),
         ("prefetch", C.c_void_p), ("prefetch_bytes", C.c_uint64),
+        ("w_bits", C.c_int32), ("w_group", C.c_int32), ("w_fp4", C.c_int32), ("ss_tiles", C.c_int32),
+        ("ss_out", C.c_void_p), ("ss_in", C.c_void_p), ("ss_ld", C.c_int32), ("ss_dim", C.c_int32),
+        ("ss_eps", C.c_float), ("reserved0", C.c_int32),
     ]
 
 
@@ -113,7 +116,9 @@ class RfStackConfig(C.Structure):
                                          "tp_world", "tp_rank", "weights_int8", "decode_gemv_max_m", "attn_gate",
                                          "gdn_Hk", "gdn_Hv", "gdn_Dk", "gdn_Dv", "gdn_conv_k", "weights_packed",
                                          "moe_experts", "moe_top_k", "moe_expert_inter", "moe_score_fn",
-                                         "moe_norm_topk")] + [("moe_routed_scale", C.c_float)]
+                                         "moe_norm_topk")] + [("moe_routed_scale", C.c_float)] + \
+               [("weights_bits", C.c_int32), ("weights_group", C.c_int32), ("norm_folded", C.c_int32),
+                ("reserved0", C.c_int32)]
 
 
 class RfLayerWeights(C.Structure):
@@ -205,6 +210,8 @@ def lib() -> C.CDLL:
         l.rf_stack_status_ptr.restype = C.c_void_p
         l.rf_kvpool_create.restype = C.c_int64
         l.rf_pack_weight_bytes.restype = C.c_uint64
+        l.rf_pack_w4_bytes.restype = C.c_uint64
+        l.rf_pack_w4_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int32, C.c_int32]
         for fn in ("rf_stack_destroy", "rf_stack_set_layer", "rf_stack_set_head", "rf_stack_set_comm",
                    "rf_stack_arena_bytes", "rf_stack_bind_arena", "rf_stack_status_ptr", "rf_stack_forward",
                    "rf_stack_head", "rf_stack_final_norm", "rf_kvpool_destroy", "rf_kvpool_reserve",

@@ -130,6 +130,75 @@ template <> __device__ __forceinline__ uint4 widen_i8x8<__nv_bfloat16>(uint2 q) 
 }
 
 
+// Eight int4 values (two's complement nibbles; nibble j of the word holds column {0,2,4,6,1,3,5,7}[j] of the group,
+// so that nibbles j and j + 4 are a pair of neighbouring columns) -> eight 16-bit values times `s`, in column order.
+// A nibble n becomes the offset code v = n ^ 8 = q + 8 dropped into the mantissa of a power of two (fp16 1024, bf16
+// 128: both hold v exactly), from which the offset is subtracted: no integer-to-float conversion.
+template <typename T> __device__ __forceinline__ uint4 widen_i4x8(uint32_t x, T s);
+template <> __device__ __forceinline__ uint4 widen_i4x8<__half>(uint32_t x, __half s) {
+  x ^= 0x88888888u;
+  const __half2 off = __half2half2(__float2half_rn(1032.f)), s2 = __half2half2(s);
+  uint4 r;
+  uint32_t* o = &r.x;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t t = ((x >> (4 * j)) & 0x000F000Fu) | 0x64006400u;
+    __half2 v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t), off), s2);
+    o[j] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  return r;
+}
+template <> __device__ __forceinline__ uint4 widen_i4x8<__nv_bfloat16>(uint32_t x, __nv_bfloat16 s) {
+  x ^= 0x88888888u;
+  const __nv_bfloat162 off = __bfloat162bfloat162(__float2bfloat16_rn(136.f)), s2 = __bfloat162bfloat162(s);
+  uint4 r;
+  uint32_t* o = &r.x;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t t = ((x >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
+    __nv_bfloat162 v = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&t), off), s2);
+    o[j] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  return r;
+}
+
+// Eight e2m1 codes (same nibble order as widen_i4x8) -> eight 16-bit values times `s`.  The magnitude index picks a byte
+// out of an eight-entry table with one byte permute per four codes (fp16: only the high byte of {0, .5, 1, 1.5, 2, 3, 4,
+// 6} is non-zero); the sign bit of the code moves to the sign bit of the value.
+template <typename T> __device__ __forceinline__ uint4 widen_e2m1x8(uint32_t x, T s);
+template <> __device__ __forceinline__ uint4 widen_e2m1x8<__half>(uint32_t x, __half s) {
+  const uint32_t m = x & 0x77777777u;
+  const uint32_t a = __byte_perm(0x3E3C3800u, 0x46444240u, m & 0xFFFFu);     // high bytes of codes 0..3
+  const uint32_t b = __byte_perm(0x3E3C3800u, 0x46444240u, m >> 16);         // high bytes of codes 4..7
+  const __half2 s2 = __half2half2(s);
+  uint4 r;
+  uint32_t* o = &r.x;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t t = (((a >> (8 * j)) & 0xFFu) << 8) | (((b >> (8 * j)) & 0xFFu) << 24) | (((x >> (4 * j)) & 0x00080008u) << 12);
+    __half2 v = __hmul2(*reinterpret_cast<__half2*>(&t), s2);
+    o[j] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  return r;
+}
+template <> __device__ __forceinline__ uint4 widen_e2m1x8<__nv_bfloat16>(uint32_t x, __nv_bfloat16 s) {
+  const uint32_t m = x & 0x77777777u;
+  // bf16 of the eight magnitudes: 0000 3F00 3F80 3FC0 4000 4040 4080 40C0
+  const uint32_t ah = __byte_perm(0x3F3F3F00u, 0x40404040u, m & 0xFFFFu), al = __byte_perm(0xC0800000u, 0xC0804000u, m & 0xFFFFu);
+  const uint32_t bh = __byte_perm(0x3F3F3F00u, 0x40404040u, m >> 16), bl = __byte_perm(0xC0800000u, 0xC0804000u, m >> 16);
+  const __nv_bfloat162 s2 = __bfloat162bfloat162(s);
+  uint4 r;
+  uint32_t* o = &r.x;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t t = ((al >> (8 * j)) & 0xFFu) | (((ah >> (8 * j)) & 0xFFu) << 8) | (((bl >> (8 * j)) & 0xFFu) << 16) |
+                 (((bh >> (8 * j)) & 0xFFu) << 24) | (((x >> (4 * j)) & 0x00080008u) << 12);
+    __nv_bfloat162 v = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&t), s2);
+    o[j] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  return r;
+}
+
 // The same on N values with the activation switch outside the element loop.
 template <int N>
 __device__ __forceinline__ void apply_act_n(int act, const float (&g)[N], const float (&u)[N], float (&v)[N]) {

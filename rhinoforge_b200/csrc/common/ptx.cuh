@@ -146,6 +146,15 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
       "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
+// The same with an L2 cache policy (createpolicy): evict_first for data that is read once.
+__device__ __forceinline__ void bulk_load_1d_hint(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar,
+                                                  uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::
+          "r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
 // Tiled bulk store shared -> global of one box of a 2-D tensor map (x = innermost coordinate, a multiple of
 // 16 bytes; parts of the box outside the tensor are not written).  The issuing thread owns the bulk group.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int x, int y) {

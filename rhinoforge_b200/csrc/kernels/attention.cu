@@ -37,14 +37,23 @@ struct alignas(8) AttnCtl {
   int32_t abort_flag;
 };
 
-template <int HD>
+// STREAM: the page is read once in this launch (decode): it takes the L2 evict-first policy, so that a step's KV
+// traffic does not push the activations and the next kernel's first weight blocks out of L2.
+template <int HD, bool STREAM = false>
 __device__ __forceinline__ void load_kv_page(const CUtensorMap* tmK, const CUtensorMap* tmV,
                                              uint8_t* page_smem, uint64_t* bar, int col0, int row) {
   constexpr int J = HD / 64;
+  uint64_t pol = 0;
+  if (STREAM) pol = l2_policy_evict_first();
 #pragma unroll
   for (int j = 0; j < J; ++j) {
-    tma_load_2d(page_smem + j * kBoxBytes, tmK, bar, col0 + j * 64, row);
-    tma_load_2d(page_smem + (J + j) * kBoxBytes, tmV, bar, col0 + j * 64, row);
+    if (STREAM) {
+      tma_load_2d_hint(page_smem + j * kBoxBytes, tmK, bar, col0 + j * 64, row, pol);
+      tma_load_2d_hint(page_smem + (J + j) * kBoxBytes, tmV, bar, col0 + j * 64, row, pol);
+    } else {
+      tma_load_2d(page_smem + j * kBoxBytes, tmK, bar, col0 + j * 64, row);
+      tma_load_2d(page_smem + (J + j) * kBoxBytes, tmV, bar, col0 + j * 64, row);
+    }
   }
 }
 
@@ -140,8 +149,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
             row = p.kv_start[seq] + pg * 16;
             col0 = kvh * HD;
           }
-          load_kv_page<HD>(&tmK, &tmV, smem + (size_t)s * kStageBytes + w * kPageBytes,
-                           &ctl->full[s], col0, row);
+          if (p.kv_stream)
+            load_kv_page<HD, true>(&tmK, &tmV, smem + (size_t)s * kStageBytes + w * kPageBytes, &ctl->full[s], col0, row);
+          else
+            load_kv_page<HD>(&tmK, &tmV, smem + (size_t)s * kStageBytes + w * kPageBytes, &ctl->full[s], col0, row);
         }
       }
     }
@@ -502,6 +513,7 @@ static int fill_params(const RfAttn* a, AttnParams* p) {
   if (paged) RF_REQUIRE(a->v_pool && a->page_table && a->pool_pages > 0, "paged attention needs v_pool, page_table, pool_pages");
   else RF_REQUIRE(a->k && a->v && a->kv_start && a->kv_rows_total > 0, "contiguous attention needs k, v, kv_start, kv_rows_total");
   p->q = a->q; p->ldq = a->ldq; p->out = a->out; p->ldo = a->ldo;
+  p->kv_stream = 0;
   p->page_table = a->page_table; p->pt_stride = a->pt_stride; p->paged = paged ? 1 : 0;
   p->num_seqs = a->num_seqs; p->Hq = a->Hq; p->Hkv = a->Hkv; p->G = a->Hq / a->Hkv;
   p->q_start = a->q_start; p->q_len = a->q_len; p->kv_start = a->kv_start; p->kv_len = a->kv_len;
@@ -574,6 +586,10 @@ static int launch_decode(const RfAttn* a, AttnParams& p, cudaStream_t s) {
   }
   p.splits = splits;
   p.pages_per_split = pl.pages_per_split;
+  {
+    static const int ef = [] { const char* e = getenv("RF_ATTN_KV_EVICT_FIRST"); return e ? atoi(e) : 1; }();
+    p.kv_stream = ef;
+  }
   dim3 grid(splits, a->Hkv, a->num_seqs);
   RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(grid), dim3(160), smem, s, 1, tmK, tmV, p));
   RF_CUDA_CHECK(cudaGetLastError());

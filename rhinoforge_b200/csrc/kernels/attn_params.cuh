@@ -19,6 +19,7 @@ struct AttnParams {
   float scale_log2;
   float* ws_o; float* ws_lse;
   int32_t splits, pages_per_split, stages;
+  int32_t kv_stream;      // decode: K/V pages are read with the L2 evict-first policy
   int32_t* status;
 };
 

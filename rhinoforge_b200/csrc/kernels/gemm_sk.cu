@@ -55,6 +55,7 @@ struct GemmSkParams {
   int tmem_cols;             // tensor-memory columns this CTA allocates (a power of two covering its accumulator buffers)
   // tensor-parallel publish (see gemm_tc.cu / ar_consume.cu)
   int ar_world, ar_rank, ar_publish, ar_cnt_base;
+  int w_evict_first;       // weights are read with the L2 evict-first policy (streamed once)
   void* const* ar_recv; uint32_t* const* ar_flags; uint32_t* ar_state; uint64_t ar_half_bytes;
 };
 
@@ -129,8 +130,12 @@ gemm_sk_kernel(const __grid_constant__ CUtensorMap tmX, const GemmSkParams p) {
         uint8_t* st = smem + (size_t)s * stage_bytes;
 #pragma unroll
         for (int wt = 0; wt < kW; ++wt)
-          bulk_load_1d(st + wt * kSkWBlock, p.w_packed + ((size_t)(t + wt * p.dual_tiles) * KB + kb) * kSkWBlock, kSkWBlock,
-                       &ctl->full[s]);
+          if (p.w_evict_first)
+            bulk_load_1d_hint(st + wt * kSkWBlock, p.w_packed + ((size_t)(t + wt * p.dual_tiles) * KB + kb) * kSkWBlock,
+                              kSkWBlock, &ctl->full[s], l2_policy_evict_first());
+          else
+            bulk_load_1d(st + wt * kSkWBlock, p.w_packed + ((size_t)(t + wt * p.dual_tiles) * KB + kb) * kSkWBlock, kSkWBlock,
+                         &ctl->full[s]);
       };
       auto load_x = [&](long long u, int s) {
         const int kb = (int)(u % KB);
@@ -417,6 +422,7 @@ static bool sk_plan(const RfGemm* g, SkPlan* pl) {
     return false;
   if (mode == 1 && ceil_div(g->N, kSkBM) < 4 * sm_count()) return false;
   if (g->ar_world > 1 && !g->ar_publish) return false;     // the in-kernel all-reduce form stays with gemm_tc.cu
+  if (g->ss_in || g->ss_out) return false;                 // folded RMSNorm lives in gemm_tc.cu's epilogue
   const bool dual = g->dual_offset > 0;
   const int bn = round_up(std::max(g->M, 16), 16);
   if ((dual ? 2 : 1) * bn > 512) return false;
@@ -485,6 +491,10 @@ static int launch_sk(const RfGemm* g, const SkPlan& pl, cudaStream_t stream) {
   p.dual_offset = g->dual_offset; p.dual_tiles = pl.tiles; p.tiles = pl.tiles; p.units = pl.units;
   p.stage_off = pl.stage_off; p.ctl_off = pl.ctl_off; p.tmem_cols = pl.tmem_cols;
   p.ar_world = g->ar_world; p.ar_rank = g->ar_rank; p.ar_publish = g->ar_publish; p.ar_cnt_base = g->ar_cnt_base;
+  {
+    static const int ef_env = [] { const char* e = getenv("RF_GEMM_W_EVICT_FIRST"); return e ? atoi(e) : 1; }();
+    p.w_evict_first = ef_env ? 1 : 0;
+  }
   p.ar_recv = g->ar_recv; p.ar_flags = g->ar_flags; p.ar_state = g->ar_state; p.ar_half_bytes = g->ar_recv_bytes;
   RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.ctas), dim3(kSkThreads), pl.smem, stream, 1, tmX, p));
   ::rf::count_launch();

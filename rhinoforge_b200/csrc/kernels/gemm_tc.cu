@@ -56,6 +56,16 @@ struct GemmTcParams {
   int ar_stage_off;   // shared-memory offset of the staging rows of the publish path
   const uint8_t* pf_ptr;   // L2 prefetch hint: memory the next kernel will read
   uint32_t pf_chunks;      // number of kPrefetchChunk-byte pieces of it, dealt out over the CTAs
+  int w4;                  // 1: int4 weight image (4096 bytes of nibbles + in-block scales per 128 x 64 block)
+  int w4_ns;               // scales per row of a block: 0 (per-channel scale in the epilogue), 1, 2 or 4
+  int w4_fp4;              // 1: the nibbles are e2m1 floating-point codes
+  int pf_ahead;            // packed weights: k blocks beyond the ring that are asked into L2 ahead of their bulk copy
+  int w_evict_first;       // packed weights are read with the L2 evict-first policy (streamed once)
+  int q_blk_bytes;         // bytes of one quantised 128 x 64 block in the staging area / the packed image
+  float* ss_out;           // per (128-column tile, token) sum of squares of the finished values (swap mode)
+  const float* ss_in;      // per (tile, token) sums of squares of the input rows: the result is scaled by their rstd
+  int ss_tiles, ss_ld;
+  float ss_inv_dim, ss_eps;
 };
 constexpr uint32_t kPrefetchChunk = 8192;
 
@@ -68,6 +78,8 @@ struct alignas(8) GemmSmemCtl {
   uint64_t accum;
   uint32_t tmem_base;
   int32_t abort_flag;
+  float rs[256];           // ss_in: reciprocal RMS of this tile's token columns
+  float ssw[4][256];       // ss_out: the four epilogue warps' partial sums of squares per token column
 };
 
 // W8 = int8 weights (W8A16): TMA brings the int8 tile into a staging area of the stage, four extra
@@ -95,9 +107,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int b_tile_bytes = bn * kBK * 2;
   constexpr int kWTiles = DUAL ? 2 : 1;                    // weight tiles per stage
   const int w_rows = SWAP ? kBM : bn;                      // rows of one weight tile
-  const int q_tile_bytes = W8 ? w_rows * kBK : 0;          // int8 staging of one weight tile
+  const int q_tile_bytes = W8 ? (w_rows / kBM) * p.q_blk_bytes + (w_rows % kBM) * kBK : 0;   // staging of one weight tile
   const int half_bytes = kATiles * kATileBytes + kBTiles * b_tile_bytes;   // the 16-bit tiles
-  const int stage_bytes = half_bytes + kWTiles * q_tile_bytes;
+  // the next stage's swizzled 16-bit tiles must start on a 1024-byte boundary (an int4 block with its scales is not
+  // a multiple of that)
+  const int stage_bytes = half_bytes + ((kWTiles * q_tile_bytes + 1023) & ~1023);
   const int act_bytes = SWAP ? b_tile_bytes : kATileBytes;
   GemmSmemCtl* ctl = reinterpret_cast<GemmSmemCtl*>(smem + p.ctl_offset);
 
@@ -157,7 +171,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int kc = kblock(i) * kBK;
       if (p.w_packed) {
         // contiguous 128-row x 64-column blocks: one bulk copy each
-        constexpr uint32_t kBlk = W8 ? (uint32_t)(kBM * kBK) : (uint32_t)kATileBytes;
+        const uint32_t kBlk = W8 ? (uint32_t)p.q_blk_bytes : (uint32_t)kATileBytes;
         const int rt0 = (SWAP ? a0 : b0) / kBM;
         const int nsub = SWAP ? 1 : bn / kBM;
 #pragma unroll
@@ -166,7 +180,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             : (SWAP ? st + wt * kATileBytes : st + kATiles * kATileBytes + wt * b_tile_bytes);
           for (int sub = 0; sub < nsub; ++sub) {
             const uint8_t* src = p.w_packed + ((size_t)(rt0 + sub + wt * p.dual_tiles) * p.kb_total + kblock(i)) * kBlk;
-            bulk_load_1d(dst + (size_t)sub * kBlk, src, kBlk, wbar);
+            if (p.w_evict_first) bulk_load_1d_hint(dst + (size_t)sub * kBlk, src, kBlk, wbar, l2_policy_evict_first());
+            else bulk_load_1d(dst + (size_t)sub * kBlk, src, kBlk, wbar);
+            // keep more bytes in flight towards HBM than the ring holds: the block that will be copied pf_ahead ring
+            // slots from now is asked into L2 already, so that its copy later completes with L2 latency
+            if (p.pf_ahead && i + p.pf_ahead < kb_count)
+              bulk_prefetch_l2(p.w_packed + ((size_t)(rt0 + sub + wt * p.dual_tiles) * p.kb_total + kblock(i + p.pf_ahead)) * kBlk, kBlk);
           }
         }
       } else if (W8) {
@@ -266,6 +285,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int wt = 0; wt < kWTiles; ++wt) {
         const uint8_t* src = st + half_bytes + wt * q_tile_bytes;
         uint8_t* dst = SWAP ? st + wt * kATileBytes : st + kATiles * kATileBytes + wt * b_tile_bytes;
+        if (p.w4) {
+          // 32 nibbles (one 16-byte piece = half a row) per thread and round -> four 16-byte pieces of the 16-bit tile
+          for (int idx = ct; idx < w_rows * 2; idx += 128) {
+            const int row = idx >> 1, h = idx & 1;
+            const uint8_t* blk = src + (size_t)(row >> 7) * p.q_blk_bytes;
+            const int r = row & 127;
+            const uint4 q = *reinterpret_cast<const uint4*>(blk + r * 32 + h * 16);
+            // word w of the piece covers columns [32 h + 8 w, +8): its scale is number (4 h + w) * ns / 8 of the row
+            const T one = Num<T>::from_f(1.f);
+            const T* srow = reinterpret_cast<const T*>(blk + 4096) + r * p.w4_ns;
+            const T s0 = p.w4_ns ? srow[(4 * h + 0) * p.w4_ns >> 3] : one, s1 = p.w4_ns ? srow[(4 * h + 1) * p.w4_ns >> 3] : one;
+            const T s2 = p.w4_ns ? srow[(4 * h + 2) * p.w4_ns >> 3] : one, s3 = p.w4_ns ? srow[(4 * h + 3) * p.w4_ns >> 3] : one;
+            uint8_t* drow = dst + row * 128;
+            const int c = 4 * h, sw = row & 7;
+            if (p.w4_fp4) {
+              *reinterpret_cast<uint4*>(drow + (((c + 0) ^ sw) << 4)) = widen_e2m1x8<T>(q.x, s0);
+              *reinterpret_cast<uint4*>(drow + (((c + 1) ^ sw) << 4)) = widen_e2m1x8<T>(q.y, s1);
+              *reinterpret_cast<uint4*>(drow + (((c + 2) ^ sw) << 4)) = widen_e2m1x8<T>(q.z, s2);
+              *reinterpret_cast<uint4*>(drow + (((c + 3) ^ sw) << 4)) = widen_e2m1x8<T>(q.w, s3);
+            } else {
+              *reinterpret_cast<uint4*>(drow + (((c + 0) ^ sw) << 4)) = widen_i4x8<T>(q.x, s0);
+              *reinterpret_cast<uint4*>(drow + (((c + 1) ^ sw) << 4)) = widen_i4x8<T>(q.y, s1);
+              *reinterpret_cast<uint4*>(drow + (((c + 2) ^ sw) << 4)) = widen_i4x8<T>(q.z, s2);
+              *reinterpret_cast<uint4*>(drow + (((c + 3) ^ sw) << 4)) = widen_i4x8<T>(q.w, s3);
+            }
+          }
+          continue;
+        }
         // 16 int8 (one 16-byte piece) per thread and round; consecutive threads take consecutive pieces, so a
         // warp reads 512 contiguous bytes (8 rows x 64) without bank conflicts
         for (int idx = ct; idx < w_rows * 4; idx += 128) {
@@ -354,10 +401,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint64_t slot_off = (uint64_t)(call & 1u) * p.ar_half_bytes;
   const uint32_t crank = p.splits > 1 ? cluster_ctarank() : 0u;
 
+  // folded RMSNorm: reciprocal RMS of every token column of this tile from the producer's per-tile sums of squares
+  const bool use_rs = SWAP && p.ss_in != nullptr;
+  if (use_rs) {
+    for (int c = tid; c < bn; c += (int)blockDim.x) {
+      const int tok = blockIdx.y * bn + c;
+      float s = 0.f;
+      if (tok < p.M)
+        for (int t = 0; t < p.ss_tiles; ++t) s += p.ss_in[(size_t)t * p.ss_ld + tok];
+      ctl->rs[c] = rsqrtf(s * p.ss_inv_dim + p.ss_eps);
+    }
+    __syncthreads();
+  }
+  const bool emit_ss = SWAP && p.ss_out != nullptr && p.ar_world <= 1;
+  // sum over this warp's 32 output features of the square of one finished value per lane, for token column c
+  auto ss_add = [&](int c, float v) {
+    float q = v * v;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    if (lane_id() == 0 && warp < 4) ctl->ssw[warp][c] = q;
+  };
+
   // per-element epilogue math shared by both paths
-  const bool affine = p.row_scale || scale || use_bias;
+  const bool affine = p.row_scale || scale || use_bias || use_rs;
   auto finish = [&](int tok, int n, float vg, float vu) -> float {
     if (!affine) return apply_act(p.act, vg, vu);
+    if (use_rs) {
+      const float rs = ctl->rs[tok - blockIdx.y * bn];
+      vg *= rs;
+      vu *= rs;
+    }
     if (p.row_scale) {
       const float rs = p.row_scale[tok];
       vg *= rs;
@@ -528,17 +601,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int n = SWAP ? a_idx : (b0 + c);
           if (pub) {
             if (epi) stage_put((c - (int)crank) / p.splits, (tok < M && n < N) ? finish(tok, n, g, u) : 0.f);
-          } else if (tok < M && n < N) {
-            const float v = finish(tok, n, g, u);
-            if (p.ar_world > 1) {
-              push_partial(tok, n, v);
-            } else {
-              float r = v;
-              if (resid) r += Num<T>::to_f(resid[(size_t)tok * p.ldr + n]);
-              out[(size_t)tok * p.ldo + n] = Num<T>::from_f(r);
+          } else {
+            float fin = 0.f;                       // the value as stored (0 outside the matrix)
+            if (tok < M && n < N) {
+              const float v = finish(tok, n, g, u);
+              if (p.ar_world > 1) {
+                push_partial(tok, n, v);
+              } else {
+                float r = v;
+                if (resid) r += Num<T>::to_f(resid[(size_t)tok * p.ldr + n]);
+                const T rt = Num<T>::from_f(r);
+                out[(size_t)tok * p.ldo + n] = rt;
+                fin = Num<T>::to_f(rt);
+              }
             }
+            if (emit_ss) ss_add(c, fin);
           }
         }
+      }
+      if (emit_ss) {
+        // the columns this CTA finished (crank, crank + S, ...): one thread each adds the four warps' sums
+        __syncthreads();
+        for (int c = (int)crank + tid * p.splits; c < ncols; c += (int)blockDim.x * p.splits)
+          p.ss_out[(size_t)blockIdx.x * p.ss_ld + b0 + c] = ctl->ssw[0][c] + ctl->ssw[1][c] + ctl->ssw[2][c] + ctl->ssw[3][c];
       }
     }
   } else if (!aborted) {
@@ -587,11 +672,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int tok = b0 + c + j;
+          float fin = 0.f;
           if (tok < M && a_idx < N) {
             float r = v[j];
             if (resid) r += Num<T>::to_f(resid[(size_t)tok * p.ldr + a_idx]);
-            out[(size_t)tok * p.ldo + a_idx] = Num<T>::from_f(r);
+            const T rt = Num<T>::from_f(r);
+            out[(size_t)tok * p.ldo + a_idx] = rt;
+            fin = Num<T>::to_f(rt);
           }
+          if (emit_ss) ss_add(c + j, fin);
+        }
+        if (emit_ss && c + 16 >= bn) {
+          // last column group: one thread per token column adds the four warps' sums
+          __syncthreads();
+          for (int cc = tid; cc < ncols; cc += (int)blockDim.x)
+            p.ss_out[(size_t)blockIdx.x * p.ss_ld + b0 + cc] = ctl->ssw[0][cc] + ctl->ssw[1][cc] + ctl->ssw[2][cc] + ctl->ssw[3][cc];
         }
       } else {
         const int n0 = b0 + c;
@@ -911,7 +1006,10 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   const int tiles = pl->grid_x * pl->grid_y;
   const int a_tiles = (swap && dual) ? 2 : 1, b_tiles = (!swap && dual) ? 2 : 1;
   int stage_bytes = a_tiles * kATileBytes + b_tiles * pl->bn * kBK * 2;
-  if (g->w_int8) stage_bytes += (dual ? 2 : 1) * (swap ? kBM : pl->bn) * kBK;   // int8 staging tiles
+  if (g->w_int8) {   // staging tiles of the quantised weights
+    const int rows = swap ? kBM : pl->bn;
+    stage_bytes += round_up((dual ? 2 : 1) * (g->w_bits == 4 ? ceil_div(rows, kBM) * rf_w4_block_bytes(g->w_group) : rows * kBK), 1024);
+  }
   const int ctl_bytes = (int)sizeof(GemmSmemCtl) + 64;
   const bool publish = g->ar_world > 1 && g->ar_publish && swap;
   static const int env_smem_kb = [] { const char* e = getenv("RF_GEMM_SMEM_KB"); return e ? atoi(e) : 0; }();
@@ -1050,6 +1148,21 @@ static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream)
   p.ar_publish = (g->ar_world > 1 && g->ar_publish && SWAP) ? 1 : 0;
   p.ar_cnt_base = g->ar_cnt_base;
   p.ar_stage_off = pl.splits > 1 ? pl.bn * (DUAL ? 2 : 1) * kBM * 4 : 0;
+  p.ss_out = SWAP ? g->ss_out : nullptr;
+  p.ss_in = SWAP ? g->ss_in : nullptr;
+  p.ss_tiles = g->ss_tiles; p.ss_ld = g->ss_ld;
+  p.ss_inv_dim = g->ss_dim > 0 ? 1.f / (float)g->ss_dim : 0.f;
+  p.ss_eps = g->ss_eps;
+  p.w4 = (W8 && g->w_bits == 4) ? 1 : 0;
+  p.w4_ns = p.w4 && g->w_group > 0 ? kBK / std::min(g->w_group, kBK) : 0;
+  p.w4_fp4 = p.w4 && g->w_fp4 ? 1 : 0;
+  {
+    static const int ahead_env = [] { const char* e = getenv("RF_GEMM_PF_AHEAD"); return e ? atoi(e) : 0; }();
+    p.pf_ahead = (g->w_packed && SWAP && ahead_env > 0) ? pl.stages + ahead_env - 1 : 0;
+    static const int ef_env = [] { const char* e = getenv("RF_GEMM_W_EVICT_FIRST"); return e ? atoi(e) : 1; }();
+    p.w_evict_first = (g->w_packed && SWAP && g->M <= 256 && ef_env) ? 1 : 0;
+  }
+  p.q_blk_bytes = p.w4 ? rf_w4_block_bytes(g->w_group) : kBM * kBK;
   p.pf_ptr = nullptr; p.pf_chunks = 0;
   if (SWAP && g->prefetch && g->prefetch_bytes >= kPrefetchChunk && g->M <= 256 &&
       (reinterpret_cast<uintptr_t>(g->prefetch) & 15u) == 0) {
@@ -1069,7 +1182,22 @@ static int check_gemm(const RfGemm* g) {
   RF_REQUIRE(g->K % 8 == 0, "GEMM K=%d must be a multiple of 8 (16-byte rows)", g->K);
   RF_REQUIRE(g->ldx % 8 == 0 && (g->w_packed || g->ldw % (g->w_int8 ? 16 : 8) == 0), "GEMM row pitches must be multiples of 16 bytes");
   if (g->w_packed) RF_REQUIRE((reinterpret_cast<uintptr_t>(g->w) & 127) == 0, "packed weights must be 128-byte aligned");
-  if (g->w_int8) RF_REQUIRE(g->scale != nullptr && g->K % 16 == 0, "int8 weights need a scale vector and K %% 16 == 0");
+  if (g->ss_in || g->ss_out) {
+    RF_REQUIRE(g->M <= 256 && g->force_swap != 0, "folded RMSNorm (ss_in / ss_out) is for at most 256 tokens (got %d)", g->M);
+    RF_REQUIRE(g->ss_ld >= g->M, "ss_ld %d is smaller than the token count %d", g->ss_ld, g->M);
+    if (g->ss_in) RF_REQUIRE(g->ss_tiles > 0 && g->ss_dim > 0, "ss_in needs ss_tiles and ss_dim");
+    if (g->ss_out) RF_REQUIRE(g->ar_world <= 1, "ss_out is not available together with the fused all-reduce");
+  }
+  if (g->w_bits == 4) {
+    RF_REQUIRE(g->w_int8 && g->w_packed, "int4 weights come as the tile-major image (w_int8 = 1, w_packed = 1)");
+    RF_REQUIRE(g->w_group == 0 || g->w_group == 32 || g->w_group == 64 || g->w_group == 128 || (g->w_fp4 && g->w_group == 16),
+               "4-bit scale group must be 0 (per channel), 32, 64 or 128 (e2m1 codes also 16), got %d", g->w_group);
+    RF_REQUIRE(g->w_group > 0 || g->scale != nullptr, "per-channel int4 weights need a scale vector");
+    RF_REQUIRE(g->w_group == 0 || g->K % g->w_group == 0, "K=%d is not a multiple of the scale group %d", g->K, g->w_group);
+  } else {
+    RF_REQUIRE(g->w_bits == 0 || g->w_bits == 8 || g->w_bits == 16, "w_bits must be 0, 4, 8 or 16, got %d", g->w_bits);
+    if (g->w_int8) RF_REQUIRE(g->scale != nullptr && g->K % 16 == 0, "int8 weights need a scale vector and K %% 16 == 0");
+  }
   RF_REQUIRE(g->dtype == 0 || g->dtype == 1, "GEMM dtype must be fp16 or bf16");
   const bool dual_act = g->act == kActSiluMul || g->act == kActGeluTanhMul;
   RF_REQUIRE(dual_act == (g->dual_offset > 0), "dual_offset and a *_mul activation go together");
@@ -1142,7 +1270,7 @@ static int run_gemm(const RfGemm* g, cudaStream_t stream, bool w8) {
   if (rc) return rc;
   if (!w8 && g->force_splits == 0 && g->force_bn == 0 && rf::gemm_ps_eligible(g, pl.swap != 0, pl.splits))
     return rf::launch_gemm_ps(g, stream);
-  if (w8 && !pl.swap && g->M > 256 && g->w_packed && g->w_scratch && g->force_splits == 0 && g->force_bn == 0) {
+  if (w8 && g->w_bits != 4 && !pl.swap && g->M > 256 && g->w_packed && g->w_scratch && g->force_splits == 0 && g->force_bn == 0) {
     // Large token counts are compute-bound: widen the int8 weight image once into the caller's scratch (a pass
     // over the weights costs a few per cent of the GEMM) and run the 16-bit kernels, whose main loop has no
     // converter stage; the per-channel scale stays in the epilogue, so the result is (X . Q^T) * s as before.
@@ -1214,6 +1342,25 @@ extern "C" int rf_gemm(const RfGemm* g, rf_stream_t stream) {
 // GLU, cluster split-K, fused all-reduce).
 extern "C" int rf_gemm_w8a16(const RfGemm* g, rf_stream_t stream) {
   RF_SKIP_IF_REPLAYING();
-  RF_REQUIRE(g && g->w_int8 && g->scale, "rf_gemm_w8a16 takes int8 weights and a scale vector");
+  RF_REQUIRE(g && g->w_int8 && (g->scale || (g->w_bits == 4 && g->w_group > 0)),
+             "rf_gemm_w8a16 takes quantised weights and their scales");
   return run_gemm(g, static_cast<cudaStream_t>(stream), true);
+}
+
+// int4 weights in the tile-major image (nibbles + in-block group scales, or a per-channel scale vector): the same
+// main loop, whose converter warps widen the nibbles and apply the group scale on the way into the 16-bit tile.
+extern "C" int rf_gemm_w4a16(const RfGemm* g, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(g && g->w_int8 && g->w_bits == 4, "rf_gemm_w4a16 takes the int4 weight image (w_int8 = 1, w_bits = 4)");
+  return run_gemm(g, static_cast<cudaStream_t>(stream), true);
+}
+
+extern "C" int32_t rf_w4_block_bytes(int32_t group) {
+  return kBM * kBK / 2 + (group > 0 ? kBM * (kBK / std::min(group, kBK)) * 2 : 0);
+}
+
+extern "C" uint64_t rf_pack_w4_bytes(int64_t rows, int64_t K, int32_t sections, int32_t group) {
+  if (rows <= 0 || K <= 0 || sections <= 0 || rows % sections) return 0;
+  const int64_t tiles = ((rows / sections + kBM - 1) / kBM) * sections, kb = (K + kBK - 1) / kBK;
+  return (uint64_t)(tiles * kb) * (uint64_t)rf_w4_block_bytes(group);
 }

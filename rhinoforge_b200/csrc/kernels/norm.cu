@@ -72,7 +72,12 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ re
       for (int j = 0; j < 8; ++j) o[j] = srow[i + j] * rstd * (1.f + sc[j]) + sh[j];
     } else {
       float wf[8];
-      load8(w + i, wf);
+      if (w) {
+        load8(w + i, wf);
+      } else {   // no weight: plain x * rstd in either form
+#pragma unroll
+        for (int j = 0; j < 8; ++j) wf[j] = (mode & 1) ? 0.f : 1.f;
+      }
       if (mode & 1) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = srow[i + j] * rstd * (1.f + wf[j]);

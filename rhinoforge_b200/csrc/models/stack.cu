@@ -32,9 +32,10 @@ struct Stack {
   uint8_t* base = nullptr;
   uint64_t bytes = 0;
   uint64_t off_xn = 0, off_attn = 0, off_tmp = 0, off_wide = 0, off_conv = 0, off_head_xn = 0, off_logits = 0,
-           off_argmax = 0, off_attn_ws = 0, off_wscratch = 0, off_moe = 0, off_sk_ws = 0, off_sk_flags = 0,
+           off_argmax = 0, off_attn_ws = 0, off_wscratch = 0, off_moe = 0, off_sk_ws = 0, off_sk_flags = 0, off_ss = 0,
            off_status = 0, total = 0;
   uint64_t attn_ws_bytes = 0, argmax_bytes = 0, wscratch_bytes = 0, sk_ws_bytes = 0;
+  int ss_ld = 0, ss_tiles = 0;
   static constexpr int kSkFlags = 1024;
 
   int qkv_dim() const { return (cfg.Hq + 2 * cfg.Hkv) * cfg.hd + (cfg.attn_gate ? cfg.Hq * cfg.hd : 0); }
@@ -64,7 +65,7 @@ struct Stack {
     off_attn_ws = o; o += al(attn_ws_bytes);
     // W8A16 with prefill-sized token counts: room for the largest weight widened to 16 bits (tile-major image)
     wscratch_bytes = 0;
-    if (cfg.weights_int8 && cfg.weights_packed && cfg.max_tokens > 256) {
+    if (cfg.weights_int8 && cfg.weights_bits != 4 && cfg.weights_packed && cfg.max_tokens > 256) {
       auto img = [](uint64_t rows, uint64_t K, uint64_t sections) {
         return sections * ((rows + 127) / 128) * 128 * ((K + 63) / 64) * 64 * 2;
       };
@@ -85,6 +86,10 @@ struct Stack {
     }
     off_sk_ws = o; o += al(sk_ws_bytes);
     off_sk_flags = o; o += al(kSkFlags * sizeof(uint32_t));
+    // folded RMSNorm: two buffers (after attention, after the MLP) of per-(128-column tile, token) sums of squares
+    ss_ld = std::min(cfg.max_tokens, 256);
+    ss_tiles = (cfg.hidden + 127) / 128;
+    off_ss = o; o += al(cfg.norm_folded ? (uint64_t)2 * ss_tiles * ss_ld * sizeof(float) : 0);
     off_status = o; o += al(kStatusWords * sizeof(int32_t));
     total = o;
   }
@@ -133,11 +138,19 @@ static void hint_next_weights(const Stack& s, const void* w, const void* scale, 
                               int tokens) {
   t_pf_ptr = nullptr; t_pf_bytes = 0;
   if (!w || tokens > 256 || prefetch_cap_bytes() == 0) return;
-  const int eb = (s.cfg.weights_int8 && scale) ? 1 : 2;
-  const uint64_t bytes = s.cfg.weights_packed ? rf_pack_weight_bytes(rows, K, sections, eb) : (uint64_t)rows * K * eb;
+  const bool quantised = s.cfg.weights_int8 && scale;
+  const int eb = quantised ? 1 : 2;
+  const uint64_t bytes = (quantised && s.cfg.weights_bits == 4) ? rf_pack_w4_bytes(rows, K, sections, s.cfg.weights_group)
+                         : s.cfg.weights_packed            ? rf_pack_weight_bytes(rows, K, sections, eb)
+                                                           : (uint64_t)rows * K * eb;
   t_pf_ptr = w;
   t_pf_bytes = bytes < prefetch_cap_bytes() ? bytes : prefetch_cap_bytes();
 }
+
+// Folded RMSNorm wiring of the next linear() call on this thread (set by the layer loop right before the call, consumed
+// by it): the buffer it writes its per-tile sums of squares to, and / or the buffer whose sums give its row scale.
+static thread_local float* t_ss_out = nullptr;
+static thread_local const float* t_ss_in = nullptr;
 
 // One linear layer: picks GEMV / tcgen05 GEMM / W8A16 and wires the fused all-reduce.  pub_ctas != null asks for
 // the publish-and-exit form: *pub_ctas receives the CTA count the consumer must wait for, or 0 when the shape took
@@ -152,6 +165,10 @@ static int linear(const Stack& s, const void* x, int64_t ldx, const void* w, con
   g.M = M; g.N = N; g.K = K; g.dtype = s.cfg.dtype; g.act = act; g.dual_offset = dual_offset;
   g.w_int8 = s.cfg.weights_int8 && scale != nullptr;
   g.w_packed = s.cfg.weights_packed;
+  if (g.w_int8 && s.cfg.weights_bits == 4) {
+    g.w_bits = 4; g.w_group = s.cfg.weights_group;
+    if (g.w_group > 0) g.scale = nullptr;      // the group scales are part of the weight image
+  }
   if (g.w_int8 && s.wscratch_bytes) {
     g.w_scratch = s.at(s.off_wscratch);
     g.w_scratch_bytes = s.wscratch_bytes;
@@ -160,6 +177,11 @@ static int linear(const Stack& s, const void* x, int64_t ldx, const void* w, con
   g.force_swap = -1;
   g.prefetch = t_pf_ptr; g.prefetch_bytes = t_pf_bytes;
   t_pf_ptr = nullptr; t_pf_bytes = 0;
+  if (t_ss_out || t_ss_in) {
+    g.ss_out = t_ss_out; g.ss_in = t_ss_in;
+    g.ss_ld = s.ss_ld; g.ss_tiles = s.ss_tiles; g.ss_dim = s.cfg.hidden; g.ss_eps = s.cfg.eps;
+    t_ss_out = nullptr; t_ss_in = nullptr;
+  }
   g.ws = s.at<float>(s.off_sk_ws); g.ws_bytes = s.sk_ws_bytes;
   g.sem = s.at<uint32_t>(s.off_sk_flags); g.sem_count = Stack::kSkFlags;
   const bool ar = all_reduce && s.cfg.tp_world > 1;
@@ -287,17 +309,29 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
   // A plain RMSNorm that follows an all-reduce can ride in the all-reduce's consumer (linear_ar)
   const bool norm_rides = !side && (c.norm_kind == RF_NORM_RMS || c.norm_kind == RF_NORM_RMS_GEMMA);
   bool have_xn = false;     // xn already holds this layer's first norm (written by the previous layer's consumer)
+  // Norm weights folded into wqkv / w_up: the norm kernels (when they run) take no weight; with at most 256 tokens
+  // they do not run at all between a residual GEMM and the next projection (sums of squares out, row scale in).
+  const bool folded = c.norm_folded != 0;
+  if (folded)
+    RF_REQUIRE(norm_rides && c.tp_world == 1 && c.moe_experts == 0 && c.gdn_Hv == 0,
+               "norm_folded needs a plain RMSNorm dense decoder on one GPU");
+  const bool fuse_ss = folded && T <= 256;
+  float* ss_attn = s.at<float>(s.off_ss);                               // sums of squares of hidden after attention
+  float* ss_mlp = ss_attn + (size_t)s.ss_tiles * s.ss_ld;               // ... after the MLP (the next layer's input)
+  bool ss_ready = false;    // ss_mlp describes f.hidden as it is now
 
   for (int l = lb; l < le; ++l) {
     const RfLayerWeights& w = s.layers[l];
     const uint8_t* mod1 = f.mod ? (const uint8_t*)f.mod + ((size_t)(l * 2 + 0) * nmods) * 3 * H * esz : nullptr;
     const uint8_t* mod2 = f.mod ? (const uint8_t*)f.mod + ((size_t)(l * 2 + 1) * nmods) * 3 * H * esz : nullptr;
     // ---- token mixer: softmax attention or Gated-DeltaNet
-    if (!have_xn) {
-      rc = norm(s, f.hidden, w.norm1_w, w.norm1_b, xn, T, mod1, f.rows_per_mod, st);
+    const bool qkv_from_hidden = fuse_ss && ss_ready;     // this layer's first norm is the QKV GEMM's row scale
+    if (!have_xn && !qkv_from_hidden) {
+      rc = norm(s, f.hidden, folded ? nullptr : w.norm1_w, w.norm1_b, xn, T, mod1, f.rows_per_mod, st);
       if (rc) return rc;
     }
     have_xn = false;
+    ss_ready = false;
     bool have_xn2 = false;  // xn holds the second norm (written by the attention all-reduce's consumer)
     const void* mix_out = attn;      // input of the output projection
     int mix_dim = AD;
@@ -330,7 +364,9 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
       mix_dim = VD;
     } else {
     hint_next_weights(s, w.wo, w.so, H, AD, 1, T);
-    rc = linear(s, xn, H, w.wqkv, w.sqkv, w.bqkv, wide, QD, nullptr, 0, T, QD, H, kActNone, 0, false, st);
+    if (qkv_from_hidden) t_ss_in = ss_mlp;
+    rc = linear(s, qkv_from_hidden ? f.hidden : xn, H, w.wqkv, w.sqkv, w.bqkv, wide, QD, nullptr, 0, T, QD, H, kActNone, 0,
+                false, st);
     if (rc) return rc;
     {
       RfRopeKv a = {};
@@ -398,6 +434,7 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
                            c.tp_world == 1 && f.mod != nullptr;
     hint_next_weights(s, w.w_up, w.s_up, s.glu() ? 2 * (int64_t)I : I, H, s.glu() ? 2 : 1, T);
     if (!side) {
+      if (fuse_ss) t_ss_out = ss_attn;
       rc = linear_ar(s, mix_out, mix_dim, w.wo, w.so, w.bo, f.hidden, f.hidden, T, mix_dim,
                      norm_rides ? w.norm2_w : nullptr, xn, &have_xn2, st);
       if (rc) return rc;
@@ -418,8 +455,8 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
       if (rc) return rc;
     }
     // ---- MLP block
-    if (!have_xn2) {
-      rc = norm(s, f.hidden, w.norm2_w, w.norm2_b, xn, T, mod2, f.rows_per_mod, st);
+    if (!have_xn2 && !fuse_ss) {
+      rc = norm(s, f.hidden, folded ? nullptr : w.norm2_w, w.norm2_b, xn, T, mod2, f.rows_per_mod, st);
       if (rc) return rc;
     }
     const bool moe = c.moe_experts > 0 && w.moe_router_w != nullptr;
@@ -441,7 +478,8 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
       if (rc) return rc;
     }
     hint_next_weights(s, w.w_down, w.s_down, H, I, 1, T);
-    rc = linear(s, xn, H, w.w_up, w.s_up, w.b_up, wide, I, nullptr, 0, T, I, H, act_of(c.mlp_kind),
+    if (fuse_ss) t_ss_in = ss_attn;
+    rc = linear(s, fuse_ss ? f.hidden : xn, H, w.w_up, w.s_up, w.b_up, wide, I, nullptr, 0, T, I, H, act_of(c.mlp_kind),
                 s.glu() ? I : 0, false, st);
     if (rc) return rc;
     if (moe) {
@@ -452,6 +490,10 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     const bool hook_after = (f.deepstack && l < f.n_deepstack && f.deepstack[l]);
     const void* next_w = (norm_rides && l + 1 < le && !hook_after) ? s.layers[l + 1].norm1_w : nullptr;
     if (l + 1 < le && s.layers[l + 1].mixer != 1) hint_next_weights(s, s.layers[l + 1].wqkv, s.layers[l + 1].sqkv, QD, H, 1, T);
+    if (fuse_ss && l + 1 < le && !hook_after) {
+      t_ss_out = ss_mlp;
+      ss_ready = true;
+    }
     if (!side) {
       rc = linear_ar(s, wide, I, w.w_down, w.s_down, w.b_down, f.hidden, f.hidden, T, I, next_w, xn, &have_xn, st);
       if (rc) return rc;

@@ -54,6 +54,16 @@ typedef struct RfStackConfig {
   int32_t moe_score_fn;         // 0 sigmoid (+ selection-only bias), 1 softmax
   int32_t moe_norm_topk;        // picked weights are normalised to sum 1 before the routed scale
   float moe_routed_scale;
+  // weights_int8 with weights_bits == 4: every quantised linear weight is the tile-major int4 image of RfGemm.w_bits
+  // (weights_group = 0: the layer's s* pointers are per-channel scale vectors; 32 / 64 / 128: the scales sit inside
+  // the image and a non-null s* pointer only marks the weight as quantised)
+  int32_t weights_bits, weights_group;
+  // 1: the norm weights of the two pre-norms are already multiplied into the columns of wqkv and w_up (plain RMSNorm or
+  // the (1 + w) form, one GPU, dense MLP).  The stack then treats norm1_w / norm2_w as all-ones: with at most 256
+  // tokens the residual GEMMs (o_proj, down_proj) emit per-token sums of squares and the next projection scales its
+  // result by the reciprocal RMS, so no RMSNorm kernel runs between them; with more tokens a weight-free RMSNorm runs.
+  int32_t norm_folded;
+  int32_t reserved0;
 } RfStackConfig;
 
 typedef struct RfLayerWeights {

@@ -73,9 +73,35 @@ typedef struct RfGemm {
   // kernel's epilogue, the launch gap and the next kernel's prologue.  Never dereferenced; 16-byte aligned.
   const void* prefetch;
   uint64_t prefetch_bytes;
+  // 4: `w` is the tile-major int4 image made by rf_pack_w4 / ops.kernels.pack_weight_int4 (w_int8 = 1, w_packed = 1):
+  // block (row tile, k block) = 128 rows x 64 columns as 4096 bytes of nibbles (two's complement; inside each group of
+  // eight columns the nibbles sit in the order 0,2,4,6,1,3,5,7) followed by the block's scales in the activation dtype,
+  // 128 x (64 / min(w_group, 64)) of them.  w_group = 0: no scales in the image, `scale` holds one per output channel.
+  int32_t w_bits;
+  int32_t w_group;     // 0, 16 (fp4 only), 32, 64 or 128 columns per scale
+  // 0: the nibbles are two's-complement integers (W4A16); 1: e2m1 floating-point codes (bit 3 sign, bits 0..2 index into
+  // {0, 0.5, 1, 1.5, 2, 3, 4, 6}) as in NVFP4, whose e4m3 block scale times the tensor scale is stored per 16 columns
+  // in the image, already multiplied out in the activation dtype.
+  int32_t w_fp4;
+  // RMSNorm folded around the GEMMs (at most 256 tokens, weights streamed with tokens on the MMA N axis):
+  //  * ss_out: this GEMM also writes, for every token and every 128-wide tile of its output columns, the sum of
+  //    squares of the finished (residual added, rounded) values: ss_out[tile * ss_ld + token], fp32.  Plain stores in
+  //    a fixed layout, so the later sum has a fixed order.
+  //  * ss_in: the input rows are un-normalised; the result is scaled per token by
+  //    rsqrt(sum_{t < ss_tiles} ss_in[t * ss_ld + token] / ss_dim + ss_eps), which together with norm weights
+  //    multiplied into the weight columns beforehand is the RMSNorm that would otherwise run as its own kernel.
+  int32_t ss_tiles;
+  float* ss_out;
+  const float* ss_in;
+  int32_t ss_ld, ss_dim;
+  float ss_eps;
+  int32_t reserved0;
 } RfGemm;
 // bytes of the tile-major image of a [rows, K] weight with `sections` equal row sections
 uint64_t rf_pack_weight_bytes(int64_t rows, int64_t K, int32_t sections, int32_t elem_bytes);
+// bytes of the tile-major int4 image (see RfGemm.w_bits) and of one of its blocks
+uint64_t rf_pack_w4_bytes(int64_t rows, int64_t K, int32_t sections, int32_t group);
+int32_t rf_w4_block_bytes(int32_t group);
 
 int rf_gemm(const RfGemm* g, rf_stream_t stream);
 // Launch plan of a shape without launching: out[10] = {swap, bn, splits, stages, grid_x, grid_y, smem bytes, k_blocks,
@@ -86,6 +112,9 @@ int rf_gemm_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* sem_count);
 // Same contract with int8 weights [N,K] and a per-output-channel scale (W8A16):
 // the int8 tile is widened to the activation dtype inside the mainloop.
 int rf_gemm_w8a16(const RfGemm* g, rf_stream_t stream);
+// int4 weights (w_bits = 4) with per-channel or group-wise scales: nibbles are widened, and group scales applied, by the
+// converter warps of the same main loop.
+int rf_gemm_w4a16(const RfGemm* g, rf_stream_t stream);
 // CUDA-core skinny GEMM (M <= 8): reference path and small-batch decode.
 int rf_gemv(const RfGemm* g, rf_stream_t stream);
 // CTAs of the launch rf_gemm / rf_gemm_w8a16 would make for this shape (each bumps the arrival counters once when

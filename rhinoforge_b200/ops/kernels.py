@@ -82,7 +82,9 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          ws: Optional[torch.Tensor] = None, sem: Optional[torch.Tensor] = None,
          comm=None, packed_shape: Optional[tuple] = None, w_scratch: Optional[torch.Tensor] = None,
          publish: bool = False, norm_w: Optional[torch.Tensor] = None, norm_out: Optional[torch.Tensor] = None,
-         norm_eps: float = 1e-6, norm_gemma: bool = False) -> torch.Tensor:
+         norm_eps: float = 1e-6, norm_gemma: bool = False, w_bits: int = 0, w_group: int = 0,
+         w_fp4: bool = False, ss_out: Optional[torch.Tensor] = None, ss_in: Optional[torch.Tensor] = None,
+         ss_dim: int = 0, ss_eps: float = 1e-6) -> torch.Tensor:
     """``out = epilogue(x @ w.T)`` on the tcgen05 kernel (or the CUDA-core GEMV).
 
     ``dual=True``: ``w`` stacks ``[gate; up]`` (2N rows) and ``act`` is a ``*_mul``
@@ -94,6 +96,13 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     ``publish`` (with ``comm``, at most 256 rows): the GEMM only pushes its partial rows to the peers and exits;
     ``rf_ar_consume`` then waits, reduces, adds ``residual`` and, with ``norm_w`` / ``norm_out``, writes the RMSNorm of
     the finished rows (``norm_gemma``: ``(1 + w)`` weights).
+    ``w_bits=4``: ``w`` is the int4 image made by :func:`pack_weight_int4` (``packed_shape`` required); ``w_group`` is
+    its scale group (0: per-channel ``scale`` vector, else 32 / 64 / 128 with the scales inside the image).
+    ``w_fp4``: the nibbles are e2m1 codes (:func:`pack_weight_nvfp4`, scale group 16).
+    ``ss_out`` (fp32 ``[ceil(N / 128), ld >= M]``, at most 256 rows): also receives the sum of squares of the finished
+    output values per 128-column tile and token.  ``ss_in`` (the ``ss_out`` of the GEMM that produced ``x``): the result
+    is scaled per token by ``rsqrt(sum(ss_in[:, token]) / ss_dim + ss_eps)``: an RMSNorm of ``x`` whose weights were
+    multiplied into the columns of ``w`` beforehand.
     """
     M, K = x.shape
     if packed_shape is not None:          # ``w`` is the tile-major image made by pack_weight(); (rows, K) is its logical shape
@@ -118,8 +127,21 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     g.dtype = dtype_code(x.dtype)
     g.act = ACT[act]
     g.dual_offset = Nn if dual else 0
-    g.w_int8 = 1 if w.dtype == torch.int8 else 0
+    g.w_int8 = 1 if (w.dtype == torch.int8 or w_bits == 4) else 0
+    if w_bits == 4:
+        if packed_shape is None or w.dtype != torch.uint8:
+            raise ValueError("w_bits=4 takes the uint8 image made by pack_weight_int4 together with packed_shape")
+        g.w_bits, g.w_group, g.w_fp4 = 4, w_group, int(w_fp4)
     g.status = _ptr(status)
+    for t in (ss_out, ss_in):
+        if t is not None:
+            assert t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1 and t.is_cuda
+            g.ss_ld = t.stride(0)
+    if ss_out is not None:
+        assert ss_out.shape[0] >= (Nn + 127) // 128
+        g.ss_out = ss_out.data_ptr()
+    if ss_in is not None:
+        g.ss_in, g.ss_tiles, g.ss_dim, g.ss_eps = ss_in.data_ptr(), ss_in.shape[0], ss_dim or K, ss_eps
     g.force_splits, g.force_swap, g.force_bn = force_splits, force_swap, force_bn
     if w_scratch is not None:
         g.w_scratch, g.w_scratch_bytes = w_scratch.data_ptr(), w_scratch.numel() * w_scratch.element_size()
@@ -145,7 +167,9 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
             ws, sem = _splitk_scratch(x.device, need_ws.value, need_sem.value)
         g.ws, g.ws_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
         g.sem, g.sem_count = sem.data_ptr(), sem.numel()
-    if w.dtype == torch.int8:
+    if w_bits == 4:
+        N.check(lib.rf_gemm_w4a16(C.byref(g), _stream()), "rf_gemm_w4a16")
+    elif w.dtype == torch.int8:
         N.check(lib.rf_gemm_w8a16(C.byref(g), _stream()), "rf_gemm_w8a16")
     else:
         N.check(lib.rf_gemm(C.byref(g), _stream()), "rf_gemm")
@@ -177,6 +201,53 @@ def pack_weight(w: torch.Tensor, sections: int = 1) -> torch.Tensor:
         src = (c ^ (r % 8)).view(1, 1, 128, 8, 1).expand_as(blk)                        # position p holds chunk p ^ (r%8)
         out = torch.gather(blk, 3, src).contiguous()
     return out.view(-1)
+
+
+_W4_NIBBLE_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)       # nibble j of a 32-bit word holds this column of its group of eight
+
+
+def pack_weight_int4(q: torch.Tensor, scales: Optional[torch.Tensor] = None, group: int = 0, *, sections: int = 1,
+                     dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """Tile-major int4 image of ``q`` (``[rows, K]`` int8 values in ``[-8, 7]``) for ``gemm(..., w_bits=4)``.
+
+    Blocks of 128 rows x 64 columns are contiguous, ordered ``[row tile][k block]``.  A block is 4096 bytes of nibbles
+    (row-major, two's complement; inside every group of eight columns the nibbles are stored in the order
+    0, 2, 4, 6, 1, 3, 5, 7, so that one shift-and-mask yields pairs of neighbouring columns) followed, for
+    ``group`` in (32, 64, 128), by the block's ``128 x (64 / min(group, 64))`` scales in ``dtype`` taken from
+    ``scales [rows, K / group]``.  ``group=0``: no scales in the image (one scale per output channel goes to the GEMM's
+    ``scale`` argument).  Padding rows / columns are zero nibbles with scale 0."""
+    rows, Kd = q.shape
+    assert rows % sections == 0 and group in (0, 16, 32, 64, 128) and (group == 0 or Kd % group == 0)
+    per = rows // sections
+    rt, kb = (per + 127) // 128, (Kd + 63) // 64
+    dev = q.device
+    full = torch.zeros((sections, rt * 128, kb * 64), dtype=torch.int16, device=dev)
+    full[:, :per, :Kd] = (q.view(sections, per, Kd).to(torch.int16) & 0xF)
+    blk = full.view(sections * rt, 128, kb, 8, 8).permute(0, 2, 1, 3, 4)                   # [tile, kb, 128, 8 groups, 8]
+    blk = blk[..., list(_W4_NIBBLE_ORDER)]                                                # storage order of the nibbles
+    byts = (blk[..., 0::2] | (blk[..., 1::2] << 4)).to(torch.uint8).reshape(sections * rt, kb, 128 * 32)
+    if group == 0:
+        return byts.reshape(-1).contiguous()
+    assert scales is not None and tuple(scales.shape) == (rows, Kd // group)
+    ge = min(group, 64)
+    ns = 64 // ge
+    sc = torch.zeros((sections, rt * 128, kb * ns), dtype=dtype, device=dev)
+    col = (torch.arange(kb * ns, device=dev) * ge) // group                               # scale column of every (kb, sub-group)
+    valid = col < Kd // group
+    sc[:, :per, valid] = scales.to(dev, dtype).view(sections, per, -1)[:, :, col[valid]]
+    sc = sc.view(sections * rt, 128, kb, ns).permute(0, 2, 1, 3).contiguous().view(sections * rt, kb, 128 * ns)
+    img = torch.cat((byts, sc.view(torch.uint8).view(sections * rt, kb, -1)), -1)
+    return img.reshape(-1).contiguous()
+
+
+def pack_weight_nvfp4(codes: torch.Tensor, scale_codes_gn: torch.Tensor, tensor_scale, *, sections: int = 1,
+                      dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """Tile-major image of an NVFP4 weight for ``gemm(..., w_bits=4, w_group=16, w_fp4=True)``: ``codes [rows, K]`` e2m1
+    codes, ``scale_codes_gn [K / 16, rows]`` e4m3 block scales (as bytes) and the fp32 tensor scale, as
+    ``quant.nvfp4_pack.quantize_nvfp4`` returns them.  The two scale levels are multiplied out into one ``dtype`` scale
+    per 16 columns, stored inside the image like the int4 group scales."""
+    eff = scale_codes_gn.t().contiguous().view(torch.float8_e4m3fn).float() * float(tensor_scale)
+    return pack_weight_int4(codes, eff, 16, sections=sections, dtype=dtype)
 
 
 def rmsnorm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, *, residual: Optional[torch.Tensor] = None,

@@ -74,7 +74,7 @@ class DecoderEngine:
     def __init__(self, cfg: DecoderConfig, get_weight: WeightGetter, *, device="cuda", dtype=torch.float16,
                  max_batch: int = 1, max_seq_len: int = 2048, max_prefill_tokens: int = 8192,
                  tp: Optional[TPContext] = None, quant: Optional[str] = None, decode_gemv_max_m: int = 0,
-                 hist_steps: int = 4096, kv_cache=None, kv_pool_tokens: Optional[int] = None):
+                 hist_steps: int = 4096, kv_cache=None, kv_pool_tokens: Optional[int] = None, w4_group: int = 64):
         if not torch.cuda.is_available():
             raise RPUBackendError("DecoderEngine needs a CUDA device")
         self.cfg, self.dtype = cfg, dtype
@@ -84,8 +84,11 @@ class DecoderEngine:
         self.max_batch = max_batch
         self.max_tokens = max(max_prefill_tokens, max_batch)
         self.quant = quant
-        if quant not in (None, "w8a16"):
+        if quant not in (None, "w8a16", "w4a16"):
             raise RPUBackendError(f"unknown quantisation {quant!r}")
+        if w4_group not in (0, 32, 64, 128):
+            raise RPUBackendError(f"w4_group must be 0 (per channel), 32, 64 or 128, got {w4_group}")
+        self.w4_group = w4_group
         H, hd = cfg.hidden_size, cfg.head_dim
         if cfg.num_heads % W or cfg.intermediate_size % W or cfg.vocab_size % W:
             raise RPUBackendError(f"{cfg.name}: heads/intermediate/vocab do not split over {W} ranks")
@@ -104,12 +107,22 @@ class DecoderEngine:
         sc.max_tokens, sc.max_seqs = self.max_tokens, max_batch
         sc.vocab_local, sc.vocab_offset = self.vocab_local, R * self.vocab_local
         sc.tp_world, sc.tp_rank = W, R
-        sc.weights_int8 = 1 if quant == "w8a16" else 0
+        sc.weights_int8 = 1 if quant in ("w8a16", "w4a16") else 0
+        if quant == "w4a16":
+            sc.weights_bits, sc.weights_group = 4, w4_group
         sc.decode_gemv_max_m = decode_gemv_max_m
         sc.attn_gate = int(cfg.attn_gate)
         # linear weights live in the tile-major layout (contiguous 16 KB blocks): see ops.kernels.pack_weight
         self.packed = os.environ.get("RF_PACKED_WEIGHTS", "1") != "0" and decode_gemv_max_m == 0
         sc.weights_packed = int(self.packed)
+        # Pre-norm weights multiplied into the columns of the projections that follow them (q/k/v, gate/up): the
+        # RMSNorm between a residual GEMM and the next projection then needs no kernel of its own at decode sizes
+        # (the residual GEMM emits sums of squares, the projection scales its rows).  One GPU, dense decoders, 16-bit
+        # weights (quantised engines keep the checkpoint's exact integer weights).
+        self.fold_norm = (W == 1 and cfg.norm in ("rms", "rms_gemma") and not any(cfg.is_linear(l) for l in range(cfg.num_layers))
+                          and quant is None and getattr(get_weight, "scale", None) is None and self.packed
+                          and os.environ.get("RF_FOLD_NORM", "1") != "0")
+        sc.norm_folded = int(self.fold_norm)
         # hybrid decoders: which layers own KV pages, and the local Gated-DeltaNet geometry
         self.attn_layers = [l for l in range(cfg.num_layers) if not cfg.is_linear(l)]
         self.kv_index = {l: i for i, l in enumerate(self.attn_layers)}
@@ -210,11 +223,70 @@ class DecoderEngine:
         self._keep.append(p)
         return p
 
-    def _lin(self, get: WeightGetter, parts, cols=None, sections: int = 1):
+    def _lin_w4(self, get: WeightGetter, parts, cols, sections: int):
+        """One int4 linear: packed checkpoint tensors (``uint8 [out, in/2]`` + group or channel scales) are unpacked, sliced
+        and re-packed into the tile-major image; 16-bit tensors are quantised here with this engine's group size."""
+        from ..quant.int4_pack import unpack_int4
+        scale_of = getattr(get, "scale", None)
+        G = self.w4_group
+        qs, ss = [], []
+        for name, rows in parts:
+            if name is None:
+                raise RPUBackendError("int4 weights do not take alignment padding rows")
+            w = get(name)
+            if w.dtype == torch.uint8:
+                sc = scale_of(name) if scale_of is not None else None
+                if sc is None:
+                    raise RPUBackendError(f"packed int4 weight {name!r} has no weight_scale")
+                q = unpack_int4(w)
+                Kd = q.shape[1]
+                sc = sc.reshape(q.shape[0], -1).float()
+                g_ck = Kd // sc.shape[1] if sc.shape[1] > 1 else 0
+                if g_ck != G:
+                    raise RPUBackendError(f"{name!r} was quantised with scale group {g_ck or 'per-channel'}, the engine was "
+                                          f"built for {G or 'per-channel'}")
+            else:
+                wf = w.to(self.device).float()
+                Kd = wf.shape[1]
+                grp = wf.view(wf.shape[0], Kd // G, G) if G else wf.view(wf.shape[0], 1, Kd)
+                sc = (grp.abs().amax(-1) / 7.0).clamp_min(1e-8)
+                q = torch.round(grp / sc[..., None]).clamp_(-8, 7).to(torch.int8).view(wf.shape[0], Kd)
+            q, sc = q[rows], sc[rows]
+            if cols is not None:
+                q = q[:, cols]
+                if G:
+                    c0, c1, _ = cols.indices(Kd)
+                    if c0 % G or c1 % G:
+                        raise RPUBackendError(f"{name!r}: the tensor-parallel shard [{c0}, {c1}) cuts a scale group of {G}")
+                    sc = sc[:, c0 // G:c1 // G]
+            qs.append(q.to(self.device))
+            ss.append(sc.to(self.device))
+        q = qs[0] if len(qs) == 1 else torch.cat(qs, 0)
+        sc = ss[0] if len(ss) == 1 else torch.cat(ss, 0)
+        if G:
+            img = K.pack_weight_int4(q, sc, G, sections=sections, dtype=self.dtype)
+            self._keep.append(img)
+            return img, img                       # the second pointer only marks the weight as quantised
+        img = K.pack_weight_int4(q, sections=sections)
+        self._keep.append(img)
+        return img, self._dev(sc.reshape(-1).to(self.dtype))
+
+    def _lin(self, get: WeightGetter, parts, cols=None, sections: int = 1, w4: bool = True, col_scale=None):
         """One packed linear: ``parts`` is a list of (tensor name, row slice); the pieces are
         concatenated along the output dim, ``cols`` slices the input dim (row-parallel shards).
         Returns (device weight, device per-channel scale or None).  int8 checkpoints keep their
         stored scales; 16-bit weights are quantised here when the engine runs W8A16."""
+        if col_scale is not None:
+            # fold a per-input-column factor (a pre-norm's weights) into the matrix before it is packed or quantised
+            inner, cs = get, col_scale.to(self.device, torch.float32)
+
+            def get(name, _g=inner):
+                t = _g(name)
+                if not t.is_floating_point():
+                    raise RPUBackendError(f"{name!r} is already quantised: the norm weights cannot be folded into it")
+                return (t.to(self.device).float() * cs).to(t.dtype)
+        if self.quant == "w4a16" and w4:
+            return self._lin_w4(get, parts, cols, sections)
         scale_of = getattr(get, "scale", None)
         ws, ss = [], []
         for name, rows in parts:
@@ -234,7 +306,7 @@ class DecoderEngine:
         if w.dtype == torch.int8:
             if any(x is None for x in ss):
                 raise RPUBackendError(f"int8 weight {parts[0][0]!r} has no weight_scale")
-            if self.quant != "w8a16":
+            if self.quant not in ("w8a16", "w4a16"):
                 raise RPUBackendError("int8 weights need quant='w8a16'")
             sc = ss[0] if len(ss) == 1 else torch.cat(ss, 0)
             sc_d = self._dev(sc.to(self.dtype))
@@ -262,6 +334,12 @@ class DecoderEngine:
                 bq, bk, bv = (get(p + f"self_attn.{n}_proj.bias") for n in "qkv")
                 bqkv = self._dev(torch.cat((bq[qs], bk[ks], bv[ks]), 0))
             lw = N.RfLayerWeights()
+
+            def norm_cols(name, _p=p):
+                if not self.fold_norm:
+                    return None
+                w = get(_p + name).float()
+                return 1.0 + w if cfg.norm == "rms_gemma" else w
             if cfg.is_linear(l):
                 t_qkv, s_qkv, t_o, s_o = self._pack_gdn(get, l, lw)
             else:
@@ -274,9 +352,10 @@ class DecoderEngine:
                 else:
                     parts = [(p + "self_attn.q_proj.weight", qs), (p + "self_attn.k_proj.weight", ks),
                              (p + "self_attn.v_proj.weight", ks)]
-                t_qkv, s_qkv = self._lin(get, parts)
+                t_qkv, s_qkv = self._lin(get, parts, col_scale=norm_cols("input_layernorm.weight"))
                 t_o, s_o = self._lin(get, [(p + "self_attn.o_proj.weight", full)], cols=qs)
-            t_gu, s_gu = self._lin(get, [(p + "mlp.gate_proj.weight", isl), (p + "mlp.up_proj.weight", isl)], sections=2)
+            t_gu, s_gu = self._lin(get, [(p + "mlp.gate_proj.weight", isl), (p + "mlp.up_proj.weight", isl)], sections=2,
+                                   col_scale=norm_cols("post_attention_layernorm.weight"))
             t_d, s_d = self._lin(get, [(p + "mlp.down_proj.weight", full)], cols=isl)
             lw.wqkv, lw.sqkv, lw.bqkv = ptr(t_qkv), ptr(s_qkv), ptr(bqkv)
             lw.wo, lw.so = ptr(t_o), ptr(s_o)
@@ -301,7 +380,7 @@ class DecoderEngine:
         names = getattr(get, "names", None)
         has_head = (names is None and not cfg.tie_embeddings) or (names is not None and "lm_head.weight" in names)
         head_name = "lm_head.weight" if has_head else "model.embed_tokens.weight"
-        t_lm, s_lm = self._lin(get, [(head_name, slice(v0, v1))])
+        t_lm, s_lm = self._lin(get, [(head_name, slice(v0, v1))], w4=False)     # the head stays 16-bit under W4A16
         self.final_norm = self._dev(get("model.norm.weight"))
         N.check(lib.rf_stack_set_head(self.handle, C.c_void_p(self.final_norm.data_ptr()), None,
                                       C.c_void_p(t_lm.data_ptr()), C.c_void_p(ptr(s_lm))), "rf_stack_set_head")

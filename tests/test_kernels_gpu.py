@@ -638,3 +638,141 @@ def _stream_k_case(dt, M, N, K, dual, status):
     _close_elementwise(y, ref, dt)
     assert torch.equal(y, y2), "two launches of the same GEMM must agree bit for bit"
     assert plan is None or plan["persistent"] in (0, 2)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M,N,K,group,dual", [(1, 1024, 4096, 64, False), (16, 1000, 1024, 32, False), (64, 384, 2048, 128, False),
+                                              (64, 2048, 1024, 0, False), (33, 1280, 512, 64, True), (200, 640, 2560, 32, False),
+                                              (300, 512, 1024, 64, False), (300, 768, 512, 128, True), (8, 256, 192, 64, False)])
+def test_gemm_w4a16(dt, M, N, K, group, dual, status):
+    """int4 weights in the tile-major image: nibbles widened and group scales applied by the converter warps of the
+    main loop (per-channel scales in the epilogue when group = 0); reference = x @ dequantised weights in fp32."""
+    from rhinoforge_b200.ops import kernels as K_
+    torch.manual_seed(N + K + group)
+    rows = 2 * N if dual else N
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    q = torch.randint(-8, 8, (rows, K), device="cuda", dtype=torch.int8)
+    r = torch.randn(M, N, device="cuda").to(dt)
+    kw = dict(packed_shape=(rows, K), w_bits=4, w_group=group, status=status)
+    if group:
+        sc = (torch.rand(rows, K // group, device="cuda") * 0.03 + 0.005).to(dt)
+        img = K_.pack_weight_int4(q, sc, group, sections=2 if dual else 1, dtype=dt)
+        wd = q.float().view(rows, K // group, group) * sc.float()[..., None]
+        wd = wd.view(rows, K)
+    else:
+        sc = (torch.rand(rows, device="cuda") * 0.03 + 0.005).to(dt)
+        img = K_.pack_weight_int4(q, sections=2 if dual else 1)
+        kw["scale"] = sc
+        wd = q.float() * sc.float()[:, None]
+    assert img.numel() == K_.N.lib().rf_pack_w4_bytes(rows, K, 2 if dual else 1, group)
+    z = x.float() @ wd.t()
+    if dual:
+        y = K_.gemm(x, img, act="silu_mul", dual=True, **kw)
+        ref = torch.nn.functional.silu(z[:, :N]) * z[:, N:]
+    else:
+        y = K_.gemm(x, img, residual=r, **kw)
+        ref = z + r.float()
+    _close(y, ref, dt, scale=max(1.0, ref.abs().max().item()) * (4 if dt == torch.bfloat16 else 1))
+
+
+@pytest.mark.parametrize("group,from_packed", [(64, False), (32, True), (0, False)])
+def test_engine_w4a16_matches_dequantised_oracle(group, from_packed):
+    """Whole decoder with int4 projections (lm_head 16-bit): prefill logits follow the oracle run on the dequantised
+    weights, whether the engine quantises 16-bit weights itself or reads a packed 4-bit checkpoint."""
+    from rhinoforge_b200.models.decoder import TorchDecoder, random_state_dict, tiny_config
+    from rhinoforge_b200.quant.int4_pack import pack_int4
+    from rhinoforge_b200.runtime.engine import DecoderEngine
+    cfg = tiny_config(num_layers=2)
+    sd = random_state_dict(cfg, seed=0, dtype=torch.float16, norm_jitter=0.05)
+
+    def quant(w):
+        wf = w.float()
+        grp = wf.view(wf.shape[0], -1, group) if group else wf.view(wf.shape[0], 1, -1)
+        sc = (grp.abs().amax(-1) / 7.0).clamp_min(1e-8)
+        q = torch.round(grp / sc[..., None]).clamp_(-8, 7)
+        return q.to(torch.int8).view_as(wf), sc, (q * sc[..., None].half().float()).view_as(wf)
+
+    deq, packed, scales = {}, {}, {}
+    for k, v in sd.items():
+        if v.dim() == 2 and "embed" not in k and "lm_head" not in k:
+            q, sc, d = quant(v)
+            deq[k], packed[k], scales[k] = d, pack_int4(q), sc.half()
+        else:
+            deq[k] = v
+    oracle = TorchDecoder(cfg, deq, dtype=torch.float32, device="cuda")
+
+    def get(n):
+        if n not in sd:
+            return sd["model.embed_tokens.weight"]
+        return packed[n] if (from_packed and n in packed) else sd[n]
+    get.scale = lambda n: scales.get(n)
+    eng = DecoderEngine(cfg, get, dtype=torch.float16, max_batch=2, max_seq_len=96, quant="w4a16", w4_group=group)
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, cfg.vocab_size, (L,), generator=g) for L in (19, 40)]
+    _, logits = eng.prefill(prompts, return_logits=True)
+    for b, p in enumerate(prompts):
+        oracle.reset()
+        ref = oracle.forward(p[None].cuda())[0, -1]
+        torch.testing.assert_close(logits[b].float(), ref.float(), rtol=2e-2, atol=2e-2)
+    toks = eng.generate(prompts, 6)
+    assert toks.shape == (2, 6)
+    eng.check_status()
+    eng.close()
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M,N,K,dual", [(1, 1024, 2048, False), (48, 520, 1024, False), (64, 768, 512, True), (300, 512, 1024, False)])
+def test_gemm_nvfp4(dt, M, N, K, dual, status):
+    """NVFP4 weights (e2m1 codes, e4m3 block scale per 16 columns, fp32 tensor scale) through the 4-bit main loop;
+    reference = x @ the exact fp32 weight the codes stand for."""
+    from rhinoforge_b200.ops import kernels as K_
+    from rhinoforge_b200.quant.nvfp4_pack import dequantize_nvfp4, quantize_nvfp4
+    torch.manual_seed(N + K)
+    rows = 2 * N if dual else N
+    w = torch.randn(rows, K, device="cuda") * 0.05
+    codes, sc, ts = quantize_nvfp4(w)
+    wd = dequantize_nvfp4(codes, sc, ts)
+    img = K_.pack_weight_nvfp4(codes, sc, ts, sections=2 if dual else 1, dtype=dt)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    kw = dict(packed_shape=(rows, K), w_bits=4, w_group=16, w_fp4=True, status=status)
+    z = x.float() @ wd.t()
+    if dual:
+        y = K_.gemm(x, img, act="silu_mul", dual=True, **kw)
+        ref = torch.nn.functional.silu(z[:, :N]) * z[:, N:]
+    else:
+        y = K_.gemm(x, img, **kw)
+        ref = z
+    _close(y, ref, dt, scale=max(1.0, ref.abs().max().item()) * (4 if dt == torch.bfloat16 else 1))
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M,H,I,splits", [(1, 1024, 2048, 0), (64, 1024, 3072, 0), (16, 512, 1024, 1), (200, 768, 1536, 0),
+                                           (33, 1280, 512, 4)])
+def test_gemm_folded_rmsnorm(dt, M, H, I, splits, status):
+    """RMSNorm without a kernel of its own: the residual GEMM writes per-tile sums of squares of its finished rows, the
+    next projection (norm weights multiplied into its columns) scales its rows by their reciprocal RMS.  Reference:
+    rmsnorm(hidden) * w @ W2^T on the rows the first GEMM stored."""
+    from rhinoforge_b200.ops import kernels as K_
+    torch.manual_seed(M + H)
+    x = (torch.randn(M, I, device="cuda") * 0.5).to(dt)
+    w1 = (torch.randn(H, I, device="cuda") * 0.05).to(dt)
+    resid = torch.randn(M, H, device="cuda").to(dt)
+    nw = (1.0 + 0.2 * torch.randn(H, device="cuda")).to(dt)
+    w2 = (torch.randn(2 * I, H, device="cuda") * 0.05).to(dt)
+    bias = (torch.randn(2 * I, device="cuda") * 0.1).to(dt)
+    tiles = (H + 127) // 128
+    ss = torch.full((tiles, 256), float("nan"), device="cuda")
+    hidden = resid.clone()
+    K_.gemm(x, K_.pack_weight(w1), packed_shape=(H, I), residual=hidden, out=hidden, ss_out=ss, status=status,
+            force_splits=splits)
+    ref_h = (x.float() @ w1.float().t() + resid.float())
+    _close(hidden, ref_h, dt, scale=max(1.0, ref_h.abs().max().item()))
+    want_ss = hidden.float().pow(2).view(M, tiles, -1).sum(-1).t()             # [tiles, M] of the rows as stored
+    torch.testing.assert_close(ss[:, :M], want_ss, rtol=1e-4, atol=1e-3)
+    w2f = (w2.float() * nw.float()[None]).to(dt)                                # norm weights folded into the columns
+    y = K_.gemm(hidden, K_.pack_weight(w2f, 2), packed_shape=(2 * I, H), bias=bias, act="silu_mul", dual=True, ss_in=ss,
+                ss_dim=H, ss_eps=1e-6, status=status)
+    hn = hidden.float() * torch.rsqrt(hidden.float().pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()
+    z = hn @ w2.float().t() + bias.float()
+    ref = torch.nn.functional.silu(z[:, :I]) * z[:, I:]
+    _close(y, ref, dt, scale=max(1.0, ref.abs().max().item()) * (4 if dt == torch.bfloat16 else 1))
