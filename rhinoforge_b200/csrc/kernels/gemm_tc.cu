@@ -78,9 +78,11 @@ struct alignas(8) GemmSmemCtl {
   uint64_t accum;
   uint32_t tmem_base;
   int32_t abort_flag;
-  float rs[256];           // ss_in: reciprocal RMS of this tile's token columns
-  float ssw[4][256];       // ss_out: the four epilogue warps' partial sums of squares per token column
 };
+// Scratch behind the control block, present only in launches with a folded RMSNorm (ss_in / ss_out):
+// rs[256] = reciprocal RMS of this tile's token columns, then ssw[4][256] = the four epilogue warps' partial sums of
+// squares per token column.
+constexpr int kSsScratchBytes = (256 + 4 * 256) * (int)sizeof(float);
 
 // W8 = int8 weights (W8A16): TMA brings the int8 tile into a staging area of the stage, four extra
 // converter warps widen it into the 128-byte-swizzled 16-bit tile the MMA reads, and the
@@ -402,6 +404,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t crank = p.splits > 1 ? cluster_ctarank() : 0u;
 
   // folded RMSNorm: reciprocal RMS of every token column of this tile from the producer's per-tile sums of squares
+  float* ss_rs = reinterpret_cast<float*>(ctl + 1);
+  float (*ss_w)[256] = reinterpret_cast<float (*)[256]>(ss_rs + 256);
   const bool use_rs = SWAP && p.ss_in != nullptr;
   if (use_rs) {
     for (int c = tid; c < bn; c += (int)blockDim.x) {
@@ -409,7 +413,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       float s = 0.f;
       if (tok < p.M)
         for (int t = 0; t < p.ss_tiles; ++t) s += p.ss_in[(size_t)t * p.ss_ld + tok];
-      ctl->rs[c] = rsqrtf(s * p.ss_inv_dim + p.ss_eps);
+      ss_rs[c] = rsqrtf(s * p.ss_inv_dim + p.ss_eps);
     }
     __syncthreads();
   }
@@ -419,7 +423,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     float q = v * v;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
-    if (lane_id() == 0 && warp < 4) ctl->ssw[warp][c] = q;
+    if (lane_id() == 0 && warp < 4) ss_w[warp][c] = q;
   };
 
   // per-element epilogue math shared by both paths
@@ -427,7 +431,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   auto finish = [&](int tok, int n, float vg, float vu) -> float {
     if (!affine) return apply_act(p.act, vg, vu);
     if (use_rs) {
-      const float rs = ctl->rs[tok - blockIdx.y * bn];
+      const float rs = ss_rs[tok - blockIdx.y * bn];
       vg *= rs;
       vu *= rs;
     }
@@ -623,7 +627,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // the columns this CTA finished (crank, crank + S, ...): one thread each adds the four warps' sums
         __syncthreads();
         for (int c = (int)crank + tid * p.splits; c < ncols; c += (int)blockDim.x * p.splits)
-          p.ss_out[(size_t)blockIdx.x * p.ss_ld + b0 + c] = ctl->ssw[0][c] + ctl->ssw[1][c] + ctl->ssw[2][c] + ctl->ssw[3][c];
+          p.ss_out[(size_t)blockIdx.x * p.ss_ld + b0 + c] = ss_w[0][c] + ss_w[1][c] + ss_w[2][c] + ss_w[3][c];
       }
     }
   } else if (!aborted) {
@@ -686,7 +690,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           // last column group: one thread per token column adds the four warps' sums
           __syncthreads();
           for (int cc = tid; cc < ncols; cc += (int)blockDim.x)
-            p.ss_out[(size_t)blockIdx.x * p.ss_ld + b0 + cc] = ctl->ssw[0][cc] + ctl->ssw[1][cc] + ctl->ssw[2][cc] + ctl->ssw[3][cc];
+            p.ss_out[(size_t)blockIdx.x * p.ss_ld + b0 + cc] = ss_w[0][cc] + ss_w[1][cc] + ss_w[2][cc] + ss_w[3][cc];
         }
       } else {
         const int n0 = b0 + c;
@@ -1010,7 +1014,7 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
     const int rows = swap ? kBM : pl->bn;
     stage_bytes += round_up((dual ? 2 : 1) * (g->w_bits == 4 ? ceil_div(rows, kBM) * rf_w4_block_bytes(g->w_group) : rows * kBK), 1024);
   }
-  const int ctl_bytes = (int)sizeof(GemmSmemCtl) + 64;
+  const int ctl_bytes = (int)sizeof(GemmSmemCtl) + 64 + ((g->ss_in || g->ss_out) ? kSsScratchBytes : 0);
   const bool publish = g->ar_world > 1 && g->ar_publish && swap;
   static const int env_smem_kb = [] { const char* e = getenv("RF_GEMM_SMEM_KB"); return e ? atoi(e) : 0; }();
 
