@@ -138,6 +138,22 @@ class PagedKV:
         v = v.permute(1, 0, 2, 3).reshape(self.num_kv_heads, npg * PAGE_TOKENS, self.head_dim)[:, :L]
         return k, v
 
+    def scatter(self, layer: int, seq: int, k: torch.Tensor, v: torch.Tensor, start: int = 0) -> None:
+        """Write dense ``k, v [kv_heads, L, head_dim]`` (already rotated) into rows ``[start, start + L)`` of one
+        sequence's pages: the inverse of :meth:`gather` (keys and values computed elsewhere, e.g. a prefix that another
+        model produced).  The pages must be owned already (:meth:`ensure`); ``lengths`` is left to the caller."""
+        L = int(k.shape[1])
+        if tuple(k.shape) != (self.num_kv_heads, L, self.head_dim) or tuple(v.shape) != tuple(k.shape):
+            raise ValueError(f"expected [kv_heads={self.num_kv_heads}, L, head_dim={self.head_dim}], got {tuple(k.shape)} / "
+                             f"{tuple(v.shape)}")
+        if start + L > int(self._capacity[seq]):
+            raise ValueError(f"rows [{start}, {start + L}) exceed the {int(self._capacity[seq])} rows sequence {seq} owns")
+        rows = torch.arange(start, start + L)
+        pages = self._pt_host[seq][(rows // PAGE_TOKENS).long()].long().to(self.device)
+        slot = (rows % PAGE_TOKENS).to(self.device)
+        for idx, t in ((0, k), (1, v)):
+            self.kv[layer, idx][pages, :, slot] = t.to(self.device, self.dtype).transpose(0, 1)
+
     def zero_(self) -> None:
         self.kv.zero_()
 
