@@ -165,6 +165,7 @@ class RfStackForward(C.Structure):
         ("n_deepstack_rows", C.c_int32),
         ("taps", C.c_void_p), ("tap_layers", C.c_void_p), ("n_taps", C.c_int32),
         ("state_slot", C.c_void_p), ("state_fresh", C.c_void_p),
+        ("twin_split", C.c_int32), ("reserved0", C.c_int32),
     ]
 
 

@@ -333,6 +333,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   }
+  // ------------- folded RMSNorm: reciprocal RMS of this tile's token columns ----
+  // Warps 2 and 3 have nothing to do until the accumulator is complete: they add up the producer kernel's per-tile sums
+  // of squares (fixed order) while the weights stream.  The block-wide barrier ahead of the epilogue publishes ss_rs.
+  if (SWAP && p.ss_in != nullptr && warp >= 2 && warp < 4) {
+    float* rs_out = reinterpret_cast<float*>(ctl + 1);
+    for (int c = tid - 64; c < bn; c += 64) {
+      const int tok = blockIdx.y * bn + c;
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      if (tok < p.M) {
+        const float* src = p.ss_in + tok;
+        int t = 0;
+        for (; t + 4 <= p.ss_tiles; t += 4) {          // four independent loads in flight per round
+          s0 += src[(size_t)(t + 0) * p.ss_ld];
+          s1 += src[(size_t)(t + 1) * p.ss_ld];
+          s2 += src[(size_t)(t + 2) * p.ss_ld];
+          s3 += src[(size_t)(t + 3) * p.ss_ld];
+        }
+        for (; t < p.ss_tiles; ++t) s0 += src[(size_t)t * p.ss_ld];
+      }
+      rs_out[c] = rsqrtf(((s0 + s1) + (s2 + s3)) * p.ss_inv_dim + p.ss_eps);
+    }
+  }
   // --------------------------------------------------------- MMA issuer ----
   if (warp == 1 && lane_id() == 0) {
     const uint32_t idesc = umma_idesc_f16(kBM, bn, Num<T>::kFmt);
@@ -406,17 +428,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // folded RMSNorm: reciprocal RMS of every token column of this tile from the producer's per-tile sums of squares
   float* ss_rs = reinterpret_cast<float*>(ctl + 1);
   float (*ss_w)[256] = reinterpret_cast<float (*)[256]>(ss_rs + 256);
-  const bool use_rs = SWAP && p.ss_in != nullptr;
-  if (use_rs) {
-    for (int c = tid; c < bn; c += (int)blockDim.x) {
-      const int tok = blockIdx.y * bn + c;
-      float s = 0.f;
-      if (tok < p.M)
-        for (int t = 0; t < p.ss_tiles; ++t) s += p.ss_in[(size_t)t * p.ss_ld + tok];
-      ss_rs[c] = rsqrtf(s * p.ss_inv_dim + p.ss_eps);
-    }
-    __syncthreads();
-  }
+  const bool use_rs = SWAP && p.ss_in != nullptr;   // ss_rs was filled by warps 2 and 3 while the main loop ran
   const bool emit_ss = SWAP && p.ss_out != nullptr && p.ar_world <= 1;
   // sum over this warp's 32 output features of the square of one finished value per lane, for token column c
   auto ss_add = [&](int c, float v) {

@@ -22,6 +22,8 @@ namespace rf {
 struct Stack {
   RfStackConfig cfg;
   std::vector<RfLayerWeights> layers;
+  std::vector<RfLayerWeights> twins;      // second weight set per layer (mixture-of-transformers); wqkv == null: none
+  const void* twin_final_norm_w = nullptr;
   const void* final_norm_w = nullptr;
   const void* final_norm_b = nullptr;
   const void* w_lm = nullptr;
@@ -285,6 +287,20 @@ static int norm(const Stack& s, const void* x, const void* w, const void* b, voi
   }
 }
 
+// A projection of rows routed to two weight sets: rows [0, split) with (wA, sA, bA), rows [split, M) with (wB, sB, bB).
+static int linear_twin(const Stack& s, const void* x, int64_t ldx, const void* wA, const void* sA, const void* bA,
+                       const void* wB, const void* sB, const void* bB, void* out, int64_t ldo, const void* residual,
+                       int64_t ldr, int M, int split, int N, int K, int act, int dual_offset, cudaStream_t st) {
+  const size_t e = 2;
+  int rc = RF_OK;
+  if (split > 0) rc = linear(s, x, ldx, wA, sA, bA, out, ldo, residual, ldr, split, N, K, act, dual_offset, false, st);
+  if (rc == RF_OK && split < M)
+    rc = linear(s, (const uint8_t*)x + (size_t)split * ldx * e, ldx, wB, sB, bB, (uint8_t*)out + (size_t)split * ldo * e, ldo,
+                residual ? (const uint8_t*)residual + (size_t)split * ldr * e : nullptr, ldr, M - split, N, K, act,
+                dual_offset, false, st);
+  return rc;
+}
+
 static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
   const RfStackConfig& c = s.cfg;
   RF_REQUIRE(s.base != nullptr, "stack arena is not bound");
@@ -316,6 +332,14 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     RF_REQUIRE(norm_rides && c.tp_world == 1 && c.moe_experts == 0 && c.gdn_Hv == 0,
                "norm_folded needs a plain RMSNorm dense decoder on one GPU");
   const bool fuse_ss = folded && T <= 256;
+  // mixture-of-transformers: rows [0, split) use the layers' own weights, rows [split, T) their twins
+  const int split = f.twin_split;
+  const bool twin = split > 0;
+  if (twin) {
+    RF_REQUIRE(split <= T && s.twins.size() == s.layers.size(), "twin_split %d needs twin weights on every layer (rows %d)", split, T);
+    RF_REQUIRE(!folded && !side && c.tp_world == 1 && c.moe_experts == 0 && !f.decode && !f.mod,
+               "twin routing runs on a plain pre-norm dense stack (prefill form, one GPU)");
+  }
   float* ss_attn = s.at<float>(s.off_ss);                               // sums of squares of hidden after attention
   float* ss_mlp = ss_attn + (size_t)s.ss_tiles * s.ss_ld;               // ... after the MLP (the next layer's input)
   bool ss_ready = false;    // ss_mlp describes f.hidden as it is now
@@ -326,7 +350,16 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     const uint8_t* mod2 = f.mod ? (const uint8_t*)f.mod + ((size_t)(l * 2 + 1) * nmods) * 3 * H * esz : nullptr;
     // ---- token mixer: softmax attention or Gated-DeltaNet
     const bool qkv_from_hidden = fuse_ss && ss_ready;     // this layer's first norm is the QKV GEMM's row scale
-    if (!have_xn && !qkv_from_hidden) {
+    const RfLayerWeights* tw = twin ? &s.twins[l] : nullptr;
+    if (twin) RF_REQUIRE(tw->wqkv && w.mixer == 0, "layer %d has no twin weights", l);
+    const size_t hrow = (size_t)H * esz;
+    if (twin) {
+      rc = norm(s, f.hidden, w.norm1_w, w.norm1_b, xn, split, nullptr, 1, st);
+      if (rc == RF_OK && split < T)
+        rc = norm(s, (const uint8_t*)f.hidden + split * hrow, tw->norm1_w, tw->norm1_b, (uint8_t*)xn + split * hrow, T - split,
+                  nullptr, 1, st);
+      if (rc) return rc;
+    } else if (!have_xn && !qkv_from_hidden) {
       rc = norm(s, f.hidden, folded ? nullptr : w.norm1_w, w.norm1_b, xn, T, mod1, f.rows_per_mod, st);
       if (rc) return rc;
     }
@@ -365,21 +398,31 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     } else {
     hint_next_weights(s, w.wo, w.so, H, AD, 1, T);
     if (qkv_from_hidden) t_ss_in = ss_mlp;
-    rc = linear(s, qkv_from_hidden ? f.hidden : xn, H, w.wqkv, w.sqkv, w.bqkv, wide, QD, nullptr, 0, T, QD, H, kActNone, 0,
-                false, st);
+    if (twin)
+      rc = linear_twin(s, xn, H, w.wqkv, w.sqkv, w.bqkv, tw->wqkv, tw->sqkv, tw->bqkv, wide, QD, nullptr, 0, T, split, QD, H,
+                       kActNone, 0, st);
+    else
+      rc = linear(s, qkv_from_hidden ? f.hidden : xn, H, w.wqkv, w.sqkv, w.bqkv, wide, QD, nullptr, 0, T, QD, H, kActNone, 0,
+                  false, st);
     if (rc) return rc;
-    {
+    // twin q/k norm weights that differ from the layer's own: the per-head norm + rope + KV insert runs per row range
+    const bool twin_qk = twin && c.qk_norm && tw->q_norm_w && (tw->q_norm_w != w.q_norm_w || tw->k_norm_w != w.k_norm_w);
+    for (int part = 0; part < (twin_qk ? 2 : 1); ++part) {
+      const int r0 = part == 0 ? 0 : split, rn = twin_qk ? (part == 0 ? split : T - split) : T;
+      if (rn <= 0) continue;
+      const RfLayerWeights& nw = part == 0 ? w : *tw;
+      const int pstride = f.pos_stride > 0 ? f.pos_stride : 1;
       RfRopeKv a = {};
-      a.qkv = wide; a.ld = QD; a.tokens = T; a.Hq = c.Hq; a.Hkv = c.Hkv; a.hd = c.hd;
+      a.qkv = (uint8_t*)wide + (size_t)r0 * QD * esz; a.ld = QD; a.tokens = rn; a.Hq = c.Hq; a.Hkv = c.Hkv; a.hd = c.hd;
       a.rot_dim = f.cos ? c.rot_dim : 0;
-      a.q_norm_w = c.qk_norm ? w.q_norm_w : nullptr;
-      a.k_norm_w = c.qk_norm ? w.k_norm_w : nullptr;
+      a.q_norm_w = c.qk_norm ? nw.q_norm_w : nullptr;
+      a.k_norm_w = c.qk_norm ? nw.k_norm_w : nullptr;
       a.eps = c.eps; a.norm_mode = c.norm_kind == RF_NORM_RMS_GEMMA ? 1 : 0;
-      a.cos = f.cos; a.sin = f.sin; a.pos = f.pos; a.pos_stride = f.pos_stride > 0 ? f.pos_stride : 1;
+      a.cos = f.cos; a.sin = f.sin; a.pos = f.pos ? f.pos + (size_t)r0 * pstride : nullptr; a.pos_stride = pstride;
       a.axis_of_freq = f.axis_of_freq;
       if (c.paged_kv) {
         a.k_pool = w.k_pool; a.v_pool = w.v_pool; a.page_table = f.page_table; a.pt_stride = f.pt_stride;
-        a.seq_of_tok = f.seq_of_tok; a.cache_pos = f.cache_pos;
+        a.seq_of_tok = f.seq_of_tok ? f.seq_of_tok + r0 : nullptr; a.cache_pos = f.cache_pos ? f.cache_pos + r0 : nullptr;
       } else {
         a.write_k_inplace = 1;
       }
@@ -433,7 +476,11 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     const bool fuse_gate = c.gated_residual && !c.sandwich_norm && f.rows_per_mod >= T && !c.weights_int8 &&
                            c.tp_world == 1 && f.mod != nullptr;
     hint_next_weights(s, w.w_up, w.s_up, s.glu() ? 2 * (int64_t)I : I, H, s.glu() ? 2 : 1, T);
-    if (!side) {
+    if (twin) {
+      rc = linear_twin(s, mix_out, mix_dim, w.wo, w.so, w.bo, tw->wo, tw->so, tw->bo, f.hidden, H, f.hidden, H, T, split, H,
+                       mix_dim, kActNone, 0, st);
+      if (rc) return rc;
+    } else if (!side) {
       if (fuse_ss) t_ss_out = ss_attn;
       rc = linear_ar(s, mix_out, mix_dim, w.wo, w.so, w.bo, f.hidden, f.hidden, T, mix_dim,
                      norm_rides ? w.norm2_w : nullptr, xn, &have_xn2, st);
@@ -455,7 +502,13 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
       if (rc) return rc;
     }
     // ---- MLP block
-    if (!have_xn2 && !fuse_ss) {
+    if (twin) {
+      rc = norm(s, f.hidden, w.norm2_w, w.norm2_b, xn, split, nullptr, 1, st);
+      if (rc == RF_OK && split < T)
+        rc = norm(s, (const uint8_t*)f.hidden + split * hrow, tw->norm2_w, tw->norm2_b, (uint8_t*)xn + split * hrow, T - split,
+                  nullptr, 1, st);
+      if (rc) return rc;
+    } else if (!have_xn2 && !fuse_ss) {
       rc = norm(s, f.hidden, folded ? nullptr : w.norm2_w, w.norm2_b, xn, T, mod2, f.rows_per_mod, st);
       if (rc) return rc;
     }
@@ -479,8 +532,12 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     }
     hint_next_weights(s, w.w_down, w.s_down, H, I, 1, T);
     if (fuse_ss) t_ss_in = ss_attn;
-    rc = linear(s, fuse_ss ? f.hidden : xn, H, w.w_up, w.s_up, w.b_up, wide, I, nullptr, 0, T, I, H, act_of(c.mlp_kind),
-                s.glu() ? I : 0, false, st);
+    if (twin)
+      rc = linear_twin(s, xn, H, w.w_up, w.s_up, w.b_up, tw->w_up, tw->s_up, tw->b_up, wide, I, nullptr, 0, T, split, I, H,
+                       act_of(c.mlp_kind), s.glu() ? I : 0, st);
+    else
+      rc = linear(s, fuse_ss ? f.hidden : xn, H, w.w_up, w.s_up, w.b_up, wide, I, nullptr, 0, T, I, H, act_of(c.mlp_kind),
+                  s.glu() ? I : 0, false, st);
     if (rc) return rc;
     if (moe) {
       rc = rf_moe_scale_blocks(wide, I, moe_dense, s.moe_ld(), T, c.moe_experts, c.moe_expert_inter, c.dtype, st);
@@ -494,7 +551,11 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
       t_ss_out = ss_mlp;
       ss_ready = true;
     }
-    if (!side) {
+    if (twin) {
+      rc = linear_twin(s, wide, I, w.w_down, w.s_down, w.b_down, tw->w_down, tw->s_down, tw->b_down, f.hidden, H, f.hidden, H, T,
+                       split, H, I, kActNone, 0, st);
+      if (rc) return rc;
+    } else if (!side) {
       rc = linear_ar(s, wide, I, w.w_down, w.s_down, w.b_down, f.hidden, f.hidden, T, I, next_w, xn, &have_xn, st);
       if (rc) return rc;
     } else if (fuse_gate && !w.b_down) {
@@ -596,6 +657,25 @@ extern "C" int rf_stack_set_layer(int64_t h, int32_t layer, const RfLayerWeights
   return RF_OK;
 }
 
+extern "C" int rf_stack_set_twin_layer(int64_t h, int32_t layer, const RfLayerWeights* w) {
+  RF_GET_STACK(h);
+  RF_REQUIRE(w && layer >= 0 && layer < s.cfg.layers, "twin layer index %d out of range", layer);
+  RF_REQUIRE(w->wqkv && w->wo && w->w_up && w->w_down, "twin layer %d: missing projection weights", layer);
+  RF_REQUIRE(w->mixer == 0 && s.cfg.tp_world == 1 && s.cfg.moe_experts == 0 && !s.cfg.norm_folded && !s.cfg.gated_residual &&
+                 !s.cfg.sandwich_norm,
+             "twin weights are for dense attention layers of a plain pre-norm stack on one GPU");
+  if (s.cfg.weights_int8) RF_REQUIRE(w->sqkv && w->so && w->s_up && w->s_down, "twin layer %d: int8 weights need scales", layer);
+  if (s.twins.size() != s.layers.size()) s.twins.assign(s.layers.size(), RfLayerWeights{});
+  s.twins[layer] = *w;
+  return RF_OK;
+}
+
+extern "C" int rf_stack_set_twin_head(int64_t h, const void* final_norm_w) {
+  RF_GET_STACK(h);
+  s.twin_final_norm_w = final_norm_w;
+  return RF_OK;
+}
+
 extern "C" int rf_stack_set_kv(int64_t h, int32_t layer, void* k_pool, void* v_pool) {
   RF_GET_STACK(h);
   RF_REQUIRE(layer >= 0 && layer < s.cfg.layers && k_pool && v_pool, "set_kv: layer %d", layer);
@@ -662,6 +742,24 @@ extern "C" int rf_stack_final_norm(int64_t h, const void* hidden, void* out, int
   Stack tmp = s;
   if (c.norm_kind == RF_NORM_ADARMS) tmp.cfg.norm_kind = RF_NORM_RMS;
   return norm(tmp, hidden, s.final_norm_w, s.final_norm_b, out, rows, nullptr, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int rf_stack_final_norm_twin(int64_t h, const void* hidden, void* out, int32_t rows, int32_t twin_split,
+                                        rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_GET_STACK(h);
+  RF_REQUIRE(s.final_norm_w && s.twin_final_norm_w, "stack has no twin final norm");
+  RF_REQUIRE(twin_split >= 0 && twin_split <= rows, "twin_split %d outside [0, %d]", twin_split, rows);
+  Stack tmp = s;
+  if (s.cfg.norm_kind == RF_NORM_ADARMS) tmp.cfg.norm_kind = RF_NORM_RMS;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t row_bytes = (size_t)s.cfg.hidden * 2;
+  int rc = RF_OK;
+  if (twin_split > 0) rc = norm(tmp, hidden, s.final_norm_w, s.final_norm_b, out, twin_split, nullptr, 1, st);
+  if (rc == RF_OK && twin_split < rows)
+    rc = norm(tmp, (const uint8_t*)hidden + twin_split * row_bytes, s.twin_final_norm_w, nullptr,
+              (uint8_t*)out + twin_split * row_bytes, rows - twin_split, nullptr, 1, st);
+  return rc;
 }
 
 extern "C" int rf_stack_head(int64_t h, const void* hidden, const int32_t* row_idx, int32_t rows,

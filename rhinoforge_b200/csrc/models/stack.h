@@ -128,11 +128,23 @@ typedef struct RfStackForward {
   // recurrent-state bookkeeping of Gated-DeltaNet layers: state slot of every sequence (null:
   // sequence index) and whether the sequence starts from an empty state (null: continue)
   const int32_t* state_slot; const int32_t* state_fresh;
+  // Mixture-of-transformers routing by row: rows [0, twin_split) run through the layer's own weights, rows
+  // [twin_split, tokens) through its twin set (rf_stack_set_twin_layer).  0: no routing.  The caller orders the rows
+  // accordingly; positions, cache rows and the attention mask are per row, so the order is free.
+  int32_t twin_split;
+  int32_t reserved0;
 } RfStackForward;
 
 int64_t rf_stack_create(const RfStackConfig* cfg);
 int rf_stack_destroy(int64_t h);
 int rf_stack_set_layer(int64_t h, int32_t layer, const RfLayerWeights* w);
+// Second weight set of a layer (mixture-of-transformers): the norms, q/k norms and the four projections of the rows
+// routed to it (RfStackForward.twin_split); the KV pool and everything else stay the layer's own.  Dense attention
+// layers on one GPU, weights in the same layout as the layer's own.
+int rf_stack_set_twin_layer(int64_t h, int32_t layer, const RfLayerWeights* w);
+// Final norm weights of the twin rows (rf_stack_final_norm_twin).
+int rf_stack_set_twin_head(int64_t h, const void* final_norm_w);
+int rf_stack_final_norm_twin(int64_t h, const void* hidden, void* out, int32_t rows, int32_t twin_split, rf_stream_t stream);
 // Re-point one layer at another KV pool (binding a different cache object).
 int rf_stack_set_kv(int64_t h, int32_t layer, void* k_pool, void* v_pool);
 // Re-point a Gated-DeltaNet layer at other state tensors (binding a different cache object).

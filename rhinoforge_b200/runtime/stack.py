@@ -90,7 +90,9 @@ class NativeStack:
     def __init__(self, spec: StackSpec, layer_weights: Sequence[Dict[str, torch.Tensor]], *, device="cuda",
                  dtype=torch.float16, final_norm_w: Optional[torch.Tensor] = None,
                  final_norm_b: Optional[torch.Tensor] = None, lm_head: Optional[torch.Tensor] = None,
-                 lm_head_scale: Optional[torch.Tensor] = None, kv_cache=None, comm=None):
+                 lm_head_scale: Optional[torch.Tensor] = None, kv_cache=None, comm=None,
+                 twin_layer_weights: Optional[Sequence[Dict[str, torch.Tensor]]] = None,
+                 twin_final_norm_w: Optional[torch.Tensor] = None):
         if len(layer_weights) != spec.layers:
             raise RPUBackendError(f"expected {spec.layers} layer weight sets, got {len(layer_weights)}")
         self.spec, self.dtype, self.device = spec, dtype, torch.device(device)
@@ -118,7 +120,11 @@ class NativeStack:
         self.handle = C.c_int64(h)
         self._keep: List[torch.Tensor] = []
         self.cache = kv_cache
-        for l, lw in enumerate(layer_weights):
+        if twin_layer_weights is not None and len(twin_layer_weights) != spec.layers:
+            raise RPUBackendError(f"expected {spec.layers} twin layer weight sets, got {len(twin_layer_weights)}")
+        sets = [(l, lw, False) for l, lw in enumerate(layer_weights)]
+        sets += [(l, lw, True) for l, lw in enumerate(twin_layer_weights or ())]
+        for l, lw, is_twin in sets:
             w = N.RfLayerWeights()
             glu = spec.mlp in ("swiglu", "geglu_tanh")
             for f in LAYER_FIELDS:
@@ -138,7 +144,13 @@ class NativeStack:
                 if kv_cache is None:
                     raise RPUBackendError("a paged-KV stack needs a kv_cache")
                 w.k_pool, w.v_pool = kv_cache.layer_ptrs(l)
-            N.check(lib.rf_stack_set_layer(self.handle, l, C.byref(w)), "rf_stack_set_layer")
+            if is_twin:      # second weight set of the layer: rows at and beyond forward(twin_split=...) run through it
+                N.check(lib.rf_stack_set_twin_layer(self.handle, l, C.byref(w)), "rf_stack_set_twin_layer")
+            else:
+                N.check(lib.rf_stack_set_layer(self.handle, l, C.byref(w)), "rf_stack_set_layer")
+        if twin_final_norm_w is not None:
+            tf = self._dev(twin_final_norm_w)
+            N.check(lib.rf_stack_set_twin_head(self.handle, C.c_void_p(tf.data_ptr())), "rf_stack_set_twin_head")
         if final_norm_w is not None:
             fw = self._dev(final_norm_w)
             fb = self._dev(final_norm_b) if final_norm_b is not None else None
@@ -189,7 +201,7 @@ class NativeStack:
                 mod: Optional[torch.Tensor] = None, rows_per_mod: int = 1, layer_range=None,
                 deepstack: Optional[Sequence[Optional[torch.Tensor]]] = None,
                 deepstack_rows: Optional[torch.Tensor] = None, taps: Optional[Dict[int, torch.Tensor]] = None,
-                kv_start: Optional[torch.Tensor] = None) -> torch.Tensor:
+                kv_start: Optional[torch.Tensor] = None, twin_split: int = 0) -> torch.Tensor:
         """Run the layer loop in place on ``hidden`` ``[tokens, hidden]`` (all metadata int32, device)."""
         f = N.RfStackForward()
         T = hidden.shape[0]
@@ -213,6 +225,7 @@ class NativeStack:
             f.mod, f.rows_per_mod = mod.data_ptr(), rows_per_mod
         if layer_range is not None:
             f.layer_begin, f.layer_end = layer_range
+        f.twin_split = int(twin_split)
         keep = []
         if deepstack is not None:
             ptrs = torch.tensor([0 if t is None else t.data_ptr() for t in deepstack], dtype=torch.int64)
@@ -233,6 +246,15 @@ class NativeStack:
         N.check(N.lib().rf_stack_final_norm(self.handle, C.c_void_p(hidden.data_ptr()), C.c_void_p(out.data_ptr()),
                                             hidden.shape[0], C.c_void_p(torch.cuda.current_stream().cuda_stream)),
                 "rf_stack_final_norm")
+        return out
+
+    def final_norm_twin(self, hidden: torch.Tensor, twin_split: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Final norm with the stack's own weights on rows ``[0, twin_split)`` and the twin's on the rest."""
+        out = torch.empty_like(hidden) if out is None else out
+        N.check(N.lib().rf_stack_final_norm_twin(self.handle, C.c_void_p(hidden.data_ptr()), C.c_void_p(out.data_ptr()),
+                                                 hidden.shape[0], int(twin_split),
+                                                 C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                "rf_stack_final_norm_twin")
         return out
 
     def check_status(self) -> None:
