@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """HY-Embodied vision-language-action policy (HunYuan-VL mixture-of-transformers + action expert).
 
-This entry point validates its configuration; the model family itself is not part of this build yet, so a
-real run stops with UnsupportedModelError before any checkpoint is read."""
+The checkpoint directory must hold model.safetensors and the tokenizer files; physical poses additionally need the
+normalisation statistics ([model].norm_stats_path, JSON) and the current end-effector pose ([request].ee_pose)."""
 from __future__ import annotations
 
 import sys
@@ -18,7 +18,7 @@ def load_config(path) -> dict:
     config = load_toml(path)
     require_model(config)
     model = config["model"]
-    for key, kind in (("dataset_key", str), ("camera_names", list), ("action_horizon", int), ("num_steps", int), ("max_seq_len", int)):
+    for key, kind in (("dtype", str), ("prefix_len", int), ("n_cameras", int), ("norm_stats_path", str)):
         if key in model and (not isinstance(model[key], kind) or isinstance(model[key], bool)):
             raise ValueError(f"[model].{key} must be of type {kind.__name__}")
     req = require_request(config, fields=(("instruction", str), ("noise_seed", int)))
@@ -36,8 +36,21 @@ def main() -> int:
     if args.check_config:
         return ok(args.config, require_model(config))
     sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
-    from rpu_backend.api.errors import UnsupportedModelError
-    raise UnsupportedModelError(f"{FAMILY} is not built in this release; supported policies: Pi0.5 (examples/pi05.py)")
+    from _config import load_image, resolve_checkpoint
+    from rpu_backend.api import HyEmbodiedPolicy
+    model, req = config["model"], config["request"]
+    images = [load_image(p) for p in req["images"]]
+    policy = HyEmbodiedPolicy.from_checkpoint(resolve_checkpoint(config), dtype=model.get("dtype", "fp16"),
+                                              prefix_len=int(model.get("prefix_len", 240)), n_cameras=len(images),
+                                              norm_stats_path=model.get("norm_stats_path")).to("rpu")
+    try:
+        out = policy.infer(images=images, instruction=req["instruction"], ee_pose=req.get("ee_pose"), state=req.get("state"),
+                           noise_seed=int(req.get("noise_seed", 0)))
+        print(f"actions_normalized={tuple(out.actions_normalized.shape)} physical={out.physical_action_available} "
+              f"latency_ms={out.latency_ms:.3f}")
+    finally:
+        policy.close()
+    return 0
 
 
 if __name__ == "__main__":

@@ -12,7 +12,8 @@ _LAZY = {
     "WallOssActionOutput": ("wall_oss", "WallOssActionOutput"),
     "Lingbot2Policy": ("lingbot2", "Lingbot2Policy"),
     "Lingbot2ActionOutput": ("lingbot2", "Lingbot2ActionOutput"),
-    "HyEmbodiedPolicy": ("_unbuilt", "HyEmbodiedPolicy"),
+    "HyEmbodiedPolicy": ("hy_embodied", "HyEmbodiedPolicy"),
+    "HyEmbodiedActionOutput": ("hy_embodied", "HyEmbodiedActionOutput"),
     "RhinoVLAPolicy": ("rhinovla", "RhinoVLAPolicy"),
 }
 

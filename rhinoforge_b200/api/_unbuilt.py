@@ -1,12 +1,9 @@
 """Policy facades of model families that this framework does not run yet.
 
-The classes exist so that ``rpu_backend.api.HyEmbodiedPolicy`` imports and fails in a defined way: every
-constructor path raises :class:`UnsupportedModelError` naming the family, what it would need and what is available
-instead, before any checkpoint is read (the reference's facade: ``python/rpu_backend/api/hy_embodied.py``).
-``WallOssPolicy``, ``Lingbot2Policy`` and ``RhinoVLAPolicy`` are not among them: they are built in
-:mod:`rhinoforge_b200.api.wall_oss`, :mod:`rhinoforge_b200.api.lingbot2` and :mod:`rhinoforge_b200.api.rhinovla`.  The shared pieces those policies use - runtime-environment
-validation, action de-normalisation, 6-D rotation decoding - are built (``_runtime_env``, ``action_denorm``,
-``hy_action_decode``), and so are the towers they start from (Qwen2.5-VL ViT, SigLIP, the Qwen2.5 / Qwen3 decoder stack).
+None is left: ``Pi05Policy``, ``Lingbot2Policy``, ``WallOssPolicy``, ``HyEmbodiedPolicy`` and ``RhinoVLAPolicy`` are built
+in :mod:`rhinoforge_b200.api.policy`, ``lingbot2``, ``wall_oss``, ``hy_embodied`` and ``rhinovla``.  The factory stays for a
+family whose facade should import and fail in a defined way - every constructor path raising
+:class:`UnsupportedModelError` that names the family and what it would need - before its runtime exists.
 """
 from __future__ import annotations
 
@@ -15,10 +12,9 @@ from typing import Any
 from .errors import UnsupportedModelError
 
 
-def _facade(name: str, family: str, needs: str):
+def unbuilt_facade(name: str, family: str, needs: str):
     def refuse(cls, *args: Any, **kwargs: Any):
-        raise UnsupportedModelError(f"{family} is not built in this framework ({needs}); "
-                                    "the policies that run today are Pi05Policy, Lingbot2Policy and WallOssPolicy")
+        raise UnsupportedModelError(f"{family} is not built in this framework ({needs})")
 
     body = {
         "__doc__": f"{family}: defined, not runnable (see :mod:`rhinoforge_b200.api._unbuilt`).",
@@ -30,7 +26,4 @@ def _facade(name: str, family: str, needs: str):
     return type(name, (), body)
 
 
-HyEmbodiedPolicy = _facade("HyEmbodiedPolicy", "HunYuan embodied VLA (HYViT2 tower, twin-weight prefill, action expert)",
-                           "needs the HYViT2 tower and row-routed twin weights")
-
-__all__ = ["HyEmbodiedPolicy"]
+__all__ = ["unbuilt_facade"]

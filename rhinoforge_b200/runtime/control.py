@@ -25,6 +25,7 @@ KEPT_ENV: Dict[str, tuple] = {
     "RPU_PI05_DENOISE_UNROLL": ("bool", True, "MODEL"),
     "RPU_LINGBOT2_DENOISE_UNROLL": ("bool", True, "MODEL"),
     "RPU_WALL_OSS_FUSED_DENOISE": ("bool", True, "MODEL"),
+    "RPU_HY_VLA_UNROLL": ("bool", True, "MODEL"),
     "RPU_QWEN3_5_FREE_HF_WEIGHTS": ("bool", False, "MODEL"),
     "QWEN3_5_TEXT_CHUNK": ("int", 0, "MODEL"),
     "QWEN3_5_TEXT_PADDING_BUDGET": ("int", 64, "MODEL"),

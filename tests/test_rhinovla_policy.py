@@ -5,7 +5,8 @@ import types
 
 import pytest
 
-from rhinoforge_b200.api import HyEmbodiedPolicy, RhinoVLAPolicy, UnsupportedModelError
+from rhinoforge_b200.api import RhinoVLAPolicy, UnsupportedModelError
+from rhinoforge_b200.api._unbuilt import unbuilt_facade
 from rhinoforge_b200.api.rhinovla import StagePlan, declared_capabilities, resolve_runtime_factory
 
 CAPS = {"prefill": ("chunk_size", "padding_rows", "padding_budget"), "action": ("chunk_size",)}
@@ -53,8 +54,11 @@ class FakeRuntime:
 def test_constructor_is_closed_and_other_families_still_refuse():
     with pytest.raises(RuntimeError, match="not a public constructor"):
         RhinoVLAPolicy()
+    Stub = unbuilt_facade("SomePolicy", "some family", "needs its runtime")
+    with pytest.raises(UnsupportedModelError, match="some family"):
+        Stub.from_pretrained("x")
     with pytest.raises(UnsupportedModelError):
-        HyEmbodiedPolicy.from_pretrained("x")
+        Stub()
 
 
 def test_from_runtime_without_execution_config_is_a_plain_wrapper():
