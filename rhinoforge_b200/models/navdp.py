@@ -1,0 +1,355 @@
+"""NavDP: a 16-layer pre-LayerNorm transformer-decoder diffusion policy (the navigation action head of InternVLA-N1).
+
+Per layer, with ``x`` the 32 action tokens of every sampled trajectory and ``memory`` 34 conditioning tokens
+(time embedding, goal embedding, 32 RGB-D tokens, plus a learned position table)::
+
+    x += self_attn(LN1(x))              # causal over the 32 action tokens
+    x += cross_attn(LN2(x), memory)     # the memory is shared by all trajectories
+    x += W2 gelu(W1 LN3(x))             # 384 -> 1536 -> 384
+
+(``d_model`` 384, 8 heads of 48, packed ``in_proj`` weights, biases everywhere.)  A prediction is 20 DDPM reverse steps
+(squared-cosine schedule, epsilon prediction, the predicted clean sample clipped to [-1, 1]) over
+``eps = action_head(LN(decoder(input_embed(x) + out_pos, memory_k)))``.
+
+Here everything of a call that does not depend on ``x`` is hoisted: the memory of all 20 steps goes through every layer's
+cross-attention K/V projection as ONE GEMM per layer (20 x 34 rows), the DDPM coefficients and the step noise are tables,
+and the whole reverse loop - 11 launches per layer: three LayerNorms, six GEMMs with bias / GELU / residual epilogues,
+two attention launches - replays from one CUDA graph.  The B sampled trajectories are packed on the GEMM row axis;
+self-attention sees them as B sequences, cross-attention as B sequences over the same memory rows.  Heads of 48 run on
+the 64-wide attention kernels with zero-padded head columns.
+
+Reference behaviour: ``src/fused/rpu_navdp_model.cpp:1-16`` (layer recipe, geometry),
+``python/rpu_backend/adapters/navdp/runtime.py:60-140,142-200,256-330`` (glue, DDPM loop and coefficients, tensor names).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, Iterator, List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+
+@dataclass
+class NavdpConfig:
+    layers: int = 16
+    hidden: int = 384
+    heads: int = 8
+    head_dim: int = 48
+    ff: int = 1536
+    memory_len: int = 34
+    predict_size: int = 32
+    action_dim: int = 3
+    eps: float = 1e-5
+    steps: int = 20
+
+
+def tiny_navdp_config(**kw) -> NavdpConfig:
+    base = dict(layers=2, hidden=96, heads=2, head_dim=48, ff=192, memory_len=10, predict_size=8, action_dim=3, steps=5)
+    base.update(kw)
+    return NavdpConfig(**base)
+
+
+def navdp_shapes(cfg: NavdpConfig) -> Iterator[Tuple[str, Tuple[int, ...], str]]:
+    H = cfg.hidden
+    yield "input_embed.weight", (H, cfg.action_dim), "matrix"
+    yield "input_embed.bias", (H,), "bias"
+    yield "out_pos_embed", (1, cfg.predict_size, H), "embed"
+    yield "cond_pos_embed", (1, cfg.memory_len, H), "embed"
+    yield "layernorm.weight", (H,), "norm"
+    yield "layernorm.bias", (H,), "bias"
+    yield "action_head.weight", (cfg.action_dim, H), "matrix"
+    yield "action_head.bias", (cfg.action_dim,), "bias"
+    for i in range(cfg.layers):
+        p = f"decoder.layers.{i}."
+        for a in ("self_attn", "multihead_attn"):
+            yield p + a + ".in_proj_weight", (3 * H, H), "matrix"
+            yield p + a + ".in_proj_bias", (3 * H,), "bias"
+            yield p + a + ".out_proj.weight", (H, H), "matrix"
+            yield p + a + ".out_proj.bias", (H,), "bias"
+        yield p + "linear1.weight", (cfg.ff, H), "matrix"
+        yield p + "linear1.bias", (cfg.ff,), "bias"
+        yield p + "linear2.weight", (H, cfg.ff), "matrix"
+        yield p + "linear2.bias", (H,), "bias"
+        for n in (1, 2, 3):
+            yield p + f"norm{n}.weight", (H,), "norm"
+            yield p + f"norm{n}.bias", (H,), "bias"
+
+
+def random_navdp_state_dict(cfg: NavdpConfig, *, seed: int = 0, std: float = 0.08, dtype=torch.float32) -> Dict[str, torch.Tensor]:
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for name, shape, kind in navdp_shapes(cfg):
+        r = torch.randn(shape, generator=g)
+        sd[name] = {"matrix": r * std, "embed": r * 0.2, "norm": 1.0 + 0.05 * r, "bias": 0.03 * r}[kind].to(dtype)
+    return sd
+
+
+def check_state_dict(cfg: NavdpConfig, sd) -> None:
+    """Every tensor of the profile present, floating point and of the profile's shape; the message lists the first few that are not."""
+    bad = []
+    for name, shape, _ in navdp_shapes(cfg):
+        t = sd.get(name) if hasattr(sd, "get") else (sd[name] if name in sd else None)
+        if t is None:
+            bad.append(f"{name}: missing, expected {shape}")
+        elif tuple(t.shape) != shape or not t.is_floating_point():
+            bad.append(f"{name}: {tuple(t.shape)} {str(t.dtype).replace('torch.', '')}, expected {shape}")
+    if bad:
+        more = f" (+{len(bad) - 8} more)" if len(bad) > 8 else ""
+        raise ValueError(f"NavDP checkpoint does not fit the {cfg.layers}-layer profile: " + "; ".join(bad[:8]) + more)
+
+
+# ----------------------------------------------------------------------------- schedule
+def sinusoidal_time_embedding(t: torch.Tensor, dim: int) -> torch.Tensor:
+    half = dim // 2
+    f = torch.exp(torch.arange(half, dtype=torch.float32) * -(math.log(10000.0) / (half - 1)))
+    a = t.float()[:, None] * f[None, :]
+    return torch.cat((a.sin(), a.cos()), -1)
+
+
+def ddpm_tables(steps: int) -> Tuple[List[int], torch.Tensor, torch.Tensor]:
+    """``(timesteps, coeff [steps, 4], sigma [steps])`` of the reverse loop over a squared-cosine schedule with ``steps``
+    training steps: ``x0 = clip(A x + B eps); x <- C x0 + D x + sigma z`` (``sigma = 0`` at the last step)."""
+    bar = lambda u: math.cos((u + 0.008) / 1.008 * math.pi / 2) ** 2
+    betas = torch.tensor([min(1 - bar((i + 1) / steps) / bar(i / steps), 0.999) for i in range(steps)], dtype=torch.float64)
+    ac = torch.cumprod(1.0 - betas, 0)
+    ts = list(range(steps - 1, -1, -1))
+    coeff, sigma = torch.zeros(steps, 4, dtype=torch.float64), torch.zeros(steps, dtype=torch.float64)
+    for idx, t in enumerate(ts):
+        ap = float(ac[t])
+        app = float(ac[t - 1]) if t > 0 else 1.0
+        bp, bpp = 1 - ap, 1 - app
+        ca = ap / app
+        cb = 1 - ca
+        coeff[idx] = torch.tensor([1 / ap ** 0.5, -(bp ** 0.5) / ap ** 0.5, (app ** 0.5 * cb) / bp, (ca ** 0.5 * bpp) / bp])
+        if t > 0:
+            sigma[idx] = max((bpp / bp) * cb, 1e-20) ** 0.5
+    return ts, coeff.float(), sigma.float()
+
+
+def memory_rows(sd, cfg: NavdpConfig, timesteps, goal_embed: torch.Tensor, rgbd_embed: torch.Tensor) -> torch.Tensor:
+    """``[steps, memory_len, H]`` fp32: ``[time_k | goal | rgbd] + cond_pos`` of every step."""
+    te = sinusoidal_time_embedding(torch.tensor(timesteps, dtype=torch.float32), cfg.hidden)
+    dev = sd["cond_pos_embed"].device
+    g, r = goal_embed.reshape(1, -1, cfg.hidden).float().to(dev), rgbd_embed.reshape(1, -1, cfg.hidden).float().to(dev)
+    n = len(timesteps)
+    mem = torch.cat((te.to(dev)[:, None], g.expand(n, -1, -1), r.expand(n, -1, -1)), 1)
+    if mem.shape[1] != cfg.memory_len:
+        raise ValueError(f"memory has {mem.shape[1]} rows (1 + goal + rgbd), the model takes {cfg.memory_len}")
+    return mem + sd["cond_pos_embed"].float()[:, :cfg.memory_len]
+
+
+# ----------------------------------------------------------------------------- fp32 oracle
+class TorchNavdp:
+    """``torch.nn.TransformerDecoder`` (pre-LN, GELU) with the checkpoint loaded, driven by the same tables."""
+
+    def __init__(self, cfg: NavdpConfig, sd: Dict[str, torch.Tensor], device="cpu"):
+        self.cfg, self.device = cfg, torch.device(device)
+        self.sd = {k: v.float().to(self.device) for k, v in sd.items()}
+        layer = torch.nn.TransformerDecoderLayer(cfg.hidden, cfg.heads, cfg.ff, dropout=0.0, activation="gelu", batch_first=True,
+                                                 norm_first=True, layer_norm_eps=cfg.eps)
+        self.dec = torch.nn.TransformerDecoder(layer, cfg.layers).to(self.device).eval()
+        self.dec.load_state_dict({k[len("decoder."):]: v for k, v in self.sd.items() if k.startswith("decoder.")})
+
+    @torch.no_grad()
+    def predict_noise(self, x: torch.Tensor, memory: torch.Tensor) -> torch.Tensor:
+        cfg, sd = self.cfg, self.sd
+        inp = F.linear(x, sd["input_embed.weight"], sd["input_embed.bias"]) + sd["out_pos_embed"][:, :cfg.predict_size]
+        mask = torch.triu(torch.full((cfg.predict_size, cfg.predict_size), float("-inf"), device=self.device), 1)
+        h = self.dec(inp, memory.expand(x.shape[0], -1, -1), tgt_mask=mask)
+        h = F.layer_norm(h, (cfg.hidden,), sd["layernorm.weight"], sd["layernorm.bias"], cfg.eps)
+        return F.linear(h, sd["action_head.weight"], sd["action_head.bias"])
+
+    @torch.no_grad()
+    def predict_action(self, goal_embed, rgbd_embed, init_noise: torch.Tensor, step_noise: torch.Tensor) -> torch.Tensor:
+        """``init_noise [B, P, A]``, ``step_noise [steps, B, P, A]`` (unit normal; scaled by sigma here)."""
+        cfg = self.cfg
+        ts, coeff, sigma = ddpm_tables(cfg.steps)
+        mem = memory_rows(self.sd, cfg, ts, goal_embed, rgbd_embed)
+        x = init_noise.float().to(self.device)
+        for k in range(cfg.steps):
+            eps = self.predict_noise(x, mem[k:k + 1])
+            A, B, C, D = (float(v) for v in coeff[k])
+            x0 = (A * x + B * eps).clamp(-1.0, 1.0)
+            x = C * x0 + D * x + float(sigma[k]) * step_noise[k].float().to(self.device)
+        return x
+
+
+# ----------------------------------------------------------------------------- device engine
+class NavdpEngine:
+    """The decoder and the DDPM loop on the accelerator for up to ``max_samples`` trajectories per call."""
+
+    def __init__(self, cfg: NavdpConfig, sd: Dict[str, torch.Tensor], *, max_samples: int = 4, device="cuda", dtype=torch.float16):
+        from ..ops import kernels as K
+        from ..runtime.stack import pad_heads
+        check_state_dict(cfg, sd)
+        self.K, self.cfg, self.device, self.dtype, self.B = K, cfg, torch.device(device), dtype, max_samples
+        dev, H, hd, Hq = self.device, cfg.hidden, cfg.head_dim, cfg.heads
+        self.hd_pad = 64 if hd <= 64 else (128 if hd <= 128 else 256)
+        if hd > 256:
+            raise ValueError(f"head_dim {hd} is beyond the attention kernels")
+        hp, D = self.hd_pad, Hq * self.hd_pad
+        self.D = D
+        t = lambda w: w.to(dev, dtype).contiguous()
+        pack = lambda w: K.pack_weight(t(w))
+        self.layers = []
+        for i in range(cfg.layers):
+            p = f"decoder.layers.{i}."
+            L = {}
+            for a, tag in (("self_attn", "s"), ("multihead_attn", "c")):
+                w, b = sd[p + a + ".in_proj_weight"], sd[p + a + ".in_proj_bias"]
+                ws = [pad_heads(w[j * H:(j + 1) * H], Hq, hd, hp, 0) for j in range(3)]
+                bs = [pad_heads(b[j * H:(j + 1) * H], Hq, hd, hp, 0) for j in range(3)]
+                if tag == "s":
+                    L["s_qkv_w"], L["s_qkv_b"] = pack(torch.cat(ws, 0)), t(torch.cat(bs, 0))
+                else:
+                    L["c_q_w"], L["c_q_b"] = pack(ws[0]), t(bs[0])
+                    L["c_kv_w"], L["c_kv_b"] = pack(torch.cat(ws[1:], 0)), t(torch.cat(bs[1:], 0))
+                L[tag + "_o_w"] = pack(pad_heads(sd[p + a + ".out_proj.weight"], Hq, hd, hp, 1))
+                L[tag + "_o_b"] = t(sd[p + a + ".out_proj.bias"])
+            L["ff1_w"], L["ff1_b"] = pack(sd[p + "linear1.weight"]), t(sd[p + "linear1.bias"])
+            L["ff2_w"], L["ff2_b"] = pack(sd[p + "linear2.weight"]), t(sd[p + "linear2.bias"])
+            for n in (1, 2, 3):
+                L[f"n{n}_w"], L[f"n{n}_b"] = t(sd[p + f"norm{n}.weight"]), t(sd[p + f"norm{n}.bias"])
+            self.layers.append(L)
+        self.a_pad = (cfg.action_dim + 7) // 8 * 8
+        self.ie_w = t(F.pad(sd["input_embed.weight"], (0, self.a_pad - cfg.action_dim)))
+        self.ie_b = t(sd["input_embed.bias"])
+        self.ah_w = t(F.pad(sd["action_head.weight"], (0, 0, 0, self.a_pad - cfg.action_dim)))
+        self.ah_b = t(F.pad(sd["action_head.bias"], (0, self.a_pad - cfg.action_dim)))
+        self.ln_w, self.ln_b = t(sd["layernorm.weight"]), t(sd["layernorm.bias"])
+        self._sd_small = {k: sd[k].float().to(dev) for k in ("cond_pos_embed",)}
+        P, M, S = cfg.predict_size, cfg.memory_len, cfg.steps
+        R = max_samples * P
+        z = lambda *s: torch.zeros(*s, dtype=dtype, device=dev)
+        self.out_pos = t(sd["out_pos_embed"][0, :P]).repeat(max_samples, 1)           # [R, H]
+        self.x, self.eps, self.x0 = z(R, self.a_pad), z(R, self.a_pad), z(R, self.a_pad)
+        self.sigz = z(S, R, self.a_pad)
+        self.h, self.hn, self.qkv, self.att = z(R, H), z(R, H), z(R, 3 * D), z(R, D)
+        self.q, self.ff = z(R, D), z(R, cfg.ff)
+        self.mem = z(S * M, H)
+        self.mem_kv = [z(S * M, 2 * D) for _ in range(cfg.layers)]
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        self.ts, coeff, sigma = ddpm_tables(S)
+        self.coeff, self.sigma = coeff.tolist(), sigma
+        self._meta = {}
+        for b in range(1, max_samples + 1):
+            self._meta[b] = dict(q_start=i32([j * P for j in range(b)]), q_len=i32([P] * b), kv_self=i32([P] * b),
+                                 kv_mem=i32([M] * b),
+                                 kv_start_step=[i32([k * M] * b) for k in range(S)])
+        self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.status = torch.zeros(32, dtype=torch.int32, device=dev)
+
+    def _decoder(self, b: int, k: int) -> None:
+        """The layers over ``self.h[:b * P]`` with the memory K/V of step ``k``."""
+        cfg, K, m = self.cfg, self.K, self._meta[b]
+        P, D, R = cfg.predict_size, self.D, b * cfg.predict_size
+        h, hn, qkv, att, q, ff = self.h[:R], self.hn[:R], self.qkv[:R], self.att[:R], self.q[:R], self.ff[:R]
+        scale = 1.0 / math.sqrt(cfg.head_dim)
+        for L, kv in zip(self.layers, self.mem_kv):
+            K.layernorm(h, L["n1_w"], L["n1_b"], cfg.eps, out=hn)
+            K.gemm(hn, L["s_qkv_w"], packed_shape=(3 * D, cfg.hidden), bias=L["s_qkv_b"], out=qkv)
+            K.attention_prefill(qkv[:, :D], att, Hq=cfg.heads, Hkv=cfg.heads, hd=self.hd_pad, q_start=m["q_start"], q_len=m["q_len"],
+                                kv_len=m["kv_self"], max_q_len=P, k=qkv[:, D:2 * D], v=qkv[:, 2 * D:], kv_start=m["q_start"],
+                                causal=True, scale=scale, status=self.status)
+            K.gemm(att, L["s_o_w"], packed_shape=(cfg.hidden, D), bias=L["s_o_b"], residual=h, out=h)
+            K.layernorm(h, L["n2_w"], L["n2_b"], cfg.eps, out=hn)
+            K.gemm(hn, L["c_q_w"], packed_shape=(D, cfg.hidden), bias=L["c_q_b"], out=q)
+            K.attention_prefill(q, att, Hq=cfg.heads, Hkv=cfg.heads, hd=self.hd_pad, q_start=m["q_start"], q_len=m["q_len"],
+                                kv_len=m["kv_mem"], max_q_len=P, k=kv[:, :D], v=kv[:, D:], kv_start=m["kv_start_step"][k],
+                                causal=False, scale=scale, status=self.status)
+            K.gemm(att, L["c_o_w"], packed_shape=(cfg.hidden, D), bias=L["c_o_b"], residual=h, out=h)
+            K.layernorm(h, L["n3_w"], L["n3_b"], cfg.eps, out=hn)
+            K.gemm(hn, L["ff1_w"], packed_shape=(cfg.ff, cfg.hidden), bias=L["ff1_b"], act="gelu_erf", out=ff)
+            K.gemm(ff, L["ff2_w"], packed_shape=(cfg.hidden, cfg.ff), bias=L["ff2_b"], residual=h, out=h)
+
+    def _loop(self, b: int) -> None:
+        cfg, K = self.cfg, self.K
+        R = b * cfg.predict_size
+        for L, kv in zip(self.layers, self.mem_kv):       # the memory of all steps through every layer's K/V projection
+            K.gemm(self.mem, L["c_kv_w"], packed_shape=(2 * self.D, cfg.hidden), bias=L["c_kv_b"], out=kv)
+        x, eps, x0 = self.x[:R], self.eps[:R], self.x0[:R]
+        for k in range(cfg.steps):
+            K.gemm(x, self.ie_w, bias=self.ie_b, residual=self.out_pos[:R], out=self.h[:R])
+            self._decoder(b, k)
+            K.layernorm(self.h[:R], self.ln_w, self.ln_b, cfg.eps, out=self.hn[:R])
+            K.gemm(self.hn[:R], self.ah_w, bias=self.ah_b, out=eps)
+            A, B, C, D = self.coeff[k]
+            torch.add(x * A, eps, alpha=B, out=x0)
+            x0.clamp_(-1.0, 1.0)
+            x.mul_(D).add_(x0, alpha=C).add_(self.sigz[k, :R])
+
+    @torch.no_grad()
+    def predict_action(self, goal_embed: torch.Tensor, rgbd_embed: torch.Tensor, init_noise: torch.Tensor,
+                       step_noise: Optional[torch.Tensor] = None, *, seed: int = 0, use_graph: bool = True) -> torch.Tensor:
+        """``goal_embed [1, 1, H]``, ``rgbd_embed [1, memory_len - 2, H]``, ``init_noise [B, predict_size, action_dim]``;
+        ``step_noise [steps, B, predict_size, action_dim]`` unit-normal (drawn from ``seed`` when absent) ->
+        ``[B, predict_size, action_dim]`` fp32 on the host side's device of choice (a fresh tensor)."""
+        cfg, dev = self.cfg, self.device
+        b, P, A = init_noise.shape[0], cfg.predict_size, cfg.action_dim
+        if b > self.B or tuple(init_noise.shape[1:]) != (P, A):
+            raise ValueError(f"init_noise must be [<= {self.B}, {P}, {A}], got {tuple(init_noise.shape)}")
+        if step_noise is None:
+            step_noise = torch.randn(cfg.steps, b, P, A, generator=torch.Generator().manual_seed(seed))
+        R = b * P
+        mem = memory_rows(self._sd_small, cfg, self.ts, goal_embed.to(dev), rgbd_embed.to(dev))
+        self.mem.copy_(mem.reshape(-1, cfg.hidden).to(self.dtype))
+        self.x.zero_()
+        self.x[:R, :A].copy_(init_noise.reshape(R, A).to(dev, self.dtype))
+        self.sigz.zero_()
+        self.sigz[:, :R, :A].copy_((step_noise.float() * self.sigma[:, None, None, None]).reshape(cfg.steps, R, A).to(dev, self.dtype))
+        if not use_graph:
+            self._loop(b)
+        else:
+            gph = self._graphs.get(b)
+            if gph is None:
+                snap = self.x.clone()
+                s = torch.cuda.Stream()
+                s.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(s):
+                    self._loop(b)                                    # warm-up: load kernels, set attributes
+                torch.cuda.current_stream().wait_stream(s)
+                self.x.copy_(snap)
+                gph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gph, stream=s):
+                    self._loop(b)
+                torch.cuda.synchronize()
+                self.x.copy_(snap)
+                self._graphs[b] = gph
+            gph.replay()
+        return self.x[:R, :A].float().reshape(b, P, A).clone()
+
+    @torch.no_grad()
+    def predict_noise(self, last_actions: torch.Tensor, step_index: int, goal_embed: torch.Tensor, rgbd_embed: torch.Tensor) -> torch.Tensor:
+        """One decoder pass at schedule position ``step_index`` -> ``eps [B, predict_size, action_dim]`` fp32 on the host."""
+        cfg, dev, K = self.cfg, self.device, self.K
+        b, P, A = last_actions.shape[0], cfg.predict_size, cfg.action_dim
+        if b > self.B or tuple(last_actions.shape[1:]) != (P, A):
+            raise ValueError(f"last_actions must be [<= {self.B}, {P}, {A}], got {tuple(last_actions.shape)}")
+        R, M, k = b * P, cfg.memory_len, int(step_index)
+        mem = memory_rows(self._sd_small, cfg, [self.ts[k]], goal_embed.to(dev), rgbd_embed.to(dev))
+        self.mem[k * M:(k + 1) * M].copy_(mem.reshape(M, cfg.hidden).to(self.dtype))
+        for L, kv in zip(self.layers, self.mem_kv):
+            K.gemm(self.mem[k * M:(k + 1) * M], L["c_kv_w"], packed_shape=(2 * self.D, cfg.hidden), bias=L["c_kv_b"], out=kv[k * M:(k + 1) * M])
+        self.x.zero_()
+        self.x[:R, :A].copy_(last_actions.reshape(R, A).to(dev, self.dtype))
+        K.gemm(self.x[:R], self.ie_w, bias=self.ie_b, residual=self.out_pos[:R], out=self.h[:R])
+        self._decoder(b, k)
+        K.layernorm(self.h[:R], self.ln_w, self.ln_b, cfg.eps, out=self.hn[:R])
+        K.gemm(self.hn[:R], self.ah_w, bias=self.ah_b, out=self.eps[:R])
+        return self.eps[:R, :A].float().reshape(b, P, A).cpu()
+
+    def check_status(self) -> None:
+        torch.cuda.synchronize()
+        st = self.status.tolist()
+        if st[0] != 0:
+            from ..runtime.errors import RPUBackendError
+            raise RPUBackendError(f"device status {st[:4]} (code, block, kernel, detail)")
+
+    def close(self) -> None:
+        self._graphs.clear()
+
+
+__all__ = ["NavdpConfig", "NavdpEngine", "TorchNavdp", "tiny_navdp_config", "navdp_shapes", "random_navdp_state_dict",
+           "check_state_dict", "ddpm_tables", "memory_rows", "sinusoidal_time_embedding"]
