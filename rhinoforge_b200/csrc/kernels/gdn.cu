@@ -5,6 +5,7 @@
 //     steps with the state held in registers, written back once),
 //   * RMSNorm over Dv gated by silu(z),
 //   * sigmoid output gate of the full-attention layers,
+//   * the same rule in its chunked (block-parallel) form for prefill: 64 tokens per step as TF32 tensor-core products,
 //   * last-dim cumulative sum and (I - M)^-1 of strictly-lower-triangular blocks, the two
 //     helper operators of the chunked formulation.
 // Semantics follow src/ops/rpu_gdn_recurrent.cpp:1-120 (decode step), src/ops/rpu_fla_conv1d.cpp,
@@ -198,6 +199,311 @@ gdn_recurrent_kernel(const RfGdn p) {
   for (int r = 0; r < RPT; ++r) S[(size_t)(rg * RPT + r) * p.Dv + j] = st[r];
 }
 
+// ------------------------------------------------ chunked delta rule (prefill) ----
+// The same recurrence evaluated 64 tokens at a time on the tensor cores.  With G_i the cumulative log decay inside a
+// chunk, S0 the incoming state and L_ij = beta_i e^{G_i - G_j} (k_i . k_j) for j < i:
+//     (I + L) U = beta * (V - e^G * (K S0))
+//     O  = e^G * (Q S0) + tril(e^{G_i - G_j} (q_i . k_j)) U
+//     S' = e^{G_C} S0 + K^T (e^{G_C - G} * U)
+// One CTA owns 32 state columns of one value head of one sequence (the same split as the recurrent kernel) and walks
+// the sequence's chunks with its [128 x 32] state slice resident in shared memory.  Every product is an fp32-accumulate
+// TF32 mma.sync (operands rounded to nearest): the state stays fp32 between chunks, and every decay factor that appears
+// is e^{G_i - G_j} with j <= i, at most one.  The unit-triangular system is solved in 16-row blocks: the four diagonal
+// blocks are inverted by forward substitution (one warp each), the rest is block forward substitution on the 32
+// right-hand-side columns.  Rows past the end of a sequence are zero tokens with beta = 0 and no decay, which leave both
+// the outputs of the real rows and the state untouched.
+constexpr int kGcC = 64;          // tokens per chunk
+constexpr int kGcThreads = 256;
+constexpr int kGcLdQK = 132;      // fp32 row pitch of the q / k tiles: (4 * row + col) mod 32 is distinct over a fragment
+constexpr int kGcLdS = 40;        // row pitch of the state slice and of the v / rhs / u tile
+constexpr int kGcLdL = 68;        // row pitch of the two chunk x chunk matrices
+constexpr int kGcLdD = 17;
+constexpr int kGcSmemFloats = 2 * kGcC * kGcLdQK + 128 * kGcLdS + kGcC * kGcLdS + 2 * kGcC * kGcLdL + 4 * 16 * kGcLdD + 3 * kGcC;
+
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// A fragment of a row-major fp32 tile: rows r0 + {g, g + 8}, columns c0 + {t, t + 4}
+__device__ __forceinline__ void frag_a(uint32_t (&a)[4], const float* m, int ld, int r0, int c0, int g, int t) {
+  a[0] = to_tf32(m[(r0 + g) * ld + c0 + t]);
+  a[1] = to_tf32(m[(r0 + g + 8) * ld + c0 + t]);
+  a[2] = to_tf32(m[(r0 + g) * ld + c0 + t + 4]);
+  a[3] = to_tf32(m[(r0 + g + 8) * ld + c0 + t + 4]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kGcThreads, 1)
+gdn_chunked_kernel(const RfGdn p) {
+  pdl_prologue();
+  constexpr int DK = 128, C = kGcC, NV = kGdnCols;
+  extern __shared__ __align__(16) float gsm[];
+  float* sQ = gsm;
+  float* sK = sQ + C * kGcLdQK;
+  float* sS = sK + C * kGcLdQK;
+  float* sV = sS + DK * kGcLdS;
+  float* sL = sV + C * kGcLdS;
+  float* sP = sL + C * kGcLdL;
+  float* sD = sP + C * kGcLdL;
+  float* sG = sD + 4 * 16 * kGcLdD;
+  float* sBeta = sG + C;
+  float* sg = sBeta + C;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int seq = blockIdx.z, hv = blockIdx.y, j0 = blockIdx.x * NV;
+  const int hk = hv / (p.Hv / p.Hk);
+  const int s0 = p.q_start ? p.q_start[seq] : seq;
+  const int n = p.q_len ? p.q_len[seq] : 1;
+  const int sl = p.slot ? p.slot[seq] : seq;
+  const int fresh = p.fresh ? p.fresh[seq] : 0;
+  float* S = p.state + (((size_t)sl * p.Hv + hv) * DK) * p.Dv + j0;
+  const T* qkv = reinterpret_cast<const T*>(p.qkv);
+  const T* bp = reinterpret_cast<const T*>(p.b);
+  const T* ap = reinterpret_cast<const T*>(p.a);
+  T* out = reinterpret_cast<T*>(p.out);
+  const int q_off = hk * DK, k_off = p.Hk * DK + hk * DK, v_off = 2 * p.Hk * DK + hv * p.Dv + j0;
+  const float A = -__expf(p.A_log[hv]), dtb = p.dt_bias[hv];
+  const float qscale = rsqrtf((float)DK);
+
+  for (int i = tid; i < DK * NV; i += kGcThreads) {
+    const int m = i / NV, c = i % NV;
+    sS[m * kGcLdS + c] = fresh ? 0.f : S[(size_t)m * p.Dv + c];
+  }
+
+  for (int c0 = 0; c0 < n; c0 += C) {
+    // ---- load: L2-normalised q (pre-scaled) and k, the v slice, beta and the log decay of 64 tokens
+    for (int rr = 0; rr < 8; ++rr) {
+      const int i = warp * 8 + rr;
+      const bool valid = c0 + i < n;
+      const size_t row = (size_t)(s0 + c0 + i);
+      const int half = lane >> 4, l16 = lane & 15;
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+      if (valid) load8(qkv + row * p.ld + (half ? k_off : q_off) + l16 * 8, f);
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float sc = rsqrtf(ss + 1e-6f) * (half ? 1.f : qscale);
+      float* dst = (half ? sK : sQ) + i * kGcLdQK + l16 * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dst[e] = f[e] * sc;
+      if (lane < NV / 8) {
+        float vv[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) vv[e] = 0.f;
+        if (valid) load8(qkv + row * p.ld + v_off + lane * 8, vv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sV[i * kGcLdS + lane * 8 + e] = vv[e];
+      }
+      if (lane == 31) {
+        float beta = 0.f, lg = 0.f;
+        if (valid) {
+          beta = 1.f / (1.f + __expf(-Num<T>::to_f(bp[row * p.ld_ba + hv])));
+          const float ar = Num<T>::to_f(ap[row * p.ld_ba + hv]) + dtb;
+          lg = A * (ar > 20.f ? ar : log1pf(__expf(ar)));
+        }
+        sBeta[i] = beta;
+        sg[i] = lg;
+      }
+    }
+    __syncthreads();
+    if (warp == 0) {      // inclusive prefix sum of the log decays
+      const float x0 = sg[2 * lane], x1 = sg[2 * lane + 1];
+      float run = x0 + x1;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float y = __shfl_up_sync(0xffffffffu, run, o);
+        if (lane >= o) run += y;
+      }
+      sG[2 * lane] = run - x1;
+      sG[2 * lane + 1] = run;
+    }
+    __syncthreads();
+
+    // ---- L = beta_i e^{G_i - G_j} (k_i . k_j) [j < i],  P = e^{G_i - G_j} (q_i . k_j) [j <= i]
+    {
+      const int rt = warp >> 1, cnt = rt + 1, nt0 = (warp & 1) * cnt;   // row tile rt has 2 (rt + 1) column tiles on or below the diagonal
+      float accL[4][4], accP[4][4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) accL[a][b] = accP[a][b] = 0.f;
+      for (int ks = 0; ks < DK / 8; ++ks) {
+        uint32_t aK[4], aQ[4];
+        frag_a(aK, sK, kGcLdQK, rt * 16, ks * 8, g, t);
+        frag_a(aQ, sQ, kGcLdQK, rt * 16, ks * 8, g, t);
+#pragma unroll
+        for (int ti = 0; ti < 4; ++ti) {
+          if (ti < cnt) {
+            const int col = (nt0 + ti) * 8 + g;
+            uint32_t b[2];
+            b[0] = to_tf32(sK[col * kGcLdQK + ks * 8 + t]);
+            b[1] = to_tf32(sK[col * kGcLdQK + ks * 8 + t + 4]);
+            mma_tf32(accL[ti], aK, b);
+            mma_tf32(accP[ti], aQ, b);
+          }
+        }
+      }
+#pragma unroll
+      for (int ti = 0; ti < 4; ++ti) {
+        if (ti < cnt) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = rt * 16 + g + (e >> 1) * 8, j = (nt0 + ti) * 8 + 2 * t + (e & 1);
+            const float dec = j <= i ? __expf(sG[i] - sG[j]) : 0.f;
+            sL[i * kGcLdL + j] = j < i ? sBeta[i] * dec * accL[ti][e] : 0.f;
+            sP[i * kGcLdL + j] = dec * accP[ti][e];
+          }
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- inverses of the four 16 x 16 diagonal blocks of I + L (warps 0..3, one column per lane)
+    if (warp < 4 && lane < 16) {
+      float x[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float acc = i == lane ? 1.f : 0.f;
+#pragma unroll
+        for (int j = 0; j < i; ++j) acc -= sL[(warp * 16 + i) * kGcLdL + warp * 16 + j] * x[j];
+        x[i] = acc;
+        sD[(warp * 16 + i) * kGcLdD + lane] = acc;
+      }
+    }
+
+    // ---- rhs = beta (V - e^G (K S0)) in place of V;  accO = e^G (Q S0)
+    const int rt = warp & 3, nh = warp >> 2;
+    float accO[2][4];
+    {
+      float accR[2][4];
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) accR[a][b] = accO[a][b] = 0.f;
+      for (int ks = 0; ks < DK / 8; ++ks) {
+        uint32_t aK[4], aQ[4];
+        frag_a(aK, sK, kGcLdQK, rt * 16, ks * 8, g, t);
+        frag_a(aQ, sQ, kGcLdQK, rt * 16, ks * 8, g, t);
+#pragma unroll
+        for (int a = 0; a < 2; ++a) {
+          const int col = (nh * 2 + a) * 8 + g;
+          uint32_t b[2];
+          b[0] = to_tf32(sS[(ks * 8 + t) * kGcLdS + col]);
+          b[1] = to_tf32(sS[(ks * 8 + t + 4) * kGcLdS + col]);
+          mma_tf32(accR[a], aK, b);
+          mma_tf32(accO[a], aQ, b);
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = rt * 16 + g + (e >> 1) * 8, j = (nh * 2 + a) * 8 + 2 * t + (e & 1);
+          const float eg = __expf(sG[i]);
+          sV[i * kGcLdS + j] = sBeta[i] * (sV[i * kGcLdS + j] - eg * accR[a][e]);
+          accO[a][e] *= eg;
+        }
+    }
+    __syncthreads();
+
+    // ---- U = (I + L)^-1 rhs by block forward substitution, in place
+    {
+      const int r = tid >> 4, cc = (tid & 15) * 2;
+      for (int b = 0; b < 4; ++b) {
+        const int i = b * 16 + r;
+        float a0 = sV[i * kGcLdS + cc], a1 = sV[i * kGcLdS + cc + 1];
+        for (int j = 0; j < b * 16; ++j) {
+          const float l = sL[i * kGcLdL + j];
+          a0 -= l * sV[j * kGcLdS + cc];
+          a1 -= l * sV[j * kGcLdS + cc + 1];
+        }
+        sV[i * kGcLdS + cc] = a0;          // rows of block b: read only by their owners until the barrier
+        sV[i * kGcLdS + cc + 1] = a1;
+        __syncthreads();
+        float u0 = 0.f, u1 = 0.f;
+        for (int r2 = 0; r2 <= r; ++r2) {
+          const float d = sD[i * kGcLdD + r2];
+          u0 += d * sV[(b * 16 + r2) * kGcLdS + cc];
+          u1 += d * sV[(b * 16 + r2) * kGcLdS + cc + 1];
+        }
+        __syncthreads();
+        sV[i * kGcLdS + cc] = u0;
+        sV[i * kGcLdS + cc + 1] = u1;
+        __syncthreads();
+      }
+    }
+
+    // ---- O = accO + P U
+    for (int ks = 0; ks <= 2 * rt + 1; ++ks) {
+      uint32_t aP[4];
+      frag_a(aP, sP, kGcLdL, rt * 16, ks * 8, g, t);
+#pragma unroll
+      for (int a = 0; a < 2; ++a) {
+        const int col = (nh * 2 + a) * 8 + g;
+        uint32_t b[2];
+        b[0] = to_tf32(sV[(ks * 8 + t) * kGcLdS + col]);
+        b[1] = to_tf32(sV[(ks * 8 + t + 4) * kGcLdS + col]);
+        mma_tf32(accO[a], aP, b);
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = rt * 16 + g + (e >> 1) * 8, j = (nh * 2 + a) * 8 + 2 * t + (e & 1);
+        if (c0 + i < n) out[(size_t)(s0 + c0 + i) * p.ldo + hv * p.Dv + j0 + j] = Num<T>::from_f(accO[a][e]);
+      }
+
+    // ---- S' = e^{G_C} S0 + K^T (e^{G_C - G} * U): warp w owns state rows 16 w .. 16 w + 15
+    {
+      const float gl = sG[C - 1], egl = __expf(gl);
+      float accS[4][4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          accS[a][e] = egl * sS[(warp * 16 + g + (e >> 1) * 8) * kGcLdS + a * 8 + 2 * t + (e & 1)];
+      for (int ks = 0; ks < C / 8; ++ks) {
+        const int ca = ks * 8 + t, cb = ks * 8 + t + 4;
+        uint32_t aT[4];
+        aT[0] = to_tf32(sK[ca * kGcLdQK + warp * 16 + g]);
+        aT[1] = to_tf32(sK[ca * kGcLdQK + warp * 16 + g + 8]);
+        aT[2] = to_tf32(sK[cb * kGcLdQK + warp * 16 + g]);
+        aT[3] = to_tf32(sK[cb * kGcLdQK + warp * 16 + g + 8]);
+        const float wa = __expf(gl - sG[ca]), wb = __expf(gl - sG[cb]);
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          uint32_t b[2];
+          b[0] = to_tf32(wa * sV[ca * kGcLdS + a * 8 + g]);
+          b[1] = to_tf32(wb * sV[cb * kGcLdS + a * 8 + g]);
+          mma_tf32(accS[a], aT, b);
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          sS[(warp * 16 + g + (e >> 1) * 8) * kGcLdS + a * 8 + 2 * t + (e & 1)] = accS[a][e];
+    }
+    __syncthreads();
+  }
+
+  for (int i = tid; i < DK * NV; i += kGcThreads) {
+    const int m = i / NV, c = i % NV;
+    S[(size_t)m * p.Dv + c] = sS[m * kGcLdS + c];
+  }
+}
+
 // ------------------------------------------------- gated RMSNorm over Dv ----
 // y = (w * rmsnorm(x)) * silu(z); one warp per (token, head) row of D <= 256 values.
 template <typename T>
@@ -334,6 +640,27 @@ extern "C" int rf_gdn_recurrent(const RfGdn* a, rf_stream_t stream) {
   const dim3 grid(a->Dv / kGdnCols, a->Hv, a->num_seqs);
   if (a->dtype == 0) RF_CUDA_CHECK(::rf::launch_k(gdn_recurrent_kernel<__half, 128>, grid, dim3(kGdnThreads), 0, s, 1, *a));
   else RF_CUDA_CHECK(::rf::launch_k(gdn_recurrent_kernel<__nv_bfloat16, 128>, grid, dim3(kGdnThreads), 0, s, 1, *a));
+  ::rf::count_launch();
+  return RF_OK;
+}
+
+extern "C" int rf_gdn_chunked(const RfGdn* a, rf_stream_t stream) {
+  RF_SKIP_IF_REPLAYING();
+  RF_REQUIRE(a && a->qkv && a->b && a->a && a->out && a->state && a->A_log && a->dt_bias, "gdn: null argument");
+  RF_REQUIRE(a->Dk == 128, "gdn: key head dim %d (only 128 is built)", a->Dk);
+  RF_REQUIRE(a->Dv % kGdnCols == 0 && a->Hv % a->Hk == 0 && a->Hk > 0, "gdn: head geometry Hk=%d Hv=%d Dv=%d", a->Hk, a->Hv, a->Dv);
+  RF_REQUIRE(a->ld % 8 == 0 && (a->Hk * a->Dk) % 8 == 0 && a->Dv % 8 == 0, "gdn: the chunked form reads 16-byte vectors (pitch %lld)", (long long)a->ld);
+  RF_REQUIRE(a->num_seqs > 0, "gdn: no sequences");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(a->Dv / kGdnCols, a->Hv, a->num_seqs);
+  constexpr size_t smem = (size_t)kGcSmemFloats * sizeof(float);
+  if (a->dtype == 0) {
+    RF_ALLOW_SMEM_PER_DEVICE(gdn_chunked_kernel<__half>, smem);
+    RF_CUDA_CHECK(::rf::launch_k(gdn_chunked_kernel<__half>, grid, dim3(kGcThreads), smem, s, 1, *a));
+  } else {
+    RF_ALLOW_SMEM_PER_DEVICE(gdn_chunked_kernel<__nv_bfloat16>, smem);
+    RF_CUDA_CHECK(::rf::launch_k(gdn_chunked_kernel<__nv_bfloat16>, grid, dim3(kGcThreads), smem, s, 1, *a));
+  }
   ::rf::count_launch();
   return RF_OK;
 }

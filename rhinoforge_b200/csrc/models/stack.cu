@@ -126,6 +126,17 @@ static bool tp_publish_enabled() {
 // L2 prefetch hint for the next linear() call on this thread (set by the layer loop right before the call, consumed
 // by it): the weights of the linear layer that FOLLOWS, so that a weight-streaming GEMM hands HBM over to its
 // successor without an idle gap.  RF_GEMM_L2_PREFETCH_MB caps the bytes asked for (0: off).
+// Shortest prefill (longest new-token run of the launch) that takes the chunked Gated-DeltaNet kernel; RF_GDN_CHUNK_MIN
+// overrides it (0 keeps every prefill on the recurrent kernel).
+static int gdn_chunk_min() {
+  static const int v = [] {
+    const char* e = getenv("RF_GDN_CHUNK_MIN");
+    const int n = e ? atoi(e) : 16;
+    return n <= 0 ? (1 << 30) : n;
+  }();
+  return v;
+}
+
 static thread_local const void* t_pf_ptr = nullptr;
 static thread_local uint64_t t_pf_bytes = 0;
 static uint64_t prefetch_cap_bytes() {
@@ -387,7 +398,8 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
       g.ld_ba = IN; g.out = attn; g.ldo = VD; g.state = w.gdn_rec_state; g.A_log = w.gdn_A_log; g.dt_bias = w.gdn_dt_bias;
       g.q_start = cv.q_start; g.q_len = cv.q_len; g.slot = f.state_slot; g.fresh = f.state_fresh;
       g.num_seqs = f.num_seqs; g.Hk = c.gdn_Hk; g.Hv = c.gdn_Hv; g.Dk = c.gdn_Dk; g.Dv = c.gdn_Dv; g.dtype = c.dtype;
-      rc = rf_gdn_recurrent(&g, st);
+      // prefill walks 64 tokens per step on the tensor cores; decode and very short inputs take the recurrent kernel
+      rc = (!f.decode && f.max_q_len >= gdn_chunk_min()) ? rf_gdn_chunked(&g, st) : rf_gdn_recurrent(&g, st);
       if (rc) return rc;
       // gated RMSNorm over Dv: the conv buffer is free again and takes the result
       rc = rf_rmsnorm_gated(attn, VD, (const uint8_t*)wide + (size_t)CD * esz, IN, w.gdn_norm_w, conv, VD, T, c.gdn_Hv,

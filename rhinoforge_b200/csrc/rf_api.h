@@ -278,6 +278,8 @@ typedef struct RfGdn {
   int32_t num_seqs, Hk, Hv, Dk, Dv, dtype;
 } RfGdn;
 int rf_gdn_recurrent(const RfGdn* a, rf_stream_t stream);
+// Same contract, evaluated 64 tokens at a time on the tensor cores (prefill; decode keeps the recurrent kernel).
+int rf_gdn_chunked(const RfGdn* a, rf_stream_t stream);
 // y[t, h, :] = (w * rmsnorm(x[t, h, :])) * silu(z[t, h, :]), D values per (token, head)
 int rf_rmsnorm_gated(const void* x, int64_t ldx, const void* z, int64_t ldz, const void* w, void* y, int64_t ldy,
                      int tokens, int heads, int D, float eps, int dtype, rf_stream_t stream);

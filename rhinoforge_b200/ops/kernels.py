@@ -483,9 +483,10 @@ def gdn_recurrent(qkv: torch.Tensor, b: torch.Tensor, a_: torch.Tensor, state: t
                   dt_bias: torch.Tensor, *, Hk: int, Hv: int, Dk: int, Dv: int, q_start: Optional[torch.Tensor] = None,
                   q_len: Optional[torch.Tensor] = None, slot: Optional[torch.Tensor] = None,
                   fresh: Optional[torch.Tensor] = None, num_seqs: Optional[int] = None,
-                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  out: Optional[torch.Tensor] = None, chunked: bool = False) -> torch.Tensor:
     """Gated delta rule; ``qkv [T, 2*Hk*Dk + Hv*Dv]``, ``b``/``a_`` ``[T, >=Hv]`` views with a common pitch,
-    ``state`` fp32 ``[slots, Hv, Dk, Dv]`` (updated in place).  Returns ``[T, Hv*Dv]``."""
+    ``state`` fp32 ``[slots, Hv, Dk, Dv]`` (updated in place).  Returns ``[T, Hv*Dv]``.  ``chunked``: the block-parallel
+    form (64 tokens per step on the tensor cores) instead of the token-by-token kernel; same contract."""
     assert state.dtype == torch.float32 and A_log.dtype == torch.float32 and dt_bias.dtype == torch.float32
     assert b.stride(0) == a_.stride(0)
     g = N.RfGdn()
@@ -498,7 +499,10 @@ def gdn_recurrent(qkv: torch.Tensor, b: torch.Tensor, a_: torch.Tensor, state: t
     g.q_start, g.q_len, g.slot, g.fresh = _i32(q_start), _i32(q_len), _i32(slot), _i32(fresh)
     g.num_seqs = int(num_seqs if num_seqs is not None else (q_len.numel() if q_len is not None else qkv.shape[0]))
     g.Hk, g.Hv, g.Dk, g.Dv, g.dtype = Hk, Hv, Dk, Dv, dtype_code(qkv.dtype)
-    N.check(N.lib().rf_gdn_recurrent(C.byref(g), _stream()), "rf_gdn_recurrent")
+    if chunked:
+        N.check(N.lib().rf_gdn_chunked(C.byref(g), _stream()), "rf_gdn_chunked")
+    else:
+        N.check(N.lib().rf_gdn_recurrent(C.byref(g), _stream()), "rf_gdn_recurrent")
     return out
 
 
