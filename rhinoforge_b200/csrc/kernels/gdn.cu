@@ -219,6 +219,17 @@ constexpr int kGcLdS = 40;        // row pitch of the state slice and of the v /
 constexpr int kGcLdL = 68;        // row pitch of the two chunk x chunk matrices
 constexpr int kGcLdD = 17;
 constexpr int kGcSmemFloats = 2 * kGcC * kGcLdQK + 128 * kGcLdS + kGcC * kGcLdS + 2 * kGcC * kGcLdL + 4 * 16 * kGcLdD + 3 * kGcC;
+// + the raw 16-bit q | k rows and v slice of the NEXT chunk, fetched with cp.async while this chunk is computed
+constexpr int kGcRawElems = kGcC * 256 + kGcC * kGdnCols;
+constexpr size_t kGcSmemBytes = (size_t)kGcSmemFloats * sizeof(float) + (size_t)kGcRawElems * 2;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  const int n = valid ? 16 : 0;                      // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t to_tf32(float x) {
   uint32_t r;
@@ -238,6 +249,14 @@ __device__ __forceinline__ void frag_a(uint32_t (&a)[4], const float* m, int ld,
   a[3] = to_tf32(m[(r0 + g + 8) * ld + c0 + t + 4]);
 }
 
+// the same for a tile whose values were rounded to TF32 when they were stored
+__device__ __forceinline__ void frag_a_bits(uint32_t (&a)[4], const float* m, int ld, int r0, int c0, int g, int t) {
+  a[0] = __float_as_uint(m[(r0 + g) * ld + c0 + t]);
+  a[1] = __float_as_uint(m[(r0 + g + 8) * ld + c0 + t]);
+  a[2] = __float_as_uint(m[(r0 + g) * ld + c0 + t + 4]);
+  a[3] = __float_as_uint(m[(r0 + g + 8) * ld + c0 + t + 4]);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kGcThreads, 1)
 gdn_chunked_kernel(const RfGdn p) {
@@ -254,6 +273,8 @@ gdn_chunked_kernel(const RfGdn p) {
   float* sG = sD + 4 * 16 * kGcLdD;
   float* sBeta = sG + C;
   float* sg = sBeta + C;
+  T* rawQK = reinterpret_cast<T*>(sg + C);             // [C][q 128 | k 128]
+  T* rawV = rawQK + C * 256;                           // [C][32]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int seq = blockIdx.z, hv = blockIdx.y, j0 = blockIdx.x * NV;
@@ -276,17 +297,42 @@ gdn_chunked_kernel(const RfGdn p) {
     sS[m * kGcLdS + c] = fresh ? 0.f : S[(size_t)m * p.Dv + c];
   }
 
+  float nb = 0.f, na = 0.f;                            // beta / decay inputs of row `tid` of the chunk in flight
+  auto prefetch = [&](int cn) {
+    if (cn < n) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int idx = tid + kGcThreads * k, i = idx >> 5, part = idx & 31;
+        const bool valid = cn + i < n;
+        const size_t row = (size_t)(s0 + (valid ? cn + i : 0));
+        cp_async16(rawQK + i * 256 + part * 8, qkv + row * p.ld + (part < 16 ? q_off + part * 8 : k_off + (part - 16) * 8), valid);
+      }
+      {
+        const int i = tid >> 2, part = tid & 3;
+        const bool valid = cn + i < n;
+        const size_t row = (size_t)(s0 + (valid ? cn + i : 0));
+        cp_async16(rawV + i * NV + part * 8, qkv + row * p.ld + v_off + part * 8, valid);
+      }
+      if (tid < C && cn + tid < n) {
+        const size_t row = (size_t)(s0 + cn + tid);
+        nb = Num<T>::to_f(bp[row * p.ld_ba + hv]);
+        na = Num<T>::to_f(ap[row * p.ld_ba + hv]);
+      }
+    }
+    cp_async_commit();
+  };
+  prefetch(0);
+
   for (int c0 = 0; c0 < n; c0 += C) {
-    // ---- load: L2-normalised q (pre-scaled) and k, the v slice, beta and the log decay of 64 tokens
+    // ---- this chunk's rows arrived through cp.async: L2-normalise q (pre-scaled) and k, widen the v slice
+    cp_async_wait_all();
+    __syncthreads();
+#pragma unroll
     for (int rr = 0; rr < 8; ++rr) {
       const int i = warp * 8 + rr;
-      const bool valid = c0 + i < n;
-      const size_t row = (size_t)(s0 + c0 + i);
       const int half = lane >> 4, l16 = lane & 15;
       float f[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = 0.f;
-      if (valid) load8(qkv + row * p.ld + (half ? k_off : q_off) + l16 * 8, f);
+      load8(rawQK + i * 256 + half * 128 + l16 * 8, f);
       float ss = 0.f;
 #pragma unroll
       for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
@@ -295,27 +341,27 @@ gdn_chunked_kernel(const RfGdn p) {
       const float sc = rsqrtf(ss + 1e-6f) * (half ? 1.f : qscale);
       float* dst = (half ? sK : sQ) + i * kGcLdQK + l16 * 8;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) dst[e] = f[e] * sc;
-      if (lane < NV / 8) {
-        float vv[8];
+      for (int e = 0; e < 8; ++e) dst[e] = __uint_as_float(to_tf32(f[e] * sc));   // rounded once here, read as TF32 bits below
+    }
+    {
+      const int i = tid >> 2, part = tid & 3;
+      float vv[8];
+      load8(rawV + i * NV + part * 8, vv);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) vv[e] = 0.f;
-        if (valid) load8(qkv + row * p.ld + v_off + lane * 8, vv);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) sV[i * kGcLdS + lane * 8 + e] = vv[e];
+      for (int e = 0; e < 8; ++e) sV[i * kGcLdS + part * 8 + e] = vv[e];
+    }
+    if (tid < C) {
+      float beta = 0.f, lg = 0.f;
+      if (c0 + tid < n) {
+        beta = 1.f / (1.f + __expf(-nb));
+        const float ar = na + dtb;
+        lg = A * (ar > 20.f ? ar : log1pf(__expf(ar)));
       }
-      if (lane == 31) {
-        float beta = 0.f, lg = 0.f;
-        if (valid) {
-          beta = 1.f / (1.f + __expf(-Num<T>::to_f(bp[row * p.ld_ba + hv])));
-          const float ar = Num<T>::to_f(ap[row * p.ld_ba + hv]) + dtb;
-          lg = A * (ar > 20.f ? ar : log1pf(__expf(ar)));
-        }
-        sBeta[i] = beta;
-        sg[i] = lg;
-      }
+      sBeta[tid] = beta;
+      sg[tid] = lg;
     }
     __syncthreads();
+    prefetch(c0 + C);                                  // the raw buffers are free again: fetch the next chunk behind the math
     if (warp == 0) {      // inclusive prefix sum of the log decays
       const float x0 = sg[2 * lane], x1 = sg[2 * lane + 1];
       float run = x0 + x1;
@@ -339,15 +385,15 @@ gdn_chunked_kernel(const RfGdn p) {
         for (int b = 0; b < 4; ++b) accL[a][b] = accP[a][b] = 0.f;
       for (int ks = 0; ks < DK / 8; ++ks) {
         uint32_t aK[4], aQ[4];
-        frag_a(aK, sK, kGcLdQK, rt * 16, ks * 8, g, t);
-        frag_a(aQ, sQ, kGcLdQK, rt * 16, ks * 8, g, t);
+        frag_a_bits(aK, sK, kGcLdQK, rt * 16, ks * 8, g, t);
+        frag_a_bits(aQ, sQ, kGcLdQK, rt * 16, ks * 8, g, t);
 #pragma unroll
         for (int ti = 0; ti < 4; ++ti) {
           if (ti < cnt) {
             const int col = (nt0 + ti) * 8 + g;
             uint32_t b[2];
-            b[0] = to_tf32(sK[col * kGcLdQK + ks * 8 + t]);
-            b[1] = to_tf32(sK[col * kGcLdQK + ks * 8 + t + 4]);
+            b[0] = __float_as_uint(sK[col * kGcLdQK + ks * 8 + t]);
+            b[1] = __float_as_uint(sK[col * kGcLdQK + ks * 8 + t + 4]);
             mma_tf32(accL[ti], aK, b);
             mma_tf32(accP[ti], aQ, b);
           }
@@ -361,7 +407,7 @@ gdn_chunked_kernel(const RfGdn p) {
             const int i = rt * 16 + g + (e >> 1) * 8, j = (nt0 + ti) * 8 + 2 * t + (e & 1);
             const float dec = j <= i ? __expf(sG[i] - sG[j]) : 0.f;
             sL[i * kGcLdL + j] = j < i ? sBeta[i] * dec * accL[ti][e] : 0.f;
-            sP[i * kGcLdL + j] = dec * accP[ti][e];
+            sP[i * kGcLdL + j] = __uint_as_float(to_tf32(dec * accP[ti][e]));
           }
         }
       }
@@ -392,8 +438,8 @@ gdn_chunked_kernel(const RfGdn p) {
         for (int b = 0; b < 4; ++b) accR[a][b] = accO[a][b] = 0.f;
       for (int ks = 0; ks < DK / 8; ++ks) {
         uint32_t aK[4], aQ[4];
-        frag_a(aK, sK, kGcLdQK, rt * 16, ks * 8, g, t);
-        frag_a(aQ, sQ, kGcLdQK, rt * 16, ks * 8, g, t);
+        frag_a_bits(aK, sK, kGcLdQK, rt * 16, ks * 8, g, t);
+        frag_a_bits(aQ, sQ, kGcLdQK, rt * 16, ks * 8, g, t);
 #pragma unroll
         for (int a = 0; a < 2; ++a) {
           const int col = (nh * 2 + a) * 8 + g;
@@ -446,7 +492,7 @@ gdn_chunked_kernel(const RfGdn p) {
     // ---- O = accO + P U
     for (int ks = 0; ks <= 2 * rt + 1; ++ks) {
       uint32_t aP[4];
-      frag_a(aP, sP, kGcLdL, rt * 16, ks * 8, g, t);
+      frag_a_bits(aP, sP, kGcLdL, rt * 16, ks * 8, g, t);
 #pragma unroll
       for (int a = 0; a < 2; ++a) {
         const int col = (nh * 2 + a) * 8 + g;
@@ -476,10 +522,10 @@ gdn_chunked_kernel(const RfGdn p) {
       for (int ks = 0; ks < C / 8; ++ks) {
         const int ca = ks * 8 + t, cb = ks * 8 + t + 4;
         uint32_t aT[4];
-        aT[0] = to_tf32(sK[ca * kGcLdQK + warp * 16 + g]);
-        aT[1] = to_tf32(sK[ca * kGcLdQK + warp * 16 + g + 8]);
-        aT[2] = to_tf32(sK[cb * kGcLdQK + warp * 16 + g]);
-        aT[3] = to_tf32(sK[cb * kGcLdQK + warp * 16 + g + 8]);
+        aT[0] = __float_as_uint(sK[ca * kGcLdQK + warp * 16 + g]);
+        aT[1] = __float_as_uint(sK[ca * kGcLdQK + warp * 16 + g + 8]);
+        aT[2] = __float_as_uint(sK[cb * kGcLdQK + warp * 16 + g]);
+        aT[3] = __float_as_uint(sK[cb * kGcLdQK + warp * 16 + g + 8]);
         const float wa = __expf(gl - sG[ca]), wb = __expf(gl - sG[cb]);
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
@@ -653,7 +699,7 @@ extern "C" int rf_gdn_chunked(const RfGdn* a, rf_stream_t stream) {
   RF_REQUIRE(a->num_seqs > 0, "gdn: no sequences");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 grid(a->Dv / kGdnCols, a->Hv, a->num_seqs);
-  constexpr size_t smem = (size_t)kGcSmemFloats * sizeof(float);
+  constexpr size_t smem = kGcSmemBytes;
   if (a->dtype == 0) {
     RF_ALLOW_SMEM_PER_DEVICE(gdn_chunked_kernel<__half>, smem);
     RF_CUDA_CHECK(::rf::launch_k(gdn_chunked_kernel<__half>, grid, dim3(kGcThreads), smem, s, 1, *a));

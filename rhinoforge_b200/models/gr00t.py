@@ -149,11 +149,12 @@ def check_state_dict(cfg: Gr00tConfig, get) -> None:
 def timestep_cond(get, cfg: Gr00tConfig, bucket: int) -> torch.Tensor:
     """``silu(timestep_embedder(bucket))`` ``[H]`` fp32: cos-first sinusoid, two linears with a SiLU between."""
     half = cfg.time_embed // 2
-    f = torch.exp(-math.log(10000.0) * torch.arange(half, dtype=torch.float32) / (half - 1))
+    te = AP + "model.timestep_encoder.timestep_embedder."
+    w1 = get(te + "linear_1.weight").float()
+    f = torch.exp(-math.log(10000.0) * torch.arange(half, dtype=torch.float32, device=w1.device) / (half - 1))
     a = float(bucket) * f
     e = torch.cat((a.cos(), a.sin()))[None]
-    te = AP + "model.timestep_encoder.timestep_embedder."
-    h = F.silu(F.linear(e, get(te + "linear_1.weight").float(), get(te + "linear_1.bias").float()))
+    h = F.silu(F.linear(e, w1, get(te + "linear_1.bias").float()))
     return F.silu(F.linear(h, get(te + "linear_2.weight").float(), get(te + "linear_2.bias").float()))[0]
 
 

@@ -67,25 +67,62 @@ class RPUCausalLM:
         return [ids[b] for b in range(ids.shape[0])]
 
     # -- forward -----------------------------------------------------------------------------------
+    @staticmethod
+    def _unpad(ids: torch.Tensor, attention_mask):
+        """Rows of a padded batch without their padding: ``(rows, keep)`` where ``keep[b]`` holds the kept column indices."""
+        if attention_mask is None:
+            return [ids[b] for b in range(ids.shape[0])], None
+        m = torch.as_tensor(attention_mask).to("cpu").bool()
+        if m.shape[-1] > ids.shape[-1]:           # a running mask of prompt + generated tokens: the new columns are the last ones
+            m = m[:, -ids.shape[-1]:]
+        if bool(m.all()):
+            return [ids[b] for b in range(ids.shape[0])], None
+        keep = []
+        for b in range(ids.shape[0]):
+            cols = m[b].nonzero().flatten()
+            if cols.numel() == 0:
+                raise RPUBackendError(f"sequence {b} is all padding")
+            if int(cols[-1] - cols[0]) + 1 != cols.numel():
+                raise RPUBackendError("attention masks with holes are not supported: padding must sit on one side")
+            keep.append(cols)
+        return [ids[b][keep[b].to(ids.device)] for b in range(ids.shape[0])], keep
+
     @torch.no_grad()
     def forward(self, input_ids: torch.Tensor = None, past_key_values=None, attention_mask=None,
                 position_ids=None, logits_to_keep: int = 1, use_cache: bool = True, return_dict: bool = True, **kw):
-        """Append ``input_ids`` at ``past_key_values.position`` and return the logits of the last
-        row of every sequence (``logits_to_keep`` must be 1: the fused head runs on one row per
-        sequence).  An all-ones ``attention_mask`` is accepted; padding masks are not."""
-        if logits_to_keep not in (1, None):
-            raise RPUBackendError("the fused lm_head returns one row per sequence: pass logits_to_keep=1")
-        if attention_mask is not None and not bool(torch.as_tensor(attention_mask).bool().all()):
-            raise RPUBackendError("only all-ones attention masks are supported (equal real lengths)")
+        """Append ``input_ids`` at ``past_key_values.position`` and return logits ``[B, rows, vocab]``:
+        ``logits_to_keep = k > 0`` the last ``k`` rows of every sequence, ``0`` every row.  A padded batch comes with its
+        ``attention_mask`` (padding on one side): the padding columns are dropped before the launch - the engine packs
+        sequences of unequal length - and their logits rows read zero."""
+        k = 1 if logits_to_keep is None else int(logits_to_keep)
+        if k < 0:
+            raise RPUBackendError("logits_to_keep must be 0 (all rows) or a positive row count")
         self._bind(past_key_values)
-        rows = self._rows(input_ids)
+        ids = input_ids if input_ids.dim() == 2 else input_ids[None]
+        rows, keep = self._unpad(ids, attention_mask)
         start = past_key_values.position
-        _, logits = self.engine.extend(rows, return_logits=True)
+        if k == 1:
+            _, last = self.engine.extend(rows, return_logits=True)
+            per_seq = [last[b:b + 1] for b in range(len(rows))]
+        else:
+            _, per_seq = self.engine.extend(rows, return_logits=True, logits_rows=k)
         if self.engine.tp.enabled:
             import torch.distributed as dist
-            parts = [torch.empty_like(logits) for _ in range(self.engine.tp.world)]
-            dist.all_gather(parts, logits, group=self.engine.tp.group)
-            logits = torch.cat(parts, -1)
+            gathered = []
+            for lg in per_seq:
+                parts = [torch.empty_like(lg) for _ in range(self.engine.tp.world)]
+                dist.all_gather(parts, lg.contiguous(), group=self.engine.tp.group)
+                gathered.append(torch.cat(parts, -1))
+            per_seq = gathered
+        L = ids.shape[1] if k == 0 else min(k, ids.shape[1])
+        if all(lg.shape[0] == L for lg in per_seq):
+            logits = torch.stack(per_seq)
+        else:                                       # unequal real lengths: rows sit where their columns were
+            logits = per_seq[0].new_zeros((len(rows), L, per_seq[0].shape[-1]))
+            first_col = ids.shape[1] - L
+            for b, lg in enumerate(per_seq):
+                cols = keep[b][-lg.shape[0]:] - first_col
+                logits[b, cols.to(logits.device)] = lg
         # the resolved plan of this call (variable-length launches run every length as it is: no padding rows)
         from .decoder import default_chunk_resolver, plan_bounded_prefill_execution
         n_rows = int(rows[0].numel())
@@ -94,7 +131,6 @@ class RPUCausalLM:
         self._rpu_last_execution_plan = {"stage": "prefill" if n_rows > 1 else "decode", "logical_len": n_rows,
                                          "execution_len": exec_len, "chunk_size": chunk,
                                          "padding_rows": exec_len - n_rows, "position": start}
-        logits = logits[:, None, :]
         if not return_dict:
             return (logits, past_key_values)
         from transformers.modeling_outputs import CausalLMOutputWithPast
@@ -103,14 +139,44 @@ class RPUCausalLM:
     __call__ = forward
 
     # -- generation --------------------------------------------------------------------------------
+    @property
+    def hf(self):
+        """This handle as a ``transformers.GenerationMixin`` model: ``model.hf.generate(...)`` is Hugging Face's own loop."""
+        if getattr(self, "_hf_adapter", None) is None:
+            from .hf_generation import make_adapter
+            self._hf_adapter = make_adapter(self)
+        return self._hf_adapter
+
+    _FAST_KWARGS = frozenset({"use_cache", "pad_token_id", "return_dict_in_generate", "num_beams", "temperature", "top_k", "top_p"})
+
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, past_key_values=None, max_new_tokens: Optional[int] = None,
                  do_sample: bool = False, attention_mask=None, eos_token_id=None, **kw) -> torch.Tensor:
-        """Greedy generation.  Returns ``[B, prompt + new]`` token ids on the input's device, like
-        Hugging Face ``generate``.  ``do_sample`` must be False; generation stops early only when
-        every sequence has produced ``eos_token_id`` (checked once per 16 steps)."""
-        if do_sample:
-            raise RPUBackendError("sampling is not supported: pass do_sample=False")
+        """``[B, prompt + new]`` token ids on the input's device, like Hugging Face ``generate``.
+
+        Greedy decoding of equal-length prompts runs on the fast path: the whole decode step, arg-max included, is one CUDA
+        graph and tokens never visit the host (generation stops early only when every sequence has produced
+        ``eos_token_id``, checked once per 16 steps).  Anything else - sampling, logits processors, stopping criteria,
+        streamers, a padded batch, ``max_length`` - is Hugging Face's unmodified ``GenerationMixin.generate`` driving this
+        handle's ``forward`` (:attr:`hf`)."""
+        ids2 = input_ids if input_ids.dim() == 2 else input_ids[None]
+        padded = attention_mask is not None and not bool(torch.as_tensor(attention_mask).bool().all())
+        plain = (not do_sample and not padded and max_new_tokens is not None and set(kw) <= self._FAST_KWARGS
+                 and kw.get("num_beams", 1) == 1 and not kw.get("return_dict_in_generate", False))
+        if not plain:
+            if past_key_values is None:
+                from ..api.cache import RPUCache
+                budget = max_new_tokens if max_new_tokens is not None else max(int(kw.get("max_length", 0)) - ids2.shape[1], 1)
+                past_key_values = RPUCache.from_model(self, input_ids=ids2, max_new_tokens=budget)
+            extra = dict(kw)
+            if max_new_tokens is not None:
+                extra["max_new_tokens"] = max_new_tokens
+            if eos_token_id is not None:
+                extra["eos_token_id"] = eos_token_id
+            out = self.hf.generate(input_ids=ids2, attention_mask=attention_mask, past_key_values=past_key_values,
+                                   do_sample=do_sample, use_cache=True, **extra)
+            self.engine.check_status()
+            return out
         if max_new_tokens is None or max_new_tokens < 1:
             raise RPUBackendError("max_new_tokens must be a positive integer")
         ids = input_ids if input_ids.dim() == 2 else input_ids[None]

@@ -535,7 +535,7 @@ class DecoderEngine:
         return self.extend(prompts, **kw)
 
     @torch.no_grad()
-    def extend(self, tokens: Sequence[torch.Tensor], *, return_logits: bool = False,
+    def extend(self, tokens: Sequence[torch.Tensor], *, return_logits: bool = False, logits_rows: int = 1,
                inputs_embeds: Optional[Sequence[torch.Tensor]] = None,
                positions3: Optional[Sequence[torch.Tensor]] = None,
                deepstack: Optional[Sequence[Optional[tuple]]] = None):
@@ -547,7 +547,10 @@ class DecoderEngine:
 
         ``inputs_embeds[s]`` ``[L, hidden]`` replaces the embedding lookup (vision rows already spliced
         in); ``positions3[s]`` ``[3, L]`` are M-RoPE positions; ``deepstack[s] = (rows, feats)`` adds
-        ``feats[l][i]`` to the hidden row ``rows[i]`` of sequence ``s`` after layer ``l`` (DeepStack)."""
+        ``feats[l][i]`` to the hidden row ``rows[i]`` of sequence ``s`` after layer ``l`` (DeepStack).
+
+        ``logits_rows`` (with ``return_logits``): 1 returns ``[B, vocab]`` of the last rows; ``k > 1`` or ``0`` (all) returns a
+        list with one ``[rows_s, vocab]`` tensor per sequence holding its last ``k`` (or all) new rows."""
         B = len(tokens)
         cache = self.cache
         if B > cache.batch_size:
@@ -580,8 +583,11 @@ class DecoderEngine:
                 off += take
         if chunk:
             items.append(chunk)
+        row_logits = None
+        if return_logits and logits_rows != 1:
+            row_logits = {"keep": int(logits_rows), "out": [[] for _ in range(B)]}
         for ch in items:
-            self._prefill_chunk(ch, tokens, lens, starts, first, logits_all, inputs_embeds, positions3, deepstack)
+            self._prefill_chunk(ch, tokens, lens, starts, first, logits_all, inputs_embeds, positions3, deepstack, row_logits)
         self.batch = B
         for s, L in enumerate(lens):
             cache.lengths[s] = starts[s] + L
@@ -598,10 +604,12 @@ class DecoderEngine:
         else:
             self.pos[:B].copy_(new_len[:, None].expand(B, self.pos_stride))
         self.kv_len[:B].copy_(new_len + 1)
+        if row_logits is not None:
+            return first, [torch.cat(parts) if parts else logits_all.new_empty((0, self.vocab_local)) for parts in row_logits["out"]]
         return (first, logits_all) if return_logits else first
 
     def _prefill_chunk(self, ch, prompts, lens, starts, first, logits_all, inputs_embeds, positions3,
-                       deepstack=None) -> None:
+                       deepstack=None, row_logits=None) -> None:
         T = sum(c[2] for c in ch)
         n = len(ch)
         meta = torch.empty((6, max(n, 1)), dtype=torch.int32)
@@ -673,6 +681,19 @@ class DecoderEngine:
             f.deepstack, f.deepstack_rows = ds_ptrs.data_ptr(), ds_rows_d.data_ptr()
             f.n_deepstack, f.n_deepstack_rows = len(ds_layers), ds_rows_d.numel()
         N.check(N.lib().rf_stack_forward(self.handle, C.byref(f), self._stream()), "rf_stack_forward")
+        if row_logits is not None:                 # logits of the requested trailing rows of every sequence in this chunk
+            keep = row_logits["keep"]
+            o2 = 0
+            for (s, off, cnt) in ch:
+                lo = 0 if keep == 0 else max(lens[s] - keep, 0)
+                a, b = max(off, lo), off + cnt
+                for r0 in range(a, b, self.max_batch):
+                    nr = min(self.max_batch, b - r0)
+                    idx = torch.arange(o2 + r0 - off, o2 + r0 - off + nr, dtype=torch.int32, device=self.device)
+                    lg = torch.empty((nr, self.vocab_local), dtype=self.dtype, device=self.device)
+                    self._head(nr, idx, lg)
+                    row_logits["out"][s].append(lg)
+                o2 += cnt
         # sequences whose prompt ends in this chunk get their first token
         done = [(j, s) for j, (s, off, cnt) in enumerate(ch) if off + cnt == lens[s]]
         if done:

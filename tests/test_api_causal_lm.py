@@ -155,3 +155,54 @@ def test_load_generate_matches_hf_model(tmp_path, monkeypatch, fresh_slot):
     dense = cache2.to_dynamic_cache()
     assert dense.get_seq_length() == 24
     model.close()
+
+
+@pytest.mark.gpu
+def test_hf_generate_drives_the_handle_unmodified(tmp_path, monkeypatch, fresh_slot):
+    """Sampling, a stopping criterion, a left-padded batch and all-row logits go through ``GenerationMixin.generate`` /
+    ``forward`` of the handle; greedy through that loop equals the handle's own graph loop."""
+    from transformers import AutoModelForCausalLM, StoppingCriteria, StoppingCriteriaList
+    from rpu_backend import RPUCache, RPUModelForCausalLM
+    monkeypatch.setenv("RPU_QWEN3_ALLOW_UNLISTED_PROFILE", "1")
+    _tiny_ckpt(tmp_path / "m", tie=True)
+    hf = AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), dtype=torch.float32).eval()
+    model = RPUModelForCausalLM.from_pretrained(str(tmp_path / "m"), dtype=torch.float16, device="rpu", max_batch=2)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(3, 512, (2, 12), generator=g)
+    fast = model.generate(ids, past_key_values=RPUCache.from_model(model, input_ids=ids, max_new_tokens=8), max_new_tokens=8)
+    slow = model.hf.generate(input_ids=ids, past_key_values=RPUCache.from_model(model, input_ids=ids, max_new_tokens=8),
+                             max_new_tokens=8, do_sample=False, pad_token_id=0)
+    assert torch.equal(fast.cpu(), slow.cpu())
+    # sampling: deterministic under a seed, different across seeds, tokens inside the vocabulary
+    outs = []
+    for seed in (1, 1, 2):
+        torch.manual_seed(seed)
+        outs.append(model.generate(ids, max_new_tokens=8, do_sample=True, top_k=20, temperature=1.5, pad_token_id=0).cpu())
+    assert torch.equal(outs[0], outs[1]) and not torch.equal(outs[0], outs[2])
+    assert outs[0].shape == (2, 20) and int(outs[0].max()) < 512 and torch.equal(outs[0][:, :12], ids)
+
+    class StopAt(StoppingCriteria):
+        def __call__(self, input_ids, scores, **kw):
+            return torch.full((input_ids.shape[0],), input_ids.shape[1] >= 15, dtype=torch.bool, device=input_ids.device)
+
+    out = model.generate(ids, max_new_tokens=30, stopping_criteria=StoppingCriteriaList([StopAt()]), pad_token_id=0)
+    assert out.shape[1] == 15 and torch.equal(out.cpu(), fast.cpu()[:, :15])
+    # a left-padded batch equals its sequences run one by one
+    short = ids[0, 5:]
+    padded = torch.cat((torch.zeros(5, dtype=ids.dtype), short))[None]
+    batch = torch.cat((padded, ids[1:2]))
+    mask = torch.ones_like(batch)
+    mask[0, :5] = 0
+    both = model.generate(batch, attention_mask=mask, max_new_tokens=6, pad_token_id=0).cpu()
+    alone = model.generate(short[None], max_new_tokens=6).cpu()
+    assert torch.equal(both[0, 5:], alone[0]) and torch.equal(both[1], fast.cpu()[1, :18])
+    # every row's logits
+    cache = RPUCache.from_model(model, max_seq_len=64)
+    o = model(input_ids=ids, past_key_values=cache, logits_to_keep=0)
+    with torch.no_grad():
+        r = hf(ids).logits
+    assert o.logits.shape == r.shape
+    torch.testing.assert_close(o.logits.float().cpu(), r, rtol=3e-2, atol=3e-2)
+    o3 = model(input_ids=ids[:, :1] * 0 + 7, past_key_values=cache, logits_to_keep=3)       # one new token: 1 row comes back
+    assert o3.logits.shape[1] == 1
+    model.close()

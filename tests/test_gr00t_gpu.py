@@ -103,9 +103,21 @@ def test_bundle_end_to_end_against_hf_backbone_and_oracle(tmp_path):
     qdir = tmp_path / "qwen3vl"
     hf_cfg.save_pretrained(str(qdir))
     ids, grid, px = _prompt()
+    # the residual stream after layer `select - 1` INCLUDING that layer's DeepStack addition (what the next layer would
+    # read): the last DeepStack tap of this tiny model sits on the cut layer, so record the stream where it is added
+    lm = ref.model.language_model
+    seen, orig = [], lm._deepstack_process
+
+    def record(*a, **k):
+        out = orig(*a, **k)
+        seen.append(out)
+        return out
+    lm._deepstack_process = record
     with torch.no_grad():
-        o = ref(input_ids=ids, pixel_values=px, image_grid_thw=grid, mm_token_type_ids=(ids == IMG).int(), output_hidden_states=True)
-    want_hidden = o.hidden_states[select][0]
+        ref(input_ids=ids, pixel_values=px, image_grid_thw=grid, mm_token_type_ids=(ids == IMG).int())
+    lm._deepstack_process = orig
+    assert len(seen) == 3
+    want_hidden = seen[select - 1][0]
     rt = build_gr00t_vla(str(ck), str(qdir), embodiment_id=1, max_vl=64, select_layer=select, max_patches=64)
     inputs = {"input_ids": ids, "pixel_values": px, "image_grid_thw": grid, "state": torch.linspace(-1, 1, cfg.state_dim - 2)}
     got_hidden = rt.backbone_hidden(inputs).float().cpu()
