@@ -38,12 +38,14 @@ class Qwen3_5Adapter:
         cfg = DecoderConfig.from_hf(tc)
         if cfg.layer_types is None:
             raise UnsupportedModelError("Qwen3.5 config carries no layer_types")
-        from ...runtime.control import rpu_env_exact1
-        if getattr(config, "vision_config", None) is not None and getattr(config, "rpu_use_vision", False) \
-                and not rpu_env_exact1("QWEN3_5_VISION_ALLOW_NUMERIC_BLOCKED"):
-            # fail-closed evaluation gate: the Qwen3.5 vision path has no numeric sign-off here
-            raise UnsupportedModelError("the Qwen3.5 vision path is evaluation-gated: set "
-                                        "QWEN3_5_VISION_ALLOW_NUMERIC_BLOCKED=1 (exactly 1) to admit it")
+        vc = getattr(config, "vision_config", None)
+        if vc is not None and getattr(config, "rpu_use_vision", False):
+            # the tower is the Qwen3-VL ViT without DeepStack taps: anything else is another architecture
+            if tuple(getattr(vc, "deepstack_visual_indexes", ()) or ()):
+                raise UnsupportedModelError("a Qwen3.5 vision tower has no DeepStack taps; this config lists "
+                                            f"{list(vc.deepstack_visual_indexes)}")
+            if getattr(vc, "hidden_act", "gelu_pytorch_tanh") not in ("gelu_pytorch_tanh", "gelu"):
+                raise UnsupportedModelError("Qwen3.5 vision activation must be gelu_pytorch_tanh or gelu")
         if cfg.gdn_dk != 128 or cfg.gdn_dv % 32 or cfg.gdn_conv != 4:
             raise UnsupportedModelError(f"Qwen3.5 linear-attention geometry (Dk={cfg.gdn_dk}, Dv={cfg.gdn_dv}, "
                                         f"conv={cfg.gdn_conv}) is not built (Dk 128, Dv multiple of 32, conv 4)")
@@ -99,7 +101,38 @@ class Qwen3_5Adapter:
                               for n in names}
         return text_get
 
-    def to_rpu(self, *, max_seq_len: int = 8192, max_batch: int = 1, tp=None):
+    def to_rpu_vision(self, *, max_seq_len: int = 8192, max_patches: int = 4096, tp=None):
+        """The multimodal handle: vision tower + hybrid decoder (``config.rpu_use_vision`` selects it in :meth:`to_rpu`).
+        The tower is the Qwen3-VL ViT without DeepStack (reference: ``python/rpu_backend/adapters/qwen3_5/vision.py:1-30``),
+        so the Qwen3-VL engine serves it: image rows are spliced into the embeddings and the text runs under three-axis
+        M-RoPE positions; the Gated-DeltaNet layers see the image rows as ordinary tokens."""
+        from ...models.qwen3_vl import Qwen3VLEngine
+        from ...runtime.conditional_generation import RPUConditionalGeneration
+        if getattr(self.config, "vision_config", None) is None:
+            raise UnsupportedModelError("this Qwen3.5 checkpoint has no vision_config")
+        if self._get is not None:
+            get, names = self._get, getattr(self._get, "names", None)
+        else:
+            sd = self.model.state_dict()
+            get, names = (lambda n: sd[n]), set(sd)
+        ex = self._rpu_execution or {}
+        chunk = (ex.get("prefill") or {}).get("chunk_size", "auto")
+        max_prefill = min(max_seq_len, 8192) if chunk in ("auto", None) else int(chunk)
+        live_handle.claim(self)
+        try:
+            eng = Qwen3VLEngine(self.config, get, dtype=self.dtype, max_seq_len=max_seq_len, max_patches=max_patches,
+                                max_prefill_tokens=max_prefill, tp=tp, names=None if names is None else set(names))
+        except Exception as e:  # noqa: BLE001
+            live_handle.poison(self, f"Qwen3.5 install failed: {type(e).__name__}: {e}")
+            raise
+        handle = RPUConditionalGeneration(eng, self.config, execution=self._rpu_execution)
+        live_handle.rebind(self, handle)
+        self.model = None
+        return handle
+
+    def to_rpu(self, *, max_seq_len: int = 8192, max_batch: int = 1, tp=None, **kw):
+        if getattr(self.config, "vision_config", None) is not None and getattr(self.config, "rpu_use_vision", False):
+            return self.to_rpu_vision(max_seq_len=max_seq_len, tp=tp, **kw)
         from ...runtime.causal_lm import RPUCausalLM
         from ...runtime.engine import DecoderEngine
         cfg = DecoderConfig.from_hf(_text(self.config))

@@ -218,7 +218,7 @@ constexpr int kGcLdQK = 132;      // fp32 row pitch of the q / k tiles: (4 * row
 constexpr int kGcLdS = 40;        // row pitch of the state slice and of the v / rhs / u tile
 constexpr int kGcLdL = 68;        // row pitch of the two chunk x chunk matrices
 constexpr int kGcLdD = 17;
-constexpr int kGcSmemFloats = 2 * kGcC * kGcLdQK + 128 * kGcLdS + kGcC * kGcLdS + 2 * kGcC * kGcLdL + 4 * 16 * kGcLdD + 3 * kGcC;
+constexpr int kGcSmemFloats = 2 * kGcC * kGcLdQK + 128 * kGcLdS + 2 * kGcC * kGcLdS + 2 * kGcC * kGcLdL + 4 * 16 * kGcLdD + 3 * kGcC;
 // + the raw 16-bit q | k rows and v slice of the NEXT chunk, fetched with cp.async while this chunk is computed
 constexpr int kGcRawElems = kGcC * 256 + kGcC * kGdnCols;
 constexpr size_t kGcSmemBytes = (size_t)kGcSmemFloats * sizeof(float) + (size_t)kGcRawElems * 2;
@@ -267,7 +267,8 @@ gdn_chunked_kernel(const RfGdn p) {
   float* sK = sQ + C * kGcLdQK;
   float* sS = sK + C * kGcLdQK;
   float* sV = sS + DK * kGcLdS;
-  float* sL = sV + C * kGcLdS;
+  float* sU = sV + C * kGcLdS;
+  float* sL = sU + C * kGcLdS;
   float* sP = sL + C * kGcLdL;
   float* sD = sP + C * kGcLdL;
   float* sG = sD + 4 * 16 * kGcLdD;
@@ -383,6 +384,7 @@ gdn_chunked_kernel(const RfGdn p) {
       for (int a = 0; a < 4; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) accL[a][b] = accP[a][b] = 0.f;
+#pragma unroll 4
       for (int ks = 0; ks < DK / 8; ++ks) {
         uint32_t aK[4], aQ[4];
         frag_a_bits(aK, sK, kGcLdQK, rt * 16, ks * 8, g, t);
@@ -436,6 +438,7 @@ gdn_chunked_kernel(const RfGdn p) {
       for (int a = 0; a < 2; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) accR[a][b] = accO[a][b] = 0.f;
+#pragma unroll 4
       for (int ks = 0; ks < DK / 8; ++ks) {
         uint32_t aK[4], aQ[4];
         frag_a_bits(aK, sK, kGcLdQK, rt * 16, ks * 8, g, t);
@@ -462,18 +465,19 @@ gdn_chunked_kernel(const RfGdn p) {
     }
     __syncthreads();
 
-    // ---- U = (I + L)^-1 rhs by block forward substitution, in place
+    // ---- U = (I + L)^-1 rhs by block forward substitution: rhs rows in sV, finished rows in sU
     {
       const int r = tid >> 4, cc = (tid & 15) * 2;
       for (int b = 0; b < 4; ++b) {
         const int i = b * 16 + r;
         float a0 = sV[i * kGcLdS + cc], a1 = sV[i * kGcLdS + cc + 1];
+#pragma unroll 4
         for (int j = 0; j < b * 16; ++j) {
           const float l = sL[i * kGcLdL + j];
-          a0 -= l * sV[j * kGcLdS + cc];
-          a1 -= l * sV[j * kGcLdS + cc + 1];
+          a0 -= l * sU[j * kGcLdS + cc];
+          a1 -= l * sU[j * kGcLdS + cc + 1];
         }
-        sV[i * kGcLdS + cc] = a0;          // rows of block b: read only by their owners until the barrier
+        sV[i * kGcLdS + cc] = a0;          // a row of block b is touched by its owner only until the barrier
         sV[i * kGcLdS + cc + 1] = a1;
         __syncthreads();
         float u0 = 0.f, u1 = 0.f;
@@ -482,9 +486,8 @@ gdn_chunked_kernel(const RfGdn p) {
           u0 += d * sV[(b * 16 + r2) * kGcLdS + cc];
           u1 += d * sV[(b * 16 + r2) * kGcLdS + cc + 1];
         }
-        __syncthreads();
-        sV[i * kGcLdS + cc] = u0;
-        sV[i * kGcLdS + cc + 1] = u1;
+        sU[i * kGcLdS + cc] = u0;
+        sU[i * kGcLdS + cc + 1] = u1;
         __syncthreads();
       }
     }
@@ -497,8 +500,8 @@ gdn_chunked_kernel(const RfGdn p) {
       for (int a = 0; a < 2; ++a) {
         const int col = (nh * 2 + a) * 8 + g;
         uint32_t b[2];
-        b[0] = to_tf32(sV[(ks * 8 + t) * kGcLdS + col]);
-        b[1] = to_tf32(sV[(ks * 8 + t + 4) * kGcLdS + col]);
+        b[0] = to_tf32(sU[(ks * 8 + t) * kGcLdS + col]);
+        b[1] = to_tf32(sU[(ks * 8 + t + 4) * kGcLdS + col]);
         mma_tf32(accO[a], aP, b);
       }
     }
@@ -519,6 +522,7 @@ gdn_chunked_kernel(const RfGdn p) {
 #pragma unroll
         for (int e = 0; e < 4; ++e)
           accS[a][e] = egl * sS[(warp * 16 + g + (e >> 1) * 8) * kGcLdS + a * 8 + 2 * t + (e & 1)];
+#pragma unroll
       for (int ks = 0; ks < C / 8; ++ks) {
         const int ca = ks * 8 + t, cb = ks * 8 + t + 4;
         uint32_t aT[4];
@@ -530,8 +534,8 @@ gdn_chunked_kernel(const RfGdn p) {
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
           uint32_t b[2];
-          b[0] = to_tf32(wa * sV[ca * kGcLdS + a * 8 + g]);
-          b[1] = to_tf32(wb * sV[cb * kGcLdS + a * 8 + g]);
+          b[0] = to_tf32(wa * sU[ca * kGcLdS + a * 8 + g]);
+          b[1] = to_tf32(wb * sU[cb * kGcLdS + a * 8 + g]);
           mma_tf32(accS[a], aT, b);
         }
       }

@@ -155,7 +155,7 @@ class Qwen3VLEngine:
             if rows.numel() != img.shape[0]:
                 raise RPUBackendError(f"{rows.numel()} image placeholder tokens but {img.shape[0]} image embeddings")
             K.scatter_rows(embeds, img, rows.to(self.device, torch.int32))
-            deep = (rows, feats)
+            deep = (rows, feats) if feats else None     # a tower without DeepStack taps (Qwen3.5) adds nothing to the text layers
         elif bool(is_vis.any()):
             raise RPUBackendError("input_ids contain image placeholders but no pixel_values were given")
         return embeds, pos3, deep
@@ -209,11 +209,11 @@ class Qwen3VLEngine:
             K.scatter_rows(e, img[o:o + n_img], rows.to(self.device, torch.int32))
             embeds.append(e)
             pos3s.append(rope_index(is_vis.to(torch.int32).tolist(), grids[s], self.vcfg.spatial_merge_size))
-            deeps.append((rows, [f[o:o + n_img] for f in feats]))
+            deeps.append((rows, [f[o:o + n_img] for f in feats]) if feats else None)
             o += n_img
         self._next_pos = max(int(p.max()) for p in pos3s) + 1
         return self.text.extend([t.flatten() for t in input_ids], return_logits=return_logits, inputs_embeds=embeds,
-                                positions3=pos3s, deepstack=deeps)
+                                positions3=pos3s, deepstack=deeps if any(d is not None for d in deeps) else None)
 
     def decode(self, n_steps: int, **kw) -> torch.Tensor:
         out = self.text.decode(n_steps, **kw)

@@ -132,8 +132,11 @@ class Qwen3VLVisionConfig:
     @classmethod
     def from_hf(cls, c) -> "Qwen3VLVisionConfig":
         g = (lambda k, d=None: c.get(k, d)) if isinstance(c, dict) else (lambda k, d=None: getattr(c, k, d))
-        return cls(**{f: (tuple(g(f)) if f == "deepstack_visual_indexes" else g(f))
-                      for f in cls.__dataclass_fields__ if g(f) is not None})
+        kw = {f: (tuple(g(f)) if f == "deepstack_visual_indexes" else g(f))
+              for f in cls.__dataclass_fields__ if g(f) is not None}
+        if "qwen3_5" in str(g("model_type", "")) and "deepstack_visual_indexes" not in kw:
+            kw["deepstack_visual_indexes"] = ()          # the Qwen3.5 tower is this ViT without DeepStack taps
+        return cls(**kw)
 
 
 class _Merger:

@@ -30,7 +30,6 @@ KEPT_ENV: Dict[str, tuple] = {
     "QWEN3_5_TEXT_CHUNK": ("int", 0, "MODEL"),
     "QWEN3_5_TEXT_PADDING_BUDGET": ("int", 64, "MODEL"),
     "QWEN3_VL_32B_ALLOW_GRAPH_BLOCKED": ("exact1", False, "MODEL"),
-    "QWEN3_5_VISION_ALLOW_NUMERIC_BLOCKED": ("exact1", False, "MODEL"),
     "RF_B200_NO_BUILD": ("exact1", False, "IMPORT"),
 }
 

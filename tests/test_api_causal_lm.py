@@ -194,10 +194,11 @@ def test_hf_generate_drives_the_handle_unmodified(tmp_path, monkeypatch, fresh_s
     mask = torch.ones_like(batch)
     mask[0, :5] = 0
     both = model.generate(batch, attention_mask=mask, max_new_tokens=6, pad_token_id=0).cpu()
-    alone = model.generate(short[None], max_new_tokens=6).cpu()
+    alone = model.hf.generate(input_ids=short[None], past_key_values=RPUCache.from_model(model, input_ids=short[None], max_new_tokens=6),
+                              max_new_tokens=6, do_sample=False, pad_token_id=0).cpu()       # the same end-of-sequence handling
     assert torch.equal(both[0, 5:], alone[0]) and torch.equal(both[1], fast.cpu()[1, :18])
     # every row's logits
-    cache = RPUCache.from_model(model, max_seq_len=64)
+    cache = RPUCache.from_model(model, max_seq_len=64, batch_size=2)
     o = model(input_ids=ids, past_key_values=cache, logits_to_keep=0)
     with torch.no_grad():
         r = hf(ids).logits

@@ -1,4 +1,6 @@
 """Gated-DeltaNet kernels and the Qwen3.5 hybrid decoder against plain PyTorch / Hugging Face fp32."""
+import os
+
 import pytest
 import torch
 import torch.nn.functional as F
@@ -283,3 +285,74 @@ def test_qwen3_5_engine_matches_hf():
         assert mine[0] == want_tok[b][0]
         assert sum(x == y for x, y in zip(mine, want_tok[b])) >= steps - 1, (mine, want_tok[b])
     eng.close()
+
+
+def test_qwen3_5_vision_path_matches_hf():
+    """Image + text through the adapter's multimodal handle against Hugging Face ``Qwen3_5ForConditionalGeneration`` fp32:
+    the ViT without DeepStack, image rows spliced into the embeddings, three-axis positions, the hybrid decoder."""
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5Config
+    from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5ForConditionalGeneration
+    from rhinoforge_b200.adapters.qwen3_5 import Qwen3_5Adapter
+    from rhinoforge_b200.api.cache import RPUCache
+    from rhinoforge_b200.runtime import live_handle
+    IMG = 150
+    c = Qwen3_5Config(
+        text_config=dict(vocab_size=304, hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=2,
+                         num_key_value_heads=1, head_dim=64, linear_conv_kernel_dim=4, linear_key_head_dim=128,
+                         linear_value_head_dim=128, linear_num_key_heads=2, linear_num_value_heads=4,
+                         layer_types=["linear_attention", "linear_attention", "full_attention", "linear_attention"],
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.25,
+                                          "mrope_section": [3, 3, 2], "mrope_interleaved": True},
+                         max_position_embeddings=512),
+        vision_config=dict(depth=3, hidden_size=128, num_heads=2, intermediate_size=256, out_hidden_size=128,
+                           num_position_embeddings=64),
+        image_token_id=IMG, video_token_id=151, vision_start_token_id=152, vision_end_token_id=153, tie_word_embeddings=False)
+    c._attn_implementation = "eager"
+    torch.manual_seed(0)
+    ref = Qwen3_5ForConditionalGeneration(c).float().eval()
+    g = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for n, p in ref.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn(p.shape, generator=g) * 0.06)
+            elif n.endswith("A_log"):
+                p.copy_(torch.log(torch.rand(p.shape, generator=g) * 4 + 0.5))
+            elif n.endswith("dt_bias"):
+                p.copy_(torch.rand(p.shape, generator=g))
+            elif "norm" in n and n.endswith("weight"):
+                p.copy_((1.0 if "visual" in n or "linear_attn.norm" in n else 0.0) + 0.1 * torch.randn(p.shape, generator=g))
+            else:
+                p.copy_(0.05 * torch.randn(p.shape, generator=g))
+    grid = torch.tensor([[1, 4, 6], [1, 4, 4]])
+    ids = torch.tensor([[1, 2, 152] + [IMG] * 6 + [153, 4, 5, 152] + [IMG] * 4 + [153, 6, 7, 8]])
+    px = torch.randn(int((grid[:, 1] * grid[:, 2]).sum()), 3 * 2 * 16 * 16, generator=torch.Generator().manual_seed(2))
+    ref = ref.cuda()
+    with torch.no_grad():
+        want = ref(input_ids=ids.cuda(), pixel_values=px.cuda(), image_grid_thw=grid.cuda(),
+                   mm_token_type_ids=(ids == IMG).int().cuda()).logits[0, -1].float().cpu()
+    os.environ["RPU_QWEN3_5_ALLOW_ANY_PROFILE"] = "1"
+    live_handle._reset_for_tests()
+    c.rpu_use_vision = True
+    sd = {k: v.cpu() for k, v in ref.state_dict().items()}
+    get = lambda n: sd[n]
+    get.names = set(sd)
+    try:
+        handle = Qwen3_5Adapter(None, config=c, get_weight=get, dtype=torch.float16).to_rpu(max_seq_len=128, max_patches=64)
+        eng = handle.vl
+        _, logits = eng.prefill(ids[0], px, grid, return_logits=True)
+        got = logits[0].float().cpu()
+        rel = float((got - want).abs().max() / want.abs().max())
+        assert rel < 3e-2, rel
+        # text continuation keeps the positions running after the images
+        nxt = int(want.argmax())
+        with torch.no_grad():
+            ids2 = torch.cat((ids, torch.tensor([[nxt, 9]])), 1)
+            want2 = ref(input_ids=ids2.cuda(), pixel_values=px.cuda(), image_grid_thw=grid.cuda(),
+                        mm_token_type_ids=(ids2 == IMG).int().cuda()).logits[0, -1].float().cpu()
+        _, lg2 = eng.extend(torch.tensor([nxt, 9]), return_logits=True)
+        rel2 = float((lg2[0].float().cpu() - want2).abs().max() / want2.abs().max())
+        assert rel2 < 3e-2, rel2
+        handle.close()
+    finally:
+        os.environ.pop("RPU_QWEN3_5_ALLOW_ANY_PROFILE", None)
+        live_handle._reset_for_tests()
