@@ -84,6 +84,7 @@ class RfRopeKv(C.Structure):
         ("page_table", C.c_void_p), ("pt_stride", C.c_int32),
         ("seq_of_tok", C.c_void_p), ("cache_pos", C.c_void_p),
         ("rope_before_norm", C.c_int32), ("write_k_inplace", C.c_int32), ("dtype", C.c_int32),
+        ("v_norm", C.c_int32),
     ]
 
 

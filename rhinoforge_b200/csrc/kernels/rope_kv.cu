@@ -89,10 +89,24 @@ __global__ void qk_norm_rope_kv_kernel(const RfRopeKv a) {
           for (int i = lane; i < hd; i += 32) src[i] = Num<T>::from_f(buf[i]);
       }
       __syncwarp();
-    } else if (page >= 0) {
-      const int vh = h - a.Hq - a.Hkv;
-      T* dst = reinterpret_cast<T*>(a.v_pool) + (((size_t)page * a.Hkv + vh) * 16 + slot) * hd;
-      for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+    } else {
+      if (a.v_norm) {                                      // unweighted RMS over the value head, in place
+        float s2 = 0.f;
+        for (int i = lane; i < hd; i += 32) {
+          const float f = Num<T>::to_f(src[i]);
+          buf[i] = f;
+          s2 += f * f;
+        }
+        s2 = warp_sum(s2);
+        const float rstd = rsqrtf(s2 / (float)hd + a.eps);
+        for (int i = lane; i < hd; i += 32) src[i] = Num<T>::from_f(buf[i] * rstd);
+        __syncwarp();
+      }
+      if (page >= 0) {
+        const int vh = h - a.Hq - a.Hkv;
+        T* dst = reinterpret_cast<T*>(a.v_pool) + (((size_t)page * a.Hkv + vh) * 16 + slot) * hd;
+        for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+      }
     }
   }
 }

@@ -195,6 +195,7 @@ typedef struct RfRopeKv {
   int32_t rope_before_norm;
   int32_t write_k_inplace;          // also write rotated k back into qkv
   int32_t dtype;
+  int32_t v_norm;                   // unweighted RMSNorm of every value head (in place, before the cache insert)
 } RfRopeKv;
 int rf_qk_norm_rope_kv(const RfRopeKv* a, rf_stream_t stream);
 

@@ -304,7 +304,10 @@ def qk_norm_rope_kv(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, *, pos: torch
                     v_pool: Optional[torch.Tensor] = None, page_table: Optional[torch.Tensor] = None,
                     seq_of_tok: Optional[torch.Tensor] = None, cache_pos: Optional[torch.Tensor] = None,
                     q_out: Optional[torch.Tensor] = None, rope_before_norm: bool = False,
-                    write_k_inplace: bool = False) -> None:
+                    write_k_inplace: bool = False, v_norm: bool = False) -> None:
+    """Per-head RMSNorm and rotary embedding of the q / k heads of a packed ``[tokens, (Hq + 2 Hkv) * hd]`` buffer (in place
+    when no pool is given), K / V insertion into a paged pool when one is.  ``v_norm``: every value head also gets an
+    unweighted RMSNorm in place."""
     a = N.RfRopeKv()
     tokens = qkv.shape[0]
     a.qkv, a.ld = qkv.data_ptr(), qkv.stride(0)
@@ -329,6 +332,7 @@ def qk_norm_rope_kv(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, *, pos: torch
         a.page_table, a.pt_stride = page_table.data_ptr(), page_table.stride(0)
     a.seq_of_tok, a.cache_pos = _ptr(seq_of_tok), _ptr(cache_pos)
     a.rope_before_norm, a.write_k_inplace = int(rope_before_norm), int(write_k_inplace)
+    a.v_norm = int(v_norm)
     a.dtype = dtype_code(qkv.dtype)
     N.check(N.lib().rf_qk_norm_rope_kv(C.byref(a), _stream()), "rf_qk_norm_rope_kv")
 
