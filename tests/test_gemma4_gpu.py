@@ -109,3 +109,52 @@ def test_gemma4_engine_matches_hf(over):
     eager = eng.decode(first, 3, use_graph=False).cpu()
     assert torch.equal(eager, toks[:, 1:4])
     eng.close()
+
+
+def test_gemma4_e4b_widths_reduced_depth():
+    """E4B layer geometry at its real widths (hidden 2560, 8 / 2 heads of 256 and 512, window 512, PLE 256) on six layers
+    and a small vocabulary: a 700-token prompt (longer than the window) and a batch-2 decode against Hugging Face fp32."""
+    from rhinoforge_b200.models.gemma4 import Gemma4Engine
+    c, ref = _tiny_gemma4(vocab_size=2048, vocab_size_per_layer_input=2048, hidden_size=2560, intermediate_size=10240,
+                          num_attention_heads=8, num_key_value_heads=2, sliding_window=512, hidden_size_per_layer_input=256,
+                          max_position_embeddings=2048,
+                          layer_types=["sliding_attention"] * 2 + ["full_attention"] + ["sliding_attention"] * 2 + ["full_attention"])
+    with torch.no_grad():
+        for n, p in ref.named_parameters():
+            if p.dim() >= 2 and "embed" not in n:
+                p.mul_(0.35)                                   # keep activations in range at this width
+    ref = ref.cuda()
+    sd = ref.state_dict()
+    eng = Gemma4Engine(c, lambda n: sd[n], max_seq_len=1024, max_batch=2, max_tokens=1024, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(7)
+    a, b = torch.randint(1, 2048, (700,), generator=g), torch.randint(1, 2048, (150,), generator=g)
+    got = eng.prefill([a, b])
+    eng.check_status()
+    for r, ids in enumerate((a, b)):
+        with torch.no_grad():
+            want = ref(ids[None].cuda()).logits[0, -1].float()
+        err = float((got[r] - want).abs().max() / want.abs().max())
+        assert err < 8e-2, (r, err)
+    first = got.argmax(-1).to(torch.int32)
+    toks = eng.decode(first, 4)
+    eng.check_status()
+    assert toks.shape == (2, 4) and int(toks.max()) < 2048
+    eng.close()
+
+
+def test_gemma4_adapter_handle():
+    from rhinoforge_b200.adapters.gemma4 import Gemma4Adapter
+    c, ref = _tiny_gemma4()
+    handle = Gemma4Adapter(ref, dtype=torch.float16).to_rpu(max_seq_len=96, max_batch=2)
+    ids = torch.randint(1, 300, (2, 20), generator=torch.Generator().manual_seed(4))
+    out = handle(ids)
+    with torch.no_grad():
+        want = ref(ids).logits
+    assert out.logits.shape == want.shape
+    assert float((out.logits.cpu() - want).abs().max() / want.abs().max()) < 4e-2
+    gen = handle.generate(ids, max_new_tokens=4)
+    assert gen.shape == (2, 24) and torch.equal(gen[:, :20], ids)
+    with torch.no_grad():
+        hf = ref.generate(ids, max_new_tokens=4, do_sample=False)
+    assert torch.equal(gen[:, 20], hf[:, 20])
+    handle.close()
