@@ -240,6 +240,90 @@ def _denoise_forward(handle: int, prefix_lens: Optional[torch.Tensor], noise: to
 
 
 # ------------------------------------------------------------------------------------------ registration
+# ------------------------------------------------------------------------------------------ action heads
+# Flow-matching / diffusion heads: the handle's configuration is the dataclass of the engine as a JSON object
+# (``{}`` = the published profile); ``set_weights`` takes the checkpoint's own tensor names.
+_HEADS = ("navdp", "gr00t", "internvla_nextdit", "rhino_vla", "qwenpi05", "gemma4")
+
+
+def _head_cfg(cls, cfg: dict):
+    fields = getattr(cls, "__dataclass_fields__", {})
+    return cls(**{k: v for k, v in cfg.items() if k in fields})
+
+
+def _head_set_weights(family: str, handle: int, names: List[str], tensors: List[torch.Tensor]) -> None:
+    e = _entry(handle, (family,))
+    if e.runtime is not None:
+        e.runtime.close()
+    sd, cfg, dtype = _sd(names, tensors), e.config, _dtype_of(e.config)
+    if family == "navdp":
+        from ..models.navdp import NavdpConfig, NavdpEngine
+        e.runtime = NavdpEngine(_head_cfg(NavdpConfig, cfg), sd, max_samples=int(cfg.get("rpu_max_samples", 4)), dtype=dtype)
+    elif family == "gr00t":
+        from ..models.gr00t import Gr00tConfig, Gr00tEngine
+        e.runtime = Gr00tEngine(_head_cfg(Gr00tConfig, cfg), sd.__getitem__, embodiment=int(cfg.get("rpu_embodiment", 0)),
+                                max_vl=int(cfg.get("rpu_max_vl", 512)), dtype=dtype)
+    elif family == "internvla_nextdit":
+        from ..models.nextdit import NextDiTConfig, NextDiTEngine
+        e.runtime = NextDiTEngine(_head_cfg(NextDiTConfig, cfg), sd, dtype=dtype)
+    elif family == "rhino_vla":
+        from ..models.rhinovla import RhinoVLAConfig, RhinoVLAEngine
+        e.runtime = RhinoVLAEngine(_head_cfg(RhinoVLAConfig, cfg), sd, max_prefix=int(cfg.get("rpu_max_prefix", 1024)), dtype=dtype)
+    elif family == "qwenpi05":
+        from ..models.qwenpi05 import QwenPI05Config, QwenPI05Engine
+        e.runtime = QwenPI05Engine(_head_cfg(QwenPI05Config, cfg), sd, max_prefix=int(cfg.get("rpu_max_prefix", 1024)), dtype=dtype)
+    elif family == "gemma4":
+        from ..models.gemma4 import Gemma4Engine
+        text = {k: v for k, v in cfg.items() if not k.startswith("rpu_")}
+        e.runtime = Gemma4Engine(text, sd.__getitem__, prefix=str(cfg.get("rpu_weight_prefix", "model.")),
+                                 max_seq_len=int(cfg.get("rpu_max_seq_len", 2048)), max_batch=int(cfg.get("rpu_max_batch", 1)),
+                                 max_tokens=int(cfg.get("rpu_max_prefill_tokens", cfg.get("rpu_max_seq_len", 2048))), dtype=dtype)
+
+
+def _navdp_forward(handle: int, goal_embed: torch.Tensor, rgbd_embed: torch.Tensor, init_noise: torch.Tensor,
+                   step_noise: torch.Tensor) -> torch.Tensor:
+    return _runtime(_entry(handle, ("navdp",))).predict_action(goal_embed, rgbd_embed, init_noise, step_noise)
+
+
+def _gr00t_vl_forward(handle: int, hidden: torch.Tensor) -> torch.Tensor:
+    return _runtime(_entry(handle, ("gr00t",))).vl_encode(hidden).clone()
+
+
+def _gr00t_denoise_forward(handle: int, noise: torch.Tensor, state: torch.Tensor, vl_embeds: torch.Tensor, image_mask: torch.Tensor,
+                           valid_mask: Optional[torch.Tensor]) -> torch.Tensor:
+    return _runtime(_entry(handle, ("gr00t",))).denoise(vl_embeds, state, noise, image_mask, valid_mask)
+
+
+def _nextdit_forward(handle: int, actions: torch.Tensor, timesteps: torch.Tensor, euler_steps: torch.Tensor,
+                     condition: torch.Tensor) -> torch.Tensor:
+    return _runtime(_entry(handle, ("internvla_nextdit",))).denoise_actions(actions, timesteps, euler_steps, condition)
+
+
+def _expert_set_prefix(families, handle: int, keys: List[torch.Tensor], values: List[torch.Tensor], prefix_valid: Optional[torch.Tensor]) -> int:
+    if len(keys) != len(values):
+        raise RPUBackendError(f"set_prefix: {len(keys)} key tensors for {len(values)} value tensors")
+    return int(_runtime(_entry(handle, families)).set_prefix(list(zip(keys, values)), prefix_valid))
+
+
+def _rhino_forward(handle: int, state: torch.Tensor, noise: torch.Tensor, state_mask: Optional[torch.Tensor],
+                   action_mask: Optional[torch.Tensor], cond_all: Optional[torch.Tensor]) -> torch.Tensor:
+    rt = _runtime(_entry(handle, ("rhino_vla",)))
+    return rt.predict(state, noise, state_mask=state_mask, action_mask=action_mask, cond_all=cond_all).clone()
+
+
+def _qwenpi05_forward(handle: int, state: Optional[torch.Tensor], noise: torch.Tensor, num_steps: int = 10) -> torch.Tensor:
+    return _runtime(_entry(handle, ("qwenpi05",))).predict(state, noise, num_steps).clone()
+
+
+def _gemma4_forward(handle: int, input_ids: torch.Tensor, reset: bool = True) -> torch.Tensor:
+    """``input_ids [B, L]`` appended to sequences ``0 .. B-1`` (from empty when ``reset``) -> last-row logits ``[B, vocab]`` fp32."""
+    rt = _runtime(_entry(handle, ("gemma4",)))
+    rows = [input_ids[b] for b in range(input_ids.shape[0])] if input_ids.dim() == 2 else [input_ids]
+    if reset:
+        rt.reset()
+    return rt.extend(rows)
+
+
 def register(lib: "torch.library.Library") -> None:
     """Define and implement the handle-family schemas on ``lib`` (the ``rpu`` namespace)."""
     def op(schema: str, fn) -> None:
@@ -280,7 +364,27 @@ def register(lib: "torch.library.Library") -> None:
                _denoise_forward)
     op("pi05_denoise_loop_forward(int handle, Tensor? prefix_lens, Tensor noise, int num_steps=10) -> Tensor", _denoise_forward)
 
+    def head(name: str, forward_schema: str, forward) -> None:
+        family(name, (name,), lambda handle, names, tensors, _n=name: _head_set_weights(_n, handle, names, tensors),
+               forward_schema, forward)
 
-FAMILIES = _DECODERS + ("qwen3vl_vision", "qwen3_5_vision", "qwen25vl_vision", "siglip", "hyvit2", "dinov3_vision") + _PI05
+    head("navdp", "(int handle, Tensor goal_embed, Tensor rgbd_embed, Tensor init_noise, Tensor step_noise) -> Tensor", _navdp_forward)
+    head("gr00t", "(int handle, Tensor noise, Tensor state, Tensor vl_embeds, Tensor image_mask, Tensor? valid_mask) -> Tensor",
+         _gr00t_denoise_forward)
+    op("gr00t_vl_encoder_forward(int handle, Tensor hidden) -> Tensor", _gr00t_vl_forward)
+    op("gr00t_denoise_unroll_forward(int handle, Tensor noise, Tensor state, Tensor vl_embeds, Tensor image_mask, Tensor? valid_mask) -> Tensor",
+       _gr00t_denoise_forward)
+    head("internvla_nextdit", "(int handle, Tensor actions, Tensor timesteps, Tensor euler_steps, Tensor condition) -> Tensor",
+         _nextdit_forward)
+    head("rhino_vla", "(int handle, Tensor state, Tensor noise, Tensor? state_mask, Tensor? action_mask, Tensor? cond_all) -> Tensor",
+         _rhino_forward)
+    head("qwenpi05", "(int handle, Tensor? state, Tensor noise, int num_steps=10) -> Tensor", _qwenpi05_forward)
+    for name in ("rhino_vla", "qwenpi05"):
+        op(f"{name}_set_prefix(int handle, Tensor[] keys, Tensor[] values, Tensor? prefix_valid) -> int",
+           lambda handle, keys, values, prefix_valid, _f=(name,): _expert_set_prefix(_f, handle, keys, values, prefix_valid))
+    head("gemma4", "(int handle, Tensor input_ids, bool reset=True) -> Tensor", _gemma4_forward)
+
+
+FAMILIES = _DECODERS + ("qwen3vl_vision", "qwen3_5_vision", "qwen25vl_vision", "siglip", "hyvit2", "dinov3_vision") + _PI05 + _HEADS
 
 __all__ = ["register", "live_handles", "FAMILIES"]

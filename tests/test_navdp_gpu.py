@@ -61,3 +61,20 @@ def test_full_profile_runs_and_stays_in_range():
     eng.check_status()
     assert torch.isfinite(got).all() and float(got.abs().max()) <= 1.0 + 1e-3
     assert float((got - want).abs().mean()) < 3e-2
+
+
+def test_navdp_through_the_op_surface():
+    import json
+    import rhinoforge_b200.ops.torch_ops  # noqa: F401  (registers torch.ops.rpu)
+    ops = torch.ops.rpu
+    cfg = nd.tiny_navdp_config()
+    sd = nd.random_navdp_state_dict(cfg, seed=2)
+    goal, rgbd, init, zs = _inputs(cfg, 2, seed=5)
+    want = nd.TorchNavdp(cfg, sd).predict_action(goal, rgbd, init, zs)
+    h = ops.navdp_create(json.dumps({**cfg.__dict__, "rpu_max_samples": 2}))
+    ops.navdp_set_weights(h, list(sd), [sd[k] for k in sd])
+    got = ops.navdp_forward(h, goal, rgbd, init, zs).cpu()
+    assert float((got - want).abs().max()) < 5e-2
+    ops.navdp_destroy(h)
+    with pytest.raises(Exception, match="unknown or destroyed"):
+        ops.navdp_forward(h, goal, rgbd, init, zs)
