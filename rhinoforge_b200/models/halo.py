@@ -235,13 +235,58 @@ class TorchHalo:
         return x
 
 
+    @torch.no_grad()
+    def rollout_cfg(self, branches: Sequence[Optional[Tuple[Sequence, int]]], x0: torch.Tensor, position_ids: torch.Tensor,
+                    text_ids: torch.Tensor, num_timesteps: int = 10, *, cfg_text_scale: float = 1.0, cfg_img_scale: float = 1.0,
+                    cfg_renorm_min: float = 0.0, cfg_renorm_type: str = "global") -> torch.Tensor:
+        """``branches = [cond, cfg_text, cfg_img]``, each ``(prefix_kv, rope_position)`` or ``None``: classifier-free guidance
+        over the three prefix banks, then the norm of the guided velocity is capped at the conditional one."""
+        sd = self.sd
+        ow, ob = ("output_linear_layer.weight", "output_linear_layer.bias") if self.mode == "act" else ("llm2vae.weight", "llm2vae.bias")
+        x = x0.float().to(self.device)
+        ts, dts = euler_schedule(num_timesteps)
+        for t, dt in zip(ts.tolist(), dts.tolist()):
+            rows = self.input_rows(x, t, position_ids, text_ids)
+            vel = lambda b: F.linear(self.decoder(rows, b[0], b[1])[1:-1].float(), sd[ow].float(), sd[ob].float())
+            v = vel(branches[0])
+            x = x - cfg_combine(v, vel(branches[1]) if cfg_text_scale > 1.0 else None, vel(branches[2]) if cfg_img_scale > 1.0 else None,
+                                cfg_text_scale, cfg_img_scale, cfg_renorm_min, cfg_renorm_type) * dt
+        return x
+
+
+def cfg_combine(v: torch.Tensor, v_text: Optional[torch.Tensor], v_img: Optional[torch.Tensor], text_scale: float, img_scale: float,
+                renorm_min: float = 0.0, renorm_type: str = "global") -> torch.Tensor:
+    """Text guidance, then image guidance, then the result is scaled back so that its norm (whole tensor or per row) does
+    not exceed the conditional velocity's (scale clamped to ``[renorm_min, 1]``).  With both scales at most 1 the
+    conditional velocity passes through."""
+    if text_scale <= 1.0 and img_scale <= 1.0:
+        return v
+    g = v
+    if text_scale > 1.0:
+        if v_text is None:
+            raise ValueError("cfg_text_scale > 1 needs the cfg_text branch")
+        g = v_text + text_scale * (v - v_text)
+    if img_scale > 1.0:
+        if v_img is None:
+            raise ValueError("cfg_img_scale > 1 needs the cfg_img branch")
+        g = v_img + img_scale * (g - v_img)
+    if renorm_type == "global":
+        n0, n1 = torch.linalg.vector_norm(v.float()), torch.linalg.vector_norm(g.float())
+    elif renorm_type == "channel":
+        n0, n1 = torch.linalg.vector_norm(v.float(), dim=-1, keepdim=True), torch.linalg.vector_norm(g.float(), dim=-1, keepdim=True)
+    else:
+        raise NotImplementedError(f"cfg_renorm_type {renorm_type!r} (global or channel)")
+    return (g.float() * (n0 / (n1 + 1e-8)).clamp(min=renorm_min, max=1.0)).to(g.dtype)
+
+
 # ----------------------------------------------------------------------------- device engine
 class HaloEngine:
     """The twin-weight decoder over a paged prefix cache for one mode (``"act"``: action expert, ``"gen"``: image-flow
     step).  ``rollout`` returns the denoised ``[rows, action_dim | latent_dim]`` in a buffer the next call overwrites."""
 
     def __init__(self, cfg: HaloConfig, sd: Dict[str, torch.Tensor], mode: str = "act", *, max_prefix: int = 1024, device="cuda",
-                 dtype=torch.float16):
+                 dtype=torch.float16, branches: int = 1):
+        """``branches``: how many prefix banks the cache holds (3 for classifier-free guidance: cond, cfg_text, cfg_img)."""
         from ..ops import kernels as K
         from ..runtime.kv_cache import PagedKV
         from ..runtime.stack import NativeStack, StackSpec
@@ -252,7 +297,8 @@ class HaloEngine:
         self.n, self.body = n, n - 2
         self.max_prefix = max_prefix
         self.max_seq = (max_prefix + n + 15) // 16 * 16
-        self.cache = PagedKV(cfg.layers, 1, self.max_seq, cfg.kv_heads, cfg.head_dim, device=device, dtype=dtype)
+        self.branches = branches
+        self.cache = PagedKV(cfg.layers, branches, self.max_seq, cfg.kv_heads, cfg.head_dim, device=device, dtype=dtype)
         self.cache.reserve_all()
         s = SUFFIX[mode]
         self.stack = NativeStack(
@@ -284,28 +330,42 @@ class HaloEngine:
         self.s_qstart = torch.zeros(1, **i32)
         self.s_qlen = torch.full((1,), n, **i32)
         self.s_kvlen = torch.zeros(1, **i32)
-        self.cos = torch.zeros(1, cfg.head_dim // 2, dtype=torch.float32, device=dev)
-        self.sin = torch.zeros(1, cfg.head_dim // 2, dtype=torch.float32, device=dev)
+        self.cos = torch.zeros(branches, cfg.head_dim // 2, dtype=torch.float32, device=dev)
+        self.sin = torch.zeros(branches, cfg.head_dim // 2, dtype=torch.float32, device=dev)
         self.prefix_len = 0
+        # per-bank row metadata of the guidance branches (bank 0 is the plain path's)
+        self.b_pos = [torch.full((n,), b, **i32) for b in range(branches)]
+        self.b_cache_pos = [torch.zeros(n, **i32) for _ in range(branches)]
+        self.b_kvlen = [torch.zeros(1, **i32) for _ in range(branches)]
+        self.b_ready = [False] * branches
+        if branches > 1:
+            self.h0 = torch.zeros(n, H, dtype=dtype, device=dev)
+            self.vel = [torch.zeros(self.body, self.w_pad, dtype=dtype, device=dev) for _ in range(branches)]
 
     # ------------------------------------------------------------------ prefix
     @torch.no_grad()
-    def set_prefix(self, prefix_kv: Sequence[Tuple[torch.Tensor, torch.Tensor]], rope_position: int) -> int:
-        """Copy the prefix's rotated keys / values (``[kv_heads, P, head_dim]`` per layer) into the cache; every row of the
-        chunk then rotates at ``rope_position``."""
+    def set_prefix(self, prefix_kv: Sequence[Tuple[torch.Tensor, torch.Tensor]], rope_position: int, *, branch: int = 0) -> int:
+        """Copy the prefix's rotated keys / values (``[kv_heads, P, head_dim]`` per layer) into bank ``branch`` of the cache;
+        every row of the chunk then rotates at ``rope_position`` when it runs against that bank."""
         cfg, dev = self.cfg, self.device
+        if not 0 <= branch < self.branches:
+            raise ValueError(f"branch {branch} is outside the engine's {self.branches} banks")
         P = int(prefix_kv[0][0].shape[1])
         if P > self.max_prefix or len(prefix_kv) != cfg.layers:
             raise ValueError(f"prefix of {P} rows / {len(prefix_kv)} layers does not fit (max_prefix {self.max_prefix}, {cfg.layers} layers)")
         for i, (k, v) in enumerate(prefix_kv):
-            self.cache.scatter(i, 0, k, v, 0)
+            self.cache.scatter(i, branch, k, v, 0)
         self.cache.sync_table()
         ang = float(rope_position) * self._inv
-        self.cos.copy_(ang.cos()[None].to(dev))
-        self.sin.copy_(ang.sin()[None].to(dev))
-        self.s_cache_pos.copy_((self.chunk_row + P).to(dev))
-        self.s_kvlen.fill_(P + self.n)
-        self.prefix_len = P
+        self.cos[branch].copy_(ang.cos().to(dev))
+        self.sin[branch].copy_(ang.sin().to(dev))
+        self.b_cache_pos[branch].copy_((self.chunk_row + P).to(dev))
+        self.b_kvlen[branch].fill_(P + self.n)
+        self.b_ready[branch] = True
+        if branch == 0:
+            self.s_cache_pos.copy_(self.b_cache_pos[0])
+            self.s_kvlen.copy_(self.b_kvlen[0])
+            self.prefix_len = P
         return P
 
     # ------------------------------------------------------------------ schedule
@@ -323,7 +383,9 @@ class HaloEngine:
         out_w = torch.stack([pad(sd[ow] * -float(d), self.w_pad, cfg.hidden) for d in dts]).to(self.dtype).contiguous()
         out_b = torch.stack([F.pad(sd[ob] * -float(d), (0, self.w_pad - self.width)) for d in dts]).to(self.dtype).contiguous()
         hit = dict(steps=int(ts.numel()), in_w=pad(sd[iw], cfg.hidden, self.w_pad).to(self.dtype).contiguous(),
-                   step_bias=(temb + sd[ib][None]).to(self.dtype).contiguous(), out_w=out_w, out_b=out_b)
+                   step_bias=(temb + sd[ib][None]).to(self.dtype).contiguous(), out_w=out_w, out_b=out_b,
+                   out_w_plain=pad(sd[ow], self.w_pad, cfg.hidden).to(self.dtype).contiguous(),
+                   out_b_plain=F.pad(sd[ob], (0, self.w_pad - self.width)).to(self.dtype).contiguous())
         self._schedules[num_timesteps] = hit
         return hit
 
@@ -340,10 +402,42 @@ class HaloEngine:
             self.stack.final_norm_twin(self.h, 2, out=self.hn)
             K.gemm(self.hn[2:], sch["out_w"][k], bias=sch["out_b"][k], residual=self.x, out=self.x)     # x <- x - dt * v
 
+    def _loop_cfg(self, num_timesteps: int, text_scale: float, img_scale: float, renorm_min: float, renorm_type: str) -> None:
+        """The guided loop: every step runs the chunk against the banks its scales ask for (the input rows are built once),
+        combines the velocities and applies the Euler update."""
+        K, sch = self.K, self.schedule(num_timesteps)
+        n = self.n
+        use = [0] + ([1] if text_scale > 1.0 else []) + ([2] if img_scale > 1.0 else [])
+        ts, dts = euler_schedule(num_timesteps)
+        ow, ob = sch["out_w_plain"], sch["out_b_plain"]
+        for k in range(sch["steps"]):
+            K.gemm(self.x, sch["in_w"], bias=sch["step_bias"][k], residual=self.row_bias, out=self.h0[2:])
+            self.h0[:2].copy_(self.text_rows)
+            for b in use:
+                self.h.copy_(self.h0)
+                self.stack.forward(self.h, q_start=self.s_qstart, q_len=self.s_qlen, kv_len=self.b_kvlen[b], max_q_len=n,
+                                   max_kv_len=self.max_seq, pos=self.b_pos[b], cos=self.cos, sin=self.sin, seq_of_tok=self.s_seq,
+                                   cache_pos=self.b_cache_pos[b], page_table=self.cache.page_table[b:b + 1], twin_split=2)
+                self.stack.final_norm_twin(self.h, 2, out=self.hn)
+                K.gemm(self.hn[2:], ow, bias=ob, out=self.vel[b])
+            v = cfg_combine(self.vel[0], self.vel[1] if 1 in use else None, self.vel[2] if 2 in use else None, text_scale, img_scale,
+                            renorm_min, renorm_type)
+            self.x.add_(v, alpha=-float(dts[k]))
+
     @torch.no_grad()
     def rollout(self, x0: torch.Tensor, position_ids: torch.Tensor, text_ids: torch.Tensor, num_timesteps: int = 10, *,
-                use_graph: bool = True) -> torch.Tensor:
+                use_graph: bool = True, cfg_text_scale: float = 1.0, cfg_img_scale: float = 1.0, cfg_renorm_min: float = 0.0,
+                cfg_renorm_type: str = "global") -> torch.Tensor:
+        """With a guidance scale above 1 the chunk also runs against bank 1 (``cfg_text``) / bank 2 (``cfg_img``), set with
+        ``set_prefix(..., branch=)``, and the velocities are combined by :func:`cfg_combine`."""
         cfg, dev = self.cfg, self.device
+        guided = cfg_text_scale > 1.0 or cfg_img_scale > 1.0
+        if guided:
+            need = [0] + ([1] if cfg_text_scale > 1.0 else []) + ([2] if cfg_img_scale > 1.0 else [])
+            if max(need) >= self.branches or not all(self.b_ready[b] for b in need):
+                raise ValueError(f"guidance needs prefix banks {need}: build the engine with branches=3 and call set_prefix(..., branch=) for each")
+            if cfg_renorm_type not in ("global", "channel"):
+                raise NotImplementedError(f"cfg_renorm_type {cfg_renorm_type!r} (global or channel)")
         if tuple(x0.shape) != (self.body, self.width):
             raise ValueError(f"x0 must be {(self.body, self.width)}, got {tuple(x0.shape)}")
         if self.mode == "act":
@@ -354,24 +448,27 @@ class HaloEngine:
         self.text_rows.copy_(self._small[MODEL_P + "embed_tokens.weight"][text_ids.flatten().long().to(dev)].to(self.dtype))
         self.x.zero_()
         self.x[:, :self.width].copy_(x0.to(dev, self.dtype))
+        run = (lambda steps: self._loop_cfg(steps, cfg_text_scale, cfg_img_scale, cfg_renorm_min, cfg_renorm_type)) if guided \
+            else self._loop
+        key = (num_timesteps, cfg_text_scale, cfg_img_scale, cfg_renorm_min, cfg_renorm_type) if guided else num_timesteps
         if not use_graph:
-            self._loop(num_timesteps)
+            run(num_timesteps)
         else:
-            gph = self._graphs.get(num_timesteps)
+            gph = self._graphs.get(key)
             if gph is None:
                 snap = self.x.clone()
                 s = torch.cuda.Stream()
                 s.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(s):
-                    self._loop(2)                                      # warm-up: one step
+                    run(2)                                             # warm-up: one step
                 torch.cuda.current_stream().wait_stream(s)
                 self.schedule(num_timesteps)
                 gph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(gph, stream=s):
-                    self._loop(num_timesteps)
+                    run(num_timesteps)
                 torch.cuda.synchronize()
                 self.x.copy_(snap)
-                self._graphs[num_timesteps] = gph
+                self._graphs[key] = gph
             gph.replay()
         return self.x[:, :self.width]
 
@@ -384,5 +481,5 @@ class HaloEngine:
         self.cache.close()
 
 
-__all__ = ["HaloConfig", "HaloEngine", "TorchHalo", "tiny_halo_config", "halo_shapes", "random_halo_state_dict",
+__all__ = ["HaloConfig", "HaloEngine", "TorchHalo", "cfg_combine", "tiny_halo_config", "halo_shapes", "random_halo_state_dict",
            "timestep_embedding", "sinusoidal_pos_embedding", "euler_schedule", "SUFFIX"]

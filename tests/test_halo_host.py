@@ -36,3 +36,24 @@ def test_names_and_chunk_layout():
                                                 torch.tensor([4, 5]))
     emb = sd["language_model.model.embed_tokens.weight"]
     assert rows.shape == (cfg.action_rows + 2, cfg.hidden) and torch.equal(rows[0], emb[4]) and torch.equal(rows[-1], emb[5])
+
+
+def test_cfg_combine_rule():
+    import pytest
+    import torch
+    from rhinoforge_b200.models.halo import cfg_combine
+    g = torch.Generator().manual_seed(0)
+    v, vt, vi = (torch.randn(6, 4, generator=g) for _ in range(3))
+    assert cfg_combine(v, None, None, 1.0, 1.0) is v
+    t = vt + 3.0 * (v - vt)
+    both = vi + 1.5 * (t - vi)
+    scale = (v.norm() / (both.norm() + 1e-8)).clamp(0.0, 1.0)
+    assert torch.allclose(cfg_combine(v, vt, vi, 3.0, 1.5), both * scale, atol=1e-6)
+    rows = (v.norm(dim=-1, keepdim=True) / (t.norm(dim=-1, keepdim=True) + 1e-8)).clamp(0.3, 1.0)
+    assert torch.allclose(cfg_combine(v, vt, None, 3.0, 1.0, 0.3, "channel"), t * rows, atol=1e-6)
+    with pytest.raises(ValueError, match="cfg_text"):
+        cfg_combine(v, None, vi, 2.0, 1.0)
+    with pytest.raises(ValueError, match="cfg_img"):
+        cfg_combine(v, vt, None, 1.0, 2.0)
+    with pytest.raises(NotImplementedError):
+        cfg_combine(v, vt, vi, 2.0, 2.0, 0.0, "text_channel")
