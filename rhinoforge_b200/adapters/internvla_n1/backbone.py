@@ -115,7 +115,13 @@ def build_qwen25vl_backbone(model_dir: str, *, get_weight: Optional[Callable[[st
                 return self[key]
             except KeyError:
                 return default
-    cfg = qwen25_text_config(hf_config)
+    tc = _get(hf_config, "text_config", None) or hf_config
+    if isinstance(tc, Mapping):                                  # a plain config.json: the decoder reader takes attributes
+        from types import SimpleNamespace
+        tc = SimpleNamespace(**tc)
+        if getattr(tc, "rope_parameters", None) is None and getattr(tc, "rope_scaling", None) is not None:
+            tc.rope_parameters = {**tc.rope_scaling, "rope_theta": getattr(tc, "rope_theta", 1e6)}
+    cfg = qwen25_text_config(tc)
     vcfg = Qwen25VLVisionConfig.from_hf(_get(hf_config, "vision_config"))
     eng = Qwen25VLEngine(cfg, vcfg, text_get, _Vision(), image_token_id=int(_get(hf_config, "image_token_id", 151655)), device=device,
                          dtype=dtype, max_seq_len=max_seq_len, max_patches=max_patches, max_prefill_tokens=max_seq_len)

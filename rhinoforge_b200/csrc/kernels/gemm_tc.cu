@@ -84,11 +84,14 @@ struct alignas(8) GemmSmemCtl {
 // squares per token column.
 constexpr int kSsScratchBytes = (256 + 4 * 256) * (int)sizeof(float);
 
-// W8 = int8 weights (W8A16): TMA brings the int8 tile into a staging area of the stage, four extra
+// Converter warps of the quantised kernels: the block is 128 threads (producer, MMA issuer, epilogue) plus these.
+constexpr int kMaxConvWarps = 8;
+
+// W8 = int8 weights (W8A16): TMA brings the int8 tile into a staging area of the stage, the extra
 // converter warps widen it into the 128-byte-swizzled 16-bit tile the MMA reads, and the
 // per-output-channel scale is applied in the epilogue: (X . Q^T) * s.
 template <typename T, bool SWAP, bool DUAL, bool W8>
-__global__ void __launch_bounds__(W8 ? 256 : 128)
+__global__ void __launch_bounds__(W8 ? 128 + 32 * kMaxConvWarps : 128)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmW, const GemmTcParams p) {
   // No alignment slack: the W8A16 decode configuration fits two CTAs per SM only without it.  The swizzled
@@ -128,9 +131,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&ctl->full[s], 1);
       mbar_init(&ctl->empty[s], 1);
-      mbar_init(&ctl->ready[s], 4);
+      mbar_init(&ctl->ready[s], (blockDim.x - 128) >> 5);     // one arrival per converter warp
       mbar_init(&ctl->qfull[s], 1);
-      mbar_init(&ctl->qempty[s], 4);
+      mbar_init(&ctl->qempty[s], (blockDim.x - 128) >> 5);
     }
     mbar_init(&ctl->accum, 1);
     ctl->abort_flag = 0;
@@ -271,7 +274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
   // ------------------------------------------------- W8A16 converter warps ----
   if (W8 && warp >= 4) {
-    const int ct = tid - 128;
+    const int ct = tid - 128, cstep = (int)blockDim.x - 128;
     for (int i = 0; i < kb_count; ++i) {
       const int s = i % p.stages;
       const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
@@ -289,7 +292,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         uint8_t* dst = SWAP ? st + wt * kATileBytes : st + kATiles * kATileBytes + wt * b_tile_bytes;
         if (p.w4) {
           // 32 nibbles (one 16-byte piece = half a row) per thread and round -> four 16-byte pieces of the 16-bit tile
-          for (int idx = ct; idx < w_rows * 2; idx += 128) {
+          for (int idx = ct; idx < w_rows * 2; idx += cstep) {
             const int row = idx >> 1, h = idx & 1;
             const uint8_t* blk = src + (size_t)(row >> 7) * p.q_blk_bytes;
             const int r = row & 127;
@@ -317,7 +320,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         // 16 int8 (one 16-byte piece) per thread and round; consecutive threads take consecutive pieces, so a
         // warp reads 512 contiguous bytes (8 rows x 64) without bank conflicts
-        for (int idx = ct; idx < w_rows * 4; idx += 128) {
+        for (int idx = ct; idx < w_rows * 4; idx += cstep) {
           const int row = idx >> 2, h = idx & 3;
           const uint4 q = *reinterpret_cast<const uint4*>(src + row * kBK + h * 16);
           const int c0 = 2 * h, c1 = 2 * h + 1;
@@ -1105,6 +1108,17 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   return RF_OK;
 }
 
+// Converter warps per CTA of the quantised kernels (RF_W8_CONV_WARPS: 4 .. 8).  The widening is a chain of shared-memory
+// loads, byte permutes and stores; more warps per scheduler hide its latencies.
+static int conv_warps() {
+  static const int v = [] {
+    const char* e = getenv("RF_W8_CONV_WARPS");
+    const int n = e ? atoi(e) : 8;
+    return std::min(std::max(n, 4), kMaxConvWarps);
+  }();
+  return v;
+}
+
 template <typename T, bool SWAP, bool DUAL, bool W8>
 static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream) {
   auto kfn = gemm_tc_kernel<T, SWAP, DUAL, W8>;
@@ -1185,7 +1199,7 @@ static int launch_gemm(const RfGemm* g, const GemmPlan& pl, cudaStream_t stream)
     p.pf_ptr = reinterpret_cast<const uint8_t*>(g->prefetch);
     p.pf_chunks = (uint32_t)std::min<uint64_t>(g->prefetch_bytes / kPrefetchChunk, 1u << 20);
   }
-  RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.grid_x, pl.grid_y, pl.splits), dim3(W8 ? 256 : 128), pl.smem_bytes, stream,
+  RF_CUDA_CHECK(::rf::launch_k(kfn, dim3(pl.grid_x, pl.grid_y, pl.splits), dim3(W8 ? 128 + 32 * conv_warps() : 128), pl.smem_bytes, stream,
                                pl.splits, tmA, tmB, tmW, p));
   ::rf::count_launch();
   return RF_OK;

@@ -34,10 +34,8 @@ def qwen25_text_config(hf_config) -> DecoderConfig:
     cfg = DecoderConfig.from_hf(tc)
     if cfg.mrope_section is None:
         raise UnsupportedModelError("Qwen2.5-VL text config carries no rope_scaling.mrope_section")
-    cfg.mrope_interleaved = False
-    cfg.attention_bias = True
-    cfg.qk_norm = False
-    return cfg
+    import dataclasses
+    return dataclasses.replace(cfg, mrope_interleaved=False, attention_bias=True, qk_norm=False)
 
 
 class Qwen25VLEngine:

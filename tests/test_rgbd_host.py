@@ -69,3 +69,17 @@ def test_backbone_preflight():
     preflight(dict(text_config={**PROFILE, "hidden_size": 2048}, vision_config={}), strict=False)
     with pytest.raises(UnsupportedModelError, match="vision_config"):
         preflight(dict(text_config=dict(PROFILE)))
+
+
+def test_qwen25_text_config_from_plain_config():
+    from types import SimpleNamespace
+    from rhinoforge_b200.models.qwen25_vl import qwen25_text_config
+    from rhinoforge_b200.runtime.errors import UnsupportedModelError
+    tc = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=2, num_key_value_heads=1,
+              vocab_size=200, max_position_embeddings=512, rms_norm_eps=1e-6, model_type="qwen2_5_vl_text",
+              rope_parameters={"rope_type": "default", "rope_theta": 1e4, "mrope_section": [8, 12, 12]})
+    c = qwen25_text_config(SimpleNamespace(**tc))
+    assert c.mrope_section == (8, 12, 12) and not c.mrope_interleaved and c.attention_bias and not c.qk_norm
+    import pytest
+    with pytest.raises(UnsupportedModelError, match="mrope_section"):
+        qwen25_text_config(SimpleNamespace(**{**tc, "rope_parameters": {"rope_type": "default", "rope_theta": 1e4}}))
