@@ -85,13 +85,13 @@ struct alignas(8) GemmSmemCtl {
 constexpr int kSsScratchBytes = (256 + 4 * 256) * (int)sizeof(float);
 
 // Converter warps of the quantised kernels: the block is 128 threads (producer, MMA issuer, epilogue) plus these.
-constexpr int kMaxConvWarps = 8;
+constexpr int kMaxConvWarps = 6;     // two CTAs of 128 + 192 threads still fit an SM's register file
 
 // W8 = int8 weights (W8A16): TMA brings the int8 tile into a staging area of the stage, the extra
 // converter warps widen it into the 128-byte-swizzled 16-bit tile the MMA reads, and the
 // per-output-channel scale is applied in the epilogue: (X . Q^T) * s.
 template <typename T, bool SWAP, bool DUAL, bool W8>
-__global__ void __launch_bounds__(W8 ? 128 + 32 * kMaxConvWarps : 128)
+__global__ void __launch_bounds__(W8 ? 128 + 32 * kMaxConvWarps : 128, W8 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmW, const GemmTcParams p) {
   // No alignment slack: the W8A16 decode configuration fits two CTAs per SM only without it.  The swizzled
@@ -1108,12 +1108,12 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
   return RF_OK;
 }
 
-// Converter warps per CTA of the quantised kernels (RF_W8_CONV_WARPS: 4 .. 8).  The widening is a chain of shared-memory
+// Converter warps per CTA of the quantised kernels (RF_W8_CONV_WARPS: 4 .. 6).  The widening is a chain of shared-memory
 // loads, byte permutes and stores; more warps per scheduler hide its latencies.
 static int conv_warps() {
   static const int v = [] {
     const char* e = getenv("RF_W8_CONV_WARPS");
-    const int n = e ? atoi(e) : 8;
+    const int n = e ? atoi(e) : 4;
     return std::min(std::max(n, 4), kMaxConvWarps);
   }();
   return v;
