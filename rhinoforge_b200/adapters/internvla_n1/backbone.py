@@ -52,7 +52,7 @@ class Qwen25VLBackbone:
         if n_rows > t.max_tokens:
             raise ValueError(f"{n_rows} rows exceed one prefill launch ({t.max_tokens}): build with a larger max_prefill_tokens")
         rows = t.hidden[n_rows - self.num_latent:n_rows]
-        out = K.rmsnorm(rows, t.final_norm, self.engine.cfg.rms_norm_eps)
+        out = K.rmsnorm(rows, t.final_norm, self.engine.cfg.rms_eps)
         t.check_status()
         return out.float()[None]
 
