@@ -1284,6 +1284,8 @@ extern "C" int rf_gemm_plan_info(const RfGemm* g, int32_t* out);
 
 namespace rf {
 bool gemm_sk_eligible(const RfGemm* g, int* ctas);               // gemm_sk.cu: persistent stream-K kernel for small M
+bool gemm_small_eligible(const RfGemm* g);                         // gemm_small.cu: latency-bound shapes (few rows, small weight)
+int gemm_small_run(const RfGemm* g, cudaStream_t stream);
 void gemm_sk_scratch(const RfGemm* g, uint64_t* ws_bytes, int32_t* flags);
 int launch_gemm_sk(const RfGemm* g, cudaStream_t stream);
 bool gemm_ps_eligible(const RfGemm* g, bool swap, int splits);   // gemm_ps.cu: persistent kernel for large M
@@ -1294,6 +1296,7 @@ int widen_packed(const void* src, void* dst, int64_t blocks, int dtype, cudaStre
 static int run_gemm(const RfGemm* g, cudaStream_t stream, bool w8) {
   int rc = check_gemm(g);
   if (rc) return rc;
+  if (!w8 && rf::gemm_small_eligible(g)) return rf::gemm_small_run(g, stream);      // latency-bound shapes: gemm_small.cu
   if (!w8 && rf::gemm_sk_eligible(g, nullptr)) return rf::launch_gemm_sk(g, stream);
   GemmPlan pl;
   rc = plan_gemm(g, &pl);

@@ -776,3 +776,45 @@ def test_gemm_folded_rmsnorm(dt, M, H, I, splits, status):
     z = hn @ w2.float().t() + bias.float()
     ref = torch.nn.functional.silu(z[:, :I]) * z[:, I:]
     _close(y, ref, dt, scale=max(1.0, ref.abs().max().item()) * (4 if dt == torch.bfloat16 else 1))
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M,N,K", [(128, 384, 1536), (128, 1536, 384), (41, 1536, 2048), (50, 1024, 4096), (31, 1024, 1024),
+                                   (7, 72, 136), (130, 200, 72), (256, 512, 640), (1, 384, 384)])
+@pytest.mark.parametrize("packed", [False, True])
+def test_gemm_small_latency_kernel(dt, M, N, K, packed, status, monkeypatch):
+    """Shapes the latency-bound kernel takes (few rows, small weight): every epilogue option against fp32 PyTorch, and the
+    same call with the kernel switched off (the streaming kernel) within rounding."""
+    from rhinoforge_b200.ops import kernels as K_
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(dt)
+    b = torch.randn(N, device="cuda").to(dt)
+    r = torch.randn(M, N, device="cuda").to(dt)
+    wk = K_.pack_weight(w) if packed else w
+    kw = dict(packed_shape=(N, K)) if packed else {}
+    ref = x.float() @ w.float().t()
+    _close(K_.gemm(x, wk, **kw), ref, dt, scale=max(1.0, float(ref.abs().max())))
+    full = torch.nn.functional.gelu(ref + b.float(), approximate="tanh") + r.float()
+    got = K_.gemm(x, wk, bias=b, act="gelu_tanh", residual=r, **kw)
+    _close(got, full, dt, scale=max(1.0, float(full.abs().max())))
+    # strided output / input views
+    buf = torch.zeros(M, N + 16, device="cuda", dtype=dt)
+    K_.gemm(x, wk, out=buf[:, 8:8 + N], **kw)
+    _close(buf[:, 8:8 + N], ref, dt, scale=max(1.0, float(ref.abs().max())))
+    assert float(buf[:, :8].abs().max()) == 0 and float(buf[:, 8 + N:].abs().max()) == 0
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("M,N,K", [(50, 4096, 1024), (128, 1536, 384), (31, 136, 200)])
+@pytest.mark.parametrize("packed", [False, True])
+def test_gemm_small_dual_glu(dt, M, N, K, packed, status):
+    from rhinoforge_b200.ops import kernels as K_
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dt)
+    w = (torch.randn(2 * N, K, device="cuda") * 0.05).to(dt)
+    b = (torch.randn(2 * N, device="cuda") * 0.1).to(dt)
+    wk = K_.pack_weight(w, sections=2) if packed else w
+    kw = dict(packed_shape=(2 * N, K)) if packed else {}
+    gte, up = x.float() @ w[:N].float().t() + b[:N].float(), x.float() @ w[N:].float().t() + b[N:].float()
+    ref = torch.nn.functional.silu(gte) * up
+    got = K_.gemm(x, wk, bias=b, act="silu_mul", dual=True, **kw)
+    _close(got, ref, dt, scale=max(1.0, float(ref.abs().max())))
