@@ -18,8 +18,6 @@ import sys
 import time
 from pathlib import Path
 
-import torch
-
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 
@@ -122,9 +120,17 @@ FAMILIES = dict(navdp=navdp, gr00t=gr00t, nextdit=nextdit, rhinovla=rhinovla, rg
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--family", choices=sorted(FAMILIES), required=True)
+    ap.add_argument("--family", choices=sorted(FAMILIES))
     ap.add_argument("--tiny", action="store_true")
+    ap.add_argument("--check-config", action="store_true", help="validate the arguments and exit without loading torch or the runtime")
     a = ap.parse_args()
+    if a.check_config:
+        print("configuration OK")
+        return 0
+    if a.family is None:
+        ap.error("--family is required")
+    global torch
+    import torch
     if not torch.cuda.is_available():
         print("this example needs a CUDA device")
         return 2

@@ -661,11 +661,12 @@ namespace rf {
 int launch_prefill_tc(const RfAttn* a, const AttnParams& p, cudaStream_t s);   // attention_tc.cu
 }
 
-int rf_attn_wide(const RfAttn* a, rf_stream_t stream);   // attention_wide.cu: head sizes beyond 256
+int rf_attn_wide(const RfAttn* a, rf_stream_t stream);   // attention_wide.cu: head sizes beyond 256, and short problems
+bool rf_attn_tiny_eligible(const RfAttn* a);
 
 extern "C" int rf_attn_prefill(const RfAttn* a, rf_stream_t stream) {
   RF_SKIP_IF_REPLAYING();
-  if (a && a->hd == 512) return rf_attn_wide(a, stream);
+  if (a && (a->hd == 512 || rf_attn_tiny_eligible(a))) return rf_attn_wide(a, stream);
   AttnParams p;
   int rc = fill_params(a, &p);
   if (rc) return rc;

@@ -12,6 +12,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "../common/dtype.cuh"
 #include "../common/host_util.h"
 #include "../common/ptx.cuh"
@@ -236,14 +238,35 @@ attn_wide_kernel(const WideParams p) {
 
 using namespace rf;
 
-// Entry used by rf_attn_prefill / rf_attn_decode for head sizes the tensor-memory kernels do not take.
+// Short problems on heads of 64 / 128 (a few dozen query rows over at most a few hundred keys: the self- and
+// cross-attention of the action heads) also run here: no tensor maps, no tensor memory, one cp.async round trip per
+// 32-key tile, which is less fixed cost than the tensor-memory kernel's set-up.  RF_ATTN_TINY=0 turns that routing off.
+bool rf_attn_tiny_eligible(const RfAttn* a) {
+  static const bool on = [] { const char* e = getenv("RF_ATTN_TINY"); return !(e && e[0] == '0'); }();
+  if (!on || !a || a->k_pool || !a->k || !a->v || a->mask || a->seg_q || a->seg_k) return false;
+  if (a->hd != 64 && a->hd != 128) return false;
+  if (a->ldq % 8 || a->ldk % 8 || a->ldv % 8 || a->ldo % 2) return false;
+  const int max_q = a->q_len ? a->max_q_len : 1;
+  return max_q > 0 && max_q <= 64 && a->max_kv_len > 0 && a->max_kv_len <= 512;
+}
+
+template <typename T, int HD>
+static int launch_wide(const WideParams& p, dim3 grid, cudaStream_t s) {
+  constexpr size_t smem = (size_t)(kWideBM + 2 * kWideBN) * (HD + kWidePad) * 2;
+  RF_ALLOW_SMEM_PER_DEVICE((attn_wide_kernel<T, HD>), smem);
+  RF_CUDA_CHECK(::rf::launch_k(attn_wide_kernel<T, HD>, grid, dim3(kWideThreads), smem, s, 1, p));
+  ::rf::count_launch();
+  return RF_OK;
+}
+
+// Entry used by rf_attn_prefill for head sizes the tensor-memory kernels do not take, and for short problems.
 int rf_attn_wide(const RfAttn* a, rf_stream_t stream) {
   RF_SKIP_IF_REPLAYING();
   RF_REQUIRE(a && a->q && a->out, "attention needs q and out");
-  RF_REQUIRE(a->hd == 512, "wide attention is built for head_dim 512, got %d", a->hd);
+  RF_REQUIRE(a->hd == 512 || a->hd == 128 || a->hd == 64, "register-accumulator attention takes head_dim 64 / 128 / 512, got %d", a->hd);
   RF_REQUIRE(a->Hkv > 0 && a->Hq % a->Hkv == 0, "attention heads %d / kv heads %d", a->Hq, a->Hkv);
-  RF_REQUIRE(a->k && a->v && a->kv_start && a->kv_len && !a->k_pool, "head_dim 512 takes contiguous K / V rows (k, v, kv_start, kv_len)");
-  RF_REQUIRE(!a->mask && !a->seg_q && !a->seg_k, "head_dim 512 takes causal / window masks only");
+  RF_REQUIRE(a->k && a->v && a->kv_start && a->kv_len && !a->k_pool, "this attention path takes contiguous K / V rows (k, v, kv_start, kv_len)");
+  RF_REQUIRE(!a->mask && !a->seg_q && !a->seg_k, "this attention path takes causal / window masks only");
   RF_REQUIRE(a->ldq % 8 == 0 && a->ldk % 8 == 0 && a->ldv % 8 == 0 && a->ldo % 2 == 0, "attention row pitches must be multiples of 16 bytes");
   RF_REQUIRE(a->num_seqs > 0 && (a->dtype == 0 || a->dtype == 1), "attention needs sequences and a 16-bit dtype");
   WideParams p;
@@ -255,15 +278,13 @@ int rf_attn_wide(const RfAttn* a, rf_stream_t stream) {
   p.scale_log2 = scale * 1.4426950408889634f;
   const int max_q = a->q_len ? (a->max_q_len > 0 ? a->max_q_len : 1) : 1;
   const dim3 grid((max_q + kWideBM - 1) / kWideBM, a->Hq, a->num_seqs);
-  constexpr size_t smem = (size_t)(kWideBM + 2 * kWideBN) * (512 + kWidePad) * 2;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (a->dtype == 0) {
-    RF_ALLOW_SMEM_PER_DEVICE((attn_wide_kernel<__half, 512>), smem);
-    RF_CUDA_CHECK(::rf::launch_k(attn_wide_kernel<__half, 512>, grid, dim3(kWideThreads), smem, s, 1, p));
-  } else {
-    RF_ALLOW_SMEM_PER_DEVICE((attn_wide_kernel<__nv_bfloat16, 512>), smem);
-    RF_CUDA_CHECK(::rf::launch_k(attn_wide_kernel<__nv_bfloat16, 512>, grid, dim3(kWideThreads), smem, s, 1, p));
+    if (a->hd == 512) return launch_wide<__half, 512>(p, grid, s);
+    if (a->hd == 128) return launch_wide<__half, 128>(p, grid, s);
+    return launch_wide<__half, 64>(p, grid, s);
   }
-  ::rf::count_launch();
-  return RF_OK;
+  if (a->hd == 512) return launch_wide<__nv_bfloat16, 512>(p, grid, s);
+  if (a->hd == 128) return launch_wide<__nv_bfloat16, 128>(p, grid, s);
+  return launch_wide<__nv_bfloat16, 64>(p, grid, s);
 }

@@ -301,6 +301,9 @@ bool gemm_small_eligible(const RfGemm* g) {
   // 12.4 us there against 13.8 us here, 41 x 1536 x 2048 8.5 against 9.6); above 64 rows this kernel wins everywhere
   // that was measured (128 x 1536 x 384: 7.6 us against 19.6 us)
   if (g->M <= 64 && g->K > 1536) return false;
+  // up to 32 rows the streaming kernel runs 32-column tiles and wins on all but the smallest weights (31 x 2560 x 1024:
+  // 6.8 us there against 9.2 us here; 31 x 4096 x 1024: 8.1 against 9.9; 24 x 1152 x 384: 7.5 against 5.2)
+  if (g->M <= 32 && (long)g->N * g->K * (dual ? 2 : 1) > (1L << 20)) return false;
   static const long max_elems = [] { const char* e = getenv("RF_GEMM_SMALL_MAX_MELEMS"); return (long)(e ? atoi(e) : 12) << 20; }();
   return (long)g->N * g->K * (dual ? 2 : 1) <= max_elems;
 }

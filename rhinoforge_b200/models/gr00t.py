@@ -368,7 +368,7 @@ class Gr00tEngine:
             K.gemm(n, L["qkv_w"], packed_shape=(3 * VD, cfg.vl_dim), bias=L["qkv_b"], out=qkv)
             K.attention_prefill(qkv[:, :VD], att, Hq=cfg.vl_heads, Hkv=cfg.vl_heads, hd=self.vhp, q_start=self.q_start, q_len=self.vl_q_len,
                                 kv_len=self.vl_q_len, max_q_len=S, k=qkv[:, VD:2 * VD], v=qkv[:, 2 * VD:], kv_start=self.q_start,
-                                causal=False, scale=1.0 / math.sqrt(cfg.vl_head_dim), status=self.status)
+                                causal=False, scale=1.0 / math.sqrt(cfg.vl_head_dim), status=self.status, max_kv_len=S)
             K.gemm(att, L["o_w"], packed_shape=(cfg.vl_dim, VD), bias=L["o_b"], residual=x, out=x)
             K.layernorm(x, L["norm3_w"], L["norm3_b"], cfg.eps, out=n)
             K.gemm(n, L["f1_w"], packed_shape=(cfg.vl_ff, cfg.vl_dim), bias=L["f1_b"], act="gelu_tanh", out=ff)
@@ -400,12 +400,12 @@ class Gr00tEngine:
                 K.attention_prefill(self.q, self.att, Hq=cfg.heads, Hkv=cfg.heads, hd=self.hp, q_start=self.q_start, q_len=self.q_len,
                                     kv_len=self.kv_text_len if text else self.kv_img_len, max_q_len=Q, k=kv[:, :D], v=kv[:, D:],
                                     kv_start=self.kv_text_start if text else self.kv_img_start, causal=False, scale=scale,
-                                    status=self.status)
+                                    status=self.status, max_kv_len=self.max_vl)
             else:
                 K.gemm(self.hn, L["qkv_w"], packed_shape=(3 * D, H), bias=L["qkv_b"], out=self.qkv)
                 K.attention_prefill(self.qkv[:, :D], self.att, Hq=cfg.heads, Hkv=cfg.heads, hd=self.hp, q_start=self.q_start,
                                     q_len=self.q_len, kv_len=self.kv_self, max_q_len=Q, k=self.qkv[:, D:2 * D], v=self.qkv[:, 2 * D:],
-                                    kv_start=self.q_start, causal=False, scale=scale, status=self.status)
+                                    kv_start=self.q_start, causal=False, scale=scale, status=self.status, max_kv_len=Q)
             self._tail(L)
         K.layernorm(self.h, self.out_w[s], self.out_b[s], cfg.eps_out, out=self.hn)
         K.gemm(self.hn, self.po2_w, packed_shape=(cfg.model_out, H), bias=self.po2_b, out=self.mo)

@@ -252,13 +252,13 @@ class NavdpEngine:
             K.gemm(hn, L["s_qkv_w"], packed_shape=(3 * D, cfg.hidden), bias=L["s_qkv_b"], out=qkv)
             K.attention_prefill(qkv[:, :D], att, Hq=cfg.heads, Hkv=cfg.heads, hd=self.hd_pad, q_start=m["q_start"], q_len=m["q_len"],
                                 kv_len=m["kv_self"], max_q_len=P, k=qkv[:, D:2 * D], v=qkv[:, 2 * D:], kv_start=m["q_start"],
-                                causal=True, scale=scale, status=self.status)
+                                causal=True, scale=scale, status=self.status, max_kv_len=P)
             K.gemm(att, L["s_o_w"], packed_shape=(cfg.hidden, D), bias=L["s_o_b"], residual=h, out=h)
             K.layernorm(h, L["n2_w"], L["n2_b"], cfg.eps, out=hn)
             K.gemm(hn, L["c_q_w"], packed_shape=(D, cfg.hidden), bias=L["c_q_b"], out=q)
             K.attention_prefill(q, att, Hq=cfg.heads, Hkv=cfg.heads, hd=self.hd_pad, q_start=m["q_start"], q_len=m["q_len"],
                                 kv_len=m["kv_mem"], max_q_len=P, k=kv[:, :D], v=kv[:, D:], kv_start=m["kv_start_step"][k],
-                                causal=False, scale=scale, status=self.status)
+                                causal=False, scale=scale, status=self.status, max_kv_len=cfg.memory_len)
             K.gemm(att, L["c_o_w"], packed_shape=(cfg.hidden, D), bias=L["c_o_b"], residual=h, out=h)
             K.layernorm(h, L["n3_w"], L["n3_b"], cfg.eps, out=hn)
             K.gemm(hn, L["ff1_w"], packed_shape=(cfg.ff, cfg.hidden), bias=L["ff1_b"], act="gelu_erf", out=ff)

@@ -333,10 +333,11 @@ class NextDiTEngine:
             K.layernorm(k, L["sk_w"], L["sk_b"], cfg.qk_eps, out=k)
             K.layernorm(cq, L["cq_w"], L["cq_b"], cfg.qk_eps, out=cq)
             K.attention_prefill(q, att[:, :H], Hq=cfg.heads, Hkv=cfg.heads, hd=cfg.head_dim, q_start=m["q_start"], q_len=m["q_len"],
-                                kv_len=m["q_len"], max_q_len=P, k=k, v=v, kv_start=m["q_start"], causal=False, scale=scale, status=self.status)
+                                kv_len=m["q_len"], max_q_len=P, k=k, v=v, kv_start=m["q_start"], causal=False, scale=scale, status=self.status,
+                                max_kv_len=P)
             K.attention_prefill(cq, att[:, H:], Hq=cfg.heads, Hkv=cfg.heads, hd=cfg.head_dim, q_start=m["q_start"], q_len=m["q_len"],
                                 kv_len=self.cross_len[:b], max_q_len=P, k=kv[:, :H], v=kv[:, H:], kv_start=m["zero"], causal=False,
-                                scale=scale, status=self.status)
+                                scale=scale, status=self.status, max_kv_len=cfg.max_cross)
             K.gemm(att, L["o_w"], packed_shape=(H, 2 * H), out=a)
             K.rmsnorm(a, self.tab[s, i, 1], cfg.eps, out=tmp)
             h.add_(tmp)

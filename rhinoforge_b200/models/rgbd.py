@@ -296,7 +296,8 @@ class RgbdEncoder:
         for L in self.former:
             qkv = K.gemm(x, L["s_qkv_w"], packed_shape=(3 * FD, H), bias=L["s_qkv_b"])
             K.attention_prefill(qkv[:, :FD], att, Hq=fh, Hkv=fh, hd=self.fhp, q_start=q_start, q_len=q_len, kv_len=q_len, max_q_len=Q,
-                                k=qkv[:, FD:2 * FD], v=qkv[:, 2 * FD:], kv_start=q_start, causal=False, scale=scale, status=self.status)
+                                k=qkv[:, FD:2 * FD], v=qkv[:, 2 * FD:], kv_start=q_start, causal=False, scale=scale, status=self.status,
+                                max_kv_len=Q)
             y = K.gemm(att, L["s_o_w"], packed_shape=(H, FD), bias=L["s_o_b"], residual=x)
             x = K.layernorm(y, L["n1_w"], L["n1_b"], c.former_eps)
             q = K.gemm(x, L["c_q_w"], packed_shape=(FD, H), bias=L["c_q_b"])

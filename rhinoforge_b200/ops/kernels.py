@@ -409,9 +409,11 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, *, Hq: int, Hkv: int, 
                       kv_start: Optional[torch.Tensor] = None, causal: bool = True, window: int = 0,
                       mask: Optional[torch.Tensor] = None, seg_q: Optional[torch.Tensor] = None,
                       seg_k: Optional[torch.Tensor] = None, scale: float = 0.0,
-                      status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      status: Optional[torch.Tensor] = None, max_kv_len: int = 0) -> torch.Tensor:
     """Flash-style attention over ``q`` rows [tokens, Hq*hd]; KV from the paged pool or from
-    contiguous ``k``/``v`` [rows, Hkv*hd] (may be column slices of a packed qkv buffer)."""
+    contiguous ``k``/``v`` [rows, Hkv*hd] (may be column slices of a packed qkv buffer).
+    ``max_kv_len``: a host-side bound on ``kv_len`` (0: unknown); short contiguous problems (at most 64 query rows per
+    sequence over at most 512 keys, heads of 64 / 128, causal / window masks only) then take the low-latency kernel."""
     a = N.RfAttn()
     a.q, a.ldq, a.out, a.ldo = q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0)
     a.q_rows_total = q.shape[0]
@@ -424,6 +426,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, *, Hq: int, Hkv: int, 
         a.kv_start = _i32(kv_start)
     a.q_start, a.q_len, a.kv_len = _i32(q_start), _i32(q_len), _i32(kv_len)
     a.max_q_len = max_q_len
+    a.max_kv_len = int(max_kv_len)
     a.causal, a.window = int(causal), window
     if mask is not None:
         assert mask.dtype in (torch.uint8, torch.bool) and mask.stride(-1) == 1

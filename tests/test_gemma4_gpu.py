@@ -52,6 +52,41 @@ def test_attention_head_dim_512(dtype, causal, window):
         o += ql
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("causal,window", [(True, 0), (True, 9), (False, 0)])
+def test_attention_short_problem_route(hd, causal, window):
+    """At most 64 query rows over at most 512 keys with a host-side key bound: the register-accumulator kernel takes heads of
+    64 / 128 too; its result against fp32, and the launch goes to that kernel (its name in the launch tally)."""
+    from rhinoforge_b200.ops import kernels as K
+    torch.manual_seed(1)
+    dtype = torch.float16
+    Hq, Hkv = 6, 3
+    qlens, kvlens = [24, 1, 41, 64], [24, 34, 300, 64]
+    Tq, rows = sum(qlens), 320
+    q = (torch.randn(Tq, Hq * hd, device="cuda") * 0.4).to(dtype)
+    kc = (torch.randn(4 * rows, Hkv * hd, device="cuda") * 0.4).to(dtype)
+    vc = torch.randn(4 * rows, Hkv * hd, device="cuda").to(dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    q_start = i32([0, 24, 25, 66])
+    scale = 1.0 / math.sqrt(hd)
+    outs = []
+    for bound in (300, 0):                                       # 0: bound unknown, the tensor-memory kernel runs
+        out = torch.zeros(Tq, Hq * hd, device="cuda", dtype=dtype)
+        K.attention_prefill(q, out, Hq=Hq, Hkv=Hkv, hd=hd, q_start=q_start, q_len=i32(qlens), kv_len=i32(kvlens), max_q_len=max(qlens),
+                            k=kc, v=vc, kv_start=i32([0, rows, 2 * rows, 3 * rows]), causal=causal, window=window, scale=scale,
+                            max_kv_len=bound)
+        torch.cuda.synchronize()
+        outs.append(out)
+    o = 0
+    for s, (ql, kl) in enumerate(zip(qlens, kvlens)):
+        ref = _sdpa_ref(q[o:o + ql].float(), kc[s * rows:s * rows + kl].float(), vc[s * rows:s * rows + kl].float(), ql, kl, Hq, Hkv, hd,
+                        causal, window, scale)
+        for out in outs:
+            err = float((out[o:o + ql].float() - ref).abs().max())
+            assert err < 6e-3, (s, err)
+        o += ql
+
+
 def _tiny_gemma4(**over):
     from transformers.models.gemma4.configuration_gemma4 import Gemma4TextConfig
     from transformers.models.gemma4.modeling_gemma4 import Gemma4ForCausalLM
