@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import statistics
 import sys
 from pathlib import Path
@@ -196,6 +197,65 @@ def bench_gdn(seqs, length, hk, hv, *, dk=128, dv=128, dtype=torch.float16):
                   hk=hk, hv=hv, us_per_token=round(us / length, 3))
 
 
+def time_hot_us(fn, n: int = 50) -> float:
+    """Mean in-stream time of ``n`` back-to-back launches of one closure in a CUDA graph, operands L2-resident: the regime
+    of the action heads' denoise loops, where the same few MB of weights serve every step."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        for _ in range(n):
+            fn()
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (5 * n)
+
+
+def heads() -> None:
+    """The latency-bound shapes of the action heads: short attention with and without the host-side key bound (which
+    selects the register-accumulator kernel), and few-row GEMMs on the kernel the router picks (set ``RF_GEMM_SMALL=0`` to
+    time the streaming kernel on the same shapes) against ``torch.matmul``."""
+    import math
+    from rhinoforge_b200.ops import kernels as K
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    for name, B, Q, KV, H, hd in (("navdp self", 4, 24, 24, 8, 64), ("navdp cross", 4, 24, 34, 8, 64), ("nextdit self", 4, 32, 32, 12, 64),
+                                  ("nextdit cross", 4, 32, 260, 12, 64), ("gr00t self", 1, 41, 41, 32, 64), ("gr00t cross", 1, 41, 148, 32, 64),
+                                  ("rgbd self", 1, 32, 32, 6, 64), ("50x350 hd128", 1, 50, 350, 16, 128), ("64x512 hd128", 2, 64, 512, 16, 128)):
+        q = torch.randn(B * Q, H * hd, device="cuda", dtype=torch.float16) * 0.3
+        k = torch.randn(B * KV, H * hd, device="cuda", dtype=torch.float16) * 0.3
+        v = torch.randn(B * KV, H * hd, device="cuda", dtype=torch.float16)
+        out = torch.empty_like(q)
+        qs, ql, ks, kl = i32([j * Q for j in range(B)]), i32([Q] * B), i32([j * KV for j in range(B)]), i32([KV] * B)
+        r = {}
+        for arm, bound in (("bounded_us", KV), ("unbounded_us", 0)):
+            r[arm] = round(time_hot_us(lambda: K.attention_prefill(q, out, Hq=H, Hkv=H, hd=hd, q_start=qs, q_len=ql, kv_len=kl, max_q_len=Q,
+                                                                   k=k, v=v, kv_start=ks, causal=False, scale=1 / math.sqrt(hd),
+                                                                   max_kv_len=bound)), 2)
+        print(json.dumps({"kernel": "attention_prefill", "case": name, "seqs": B, "q": Q, "kv": KV, "heads": H, "hd": hd, **r}), flush=True)
+    for M, N, Kd, dual in ((128, 384, 1536, False), (128, 1536, 384, False), (128, 1152, 384, False), (96, 384, 384, False), (24, 1152, 384, False),
+                           (24, 384, 384, False), (31, 1024, 1024, False), (31, 2560, 1024, False), (31, 4096, 1024, True), (50, 2560, 1024, False),
+                           (50, 4096, 1024, True), (50, 1024, 2048, False), (41, 4608, 1536, False), (41, 1536, 6144, False)):
+        x = torch.randn(M, Kd, device="cuda", dtype=torch.float16)
+        w = torch.randn(N * (2 if dual else 1), Kd, device="cuda", dtype=torch.float16) * 0.05
+        wp = K.pack_weight(w, sections=2) if dual else K.pack_weight(w)
+        out = torch.empty(M, N, device="cuda", dtype=torch.float16)
+        kw = dict(act="silu_mul", dual=True) if dual else {}
+        us = time_hot_us(lambda: K.gemm(x, wp, packed_shape=(w.shape[0], Kd), out=out, **kw))
+        ref = torch.empty(M, w.shape[0], device="cuda", dtype=torch.float16)
+        lib = time_hot_us(lambda: torch.matmul(x, w.t(), out=ref))
+        print(json.dumps({"kernel": "gemm", "m": M, "n": N, "k": Kd, "dual": dual, "small_kernel": os.environ.get("RF_GEMM_SMALL", "1") != "0",
+                          "us": round(us, 2), "torch_matmul_us": round(lib, 2)}), flush=True)
+
+
 def sweep() -> None:
     """Split-K factors around the planner's choice for the Qwen3-8B decode GEMMs and two mid-size GEMMs."""
     for shape in ((64, 6144, 4096, False), (64, 4096, 4096, False), (64, 12288, 4096, True), (64, 4096, 12288, False),
@@ -227,7 +287,7 @@ def suite() -> None:
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["gemm", "attn_prefill", "attn_decode", "gdn", "suite", "sweep"])
+    ap.add_argument("what", choices=["gemm", "attn_prefill", "attn_decode", "gdn", "suite", "sweep", "heads"])
     for name, d in (("m", 64), ("n", 4096), ("k", 4096), ("seqs", 4), ("len", 2048), ("heads", 32), ("kv-heads", 8),
                     ("hd", 128), ("hk", 16), ("hv", 32)):
         ap.add_argument(f"--{name}", type=int, default=d)
@@ -251,6 +311,8 @@ def main() -> int:
         bench_gdn(a.seqs, a.len, a.hk, a.hv, dtype=dt)
     elif a.what == "sweep":
         sweep()
+    elif a.what == "heads":
+        heads()
     else:
         suite()
     return 0

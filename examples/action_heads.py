@@ -21,7 +21,19 @@ from pathlib import Path
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 
+PROFILE = False
+
+
 def timed(fn, reps: int = 5):
+    if PROFILE:                      # three warm-up calls, then one call inside a profiler range (ncu --profile-from-start off)
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        out = fn()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        return out, float("nan")
     fn()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -122,6 +134,8 @@ def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--family", choices=sorted(FAMILIES))
     ap.add_argument("--tiny", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="run the call once inside cudaProfilerStart/Stop after three warm-up calls (for ncu --profile-from-start off)")
     ap.add_argument("--check-config", action="store_true", help="validate the arguments and exit without loading torch or the runtime")
     a = ap.parse_args()
     if a.check_config:
@@ -129,8 +143,9 @@ def main() -> int:
         return 0
     if a.family is None:
         ap.error("--family is required")
-    global torch
+    global torch, PROFILE
     import torch
+    PROFILE = a.profile
     if not torch.cuda.is_available():
         print("this example needs a CUDA device")
         return 2

@@ -45,7 +45,7 @@ class RfGemm(C.Structure):
         ("prefetch", C.c_void_p), ("prefetch_bytes", C.c_uint64),
         ("w_bits", C.c_int32), ("w_group", C.c_int32), ("w_fp4", C.c_int32), ("ss_tiles", C.c_int32),
         ("ss_out", C.c_void_p), ("ss_in", C.c_void_p), ("ss_ld", C.c_int32), ("ss_dim", C.c_int32),
-        ("ss_eps", C.c_float), ("reserved0", C.c_int32),
+        ("ss_eps", C.c_float), ("streaming_only", C.c_int32),
     ]
 
 
@@ -119,7 +119,7 @@ class RfStackConfig(C.Structure):
                                          "moe_experts", "moe_top_k", "moe_expert_inter", "moe_score_fn",
                                          "moe_norm_topk")] + [("moe_routed_scale", C.c_float)] + \
                [("weights_bits", C.c_int32), ("weights_group", C.c_int32), ("norm_folded", C.c_int32),
-                ("reserved0", C.c_int32)]
+                ("gemm_streaming_only", C.c_int32)]
 
 
 class RfLayerWeights(C.Structure):
@@ -145,6 +145,7 @@ class RfArRows(C.Structure):
         ("partial_tab", C.c_void_p), ("out_tab", C.c_void_p), ("norm_tab", C.c_void_p), ("ar_flags", C.c_void_p),
         ("ar_state", C.c_void_p), ("flag_base", C.c_int32), ("add_residual", C.c_int32),
         ("norm_w", C.c_void_p), ("eps", C.c_float), ("norm_mode", C.c_int32), ("status", C.c_void_p), ("dtype", C.c_int32),
+        ("out_local", C.c_int32),
     ]
 
 

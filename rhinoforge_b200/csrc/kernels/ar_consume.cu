@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(kArThreads) ar_consume_kernel(const ArConsumeP
 struct ArRowsParams {
   void* const* partial_tab; void* const* out_tab; void* const* norm_tab;
   uint32_t* const* flag_tab; uint32_t* state;
-  int world, rank, M, N, flag_base, add_residual;
+  int world, rank, M, N, flag_base, add_residual, out_local;
   const void* norm_w; float eps; int norm_mode;
   int32_t* status;
 };
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(kArThreads) ar_rows_kernel(const ArRowsParams 
           }
 #pragma unroll
           for (int d = 0; d < 8; ++d)
-            if (d < p.world) *reinterpret_cast<Vec8<T>*>(outs[d] + at) = packed;
+            if (d < p.world && (!p.out_local || d == p.rank)) *reinterpret_cast<Vec8<T>*>(outs[d] + at) = packed;
         }
       }
       if (p.norm_mode != 0) {
@@ -369,10 +369,12 @@ extern "C" int rf_ar_rows(const RfArRows* a, rf_stream_t stream) {
   RF_REQUIRE(a->partial_tab && a->out_tab && a->ar_flags && a->ar_state && a->flag_base >= 0, "ar_rows needs the buffer tables, flags and state");
   RF_REQUIRE(a->dtype == 0 || a->dtype == 1, "ar_rows dtype");
   if (a->norm_mode != 0) RF_REQUIRE(a->norm_w && a->norm_tab && (a->norm_mode == 1 || a->norm_mode == 2), "ar_rows fused norm arguments");
+  RF_REQUIRE(!a->out_local || a->norm_mode != 0, "ar_rows: rows that stay on their owner need the gathered normalised rows as the result every rank reads");
   ArRowsParams p;
   p.partial_tab = a->partial_tab; p.out_tab = a->out_tab; p.norm_tab = a->norm_tab;
   p.flag_tab = a->ar_flags; p.state = a->ar_state;
   p.world = a->world; p.rank = a->rank; p.M = a->M; p.N = a->N; p.flag_base = a->flag_base; p.add_residual = a->add_residual;
+  p.out_local = a->out_local;
   p.norm_w = a->norm_w; p.eps = a->eps; p.norm_mode = a->norm_mode; p.status = a->status;
   const int nvec = a->N / 8;
   const int vpt = ceil_div(nvec, kArThreads);

@@ -247,6 +247,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           sv[i] = __float_as_uint(v);
           mx = fmaxf(mx, v);
         }
+      } else if (mrow != nullptr && p.seg_q == nullptr && ((reinterpret_cast<uintptr_t>(mrow) + (uintptr_t)t0) & 15u) == 0 &&
+                 t0 + KVB <= p.mask_ld) {
+        // boolean mask, 16-byte aligned and wholly inside the row: the block's KVB mask bytes come as 16-byte
+        // loads that are all in flight at once (byte loads chained behind the range test cost a cache round
+        // trip each and made a 31 x 331 problem take 60 us)
+        uint4 mv[KVB / 16];
+        const uint4* m16 = reinterpret_cast<const uint4*>(mrow + t0);
+#pragma unroll
+        for (int c = 0; c < KVB / 16; ++c) mv[c] = __ldg(m16 + c);
+#pragma unroll
+        for (int i = 0; i < KVB; ++i) {
+          const int tk = t0 + i;
+          const uint32_t word = reinterpret_cast<const uint32_t*>(&mv[i >> 4])[(i >> 2) & 3];
+          const bool v = tk >= lo_row && tk <= hi_row && ((word >> ((i & 3) * 8)) & 0xffu) != 0;
+          const float x = v ? __uint_as_float(sv[i]) * p.scale_log2 : -INFINITY;
+          sv[i] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < KVB; ++i) {

@@ -291,7 +291,7 @@ static bool small_enabled() {
 // finishes in one short wave, and only the plain epilogue options.
 bool gemm_small_eligible(const RfGemm* g) {
   if (!small_enabled() || g->w_int8 || g->scale || g->row_scale || g->ar_world > 1 || g->ar_publish || g->ss_in || g->ss_out ||
-      g->prefetch || g->force_splits || g->force_bn || g->force_swap >= 0)
+      g->prefetch || g->force_splits || g->force_bn || g->force_swap >= 0 || g->streaming_only)
     return false;
   if (g->M > 256 || g->N % 8 || g->K % 8 || g->ldx % 8 || g->ldo % 2 || (g->residual && g->ldr % 2)) return false;
   if (!g->w_packed && g->ldw % 8) return false;

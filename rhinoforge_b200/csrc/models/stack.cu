@@ -123,6 +123,13 @@ static bool tp_publish_enabled() {
   return v;
 }
 
+// Under tensor parallelism with prefill-sized rows the residual stream stays sharded by rows between the layers (each
+// rank keeps the rows it reduces; only their RMSNorm is gathered).  RF_TP_SEQ_SHARD=0 gathers the stream itself too.
+static bool tp_seq_shard_enabled() {
+  static const bool v = [] { const char* e = getenv("RF_TP_SEQ_SHARD"); return !(e && e[0] == '0'); }();
+  return v;
+}
+
 // L2 prefetch hint for the next linear() call on this thread (set by the layer loop right before the call, consumed
 // by it): the weights of the linear layer that FOLLOWS, so that a weight-streaming GEMM hands HBM over to its
 // successor without an idle gap.  RF_GEMM_L2_PREFETCH_MB caps the bytes asked for (0: off).
@@ -188,6 +195,7 @@ static int linear(const Stack& s, const void* x, int64_t ldx, const void* w, con
   }
   g.status = s.status();
   g.force_swap = -1;
+  g.streaming_only = s.cfg.gemm_streaming_only;
   g.prefetch = t_pf_ptr; g.prefetch_bytes = t_pf_bytes;
   t_pf_ptr = nullptr; t_pf_bytes = 0;
   if (t_ss_out || t_ss_in) {
@@ -243,7 +251,7 @@ static int consume(const Stack& s, int pub_ctas, const void* residual, void* out
 // in next_xn) rides in the consumer: *normed tells the caller that next_xn is valid.
 static int linear_ar(const Stack& s, const void* x, int64_t ldx, const void* w, const void* scale, const void* bias,
                      void* out, const void* residual, int M, int K, const void* next_norm_w, void* next_xn,
-                     bool* normed, cudaStream_t st) {
+                     bool* normed, cudaStream_t st, bool rows_stay = false) {
   const int H = s.cfg.hidden;
   if (normed) *normed = false;
   if (s.cfg.tp_world > 1 && tp_publish_enabled() && M > 256 && s.comm.sym_rows >= M &&
@@ -264,6 +272,9 @@ static int linear_ar(const Stack& s, const void* x, int64_t ldx, const void* w, 
       a.norm_tab = s.comm.xn_tab; a.norm_w = next_norm_w; a.eps = s.cfg.eps;
       a.norm_mode = s.cfg.norm_kind == RF_NORM_RMS_GEMMA ? 2 : 1;
       if (normed) *normed = true;
+      // sequence-sharded residual stream: the next reader of these rows is the owner's own next reduction, so they
+      // stay there and only their RMSNorm is gathered
+      a.out_local = (rows_stay && residual && tp_seq_shard_enabled()) ? 1 : 0;
     }
     a.status = s.status(); a.dtype = s.cfg.dtype;
     return rf_ar_rows(&a, st);
@@ -495,7 +506,7 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
     } else if (!side) {
       if (fuse_ss) t_ss_out = ss_attn;
       rc = linear_ar(s, mix_out, mix_dim, w.wo, w.so, w.bo, f.hidden, f.hidden, T, mix_dim,
-                     norm_rides ? w.norm2_w : nullptr, xn, &have_xn2, st);
+                     norm_rides ? w.norm2_w : nullptr, xn, &have_xn2, st, /*rows_stay=*/true);
       if (rc) return rc;
     } else if (fuse_gate && !w.bo) {
       rc = linear(s, mix_out, mix_dim, w.wo, mod1 + (size_t)2 * H * esz, nullptr, f.hidden, H, f.hidden, H, T, H, mix_dim,
@@ -568,7 +579,11 @@ static int forward(Stack& s, const RfStackForward& f, cudaStream_t st) {
                        split, H, I, kActNone, 0, st);
       if (rc) return rc;
     } else if (!side) {
-      rc = linear_ar(s, wide, I, w.w_down, w.s_down, w.b_down, f.hidden, f.hidden, T, I, next_w, xn, &have_xn, st);
+      // every rank needs all rows of the stream again after the last layer of this call and where a tap copies them
+      bool tapped = false;
+      for (int i = 0; i < f.n_taps; ++i) tapped |= f.tap_layers[i] == l;
+      rc = linear_ar(s, wide, I, w.w_down, w.s_down, w.b_down, f.hidden, f.hidden, T, I, next_w, xn, &have_xn, st,
+                     /*rows_stay=*/next_w != nullptr && !tapped);
       if (rc) return rc;
     } else if (fuse_gate && !w.b_down) {
       rc = linear(s, wide, I, w.w_down, mod2 + (size_t)2 * H * esz, nullptr, f.hidden, H, f.hidden, H, T, H, I, kActNone,

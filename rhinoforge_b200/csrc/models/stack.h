@@ -63,7 +63,10 @@ typedef struct RfStackConfig {
   // tokens the residual GEMMs (o_proj, down_proj) emit per-token sums of squares and the next projection scales its
   // result by the reciprocal RMS, so no RMSNorm kernel runs between them; with more tokens a weight-free RMSNorm runs.
   int32_t norm_folded;
-  int32_t reserved0;
+  // 1: every GEMM of the stack runs on the tcgen05 kernels.  Decoder engines set it so that the tokens of a tensor-
+  // parallel run and of a one-GPU run come from one kernel family (the row-parallel GEMMs with a collective in them
+  // always do); the action heads leave it 0 and take the latency-bound kernel for their few-row shapes.
+  int32_t gemm_streaming_only;
 } RfStackConfig;
 
 typedef struct RfLayerWeights {

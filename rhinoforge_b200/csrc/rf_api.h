@@ -95,7 +95,7 @@ typedef struct RfGemm {
   const float* ss_in;
   int32_t ss_ld, ss_dim;
   float ss_eps;
-  int32_t reserved0;
+  int32_t streaming_only;      // 1: never the latency-bound mma.sync kernel (gemm_small.cu), whatever the shape
 } RfGemm;
 // bytes of the tile-major image of a [rows, K] weight with `sections` equal row sections
 uint64_t rf_pack_weight_bytes(int64_t rows, int64_t K, int32_t sections, int32_t elem_bytes);
@@ -150,7 +150,9 @@ int rf_ar_consume(const RfArConsume* a, rf_stream_t stream);
 // rows [r * ceil(M / world), ...): it reads those rows of EVERY rank's partial over NVLink (reduce-scatter by peer
 // loads, summed in rank order in fp32), adds the residual, and writes the finished rows -- and, when norm_mode != 0,
 // the RMSNorm of them -- into every rank's `out` (and `norm_out`) buffer (all-gather by peer stores).  The residual is
-// read from this rank's own `out` buffer when add_residual is set (the residual stream lives there).  Flags:
+// read from this rank's own `out` buffer when add_residual is set (the residual stream lives there).  With out_local
+// the finished rows are written on their owner only: each rank then holds M / world rows of the residual stream, and
+// what crosses NVLink is a reduce-scatter of the partials plus an all-gather of the normalised rows.  Flags:
 // world "partial ready" + world "rows written" words per rank at flag_base; state word 6 is the epoch.
 typedef struct RfArRows {
   int32_t M, N, world, rank;
@@ -163,6 +165,8 @@ typedef struct RfArRows {
   int32_t add_residual;
   const void* norm_w; float eps; int32_t norm_mode;
   int32_t* status; int32_t dtype;
+  int32_t out_local;           // 1: the finished rows stay on their owner (sequence-sharded residual stream); only the
+                               // normalised rows are gathered on every rank
 } RfArRows;
 int rf_ar_rows(const RfArRows* a, rf_stream_t stream);
 

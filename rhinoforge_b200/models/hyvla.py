@@ -355,7 +355,7 @@ class HyVlaEngine:
         self.s_qstart = torch.zeros(1, **i32)
         self.s_qlen = torch.full((1,), L, **i32)
         self.s_kvlen = torch.zeros(1, **i32)
-        self.mask = torch.zeros(L, self.max_seq, dtype=torch.uint8, device=dev)
+        self.mask = torch.zeros(L, (self.max_seq + 127) // 128 * 128, dtype=torch.uint8, device=dev)[:, :self.max_seq]   # pitch: whole 128-key blocks
         self.p_hidden = torch.zeros(self.vlm.spec.max_tokens, cfg.vlm_hidden, dtype=dtype, device=dev)
         self.prefix_len = 0
 

@@ -339,7 +339,7 @@ class Lingbot2Engine:
         self.s_qstart = torch.zeros(1, **i32)
         self.s_qlen = torch.full((1,), n, **i32)
         self.s_kvlen = torch.zeros(1, **i32)
-        self.mask = torch.zeros(n, self.max_seq, dtype=torch.uint8, device=dev)
+        self.mask = torch.zeros(n, (self.max_seq + 127) // 128 * 128, dtype=torch.uint8, device=dev)[:, :self.max_seq]   # pitch: whole 128-key blocks
         self.image_token_id = self.vlm.image_token_id
         cg = lambda k, d: hf_vlm_config.get(k, d) if isinstance(hf_vlm_config, dict) else getattr(hf_vlm_config, k, d)
         self.vision_start_id, self.vision_end_id = int(cg("vision_start_token_id", 151652)), int(cg("vision_end_token_id", 151653))

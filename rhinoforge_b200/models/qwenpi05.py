@@ -284,7 +284,8 @@ class QwenPI05Engine:
         self.s_qstart = torch.zeros(1, **i32)
         self.s_qlen = torch.full((1,), n, **i32)
         self.s_kvlen = torch.zeros(1, **i32)
-        self.mask = torch.zeros(n, self.max_seq, dtype=torch.uint8, device=dev)
+        # row pitch a multiple of the attention kernel's 128-key block: its 16-byte mask loads then never cross a row end
+        self.mask = torch.zeros(n, (self.max_seq + 127) // 128 * 128, dtype=torch.uint8, device=dev)[:, :self.max_seq]
         self.prefix_len = 0
 
     # ------------------------------------------------------------------ prefix

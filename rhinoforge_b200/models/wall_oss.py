@@ -352,7 +352,7 @@ class WallOssEngine:
         self.s_qstart = torch.zeros(1, **i32)
         self.s_qlen = torch.full((1,), n, **i32)
         self.s_kvlen = torch.zeros(1, **i32)
-        self.mask = torch.zeros(n, self.max_seq, dtype=torch.uint8, device=dev)
+        self.mask = torch.zeros(n, (self.max_seq + 127) // 128 * 128, dtype=torch.uint8, device=dev)[:, :self.max_seq]   # pitch: whole 128-key blocks
 
     # ------------------------------------------------------------------ per-num_steps constants
     def schedule(self, num_steps: int) -> dict:

@@ -123,6 +123,7 @@ class DecoderEngine:
                           and quant is None and getattr(get_weight, "scale", None) is None and self.packed
                           and os.environ.get("RF_FOLD_NORM", "1") != "0")
         sc.norm_folded = int(self.fold_norm)
+        sc.gemm_streaming_only = 1          # one GEMM kernel family at every tensor-parallel degree
         # hybrid decoders: which layers own KV pages, and the local Gated-DeltaNet geometry
         self.attn_layers = [l for l in range(cfg.num_layers) if not cfg.is_linear(l)]
         self.kv_index = {l: i for i, l in enumerate(self.attn_layers)}
