@@ -324,11 +324,22 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The same rendezvous without memory ordering: for "every CTA has finished reading its peers' shared memory" before any of
+// them exits, where the reads' values were already consumed and nothing written needs to become visible.
+__device__ __forceinline__ void cluster_sync_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+}
 // Address of the same shared-memory location in CTA `rank` of this cluster.
 __device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_smem_addr, uint32_t rank) {
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
   return r;
+}
+__device__ __forceinline__ float2 ld_dsmem_f32x2(uint32_t addr) {   // addr: 8-byte aligned
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+  return v;
 }
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
   float v;

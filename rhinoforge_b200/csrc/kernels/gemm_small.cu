@@ -258,21 +258,27 @@ gemm_small_kernel(const SmallParams p) {
     const uint32_t base = smem_u32(part);
     for (int idx = tid; idx < rows * (kSmBN / 2); idx += kSmThreads) {
       const int r = r_lo + idx / (kSmBN / 2), c = (idx % (kSmBN / 2)) * 2;
+      // every CTA's pair in flight before the first add (a loop over a run-time split count would chain the
+      // distributed-shared-memory round trips one behind the other)
+      float2 v[kWT][8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+#pragma unroll
+        for (int wt = 0; wt < kWT; ++wt)
+          v[wt][k] = k < p.splits
+                         ? ld_dsmem_f32x2(dsmem_addr(base + (uint32_t)((((size_t)wt * BM + r) * kSmPartLd + c) * sizeof(float)), (uint32_t)k))
+                         : make_float2(0.f, 0.f);
       float s[kWT][2];
 #pragma unroll
-      for (int wt = 0; wt < kWT; ++wt) s[wt][0] = s[wt][1] = 0.f;
-      for (int k = 0; k < p.splits; ++k) {
+      for (int wt = 0; wt < kWT; ++wt) {
+        s[wt][0] = s[wt][1] = 0.f;
 #pragma unroll
-        for (int wt = 0; wt < kWT; ++wt) {
-          const uint32_t a = dsmem_addr(base + (uint32_t)((((size_t)wt * BM + r) * kSmPartLd + c) * sizeof(float)), (uint32_t)k);
-          s[wt][0] += ld_dsmem_f32(a);
-          s[wt][1] += ld_dsmem_f32(a + 4);
-        }
+        for (int k = 0; k < 8; ++k) { s[wt][0] += v[wt][k].x; s[wt][1] += v[wt][k].y; }
       }
       finish_pair(m0 + r, f0 + c, s[0][0], s[0][1], DUAL ? s[kWT - 1][0] : 0.f, DUAL ? s[kWT - 1][1] : 0.f);
     }
   }
-  cluster_sync_all();                                         // peers may still be reading this CTA's partial
+  cluster_sync_relaxed();                                     // peers may still be reading this CTA's partial
 }
 
 template <int BM, bool DUAL, int STAGES>
@@ -300,7 +306,8 @@ bool gemm_small_eligible(const RfGemm* g) {
   // up to 64 rows with a long K the streaming kernel's deep TMA ring is as fast or faster (measured: 41 x 1536 x 6144
   // 12.4 us there against 13.8 us here, 41 x 1536 x 2048 8.5 against 9.6); above 64 rows this kernel wins everywhere
   // that was measured (128 x 1536 x 384: 7.6 us against 19.6 us)
-  if (g->M <= 64 && g->K > 1536) return false;
+  static const int max_k64 = [] { const char* e = getenv("RF_GEMM_SMALL_MAX_K"); return e ? atoi(e) : 1536; }();
+  if (g->M <= 64 && g->K > max_k64) return false;
   // up to 32 rows the streaming kernel runs 32-column tiles and wins on all but the smallest weights (31 x 2560 x 1024:
   // 6.8 us there against 9.2 us here; 31 x 4096 x 1024: 8.1 against 9.9; 24 x 1152 x 384: 7.5 against 5.2)
   if (g->M <= 32 && (long)g->N * g->K * (dual ? 2 : 1) > (1L << 20)) return false;

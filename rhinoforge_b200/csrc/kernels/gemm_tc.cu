@@ -981,8 +981,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   }
-  // peers may still be reading this CTA's partial over DSMEM
-  if (p.splits > 1) cluster_sync_all();
+  // peers may still be reading this CTA's partial over DSMEM: a rendezvous without memory ordering (the values read
+  // were consumed before the arrive; a release here would make every CTA wait for its output stores to drain)
+  if (p.splits > 1) cluster_sync_relaxed();
 
   // ----------------------------------------------------------- teardown ----
   tc_fence_before_sync();

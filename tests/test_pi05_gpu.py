@@ -21,6 +21,26 @@ def _inputs(cfg, B, seed=0):
     return images, image_mask, tokens, token_mask, noise
 
 
+@pytest.mark.parametrize("form", ["decode", "block"])
+@pytest.mark.parametrize("B", [1, 5])
+def test_suffix_attention_forms(B, form):
+    """Both launch forms of the action rows' attention (one-token sequences on the decode kernel; one bidirectional
+    query block per sample on the prefill kernel) against the fp32 formulation; ``auto`` picks by sample count."""
+    from rhinoforge_b200.models.pi05 import Pi05Engine, TorchPi05, random_pi05_state_dict, tiny_pi05_config
+    cfg = tiny_pi05_config()
+    sd = random_pi05_state_dict(cfg, dtype=torch.float32, std=0.08, seed=3)
+    args = _inputs(cfg, B, seed=2)
+    want = TorchPi05(cfg, sd, device="cuda").sample_actions(*args, num_steps=4).cpu()
+    eng = Pi05Engine(cfg, sd, max_batch=B)
+    assert eng.suffix_attn == "auto"
+    eng.suffix_attn = form
+    for use_graph in (False, True):
+        got = eng.predict(*args, num_steps=4, use_graph=use_graph).float().cpu()
+        eng.check_status()
+        assert float((got - want).abs().max() / want.abs().max()) < 3e-2, (form, use_graph)
+    eng.close()
+
+
 @pytest.mark.parametrize("B,steps", [(1, 10), (3, 4)])
 def test_actions_match_fp32_reference(B, steps):
     from rhinoforge_b200.models.pi05 import Pi05Engine, TorchPi05, random_pi05_state_dict, tiny_pi05_config
