@@ -35,6 +35,7 @@ struct SmallParams {
   void* out; int64_t ldo;
   const void* residual; int64_t ldr;
   const void* bias;
+  const void* scale;          // optional per-output-column factor, applied before the bias (16-bit weights only)
   int M, N, K, act, dual_offset, packed, kb_total, dual_tiles, splits;
 };
 
@@ -200,11 +201,20 @@ gemm_small_kernel(const SmallParams p) {
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 
   const T* bias = reinterpret_cast<const T*>(p.bias);
+  const T* scale = reinterpret_cast<const T*>(p.scale);
   const T* res = reinterpret_cast<const T*>(p.residual);
   T* out = reinterpret_cast<T*>(p.out);
   auto finish_pair = [&](int m, int n, float g0, float g1, float u0, float u1) {
     // features n and n + 1 of token row m (n is even; N is a multiple of 8)
     if (m >= p.M || n >= p.N) return;
+    if (scale) {
+      g0 *= Num<T>::to_f(scale[n]);
+      g1 *= Num<T>::to_f(scale[n + 1]);
+      if (DUAL) {
+        u0 *= Num<T>::to_f(scale[p.dual_offset + n]);
+        u1 *= Num<T>::to_f(scale[p.dual_offset + n + 1]);
+      }
+    }
     if (bias) {
       g0 += Num<T>::to_f(bias[n]);
       g1 += Num<T>::to_f(bias[n + 1]);
@@ -296,17 +306,18 @@ static bool small_enabled() {
 // Shapes this kernel takes over from the streaming kernel: few token rows, a weight that an SM-count's worth of CTAs
 // finishes in one short wave, and only the plain epilogue options.
 bool gemm_small_eligible(const RfGemm* g) {
-  if (!small_enabled() || g->w_int8 || g->scale || g->row_scale || g->ar_world > 1 || g->ar_publish || g->ss_in || g->ss_out ||
+  if (!small_enabled() || g->w_int8 || g->w_bits || g->row_scale || g->ar_world > 1 || g->ar_publish || g->ss_in || g->ss_out ||
       g->prefetch || g->force_splits || g->force_bn || g->force_swap >= 0 || g->streaming_only)
     return false;
   if (g->M > 256 || g->N % 8 || g->K % 8 || g->ldx % 8 || g->ldo % 2 || (g->residual && g->ldr % 2)) return false;
   if (!g->w_packed && g->ldw % 8) return false;
   const bool dual = g->dual_offset > 0;
   if (dual && !g->w_packed && g->dual_offset % 8) return false;
-  // up to 64 rows with a long K the streaming kernel's deep TMA ring is as fast or faster (measured: 41 x 1536 x 6144
-  // 12.4 us there against 13.8 us here, 41 x 1536 x 2048 8.5 against 9.6); above 64 rows this kernel wins everywhere
-  // that was measured (128 x 1536 x 384: 7.6 us against 19.6 us)
-  static const int max_k64 = [] { const char* e = getenv("RF_GEMM_SMALL_MAX_K"); return e ? atoi(e) : 1536; }();
+  // up to 64 rows the two kernels are close once K is long (41 x 1536 x 6144: 12.0 us on the streaming kernel, 11.6 us
+  // here; 50 x 1024 x 2048: 8.5 against 5.7; inside the Pi0.5 denoise loop, K = 2048 / 4096 at 50 rows: 24.8 ms per chunk with
+  // this bound at 2048, 23.9 ms at 8192); above 64 rows this kernel wins everywhere that was measured
+  // (128 x 1536 x 384: 5.6 us against 19.6 us)
+  static const int max_k64 = [] { const char* e = getenv("RF_GEMM_SMALL_MAX_K"); return e ? atoi(e) : 8192; }();
   if (g->M <= 64 && g->K > max_k64) return false;
   // up to 32 rows the streaming kernel runs 32-column tiles and wins on all but the smallest weights (31 x 2560 x 1024:
   // 6.8 us there against 9.2 us here; 31 x 4096 x 1024: 8.1 against 9.9; 24 x 1152 x 384: 7.5 against 5.2)
@@ -340,7 +351,7 @@ int gemm_small_run(const RfGemm* g, cudaStream_t s) {
   const bool dual = g->dual_offset > 0;
   SmallParams p;
   p.x = g->x; p.ldx = g->ldx; p.w = g->w; p.ldw = g->ldw; p.out = g->out; p.ldo = g->ldo;
-  p.residual = g->residual; p.ldr = g->ldr; p.bias = g->bias;
+  p.residual = g->residual; p.ldr = g->ldr; p.bias = g->bias; p.scale = g->scale;
   p.M = g->M; p.N = g->N; p.K = g->K; p.act = g->act; p.dual_offset = g->dual_offset; p.packed = g->w_packed ? 1 : 0;
   p.kb_total = (g->K + 63) / 64;
   p.dual_tiles = dual ? (g->dual_offset + 127) / 128 : 0;    // the up section starts this many 128-row tiles after the gate section

@@ -797,6 +797,10 @@ def test_gemm_small_latency_kernel(dt, M, N, K, packed, status, monkeypatch):
     full = torch.nn.functional.gelu(ref + b.float(), approximate="tanh") + r.float()
     got = K_.gemm(x, wk, bias=b, act="gelu_tanh", residual=r, **kw)
     _close(got, full, dt, scale=max(1.0, float(full.abs().max())))
+    # per-column factor before the bias (the gate of a gated residual): r + (x.w^T * s + b)
+    sc = (torch.randn(N, device="cuda") * 0.5).to(dt)
+    gated = ref * sc.float() + b.float() + r.float()
+    _close(K_.gemm(x, wk, scale=sc, bias=b, residual=r, **kw), gated, dt, scale=max(1.0, float(gated.abs().max())))
     # strided output / input views
     buf = torch.zeros(M, N + 16, device="cuda", dtype=dt)
     K_.gemm(x, wk, out=buf[:, 8:8 + N], **kw)
