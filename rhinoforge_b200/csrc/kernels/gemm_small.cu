@@ -319,9 +319,12 @@ bool gemm_small_eligible(const RfGemm* g) {
   // (128 x 1536 x 384: 5.6 us against 19.6 us)
   static const int max_k64 = [] { const char* e = getenv("RF_GEMM_SMALL_MAX_K"); return e ? atoi(e) : 8192; }();
   if (g->M <= 64 && g->K > max_k64) return false;
-  // up to 32 rows the streaming kernel runs 32-column tiles and wins on all but the smallest weights (31 x 2560 x 1024:
-  // 6.8 us there against 9.2 us here; 31 x 4096 x 1024: 8.1 against 9.9; 24 x 1152 x 384: 7.5 against 5.2)
-  if (g->M <= 32 && (long)g->N * g->K * (dual ? 2 : 1) > (1L << 20)) return false;
+  // up to 32 rows the streaming kernel runs 32-column tiles; it won on all but the smallest weights before the split-K
+  // reduction here had its loads batched (31 x 2560 x 1024: 6.8 us there against 9.2 us here), and loses since then
+  // inside the loops that matter (RhinoVLA expert, 31 rows: 12.6 ms per call with this bound at 1 Mi elements, 11.9 ms
+  // without it), so the bound now sits above the kernel's general weight cap
+  static const long max_elems32 = [] { const char* e = getenv("RF_GEMM_SMALL_ROWS32_MAX_KELEMS"); return (long)(e ? atoi(e) : 16384) << 10; }();
+  if (g->M <= 32 && (long)g->N * g->K * (dual ? 2 : 1) > max_elems32) return false;
   static const long max_elems = [] { const char* e = getenv("RF_GEMM_SMALL_MAX_MELEMS"); return (long)(e ? atoi(e) : 12) << 20; }();
   return (long)g->N * g->K * (dual ? 2 : 1) <= max_elems;
 }
