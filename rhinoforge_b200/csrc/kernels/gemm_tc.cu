@@ -550,16 +550,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           float ag[8], au[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) { ag[j] = 0.f; au[j] = 0.f; }
-          for (int s = 0; s < p.splits; ++s) {
-            float tg[8], tu[8];
+          if constexpr (W8) {
+            // the quantised main loop's register budget (two CTAs per SM) has no room for every split at once
+            for (int s = 0; s < p.splits; ++s) {
+              float tg[8], tu[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int c = g0 + j;
+                tg[j] = (c < ncols && epi) ? ld_dsmem_f32(peer_part[s] + (uint32_t)(c * kBM + tid) * 4u) : 0.f;
+                tu[j] = (DUAL && c < ncols && epi) ? ld_dsmem_f32(peer_part[s] + (uint32_t)((bn + c) * kBM + tid) * 4u) : 0.f;
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { ag[j] += tg[j]; au[j] += tu[j]; }
+            }
+          } else {
+          // every split's eight values in flight before the first add: a loop over the run-time split count would put
+          // one distributed-shared-memory round trip per split and column group behind the other (a 128 x 256 tile
+          // split in two spent ~30 us here)
+          float tg[8][8], tu[DUAL ? 8 : 1][8];
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const int c = g0 + j;
-              tg[j] = (c < ncols && epi) ? ld_dsmem_f32(peer_part[s] + (uint32_t)(c * kBM + tid) * 4u) : 0.f;
-              tu[j] = (DUAL && c < ncols && epi) ? ld_dsmem_f32(peer_part[s] + (uint32_t)((bn + c) * kBM + tid) * 4u) : 0.f;
+              const bool on = s < p.splits && c < ncols && epi;
+              tg[s][j] = on ? ld_dsmem_f32(peer_part[s] + (uint32_t)(c * kBM + tid) * 4u) : 0.f;
+              if constexpr (DUAL) tu[s][j] = on ? ld_dsmem_f32(peer_part[s] + (uint32_t)((bn + c) * kBM + tid) * 4u) : 0.f;
             }
+          }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { ag[j] += tg[j]; au[j] += tu[j]; }
+          for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {          // split order; absent splits contribute +0
+              ag[j] += tg[s][j];
+              if constexpr (DUAL) au[j] += tu[s][j];
+            }
+          }
           }
           const int n0 = b0 + g0;
           if (a_idx < M) {
