@@ -550,42 +550,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           float ag[8], au[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) { ag[j] = 0.f; au[j] = 0.f; }
-          if constexpr (W8) {
-            // the quantised main loop's register budget (two CTAs per SM) has no room for every split at once
-            for (int s = 0; s < p.splits; ++s) {
-              float tg[8], tu[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int c = g0 + j;
-                tg[j] = (c < ncols && epi) ? ld_dsmem_f32(peer_part[s] + (uint32_t)(c * kBM + tid) * 4u) : 0.f;
-                tu[j] = (DUAL && c < ncols && epi) ? ld_dsmem_f32(peer_part[s] + (uint32_t)((bn + c) * kBM + tid) * 4u) : 0.f;
-              }
-#pragma unroll
-              for (int j = 0; j < 8; ++j) { ag[j] += tg[j]; au[j] += tu[j]; }
-            }
-          } else {
-          // every split's eight values in flight before the first add: a loop over the run-time split count would put
-          // one distributed-shared-memory round trip per split and column group behind the other (a 128 x 256 tile
-          // split in two spent ~30 us here)
-          float tg[8][8], tu[DUAL ? 8 : 1][8];
-#pragma unroll
-          for (int s = 0; s < 8; ++s) {
+          // one split at a time, eight loads in flight: fetching every split's values up front (64 loads per thread)
+          // measured slower here (968 x 2048 x 16384: 114.6 us against 87.5 us), unlike in the token-column path
+          for (int s = 0; s < p.splits; ++s) {
+            float tg[8], tu[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const int c = g0 + j;
-              const bool on = s < p.splits && c < ncols && epi;
-              tg[s][j] = on ? ld_dsmem_f32(peer_part[s] + (uint32_t)(c * kBM + tid) * 4u) : 0.f;
-              if constexpr (DUAL) tu[s][j] = on ? ld_dsmem_f32(peer_part[s] + (uint32_t)((bn + c) * kBM + tid) * 4u) : 0.f;
+              tg[j] = (c < ncols && epi) ? ld_dsmem_f32(peer_part[s] + (uint32_t)(c * kBM + tid) * 4u) : 0.f;
+              tu[j] = (DUAL && c < ncols && epi) ? ld_dsmem_f32(peer_part[s] + (uint32_t)((bn + c) * kBM + tid) * 4u) : 0.f;
             }
-          }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {          // split order; absent splits contribute +0
-              ag[j] += tg[s][j];
-              if constexpr (DUAL) au[j] += tu[s][j];
-            }
-          }
+            for (int j = 0; j < 8; ++j) { ag[j] += tg[j]; au[j] += tu[j]; }
           }
           const int n0 = b0 + g0;
           if (a_idx < M) {
@@ -1039,7 +1015,12 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
     pl->grid_x = ceil_div(g->N, kBM);
     pl->grid_y = ceil_div(g->M, bn);
   } else {
-    int bn = g->force_bn > 0 ? g->force_bn : ((g->N % 256 == 0 && !dual) ? 256 : 128);
+    // 256-wide tiles only where they fill the GPU on their own: with fewer of them than SMs the kernel would split K to
+    // make CTAs, and the split-K reduction of a 128 x 256 fp32 tile over distributed shared memory costs more than the
+    // operand re-reads that 128-wide tiles add (measured, with a residual epilogue: 968 x 2048 x 2048 42.9 us at 256 x 2
+    // splits against 32.3 us at 128 x 2; 968 x 2048 x 16384 113.2 against 97.2; 400 x 1024 x 4096 40.6 against 20.9)
+    const bool wide_fills = (long)ceil_div(g->M, kBM) * (g->N / 256) >= sm_count() || (g->ar_world > 1 && g->M > 256);
+    int bn = g->force_bn > 0 ? g->force_bn : ((g->N % 256 == 0 && !dual && wide_fills) ? 256 : 128);
     if (g->N < 128 && !g->w_packed) bn = round_up(g->N, 16);
     if (g->w_packed && bn != 128 && bn != 256) bn = 128;   // packed weights come in 128-row blocks
     pl->bn = bn;
