@@ -504,6 +504,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ([column][lane], conflict-free), then CTA r reduces columns r, r+S, ...
     // over distributed shared memory in split order and finishes them.
     float* part = reinterpret_cast<float*>(smem);
+    // Token-row tiles PUSH instead: a thread owns one output row and 8-column groups are dealt round-robin to the
+    // cluster's CTAs, so every CTA stores each group of its partial straight into the owner's shared memory (slot =
+    // sender, [column][lane]); remote stores do not wait for a round trip, and the owner then sums from its own shared
+    // memory.  (Pulling the same values cost one distributed-shared-memory round trip per split and column group:
+    // ~10 us for a 128 x 128 tile split in four.)  The peers' operand rings must be idle first: one more rendezvous.
+    const int gpo = (((bn + 7) >> 3) + p.splits - 1) / p.splits;   // column groups per owner
+    const int cpo = gpo * 8;                                       // receive columns per owner and sender
+    const uint32_t acc2 = (uint32_t)p.splits * cpo * kBM;          // floats before the second accumulator's slots
+    if constexpr (!SWAP) {
+      cluster_sync_all();
+      if (!aborted) {
+        const uint32_t my_slot = smem_u32(part) + ((uint32_t)crank * cpo * kBM + tid) * 4u;
+        auto push16 = [&](int c, const uint32_t* rg, const uint32_t* ru) {   // columns c .. c + 15 of this row
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int gi = (c >> 3) + h;
+            const uint32_t dst = dsmem_addr(my_slot + (uint32_t)((gi / p.splits) * 8 * kBM) * 4u, (uint32_t)(gi % p.splits));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              st_dsmem_u32(dst + (uint32_t)(j * kBM) * 4u, rg[h * 8 + j]);
+              if (DUAL) st_dsmem_u32(dst + (acc2 + (uint32_t)(j * kBM)) * 4u, ru[h * 8 + j]);
+            }
+          }
+        };
+        if ((bn & 31) == 0) {
+          for (int c = 0; c < bn; c += 32) {
+            uint32_t rg[32], ru[32];
+            tmem_ld32(trow + c, rg);
+            if (DUAL) tmem_ld32(trow + bn + c, ru);
+            tmem_ld_wait();
+            if (epi) {
+              push16(c, rg, ru);
+              push16(c + 16, rg + 16, ru + 16);
+            }
+          }
+        } else {
+          for (int c = 0; c < bn; c += 16) {
+            uint32_t rg[16], ru[16];
+            tmem_ld16(trow + c, rg);
+            if (DUAL) tmem_ld16(trow + bn + c, ru);
+            tmem_ld_wait();
+            if (epi) push16(c, rg, ru);
+          }
+        }
+      }
+    } else
     if (!aborted) {
       if ((bn & 31) == 0) {
         // 32 columns (of each accumulator) per tensor-memory round trip: the round trip, not the copy, is the cost
@@ -550,18 +596,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           float ag[8], au[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) { ag[j] = 0.f; au[j] = 0.f; }
-          // one split at a time, eight loads in flight: fetching every split's values up front (64 loads per thread)
-          // measured slower here (968 x 2048 x 16384: 114.6 us against 87.5 us), unlike in the token-column path
+          // the senders' slots of this group, from this CTA's own shared memory, summed in split order
+          const float* slot0 = part + (size_t)((g0 >> 3) / p.splits) * 8 * kBM + tid;
           for (int s = 0; s < p.splits; ++s) {
-            float tg[8], tu[8];
+            const float* sp = slot0 + (size_t)s * cpo * kBM;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const int c = g0 + j;
-              tg[j] = (c < ncols && epi) ? ld_dsmem_f32(peer_part[s] + (uint32_t)(c * kBM + tid) * 4u) : 0.f;
-              tu[j] = (DUAL && c < ncols && epi) ? ld_dsmem_f32(peer_part[s] + (uint32_t)((bn + c) * kBM + tid) * 4u) : 0.f;
+              const bool on = g0 + j < ncols && epi;
+              ag[j] += on ? sp[j * kBM] : 0.f;
+              if (DUAL) au[j] += on ? sp[acc2 + j * kBM] : 0.f;
             }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) { ag[j] += tg[j]; au[j] += tu[j]; }
           }
           const int n0 = b0 + g0;
           if (a_idx < M) {
@@ -985,7 +1029,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
   // peers may still be reading this CTA's partial over DSMEM: a rendezvous without memory ordering (the values read
   // were consumed before the arrive; a release here would make every CTA wait for its output stores to drain)
-  if (p.splits > 1) cluster_sync_relaxed();
+  if (SWAP && p.splits > 1) cluster_sync_relaxed();   // token-row tiles push: nothing reads a peer after their second rendezvous
 
   // ----------------------------------------------------------- teardown ----
   tc_fence_before_sync();
@@ -1023,6 +1067,9 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
     int bn = g->force_bn > 0 ? g->force_bn : ((g->N % 256 == 0 && !dual && wide_fills) ? 256 : 128);
     if (g->N < 128 && !g->w_packed) bn = round_up(g->N, 16);
     if (g->w_packed && bn != 128 && bn != 256) bn = 128;   // packed weights come in 128-row blocks
+    // a 256-wide tile is two 128-row blocks of the tile-major image: with an odd number of blocks the last tile's second
+    // block would lie past the end of the image (a forced width can ask for this; the planner's own choice cannot)
+    if (g->w_packed && bn == 256 && ceil_div(dual ? g->dual_offset : g->N, 128) % 2 != 0) bn = 128;
     pl->bn = bn;
     pl->grid_x = ceil_div(g->M, kBM);
     pl->grid_y = ceil_div(g->N, bn);
@@ -1048,7 +1095,9 @@ static int plan_gemm(const RfGemm* g, GemmPlan* pl) {
     st = std::min(st, std::max(2, ceil_div(pl->k_blocks, S)));
     // the split-K partial ([columns][128] fp32 per accumulator) reuses the stage ring; the publish path parks this
     // CTA's finished rows behind it (peers still read the partial over DSMEM while the rows are pushed)
-    int part = S > 1 ? pl->bn * (dual ? 2 : 1) * kBM * 4 : 0;
+    // (token-row tiles receive pushed slices: splits x ceil(groups / splits) 8-column groups per accumulator)
+    const int part_cols = swap ? pl->bn : ceil_div(ceil_div(pl->bn, 8), S) * 8 * S;
+    int part = S > 1 ? part_cols * (dual ? 2 : 1) * kBM * 4 : 0;
     if (S > 1 && publish) part += ceil_div(pl->bn, S) * kBM * (g->M <= RF_AR_F32_MAX_ROWS ? 4 : 2);
     *stages_out = st;
     *part_out = part;

@@ -808,6 +808,22 @@ def test_gemm_small_latency_kernel(dt, M, N, K, packed, status, monkeypatch):
     assert float(buf[:, :8].abs().max()) == 0 and float(buf[:, 8 + N:].abs().max()) == 0
 
 
+def test_gemm_forced_wide_tile_over_odd_block_count(status):
+    """A forced 256-wide tile on a tile-major weight with an odd number of 128-row blocks (N = 1152: nine) falls back to
+    128-wide tiles instead of copying a tenth block that is not there; token-row split K (pushed partial slices) on
+    the same shape at 2 and 4 splits."""
+    from rhinoforge_b200.ops import kernels as K_
+    M, N, K = 768, 1152, 1152
+    x = (torch.randn(M, K, device="cuda") * 0.5).half()
+    w = (torch.randn(N, K, device="cuda") * 0.05).half()
+    r = torch.randn(M, N, device="cuda").half()
+    wp = K_.pack_weight(w)
+    ref = x.float() @ w.float().t() + r.float()
+    for kw in (dict(force_bn=256), dict(force_bn=256, force_splits=2), dict(force_bn=128, force_splits=4), dict(force_splits=3)):
+        got = K_.gemm(x, wp, packed_shape=(N, K), residual=r, status=status, **kw)
+        _close(got, ref, torch.float16, scale=max(1.0, float(ref.abs().max())))
+
+
 @pytest.mark.parametrize("dt", DT)
 @pytest.mark.parametrize("M,N,K", [(50, 4096, 1024), (128, 1536, 384), (31, 136, 200)])
 @pytest.mark.parametrize("packed", [False, True])
