@@ -551,8 +551,15 @@ static DecodeSplitPlan plan_decode_split(int num_seqs, int Hq, int Hkv, int hd, 
   const int max_pages = std::max(1, (max_kv_len + 15) / 16);
   const int ctas = num_seqs * Hkv;
   int splits = 1;
-  if (allow_split && ctas < 2 * sm_count()) {
-    splits = std::min(std::max(1, (2 * sm_count()) / ctas), std::max(1, max_pages / 8));
+  // RF_ATTN_DECODE_CTAS_PER_SM (default 2; 1 for heads of 256): CTAs per SM the split aims at; RF_ATTN_DECODE_MIN_PAGES (default 8): fewest
+  // pages a split may cover
+  // (heads of 256 run one CTA per SM: measured on the Pi0.5 denoise loop, 50 rows x 1 KV head over ~870 keys, 12.5 ms at
+  // two per SM against 11.6 ms at one; heads of 128, Qwen3-8B decode at batch 1 / 8: 3.41 / 3.83 ms against 3.51 / 4.03)
+  static const int per_sm_env = [] { const char* e = getenv("RF_ATTN_DECODE_CTAS_PER_SM"); return e ? std::max(1, atoi(e)) : 0; }();
+  const int per_sm = per_sm_env > 0 ? per_sm_env : (hd >= 256 ? 1 : 2);
+  static const int min_pages = [] { const char* e = getenv("RF_ATTN_DECODE_MIN_PAGES"); return e ? std::max(4, atoi(e)) : 8; }();
+  if (allow_split && ctas < per_sm * sm_count()) {
+    splits = std::min(std::max(1, (per_sm * sm_count()) / ctas), std::max(1, max_pages / min_pages));
     splits = std::min(splits, 64);
   }
   DecodeSplitPlan pl;
