@@ -22,6 +22,14 @@ sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 
 PROFILE = False
+BASELINE = False          # also time the plain PyTorch (fp32, eager) formulation of the same call on the same GPU
+
+
+def vs_eager(what: str, ms: float, fn) -> str:
+    if not BASELINE:
+        return what
+    _, ref_ms = timed(fn, reps=2)
+    return f"{what} [PyTorch eager fp32, same GPU: {ref_ms:.1f} ms per call, {ref_ms / ms:.1f}x]"
 
 
 def timed(fn, reps: int = 5):
@@ -50,7 +58,13 @@ def navdp(tiny: bool):
     goal, rgbd = torch.randn(1, 1, cfg.hidden), torch.randn(1, cfg.memory_len - 2, cfg.hidden)
     init = torch.randn(4, cfg.predict_size, cfg.action_dim)
     out, ms = timed(lambda: eng.predict_action(goal, rgbd, init, seed=1))
-    return f"actions {tuple(out.shape)}, {cfg.steps} DDPM steps", ms
+    what = f"actions {tuple(out.shape)}, {cfg.steps} DDPM steps"
+    if BASELINE:
+        sd32 = {k: v.float() for k, v in m.random_navdp_state_dict(cfg, std=0.03).items()}
+        ref = m.TorchNavdp(cfg, {k: v.cuda() for k, v in sd32.items()}, device="cuda")
+        step_noise = torch.randn(cfg.steps, *init.shape)
+        what = vs_eager(what, ms, lambda: ref.predict_action(goal.cuda(), rgbd.cuda(), init, step_noise))
+    return what, ms
 
 
 def gr00t(tiny: bool):
@@ -74,7 +88,11 @@ def nextdit(tiny: bool):
     acts, cond = torch.randn(4, cfg.action_seq, cfg.action_dim), torch.randn(1, min(260, cfg.max_cross), cfg.cond_dim)
     ts, dts = torch.linspace(1.0, 0.1, 10), torch.full((10,), -0.1)
     out, ms = timed(lambda: eng.denoise_actions(acts, ts, dts, cond))
-    return f"actions {tuple(out.shape)}, 10 Euler steps", ms
+    what = f"actions {tuple(out.shape)}, 10 Euler steps"
+    if BASELINE:
+        ref = m.TorchNextDiT(cfg, {k: v.float().cuda() for k, v in m.random_nextdit_state_dict(cfg).items()}, device="cuda")
+        what = vs_eager(what, ms, lambda: ref.denoise_actions(acts, ts.tolist(), dts.tolist(), cond[0].cuda()))
+    return what, ms
 
 
 def rhinovla(tiny: bool):
@@ -96,7 +114,11 @@ def rgbd(tiny: bool):
     S = cfg.image_size
     img, dep = torch.rand(1, cfg.memory_size, S, S, 3), torch.rand(1, cfg.memory_size, S, S, 1)
     out, ms = timed(lambda: enc(img, dep))
-    return f"memory tokens {tuple(out.shape)}", ms
+    what = f"memory tokens {tuple(out.shape)}"
+    if BASELINE:
+        ref = m.TorchRgbdEncoder(cfg, {k: v.float().cuda() for k, v in m.random_rgbd_state_dict(cfg).items()}, device="cuda")
+        what = vs_eager(what, ms, lambda: ref.forward(img, dep))
+    return what, ms
 
 
 def gemma4(tiny: bool):
@@ -136,6 +158,8 @@ def main() -> int:
     ap.add_argument("--tiny", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="run the call once inside cudaProfilerStart/Stop after three warm-up calls (for ncu --profile-from-start off)")
+    ap.add_argument("--baseline", action="store_true",
+                    help="navdp / nextdit / rgbd: also time the PyTorch fp32 eager formulation of the same call on the same GPU")
     ap.add_argument("--check-config", action="store_true", help="validate the arguments and exit without loading torch or the runtime")
     a = ap.parse_args()
     if a.check_config:
@@ -143,9 +167,9 @@ def main() -> int:
         return 0
     if a.family is None:
         ap.error("--family is required")
-    global torch, PROFILE
+    global torch, PROFILE, BASELINE
     import torch
-    PROFILE = a.profile
+    PROFILE, BASELINE = a.profile, a.baseline
     if not torch.cuda.is_available():
         print("this example needs a CUDA device")
         return 2
