@@ -309,7 +309,13 @@ bool gemm_small_eligible(const RfGemm* g) {
   if (!small_enabled() || g->w_int8 || g->w_bits || g->row_scale || g->ar_world > 1 || g->ar_publish || g->ss_in || g->ss_out ||
       g->prefetch || g->force_splits || g->force_bn || g->force_swap >= 0 || g->streaming_only)
     return false;
-  if (g->M > 256 || g->N % 8 || g->K % 8 || g->ldx % 8 || g->ldo % 2 || (g->residual && g->ldr % 2)) return false;
+  // Up to 256 rows the weight-size cap below decides.  Up to RF_GEMM_SMALL_MAX_ROWS rows (default 2048) only weights of at
+  // most 1 Mi elements qualify: such GEMMs (ViT-S towers: ~1 000 patch rows, 384-wide) are still bound by launch and
+  // set-up cost, not by tensor throughput (RGB-D encoder 4.07 -> 2.82 ms per call); with SigLIP-sized weights
+  // (1152 x 1152 and up, 768 rows) the tcgen05 kernels win (Pi0.5 vision tower 4.4 ms against 6.2 ms here).
+  static const int max_rows = [] { const char* e = getenv("RF_GEMM_SMALL_MAX_ROWS"); return e ? atoi(e) : 2048; }();
+  if (g->M > 256 && (g->M > max_rows || (long)g->N * g->K * (g->dual_offset > 0 ? 2 : 1) > (1L << 20))) return false;
+  if (g->N % 8 || g->K % 8 || g->ldx % 8 || g->ldo % 2 || (g->residual && g->ldr % 2)) return false;
   if (!g->w_packed && g->ldw % 8) return false;
   const bool dual = g->dual_offset > 0;
   if (dual && !g->w_packed && g->dual_offset % 8) return false;

@@ -780,7 +780,7 @@ def test_gemm_folded_rmsnorm(dt, M, H, I, splits, status):
 
 @pytest.mark.parametrize("dt", DT)
 @pytest.mark.parametrize("M,N,K", [(128, 384, 1536), (128, 1536, 384), (41, 1536, 2048), (50, 1024, 4096), (31, 1024, 1024),
-                                   (7, 72, 136), (130, 200, 72), (256, 512, 640), (1, 384, 384)])
+                                   (7, 72, 136), (130, 200, 72), (256, 512, 640), (1, 384, 384), (1028, 1152, 384), (600, 384, 1536)])
 @pytest.mark.parametrize("packed", [False, True])
 def test_gemm_small_latency_kernel(dt, M, N, K, packed, status, monkeypatch):
     """Shapes the latency-bound kernel takes (few rows, small weight): every epilogue option against fp32 PyTorch, and the
