@@ -499,6 +499,12 @@ def run_qwen3vl(args) -> dict:
     prefill()
     prefill_launches = int(lib.rf_launch_count() - c0)
     ms, clocks = _timed(prefill, max(3, args.ttft_samples), 3)
+    if args.profiler_range:                      # one multimodal prefill for ncu --profile-from-start off
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        prefill()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     prefill()
     c0 = lib.rf_launch_count()
     eng.text.capture(BATCH)

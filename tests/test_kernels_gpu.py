@@ -219,6 +219,59 @@ def test_qk_norm_rope_kv_insert(dt, hd, rot):
         _close(v_pool[page, :, p % 16], v_ref[t], dt)
 
 
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("hd,rot,Hq,Hkv", [(64, 64, 6, 6), (128, 128, 5, 2), (256, 64, 3, 1), (128, 64, 4, 4)])
+@pytest.mark.parametrize("variant", ["plain", "norm", "gemma_rope_first", "mrope_vnorm", "pool"])
+def test_qk_norm_rope_kv_prefill_sized(dt, hd, rot, Hq, Hkv, variant):
+    """Launches of 512 tokens or more take the 16-byte kernel: the same rows through one 640-token launch and through
+    two launches of 320 (below the switch, the scalar kernel) must agree to one rounding step, in every mode."""
+    from rhinoforge_b200.ops import kernels as K_
+    torch.manual_seed(3)
+    T, half = 640, rot // 2
+    W = (Hq + 2 * Hkv) * hd
+    qkv = (torch.randn(T, W, device="cuda") * 0.7).to(dt)
+    axes = 3 if variant == "mrope_vnorm" else 1
+    pos = torch.randint(0, 900, (T, axes), device="cuda", dtype=torch.int32)
+    ang = torch.arange(1024, device="cuda", dtype=torch.float32)[:, None] * (1.0 / 10000 ** (torch.arange(half, device="cuda") / half))[None]
+    kw = dict(pos=pos, cos=ang.cos().contiguous(), sin=ang.sin().contiguous(), rot_dim=rot)
+    if variant in ("norm", "gemma_rope_first", "mrope_vnorm", "pool"):
+        kw.update(q_norm_w=(1 + 0.1 * torch.randn(hd, device="cuda")).to(dt), k_norm_w=(1 + 0.1 * torch.randn(hd, device="cuda")).to(dt))
+    if variant == "gemma_rope_first":
+        kw.update(gemma=True, rope_before_norm=True)
+    if variant == "mrope_vnorm":
+        kw.update(axis_of_freq=torch.randint(0, 3, (half,), device="cuda", dtype=torch.int8), v_norm=True)
+    outs = []
+    pt = torch.randperm(T // 16 + 2, device="cuda").to(torch.int32)[None].contiguous()     # one shuffled page table for both runs
+    for chunks in (1, 2):
+        buf = qkv.clone()
+        q_out = torch.zeros(T, Hq * hd, device="cuda", dtype=dt) if variant == "pool" else None
+        pools = None
+        if variant == "pool":
+            pages = T // 16 + 2
+            pools = (torch.zeros(pages, Hkv, 16, hd, device="cuda", dtype=dt), torch.zeros(pages, Hkv, 16, hd, device="cuda", dtype=dt))
+        n = T // chunks
+        for c in range(chunks):
+            sl = slice(c * n, (c + 1) * n)
+            extra = {}
+            if variant == "pool":
+                extra = dict(k_pool=pools[0], v_pool=pools[1], page_table=pt, seq_of_tok=torch.zeros(n, device="cuda", dtype=torch.int32),
+                             cache_pos=torch.arange(c * n, (c + 1) * n, device="cuda", dtype=torch.int32), q_out=q_out[sl])
+            K_.qk_norm_rope_kv(buf[sl], Hq, Hkv, hd, **{**kw, "pos": pos[sl].contiguous()}, **extra)
+        torch.cuda.synchronize()
+        outs.append((buf, q_out, pools))
+    (b1, q1, p1), (b2, q2, p2) = outs
+
+    def same(x, y):            # one rounding step of the 16-bit type at most (the two kernels may contract their FMAs differently)
+        tol = (2.0 ** -10 if dt == torch.float16 else 2.0 ** -7) * max(1.0, float(y.float().abs().max()))
+        return float((x.float() - y.float()).abs().max()) <= tol
+    assert same(b1, b2)
+    if variant == "pool":
+        assert same(q1, q2) and same(p1[0], p2[0]) and same(p1[1], p2[1])
+        assert float(p1[0].abs().max()) > 0 and float(q1.abs().max()) > 0
+    else:
+        assert not torch.equal(b1, qkv)
+
+
 def test_mrope_axis_select():
     from rhinoforge_b200.ops import kernels as K_
     dt, hd, T = torch.float16, 128, 9
